@@ -1,0 +1,195 @@
+// pybind11 surface of the GPU-resident tier.  Tensors stay owned by Python (torch); this module
+// only sees raw device addresses as integers, so it needs neither torch headers nor torch's ABI.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "launchers.h"
+
+namespace py = pybind11;
+using st::ApplyArgs;
+using st::SelectArgs;
+
+namespace {
+
+template <typename T>
+T* as_ptr(uint64_t v) { return reinterpret_cast<T*>(static_cast<uintptr_t>(v)); }
+
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// One bucket's pre-filled kernel arguments.  Filled once at set-up; `select` and `apply` are then
+// a handful of kernel launches without any per-call marshalling.
+struct BucketHandle {
+  SelectArgs sel;
+  ApplyArgs app;
+  uint32_t randomk_seed = 0x5DEECE66u;
+  int max_ctas_per_source = 148 * 2;
+
+  BucketHandle() {
+    std::memset(&sel, 0, sizeof(sel));
+    std::memset(&app, 0, sizeof(app));
+    sel.timeout_ns = app.timeout_ns = 2000000000ull;
+  }
+
+  void set_data(uint64_t grad, uint64_t grad_tab, uint64_t resid, uint64_t param, uint64_t m, uint64_t v,
+                uint64_t vmax, uint64_t last, uint64_t acc, uint64_t stamp, uint32_t n_total) {
+    sel.grad = as_ptr<float>(grad);
+    sel.grad_tab = as_ptr<float*>(grad_tab);
+    sel.resid = as_ptr<float>(resid);
+    sel.n_total = n_total;
+    app.param = as_ptr<float>(param);
+    app.m = as_ptr<float>(m);
+    app.v = as_ptr<float>(v);
+    app.vmax = as_ptr<float>(vmax);
+    app.last = as_ptr<uint32_t>(last);
+    app.acc = as_ptr<float>(acc);
+    app.stamp = as_ptr<uint32_t>(stamp);
+    app.n_total = n_total;
+  }
+
+  void set_tables(uint64_t segs, uint64_t state, uint64_t work, uint64_t chunks, uint64_t chunk_cnt,
+                  uint64_t chunk_pos, uint64_t hist, uint32_t n_segs, uint32_t n_chunks, uint32_t cap) {
+    sel.segs = as_ptr<const st::SegDesc>(segs);
+    sel.state = as_ptr<st::SegState>(state);
+    sel.work = as_ptr<st::SegWork>(work);
+    sel.chunks = as_ptr<const st::Chunk>(chunks);
+    sel.chunk_cnt = as_ptr<uint32_t>(chunk_cnt);
+    sel.chunk_pos = as_ptr<uint32_t>(chunk_pos);
+    sel.hist = as_ptr<uint32_t>(hist);
+    sel.n_segs = n_segs;
+    sel.n_chunks = n_chunks;
+    app.cap = cap;
+  }
+
+  void set_scratch(uint64_t cand, uint64_t cand_cursor, uint32_t cand_cap) {
+    sel.cand = as_ptr<uint2>(cand);
+    sel.cand_cursor = as_ptr<uint32_t>(cand_cursor);
+    sel.cand_cap = cand_cap;
+  }
+
+  // counters: [sel_epoch, app_epoch, sel_done, app_done] as four u32 words; status: one u32 word
+  void set_control(uint64_t counters, uint64_t status, uint64_t opt, uint64_t weight, uint64_t timeout_ns) {
+    uint32_t* c = as_ptr<uint32_t>(counters);
+    sel.epoch = c + 0;
+    app.epoch = c + 1;
+    sel.done_ctr = c + 2;
+    app.done_ctr = c + 3;
+    sel.status = app.status = as_ptr<uint32_t>(status);
+    app.opt = as_ptr<st::OptState>(opt);
+    app.weight = as_ptr<const float>(weight);
+    sel.timeout_ns = app.timeout_ns = timeout_ns;
+  }
+
+  // Exchange wiring.  recv_local: this rank's receive area [2][world][cap] of (idx,val) pairs.
+  // peer_recv[p]: address of peer p's receive area (p == rank: recv_local).  flags/acks likewise:
+  // flag areas are [2][world] u64 indexed [slot][source]; ack areas are [2][world] u64 indexed
+  // [slot][consumer].
+  void set_comm(int world, int rank, uint64_t recv_local, const std::vector<uint64_t>& peer_recv,
+                uint64_t recv_mc, uint64_t flag_local, const std::vector<uint64_t>& peer_flag,
+                uint64_t ack_local, const std::vector<uint64_t>& peer_ack, bool use_flags, bool use_acks) {
+    if (world < 1 || world > st::kMaxWorld) throw std::runtime_error("world size out of range");
+    if ((int)peer_recv.size() != world || (int)peer_flag.size() != world || (int)peer_ack.size() != world)
+      throw std::runtime_error("peer pointer lists must have one entry per rank");
+    const uint64_t cap = app.cap;
+    sel.world = app.world = world;
+    sel.rank = app.rank = rank;
+    sel.slot_stride = app.slot_stride = (uint64_t)world * cap;
+    sel.flag_slot_stride = world;
+    app.ack_slot_stride = world;
+    for (int p = 0; p < world; ++p) {
+      sel.out[p] = as_ptr<uint2>(peer_recv[p]) + (uint64_t)rank * cap;
+      sel.flag[p] = as_ptr<uint64_t>(peer_flag[p]) + rank;
+      app.ack[p] = as_ptr<uint64_t>(peer_ack[p]) + rank;
+    }
+    sel.out_mc = recv_mc ? as_ptr<uint2>(recv_mc) + (uint64_t)rank * cap : nullptr;
+    app.recv = as_ptr<const uint2>(recv_local);
+    app.flag_local = as_ptr<const uint64_t>(flag_local);
+    sel.ack_local = as_ptr<const uint64_t>(ack_local);
+    sel.use_acks = app.use_acks = use_acks ? 1u : 0u;
+    sel.publish = app.use_flags = use_flags ? 1u : 0u;
+  }
+
+  void set_options(uint32_t compressor, bool zero_grad, bool skip_ef) {
+    sel.compressor = compressor;
+    sel.zero_grad = zero_grad ? 1u : 0u;
+    sel.skip_ef = skip_ef ? 1u : 0u;
+  }
+
+  void select(uint64_t stream) {
+    check(st::launch_select(sel, randomk_seed, as_ptr<CUstream_st>(stream)), "launch_select");
+  }
+  void apply(uint64_t stream) {
+    check(st::launch_apply(app, max_ctas_per_source, as_ptr<CUstream_st>(stream)), "launch_apply");
+  }
+};
+
+py::bytes ipc_get_handle(uint64_t ptr) {
+  cudaIpcMemHandle_t h;
+  check(cudaIpcGetMemHandle(&h, as_ptr<void>(ptr)), "cudaIpcGetMemHandle");
+  return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+}
+
+uint64_t ipc_open_handle(const std::string& raw) {
+  if (raw.size() != sizeof(cudaIpcMemHandle_t)) throw std::runtime_error("bad IPC handle size");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, raw.data(), sizeof(h));
+  void* p = nullptr;
+  check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+  return (uint64_t)(uintptr_t)p;
+}
+
+void ipc_close_handle(uint64_t ptr) { check(cudaIpcCloseMemHandle(as_ptr<void>(ptr)), "cudaIpcCloseMemHandle"); }
+
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "sm_100a kernels of the GPU-resident sparse data-parallel tier";
+  m.attr("MAX_WORLD") = st::kMaxWorld;
+  m.attr("HIST_BINS") = st::kHistBins;
+  m.attr("SENTINEL_IDX") = st::kSentinelIdx;
+  m.attr("SIZEOF_SEG_DESC") = sizeof(st::SegDesc);
+  m.attr("SIZEOF_SEG_STATE") = sizeof(st::SegState);
+  m.attr("SIZEOF_SEG_WORK") = sizeof(st::SegWork);
+  m.attr("SIZEOF_CHUNK") = sizeof(st::Chunk);
+  m.attr("SIZEOF_OPT_STATE") = sizeof(st::OptState);
+
+  py::class_<BucketHandle>(m, "BucketHandle")
+      .def(py::init<>())
+      .def("set_data", &BucketHandle::set_data, py::arg("grad"), py::arg("grad_tab"), py::arg("resid"),
+           py::arg("param"), py::arg("m"), py::arg("v"), py::arg("vmax"), py::arg("last"), py::arg("acc"),
+           py::arg("stamp"), py::arg("n_total"))
+      .def("set_tables", &BucketHandle::set_tables, py::arg("segs"), py::arg("state"), py::arg("work"),
+           py::arg("chunks"), py::arg("chunk_cnt"), py::arg("chunk_pos"), py::arg("hist"), py::arg("n_segs"),
+           py::arg("n_chunks"), py::arg("cap"))
+      .def("set_scratch", &BucketHandle::set_scratch, py::arg("cand"), py::arg("cand_cursor"), py::arg("cand_cap"))
+      .def("set_control", &BucketHandle::set_control, py::arg("counters"), py::arg("status"), py::arg("opt"),
+           py::arg("weight"), py::arg("timeout_ns"))
+      .def("set_comm", &BucketHandle::set_comm, py::arg("world"), py::arg("rank"), py::arg("recv_local"),
+           py::arg("peer_recv"), py::arg("recv_mc"), py::arg("flag_local"), py::arg("peer_flag"),
+           py::arg("ack_local"), py::arg("peer_ack"), py::arg("use_flags"), py::arg("use_acks"))
+      .def("set_options", &BucketHandle::set_options, py::arg("compressor"), py::arg("zero_grad"),
+           py::arg("skip_ef") = false)
+      .def_readwrite("randomk_seed", &BucketHandle::randomk_seed)
+      .def_readwrite("max_ctas_per_source", &BucketHandle::max_ctas_per_source)
+      .def("select", &BucketHandle::select, py::arg("stream"))
+      .def("apply", &BucketHandle::apply, py::arg("stream"));
+
+  m.def("max_abs_diff", [](uint64_t a, uint64_t b, uint64_t n, uint64_t out_bits, uint64_t stream) {
+    check(st::launch_max_abs_diff(as_ptr<const float>(a), as_ptr<const float>(b), n, as_ptr<uint32_t>(out_bits),
+                                  as_ptr<CUstream_st>(stream)), "max_abs_diff");
+  });
+  m.def("peer_copy", [](uint64_t dst, uint64_t src, uint64_t n, uint64_t stream) {
+    check(st::launch_peer_copy(as_ptr<float>(dst), as_ptr<const float>(src), n, as_ptr<CUstream_st>(stream)),
+          "peer_copy");
+  });
+  m.def("ipc_get_handle", &ipc_get_handle);
+  m.def("ipc_open_handle", &ipc_open_handle);
+  m.def("ipc_close_handle", &ipc_close_handle);
+}

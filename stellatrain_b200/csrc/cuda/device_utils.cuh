@@ -1,0 +1,110 @@
+// Device-side primitives shared by the select and apply kernels: system-scope flag accesses,
+// bounded waits, block scans and the stores that push stream entries into peer memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "sparse_types.h"
+
+namespace st {
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ uint64_t ld_acquire_sys_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Spin until *p >= want.  Gives up after timeout_ns or a fixed number of polls, whichever comes
+// first, so that a missing peer can never hang the GPU; the caller records the failure.
+__device__ __forceinline__ bool wait_ge_bounded(const uint64_t* p, uint64_t want, uint64_t timeout_ns) {
+  if (ld_acquire_sys_u64(p) >= want) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    if (ld_acquire_sys_u64(p) >= want) return true;
+    if ((it & 15u) == 15u) {
+      if (global_timer_ns() - t0 > timeout_ns) return false;
+      __nanosleep(256);
+    }
+  }
+  return false;
+}
+
+__device__ __forceinline__ void set_status(uint32_t* status, uint32_t code) {
+  atomicCAS(status, (uint32_t)kOk, code);
+}
+
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
+  return *reinterpret_cast<const volatile uint32_t*>(p);
+}
+
+// One 8-byte store that NVSwitch replicates into every GPU bound to the multicast object.
+__device__ __forceinline__ void multimem_st_pair(uint2* mc_addr, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y))
+               : "memory");
+}
+
+// Store one stream entry into the receive area of every destination.
+__device__ __forceinline__ void emit_entry(const SelectArgs& A, uint64_t slot_off, uint32_t pos,
+                                           uint32_t idx, float val) {
+  const uint2 e = make_uint2(idx, __float_as_uint(val));
+  if (A.out_mc != nullptr) {
+    multimem_st_pair(A.out_mc + slot_off + pos, e);
+  } else {
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p) {
+      if (p < A.world) A.out[p][slot_off + pos] = e;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t warp_incl_scan(uint32_t v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    uint32_t o = __shfl_up_sync(0xffffffffu, v, d);
+    if (lane >= d) v += o;
+  }
+  return v;
+}
+
+// Exclusive scan over the CTA in thread order.  `total` receives the CTA sum.  `s` must hold
+// blockDim.x/32 + 1 words.  Contains two barriers; all threads of the CTA must call it.
+__device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* s, uint32_t& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const uint32_t incl = warp_incl_scan(v);
+  __syncthreads();  // protects s against a previous call
+  if (lane == 31) s[warp] = incl;
+  __syncthreads();
+  uint32_t warp_off = 0, sum = 0;
+  for (int w = 0; w < nwarp; ++w) {
+    const uint32_t x = s[w];
+    if (w < warp) warp_off += x;
+    sum += x;
+  }
+  total = sum;
+  return warp_off + incl - v;
+}
+
+__device__ __forceinline__ uint32_t block_max_u32(uint32_t v, uint32_t* s) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, d));
+  __syncthreads();
+  if (lane == 0) s[warp] = v;
+  __syncthreads();
+  uint32_t r = 0;
+  for (int w = 0; w < nwarp; ++w) r = max(r, s[w]);
+  return r;
+}
+
+}  // namespace st

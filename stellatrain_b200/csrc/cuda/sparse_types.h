@@ -1,0 +1,142 @@
+// Shared host/device plain-data types of the GPU-resident sparse data-parallel path.
+//
+// One "bucket" is a flat fp32 range that holds several parameter tensors ("segments"), each
+// starting on a 16-element (64-byte) boundary and zero-padded to a multiple of 16.  All per-tensor
+// semantics of the reference engine (k per tensor: backend/src/engine/modules/compress.cpp:44-52,
+// threshold per tensor: backend/src/compress/thresholdv16.cpp:81-97) live in the segment tables.
+#pragma once
+#include <stdint.h>
+
+namespace st {
+
+constexpr int kMaxWorld = 16;          // peers addressable by one kernel launch
+constexpr int kHistBits = 11;          // first radix digit: exponent + 3 mantissa bits of |x|
+constexpr int kHistBins = 1 << kHistBits;
+constexpr int kHistShift = 31 - kHistBits;  // 20 low bits are resolved on the candidate set
+constexpr uint32_t kSentinelIdx = 0xFFFFFFFFu;  // "no entry" marker in an (idx,val) stream
+
+enum Compressor : uint32_t { kTopk = 0, kThresholdv = 1, kThresholdv16 = 2, kRandomk = 3 };
+enum SegMode : uint32_t { kModeNone = 0, kModeInOrder = 1, kModeTop = 2 };
+
+// Status word written by kernels, read by the host. 0 means success; the first error wins.
+enum Status : uint32_t {
+  kOk = 0,
+  kTimeoutAck = 1,    // a peer did not acknowledge the previous use of a receive slot in time
+  kTimeoutFlag = 2,   // a peer's stream did not arrive in time
+  kBadIndex = 3,      // a received index is outside the bucket
+  kBadCandidate = 4,  // candidate scratch exhausted (cannot happen with a correctly sized scratch)
+  kBadSize = 5,       // request exceeds a compiled-in limit
+};
+
+struct SegDesc {          // static per segment (re-uploaded when the compression ratio changes)
+  uint32_t off;           // first element inside the bucket, multiple of 16
+  uint32_t n;             // valid elements
+  uint32_t n_pad;         // n rounded up to 16
+  uint32_t k;             // entries this rank emits for the segment
+  uint32_t out_off;       // position of the segment's first entry in the bucket's stream
+  uint32_t chunk_begin;   // first chunk of the segment in the chunk table
+  uint32_t chunk_cnt;     // number of chunks
+  uint32_t reserved;
+};
+
+struct SegState {         // persistent per segment, saved in checkpoints
+  float tau;              // threshold (element magnitude or 16-block L1 norm)
+  float tau_inc;          // additive step of threshold-v16
+  uint32_t inited;        // 0 until the first threshold was measured
+  uint32_t reserved;
+};
+
+struct SegWork {          // scratch per segment, valid within one select
+  uint32_t mode;          // SegMode
+  uint32_t thr_bin;       // histogram bin that contains the k-th largest key
+  uint32_t k_rem;         // items still to be taken from that bin
+  uint32_t cand_off;      // start of the segment's candidate range in the candidate scratch
+  uint32_t cand_cnt;      // candidates appended so far
+  uint32_t out_cursor;    // items appended to the stream so far (unordered mode)
+  uint32_t found;         // items over the threshold (ordered mode)
+  uint32_t max_bits;      // running max |x| of the segment as float bits (reset by plan)
+  uint32_t max_saved;     // max |x| of the current select
+  uint32_t tau_bits;      // threshold the current select was counted with
+  uint32_t reserved[2];
+};
+
+struct Chunk {            // unit of work of the streaming passes; never spans two segments
+  uint32_t seg;
+  uint32_t start;         // bucket offset, multiple of 16
+  uint32_t len;           // elements, multiple of 16
+  uint32_t reserved;
+};
+
+// Hyper-parameters and counters of the sparse optimisers, resident on the device so that a step
+// captured in a CUDA graph sees later changes (learning-rate schedules, step counters).
+struct OptState {
+  float lr, momentum, dampening, weight_decay;
+  float beta1, beta2, eps, reserved0;
+  uint32_t nesterov, maximize, amsgrad, smart_momentum;
+  uint32_t tick;          // calls so far + 1 (Adam bias correction; reference optim/adam.cpp:30-43)
+  uint32_t first;         // 1 until the first SGD call happened (reference optim/sgd.cpp:41-50)
+  uint32_t kind;          // 0 = SGD, 1 = Adam
+  uint32_t reserved1;
+};
+
+struct SelectArgs {
+  float* grad;                 // flat gradients of the bucket (used when grad_tab is null)
+  float* const* grad_tab;      // optional per-segment gradient pointers
+  float* resid;                // error-feedback residual, flat
+  const SegDesc* segs;
+  SegState* state;
+  SegWork* work;
+  const Chunk* chunks;
+  uint32_t* chunk_cnt;         // items over the threshold per chunk
+  uint32_t* chunk_pos;         // exclusive prefix of chunk_cnt inside the segment
+  uint32_t* hist;              // [n_segs][kHistBins]
+  uint2* cand;                 // candidate scratch: (item id, key)
+  uint32_t* cand_cursor;       // bump pointer into cand
+  uint32_t cand_cap;
+  uint32_t n_segs, n_chunks, n_total;
+  uint32_t compressor;         // Compressor
+  uint32_t zero_grad;          // write zeros over consumed gradients
+  uint32_t skip_ef;            // 1: the residual already holds g + r (re-selection), skip the add
+  // exchange
+  int32_t world, rank;
+  uint2* out[kMaxWorld];       // per destination: its receive area for source `rank`, slot 0
+  uint2* out_mc;               // multicast alias of the same area (NVLS), or null
+  uint64_t slot_stride;        // entries between slot 0 and slot 1 of a receive area
+  uint64_t* flag[kMaxWorld];   // per destination: its arrival flag for source `rank`, slot 0
+  uint64_t flag_slot_stride;   // u64 words between the flags of slot 0 and slot 1
+  const uint64_t* ack_local;   // [2][world] acknowledgements written by the destinations
+  uint32_t use_acks;           // wait for acknowledgements before overwriting a slot
+  uint32_t publish;            // publish arrival flags when the stream is complete
+  uint32_t* epoch;             // select epoch of this bucket (starts at 1)
+  uint32_t* done_ctr;          // CTA completion counter of the last kernel of the chain
+  uint32_t* status;            // Status
+  uint64_t timeout_ns;
+};
+
+struct ApplyArgs {
+  const uint2* recv;           // [2 slots][world][cap] received streams (local memory)
+  uint64_t slot_stride;        // entries per slot (= world * cap)
+  uint32_t cap;                // entries per source
+  uint32_t n_total;            // elements in the bucket
+  int32_t world, rank;
+  const uint64_t* flag_local;  // [2][world] arrival flags written by the sources
+  uint64_t* ack[kMaxWorld];    // per source: its acknowledgement word for consumer `rank`, slot 0
+  uint64_t ack_slot_stride;
+  uint32_t use_flags;          // wait on arrival flags (0 when a library collective filled recv)
+  uint32_t use_acks;
+  const float* weight;         // [world] weight of each source in the merge (default 1/world)
+  float* acc;                  // dense accumulator, zero outside a scatter/apply pair
+  uint32_t* stamp;             // last epoch at which an element was updated
+  float* param;
+  float* m;                    // momentum buffer (SGD) or first moment (Adam)
+  float* v;                    // second moment (Adam)
+  float* vmax;                 // AMSGrad maximum, or null
+  uint32_t* last;              // smart momentum: step of the last touch, or null
+  OptState* opt;
+  uint32_t* epoch;             // apply epoch of this bucket (starts at 1)
+  uint32_t* done_ctr;
+  uint32_t* status;
+  uint64_t timeout_ns;
+};
+
+}  // namespace st

@@ -1,0 +1,279 @@
+"""Device state of one bucket and the thin Python handle that launches its kernels.
+
+Everything the reference keeps per tensor on the CPU lives here per bucket on the GPU: the error-feedback
+residual (backend/src/engine/core.h:63), the thresholds of threshold-v / threshold-v16
+(backend/src/compress/thresholdv16.h:13-14), the optimiser state (backend/src/optim/sgd.h:15-18,
+backend/src/optim/adam.h:15-18) and the master parameters (backend/src/engine/core.cpp:807-830).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import buckets as B
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "timeout waiting for a peer's acknowledgement",
+    2: "timeout waiting for a peer's stream",
+    3: "received index outside the bucket",
+    4: "candidate scratch exhausted",
+    5: "size beyond a compiled-in limit",
+}
+
+
+class SparseStepError(RuntimeError):
+    """A kernel of the sparse path reported a non-zero status (for example a peer that never pushed)."""
+
+    def __init__(self, bucket: int, code: int):
+        super().__init__(f"bucket {bucket}: {STATUS_NAMES.get(code, 'unknown error')} (status {code})")
+        self.bucket = bucket
+        self.code = code
+
+
+def _ext():
+    from .. import _build
+
+    return _build.load_extension("_C")
+
+
+def _dev_bytes(arr: np.ndarray, device: torch.device) -> torch.Tensor:
+    raw = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
+    return torch.from_numpy(raw.copy()).to(device)
+
+
+@dataclass
+class Wiring:
+    """Where a bucket's streams go: addresses of every rank's receive area, flags and acks."""
+
+    world: int
+    rank: int
+    recv_local: torch.Tensor                 # uint8 view holding [2][world][cap] (idx,val) pairs
+    peer_recv: Sequence[int]
+    flag_local: Optional[torch.Tensor]       # int64 [2][world]
+    peer_flag: Sequence[int]
+    ack_local: Optional[torch.Tensor]        # int64 [2][world]
+    peer_ack: Sequence[int]
+    recv_mc: int = 0
+    use_flags: bool = False
+    use_acks: bool = False
+
+
+class GpuBucket:
+    def __init__(
+        self,
+        index: int,
+        layout: B.BucketLayout,
+        device: torch.device,
+        compressor: str = "thresholdv16",
+        ratio: float = 0.99,
+        world: int = 1,
+        rank: int = 0,
+        optimizer: str = "sgd",
+        amsgrad: bool = False,
+        smart_momentum: bool = False,
+        min_ratio: Optional[float] = None,
+        scratch: Optional["CandidateScratch"] = None,
+        timeout_s: float = 2.0,
+        divide_k_by_world: bool = True,
+    ) -> None:
+        self.index = index
+        self.layout = layout
+        self.device = device
+        self.world, self.rank = world, rank
+        self.k_world = world if divide_k_by_world else 1
+        self.compressor = compressor
+        self.ratio = ratio
+        self.min_ratio = ratio if min_ratio is None else min(min_ratio, ratio)
+        self.optimizer = optimizer
+        self.timeout_ns = int(timeout_s * 1e9)
+        n = layout.n_total
+        f32 = dict(dtype=torch.float32, device=device)
+        self.grad = torch.zeros(n, **f32)
+        self.resid = torch.zeros(n, **f32)
+        self.param = torch.zeros(n, **f32)
+        self.acc = torch.zeros(n, **f32)
+        self.stamp = torch.zeros(n, dtype=torch.int32, device=device)
+        self.m = torch.zeros(n, **f32)
+        self.v = torch.zeros(n, **f32) if optimizer == "adam" else None
+        self.vmax = torch.zeros(n, **f32) if (optimizer == "adam" and amsgrad) else None
+        self.last = torch.zeros(n, dtype=torch.int32, device=device) if smart_momentum else None
+
+        layout.set_ratio(ratio, self.k_world)
+        self.cap_max = max(layout.max_cap(self.min_ratio, self.k_world), layout.cap, 1)
+        n_segs = len(layout.segments)
+        self.segs = _dev_bytes(layout.seg_table(), device)
+        self.state = torch.zeros(n_segs * B.SEG_STATE_DTYPE.itemsize, dtype=torch.uint8, device=device)
+        self.work = torch.zeros(n_segs * B.SEG_WORK_WORDS, dtype=torch.int32, device=device)
+        self.chunks = _dev_bytes(layout.chunk_table(), device)
+        self.chunk_cnt = torch.zeros(layout.n_chunks, dtype=torch.int32, device=device)
+        self.chunk_pos = torch.zeros(layout.n_chunks, dtype=torch.int32, device=device)
+        self.hist = torch.zeros(n_segs * 2048, dtype=torch.int32, device=device)
+        self.counters = torch.tensor([1, 1, 0, 0], dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.weight = torch.full((world,), 1.0 / world, **f32)
+        opt = np.zeros(1, dtype=B.OPT_STATE_DTYPE)
+        opt["lr"] = 1e-3
+        opt["beta1"], opt["beta2"], opt["eps"] = 0.9, 0.999, 1e-8
+        opt["tick"], opt["first"] = 1, 1
+        opt["kind"] = 1 if optimizer == "adam" else 0
+        opt["amsgrad"] = 1 if amsgrad else 0
+        opt["smart_momentum"] = 1 if smart_momentum else 0
+        self._opt_host = opt
+        self.opt = _dev_bytes(opt, device)
+        self.scratch = scratch if scratch is not None else CandidateScratch(device)
+        self.scratch.reserve(n)
+        self.handle = _ext().BucketHandle()
+        self.wiring: Optional[Wiring] = None
+        self.zero_grad_in_select = True
+        self._bind()
+
+    # ------------------------------------------------------------------ wiring
+    def _ptr(self, t: Optional[torch.Tensor]) -> int:
+        return 0 if t is None else t.data_ptr()
+
+    def _bind(self) -> None:
+        h, L = self.handle, self.layout
+        h.set_data(
+            grad=self.grad.data_ptr(), grad_tab=0, resid=self.resid.data_ptr(), param=self.param.data_ptr(),
+            m=self.m.data_ptr(), v=self._ptr(self.v), vmax=self._ptr(self.vmax), last=self._ptr(self.last),
+            acc=self.acc.data_ptr(), stamp=self.stamp.data_ptr(), n_total=L.n_total,
+        )
+        h.set_tables(
+            segs=self.segs.data_ptr(), state=self.state.data_ptr(), work=self.work.data_ptr(),
+            chunks=self.chunks.data_ptr(), chunk_cnt=self.chunk_cnt.data_ptr(), chunk_pos=self.chunk_pos.data_ptr(),
+            hist=self.hist.data_ptr(), n_segs=len(L.segments), n_chunks=L.n_chunks, cap=L.cap,
+        )
+        self.scratch.bind(h)
+        h.set_control(
+            counters=self.counters.data_ptr(), status=self.status.data_ptr(), opt=self.opt.data_ptr(),
+            weight=self.weight.data_ptr(), timeout_ns=self.timeout_ns,
+        )
+        h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False)
+        if self.wiring is not None:
+            self._apply_wiring()
+
+    def recv_bytes(self) -> int:
+        """Bytes of receive area one rank needs for this bucket (two slots, all sources)."""
+        return 2 * self.world * self.cap_max * 8
+
+    def wire_local(self) -> None:
+        """Single-process wiring: the stream goes to this GPU's own receive area, stream order is
+        the only synchronisation."""
+        recv = torch.zeros(self.recv_bytes(), dtype=torch.uint8, device=self.device)
+        self.wire(Wiring(1, 0, recv, [recv.data_ptr()], None, [0], None, [0]))
+
+    def wire(self, w: Wiring) -> None:
+        self.wiring = w
+        self._apply_wiring()
+
+    def _apply_wiring(self) -> None:
+        w = self.wiring
+        self.handle.set_comm(
+            world=w.world, rank=w.rank, recv_local=w.recv_local.data_ptr(), peer_recv=list(w.peer_recv),
+            recv_mc=w.recv_mc, flag_local=self._ptr(w.flag_local), peer_flag=list(w.peer_flag),
+            ack_local=self._ptr(w.ack_local), peer_ack=list(w.peer_ack), use_flags=w.use_flags,
+            use_acks=w.use_acks,
+        )
+
+    # ------------------------------------------------------------------ configuration
+    def set_ratio(self, ratio: float) -> None:
+        """Change the compression ratio. The caller guarantees that no select/apply is in flight."""
+        if ratio < self.min_ratio - 1e-12:
+            raise ValueError(f"ratio {ratio} is below the provisioned minimum {self.min_ratio}")
+        self.ratio = ratio
+        self.layout.set_ratio(ratio, self.k_world)
+        self.segs.copy_(_dev_bytes(self.layout.seg_table(), self.device))
+        self._bind()
+
+    def set_optimizer_options(self, **kw) -> None:
+        """Update hyper-parameters on the device; counters (tick, first) are left untouched."""
+        for k, v in kw.items():
+            if k not in self._opt_host.dtype.names or k in ("tick", "first", "kind"):
+                raise KeyError(k)
+            self._opt_host[k] = v
+        raw = np.ascontiguousarray(self._opt_host).view(np.uint8).reshape(-1)[:48].copy()
+        self.opt[:48].copy_(torch.from_numpy(raw), non_blocking=False)
+
+    def set_weights(self, weights: Sequence[float]) -> None:
+        self.weight.copy_(torch.tensor(list(weights), dtype=torch.float32))
+
+    # ------------------------------------------------------------------ execution
+    def select(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        self.handle.select(s.cuda_stream)
+
+    def apply(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        self.handle.apply(s.cuda_stream)
+
+    def check_status(self) -> None:
+        code = int(self.status.item())
+        if code != 0:
+            raise SparseStepError(self.index, code)
+
+    # ------------------------------------------------------------------ views and state
+    def view(self, buf: torch.Tensor, seg: int) -> torch.Tensor:
+        s = self.layout.segments[seg]
+        return buf[s.off : s.off + s.numel]
+
+    def stream_of(self, slot: int, src: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """(idx, val) of one received stream, for tests and debugging."""
+        cap = self.layout.cap
+        w = self.wiring
+        pairs = w.recv_local.view(torch.int32)[: 2 * w.world * cap * 2].view(2, w.world, cap, 2)
+        e = pairs[slot, src]
+        return e[:, 0].clone(), e[:, 1].clone().view(torch.float32)
+
+    def seg_state(self) -> np.ndarray:
+        return self.state.cpu().numpy().view(B.SEG_STATE_DTYPE).copy()
+
+    def state_dict(self) -> dict:
+        d = {
+            "resid": self.resid, "param": self.param, "m": self.m, "seg_state": self.state,
+            "opt": self.opt, "counters": self.counters, "stamp": self.stamp, "ratio": self.ratio,
+        }
+        for k in ("v", "vmax", "last"):
+            t = getattr(self, k)
+            if t is not None:
+                d[k] = t
+        return {k: (v.detach().cpu().clone() if torch.is_tensor(v) else v) for k, v in d.items()}
+
+    def load_state_dict(self, d: dict) -> None:
+        if abs(d["ratio"] - self.ratio) > 1e-12:
+            self.set_ratio(d["ratio"])
+        for k in ("resid", "param", "m", "v", "vmax", "last", "stamp", "opt", "counters"):
+            t = getattr(self, k)
+            if t is not None and k in d:
+                t.copy_(d[k])
+        self.state.copy_(d["seg_state"])
+        self._opt_host = self.opt.cpu().numpy().view(B.OPT_STATE_DTYPE).copy()
+        self.acc.zero_()
+        self.grad.zero_()
+
+
+class CandidateScratch:
+    """Scratch for the undecided items of the threshold bin, shared by all buckets that run their
+    selects on one stream (worst case: every item of the largest bucket)."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.cap = 0
+        self.buf: Optional[torch.Tensor] = None
+        self.cursor = torch.zeros(1, dtype=torch.int32, device=device)
+        self._bound: list = []
+
+    def reserve(self, items: int) -> None:
+        if items > self.cap:
+            self.cap = items
+            self.buf = torch.empty(items * 2, dtype=torch.int32, device=self.device)
+            for h in self._bound:
+                self.bind(h, remember=False)
+
+    def bind(self, handle, remember: bool = True) -> None:
+        handle.set_scratch(self.buf.data_ptr(), self.cursor.data_ptr(), self.cap)
+        if remember:
+            self._bound.append(handle)

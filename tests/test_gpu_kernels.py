@@ -1,0 +1,220 @@
+"""sm_100a select/apply kernels against the plain-PyTorch oracle, one GPU."""
+import numpy as np
+import pytest
+import torch
+
+from stellatrain_b200.ops import oracle as O
+from stellatrain_b200.parallel import buckets as B
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 15, 16, 17, 1000, 4096, 65535, 65536, 70001, 300000]
+
+
+def make_bucket(compressor, ratio, optimizer="sgd", sizes=SIZES, chunk=4096, **kw):
+    from stellatrain_b200.parallel.gpu_bucket import GpuBucket
+
+    dev = torch.device("cuda:0")
+    layout = B.BucketLayout([f"t{i}" for i in range(len(sizes))], sizes, chunk_elems=chunk)
+    b = GpuBucket(0, layout, dev, compressor=compressor, ratio=ratio, optimizer=optimizer, **kw)
+    b.wire_local()
+    return b
+
+
+def seg_slices(b):
+    return [(s, slice(s.off, s.off + s.numel), slice(s.off, s.off + s.n_pad)) for s in b.layout.segments]
+
+
+def read_stream(b, epoch):
+    idx, val = b.stream_of(epoch & 1, 0)
+    return idx.cpu().numpy().view(np.uint32).astype(np.int64), val.cpu()
+
+
+def oracle_states(b):
+    st = b.seg_state()
+    return [O.ThresholdState(float(s["tau"]), float(s["tau_inc"]), bool(s["inited"])) for s in st]
+
+
+def fill_grads(b, gen, scale=1e-2, mode="normal"):
+    for s, sl, _ in seg_slices(b):
+        if mode == "normal":
+            g = torch.randn(s.numel, generator=gen, device="cuda") * scale
+        elif mode == "ties":
+            g = torch.randint(-3, 4, (s.numel,), generator=gen, device="cuda").float() * scale
+        elif mode == "zero":
+            g = torch.zeros(s.numel, device="cuda")
+        b.grad[sl] = g
+
+
+@pytest.mark.parametrize("compressor", ["topk", "thresholdv", "thresholdv16"])
+@pytest.mark.parametrize("mode", ["normal", "ties", "zero"])
+def test_select_matches_oracle(compressor, mode):
+    torch.manual_seed(0)
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    b = make_bucket(compressor, 0.99)
+    resid_ref = torch.zeros_like(b.resid)
+    steps = 5 if mode == "normal" else 3
+    for step in range(steps):
+        epoch = step + 1
+        fill_grads(b, gen, mode=mode if not (mode == "zero" and step == 1) else "normal")
+        grad = b.grad.clone()
+        states = oracle_states(b)
+        b.select()
+        torch.cuda.synchronize()
+        b.check_status()
+        assert float(b.grad.abs().max()) == 0.0, "consumed gradients must be zeroed"
+        idx_all, val_all = read_stream(b, epoch)
+        new_states = b.seg_state()
+        for si, (s, sl, slp) in enumerate(seg_slices(b)):
+            k = s.k
+            got_idx = idx_all[s.out_off : s.out_off + k]
+            got_val = val_all[s.out_off : s.out_off + k]
+            st = states[si]
+            pad = compressor == "thresholdv16"
+            g = grad[slp] if pad else grad[sl]
+            r = resid_ref[slp] if pad else resid_ref[sl]
+            want_idx, want_val, new_r = O.compress_step(compressor, g, r, k, st)
+            want_idx = want_idx.cpu().numpy() + s.off
+            valid = got_idx != O.SENTINEL
+            order_g = np.argsort(got_idx[valid], kind="stable")
+            order_w = np.argsort(want_idx, kind="stable")
+            assert np.array_equal(got_idx[valid][order_g], want_idx[order_w]), (compressor, mode, step, s.name)
+            assert torch.equal(got_val[torch.from_numpy(valid)][torch.from_numpy(order_g)],
+                               want_val.cpu()[torch.from_numpy(order_w)])
+            if pad:
+                resid_ref[slp] = new_r
+            else:
+                resid_ref[sl] = new_r
+            if compressor != "topk":
+                assert bool(new_states[si]["inited"])
+                assert new_states[si]["tau"] == pytest.approx(st.tau, rel=1e-5, abs=1e-30)
+        assert torch.equal(b.resid, resid_ref), (compressor, mode, step)
+
+
+def test_select_drops_nan():
+    b = make_bucket("topk", 0.9, sizes=[1000, 5000])
+    g = torch.randn(b.layout.n_total, device="cuda")
+    g[3] = float("nan")
+    g[1500] = float("nan")
+    b.grad.copy_(g)
+    # padding must stay zero
+    for s, sl, slp in seg_slices(b):
+        b.grad[s.off + s.numel : s.off + s.n_pad] = 0
+    b.select()
+    torch.cuda.synchronize()
+    b.check_status()
+    assert not torch.isnan(b.resid).any()
+    idx, val = read_stream(b, 1)
+    assert 3 not in idx and 1500 not in idx
+    assert not torch.isnan(val).any()
+
+
+@pytest.mark.parametrize("optimizer", ["sgd", "adam"])
+def test_apply_matches_oracle(optimizer):
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    b = make_bucket("topk", 0.95, optimizer=optimizer)
+    if optimizer == "sgd":
+        b.set_optimizer_options(lr=0.1, momentum=0.9, weight_decay=1e-4)
+        cfg, st = O.SGDConfig(lr=0.1, momentum=0.9, weight_decay=1e-4), O.SGDState()
+    else:
+        b.set_optimizer_options(lr=1e-3, weight_decay=1e-2)
+        cfg, st = O.AdamConfig(lr=1e-3, weight_decay=1e-2), O.AdamState()
+    b.param.copy_(torch.randn(b.layout.n_total, generator=gen, device="cuda"))
+    p_ref = b.param.clone()
+    for step in range(4):
+        epoch = step + 1
+        fill_grads(b, gen)
+        b.select()
+        b.apply()
+        torch.cuda.synchronize()
+        b.check_status()
+        idx, val = read_stream(b, epoch)
+        g, touched = O.merge_streams(b.layout.n_total, [(torch.from_numpy(idx).cuda(), val.cuda())], [1.0])
+        if optimizer == "sgd":
+            O.sparse_sgd(p_ref, g, touched, cfg, st)
+        else:
+            O.sparse_adam(p_ref, g, touched, cfg, st)
+        torch.testing.assert_close(b.param, p_ref, rtol=2e-5, atol=1e-6)
+        assert float(b.acc.abs().max()) == 0.0, "accumulator must be clean after apply"
+    if optimizer == "sgd":
+        torch.testing.assert_close(b.m, st.b, rtol=2e-5, atol=1e-7)
+    else:
+        torch.testing.assert_close(b.m, st.m, rtol=2e-5, atol=1e-7)
+        torch.testing.assert_close(b.v, st.v, rtol=2e-5, atol=1e-10)
+
+
+def test_apply_options_nesterov_smart_amsgrad():
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    b = make_bucket("topk", 0.9, optimizer="sgd", sizes=[5000, 33], smart_momentum=True)
+    b.set_optimizer_options(lr=0.05, momentum=0.8, nesterov=1, dampening=0.1)
+    cfg, st = O.SGDConfig(lr=0.05, momentum=0.8, nesterov=True, dampening=0.1, smart_momentum=True), O.SGDState()
+    p_ref = b.param.clone()
+    for step in range(4):
+        fill_grads(b, gen)
+        b.select(); b.apply()
+        torch.cuda.synchronize()
+        idx, val = read_stream(b, step + 1)
+        g, touched = O.merge_streams(b.layout.n_total, [(torch.from_numpy(idx).cuda(), val.cuda())], [1.0])
+        O.sparse_sgd(p_ref, g, touched, cfg, st)
+        torch.testing.assert_close(b.param, p_ref, rtol=1e-4, atol=1e-6)
+
+    b = make_bucket("topk", 0.9, optimizer="adam", sizes=[5000, 33], amsgrad=True)
+    b.set_optimizer_options(lr=1e-2, maximize=1)
+    cfg, st = O.AdamConfig(lr=1e-2, amsgrad=True, maximize=True), O.AdamState()
+    p_ref = b.param.clone()
+    for step in range(4):
+        fill_grads(b, gen)
+        b.select(); b.apply()
+        torch.cuda.synchronize()
+        idx, val = read_stream(b, step + 1)
+        g, touched = O.merge_streams(b.layout.n_total, [(torch.from_numpy(idx).cuda(), val.cuda())], [1.0])
+        O.sparse_adam(p_ref, g, touched, cfg, st)
+        torch.testing.assert_close(b.param, p_ref, rtol=1e-4, atol=1e-6)
+
+
+def test_randomk_stream_is_valid():
+    b = make_bucket("randomk", 0.9, sizes=[1000, 4096, 17])
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    fill_grads(b, gen)
+    grad = b.grad.clone()
+    b.select()
+    torch.cuda.synchronize()
+    b.check_status()
+    idx, val = read_stream(b, 1)
+    for s, sl, _ in seg_slices(b):
+        i = idx[s.out_off : s.out_off + s.k]
+        assert len(np.unique(i)) == s.k
+        assert (i >= s.off).all() and (i < s.off + s.numel).all()
+        assert torch.equal(val[s.out_off : s.out_off + s.k], grad[torch.from_numpy(i).cuda()].cpu())
+    assert float(b.resid[torch.from_numpy(idx).cuda()].abs().max()) == 0.0
+
+
+def test_change_ratio_between_steps():
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    b = make_bucket("topk", 0.99, sizes=[20000, 300], min_ratio=0.9)
+    fill_grads(b, gen); b.select(); b.apply(); torch.cuda.synchronize(); b.check_status()
+    cap0 = b.layout.cap
+    b.set_ratio(0.9)
+    assert b.layout.cap > cap0
+    fill_grads(b, gen)
+    a = b.grad + b.resid
+    b.select(); torch.cuda.synchronize(); b.check_status()
+    idx, val = read_stream(b, 2)
+    s = b.layout.segments[0]
+    want = O.select_topk(a[: s.numel], s.k).cpu().numpy()
+    assert np.array_equal(np.sort(idx[: s.k]), np.sort(want))
+
+
+def test_peer_copy_and_max_abs_diff():
+    from stellatrain_b200 import _build
+
+    C = _build.load_extension("_C")
+    a = torch.randn(4096, device="cuda")
+    bb = torch.empty_like(a)
+    s = torch.cuda.current_stream().cuda_stream
+    C.peer_copy(bb.data_ptr(), a.data_ptr(), a.numel(), s)
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bb[17] += 0.5
+    C.max_abs_diff(a.data_ptr(), bb.data_ptr(), a.numel(), out.data_ptr(), s)
+    torch.cuda.synchronize()
+    assert out.view(torch.float32).item() == pytest.approx(0.5, rel=1e-6)
