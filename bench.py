@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-152 sparse data-parallel training throughput (images/s) on N B200s.
+
+Configuration (the reference's smoke workload shape, backend/test/test_end_to_end.py:21-52, at the
+baseline's operating point): torchvision ResNet-152 with a 100-class head, fp32, batch 32 per GPU,
+synthetic 3x224x224 N(0,1) images with uniform labels, threshold-v16 compression keeping 1 % of the
+gradient entries with error feedback, sparse Adam lr 1e-3, bounded staleness 1, random-init weights.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+Rank 0 prints ONE JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with inputs already
+on the device; ``e2e`` is the same loop through the public API with, every step, the host-to-device copy
+of the batch from pinned memory and a device-to-host read of the loss inside the timed region.
+Other arms: ``--impl reference`` (the unmodified reference; not installable here, prints why),
+``--impl nccl_sparse`` (same kernels, streams moved by ncclAllGather) and ``--impl ddp`` (dense
+all-reduce + torch.optim.Adam) as library baselines.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REFERENCE_UNAVAILABLE = (
+    "reference is a CMake project without setup.py/pyproject.toml: `pip install --no-index "
+    "--no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref /root/reference` fails with "
+    "\"Neither 'setup.py' nor 'pyproject.toml' found\"; it also ships no GPU kernels and no NCCL path"
+)
+
+
+def parse_args() -> argparse.Namespace:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_sparse", "ddp", "dense_single"])
+    ap.add_argument("--model", default="resnet152")
+    ap.add_argument("--batch", type=int, default=32, help="per-GPU batch size")
+    ap.add_argument("--num-classes", type=int, default=100)
+    ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--compressor", default="thresholdv16")
+    ap.add_argument("--ratio", type=float, default=0.99, help="fraction of gradient entries dropped")
+    ap.add_argument("--optimizer", default="adam")
+    ap.add_argument("--lr", type=float, default=1e-3)
+    ap.add_argument("--staleness", type=int, default=1)
+    ap.add_argument("--bucket-mb", type=float, default=32.0)
+    ap.add_argument("--graph", type=int, default=0, help="capture the training step in a CUDA graph")
+    ap.add_argument("--channels-last", type=int, default=0)
+    ap.add_argument("--amp", default="none", choices=["none", "bf16"])
+    ap.add_argument("--no-multicast", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); smax.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return
+
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import stellatrain_b200 as st
+    from stellatrain_b200.models.registry import build_model, is_language_model, synthetic_batch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+        args.gpus = world
+    master_addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    master_port = int(os.environ.get("MASTER_PORT", "29500"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    torch.manual_seed(1234)
+    torch.backends.cudnn.benchmark = True
+
+    lm = is_language_model(args.model)
+    model = build_model(args.model, args.num_classes).to(dev)
+    if args.channels_last and not lm:
+        model = model.to(memory_format=torch.channels_last)
+    n_params = sum(p.numel() for p in model.parameters())
+
+    engine = None
+    opt = None
+    if args.impl in ("ours", "nccl_sparse"):
+        st.configure(master_addr, master_port, 1, 0, os.getpid(), world, rank, args.compressor, 1,
+                     staleness=args.staleness, transport=("nccl" if args.impl == "nccl_sparse" else None))
+        st.configure_compression_ratio(args.ratio)
+        st.set_optimizer(args.optimizer)
+        st.configure_optimizer("lr", args.lr)
+        st.state().engine_cfg.bucket_mb = args.bucket_mb
+        st.state().engine_cfg.multicast = not args.no_multicast
+        net = st.FasterDpModelWrapper(model, sequential=False)
+        net._ensure_engine()
+        engine = net.engine
+    else:
+        if world > 1:
+            dist.init_process_group("nccl", init_method=f"tcp://{master_addr}:{master_port}", world_size=world,
+                                    rank=rank, device_id=dev)
+        net = model
+        if args.impl == "ddp" and world > 1:
+            net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True)
+        opt = (torch.optim.Adam(model.parameters(), lr=args.lr) if args.optimizer == "adam"
+               else torch.optim.SGD(model.parameters(), lr=args.lr, momentum=0.9))
+
+    gen = torch.Generator().manual_seed(100 + rank)
+    n_host = 4
+    host_batches = []
+    for _ in range(n_host):
+        x, y = synthetic_batch(args.model, args.batch, args.num_classes, args.seq_len, generator=gen)
+        host_batches.append((x.pin_memory(), y.pin_memory()))
+    dev_x = host_batches[0][0].to(dev)
+    dev_y = host_batches[0][1].to(dev)
+    if args.channels_last and not lm:
+        dev_x = dev_x.contiguous(memory_format=torch.channels_last)
+    h2d_bytes = sum(t.numel() * t.element_size() for t in host_batches[0])
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    amp = torch.autocast("cuda", dtype=torch.bfloat16) if args.amp == "bf16" else None
+
+    def fwd_bwd(x, y):
+        if amp is not None:
+            with amp:
+                loss = net(x, y)[1] if lm else F.cross_entropy(net(x), y)
+        else:
+            loss = net(x, y)[1] if lm else F.cross_entropy(net(x), y)
+        loss.backward()
+        return loss
+
+    def train_step(x, y):
+        loss = fwd_bwd(x, y)
+        if opt is not None:
+            opt.step()
+            opt.zero_grad(set_to_none=False)
+        return loss
+
+    graphed = None
+    if args.graph and engine is not None:
+        from stellatrain_b200.parallel.graphs import GraphedStep
+
+        graphed = GraphedStep(engine, lambda x, y: fwd_bwd(x, y), (dev_x, dev_y), warmup=max(3, args.warmup))
+
+    def run_step_device():
+        if graphed is not None:
+            return graphed.replay()
+        return train_step(dev_x, dev_y)
+
+    def run_step_e2e(i):
+        hx, hy = host_batches[i % n_host]
+        if graphed is not None:
+            graphed.copy_inputs(hx, hy)
+            loss = graphed.replay()
+        else:
+            x = hx.to(dev, non_blocking=True)
+            y = hy.to(dev, non_blocking=True)
+            if args.channels_last and not lm:
+                x = x.contiguous(memory_format=torch.channels_last)
+            loss = train_step(x, y)
+        loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the step's result is read on the host
+        return float(loss_host[0])
+
+    def sync_all():
+        if engine is not None:
+            engine.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        launches0 = engine.stats["kernels"] if engine is not None else 0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        if engine is not None:
+            engine.synchronize()     # the last updates are part of the measured work
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            dist.barrier()
+        launches = (engine.stats["kernels"] - launches0) if engine is not None else 0
+        return ms, clocks, launches
+
+    for i in range(max(3, args.warmup)):
+        run_step_device()
+    ms, clocks, launches = timed(lambda i: run_step_device(), args.steps)
+    per_step = ms / args.steps
+    unit_per_step = args.batch * world * (args.seq_len if lm else 1)
+    value = unit_per_step / (per_step / 1e3)
+
+    e2e = None
+    if not args.skip_e2e:
+        for i in range(3):
+            run_step_e2e(i)
+        ms2, clocks2, _ = timed(run_step_e2e, args.steps)
+        e2e = {"value": unit_per_step / (ms2 / args.steps / 1e3), "unit": "tokens/s" if lm else "images/s",
+               "ms_per_step": ms2 / args.steps, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
+               "clocks": clocks2}
+
+    final_loss = float(train_step(dev_x, dev_y).detach()) if graphed is None else float(graphed.replay())
+    if engine is not None:
+        engine.synchronize()
+        engine.check_status()
+
+    if rank == 0:
+        out = {
+            "metric": f"{args.model} training throughput, sparse data parallel ({args.compressor} keeping "
+                      f"{(1 - args.ratio) * 100:g}% of gradient entries, error feedback, sparse {args.optimizer})",
+            "impl": args.impl,
+            "value": value, "unit": "tokens/s" if lm else "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 autocast" if args.amp == "bf16" else "fp32 (torch defaults: TF32 cuDNN convolutions)",
+            "data": "synthetic N(0,1) images / uniform labels, random-init weights" if not lm
+                    else "synthetic uniform token ids, random-init weights",
+            "config": {
+                "model": args.model, "params": n_params, "global_batch": args.batch * world,
+                "per_gpu_batch": args.batch, "seq_len": args.seq_len if lm else None, "parallelism": f"dp{world}",
+                "compressor": args.compressor, "kept_fraction": 1 - args.ratio, "optimizer": args.optimizer,
+                "lr": args.lr, "staleness": args.staleness, "bucket_mb": args.bucket_mb,
+                "transport": engine.transport if engine is not None else args.impl,
+                "multicast": bool(engine is not None and engine.pool is not None and engine.pool.mc_ptr),
+                "cuda_graph": bool(args.graph), "channels_last": bool(args.channels_last),
+                "l2": "per-step working set (233 MB of parameters plus activations) exceeds the 126 MB L2; no flush needed",
+            },
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,500 @@
+"""GPU-resident sparse data-parallel engine (one process per GPU).
+
+Role of the reference's ``FasterDpEngine`` (backend/src/engine/core.cpp:64-183, 712-758, 761-834,
+1025-1140) with the CPU hop removed: gradients land in flat device buckets, a post-accumulate hook marks
+a bucket ready, and the bucket's select+push and scatter+apply kernels run on a high-priority side
+stream ordered against the compute stream with events only.  The bounded-staleness protocol of the
+reference (backend/src/engine/core.cpp:730-739, 898-908; backend/src/engine/core_module_api.cpp:290) is
+kept: with staleness 1 the update of iteration i is applied once backward i+1 of the same bucket has run
+and forward i+2 waits for it; staleness 0 applies right after the select.
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Iterable, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import buckets as B
+from . import symm
+from .gpu_bucket import CandidateScratch, GpuBucket, SparseStepError, Wiring
+
+
+@dataclass
+class EngineConfig:
+    compressor: str = "thresholdv16"      # default of the reference (backend/src/engine/core.cpp:25)
+    ratio: float = 0.99                   # fraction dropped (backend/src/engine/core.cpp:23)
+    min_ratio: Optional[float] = None     # lowest ratio the controller may ask for (sizes receive areas)
+    optimizer: str = "sgd"
+    optimizer_options: dict = field(default_factory=dict)
+    staleness: int = 1                    # backend/src/engine/core.cpp:80
+    grad_accumulation: int = 1
+    bucket_mb: float = 32.0
+    chunk_elems: int = 16384
+    transport: str = "auto"               # auto | peer | nccl | local
+    multicast: bool = True                # use the NVLS multicast alias for pushes when available
+    timeout_s: float = 10.0               # bound of every device-side wait
+    broadcast_init: bool = True
+    divide_k_by_world: bool = True        # k per rank = kept budget / world (compress.cpp:44)
+    amsgrad: bool = False
+    smart_momentum: bool = False
+    fine_grained_gating: bool = False     # wait per first-using module instead of at the root
+    status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
+
+
+class _BucketRuntime:
+    __slots__ = ("bucket", "params", "pending", "full", "grad_ready", "apply_done", "has_pending_apply",
+                 "select_count", "apply_count", "first_module")
+
+    def __init__(self, bucket: GpuBucket, params: list[nn.Parameter], ga: int):
+        self.bucket = bucket
+        self.params = params
+        self.full = len(params) * ga
+        self.pending = self.full
+        self.grad_ready = torch.cuda.Event()
+        self.apply_done: Optional[torch.cuda.Event] = None
+        self.has_pending_apply = False
+        self.select_count = 0
+        self.apply_count = 0
+        self.first_module = None
+
+
+class SparseDPEngine:
+    """Owns buckets, streams and the step protocol for one ``nn.Module`` replica."""
+
+    def __init__(self, module: nn.Module, config: Optional[EngineConfig] = None, process_group=None,
+                 device: Optional[torch.device] = None) -> None:
+        self.cfg = cfg = config or EngineConfig()
+        self.module = module
+        self.group = process_group
+        self.dist_on = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(process_group) if self.dist_on else 1
+        self.rank = dist.get_rank(process_group) if self.dist_on else 0
+        params = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
+        if not params:
+            raise ValueError("module has no trainable parameters")
+        self.device = device or params[0][1].device
+        if self.device.type != "cuda":
+            raise RuntimeError("the GPU-resident engine needs CUDA parameters; use the CPU tier otherwise")
+        torch.cuda.set_device(self.device)
+        if cfg.staleness not in (0, 1):
+            raise ValueError("staleness must be 0 or 1")
+        transport = cfg.transport
+        if transport == "auto":
+            transport = "local" if self.world == 1 else "peer"
+        self.transport = transport
+        low, high = torch.cuda.Stream.priority_range()
+        self.sparse_stream = torch.cuda.Stream(device=self.device, priority=high)
+        self.iteration = 0            # completed optimiser iterations (selects issued per bucket)
+        self.micro_step = 0
+        self._failed: Optional[SparseStepError] = None
+        self._capturing = False       # set while a CUDA graph of the step is being captured
+        self._build_buckets(params)
+        self._wire()
+        self._install_hooks()
+        if cfg.optimizer_options:
+            self.configure_optimizer(**cfg.optimizer_options)
+        if cfg.broadcast_init and self.world > 1:
+            self.broadcast_parameters()
+        self._status_host = torch.zeros(len(self.buckets), dtype=torch.int32).pin_memory()
+        self._status_dev = torch.zeros(len(self.buckets), dtype=torch.int32, device=self.device)
+        self._status_event: Optional[torch.cuda.Event] = None
+        self.stats = {"select_launches": 0, "apply_launches": 0, "kernels": 0}
+
+    # ------------------------------------------------------------------ construction
+    def _build_buckets(self, params: list[tuple[str, nn.Parameter]]) -> None:
+        cfg = self.cfg
+        # gradients become ready roughly in reverse registration order
+        order = list(reversed(range(len(params))))
+        numels = [params[i][1].numel() for i in order]
+        groups = B.plan_buckets(numels, int(cfg.bucket_mb * (1 << 20) / 4))
+        self.scratch = CandidateScratch(self.device)
+        self.buckets: list[_BucketRuntime] = []
+        self.param_names: list[list[str]] = []
+        self._param_to_bucket: dict[int, int] = {}
+        for bi, grp in enumerate(groups):
+            idxs = [order[j] for j in grp]
+            names = [params[i][0] for i in idxs]
+            plist = [params[i][1] for i in idxs]
+            layout = B.BucketLayout(names, [p.numel() for p in plist], chunk_elems=cfg.chunk_elems)
+            bucket = GpuBucket(
+                bi, layout, self.device, compressor=cfg.compressor, ratio=cfg.ratio, world=self.world,
+                rank=self.rank, optimizer=cfg.optimizer, amsgrad=cfg.amsgrad,
+                smart_momentum=cfg.smart_momentum, min_ratio=cfg.min_ratio, scratch=self.scratch,
+                timeout_s=cfg.timeout_s, divide_k_by_world=cfg.divide_k_by_world,
+            )
+            with torch.no_grad():
+                for seg, p in zip(layout.segments, plist):
+                    dense = _dense_like(p)
+                    flat_p = bucket.param[seg.off : seg.off + seg.numel]
+                    flat_g = bucket.grad[seg.off : seg.off + seg.numel]
+                    flat_p.copy_(_flatten_storage_order(dense))
+                    p.data = flat_p.as_strided(dense.shape, dense.stride())
+                    p.grad = flat_g.as_strided(dense.shape, dense.stride())
+            rt = _BucketRuntime(bucket, plist, cfg.grad_accumulation)
+            self.buckets.append(rt)
+            self.param_names.append(names)
+            for p in plist:
+                self._param_to_bucket[id(p)] = bi
+
+    def _wire(self) -> None:
+        if self.transport == "local":
+            if self.world != 1:
+                raise ValueError("transport 'local' needs world size 1")
+            for rt in self.buckets:
+                rt.bucket.wire_local()
+            self.pool = None
+            return
+        W = self.world
+        max_n = max(rt.bucket.layout.n_total for rt in self.buckets)
+        need = sum(rt.bucket.recv_bytes() + 4 * W * 8 + 1024 for rt in self.buckets) + max_n * 4 + 65536
+        if self.transport == "nccl":
+            # library baseline: streams are staged locally and moved by ncclAllGather
+            self.pool = symm._alloc_local(need, self.device, 1, 0)
+        else:
+            self.pool = symm.allocate(need, self.device, self.group, multicast=self.cfg.multicast)
+        pool = self.pool
+        self._staging_off = pool.take(max_n * 4)
+        self._staging_elems = max_n
+        for rt in self.buckets:
+            b = rt.bucket
+            if self.transport == "nccl":
+                send = torch.zeros(2 * b.cap_max * 8, dtype=torch.uint8, device=self.device)
+                gathered = torch.zeros(b.recv_bytes(), dtype=torch.uint8, device=self.device)
+                b._nccl_send, b._nccl_recv = send, gathered
+                # select side: a world of one writing into the send buffer; apply side: all sources
+                b.wire(Wiring(W, self.rank, gathered, [0] * W, None, [0] * W, None, [0] * W))
+                b.wire_select(Wiring(1, 0, send, [send.data_ptr()], None, [0], None, [0]))
+                continue
+            r_off = pool.take(b.recv_bytes())
+            f_off = pool.take(2 * W * 8)
+            a_off = pool.take(2 * W * 8)
+            b.wire(Wiring(
+                world=W, rank=self.rank,
+                recv_local=pool.local_view(r_off, b.recv_bytes()),
+                peer_recv=[pool.peer_addr(r, r_off) for r in range(W)],
+                flag_local=pool.local_view(f_off, 2 * W * 8).view(torch.int64),
+                peer_flag=[pool.peer_addr(r, f_off) for r in range(W)],
+                ack_local=pool.local_view(a_off, 2 * W * 8).view(torch.int64),
+                peer_ack=[pool.peer_addr(r, a_off) for r in range(W)],
+                recv_mc=pool.mc_addr(r_off), use_flags=True, use_acks=True,
+            ))
+        if self.dist_on:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+
+    def _install_hooks(self) -> None:
+        self._hooks = []
+        for bi, rt in enumerate(self.buckets):
+            for p in rt.params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(bi)))
+        # forward gating: wait for the updates this forward must see
+        first_owner: dict[int, nn.Module] = {}
+        if self.cfg.fine_grained_gating:
+            for mod in self.module.modules():
+                for p in mod.parameters(recurse=False):
+                    bi = self._param_to_bucket.get(id(p))
+                    if bi is not None and bi not in first_owner:
+                        first_owner[bi] = mod
+        gate: dict[int, list[int]] = {}
+        for bi, mod in first_owner.items():
+            gate.setdefault(id(mod), []).append(bi)
+            self.buckets[bi].first_module = mod
+        self._gated = set(first_owner.keys())
+        for mod in self.module.modules():
+            bis = gate.get(id(mod))
+            if bis:
+                self._hooks.append(mod.register_forward_pre_hook(self._make_gate(bis)))
+        self._hooks.append(self.module.register_forward_pre_hook(self._root_pre_forward))
+
+    # ------------------------------------------------------------------ hooks
+    def _make_hook(self, bi: int) -> Callable:
+        rt = self.buckets[bi]
+
+        def hook(_param) -> None:
+            rt.pending -= 1
+            if rt.pending == 0:
+                rt.pending = rt.full
+                self._bucket_ready(bi)
+
+        return hook
+
+    def _make_gate(self, bis: list[int]) -> Callable:
+        def pre(_mod, _inp) -> None:
+            if self._capturing:
+                return
+            cur = torch.cuda.current_stream(self.device)
+            for bi in bis:
+                ev = self.buckets[bi].apply_done
+                if ev is not None:
+                    cur.wait_event(ev)
+
+        return pre
+
+    def _root_pre_forward(self, _mod, _inp) -> None:
+        if self._failed is not None:
+            raise self._failed
+        if self._capturing:
+            # replays of a captured step serialise on their stream, which already orders this
+            # forward after every update of the previous replay
+            return
+        cur = torch.cuda.current_stream(self.device)
+        for bi, rt in enumerate(self.buckets):
+            if bi in self._gated:
+                continue
+            if rt.apply_done is not None:
+                cur.wait_event(rt.apply_done)
+        self._forward_count = getattr(self, "_forward_count", 0) + 1
+        if self.cfg.status_poll_interval and self._forward_count % self.cfg.status_poll_interval == 0:
+            self._poll_status()
+
+    def _bucket_ready(self, bi: int) -> None:
+        rt = self.buckets[bi]
+        cur = torch.cuda.current_stream(self.device)
+        rt.grad_ready.record(cur)
+        s = self.sparse_stream
+        s.wait_event(rt.grad_ready)
+        if self.cfg.staleness == 1 and rt.has_pending_apply:
+            self._apply(rt)
+        self._select(rt)
+        if self.cfg.staleness == 0:
+            self._apply(rt)
+        else:
+            rt.has_pending_apply = True
+
+    def _select(self, rt: _BucketRuntime) -> None:
+        b = rt.bucket
+        s = self.sparse_stream
+        if self.transport == "nccl":
+            b.select(s)
+            slot = (rt.select_count + 1) & 1
+            cap = b.layout.cap
+            send = b._nccl_send.view(torch.int64)[slot * cap : (slot + 1) * cap]
+            recv = b._nccl_recv.view(torch.int64)[slot * self.world * cap : (slot + 1) * self.world * cap]
+            with torch.cuda.stream(s):
+                dist.all_gather_into_tensor(recv, send, group=self.group)
+        else:
+            b.select(s)
+        rt.select_count += 1
+        self.stats["select_launches"] += 1
+        self.stats["kernels"] += 2 if b.compressor == "randomk" else 4
+
+    def _apply(self, rt: _BucketRuntime) -> None:
+        s = self.sparse_stream
+        rt.bucket.handle.apply(s.cuda_stream)
+        ev = torch.cuda.Event()
+        ev.record(s)
+        rt.apply_done = ev
+        rt.has_pending_apply = False
+        rt.apply_count += 1
+        self.stats["apply_launches"] += 1
+        self.stats["kernels"] += 2
+
+    # ------------------------------------------------------------------ public control
+    def synchronize(self) -> None:
+        """Flush every pending update and wait for the sparse stream
+        (role of backend/src/engine/core.cpp:1097-1140)."""
+        cur = torch.cuda.current_stream(self.device)
+        self.sparse_stream.wait_stream(cur)
+        for rt in self.buckets:
+            if rt.has_pending_apply:
+                self._apply(rt)
+        cur.wait_stream(self.sparse_stream)
+        self.sparse_stream.synchronize()
+        self.check_status()
+
+    def barrier(self) -> None:
+        torch.cuda.synchronize(self.device)
+        if self.dist_on:
+            dist.barrier(self.group)
+
+    def _poll_status(self) -> None:
+        """Non-blocking: looks at the status words copied to pinned memory after an earlier step."""
+        if self._status_event is not None and self._status_event.query():
+            bad = torch.nonzero(self._status_host).flatten()
+            if len(bad):
+                bi = int(bad[0])
+                self._failed = SparseStepError(bi, int(self._status_host[bi]))
+                raise self._failed
+            self._status_event = None
+        if self._status_event is None:
+            s = self.sparse_stream
+            with torch.cuda.stream(s):
+                torch.stack([rt.bucket.status[0] for rt in self.buckets], out=self._status_dev)
+                self._status_host.copy_(self._status_dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(s)
+            self._status_event = ev
+
+    def check_status(self) -> None:
+        for rt in self.buckets:
+            try:
+                rt.bucket.check_status()
+            except SparseStepError as e:
+                self._failed = e
+                raise
+
+    def configure_optimizer(self, **options) -> None:
+        """Hyper-parameters by the reference's option names (backend/src/optim/sgd.cpp:266-297,
+        backend/src/optim/adam.cpp:91-122): lr, momentum, weight_decay, dampening, nestrov/nesterov,
+        maximize, smart_momentum; lr, b1, b2, weight_decay, eps, amsgrad, maximize."""
+        alias = {"nestrov": "nesterov", "b1": "beta1", "b2": "beta2"}
+        opts = {}
+        for k, v in options.items():
+            k = alias.get(k, k)
+            if k == "smart_momentum" and bool(v) and not self.cfg.smart_momentum:
+                raise RuntimeError("smart_momentum must be enabled in EngineConfig (it allocates state)")
+            if k == "amsgrad" and bool(v) and not self.cfg.amsgrad:
+                raise RuntimeError("amsgrad must be enabled in EngineConfig (it allocates state)")
+            opts[k] = int(v) if isinstance(v, bool) else v
+        for rt in self.buckets:
+            rt.bucket.set_optimizer_options(**opts)
+
+    def set_compression_ratio(self, ratio: float) -> None:
+        """Takes effect at an iteration boundary: the pipeline is drained first."""
+        if not (0.0 < ratio <= 1.0):
+            raise ValueError("compression ratio must be in (0, 1]")
+        self.synchronize()
+        for rt in self.buckets:
+            rt.bucket.set_ratio(ratio)
+        self.cfg.ratio = ratio
+
+    def set_rank_weights(self, weights: Iterable[float]) -> None:
+        """Weight of each rank's gradient in the merge, e.g. batch_r / sum(batch) for unequal
+        per-GPU batch sizes (the reference averages with 1/W, cpu_optimize.cpp:55)."""
+        w = list(weights)
+        if len(w) != self.world:
+            raise ValueError("one weight per rank")
+        self.synchronize()
+        for rt in self.buckets:
+            rt.bucket.set_weights(w)
+
+    # ------------------------------------------------------------------ replicas
+    def broadcast_parameters(self, src: int = 0) -> None:
+        """Make every replica equal to rank ``src`` (backend/src/engine/core.cpp:841-885)."""
+        if self.world == 1:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.transport == "peer":
+            from .. import _build
+            C = _build.load_extension("_C")
+            pool = self.pool
+            stage = pool.local_view(self._staging_off, self._staging_elems * 4).view(torch.float32)
+            s = torch.cuda.current_stream(self.device)
+            for rt in self.buckets:
+                n = rt.bucket.layout.n_total
+                if self.rank == src:
+                    stage[:n].copy_(rt.bucket.param)
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.group)
+                if self.rank != src:
+                    C.peer_copy(rt.bucket.param.data_ptr(), pool.peer_addr(src, self._staging_off), n, s.cuda_stream)
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.group)
+        else:
+            for rt in self.buckets:
+                dist.broadcast(rt.bucket.param, src=src, group=self.group)
+        for mod in self.module.buffers():
+            dist.broadcast(mod, src=src, group=self.group)
+
+    def replica_drift(self) -> float:
+        """max |param - neighbour's param| over all buckets; 0.0 when replicas agree bit for bit
+        (the reference's dry-run model sync, backend/src/engine/core.cpp:843-847, 874-878)."""
+        if self.world == 1:
+            return 0.0
+        self.synchronize()
+        out = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if self.transport == "peer":
+            from .. import _build
+            C = _build.load_extension("_C")
+            pool = self.pool
+            stage = pool.local_view(self._staging_off, self._staging_elems * 4).view(torch.float32)
+            s = torch.cuda.current_stream(self.device)
+            nb = (self.rank + 1) % self.world
+            for rt in self.buckets:
+                n = rt.bucket.layout.n_total
+                stage[:n].copy_(rt.bucket.param)
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.group)
+                C.max_abs_diff(rt.bucket.param.data_ptr(), pool.peer_addr(nb, self._staging_off), n,
+                               out.data_ptr(), s.cuda_stream)
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.group)
+            drift = out.view(torch.float32).clone()
+        else:
+            drift = torch.zeros(1, device=self.device)
+            for rt in self.buckets:
+                ref = rt.bucket.param.clone()
+                dist.broadcast(ref, src=0, group=self.group)
+                drift = torch.maximum(drift, (ref - rt.bucket.param).abs().max().reshape(1))
+        dist.all_reduce(drift, op=dist.ReduceOp.MAX, group=self.group)
+        return float(drift.item())
+
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self) -> dict:
+        self.synchronize()
+        return {
+            "format": 1,
+            "iteration": [rt.select_count for rt in self.buckets],
+            "config": {k: getattr(self.cfg, k) for k in ("compressor", "ratio", "optimizer", "staleness",
+                                                         "grad_accumulation", "bucket_mb", "chunk_elems")},
+            "param_names": self.param_names,
+            "buckets": [rt.bucket.state_dict() for rt in self.buckets],
+            "world": self.world,
+        }
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.synchronize()
+        if sd["param_names"] != self.param_names:
+            raise ValueError("checkpoint was written for a different model or bucket plan")
+        if sd["world"] != self.world:
+            raise ValueError(f"checkpoint world size {sd['world']} != {self.world}: receive slots and "
+                             f"per-rank k depend on it")
+        for rt, bsd, it in zip(self.buckets, sd["buckets"], sd["iteration"]):
+            rt.bucket.load_state_dict(bsd)
+            rt.select_count = rt.apply_count = it
+            rt.has_pending_apply = False
+            rt.pending = rt.full
+        if self.transport == "peer":
+            # flags and acks restart from the restored epochs
+            for rt in self.buckets:
+                w = rt.bucket.wiring
+                e = int(sd["iteration"][rt.bucket.index])
+                w.flag_local.fill_(e)
+                w.ack_local.fill_(e)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+
+    def close(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+
+def _is_dense(t: torch.Tensor) -> bool:
+    """True when the elements occupy numel() consecutive slots in some permutation of the dims."""
+    expect = 1
+    for size, stride in sorted(((sz, st) for sz, st in zip(t.shape, t.stride()) if sz != 1), key=lambda x: x[1]):
+        if stride != expect:
+            return False
+        expect *= size
+    return True
+
+
+def _dense_like(p: torch.Tensor) -> torch.Tensor:
+    """The parameter itself when its memory is dense and non-overlapping (any permutation of
+    strides, e.g. channels_last), else a contiguous copy."""
+    d = p.detach()
+    return d if _is_dense(d) else d.contiguous()
+
+
+def _flatten_storage_order(t: torch.Tensor) -> torch.Tensor:
+    """Elements of a dense tensor in the order they sit in memory."""
+    if t.is_contiguous():
+        return t.reshape(-1)
+    order = sorted(range(t.dim()), key=lambda d: (-t.stride(d), d))
+    return t.permute(order).contiguous().reshape(-1)

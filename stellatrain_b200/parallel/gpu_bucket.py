@@ -128,6 +128,9 @@ class GpuBucket:
         self.scratch.reserve(n)
         self.handle = _ext().BucketHandle()
         self.wiring: Optional[Wiring] = None
+        # library-collective baseline: a second handle whose only destination is a local send buffer
+        self.select_handle = None
+        self.select_wiring: Optional[Wiring] = None
         self.zero_grad_in_select = True
         self._bind()
 
@@ -136,7 +139,12 @@ class GpuBucket:
         return 0 if t is None else t.data_ptr()
 
     def _bind(self) -> None:
-        h, L = self.handle, self.layout
+        self._bind_one(self.handle, self.wiring)
+        if self.select_handle is not None:
+            self._bind_one(self.select_handle, self.select_wiring)
+
+    def _bind_one(self, h, wiring: Optional[Wiring]) -> None:
+        L = self.layout
         h.set_data(
             grad=self.grad.data_ptr(), grad_tab=0, resid=self.resid.data_ptr(), param=self.param.data_ptr(),
             m=self.m.data_ptr(), v=self._ptr(self.v), vmax=self._ptr(self.vmax), last=self._ptr(self.last),
@@ -153,8 +161,8 @@ class GpuBucket:
             weight=self.weight.data_ptr(), timeout_ns=self.timeout_ns,
         )
         h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False)
-        if self.wiring is not None:
-            self._apply_wiring()
+        if wiring is not None:
+            self._apply_wiring(h, wiring)
 
     def recv_bytes(self) -> int:
         """Bytes of receive area one rank needs for this bucket (two slots, all sources)."""
@@ -168,11 +176,18 @@ class GpuBucket:
 
     def wire(self, w: Wiring) -> None:
         self.wiring = w
-        self._apply_wiring()
+        self._apply_wiring(self.handle, w)
 
-    def _apply_wiring(self) -> None:
-        w = self.wiring
-        self.handle.set_comm(
+    def wire_select(self, w: Wiring) -> None:
+        """Give the select its own destination list (used when a library collective moves the
+        stream afterwards); apply keeps using the main wiring."""
+        if self.select_handle is None:
+            self.select_handle = _ext().BucketHandle()
+        self.select_wiring = w
+        self._bind_one(self.select_handle, w)
+
+    def _apply_wiring(self, h, w: Wiring) -> None:
+        h.set_comm(
             world=w.world, rank=w.rank, recv_local=w.recv_local.data_ptr(), peer_recv=list(w.peer_recv),
             recv_mc=w.recv_mc, flag_local=self._ptr(w.flag_local), peer_flag=list(w.peer_flag),
             ack_local=self._ptr(w.ack_local), peer_ack=list(w.peer_ack), use_flags=w.use_flags,
@@ -204,7 +219,7 @@ class GpuBucket:
     # ------------------------------------------------------------------ execution
     def select(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
-        self.handle.select(s.cuda_stream)
+        (self.select_handle or self.handle).select(s.cuda_stream)
 
     def apply(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
@@ -275,5 +290,5 @@ class CandidateScratch:
 
     def bind(self, handle, remember: bool = True) -> None:
         handle.set_scratch(self.buf.data_ptr(), self.cursor.data_ptr(), self.cap)
-        if remember:
+        if remember and not any(h is handle for h in self._bound):
             self._bound.append(handle)

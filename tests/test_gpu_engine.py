@@ -1,0 +1,221 @@
+"""Engine-level behaviour on one GPU: dense equivalence, staleness protocol, accumulation, checkpoint."""
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def small_net():
+    torch.manual_seed(0)
+    return nn.Sequential(
+        nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(), nn.Conv2d(8, 8, 3, padding=1), nn.ReLU(),
+        nn.AdaptiveAvgPool2d(4), nn.Flatten(1), nn.Linear(128, 37), nn.ReLU(), nn.Linear(37, 10),
+    ).cuda()
+
+
+def batches(n, bs=16):
+    g = torch.Generator(device="cuda").manual_seed(42)
+    return [(torch.randn(bs, 3, 16, 16, device="cuda", generator=g),
+             torch.randint(0, 10, (bs,), device="cuda", generator=g)) for _ in range(n)]
+
+
+def make_engine(model, **kw):
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+
+    cfg = EngineConfig(**{"bucket_mb": 0.004, "chunk_elems": 1024, **kw})
+    return SparseDPEngine(model, cfg)
+
+
+@pytest.mark.parametrize("optimizer", ["sgd", "adam"])
+def test_keep_everything_equals_dense_optimizer(optimizer):
+    model = small_net()
+    ref = copy.deepcopy(model)
+    eng = make_engine(model, compressor="topk", ratio=0.0, optimizer=optimizer, staleness=0,
+                      optimizer_options={"lr": 0.05} if optimizer == "sgd" else {"lr": 1e-2})
+    assert len(eng.buckets) > 1
+    opt = torch.optim.SGD(ref.parameters(), lr=0.05) if optimizer == "sgd" else torch.optim.Adam(ref.parameters(), lr=1e-2)
+    for x, y in batches(5):
+        F.cross_entropy(model(x), y).backward()
+        opt.zero_grad()
+        F.cross_entropy(ref(x), y).backward()
+        opt.step()
+    eng.synchronize()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        torch.testing.assert_close(p, q, rtol=1e-4, atol=1e-5)
+    eng.close()
+
+
+def test_staleness_one_sees_updates_up_to_two_iterations_back():
+    model = small_net()
+    names = [n for n, _ in model.named_parameters()]
+    p0 = {n: p.detach().clone() for n, p in model.named_parameters()}
+    lr = 0.1
+    eng = make_engine(model, compressor="topk", ratio=0.0, optimizer="sgd", staleness=1,
+                      optimizer_options={"lr": lr})
+    data = batches(5)
+    for x, y in data:
+        F.cross_entropy(model(x), y).backward()
+    eng.synchronize()
+    # simulate: gradient j is taken at the parameters that contain updates 0..j-2
+    shadow = small_net()
+    grads = []
+    for j, (x, y) in enumerate(data):
+        with torch.no_grad():
+            for n, p in shadow.named_parameters():
+                p.copy_(p0[n] - lr * sum((g[n] for g in grads[: max(0, j - 1)]), torch.zeros_like(p0[n])))
+        shadow.zero_grad()
+        F.cross_entropy(shadow(x), y).backward()
+        grads.append({n: p.grad.detach().clone() for n, p in shadow.named_parameters()})
+    for n, p in model.named_parameters():
+        want = p0[n] - lr * sum(g[n] for g in grads)
+        torch.testing.assert_close(p, want, rtol=1e-4, atol=1e-5)
+    eng.close()
+
+
+def test_gradient_accumulation_sums_micro_batches():
+    model = small_net()
+    ref = copy.deepcopy(model)
+    eng = make_engine(model, compressor="topk", ratio=0.0, optimizer="sgd", staleness=0, grad_accumulation=2,
+                      optimizer_options={"lr": 0.05})
+    opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    for x, y in batches(3, bs=16):
+        for xm, ym in zip(x.chunk(2), y.chunk(2)):
+            F.cross_entropy(model(xm), ym).backward()
+        opt.zero_grad()
+        for xm, ym in zip(x.chunk(2), y.chunk(2)):
+            F.cross_entropy(ref(xm), ym).backward()
+        opt.step()
+    eng.synchronize()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        torch.testing.assert_close(p, q, rtol=1e-4, atol=1e-5)
+    eng.close()
+
+
+@pytest.mark.parametrize("compressor", ["thresholdv16", "topk", "thresholdv", "randomk"])
+@pytest.mark.parametrize("staleness", [0, 1])
+def test_sparse_training_reduces_loss(compressor, staleness):
+    torch.manual_seed(3)
+    teacher = nn.Linear(32, 10).cuda()
+    model = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 10)).cuda()
+    eng = make_engine(model, compressor=compressor, ratio=0.9, optimizer="adam", staleness=staleness,
+                      optimizer_options={"lr": 1e-2})
+    x = torch.randn(256, 32, device="cuda")
+    y = teacher(x).argmax(1)
+    losses = []
+    for _ in range(200):
+        loss = F.cross_entropy(model(x), y)
+        loss.backward()
+        losses.append(float(loss.detach()))
+    eng.synchronize()
+    eng.check_status()
+    assert losses[-1] < 0.5 * losses[0], losses[::20]
+    eng.close()
+
+
+def test_graphed_step_matches_eager():
+    from stellatrain_b200.parallel.graphs import GraphedStep
+
+    data = batches(6)
+    results = []
+    for use_graph in (False, True):
+        model = small_net()
+        eng = make_engine(model, compressor="topk", ratio=0.9, optimizer="adam", staleness=1)
+        step = lambda x, y: _fwd_bwd(model, x, y)
+        if not use_graph:
+            for x, y in data[:3] + data:     # same number of warm-up steps as the graphed run
+                step(x, y)
+        else:
+            x0, y0 = data[0]
+            # warm-up inside GraphedStep runs on its static copies: feed the same three batches
+            g = None
+            for x, y in data[:2]:
+                step(x, y)
+            g = GraphedStep(eng, step, data[2], warmup=1)
+            for x, y in data:
+                g.copy_inputs(x, y)
+                g.replay()
+        eng.synchronize()
+        eng.check_status()
+        results.append([p.detach().clone() for p in model.parameters()])
+        eng.close()
+    for p, q in zip(*results):
+        torch.testing.assert_close(p, q, rtol=1e-5, atol=1e-6)
+
+
+def _fwd_bwd(model, x, y):
+    loss = F.cross_entropy(model(x), y)
+    loss.backward()
+    return loss
+
+
+def test_checkpoint_resume_is_bit_exact():
+    data = batches(8)
+    model = small_net()
+    eng = make_engine(model, compressor="thresholdv16", ratio=0.9, optimizer="adam", staleness=1)
+    for x, y in data[:4]:
+        F.cross_entropy(model(x), y).backward()
+    sd = {"engine": eng.state_dict(), "model": copy.deepcopy(model.state_dict())}
+    for x, y in data[4:]:
+        F.cross_entropy(model(x), y).backward()
+    eng.synchronize()
+    want = [p.detach().clone() for p in model.parameters()]
+    eng.close()
+
+    model2 = small_net()
+    eng2 = make_engine(model2, compressor="thresholdv16", ratio=0.9, optimizer="adam", staleness=1)
+    eng2.load_state_dict(sd["engine"])
+    for x, y in data[4:]:
+        F.cross_entropy(model2(x), y).backward()
+    eng2.synchronize()
+    for p, q in zip(model2.parameters(), want):
+        assert torch.equal(p, q)
+    eng2.close()
+
+
+def test_channels_last_parameters_are_supported():
+    model = small_net().to(memory_format=torch.channels_last)
+    ref = copy.deepcopy(model)
+    eng = make_engine(model, compressor="topk", ratio=0.0, optimizer="sgd", staleness=0, optimizer_options={"lr": 0.05})
+    opt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    for x, y in batches(3):
+        x = x.contiguous(memory_format=torch.channels_last)
+        F.cross_entropy(model(x), y).backward()
+        opt.zero_grad()
+        F.cross_entropy(ref(x), y).backward()
+        opt.step()
+    eng.synchronize()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        torch.testing.assert_close(p, q, rtol=1e-4, atol=1e-5)
+    eng.close()
+
+
+def test_wrapper_and_module_api():
+    import stellatrain_b200 as st
+
+    st.detach()
+    st.configure("127.0.0.1", 29533, 1, 0, 0, 1, 0, "topk", 1, staleness=0)
+    st.configure_compression_ratio(0.5)
+    st.set_optimizer("sgd")
+    st.configure_optimizer("lr", 0.1)
+    st.configure_optimizer("momentum", 0.9)
+    with pytest.raises(RuntimeError, match="NO OPTION"):
+        st.configure_optimizer("b1", 0.5)
+    import torchvision
+
+    model = st.FasterDpModelWrapper(torchvision.models.resnet18(num_classes=10).cuda())
+    assert isinstance(model.module, nn.Sequential)
+    x = torch.randn(4, 3, 64, 64, device="cuda")
+    y = torch.randint(0, 10, (4,), device="cuda")
+    loader = st.StellaTrainDataLoader([(x, y)] * 3)
+    for xb, yb in loader:
+        assert loader.is_eoi
+        F.cross_entropy(model(xb), yb).backward()
+    st.synchronize()
+    idx, val = st.compress("probe", torch.randn(10000, device="cuda"), 0.99)
+    assert idx.numel() == 100 and val.numel() == 100 and idx.dtype == torch.int32
+    assert st.force_model_sync(0, "x", True) == 0.0
+    st.detach()
