@@ -1,0 +1,189 @@
+"""Peer-memory exchange on 2+ GPUs: one process per GPU, NCCL only for rendezvous and barriers."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _spawn(fn, world, *args, env=None):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    procs = []
+    for r in range(world):
+        p = ctx.Process(target=_entry, args=(fn, r, world, port, q, env or {}, args))
+        p.start()
+        procs.append(p)
+    for p in procs:
+        p.join(timeout=300)
+    results = {}
+    while not q.empty():
+        r, ok, payload = q.get()
+        results[r] = (ok, payload)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            pytest.fail("worker did not finish")
+    assert len(results) == world, f"missing results: {sorted(results)}"
+    for r in range(world):
+        ok, payload = results[r]
+        assert ok, f"rank {r} failed:\n{payload}"
+    return [results[r][1] for r in range(world)]
+
+
+def _entry(fn, rank, world, port, q, env, args):
+    import traceback
+
+    os.environ.update(env)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    try:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", world_size=world, rank=rank,
+                                device_id=torch.device("cuda", rank))
+        out = fn(rank, world, *args)
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, True, out))
+    except Exception:  # noqa: BLE001
+        q.put((rank, False, traceback.format_exc()))
+
+
+def _net():
+    import torch.nn as nn
+
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Linear(48, 96), nn.ReLU(), nn.Linear(96, 96), nn.ReLU(), nn.Linear(96, 10)).cuda()
+
+
+def _data(rank, steps, bs=32):
+    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    return [(torch.randn(bs, 48, device="cuda", generator=g), torch.randint(0, 10, (bs,), device="cuda", generator=g))
+            for _ in range(steps)]
+
+
+def _worker_dense_equivalence(rank, world, transport, multicast):
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+
+    model = _net()
+    eng = SparseDPEngine(model, EngineConfig(compressor="topk", ratio=0.0, optimizer="sgd", staleness=0,
+                                             divide_k_by_world=False, bucket_mb=0.02, chunk_elems=1024,
+                                             transport=transport, multicast=multicast,
+                                             optimizer_options={"lr": 0.1}))
+    steps = 4
+    mine = _data(rank, steps)
+    for x, y in mine:
+        F.cross_entropy(model(x), y).backward()
+    eng.synchronize()
+    drift = eng.replica_drift()
+    # dense reference: mean over ranks of the per-rank mean gradient == one big batch of equal shards
+    ref = _net()
+    opt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    everyone = [_data(r, steps) for r in range(world)]
+    for s in range(steps):
+        opt.zero_grad()
+        x = torch.cat([everyone[r][s][0] for r in range(world)])
+        y = torch.cat([everyone[r][s][1] for r in range(world)])
+        F.cross_entropy(ref(x), y).backward()
+        opt.step()
+    err = max(float((p - q).abs().max()) for p, q in zip(model.parameters(), ref.parameters()))
+    info = {"drift": drift, "err": err, "backend": eng.pool.backend if eng.pool else "local",
+            "mc": bool(eng.pool and eng.pool.mc_ptr)}
+    eng.close()
+    return info
+
+
+@pytest.mark.parametrize("transport,multicast", [("peer", False), ("peer", True), ("nccl", False)])
+def test_exchange_equals_dense_data_parallel(transport, multicast):
+    world = min(torch.cuda.device_count(), 4)
+    outs = _spawn(_worker_dense_equivalence, world, transport, multicast)
+    for o in outs:
+        assert o["err"] < 1e-4, outs
+        assert o["drift"] <= 1e-6, outs      # replicas may differ only by atomic-add rounding order
+
+
+def _worker_sparse_parity(rank, world, compressor, staleness):
+    import torch.nn.functional as F
+
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+
+    model = _net()
+    if rank != 0:   # broadcast_init must overwrite this
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(1.0)
+    eng = SparseDPEngine(model, EngineConfig(compressor=compressor, ratio=0.9, optimizer="adam", staleness=staleness,
+                                             bucket_mb=0.02, chunk_elems=1024, optimizer_options={"lr": 1e-2}))
+    first = None
+    for x, y in _data(rank, 30):
+        loss = F.cross_entropy(model(x), y)
+        loss.backward()
+        first = first if first is not None else float(loss.detach())
+    eng.synchronize()
+    eng.check_status()
+    drift = eng.replica_drift()
+    eng.close()
+    return {"drift": drift, "first": first, "last": float(loss.detach())}
+
+
+@pytest.mark.parametrize("compressor", ["thresholdv16", "topk", "thresholdv"])
+@pytest.mark.parametrize("staleness", [0, 1])
+def test_sparse_replicas_stay_in_sync(compressor, staleness):
+    world = min(torch.cuda.device_count(), 4)
+    outs = _spawn(_worker_sparse_parity, world, compressor, staleness)
+    for o in outs:
+        assert o["drift"] <= 1e-5, outs
+        assert o["first"] == pytest.approx(outs[0]["first"], rel=0.5)
+
+
+def _worker_missing_peer(rank, world):
+    """Rank 1 leaves between steps (host-side decision); rank 0's next step must end with a timeout
+    status instead of a hang.  Plain peer stores only (NVLS disabled by the environment)."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+    from stellatrain_b200.parallel.gpu_bucket import SparseStepError
+
+    model = _net()
+    eng = SparseDPEngine(model, EngineConfig(compressor="topk", ratio=0.9, optimizer="sgd", staleness=0,
+                                             bucket_mb=1.0, timeout_s=1.0, multicast=False))
+    data = _data(rank, 3)
+    for x, y in data[:2]:
+        F.cross_entropy(model(x), y).backward()
+    eng.synchronize()
+    dist.barrier()
+    outcome = "skipped"
+    if rank != 1:
+        x, y = data[2]
+        F.cross_entropy(model(x), y).backward()
+        try:
+            eng.synchronize()
+            outcome = "no error"
+        except SparseStepError as e:
+            outcome = f"status {e.code}"
+    torch.cuda.synchronize()
+    eng.close()
+    return outcome
+
+
+def test_missing_peer_times_out_cleanly():
+    outs = _spawn(_worker_missing_peer, 2, env={"STELLATRAIN_NVLS": "0", "NCCL_NVLS_ENABLE": "0"})
+    assert outs[1] == "skipped"
+    assert outs[0] == "status 2", outs
