@@ -50,8 +50,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--staleness", type=int, default=1)
     ap.add_argument("--bucket-mb", type=float, default=32.0)
-    ap.add_argument("--graph", type=int, default=0, help="capture the training step in a CUDA graph")
-    ap.add_argument("--channels-last", type=int, default=0)
+    ap.add_argument("--graph", type=int, default=1, help="capture the training step in a CUDA graph")
+    ap.add_argument("--channels-last", type=int, default=1, help="NHWC memory format for vision models")
     ap.add_argument("--amp", default="none", choices=["none", "bf16"])
     ap.add_argument("--no-multicast", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -103,8 +103,26 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def arm_watchdog(seconds: float) -> None:
+    """Hard limit for the whole run: dump every thread's stack and leave without running destructors,
+    so that a stuck rank can never hold the GPUs until an outer limit kills the job."""
+    import faulthandler
+    import threading
+
+    def fire() -> None:
+        sys.stderr.write(f"[bench] watchdog: no result after {seconds:.0f}s, aborting\n")
+        faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+        sys.stderr.flush()
+        os._exit(3)
+
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+
+
 def main() -> None:
     args = parse_args()
+    arm_watchdog(float(os.environ.get("BENCH_WATCHDOG_S", "420")))
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return
@@ -193,7 +211,11 @@ def main() -> None:
     if args.graph and engine is not None:
         from stellatrain_b200.parallel.graphs import GraphedStep
 
-        graphed = GraphedStep(engine, lambda x, y: fwd_bwd(x, y), (dev_x, dev_y), warmup=max(3, args.warmup))
+        try:
+            graphed = GraphedStep(engine, lambda x, y: fwd_bwd(x, y), (dev_x, dev_y), warmup=max(3, args.warmup))
+        except Exception as e:  # noqa: BLE001 - fall back to eager launches, and say so in the result
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({e!r}); running eagerly\n")
+            args.graph = 0
 
     def run_step_device():
         if graphed is not None:
@@ -262,7 +284,7 @@ def main() -> None:
                "ms_per_step": ms2 / args.steps, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
                "clocks": clocks2}
 
-    final_loss = float(train_step(dev_x, dev_y).detach()) if graphed is None else float(graphed.replay())
+    final_loss = float(train_step(dev_x, dev_y).detach()) if graphed is None else float(graphed.replay().detach())
     if engine is not None:
         engine.synchronize()
         engine.check_status()
@@ -296,4 +318,12 @@ def main() -> None:
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:  # noqa: BLE001 - report, then leave without touching communicators again
+        import traceback
+
+        traceback.print_exc()
+        sys.stderr.flush()
+        sys.stdout.flush()
+        os._exit(1)

@@ -26,6 +26,9 @@ __global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
   const int src = blockIdx.y;
   const uint32_t epoch = *A.epoch;
   const uint32_t slot = epoch & 1u;
+  // Nothing was selected for this epoch yet (e.g. a captured step replayed right after a flush):
+  // the pair of kernels is a no-op and leaves every counter untouched.
+  if (epoch >= ld_volatile_u32(A.sel_epoch)) return;
   if (threadIdx.x == 0) {
     int ok = ld_volatile_u32(A.status) == kOk;
     if (ok && A.use_flags) {
@@ -51,6 +54,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {
   const int src = blockIdx.y;
   const uint32_t epoch = *A.epoch;
   const uint32_t slot = epoch & 1u;
+  if (epoch >= ld_volatile_u32(A.sel_epoch)) return;
   const bool ok = ld_volatile_u32(A.status) == kOk;
   const OptState o = *A.opt;
 

@@ -79,6 +79,7 @@ struct BucketHandle {
     uint32_t* c = as_ptr<uint32_t>(counters);
     sel.epoch = c + 0;
     app.epoch = c + 1;
+    app.sel_epoch = c + 0;
     sel.done_ctr = c + 2;
     app.done_ctr = c + 3;
     sel.status = app.status = as_ptr<uint32_t>(status);

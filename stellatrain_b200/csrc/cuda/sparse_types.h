@@ -134,6 +134,7 @@ struct ApplyArgs {
   uint32_t* last;              // smart momentum: step of the last touch, or null
   OptState* opt;
   uint32_t* epoch;             // apply epoch of this bucket (starts at 1)
+  const uint32_t* sel_epoch;   // select epoch: an apply with epoch >= *sel_epoch has nothing to consume
   uint32_t* done_ctr;
   uint32_t* status;
   uint64_t timeout_ns;

@@ -38,6 +38,8 @@ class GraphedStep:
             import torch.distributed as dist
             dist.barrier(engine.group)
 
+        if engine.cfg.staleness == 1 and not all(rt.has_pending_apply for rt in engine.buckets):
+            raise RuntimeError("capture needs a steady-state step: run at least one warm-up step first")
         before = [(rt.select_count, rt.apply_count) for rt in engine.buckets]
         kernels0 = engine.stats["kernels"]
         self.graph = torch.cuda.CUDAGraph()
