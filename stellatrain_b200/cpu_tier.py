@@ -1,0 +1,219 @@
+"""Python face of the CPU-offload tier (native module ``_Ccpu``).
+
+The reference *is* this tier: gradients leave the GPU, are reduced, sparsified, exchanged and applied on
+the CPU, and parameters come back (backend/src/engine/modules/*.cpp).  Here it is an option next to the
+GPU-resident engine: the stand-in baseline for the reference pipeline, the home of the flat-gradient CPU
+benchmark, and a way to train when optimiser state should not live in HBM.
+
+``CpuOffloadEngine`` drives the native ``CpuEngine`` for an ``nn.Module``:
+
+* host parameters: the engine reads gradients from and writes parameters to the tensors directly;
+* CUDA parameters: gradients are copied into the pinned shared slots on a side stream, the native
+  pipeline starts when the copy's event has fired, and updated parameters are copied back by a small
+  completion thread (the reference's D2H_Copy / H2D_Copy stages, d2h_copy.cpp:20-66, h2d_copy.cpp:31-56).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+_ext = None
+
+
+def _load():
+    global _ext
+    if _ext is None:
+        from . import _build
+
+        _ext = _build.load_extension("_Ccpu")
+    return _ext
+
+
+def available() -> bool:
+    try:
+        _load()
+        return True
+    except Exception:  # noqa: BLE001
+        return False
+
+
+_compressors: dict = {}
+
+
+def get_compressor(method: str):
+    c = _compressors.get(method)
+    if c is None:
+        c = _load().Compressor(method)
+        _compressors[method] = c
+    return c
+
+
+def compress(name: str, flat: torch.Tensor, k: int, method: str):
+    """One tensor, no residual: (idx:int32, val:float32) with at most k entries."""
+    flat = flat.detach().contiguous().float().reshape(-1)
+    idx = torch.empty(k, dtype=torch.int32)
+    val = torch.empty(k, dtype=torch.float32)
+    n = get_compressor(method).compress(name, flat.data_ptr(), flat.numel(), k, idx.data_ptr(), val.data_ptr())
+    return idx[:n], val[:n]
+
+
+def compress_with_feedback(name: str, grad: torch.Tensor, resid: torch.Tensor, k: int, method: str):
+    """Error-feedback compression in place on ``resid``; returns (idx:int64 view of uint32, val)."""
+    assert grad.dtype == torch.float32 and resid.dtype == torch.float32 and grad.is_contiguous() and resid.is_contiguous()
+    idx = torch.empty(k, dtype=torch.int32)
+    val = torch.empty(k, dtype=torch.float32)
+    n = get_compressor(method).compress_with_feedback(name, grad.data_ptr(), resid.data_ptr(), grad.numel(), k,
+                                                      idx.data_ptr(), val.data_ptr())
+    return idx[:n], val[:n]
+
+
+def make_optimizer(kind: str):
+    ext = _load()
+    return {"sgd": ext.SGD, "adam": ext.Adam, "sgd_naive": ext.SGDNaive}[kind]()
+
+
+def _from_ptr(ptr: int, numel: int) -> torch.Tensor:
+    """A float32 tensor over foreign host memory (the shared-memory pool); no ownership."""
+    buf = (ctypes.c_float * numel).from_address(ptr)
+    return torch.frombuffer(buf, dtype=torch.float32, count=numel)
+
+
+class CpuOffloadEngine:
+    def __init__(self, module: nn.Module, *, master_addr: str = "127.0.0.1", master_port: int = 5555, world_size: int = 1,
+                 rank: int = 0, session: Optional[int] = None, local_world_size: int = 1, local_rank: int = 0,
+                 method: str = "thresholdv16", gradient_accumulation: int = 1, staleness: int = 1, ratio: float = 0.99,
+                 optimizer: str = "sgd", optimizer_options: Optional[dict] = None, data_bytes: int = 0,
+                 timeout_ms: int = 30000, workers: int = 0, debug_accuracy: bool = False, debug_barrier: bool = False):
+        ext = _load()
+        self.module = module
+        self.engine = ext.CpuEngine()
+        params = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
+        self.cuda = params[0][1].is_cuda
+        if data_bytes == 0:
+            # parameter + residual + 2 * local_world gradient slots per element, with head-room
+            need = sum(p.numel() for _, p in params) * 4 * (2 + 2 * local_world_size)
+            data_bytes = max(64 << 20, int(need * 1.25) + (8 << 20))
+        self.engine.configure(master_addr, master_port, world_size, rank, os.getpid() if session is None else session,
+                              local_world_size, local_rank, method, gradient_accumulation, staleness, ratio,
+                              data_bytes, timeout_ms, workers, self.cuda, debug_accuracy, debug_barrier)
+        self.engine.set_optimizer(optimizer)
+        for k, v in (optimizer_options or {}).items():
+            self.engine.configure_optimizer(k, v)
+        self.grad_accumulation = gradient_accumulation
+        self.params = []
+        self._index = {}
+        for li, (name, p) in enumerate(params):
+            if not p.is_contiguous():
+                raise ValueError(f"parameter {name} must be contiguous")
+            user = 0 if self.cuda else p.data.data_ptr()
+            idx = self.engine.pre_train_init(li, name[-40:], p.numel(), user)
+            self.params.append(p)
+            self._index[id(p)] = idx
+            if self.cuda:
+                master = _from_ptr(self.engine.master_param(idx), p.numel())
+                p.data.copy_(master.view_as(p), non_blocking=False)
+        self._hooks = [p.register_post_accumulate_grad_hook(self._on_grad) for p in self.params]
+        self._hooks.append(module.register_forward_pre_hook(self._pre_forward))
+        self._stop = False
+        self._copy_stream = torch.cuda.Stream() if self.cuda else None
+        self._h2d_thread = None
+        self._pending_events: list = []
+        if self.cuda:
+            self._h2d_thread = threading.Thread(target=self._h2d_main, name="H2DCopy", daemon=True)
+            self._h2d_thread.start()
+            self._d2h_thread = threading.Thread(target=self._d2h_main, name="D2HCopy", daemon=True)
+            self._d2h_cv = threading.Condition()
+            self._d2h_thread.start()
+
+    # ------------------------------------------------------------------ hooks
+    def _pre_forward(self, _mod, _inp) -> None:
+        if self._micro != 0:
+            return   # later micro-iterations do not wait (model_wrapper.py:88-92)
+        for i in range(len(self.params)):
+            self.engine.pre_forward_process(i)
+
+    def _on_grad(self, p: torch.Tensor) -> None:
+        idx = self._index[id(p)]
+        g = p.grad
+        if not self.cuda:
+            self.engine.post_backward_process(idx, g.contiguous().data_ptr())
+            p.grad = None
+        else:
+            # device accumulation across micro-iterations, one D2H at the end (core.cpp:781-788)
+            last = (self._micro == self.grad_accumulation - 1)
+            if last:
+                slot = _from_ptr(self.engine.grad_slot(idx), p.numel())
+                ev = torch.cuda.Event()
+                cur = torch.cuda.current_stream()
+                self._copy_stream.wait_stream(cur)
+                with torch.cuda.stream(self._copy_stream):
+                    slot.copy_(g.reshape(-1), non_blocking=True)
+                    g.record_stream(self._copy_stream)
+                    ev.record(self._copy_stream)
+                p.grad = None
+                with self._d2h_cv:
+                    self._pending_events.append((ev, idx))
+                    self._d2h_cv.notify()
+
+    @property
+    def _micro(self) -> int:
+        """Micro-iteration index published by StellaTrainDataLoader (0 outside a loader loop)."""
+        from .utils.loader import current_micro_step
+
+        return max(0, current_micro_step())
+
+    def _d2h_main(self) -> None:
+        while not self._stop:
+            with self._d2h_cv:
+                if not self._pending_events:
+                    self._d2h_cv.wait(timeout=0.05)
+                    continue
+                ev, idx = self._pending_events.pop(0)
+            ev.synchronize()
+            for _ in range(self.grad_accumulation):
+                self.engine.post_backward_in_slot(idx)
+
+    def _h2d_main(self) -> None:
+        stream = torch.cuda.Stream()
+        while not self._stop:
+            for idx, it in self.engine.pop_ready_updates(50):
+                p = self.params[idx]
+                master = _from_ptr(self.engine.master_param(idx), p.numel())
+                with torch.cuda.stream(stream):
+                    p.data.copy_(master.view_as(p), non_blocking=True)
+                stream.synchronize()
+                self.engine.copy_out_done(idx, it)
+
+    # ------------------------------------------------------------------ control
+    def synchronize(self) -> None:
+        if self.cuda:
+            torch.cuda.synchronize()
+            import time
+            while True:
+                with self._d2h_cv:
+                    if not self._pending_events:
+                        break
+                time.sleep(0.001)
+        self.engine.synchronize()
+        if self.cuda:
+            torch.cuda.synchronize()
+
+    def barrier(self) -> None:
+        self.engine.barrier()
+
+    def stats_json(self, clear: bool = False) -> str:
+        return self.engine.stats_json(clear)
+
+    def close(self) -> None:
+        self._stop = True
+        for h in self._hooks:
+            h.remove()
+        if self._h2d_thread is not None:
+            self._h2d_thread.join(timeout=2)
+            self._d2h_thread.join(timeout=2)
+        self.engine = None

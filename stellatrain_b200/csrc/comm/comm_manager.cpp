@@ -1,0 +1,480 @@
+#include "comm_manager.h"
+
+#include <poll.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstring>
+#include <stdexcept>
+
+#include "../core/logger.h"
+#include "../cpu/array_util.h"
+
+namespace stc {
+
+namespace {
+
+constexpr uint32_t kMagic = 0x32425453u;   // "STB2"
+
+enum MsgType : uint32_t {
+  kInitReq = 1, kInitRes, kModelPut, kModelGet, kModelRep, kSyncTime, kStatRep, kBarrier, kOk, kConfigUpd, kGrad,
+  kBye,
+};
+
+struct FrameHeader {
+  uint32_t magic, type, key_len, flags;
+  uint64_t payload_len;
+};
+
+struct InitReq {            // cf. reference MsgInitReq (backend/src/engine/message.h:10-25)
+  uint16_t rank, listen_port, num_gpus, reserved;
+  int64_t timestamp_ns;
+  char ip[64];
+};
+struct InitRes {
+  uint8_t success;
+  uint8_t pad[3];
+  uint16_t target_port, target_rank;
+  char target_ip[64];
+};
+
+int64_t now_ns() {
+  return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+bool send_frame(int fd, uint32_t type, const std::string& key, uint32_t flags, const void* payload, size_t len,
+                int timeout_ms) {
+  FrameHeader h{kMagic, type, static_cast<uint32_t>(key.size()), flags, len};
+  if (!send_all(fd, &h, sizeof(h), timeout_ms)) return false;
+  if (!key.empty() && !send_all(fd, key.data(), key.size(), timeout_ms)) return false;
+  if (len && !send_all(fd, payload, len, timeout_ms)) return false;
+  return true;
+}
+
+bool recv_frame(int fd, FrameHeader* h, std::string* key, std::vector<unsigned char>* payload, int timeout_ms) {
+  if (!recv_all(fd, h, sizeof(*h), timeout_ms)) return false;
+  if (h->magic != kMagic || h->key_len > 4096 || h->payload_len > (1ull << 34)) return false;   // truncated or foreign
+  key->resize(h->key_len);
+  if (h->key_len && !recv_all(fd, &(*key)[0], h->key_len, timeout_ms)) return false;
+  payload->resize(h->payload_len);
+  if (h->payload_len && !recv_all(fd, payload->data(), h->payload_len, timeout_ms)) return false;
+  return true;
+}
+
+}  // namespace
+
+CommManager::CommManager(const std::string& master_addr, uint16_t master_port, int timeout_ms)
+    : master_addr_(master_addr), master_port_(master_port), timeout_ms_(timeout_ms) {}
+
+CommManager::~CommManager() {
+  stop_ = true;
+  tx_cv_.notify_all();
+  if (control_fd_ >= 0) {
+    std::lock_guard<std::mutex> lk(control_mu_);
+    send_frame(control_fd_, kBye, "", 0, nullptr, 0, 200);
+  }
+  if (push_thread_.joinable()) push_thread_.join();
+  if (pull_thread_.joinable()) pull_thread_.join();
+  close_fd(push_fd_);
+  close_fd(pull_fd_);
+  close_fd(data_listen_fd_);
+  close_fd(control_fd_);
+  if (broker_thread_.joinable()) broker_thread_.join();
+  close_fd(broker_listen_fd_);
+}
+
+void CommManager::set_failed(const std::string& why) {
+  std::lock_guard<std::mutex> lk(fail_mu_);
+  if (!failed_) {
+    failure_ = why;
+    failed_ = true;
+    LOG_ERROR("CommManager", why);
+  }
+}
+
+std::string CommManager::failure() const {
+  std::lock_guard<std::mutex> lk(fail_mu_);
+  return failure_;
+}
+
+// ---------------------------------------------------------------- broker (rank 0)
+void CommManager::start_server(int world) {
+  uint16_t bound = 0;
+  broker_listen_fd_ = tcp_listen(master_port_, &bound);
+  if (broker_listen_fd_ < 0) throw std::runtime_error("broker cannot listen on port " + std::to_string(master_port_));
+  broker_thread_ = std::thread([this, world] { broker_main(world); });
+}
+
+void CommManager::broker_main(int world) {
+  pthread_setname_np(pthread_self(), "CommBroker");
+  struct Client {
+    int fd = -1;
+    InitReq req{};
+    bool registered = false;
+  };
+  std::vector<Client> clients;
+  std::map<std::string, std::vector<unsigned char>> models;             // key -> parameter bytes
+  std::map<std::string, std::vector<int>> model_waiters;                // key -> client slots waiting
+  std::vector<int> barrier_waiters;
+  int registered = 0;
+  bool ring_sent = false;
+
+  while (!stop_) {
+    std::vector<pollfd> pfds;
+    pfds.push_back({broker_listen_fd_, POLLIN, 0});
+    for (auto& c : clients) pfds.push_back({c.fd, static_cast<short>(c.fd >= 0 ? POLLIN : 0), 0});
+    const int rc = poll(pfds.data(), pfds.size(), 100);
+    if (rc <= 0) continue;
+    if (pfds[0].revents & POLLIN) {
+      const int fd = tcp_accept(broker_listen_fd_, 0);
+      if (fd >= 0) {
+        Client c;
+        c.fd = fd;
+        clients.push_back(c);
+      }
+    }
+    for (size_t ci = 0; ci + 1 < pfds.size() && ci < clients.size(); ++ci) {
+      if (!(pfds[ci + 1].revents & (POLLIN | POLLHUP | POLLERR))) continue;
+      Client& c = clients[ci];
+      if (c.fd < 0) continue;
+      FrameHeader h;
+      std::string key;
+      std::vector<unsigned char> payload;
+      if (!recv_frame(c.fd, &h, &key, &payload, timeout_ms_)) {
+        close_fd(c.fd);   // a node that disappears is simply dropped; its peers time out on data
+        continue;
+      }
+      switch (h.type) {
+        case kInitReq: {
+          if (payload.size() == sizeof(InitReq)) {
+            std::memcpy(&c.req, payload.data(), sizeof(InitReq));
+            c.registered = true;
+            ++registered;
+          }
+          break;
+        }
+        case kModelPut: {
+          models[key] = std::move(payload);
+          send_frame(c.fd, kOk, key, 0, nullptr, 0, timeout_ms_);
+          auto it = model_waiters.find(key);
+          if (it != model_waiters.end()) {
+            for (int w : it->second)
+              if (clients[w].fd >= 0)
+                send_frame(clients[w].fd, kModelRep, key, 0, models[key].data(), models[key].size(), timeout_ms_);
+            model_waiters.erase(it);
+          }
+          break;
+        }
+        case kModelGet: {
+          auto it = models.find(key);
+          if (it != models.end()) send_frame(c.fd, kModelRep, key, 0, it->second.data(), it->second.size(), timeout_ms_);
+          else model_waiters[key].push_back(static_cast<int>(ci));
+          break;
+        }
+        case kSyncTime: {
+          const int64_t t = now_ns();
+          send_frame(c.fd, kSyncTime, "", 0, &t, sizeof(t), timeout_ms_);
+          break;
+        }
+        case kStatRep: {
+          if (payload.size() == sizeof(PeerStat)) {
+            PeerStat s;
+            std::memcpy(&s, payload.data(), sizeof(s));
+            std::lock_guard<std::mutex> lk(stats_mu_);
+            stats_[s.rank] = s;
+          }
+          send_frame(c.fd, kOk, "", 0, nullptr, 0, timeout_ms_);
+          break;
+        }
+        case kBarrier: {
+          barrier_waiters.push_back(static_cast<int>(ci));
+          if (static_cast<int>(barrier_waiters.size()) == world) {
+            for (int w : barrier_waiters)
+              if (clients[w].fd >= 0) send_frame(clients[w].fd, kOk, "", 0, nullptr, 0, timeout_ms_);
+            barrier_waiters.clear();
+          }
+          break;
+        }
+        case kConfigUpd:   // placeholder in the reference too (comm_manager.cpp:312-328)
+          send_frame(c.fd, kOk, "", 0, nullptr, 0, timeout_ms_);
+          break;
+        case kBye:
+          close_fd(c.fd);
+          break;
+        default:
+          break;
+      }
+    }
+    if (!ring_sent && registered == world) {
+      // ring in rank order: the successor of rank r is rank (r + 1) mod world
+      std::map<int, Client*> by_rank;
+      for (auto& c : clients)
+        if (c.registered) by_rank[c.req.rank] = &c;
+      if (static_cast<int>(by_rank.size()) == world) {
+        for (auto& kv : by_rank) {
+          Client* succ = by_rank[(kv.first + 1) % world];
+          InitRes res{};
+          res.success = 1;
+          res.target_port = succ->req.listen_port;
+          res.target_rank = succ->req.rank;
+          std::strncpy(res.target_ip, succ->req.ip, sizeof(res.target_ip) - 1);
+          send_frame(kv.second->fd, kInitRes, "", 0, &res, sizeof(res), timeout_ms_);
+        }
+        ring_sent = true;
+      }
+    }
+  }
+  for (auto& c : clients) close_fd(c.fd);
+}
+
+// ---------------------------------------------------------------- client
+bool CommManager::start_client(int rank, int world, int num_gpus) {
+  rank_ = rank;
+  world_ = world;
+  control_fd_ = tcp_connect(master_addr_, master_port_, timeout_ms_);
+  if (control_fd_ < 0) { set_failed("cannot reach the broker at " + master_addr_); return false; }
+  uint16_t port = 0;
+  data_listen_fd_ = tcp_listen(0, &port, true);
+  if (data_listen_fd_ < 0) { set_failed("cannot open a data port"); return false; }
+  InitReq req{};
+  req.rank = static_cast<uint16_t>(rank);
+  req.listen_port = port;
+  req.num_gpus = static_cast<uint16_t>(num_gpus);
+  req.timestamp_ns = now_ns();
+  const std::string ip = master_addr_ == "127.0.0.1" || master_addr_ == "localhost" ? "127.0.0.1" : pick_local_ip();
+  std::strncpy(req.ip, ip.c_str(), sizeof(req.ip) - 1);
+  FrameHeader h;
+  std::string key;
+  std::vector<unsigned char> payload;
+  {
+    std::lock_guard<std::mutex> lk(control_mu_);
+    if (!send_frame(control_fd_, kInitReq, "", 0, &req, sizeof(req), timeout_ms_) ||
+        !recv_frame(control_fd_, &h, &key, &payload, timeout_ms_) || h.type != kInitRes ||
+        payload.size() != sizeof(InitRes)) {
+      set_failed("rendezvous with the broker failed (are all " + std::to_string(world) + " nodes up?)");
+      return false;
+    }
+  }
+  InitRes res;
+  std::memcpy(&res, payload.data(), sizeof(res));
+  push_fd_ = tcp_connect(res.target_ip, res.target_port, timeout_ms_);
+  pull_fd_ = tcp_accept(data_listen_fd_, timeout_ms_);
+  if (push_fd_ < 0 || pull_fd_ < 0) { set_failed("cannot establish the data ring"); return false; }
+  LOG_INFO("CommManager", "rank " << rank << " -> rank " << res.target_rank << " at " << res.target_ip << ":" << res.target_port);
+  push_thread_ = std::thread([this] { push_main(); });
+  pull_thread_ = std::thread([this] { pull_main(); });
+  return true;
+}
+
+void CommManager::set_tx_fault_hook(std::function<bool(const std::string&, int*)> hook) {
+  std::lock_guard<std::mutex> lk(tx_mu_);
+  tx_hook_ = std::move(hook);
+}
+
+void CommManager::queue_tx(int64_t priority, const std::string& key, const uint32_t* idx, const float* val, size_t count,
+                           uint32_t tensor_numel, bool allow_u16, int value_format) {
+  auto item = std::make_shared<TxItem>();
+  item->priority = priority;
+  item->key = key;
+  item->count = static_cast<uint32_t>(count);
+  item->flags = 0;
+  // index narrowing when every index fits (reference: tensor_numel < 65536, comm_manager.cpp:579-583);
+  // the sentinel index used for padding does not fit and keeps the stream wide
+  bool narrow = allow_u16 && tensor_numel <= 65536;
+  if (narrow)
+    for (size_t i = 0; i < count && narrow; ++i) narrow = idx[i] < 65536u;
+  if (narrow) {
+    item->flags |= kFlagIdxU16;
+    item->idx_bytes.resize(count * 2);
+    narrow_u32_to_u16(idx, reinterpret_cast<uint16_t*>(item->idx_bytes.data()), count);
+  } else {
+    item->idx_bytes.resize(count * 4);
+    std::memcpy(item->idx_bytes.data(), idx, count * 4);
+  }
+  if (value_format == 1) {
+    item->flags |= kFlagValF16;
+    item->val_bytes.resize(count * 2);
+    f32_to_f16(val, reinterpret_cast<uint16_t*>(item->val_bytes.data()), count);
+  } else if (value_format == 2) {
+    item->flags |= kFlagValBF16;
+    item->val_bytes.resize(count * 2);
+    f32_to_bf16(val, reinterpret_cast<uint16_t*>(item->val_bytes.data()), count);
+  } else {
+    item->val_bytes.resize(count * 4);
+    std::memcpy(item->val_bytes.data(), val, count * 4);
+  }
+  {
+    std::lock_guard<std::mutex> lk(tx_mu_);
+    item->seq = tx_seq_++;
+    tx_queue_.push(std::move(item));
+  }
+  tx_cv_.notify_one();
+}
+
+void CommManager::push_main() {
+  pthread_setname_np(pthread_self(), "CommPushThread");
+  while (!stop_) {
+    std::shared_ptr<TxItem> item;
+    std::function<bool(const std::string&, int*)> hook;
+    {
+      std::unique_lock<std::mutex> lk(tx_mu_);
+      tx_cv_.wait_for(lk, std::chrono::milliseconds(100), [this] { return stop_ || !tx_queue_.empty(); });
+      if (stop_) return;
+      if (tx_queue_.empty()) continue;
+      item = tx_queue_.top();
+      tx_queue_.pop();
+      hook = tx_hook_;
+    }
+    if (hook) {
+      int delay = 0;
+      if (hook(item->key, &delay)) continue;   // dropped on purpose by a test
+      if (delay > 0) std::this_thread::sleep_for(std::chrono::milliseconds(delay));
+    }
+    std::vector<unsigned char> payload(4 + item->idx_bytes.size() + item->val_bytes.size());
+    std::memcpy(payload.data(), &item->count, 4);
+    std::memcpy(payload.data() + 4, item->idx_bytes.data(), item->idx_bytes.size());
+    std::memcpy(payload.data() + 4 + item->idx_bytes.size(), item->val_bytes.data(), item->val_bytes.size());
+    if (!send_frame(push_fd_, kGrad, item->key, item->flags, payload.data(), payload.size(), timeout_ms_)) {
+      if (!stop_) set_failed("send to the ring successor failed for " + item->key);
+      return;
+    }
+    bytes_sent_ += sizeof(FrameHeader) + item->key.size() + payload.size();
+  }
+}
+
+void CommManager::pull_main() {
+  pthread_setname_np(pthread_self(), "CommPullThread");
+  while (!stop_) {
+    if (!wait_readable(pull_fd_, 100)) continue;
+    FrameHeader h;
+    std::string key;
+    std::vector<unsigned char> payload;
+    if (!recv_frame(pull_fd_, &h, &key, &payload, timeout_ms_)) {
+      if (!stop_) set_failed("the ring predecessor closed the connection or sent a truncated frame");
+      return;
+    }
+    if (h.type != kGrad || payload.size() < 4) continue;
+    SparseMessage m;
+    m.key = key;
+    m.flags = static_cast<uint8_t>(h.flags);
+    uint32_t count;
+    std::memcpy(&count, payload.data(), 4);
+    const size_t idx_bytes = static_cast<size_t>(count) * ((m.flags & kFlagIdxU16) ? 2 : 4);
+    const size_t val_bytes = static_cast<size_t>(count) * ((m.flags & (kFlagValF16 | kFlagValBF16)) ? 2 : 4);
+    if (payload.size() != 4 + idx_bytes + val_bytes) {
+      set_failed("malformed gradient frame for " + key);
+      return;
+    }
+    m.idx.resize(count);
+    m.val.resize(count);
+    const unsigned char* pi = payload.data() + 4;
+    const unsigned char* pv = pi + idx_bytes;
+    if (m.flags & kFlagIdxU16) widen_u16_to_u32(reinterpret_cast<const uint16_t*>(pi), m.idx.data(), count);
+    else std::memcpy(m.idx.data(), pi, idx_bytes);
+    if (m.flags & kFlagValF16) f16_to_f32(reinterpret_cast<const uint16_t*>(pv), m.val.data(), count);
+    else if (m.flags & kFlagValBF16) bf16_to_f32(reinterpret_cast<const uint16_t*>(pv), m.val.data(), count);
+    else std::memcpy(m.val.data(), pv, val_bytes);
+    m.wire_bytes = sizeof(FrameHeader) + key.size() + payload.size();
+    bytes_recv_ += m.wire_bytes;
+    rx_mon_.add(m.wire_bytes);
+    std::function<void(SparseMessage&&)> cb;
+    {
+      std::lock_guard<std::mutex> lk(rx_mu_);
+      auto it = posted_.find(key);
+      if (it != posted_.end()) {
+        cb = std::move(it->second);
+        posted_.erase(it);
+      } else {
+        stash_[key] = std::move(m);   // arrived before its receive was posted
+      }
+    }
+    if (cb) cb(std::move(m));
+  }
+}
+
+void CommManager::post_recv(const std::string& key, std::function<void(SparseMessage&&)> cb) {
+  SparseMessage m;
+  bool have = false;
+  {
+    std::lock_guard<std::mutex> lk(rx_mu_);
+    auto it = stash_.find(key);
+    if (it != stash_.end()) {
+      m = std::move(it->second);
+      stash_.erase(it);
+      have = true;
+    } else {
+      posted_[key] = std::move(cb);
+    }
+  }
+  if (have) cb(std::move(m));
+}
+
+bool CommManager::cancel_recv(const std::string& key) {
+  std::lock_guard<std::mutex> lk(rx_mu_);
+  return posted_.erase(key) > 0;
+}
+
+size_t CommManager::stashed() const {
+  std::lock_guard<std::mutex> lk(rx_mu_);
+  return stash_.size();
+}
+
+// ---------------------------------------------------------------- control plane
+bool CommManager::control_roundtrip(uint32_t type, const std::string& key, const void* payload, size_t payload_len,
+                                    std::vector<unsigned char>* reply, int timeout_ms) {
+  std::lock_guard<std::mutex> lk(control_mu_);
+  if (control_fd_ < 0) return false;
+  if (!send_frame(control_fd_, type, key, 0, payload, payload_len, timeout_ms)) return false;
+  FrameHeader h;
+  std::string rkey;
+  std::vector<unsigned char> rp;
+  if (!recv_frame(control_fd_, &h, &rkey, &rp, timeout_ms)) return false;
+  if (reply) *reply = std::move(rp);
+  return true;
+}
+
+bool CommManager::send_init_model(const std::string& key, const float* data, size_t n) {
+  return control_roundtrip(kModelPut, key, data, n * sizeof(float), nullptr, timeout_ms_);
+}
+
+bool CommManager::recv_init_model(const std::string& key, float* data, size_t n) {
+  std::vector<unsigned char> reply;
+  if (!control_roundtrip(kModelGet, key, nullptr, 0, &reply, timeout_ms_)) return false;
+  if (reply.size() != n * sizeof(float)) return false;
+  std::memcpy(data, reply.data(), reply.size());
+  return true;
+}
+
+bool CommManager::global_barrier() { return control_roundtrip(kBarrier, "", nullptr, 0, nullptr, timeout_ms_); }
+
+double CommManager::sync_time(int pings) {
+  // offset = server_time - (t_send + t_recv) / 2, smoothed with weights 0.9 / 0.1 (reference 286-311)
+  double offset_ms = 0.0;
+  bool first = true;
+  for (int i = 0; i < pings; ++i) {
+    const int64_t t0 = now_ns();
+    std::vector<unsigned char> reply;
+    if (!control_roundtrip(kSyncTime, "", &t0, sizeof(t0), &reply, timeout_ms_) || reply.size() != sizeof(int64_t)) break;
+    const int64_t t1 = now_ns();
+    int64_t ts;
+    std::memcpy(&ts, reply.data(), sizeof(ts));
+    const double off = (static_cast<double>(ts) - (static_cast<double>(t0) + static_cast<double>(t1)) / 2.0) / 1e6;
+    offset_ms = first ? off : 0.9 * offset_ms + 0.1 * off;
+    first = false;
+  }
+  return offset_ms;
+}
+
+bool CommManager::report_stat(double send_mbps, double recv_mbps) {
+  PeerStat s{rank_, send_mbps, recv_mbps, 0.0};
+  return control_roundtrip(kStatRep, "", &s, sizeof(s), nullptr, timeout_ms_);
+}
+
+std::vector<PeerStat> CommManager::broker_stats() {
+  std::lock_guard<std::mutex> lk(stats_mu_);
+  std::vector<PeerStat> out;
+  for (auto& kv : stats_) out.push_back(kv.second);
+  return out;
+}
+
+}  // namespace stc

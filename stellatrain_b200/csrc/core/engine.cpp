@@ -1,0 +1,480 @@
+#include "engine.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <sstream>
+#include <stdexcept>
+
+#include "../cpu/array_util.h"
+#include "config.h"
+#include "logger.h"
+
+namespace stc {
+
+struct SharedParamEntry {
+  char name[cfg::kMaxNameLen + 1];
+  uint32_t numel;
+  uint32_t ready;      // 0 absent, 1 allocated and initialised locally, 2 synchronised across nodes
+  uint64_t master_off, resid_off;
+  uint64_t slot_off[2][cfg::kMaxLocalRanks];
+};
+
+using Clock = std::chrono::steady_clock;
+
+CpuEngine::CpuEngine() = default;
+
+CpuEngine::~CpuEngine() {
+  stop_ = true;
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    version_cv_.notify_all();
+  }
+  if (barrier_thread_.joinable()) barrier_thread_.join();
+  pool_.reset();      // joins the workers before the memory they use goes away
+  comm_.reset();
+  shm_.reset();
+}
+
+// ---------------------------------------------------------------- configuration
+void CpuEngine::configure(const EngineOptions& o) {
+  if (ready_) throw std::runtime_error("engine is already configured");
+  if (o.local_world < 1 || o.local_world > cfg::kMaxLocalRanks) throw std::invalid_argument("local_world out of range");
+  if (o.staleness < 0 || o.staleness > 1) throw std::invalid_argument("staleness must be 0 or 1");
+  opt_ = o;
+  ratio_ = o.ratio;
+  const int workers = o.workers > 0 ? o.workers : (node_master() ? cfg::kWorkersNodeMaster : cfg::kWorkersOther);
+  pool_ = std::make_unique<ThreadPool>(static_cast<size_t>(workers));
+  const size_t data_bytes = o.data_bytes ? o.data_bytes : static_cast<size_t>(cfg::env_long("STELLATRAIN_SHM_BYTES", static_cast<long>(cfg::kShmDataBytes)));
+  const size_t meta_bytes = o.meta_bytes ? o.meta_bytes : cfg::kShmMetaBytes;
+  shm_ = std::make_unique<ShmManager>(node_master(), o.session, o.local_rank, o.local_world, data_bytes, meta_bytes, o.timeout_ms);
+  const size_t table_bytes = 64 + sizeof(SharedParamEntry) * cfg::kMaxParams;
+  unsigned char* base;
+  if (node_master()) {
+    base = static_cast<unsigned char*>(shm_->alloc_meta(table_bytes));
+    std::memset(base, 0, table_bytes);
+    if (base != shm_->meta_first()) throw std::logic_error("parameter table is not the first metadata allocation");
+  } else {
+    base = static_cast<unsigned char*>(shm_->meta_first());
+  }
+  table_count_ = reinterpret_cast<uint32_t*>(base);
+  table_ = reinterpret_cast<SharedParamEntry*>(base + 64);
+  if (o.pin_cuda) shm_->pin_for_cuda();
+  compressor_ = make_compressor(o.method, pool_.get());
+  optimizer_ = make_optimizer("sgd");
+  load_modules();
+  if (o.world > 1 && node_master()) {
+    comm_ = std::make_unique<CommManager>(o.master_addr, o.master_port, o.timeout_ms);
+    if (o.rank == 0) comm_->start_server(o.world);
+    if (!comm_->start_client(o.rank, o.world, o.local_world)) throw std::runtime_error("comm start failed: " + comm_->failure());
+  }
+  if (!shm_->barrier(o.timeout_ms)) throw std::runtime_error("local processes did not all reach configure()");
+  barrier_thread_ = std::thread([this] { barrier_manager_main(); });
+  ready_ = true;
+}
+
+void CpuEngine::set_optimizer(const std::string& name) { optimizer_ = make_optimizer(name); }
+
+void CpuEngine::configure_compression(const std::string& method) { compressor_ = make_compressor(method, pool_.get()); }
+
+void CpuEngine::configure_compression_ratio(double ratio) {
+  if (!(ratio > 0.0 && ratio <= 1.0)) throw std::invalid_argument("compression ratio must be in (0, 1]");
+  ratio_ = ratio;
+}
+
+void CpuEngine::barrier() {
+  if (!shm_->barrier(opt_.timeout_ms)) throw std::runtime_error("node barrier timed out");
+  if (comm_ && !comm_->global_barrier()) throw std::runtime_error("global barrier timed out");
+  if (!shm_->barrier(opt_.timeout_ms)) throw std::runtime_error("node barrier timed out");
+}
+
+// ---------------------------------------------------------------- registration
+int CpuEngine::pre_train_init(int layer, const std::string& name, uint32_t numel, float* user_param) {
+  if (!ready_) throw std::runtime_error("configure() first");
+  const int index = static_cast<int>(params_.size());
+  if (index >= cfg::kMaxParams) throw std::runtime_error("too many parameters");
+  const std::string pkey = std::to_string(layer) + "@" + name;
+  if (static_cast<int>(pkey.size()) > cfg::kMaxNameLen) throw std::runtime_error("parameter key too long: " + pkey);
+  SharedParamEntry* e = &table_[index];
+  const int N = opt_.local_world;
+  if (node_master()) {
+    std::strncpy(e->name, pkey.c_str(), cfg::kMaxNameLen);
+    e->numel = numel;
+    const size_t bytes = static_cast<size_t>(numel) * sizeof(float);
+    float* master = static_cast<float*>(shm_->alloc(bytes));
+    float* resid = static_cast<float*>(shm_->alloc(bytes));
+    std::memset(resid, 0, bytes);
+    if (user_param) std::memcpy(master, user_param, bytes); else std::memset(master, 0, bytes);
+    e->master_off = shm_->offset_of(master);
+    e->resid_off = shm_->offset_of(resid);
+    for (int s = 0; s < 2; ++s)
+      for (int r = 0; r < N; ++r) {
+        float* g = static_cast<float*>(shm_->alloc(bytes));
+        std::memset(g, 0, bytes);
+        e->slot_off[s][r] = shm_->offset_of(g);
+      }
+    __atomic_store_n(&e->ready, 1u, __ATOMIC_RELEASE);
+    // every node starts from rank 0's values (reference core.cpp:841-885)
+    if (comm_) {
+      const std::string key = "init@" + pkey;
+      const bool ok = opt_.rank == 0 ? comm_->send_init_model(key, master, numel) : comm_->recv_init_model(key, master, numel);
+      if (!ok) throw std::runtime_error("initial model exchange failed for " + pkey);
+    }
+    __atomic_store_n(&e->ready, 2u, __ATOMIC_RELEASE);
+    __atomic_store_n(table_count_, static_cast<uint32_t>(index + 1), __ATOMIC_RELEASE);
+  } else {
+    const auto t0 = Clock::now();
+    while (__atomic_load_n(&e->ready, __ATOMIC_ACQUIRE) != 2u) {
+      if (Clock::now() - t0 > std::chrono::milliseconds(opt_.timeout_ms))
+        throw std::runtime_error("node master never registered parameter " + pkey);
+      std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    if (pkey != e->name || e->numel != numel)
+      throw std::runtime_error("parameter registration order differs between local processes at " + pkey);
+  }
+  ParamLocal p;
+  p.layer = layer;
+  p.name = name;
+  p.numel = numel;
+  p.user_param = user_param;
+  p.master = static_cast<float*>(shm_->from_offset(e->master_off));
+  p.resid = static_cast<float*>(shm_->from_offset(e->resid_off));
+  for (int s = 0; s < 2; ++s)
+    for (int r = 0; r < N; ++r) p.slot[s].push_back(static_cast<float*>(shm_->from_offset(e->slot_off[s][r])));
+  if (user_param) std::memcpy(user_param, p.master, static_cast<size_t>(numel) * sizeof(float));
+  params_.push_back(std::move(p));
+  return index;
+}
+
+const float* CpuEngine::master_param(int index) const { return params_.at(index).master; }
+
+int64_t CpuEngine::model_version(int index) const { return params_.at(index).model_version; }
+
+// ---------------------------------------------------------------- forward gate
+void CpuEngine::pre_forward_process(int index) {
+  ParamLocal& p = params_.at(index);
+  std::unique_lock<std::mutex> lk(version_mu_);
+  const int64_t j = p.iteration_cnt++;
+  const int64_t need = j - opt_.staleness;
+  const bool ok = version_cv_.wait_for(lk, std::chrono::milliseconds(opt_.timeout_ms), [&] {
+    return stop_ || !first_error_.empty() || p.model_version >= need;
+  });
+  if (!first_error_.empty()) throw std::runtime_error("pipeline failed: " + first_error_);
+  if (!ok) throw std::runtime_error("timed out waiting for update " + std::to_string(need) + " of " + p.name);
+}
+
+// ---------------------------------------------------------------- backward
+float* CpuEngine::grad_slot(int index) {
+  ParamLocal& p = params_.at(index);
+  return p.slot[p.alloc_cnt % 2][opt_.local_rank];
+}
+
+void CpuEngine::post_backward_process(int index, const float* grad) {
+  ParamLocal& p = params_.at(index);
+  float* slot = grad_slot(index);
+  if (p.micro == 0) std::memcpy(slot, grad, static_cast<size_t>(p.numel) * sizeof(float));
+  else add_arrays(slot, grad, p.numel);
+  if (++p.micro < opt_.grad_accumulation) return;
+  p.micro = 0;
+  start_task(index);
+}
+
+void CpuEngine::post_backward_in_slot(int index) {
+  ParamLocal& p = params_.at(index);
+  if (++p.micro < opt_.grad_accumulation) return;
+  p.micro = 0;
+  start_task(index);
+}
+
+void CpuEngine::notify_layer_usage_finished(ParamLocal& p, int64_t iter) {
+  std::lock_guard<std::mutex> lk(version_mu_);
+  p.completed_version = std::max<int64_t>(-1, iter - opt_.staleness);
+}
+
+void CpuEngine::start_task(int index) {
+  ParamLocal& p = params_.at(index);
+  const int64_t iter = p.alloc_cnt++;
+  notify_layer_usage_finished(p, iter);
+  auto task = std::make_shared<TrainTask>(iter, p.layer, p.name);
+  task->numel = p.numel;
+  task->param_index = index;
+  task->stat_start("Total");
+  auto prom = std::make_shared<std::promise<void>>();
+  {
+    std::lock_guard<std::mutex> lk(tasks_mu_);
+    tasks_[task->key] = task;
+    promises_[task->key] = prom;
+    futures_.emplace_back(task->key, prom->get_future().share());
+  }
+  // tasks blocked on "previous version no longer in use" may be able to run now
+  std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> runnable;
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    for (auto it = waiting_model_.begin(); it != waiting_model_.end();) {
+      ParamLocal& q = params_[it->second->param_index];
+      if (q.completed_version >= it->second->iter) {
+        runnable.push_back(*it);
+        it = waiting_model_.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  }
+  for (auto& r : runnable) schedule(r.first, r.second);
+  Module* first = opt_.debug_barrier && !p.checked_barrier ? module("BarrierChecker") : module("CopyIn");
+  p.checked_barrier = true;
+  schedule_after_use(first, task);
+}
+
+// ---------------------------------------------------------------- module API
+void CpuEngine::schedule(Module* m, const std::shared_ptr<TrainTask>& t) {
+  pool_->enqueue(t->priority(), [this, m, t] {
+    if (t->state() == TaskState::Failed) return;
+    try {
+      t->stat_start(m->name());
+      m->run(*this, t);
+      t->stat_end(m->name());
+    } catch (const std::exception& e) {
+      fail_task(t, std::string(m->name()) + ": " + e.what());
+    }
+  });
+}
+
+void CpuEngine::fail_task(const std::shared_ptr<TrainTask>& t, const std::string& why) {
+  LOG_ERROR("CpuEngine", "task " << t->key << " failed: " << why);
+  t->fail(why);
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    if (first_error_.empty()) first_error_ = t->key + ": " + why;
+    version_cv_.notify_all();
+  }
+  std::shared_ptr<std::promise<void>> prom;
+  {
+    std::lock_guard<std::mutex> lk(tasks_mu_);
+    auto it = promises_.find(t->key);
+    if (it != promises_.end()) { prom = it->second; promises_.erase(it); }
+    tasks_.erase(t->key);
+  }
+  if (prom) prom->set_exception(std::make_exception_ptr(std::runtime_error(t->key + ": " + why)));
+}
+
+void CpuEngine::schedule_after_barrier(Module* next, const std::shared_ptr<TrainTask>& t, int stage_id) {
+  const int N = opt_.local_world;
+  if (N == 1) { schedule(next, t); return; }
+  const uint64_t key = t->barrier_key(stage_id);
+  if (shm_->arrive(key, N)) {
+    shm_->depart(key, N);
+    schedule(next, t);
+    return;
+  }
+  std::lock_guard<std::mutex> lk(barrier_mu_);
+  pending_barriers_.push_back({key, next, t, Clock::now() + std::chrono::milliseconds(opt_.timeout_ms)});
+}
+
+void CpuEngine::barrier_manager_main() {
+  pthread_setname_np(pthread_self(), "BarrierManager");
+  while (!stop_) {
+    shm_->wait_change(5);
+    std::list<PendingBarrier> done, late;
+    {
+      std::lock_guard<std::mutex> lk(barrier_mu_);
+      const auto now = Clock::now();
+      for (auto it = pending_barriers_.begin(); it != pending_barriers_.end();) {
+        if (shm_->complete(it->key)) { done.push_back(*it); it = pending_barriers_.erase(it); }
+        else if (now > it->deadline) { late.push_back(*it); it = pending_barriers_.erase(it); }
+        else ++it;
+      }
+    }
+    for (auto& b : done) {
+      shm_->depart(b.key, opt_.local_world);
+      schedule(b.next, b.task);
+    }
+    for (auto& b : late) fail_task(b.task, "a local process did not reach the barrier before " + std::string(b.next->name()));
+  }
+}
+
+void CpuEngine::schedule_after_comm(Module* next, const std::shared_ptr<TrainTask>& t, const std::string& key, int slot) {
+  if (!comm_) throw std::logic_error("schedule_after_comm without a comm manager");
+  comm_->post_recv(key, [this, next, t, slot](SparseMessage&& m) {
+    const size_t k = t->k;
+    const size_t n = std::min(m.idx.size(), k);
+    std::copy(m.idx.begin(), m.idx.begin() + static_cast<long>(n), t->idx.begin() + static_cast<long>(slot * k));
+    std::copy(m.val.begin(), m.val.begin() + static_cast<long>(n), t->val.begin() + static_cast<long>(slot * k));
+    t->counts[slot] = n;
+    ++t->exchange_round;
+    schedule(next, t);
+  });
+}
+
+void CpuEngine::schedule_after_model_complete(Module* next, const std::shared_ptr<TrainTask>& t) {
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    if (params_[t->param_index].completed_version < t->iter) {
+      waiting_model_.emplace_back(next, t);
+      return;
+    }
+  }
+  schedule(next, t);
+}
+
+void CpuEngine::schedule_after_use(Module* next, const std::shared_ptr<TrainTask>& t) {
+  const std::string slot_key = t->persistent_key + "#" + std::to_string(t->iter % 2);
+  {
+    std::lock_guard<std::mutex> lk(use_mu_);
+    if (in_use_[slot_key]) {
+      use_waiters_[slot_key].emplace_back(next, t);
+      return;
+    }
+    in_use_[slot_key] = true;
+  }
+  schedule(next, t);
+}
+
+void CpuEngine::return_after_use(const std::shared_ptr<TrainTask>& t) {
+  const std::string slot_key = t->persistent_key + "#" + std::to_string(t->iter % 2);
+  std::pair<Module*, std::shared_ptr<TrainTask>> next{nullptr, nullptr};
+  {
+    std::lock_guard<std::mutex> lk(use_mu_);
+    auto& q = use_waiters_[slot_key];
+    if (q.empty()) in_use_[slot_key] = false;
+    else { next = q.front(); q.pop_front(); }
+  }
+  if (next.first) schedule(next.first, next.second);
+}
+
+void CpuEngine::update_model_version(const std::shared_ptr<TrainTask>& t) {
+  std::lock_guard<std::mutex> lk(version_mu_);
+  ++params_[t->param_index].model_version;
+  version_cv_.notify_all();
+}
+
+void CpuEngine::schedule_terminate(const std::shared_ptr<TrainTask>& t) {
+  t->stat_end("Total");
+  {
+    std::lock_guard<std::mutex> lk(stats_mu_);
+    stat_ring_.emplace_back(t->key, t->stats());
+    if (stat_ring_.size() > 8192) stat_ring_.pop_front();   // bounded, unlike the reference's map
+  }
+  std::shared_ptr<std::promise<void>> prom;
+  {
+    std::lock_guard<std::mutex> lk(tasks_mu_);
+    auto it = promises_.find(t->key);
+    if (it != promises_.end()) { prom = it->second; promises_.erase(it); }
+    tasks_.erase(t->key);
+  }
+  if (prom) prom->set_value();
+}
+
+void CpuEngine::push_ready_update(int index, int64_t iter) {
+  std::lock_guard<std::mutex> lk(ready_mu_);
+  ready_updates_.emplace_back(index, iter);
+  ready_cv_.notify_all();
+}
+
+std::vector<std::pair<int, int64_t>> CpuEngine::pop_ready_updates(int max_wait_ms) {
+  std::unique_lock<std::mutex> lk(ready_mu_);
+  if (ready_updates_.empty() && max_wait_ms > 0)
+    ready_cv_.wait_for(lk, std::chrono::milliseconds(max_wait_ms), [this] { return !ready_updates_.empty() || stop_; });
+  std::vector<std::pair<int, int64_t>> out(ready_updates_.begin(), ready_updates_.end());
+  ready_updates_.clear();
+  return out;
+}
+
+void CpuEngine::copy_out_done(int index, int64_t iter) {
+  ParamLocal& p = params_.at(index);
+  std::shared_ptr<TrainTask> t;
+  {
+    std::lock_guard<std::mutex> lk(tasks_mu_);
+    auto it = tasks_.find(std::to_string(iter) + "@" + std::to_string(p.layer) + "@" + p.name);
+    if (it == tasks_.end()) throw std::runtime_error("copy_out_done for an unknown task");
+    t = it->second;
+  }
+  t->advance(TaskState::Finished);
+  update_model_version(t);
+  return_after_use(t);
+  schedule_terminate(t);
+}
+
+// ---------------------------------------------------------------- synchronize
+void CpuEngine::synchronize() {
+  // release every "previous version still in use" gate (reference core.cpp:910-922)
+  std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> runnable;
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    for (auto& p : params_) p.completed_version = p.alloc_cnt - 1;
+    runnable.swap(waiting_model_);
+  }
+  for (auto& r : runnable) schedule(r.first, r.second);
+  std::list<std::pair<std::string, std::shared_future<void>>> futs;
+  {
+    std::lock_guard<std::mutex> lk(tasks_mu_);
+    futs.swap(futures_);
+  }
+  std::string err;
+  const auto deadline = Clock::now() + std::chrono::milliseconds(opt_.timeout_ms);
+  for (auto& f : futs) {
+    for (;;) {
+      const auto st = f.second.wait_for(std::chrono::seconds(5));
+      if (st == std::future_status::ready) break;
+      LOG_WARN("CpuEngine", "waiting for " << f.first << " for more than 5 s (" << futs.size() << " tasks in flight)");
+      if (Clock::now() > deadline) {
+        err = "synchronize timed out on " + f.first;
+        break;
+      }
+    }
+    if (!err.empty()) break;
+    try {
+      f.second.get();
+    } catch (const std::exception& e) {
+      if (err.empty()) err = e.what();
+    }
+  }
+  if (!err.empty()) throw std::runtime_error(err);
+}
+
+// ---------------------------------------------------------------- model sync
+double CpuEngine::force_model_sync(int index, bool dry_run) {
+  ParamLocal& p = params_.at(index);
+  double drift = 0.0;
+  static std::atomic<uint64_t> serial{0};
+  if (comm_ && node_master()) {
+    const std::string key = "sync" + std::to_string(serial++) + "@" + std::to_string(p.layer) + "@" + p.name;
+    if (opt_.rank == 0) {
+      if (!comm_->send_init_model(key, p.master, p.numel)) throw std::runtime_error("model sync send failed");
+    } else {
+      std::vector<float> ref(p.numel);
+      if (!comm_->recv_init_model(key, ref.data(), p.numel)) throw std::runtime_error("model sync receive failed");
+      for (uint32_t i = 0; i < p.numel; ++i) drift = std::max(drift, static_cast<double>(std::fabs(ref[i] - p.master[i])));
+      if (!dry_run) std::memcpy(p.master, ref.data(), static_cast<size_t>(p.numel) * sizeof(float));
+    }
+  }
+  if (!dry_run && p.user_param) {
+    if (!shm_->barrier(opt_.timeout_ms)) throw std::runtime_error("node barrier timed out in model sync");
+    std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
+  }
+  return drift;
+}
+
+// ---------------------------------------------------------------- stats
+std::string CpuEngine::stats_json(bool clear) {
+  std::lock_guard<std::mutex> lk(stats_mu_);
+  std::ostringstream os;
+  os << "{";
+  bool first = true;
+  for (auto& kv : stat_ring_) {
+    os << (first ? "" : ",") << "\"" << kv.first << "\":{";
+    bool f2 = true;
+    for (auto& ev : kv.second) {
+      os << (f2 ? "" : ",") << "\"" << ev.first << "\":" << ev.second;
+      f2 = false;
+    }
+    os << "}";
+    first = false;
+  }
+  os << "}";
+  if (clear) stat_ring_.clear();
+  return os.str();
+}
+
+}  // namespace stc

@@ -1,0 +1,204 @@
+// Engine of the CPU-offload tier: per-parameter task pipeline over shared memory and TCP.
+//
+// Structure after the reference's FasterDpEngine and its module API
+// (backend/src/engine/core.h:47-310, core.cpp:64-183 configure, 712-758 pre_forward_process, 761-834
+// pre_train_init, 1025-1095 post_backward_process, 1097-1140 synchronize_backend; core_module_api.cpp:
+// schedule 7-24, schedule_terminate 27-40, schedule_after_use 43-109, schedule_after_barrier 113-199,
+// schedule_after_model_complete 279-310, schedule_after_comm 313-375, update_model_version 462-472).
+// One process per local device; the processes of a node share gradients and master parameters through
+// ShmManager, the node master compresses, exchanges and optimises; nodes form a TCP ring.
+//
+// Device copies stay in the framework: the engine works on host pointers.  For CUDA training the
+// Python side copies gradients into the pinned shared slots and parameters back (see
+// stellatrain_b200/cpu_tier.py); for host tensors the engine copies by itself.
+//
+// Every wait is bounded: a timeout marks the task Failed and surfaces as an exception from
+// synchronize()/pre_forward(), it never blocks forever.
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <cstdint>
+#include <functional>
+#include <future>
+#include <list>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../comm/comm_manager.h"
+#include "../cpu/compressors.h"
+#include "../cpu/optimizers.h"
+#include "shm_manager.h"
+#include "task.h"
+#include "threadpool.h"
+
+namespace stc {
+
+struct EngineOptions {
+  std::string master_addr = "127.0.0.1";
+  uint16_t master_port = 5555;
+  int world = 1;              // nodes
+  int rank = 0;               // node rank
+  int64_t session = 0;        // names the node's shared-memory segments
+  int local_world = 1;
+  int local_rank = 0;
+  std::string method = "thresholdv16";
+  int grad_accumulation = 1;
+  int staleness = 1;
+  double ratio = 0.99;        // fraction dropped
+  size_t data_bytes = 0;      // 0: default from config.h
+  size_t meta_bytes = 0;
+  int timeout_ms = 30000;
+  int workers = 0;            // 0: 32 on the node master, 16 otherwise
+  bool pin_cuda = false;      // cudaHostRegister the data segment
+  bool debug_accuracy = false;
+  bool debug_barrier = false; // run the barrier self-check before the first task of every parameter
+};
+
+struct SharedParamEntry;       // row of the parameter table in shared memory
+
+class CpuEngine;
+
+// A pipeline stage ("module" in the reference, backend/src/engine/modules/module.h:18-34).
+class Module {
+ public:
+  virtual ~Module() = default;
+  virtual const char* name() const = 0;
+  virtual void run(CpuEngine& engine, const std::shared_ptr<TrainTask>& task) = 0;
+};
+
+class CpuEngine {
+ public:
+  CpuEngine();
+  ~CpuEngine();
+
+  // ---- lifecycle and configuration
+  void configure(const EngineOptions& opt);
+  bool ready() const { return ready_; }
+  const EngineOptions& options() const { return opt_; }
+  bool node_master() const { return opt_.local_rank == 0; }
+  void set_optimizer(const std::string& name);
+  SparseOptimizer* sparse_optimizer() { return optimizer_.get(); }
+  void configure_compression(const std::string& method);
+  void configure_compression_ratio(double ratio);
+  double compression_ratio() const { return ratio_; }
+  int gradient_accumulation() const { return opt_.grad_accumulation; }
+  void barrier();               // all processes of all nodes
+  void synchronize();           // flush the pipeline (throws on failed tasks)
+  std::string stats_json(bool clear);
+
+  // ---- per-parameter protocol
+  // Registers a parameter (same order in every process).  `user_param` may be null when the caller
+  // moves data itself.  Returns the parameter index.
+  int pre_train_init(int layer, const std::string& name, uint32_t numel, float* user_param);
+  void pre_forward_process(int param_index);
+  // `grad` is a host pointer with numel floats; it is accumulated into this process's slot of the
+  // current iteration.  The last micro-iteration starts the pipeline.
+  void post_backward_process(int param_index, const float* grad);
+  // Callers that copy by themselves:
+  float* grad_slot(int param_index);              // where to put this iteration's gradient (zeroed by the engine)
+  void post_backward_in_slot(int param_index);    // gradient already is in grad_slot()
+  const float* master_param(int param_index) const;
+  // Updates whose parameters are ready to be copied out by the caller: (param_index, iteration)
+  std::vector<std::pair<int, int64_t>> pop_ready_updates(int max_wait_ms);
+  void copy_out_done(int param_index, int64_t iter);
+  double force_model_sync(int param_index, bool dry_run);
+  int64_t model_version(int param_index) const;
+  int num_params() const { return static_cast<int>(params_.size()); }
+
+  // ---- module API used by the stages
+  void schedule(Module* m, const std::shared_ptr<TrainTask>& t);
+  void schedule_after_barrier(Module* m, const std::shared_ptr<TrainTask>& t, int stage_id);
+  void schedule_after_comm(Module* m, const std::shared_ptr<TrainTask>& t, const std::string& key, int slot);
+  void schedule_after_model_complete(Module* m, const std::shared_ptr<TrainTask>& t);
+  void schedule_after_use(Module* m, const std::shared_ptr<TrainTask>& t);
+  void return_after_use(const std::shared_ptr<TrainTask>& t);
+  void schedule_terminate(const std::shared_ptr<TrainTask>& t);
+  void update_model_version(const std::shared_ptr<TrainTask>& t);
+  void fail_task(const std::shared_ptr<TrainTask>& t, const std::string& why);
+
+  // accessors for stages
+  ShmManager& shm() { return *shm_; }
+  CommManager* comm() { return comm_.get(); }
+  ThreadPool& pool() { return *pool_; }
+  Compressor& compressor() { return *compressor_; }
+  struct ParamLocal {
+    int layer = 0;
+    std::string name;
+    uint32_t numel = 0;
+    float* user_param = nullptr;
+    float* master = nullptr;                 // shared master copy
+    float* resid = nullptr;                  // shared residual (node master writes)
+    std::vector<float*> slot[2];             // [iter % 2][local rank]
+    int64_t iteration_cnt = 0;               // forwards seen
+    int64_t model_version = 0;               // updates applied
+    int64_t alloc_cnt = 0;                   // backwards (tasks) created
+    int64_t completed_version = -1;
+    int micro = 0;
+    bool checked_barrier = false;
+    std::vector<float> merge_scratch;        // node master: dense accumulator of the merge
+    std::vector<uint8_t> merge_touched;
+  };
+  ParamLocal& param(int index) { return params_[index]; }
+  Module* module(const std::string& name) { return modules_.at(name).get(); }
+  void push_ready_update(int param_index, int64_t iter);
+
+ private:
+  void load_modules();
+  void barrier_manager_main();
+  void start_task(int param_index);
+  void notify_layer_usage_finished(ParamLocal& p, int64_t iter);
+
+  EngineOptions opt_;
+  std::atomic<bool> ready_{false};
+  std::atomic<bool> stop_{false};
+  double ratio_ = 0.99;
+  std::unique_ptr<ThreadPool> pool_;
+  std::unique_ptr<ShmManager> shm_;
+  std::unique_ptr<CommManager> comm_;
+  std::unique_ptr<Compressor> compressor_;
+  std::unique_ptr<SparseOptimizer> optimizer_;
+  std::map<std::string, std::unique_ptr<Module>> modules_;
+  SharedParamEntry* table_ = nullptr;
+  uint32_t* table_count_ = nullptr;
+  std::vector<ParamLocal> params_;
+
+  // barrier manager
+  struct PendingBarrier {
+    uint64_t key;
+    Module* next;
+    std::shared_ptr<TrainTask> task;
+    std::chrono::steady_clock::time_point deadline;
+  };
+  std::thread barrier_thread_;
+  std::mutex barrier_mu_;
+  std::list<PendingBarrier> pending_barriers_;
+
+  // model-version gates
+  std::mutex version_mu_;
+  std::condition_variable version_cv_;
+  std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_model_;
+
+  // exclusive use of (parameter, slot)
+  std::mutex use_mu_;
+  std::map<std::string, bool> in_use_;
+  std::map<std::string, std::list<std::pair<Module*, std::shared_ptr<TrainTask>>>> use_waiters_;
+
+  // bookkeeping
+  std::mutex tasks_mu_;
+  std::map<std::string, std::shared_ptr<TrainTask>> tasks_;
+  std::list<std::pair<std::string, std::shared_future<void>>> futures_;
+  std::map<std::string, std::shared_ptr<std::promise<void>>> promises_;
+  std::string first_error_;
+  std::mutex stats_mu_;
+  std::list<std::pair<std::string, std::map<std::string, double>>> stat_ring_;   // bounded history
+
+  std::mutex ready_mu_;
+  std::condition_variable ready_cv_;
+  std::list<std::pair<int, int64_t>> ready_updates_;
+};
+
+}  // namespace stc

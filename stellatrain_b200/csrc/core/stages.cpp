@@ -1,0 +1,234 @@
+// Pipeline stages of the CPU tier, in execution order.  Stage-by-stage counterpart of the
+// reference's modules (backend/src/engine/modules/: d2h_copy.cpp:20-94, cpu_gather.cpp:32-92,
+// compress.cpp:19-216, grad_exchange.cpp:18-81, cpu_optimize.cpp:26-140, h2d_copy.cpp:15-72,
+// barrier_checker.cpp:5-30, null.cpp:3-9), instantiated by load_modules like core_module_load.cpp:15-28.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <stdexcept>
+
+#include "../cpu/array_util.h"
+#include "config.h"
+#include "engine.h"
+#include "logger.h"
+
+namespace stc {
+
+namespace {
+
+enum BarrierStage : int { kAfterCopyIn = 0, kAfterGather = 1, kAfterOptimize = 2, kCheckerBase = 16 };
+
+uint32_t entries_for(uint32_t numel, double ratio, int world) {
+  // k = max(min(n, 1), n * (1 - ratio) / W)   (reference compress.cpp:44-52)
+  const double k_frac = (1.0 - ratio) / std::max(1, world);
+  const uint32_t k = static_cast<uint32_t>(static_cast<double>(numel) * k_frac);
+  return std::min(numel, std::max<uint32_t>(std::min<uint32_t>(numel, 1u), k));
+}
+
+class ModuleNull : public Module {
+ public:
+  const char* name() const override { return "Null"; }
+  void run(CpuEngine&, const std::shared_ptr<TrainTask>&) override {}
+};
+
+// Writes this process's slot of a scratch line and reads the neighbour's through 60 barrier rounds;
+// a lost wake-up or a miscounted barrier shows up as a wrong value or a timeout.
+class ModuleBarrierChecker : public Module {
+ public:
+  const char* name() const override { return "BarrierChecker"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    auto& p = e.param(t->param_index);
+    const int N = e.options().local_world, r = e.options().local_rank;
+    std::lock_guard<std::mutex> lk(mu_);
+    int& round = rounds_[t->key];
+    float* mine = p.slot[t->iter % 2][r];
+    if (round > 0 && N > 1 && p.numel >= 1) {
+      const float seen = p.slot[t->iter % 2][(r + 1) % N][0];
+      if (seen != static_cast<float>(-round)) throw std::runtime_error("barrier self-check read a stale value");
+    }
+    if (round == 60) {
+      rounds_.erase(t->key);
+      // restore: the real gradient was parked in the task while the check ran
+      std::memcpy(mine, parked_[t->key].data(), static_cast<size_t>(p.numel) * sizeof(float));
+      parked_.erase(t->key);
+      e.schedule_after_barrier(e.module("CopyIn"), t, kCheckerBase + 61);
+      return;
+    }
+    if (round == 0) parked_[t->key].assign(mine, mine + p.numel);
+    ++round;
+    if (p.numel >= 1) mine[0] = static_cast<float>(-round);
+    e.schedule_after_barrier(this, t, kCheckerBase + round);
+  }
+
+ private:
+  std::mutex mu_;
+  std::map<std::string, int> rounds_;
+  std::map<std::string, std::vector<float>> parked_;
+};
+
+class ModuleCopyIn : public Module {
+ public:
+  const char* name() const override { return "CopyIn"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    t->advance(TaskState::CopyIn);
+    if (e.options().debug_accuracy) {
+      auto& p = e.param(t->param_index);
+      if (has_nan(p.slot[t->iter % 2][e.options().local_rank], p.numel)) throw std::runtime_error("NaN in the gradient");
+    }
+    e.schedule_after_barrier(e.module("Gather"), t, kAfterCopyIn);
+  }
+};
+
+class ModuleGather : public Module {
+ public:
+  const char* name() const override { return "Gather"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    t->advance(TaskState::Gather);
+    auto& p = e.param(t->param_index);
+    const int N = e.options().local_world, r = e.options().local_rank;
+    const size_t len = p.numel;
+    const size_t b = len * static_cast<size_t>(r) / N, en = len * static_cast<size_t>(r + 1) / N;
+    float* dst = p.slot[t->iter % 2][0] + b;
+    t->stat_start("CRIT_PATH_gather");
+    add_arrays(dst, p.resid + b, en - b);                       // error feedback (shared residual)
+    for (int g = 1; g < N; ++g) add_arrays(dst, p.slot[t->iter % 2][g] + b, en - b);
+    t->stat_end("CRIT_PATH_gather");
+    e.schedule_after_barrier(e.module("Compress"), t, kAfterGather);
+  }
+};
+
+class ModuleCompress : public Module {
+ public:
+  const char* name() const override { return "Compress"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    t->advance(TaskState::Compress);
+    if (!e.node_master()) {
+      e.schedule_after_barrier(e.module("WaitModel"), t, kAfterOptimize);
+      return;
+    }
+    auto& p = e.param(t->param_index);
+    const int W = e.options().world;
+    float* acc = p.slot[t->iter % 2][0];
+    for (uint32_t i = 0; i < p.numel; ++i)
+      if (acc[i] != acc[i]) acc[i] = 0.f;                        // NaN policy shared with the GPU tier
+    const uint32_t k = entries_for(p.numel, e.compression_ratio(), W);
+    t->k = k;
+    t->idx.assign(static_cast<size_t>(k) * W, 0xFFFFFFFFu);
+    t->val.assign(static_cast<size_t>(k) * W, 0.f);
+    t->counts.assign(W, 0);
+    t->stat_start("CRIT_PATH_compress");
+    const size_t cnt = e.compressor().compress(t->persistent_key, acc, p.numel, k, t->idx.data(), t->val.data(), 0);
+    t->stat_end("CRIT_PATH_compress");
+    t->counts[0] = cnt;
+    if (e.options().debug_accuracy)
+      for (size_t j = 0; j < cnt; ++j)
+        if (t->idx[j] >= p.numel || t->val[j] != acc[t->idx[j]]) throw std::runtime_error("compressor output is inconsistent");
+    t->stat_start("CRIT_PATH_save_residual");
+    for (size_t j = 0; j < cnt; ++j) acc[t->idx[j]] = 0.f;
+    std::memcpy(p.resid, acc, static_cast<size_t>(p.numel) * sizeof(float));
+    t->stat_end("CRIT_PATH_save_residual");
+    e.schedule(e.module(W == 1 ? "Optimize" : "GradExchange"), t);
+  }
+};
+
+class ModuleGradExchange : public Module {
+ public:
+  const char* name() const override { return "GradExchange"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    if (t->state() != TaskState::Exchange) t->advance(TaskState::Exchange);
+    const int W = e.options().world;
+    const int round = t->exchange_round;
+    if (round >= W - 1) {
+      e.schedule(e.module("Optimize"), t);
+      return;
+    }
+    // ring all-gather: forward slot `round` to the successor, expect slot `round + 1` from the predecessor
+    const std::string key = t->key + "!" + std::to_string(round);
+    const size_t off = static_cast<size_t>(round) * t->k;
+    e.comm()->queue_tx(t->priority(), key, t->idx.data() + off, t->val.data() + off, t->counts[round], t->numel);
+    e.schedule_after_comm(this, t, key, round + 1);
+  }
+};
+
+class ModuleOptimize : public Module {
+ public:
+  const char* name() const override { return "Optimize"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    t->advance(TaskState::Optimize);
+    auto& p = e.param(t->param_index);
+    const int W = e.options().world;
+    if (p.merge_scratch.size() != p.numel) {
+      p.merge_scratch.assign(p.numel, 0.f);
+      p.merge_touched.assign(p.numel, 0);
+    }
+    std::vector<const uint32_t*> idx(W);
+    std::vector<const float*> val(W);
+    std::vector<float> weights(W, 1.0f / static_cast<float>(W));   // mean over nodes (cpu_optimize.cpp:55)
+    size_t total = 0;
+    for (int s = 0; s < W; ++s) {
+      idx[s] = t->idx.data() + static_cast<size_t>(s) * t->k;
+      val[s] = t->val.data() + static_cast<size_t>(s) * t->k;
+      total += t->counts[s];
+    }
+    std::vector<uint32_t> midx(total);
+    std::vector<float> mval(total);
+    const size_t n = merge_streams(idx.data(), val.data(), t->counts.data(), weights.data(), W, p.merge_scratch.data(),
+                                   p.merge_touched.data(), p.numel, midx.data(), mval.data());
+    t->stat_start("CRIT_PATH_optimize_raw");
+    e.sparse_optimizer()->optimize_raw(p.master, p.numel, t->persistent_key, mval.data(), midx.data(), static_cast<uint32_t>(n));
+    t->stat_end("CRIT_PATH_optimize_raw");
+    if (e.options().debug_accuracy && has_nan(p.master, p.numel)) throw std::runtime_error("NaN in the parameter");
+    t->idx.clear(); t->idx.shrink_to_fit();
+    t->val.clear(); t->val.shrink_to_fit();
+    e.schedule_after_barrier(e.module("WaitModel"), t, kAfterOptimize);
+  }
+};
+
+class ModuleWaitModel : public Module {
+ public:
+  const char* name() const override { return "WaitModel"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    t->advance(TaskState::WaitModel);
+    e.schedule_after_model_complete(e.module("CopyOut"), t);
+  }
+};
+
+class ModuleCopyOut : public Module {
+ public:
+  const char* name() const override { return "CopyOut"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
+    t->advance(TaskState::CopyOut);
+    auto& p = e.param(t->param_index);
+    // the slot is consumed: clear this process's part for the next use
+    std::memset(p.slot[t->iter % 2][e.options().local_rank], 0, static_cast<size_t>(p.numel) * sizeof(float));
+    if (p.user_param == nullptr) {
+      e.push_ready_update(t->param_index, t->iter);   // the caller copies and reports copy_out_done()
+      return;
+    }
+    std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
+    t->advance(TaskState::Finished);
+    e.update_model_version(t);
+    e.return_after_use(t);
+    e.schedule_terminate(t);
+  }
+};
+
+}  // namespace
+
+void CpuEngine::load_modules() {
+  auto add = [this](std::unique_ptr<Module> m) {
+    const std::string n = m->name();
+    modules_[n] = std::move(m);
+  };
+  add(std::make_unique<ModuleNull>());
+  add(std::make_unique<ModuleBarrierChecker>());
+  add(std::make_unique<ModuleCopyIn>());
+  add(std::make_unique<ModuleGather>());
+  add(std::make_unique<ModuleCompress>());
+  add(std::make_unique<ModuleGradExchange>());
+  add(std::make_unique<ModuleOptimize>());
+  add(std::make_unique<ModuleWaitModel>());
+  add(std::make_unique<ModuleCopyOut>());
+}
+
+}  // namespace stc

@@ -128,7 +128,9 @@ __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {
 cudaError_t launch_apply(const ApplyArgs& A, int max_ctas_per_source, cudaStream_t stream) {
   if (A.cap == 0 || A.world <= 0) return cudaSuccess;
   if (A.world > kMaxWorld) return cudaErrorInvalidValue;
-  int parts = (int)((A.cap + kThreads * 4 - 1) / (kThreads * 4));
+  // one entry per thread: the update of an entry is a chain of dependent random accesses, so the
+  // only way to hide its latency is to have every entry in flight at once
+  int parts = (int)((A.cap + kThreads - 1) / kThreads);
   if (parts < 1) parts = 1;
   if (parts > max_ctas_per_source) parts = max_ctas_per_source;
   dim3 grid(parts, A.world);

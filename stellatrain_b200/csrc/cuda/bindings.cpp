@@ -30,7 +30,7 @@ struct BucketHandle {
   SelectArgs sel;
   ApplyArgs app;
   uint32_t randomk_seed = 0x5DEECE66u;
-  int max_ctas_per_source = 148 * 2;
+  int max_ctas_per_source = 148 * 16;
 
   BucketHandle() {
     std::memset(&sel, 0, sizeof(sel));

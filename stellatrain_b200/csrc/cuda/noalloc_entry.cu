@@ -65,8 +65,7 @@ __global__ void __launch_bounds__(256) k_noalloc_setup(const float* values, uint
     sd.off = 0; sd.n = n; sd.n_pad = n_pad; sd.k = k; sd.out_off = 0; sd.chunk_begin = 0; sd.chunk_cnt = n_chunks;
     sd.reserved = 0;
     *reinterpret_cast<st::SegDesc*>(g_scratch + Layout::seg) = sd;
-    st::SegState ss;
-    ss.tau = 0.f; ss.tau_inc = 0.f; ss.inited = 0; ss.reserved = 0;
+    st::SegState ss = {};   // no threshold, coarse histogram window
     *reinterpret_cast<st::SegState*>(g_scratch + Layout::state) = ss;
     uint32_t* work = reinterpret_cast<uint32_t*>(g_scratch + Layout::work);
     for (uint32_t i = 0; i < sizeof(st::SegWork) / 4; ++i) work[i] = 0;

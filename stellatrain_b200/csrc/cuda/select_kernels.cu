@@ -64,6 +64,35 @@ __device__ __forceinline__ float quad_l1(const float4& a) {
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------
+// histogram window
+// ------------------------------------------------------------------------------------------------
+struct HistWindow {
+  uint32_t base, shift;
+};
+
+__device__ __forceinline__ HistWindow window_of(const SegState& ss) {
+  HistWindow w;
+  w.base = ss.hist_shift ? ss.hist_base : 0u;
+  w.shift = ss.hist_shift ? ss.hist_shift : (uint32_t)kHistShift;
+  return w;
+}
+
+// Monotone in key, so "bin > b" implies "key above every key of bin b".
+__device__ __forceinline__ uint32_t bin_of(uint32_t key, const HistWindow& w) {
+  if (key < w.base) return 0u;
+  const uint32_t b = (key - w.base) >> w.shift;
+  return b < (uint32_t)(kHistBins - 1) ? b : (uint32_t)(kHistBins - 1);
+}
+
+// Window for the next select: 2048 bins of 2^13 key units (2^-10 relative) centred on `key`,
+// i.e. one octave to either side; keys outside fall into the two end bins.
+__device__ __forceinline__ void centre_window(SegState& ss, uint32_t key) {
+  const uint32_t half = (uint32_t)(kHistBins / 2) << kFineShift;
+  ss.hist_shift = kFineShift;
+  ss.hist_base = key > half ? key - half : 0u;
+}
+
+// ------------------------------------------------------------------------------------------------
 // pass 1
 // ------------------------------------------------------------------------------------------------
 template <bool B16>
@@ -77,6 +106,7 @@ __global__ void __launch_bounds__(kThreads) k_pass1(SelectArgs A) {
   const bool need_hist = (A.compressor == kTopk) || (A.compressor == kThresholdv16) || !ss.inited;
   const bool need_count = (A.compressor != kTopk) && ss.inited;
   const uint32_t tau_bits = __float_as_uint(ss.tau);
+  const HistWindow win = window_of(ss);
 
   if (blockIdx.x == 0 && threadIdx.x == 0) *A.cand_cursor = 0;
   if (need_hist) {
@@ -91,7 +121,10 @@ __global__ void __launch_bounds__(kThreads) k_pass1(SelectArgs A) {
   const uint32_t g_valid = tab ? (sd.n > seg_rel ? min(ch.len, sd.n - seg_rel) : 0u) : ch.len;
   float* r = A.resid + ch.start;
 
-  uint32_t cnt = 0, mx = 0;
+  // Bin 0 is never counted (plan derives it from the item count) and the top bin is counted in a
+  // register: with a window centred on the threshold these two bins hold most items, and counting
+  // them with shared-memory atomics would serialise on two addresses.
+  uint32_t cnt = 0, mx = 0, top = 0;
   const uint32_t len_up = (ch.len + kPerIter - 1) / kPerIter * kPerIter;
   for (uint32_t i = threadIdx.x * 4; i < len_up; i += kPerIter) {
     const bool act = i < ch.len;
@@ -112,33 +145,41 @@ __global__ void __launch_bounds__(kThreads) k_pass1(SelectArgs A) {
     }
     if (!B16) {
       if (act) {
-        const uint32_t k0 = key_bits(a.x), k1 = key_bits(a.y), k2 = key_bits(a.z), k3 = key_bits(a.w);
-        if (need_hist) {
-          atomicAdd(&s_hist[k0 >> kHistShift], 1u);
-          atomicAdd(&s_hist[k1 >> kHistShift], 1u);
-          atomicAdd(&s_hist[k2 >> kHistShift], 1u);
-          atomicAdd(&s_hist[k3 >> kHistShift], 1u);
+        const uint32_t key[4] = {key_bits(a.x), key_bits(a.y), key_bits(a.z), key_bits(a.w)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (need_hist) {
+            const uint32_t b = bin_of(key[j], win);
+            if (b == (uint32_t)(kHistBins - 1)) ++top;
+            else if (b != 0u) atomicAdd(&s_hist[b], 1u);
+          }
+          if (need_count) cnt += (key[j] >= tau_bits);
+          mx = max(mx, key[j]);
         }
-        if (need_count) cnt += (k0 >= tau_bits) + (k1 >= tau_bits) + (k2 >= tau_bits) + (k3 >= tau_bits);
-        mx = max(max(mx, k0), max(max(k1, k2), k3));
       }
     } else {
       const uint32_t key = __float_as_uint(quad_l1(a));
       if (act && (threadIdx.x & 3) == 0) {
-        if (need_hist) atomicAdd(&s_hist[key >> kHistShift], 1u);
+        if (need_hist) {
+          const uint32_t b = bin_of(key, win);
+          if (b == (uint32_t)(kHistBins - 1)) ++top;
+          else if (b != 0u) atomicAdd(&s_hist[b], 1u);
+        }
         if (need_count) cnt += (key >= tau_bits);
       }
     }
   }
   __syncthreads();
+  uint32_t total, top_total = 0;
   if (need_hist) {
     uint32_t* gh = A.hist + (size_t)ch.seg * kHistBins;
     for (int b = threadIdx.x; b < kHistBins; b += kThreads) {
       const uint32_t h = s_hist[b];
       if (h) atomicAdd(&gh[b], h);
     }
+    block_excl_scan(top, s_tmp, top_total);
+    if (threadIdx.x == 0 && top_total) atomicAdd(&gh[kHistBins - 1], top_total);
   }
-  uint32_t total;
   block_excl_scan(cnt, s_tmp, total);
   if (!B16) mx = block_max_u32(mx, s_tmp);
   if (threadIdx.x == 0) {
@@ -161,6 +202,7 @@ __global__ void __launch_bounds__(kThreads) k_plan(SelectArgs A) {
   const uint32_t epoch = *A.epoch;
   const bool b16 = A.compressor == kThresholdv16;
   const uint32_t kk = b16 ? (sd.k + 15u) / 16u : sd.k;   // items to take
+  const uint32_t n_items = b16 ? sd.n_pad / 16u : sd.n_pad;
 
   // The receive slot about to be overwritten was last used two epochs ago; every destination
   // must have consumed it.  One thread of one CTA waits; the kernels that store come later in
@@ -209,6 +251,8 @@ __global__ void __launch_bounds__(kThreads) k_plan(SelectArgs A) {
     }
     uint32_t total;
     uint32_t running = block_excl_scan(local, s_tmp, total);
+    // bin 0 is not counted by pass 1: it holds whatever the other bins do not
+    if (threadIdx.x == kThreads - 1) h[kPer - 1] = n_items > total ? n_items - total : 0u;
     if (threadIdx.x == 0) { s_res[0] = 0; s_res[1] = 0; s_res[2] = 0; }
     __syncthreads();
 #pragma unroll
@@ -260,6 +304,7 @@ __global__ void __launch_bounds__(kThreads) k_plan(SelectArgs A) {
       else if (sd.k < found) ss.tau = ss.tau + 0.01f * ((float)found / (float)sd.k) * max_abs;
     } else {                              // over-filled: thresholdv16.cpp:249-252
       ss.tau += ss.tau_inc;
+      centre_window(ss, __float_as_uint(ss.tau));   // keep the fallback histogram centred
     }
     A.state[seg] = ss;
   }
@@ -270,9 +315,22 @@ __global__ void __launch_bounds__(kThreads) k_plan(SelectArgs A) {
 // ------------------------------------------------------------------------------------------------
 // pass 2
 // ------------------------------------------------------------------------------------------------
+constexpr uint32_t kQueueCap = 2048;   // per-CTA staging of selected / candidate items
+constexpr uint32_t kP2PerThread = 16;  // consecutive elements per thread: one block of threshold-v16
+constexpr uint32_t kP2PerIter = kThreads * kP2PerThread;
+
+// Every thread owns 16 consecutive elements per iteration (four independent 16-byte loads in
+// flight), and the CTA needs one scan per 4096 elements to turn per-thread counts into stream
+// positions.  Ordered mode writes at chunk_pos + rank; unordered mode stages items in shared memory
+// and reserves positions with ONE global atomic per flush, so that stores into peer memory are
+// consecutive and the per-segment cursor is not hammered by every warp.
 template <bool B16>
 __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
   __shared__ uint32_t s_tmp[kThreads / 32 + 1];
+  __shared__ uint2 s_sel[B16 ? 1 : kQueueCap];      // element mode: (idx, value bits)
+  __shared__ uint32_t s_selb[B16 ? kQueueCap : 1];  // block mode: block ids
+  __shared__ uint2 s_cnd[kQueueCap];                // (item id, key)
+  __shared__ uint32_t s_base[2];
   if (ld_volatile_u32(A.status) != kOk) return;
 
   const Chunk ch = A.chunks[blockIdx.x];
@@ -283,148 +341,209 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
   const uint32_t thr_bin = wp->thr_bin;
   const uint32_t tau_bits = wp->tau_bits;
   const uint32_t cand_off = wp->cand_off;
+  const HistWindow win = window_of(A.state[ch.seg]);
   const uint32_t epoch = *A.epoch;
   const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
   const uint32_t kk = B16 ? (sd.k + 15u) / 16u : sd.k;
   const uint32_t base_pos = A.chunk_pos[blockIdx.x];
   float* r = A.resid + ch.start;
-  const int lane = threadIdx.x & 31;
   bool emitted = false;
   uint32_t running = 0;
+  uint32_t fill_sel = 0, fill_cnd = 0;   // uniform over the CTA
 
-  const uint32_t len_up = (ch.len + kPerIter - 1) / kPerIter * kPerIter;
-  for (uint32_t i = threadIdx.x * 4; i < len_up; i += kPerIter) {
-    const bool act = i < ch.len;
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (act) a = *reinterpret_cast<const float4*>(r + i);
-    const uint32_t gi = ch.start + i;   // bucket offset of a.x
+  auto emit_block = [&](uint32_t pos, uint32_t gi0) {   // one 16-element block at block position pos
+#pragma unroll 4
+    for (uint32_t e = 0; e < 16u; ++e) {
+      const uint32_t p = pos * 16u + e;
+      if (p < sd.k) {
+        emit_entry(A, slot_off, p, gi0 + e, A.resid[gi0 + e]);
+        A.resid[gi0 + e] = 0.f;
+      }
+    }
+  };
 
+  auto flush = [&]() {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_base[0] = fill_sel ? atomicAdd(&wp->out_cursor, fill_sel) : 0u;
+      s_base[1] = fill_cnd ? atomicAdd(&wp->cand_cnt, fill_cnd) : 0u;
+    }
+    __syncthreads();
+    const uint32_t b_sel = s_base[0], b_cnd = s_base[1];
     if (!B16) {
-      const float av[4] = {a.x, a.y, a.z, a.w};
-      uint32_t key[4];
-      bool sel[4], cnd[4];
-      uint32_t n_sel = 0, n_cnd = 0;
+      for (uint32_t j = threadIdx.x; j < fill_sel; j += kThreads) {
+        const uint2 e = s_sel[j];
+        if (b_sel + j < kk) emit_entry(A, slot_off, b_sel + j, e.x, __uint_as_float(e.y));
+      }
+    } else {
+      for (uint32_t t = threadIdx.x; t < fill_sel * 16u; t += kThreads) {
+        const uint32_t q = t >> 4, e = t & 15u;
+        const uint32_t gi = s_selb[q] * 16u + e;
+        const uint32_t p = (b_sel + q) * 16u + e;
+        if (p < sd.k) {
+          emit_entry(A, slot_off, p, gi, A.resid[gi]);
+          A.resid[gi] = 0.f;
+        }
+      }
+    }
+    for (uint32_t j = threadIdx.x; j < fill_cnd; j += kThreads) A.cand[cand_off + b_cnd + j] = s_cnd[j];
+    if (fill_sel) emitted = true;
+    fill_sel = 0;
+    fill_cnd = 0;
+    __syncthreads();
+  };
+
+  for (uint32_t it = 0; it < ch.len; it += kP2PerIter) {
+    const uint32_t i = it + threadIdx.x * kP2PerThread;
+    const bool act = i < ch.len;   // chunk lengths are multiples of 16: a thread is all in or all out
+    float v[16];
+    if (act) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        key[j] = key_bits(av[j]);
+      for (int q = 0; q < 4; ++q) {
+        const float4 a = *reinterpret_cast<const float4*>(r + i + 4 * q);
+        v[4 * q + 0] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    }
+    const uint32_t gi = ch.start + i;   // bucket offset of v[0]
+
+    uint32_t sel_mask = 0, cnd_mask = 0, bkey = 0;
+    if (!B16) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const uint32_t key = key_bits(v[j]);
         if (mode == kModeTop) {
-          const uint32_t bin = key[j] >> kHistShift;
-          sel[j] = act && bin > thr_bin;
-          cnd[j] = act && bin == thr_bin;
+          const uint32_t bin = bin_of(key, win);
+          sel_mask |= (uint32_t)(act && bin > thr_bin) << j;
+          cnd_mask |= (uint32_t)(act && bin == thr_bin) << j;
         } else {
-          sel[j] = act && key[j] >= tau_bits;
-          cnd[j] = false;
-        }
-        n_sel += sel[j];
-        n_cnd += cnd[j];
-      }
-      uint32_t pos = 0;
-      if (mode == kModeTop) {
-        if (__any_sync(0xffffffffu, n_sel != 0)) {
-          const uint32_t incl = warp_incl_scan(n_sel);
-          uint32_t base = 0;
-          if (lane == 31) base = atomicAdd(&wp->out_cursor, incl);
-          base = __shfl_sync(0xffffffffu, base, 31);
-          pos = base + incl - n_sel;
-        }
-        if (__any_sync(0xffffffffu, n_cnd != 0)) {
-          const uint32_t incl = warp_incl_scan(n_cnd);
-          uint32_t base = 0;
-          if (lane == 31) base = atomicAdd(&wp->cand_cnt, incl);
-          base = __shfl_sync(0xffffffffu, base, 31);
-          uint32_t cpos = cand_off + base + incl - n_cnd;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (cnd[j]) A.cand[cpos++] = make_uint2(gi + j, key[j]);
-        }
-      } else {
-        uint32_t total;
-        const uint32_t ex = block_excl_scan(n_sel, s_tmp, total);
-        pos = base_pos + running + ex;
-        running += total;
-      }
-      if (n_sel) {
-        float out[4] = {a.x, a.y, a.z, a.w};
-        bool any = false;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (sel[j]) {
-            if (pos < kk) {   // ordered mode truncates at k; the rest stays in the residual
-              emit_entry(A, slot_off, pos, gi + j, av[j]);
-              out[j] = 0.f;
-              any = true;
-            }
-            ++pos;
-          }
-        }
-        if (any) {
-          *reinterpret_cast<float4*>(r + i) = make_float4(out[0], out[1], out[2], out[3]);
-          emitted = true;
+          sel_mask |= (uint32_t)(act && key >= tau_bits) << j;
         }
       }
     } else {
-      const uint32_t key = __float_as_uint(quad_l1(a));
-      const bool leader = (lane & 3) == 0;
-      bool sel, cnd = false;
-      if (mode == kModeTop) {
-        const uint32_t bin = key >> kHistShift;
-        sel = act && bin > thr_bin;
-        cnd = act && bin == thr_bin;
-      } else {
-        sel = act && key >= tau_bits;
-      }
-      const uint32_t n_sel = (leader && sel) ? 1u : 0u;
-      uint32_t pos = 0;
-      if (mode == kModeTop) {
-        if (__any_sync(0xffffffffu, n_sel != 0)) {
-          const uint32_t incl = warp_incl_scan(n_sel);
-          uint32_t base = 0;
-          if (lane == 31) base = atomicAdd(&wp->out_cursor, incl);
-          base = __shfl_sync(0xffffffffu, base, 31);
-          pos = base + incl - n_sel;
-        }
-        const uint32_t n_cnd = (leader && cnd) ? 1u : 0u;
-        if (__any_sync(0xffffffffu, n_cnd != 0)) {
-          const uint32_t incl = warp_incl_scan(n_cnd);
-          uint32_t base = 0;
-          if (lane == 31) base = atomicAdd(&wp->cand_cnt, incl);
-          base = __shfl_sync(0xffffffffu, base, 31);
-          if (n_cnd) A.cand[cand_off + base + incl - 1] = make_uint2(gi >> 4, key);
-        }
-      } else {
-        uint32_t total;
-        const uint32_t ex = block_excl_scan(n_sel, s_tmp, total);
-        pos = base_pos + running + ex;
-        running += total;
-      }
-      pos = __shfl_sync(0xffffffffu, pos, lane & ~3);   // block position from the quad leader
-      if (sel && pos < kk) {
-        const float av[4] = {a.x, a.y, a.z, a.w};
-        const uint32_t e0 = pos * 16u + (uint32_t)(lane & 3) * 4u;
+      float g[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (e0 + j < sd.k) emit_entry(A, slot_off, e0 + j, gi + j, av[j]);
-        // A truncated last block still leaves the residual exact: only emitted elements are zeroed.
-        float4 o = a;
-        if (e0 + 0 < sd.k) o.x = 0.f;
-        if (e0 + 1 < sd.k) o.y = 0.f;
-        if (e0 + 2 < sd.k) o.z = 0.f;
-        if (e0 + 3 < sd.k) o.w = 0.f;
-        *reinterpret_cast<float4*>(r + i) = o;
-        emitted = true;
+      for (int q = 0; q < 4; ++q)
+        g[q] = (fabsf(v[4 * q]) + fabsf(v[4 * q + 1])) + (fabsf(v[4 * q + 2]) + fabsf(v[4 * q + 3]));
+      bkey = __float_as_uint((g[0] + g[1]) + (g[2] + g[3]));   // same tree as quad_l1
+      if (mode == kModeTop) {
+        const uint32_t bin = bin_of(bkey, win);
+        sel_mask = act && bin > thr_bin;
+        cnd_mask = act && bin == thr_bin;
+      } else {
+        sel_mask = act && bkey >= tau_bits;
+      }
+    }
+    const uint32_t n_sel = __popc(sel_mask), n_cnd = __popc(cnd_mask);
+    uint32_t total;
+    const uint32_t ex = block_excl_scan(n_sel | (n_cnd << 16), s_tmp, total);
+    const uint32_t t_sel = total & 0xffffu, t_cnd = total >> 16;
+
+    if (mode == kModeTop) {
+      if (fill_sel + t_sel > kQueueCap || fill_cnd + t_cnd > kQueueCap) flush();
+      const bool direct = t_sel > kQueueCap || t_cnd > kQueueCap;   // dense selection: bypass the queue
+      uint32_t p = fill_sel + (ex & 0xffffu), q = fill_cnd + (ex >> 16);
+      if (direct) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          s_base[0] = atomicAdd(&wp->out_cursor, t_sel);
+          s_base[1] = atomicAdd(&wp->cand_cnt, t_cnd);
+        }
+        __syncthreads();
+        p = s_base[0] + (ex & 0xffffu);
+        q = cand_off + s_base[1] + (ex >> 16);
+      }
+      if (!B16) {
+        if (sel_mask | cnd_mask) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (sel_mask >> j & 1u) {
+              if (direct) { if (p < kk) emit_entry(A, slot_off, p, gi + j, v[j]); }
+              else s_sel[p] = make_uint2(gi + j, __float_as_uint(v[j]));
+              ++p;
+              v[j] = 0.f;
+            }
+            if (cnd_mask >> j & 1u) {
+              const uint2 c = make_uint2(gi + j, key_bits(v[j]));
+              if (direct) A.cand[q] = c; else s_cnd[q] = c;
+              ++q;
+            }
+          }
+          if (sel_mask) {
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd)
+              *reinterpret_cast<float4*>(r + i + 4 * qd) = make_float4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
+            if (direct) emitted = true;
+          }
+        }
+      } else {
+        if (sel_mask) {
+          if (direct) { emit_block(p, gi); emitted = true; }
+          else s_selb[p] = gi >> 4;
+        }
+        if (cnd_mask) {
+          const uint2 c = make_uint2(gi >> 4, bkey);
+          if (direct) A.cand[q] = c; else s_cnd[q] = c;
+        }
+      }
+      if (!direct) {
+        fill_sel += t_sel;
+        fill_cnd += t_cnd;
+      }
+    } else {
+      uint32_t pos = base_pos + running + (ex & 0xffffu);
+      running += t_sel;
+      if (sel_mask) {
+        if (!B16) {
+          bool any = false;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (sel_mask >> j & 1u) {
+              if (pos < kk) {   // ordered mode truncates at k; the rest stays in the residual
+                emit_entry(A, slot_off, pos, gi + j, v[j]);
+                v[j] = 0.f;
+                any = true;
+              }
+              ++pos;
+            }
+          }
+          if (any) {
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd)
+              *reinterpret_cast<float4*>(r + i + 4 * qd) = make_float4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
+            emitted = true;
+          }
+        } else if (pos < kk) {
+          // a truncated last block still leaves the residual exact: only emitted elements are zeroed
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (pos * 16u + j < sd.k) {
+              emit_entry(A, slot_off, pos * 16u + j, gi + j, v[j]);
+              v[j] = 0.f;
+            }
+          }
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd)
+            *reinterpret_cast<float4*>(r + i + 4 * qd) = make_float4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
+          emitted = true;
+        }
       }
     }
   }
+  if (mode == kModeTop && (fill_sel | fill_cnd)) flush();
   if (emitted) __threadfence_system();
 }
 
 // ------------------------------------------------------------------------------------------------
 // candidates + completion
 // ------------------------------------------------------------------------------------------------
-constexpr int kCandThreads = 512;
+constexpr int kCandThreads = 1024;
+constexpr int kCandIlp = 4;   // independent loads in flight per thread
 
 __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
-  __shared__ uint32_t s_hist[1024];
+  __shared__ uint32_t s_hist[2048];
   __shared__ uint32_t s_tmp[kCandThreads / 32 + 1];
   __shared__ uint32_t s_res[4];
 
@@ -444,39 +563,51 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
     const uint2* cand = A.cand + wp->cand_off;
     uint32_t rem = wp->k_rem, ties = 0;
     uint32_t prefix = 0, mask = 0;
-    // two 10-bit digits over the low 20 key bits, largest first
-    for (int pass = 0; pass < 2; ++pass) {
-      const int shift = 10 - 10 * pass;
-      for (int b = tid; b < 1024; b += kCandThreads) s_hist[b] = 0;
+    // radix select over the full 31-bit key, largest first: digits of 11, 11 and 9 bits
+    const int shifts[3] = {20, 9, 0};
+    const uint32_t widths[3] = {2048u, 2048u, 512u};
+    for (int pass = 0; pass < 3; ++pass) {
+      const int shift = shifts[pass];
+      const uint32_t nb = widths[pass];
+      for (uint32_t b = tid; b < nb; b += kCandThreads) s_hist[b] = 0;
       __syncthreads();
-      for (uint32_t i = tid; i < c; i += kCandThreads) {
-        const uint32_t low = cand[i].y & 0xFFFFFu;
-        if ((low & mask) == prefix) atomicAdd(&s_hist[(low >> shift) & 1023u], 1u);
+      for (uint32_t i0 = tid; i0 < c; i0 += kCandThreads * kCandIlp) {
+        uint32_t key[kCandIlp];
+#pragma unroll
+        for (int u = 0; u < kCandIlp; ++u) {
+          const uint32_t i = i0 + u * kCandThreads;
+          key[u] = i < c ? cand[i].y : 0xFFFFFFFFu;
+        }
+#pragma unroll
+        for (int u = 0; u < kCandIlp; ++u)
+          if (key[u] != 0xFFFFFFFFu && (key[u] & mask) == prefix) atomicAdd(&s_hist[(key[u] >> shift) & (nb - 1)], 1u);
       }
       __syncthreads();
-      const uint32_t h0 = s_hist[1023 - 2 * tid], h1 = s_hist[1022 - 2 * tid];
+      // thread t owns bins nb-1-2t and nb-2-2t (descending)
+      const uint32_t h0 = 2 * tid < nb ? s_hist[nb - 1 - 2 * tid] : 0u;
+      const uint32_t h1 = 2 * tid + 1 < nb ? s_hist[nb - 2 - 2 * tid] : 0u;
       uint32_t total;
       const uint32_t ex = block_excl_scan(h0 + h1, s_tmp, total);
       if (ex < rem && ex + h0 >= rem) {
-        s_res[0] = 1023 - 2 * tid; s_res[1] = rem - ex; s_res[2] = h0;
+        s_res[0] = nb - 1 - 2 * tid; s_res[1] = rem - ex; s_res[2] = h0;
       } else if (ex + h0 < rem && ex + h0 + h1 >= rem) {
-        s_res[0] = 1022 - 2 * tid; s_res[1] = rem - ex - h0; s_res[2] = h1;
+        s_res[0] = nb - 2 - 2 * tid; s_res[1] = rem - ex - h0; s_res[2] = h1;
       }
       __syncthreads();
       prefix |= s_res[0] << shift;
-      mask |= 1023u << shift;
+      mask |= (nb - 1) << shift;
       rem = s_res[1];
       ties = s_res[2];
       __syncthreads();
     }
-    const uint32_t t_key = (wp->thr_bin << kHistShift) | prefix;
+    const uint32_t t_key = prefix;
     // among equal keys take the lowest item ids: radix select on the id, smallest first
     uint32_t id_thr = 0xFFFFFFFFu;
     if (rem < ties) {
       uint32_t ipre = 0, imask = 0, irem = rem;
       for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
-        for (int b = tid; b < 256; b += kCandThreads) s_hist[b] = 0;
+        for (uint32_t b = tid; b < 256; b += kCandThreads) s_hist[b] = 0;
         __syncthreads();
         for (uint32_t i = tid; i < c; i += kCandThreads) {
           const uint2 e = cand[i];
@@ -532,9 +663,14 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
       }
     }
     if (emitted) __threadfence_system();
-    if (tid == 0 && A.compressor != kTopk) {
+    if (tid == 0) {
       SegState ss = A.state[seg];
-      if (!ss.inited) {
+      // Next select: centre the histogram on the threshold just found, unless it fell off the
+      // window (the distribution moved by more than an octave), then start coarse again.
+      const uint32_t tb = wp->thr_bin;
+      if (tb == 0u || tb == (uint32_t)(kHistBins - 1)) { ss.hist_shift = 0; ss.hist_base = 0; }
+      else centre_window(ss, t_key);
+      if (A.compressor != kTopk && !ss.inited) {
         // first threshold = the smallest selected key (thresholdv.cpp:27-37 takes the next one
         // down; the first AIMD step below is the one the reference applies right away)
         const float t0 = __uint_as_float(t_key);
@@ -547,8 +683,8 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
           ss.tau_inc = 0.f;
         }
         ss.inited = 1;
-        A.state[seg] = ss;
       }
+      A.state[seg] = ss;
     }
   } else if (ok && mode == kModeInOrder && !b16 && wp->found < sd.k) {
     // threshold-v may under-fill (thresholdv.cpp:82): pad the fixed-size stream

@@ -12,7 +12,8 @@ namespace st {
 constexpr int kMaxWorld = 16;          // peers addressable by one kernel launch
 constexpr int kHistBits = 11;          // first radix digit: exponent + 3 mantissa bits of |x|
 constexpr int kHistBins = 1 << kHistBits;
-constexpr int kHistShift = 31 - kHistBits;  // 20 low bits are resolved on the candidate set
+constexpr int kHistShift = 31 - kHistBits;  // shift of the coarse window
+constexpr int kFineShift = 13;              // shift of the window centred on the previous threshold
 constexpr uint32_t kSentinelIdx = 0xFFFFFFFFu;  // "no entry" marker in an (idx,val) stream
 
 enum Compressor : uint32_t { kTopk = 0, kThresholdv = 1, kThresholdv16 = 2, kRandomk = 3 };
@@ -43,7 +44,13 @@ struct SegState {         // persistent per segment, saved in checkpoints
   float tau;              // threshold (element magnitude or 16-block L1 norm)
   float tau_inc;          // additive step of threshold-v16
   uint32_t inited;        // 0 until the first threshold was measured
-  uint32_t reserved;
+  // Histogram window of the next select: bin(key) = clamp((key - hist_base) >> hist_shift, 0, 2047).
+  // hist_shift == 0 means "coarse": base 0, shift 20 (exponent + 3 mantissa bits).  After a select
+  // the window is centred on the k-th largest key found, so that in steady state the bin that
+  // holds the next threshold is 2^-10 wide (relative) and the candidate set is tiny.
+  uint32_t hist_base;
+  uint32_t hist_shift;
+  uint32_t reserved[3];
 };
 
 struct SegWork {          // scratch per segment, valid within one select

@@ -18,7 +18,8 @@ SEG_DESC_DTYPE = np.dtype(
     [("off", "<u4"), ("n", "<u4"), ("n_pad", "<u4"), ("k", "<u4"), ("out_off", "<u4"),
      ("chunk_begin", "<u4"), ("chunk_cnt", "<u4"), ("reserved", "<u4")]
 )
-SEG_STATE_DTYPE = np.dtype([("tau", "<f4"), ("tau_inc", "<f4"), ("inited", "<u4"), ("reserved", "<u4")])
+SEG_STATE_DTYPE = np.dtype([("tau", "<f4"), ("tau_inc", "<f4"), ("inited", "<u4"), ("hist_base", "<u4"),
+                            ("hist_shift", "<u4"), ("r0", "<u4"), ("r1", "<u4"), ("r2", "<u4")])
 SEG_WORK_WORDS = 12
 CHUNK_DTYPE = np.dtype([("seg", "<u4"), ("start", "<u4"), ("len", "<u4"), ("reserved", "<u4")])
 OPT_STATE_DTYPE = np.dtype(
