@@ -36,7 +36,10 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function", "-pthread"]
+# -ffp-contract=off: vector and scalar variants of a kernel must round identically, so that replicas
+# that process an element on different paths stay bit-equal
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function", "-pthread",
+             "-ffp-contract=off"]
 
 
 def _pybind_includes() -> list[str]:

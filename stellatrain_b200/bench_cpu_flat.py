@@ -52,6 +52,7 @@ def run(numel: int = 11_689_512, steps: int = 20, method: str = "topk", seed: in
         if time_oracle:
             t0 = time.perf_counter()
             oi, ov, o_resid = O.compress_step(method, grad, o_resid, k, o_state)
+            o_resid = o_resid[:numel]
             oracle_ms.append((time.perf_counter() - t0) * 1e3)
     conserved = torch.allclose(sent_sum + resid.double(), grad_sum, rtol=0, atol=1e-4)
     d_sparse, d_dense = param, dense_param

@@ -232,7 +232,11 @@ PYBIND11_MODULE(_Ccpu, m) {
            py::call_guard<py::gil_scoped_release>())
       .def("recv_init_model", [](CommBox& b, const std::string& key, size_t n) {
         std::vector<float> v(n);
-        const bool ok = b.c->recv_init_model(key, v.data(), n);
+        bool ok;
+        {
+          py::gil_scoped_release rel;
+          ok = b.c->recv_init_model(key, v.data(), n);
+        }
         return py::make_tuple(ok, v);
       })
       .def("global_barrier", [](CommBox& b) { return b.c->global_barrier(); }, py::call_guard<py::gil_scoped_release>())

@@ -318,6 +318,32 @@ void CpuEngine::schedule_after_model_complete(Module* next, const std::shared_pt
   schedule(next, t);
 }
 
+void CpuEngine::schedule_after_previous(Module* next, const std::shared_ptr<TrainTask>& t) {
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    if (params_[t->param_index].sequenced_iter < t->iter - 1) {
+      waiting_prev_.emplace_back(next, t);
+      return;
+    }
+  }
+  schedule(next, t);
+}
+
+void CpuEngine::mark_sequenced(const std::shared_ptr<TrainTask>& t) {
+  std::pair<Module*, std::shared_ptr<TrainTask>> next{nullptr, nullptr};
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    params_[t->param_index].sequenced_iter = t->iter;
+    for (auto it = waiting_prev_.begin(); it != waiting_prev_.end(); ++it)
+      if (it->second->param_index == t->param_index && it->second->iter == t->iter + 1) {
+        next = *it;
+        waiting_prev_.erase(it);
+        break;
+      }
+  }
+  if (next.first) schedule(next.first, next.second);
+}
+
 void CpuEngine::schedule_after_use(Module* next, const std::shared_ptr<TrainTask>& t) {
   const std::string slot_key = t->persistent_key + "#" + std::to_string(t->iter % 2);
   {
@@ -415,9 +441,13 @@ void CpuEngine::synchronize() {
   const auto deadline = Clock::now() + std::chrono::milliseconds(opt_.timeout_ms);
   for (auto& f : futs) {
     for (;;) {
-      const auto st = f.second.wait_for(std::chrono::seconds(5));
+      const auto st = f.second.wait_for(std::chrono::milliseconds(std::min(5000, std::max(100, opt_.timeout_ms / 4))));
       if (st == std::future_status::ready) break;
       LOG_WARN("CpuEngine", "waiting for " << f.first << " for more than 5 s (" << futs.size() << " tasks in flight)");
+      if (comm_ && comm_->failed()) {
+        err = "communication failed: " + comm_->failure();
+        break;
+      }
       if (Clock::now() > deadline) {
         err = "synchronize timed out on " + f.first;
         break;

@@ -114,6 +114,11 @@ class CpuEngine {
   void schedule_after_barrier(Module* m, const std::shared_ptr<TrainTask>& t, int stage_id);
   void schedule_after_comm(Module* m, const std::shared_ptr<TrainTask>& t, const std::string& key, int slot);
   void schedule_after_model_complete(Module* m, const std::shared_ptr<TrainTask>& t);
+  // Runs `m` once the previous iteration of the same parameter has left its optimise stage:
+  // residual, optimiser state and master parameter are per-parameter state that iteration i+1 must
+  // see as iteration i left it.
+  void schedule_after_previous(Module* m, const std::shared_ptr<TrainTask>& t);
+  void mark_sequenced(const std::shared_ptr<TrainTask>& t);
   void schedule_after_use(Module* m, const std::shared_ptr<TrainTask>& t);
   void return_after_use(const std::shared_ptr<TrainTask>& t);
   void schedule_terminate(const std::shared_ptr<TrainTask>& t);
@@ -137,6 +142,7 @@ class CpuEngine {
     int64_t model_version = 0;               // updates applied
     int64_t alloc_cnt = 0;                   // backwards (tasks) created
     int64_t completed_version = -1;
+    int64_t sequenced_iter = -1;             // last iteration that left the optimise stage
     int micro = 0;
     bool checked_barrier = false;
     std::vector<float> merge_scratch;        // node master: dense accumulator of the merge
@@ -181,6 +187,7 @@ class CpuEngine {
   std::mutex version_mu_;
   std::condition_variable version_cv_;
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_model_;
+  std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_prev_;
 
   // exclusive use of (parameter, slot)
   std::mutex use_mu_;

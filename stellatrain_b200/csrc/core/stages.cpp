@@ -31,8 +31,8 @@ class ModuleNull : public Module {
   void run(CpuEngine&, const std::shared_ptr<TrainTask>&) override {}
 };
 
-// Writes this process's slot of a scratch line and reads the neighbour's through 60 barrier rounds;
-// a lost wake-up or a miscounted barrier shows up as a wrong value or a timeout.
+// Self-check of the task barriers: 60 rounds of "write own slot | barrier | read the neighbour's slot
+// | barrier"; a lost wake-up or a miscounted barrier shows up as a wrong value or a timeout.
 class ModuleBarrierChecker : public Module {
  public:
   const char* name() const override { return "BarrierChecker"; }
@@ -40,29 +40,30 @@ class ModuleBarrierChecker : public Module {
     auto& p = e.param(t->param_index);
     const int N = e.options().local_world, r = e.options().local_rank;
     std::lock_guard<std::mutex> lk(mu_);
-    int& round = rounds_[t->key];
+    int& step = steps_[t->key];           // even: write phase, odd: read phase
     float* mine = p.slot[t->iter % 2][r];
-    if (round > 0 && N > 1 && p.numel >= 1) {
+    if (step == 0) parked_[t->key].assign(mine, mine + p.numel);   // the real gradient waits here
+    const int round = step / 2 + 1;
+    if (step == 120) {
+      steps_.erase(t->key);
+      std::memcpy(mine, parked_[t->key].data(), static_cast<size_t>(p.numel) * sizeof(float));
+      parked_.erase(t->key);
+      e.schedule(e.module("CopyIn"), t);
+      return;
+    }
+    if (step % 2 == 0) {
+      if (p.numel >= 1) mine[0] = static_cast<float>(-round);
+    } else if (N > 1 && p.numel >= 1) {
       const float seen = p.slot[t->iter % 2][(r + 1) % N][0];
       if (seen != static_cast<float>(-round)) throw std::runtime_error("barrier self-check read a stale value");
     }
-    if (round == 60) {
-      rounds_.erase(t->key);
-      // restore: the real gradient was parked in the task while the check ran
-      std::memcpy(mine, parked_[t->key].data(), static_cast<size_t>(p.numel) * sizeof(float));
-      parked_.erase(t->key);
-      e.schedule_after_barrier(e.module("CopyIn"), t, kCheckerBase + 61);
-      return;
-    }
-    if (round == 0) parked_[t->key].assign(mine, mine + p.numel);
-    ++round;
-    if (p.numel >= 1) mine[0] = static_cast<float>(-round);
-    e.schedule_after_barrier(this, t, kCheckerBase + round);
+    ++step;
+    e.schedule_after_barrier(this, t, kCheckerBase + step);
   }
 
  private:
   std::mutex mu_;
-  std::map<std::string, int> rounds_;
+  std::map<std::string, int> steps_;
   std::map<std::string, std::vector<float>> parked_;
 };
 
@@ -75,8 +76,16 @@ class ModuleCopyIn : public Module {
       auto& p = e.param(t->param_index);
       if (has_nan(p.slot[t->iter % 2][e.options().local_rank], p.numel)) throw std::runtime_error("NaN in the gradient");
     }
-    e.schedule_after_barrier(e.module("Gather"), t, kAfterCopyIn);
+    e.schedule_after_barrier(e.module("GatherGate"), t, kAfterCopyIn);
   }
+};
+
+// Iterations of one parameter pass gather..optimise one at a time (error-feedback residual, optimiser
+// state and master copy are carried from one iteration to the next).
+class ModuleGatherGate : public Module {
+ public:
+  const char* name() const override { return "GatherGate"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override { e.schedule_after_previous(e.module("Gather"), t); }
 };
 
 class ModuleGather : public Module {
@@ -189,6 +198,7 @@ class ModuleWaitModel : public Module {
   const char* name() const override { return "WaitModel"; }
   void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
     t->advance(TaskState::WaitModel);
+    e.mark_sequenced(t);
     e.schedule_after_model_complete(e.module("CopyOut"), t);
   }
 };
@@ -223,6 +233,7 @@ void CpuEngine::load_modules() {
   add(std::make_unique<ModuleNull>());
   add(std::make_unique<ModuleBarrierChecker>());
   add(std::make_unique<ModuleCopyIn>());
+  add(std::make_unique<ModuleGatherGate>());
   add(std::make_unique<ModuleGather>());
   add(std::make_unique<ModuleCompress>());
   add(std::make_unique<ModuleGradExchange>());

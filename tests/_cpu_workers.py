@@ -1,0 +1,57 @@
+"""Worker entry points for multi-process tests of the CPU tier (importable for the spawn start method)."""
+import os
+import sys
+import traceback
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+SIZES = [1000, 37, 4096]
+
+
+def synthetic_grad(node, local, step, pi, n):
+    g = torch.Generator().manual_seed(1_000_003 * node + 10_007 * local + 101 * step + pi)
+    return torch.randn(n, generator=g) * 1e-2
+
+
+def engine_worker(q, port, session_base, world, node, local_world, local, steps, method, optimizer, staleness, mode):
+    """mode: 'ok' | 'absent' (never configures) | 'drop' (node 1 drops its gradient sends) | 'die' (node 1 exits mid-run)"""
+    try:
+        from stellatrain_b200 import cpu_tier
+
+        ext = cpu_tier._load()
+        ext.set_log_level(3)
+        if mode == "absent" and local == local_world - 1:
+            q.put((node, local, "absent", None))
+            return
+        eng = ext.CpuEngine()
+        timeout_ms = 4000 if mode != "ok" else 30000
+        eng.configure("127.0.0.1", port, world, node, session_base + node, local_world, local, method, 1, staleness,
+                      0.9, 32 << 20, timeout_ms, 4, False, True, mode == "ok")
+        eng.set_optimizer(optimizer)
+        eng.configure_optimizer("lr", 0.1 if optimizer == "sgd" else 1e-2)
+        if optimizer == "sgd":
+            eng.configure_optimizer("momentum", 0.9)
+        params = [torch.full((n,), 0.5 + node + local) for n in SIZES]   # only node 0 / local 0 values must survive
+        idxs = [eng.pre_train_init(pi, f"p{pi}", p.numel(), p.data_ptr()) for pi, p in enumerate(params)]
+        if mode == "drop" and node == 1:
+            eng.drop_tx_containing("@")
+        for step in range(steps):
+            if mode == "die" and node == 1 and step == 2:
+                os._exit(0)
+            for pi in idxs:
+                eng.pre_forward_process(pi)
+            for pi in reversed(idxs):
+                g = synthetic_grad(node, local, step, pi, SIZES[pi])
+                eng.post_backward_process(pi, g.data_ptr())
+        eng.synchronize()
+        drift = max(eng.force_model_sync(pi, True) for pi in idxs)
+        stats = eng.stats_json(False)
+        eng.barrier()
+        q.put((node, local, "ok", {"params": [p.numpy().copy() for p in params], "drift": drift,
+                                   "versions": [eng.model_version(pi) for pi in idxs], "stats_len": len(stats)}))
+        del eng
+    except Exception as e:  # noqa: BLE001
+        q.put((node, local, "error", f"{type(e).__name__}: {e}\n{traceback.format_exc()[-600:]}"))

@@ -1,0 +1,214 @@
+"""Host-side machinery of the CPU tier: shared memory, TCP ring, multi-process pipeline, failure handling.
+Everything here runs on CPU ranks on localhost; failures are injected on the host (a process that
+never joins, a sender that drops its messages, a node that exits)."""
+import multiprocessing as mp
+import os
+import socket
+import threading
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from stellatrain_b200 import cpu_tier
+from stellatrain_b200.ops import oracle as O
+
+ext = cpu_tier._load()
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_shm_manager_offsets_and_barriers():
+    session = os.getpid() * 100 + 7
+    master = ext.ShmManager(True, session, 0, 2, 1 << 20)
+    other = ext.ShmManager(False, session, 1, 2, 1 << 20)
+    p = master.alloc(4096)
+    off = master.offset_of(p)
+    q = other.from_offset(off)
+    a = cpu_tier._from_ptr(p, 16); b = cpu_tier._from_ptr(q, 16)
+    a.fill_(3.5)
+    assert float(b.sum()) == 56.0, "both mappings must see the same bytes"
+    assert other.alloc(64) != p and master.data_used() >= 4096 + 64
+    with pytest.raises(MemoryError):
+        master.alloc(2 << 20)
+    t0 = time.time()
+    assert master.barrier(200) is False and time.time() - t0 < 2.0     # the other process never arrives
+    res = []
+    th = threading.Thread(target=lambda: res.append(other.barrier(5000)))
+    th.start()
+    assert master.barrier(5000) is True
+    th.join()
+    assert res == [True]
+    assert master.arrive(42, 2) is False and master.complete(42) is False
+    assert other.arrive(42, 2) is True and master.complete(42) is True
+    master.depart(42, 2); other.depart(42, 2)
+    del other, master
+
+
+def _ring(world, port):
+    boxes = [ext.CommManager("127.0.0.1", port, 5000) for _ in range(world)]
+    boxes[0].start_server(world)
+    oks = [None] * world
+    ths = [threading.Thread(target=lambda r=r: oks.__setitem__(r, boxes[r].start_client(r, world, 1))) for r in range(world)]
+    [t.start() for t in ths]; [t.join() for t in ths]
+    assert oks == [True] * world
+    return boxes
+
+
+def _wait_for(fn, timeout=5.0):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        v = fn()
+        if v:
+            return v
+        time.sleep(0.01)
+    return fn()
+
+
+def test_comm_ring_stash_narrowing_and_control_plane():
+    boxes = _ring(3, free_port())
+    try:
+        # rank 0 -> 1: message arrives BEFORE its receive is posted (stash), 16-bit indices, fp16 values
+        boxes[0].queue_tx(5, "3@1@w!0", [1, 40000, 65535], [0.5, -2.0, 1024.0], 65536, True, 1)
+        assert _wait_for(lambda: boxes[1].stashed() == 1)
+        boxes[1].post_recv("3@1@w!0")
+        (key, flags, idx, val), = boxes[1].drain()
+        assert key == "3@1@w!0" and flags == 0x03 and idx == [1, 40000, 65535] and val == [0.5, -2.0, 1024.0]
+        # wide indices stay 32-bit; priority: the smaller number leaves first
+        boxes[1].post_recv("a"); boxes[1].post_recv("b")
+        boxes[0].drop_keys_containing("hold", 150)          # stall the sender so both wait in the queue
+        boxes[0].queue_tx(0, "hold", [0], [0.0], 10)
+        boxes[0].queue_tx(9, "b", [70000], [1.0], 100000)
+        boxes[0].queue_tx(1, "a", [70001], [2.0], 100000)
+        got = _wait_for(lambda: (lambda d: d if len(d) == 2 else None)(boxes[1].drain() if boxes[1].stashed() >= 0 and time.sleep(0.4) is None else []))
+        assert [g[0] for g in got] == ["a", "b"] and got[0][1] == 0 and got[0][2] == [70001]
+        # a dropped message never arrives; nothing hangs
+        boxes[2].drop_keys_containing("lost")
+        boxes[0].post_recv("lost!0")
+        boxes[2].queue_tx(0, "lost!0", [1], [1.0], 10)
+        time.sleep(0.3)
+        assert boxes[0].drain() == []
+        # control plane: model relay through the broker, barrier, clock offset, stats
+        res = {}
+        th = threading.Thread(target=lambda: res.__setitem__("r", boxes[2].recv_init_model("init@0@w", 4)))
+        th.start()
+        time.sleep(0.1)
+        assert boxes[0].send_init_model("init@0@w", [1.0, 2.0, 3.0, 4.0])
+        th.join()
+        assert res["r"] == (True, [1.0, 2.0, 3.0, 4.0])
+        ths = [threading.Thread(target=lambda b=b: res.__setitem__(id(b), b.global_barrier())) for b in boxes]
+        [t.start() for t in ths]; [t.join() for t in ths]
+        assert all(res[id(b)] for b in boxes)
+        assert abs(boxes[1].sync_time(4)) < 50.0
+        assert boxes[1].report_stat(100.0, 90.0) and _wait_for(lambda: boxes[0].broker_stats()) == [(1, 100.0, 90.0)]
+        assert boxes[0].bytes_sent() > 0 and boxes[1].bytes_received() > 0 and boxes[1].rx_peak_bytes_per_s() > 0
+    finally:
+        for b in boxes[::-1]:
+            b.close()
+
+
+def test_bandwidth_monitor_and_interfaces():
+    m = ext.BandwidthMonitor()
+    for _ in range(5):
+        m.add(1000)
+    assert m.total_bytes() == 5000 and m.peak_bytes_per_s() >= 10000 and m.mean_bytes_per_s() == 5000
+    assert any(ip == "127.0.0.1" for _, ip, lo, _ in ext.list_interfaces())
+    os.environ["PUBLIC_IP"] = "10.1.2.3"
+    try:
+        assert ext.pick_local_ip() == "10.1.2.3"
+    finally:
+        del os.environ["PUBLIC_IP"]
+
+
+def _oracle_run(world, local_world, steps, method, optimizer):
+    from _cpu_workers import SIZES, synthetic_grad
+
+    params = [torch.full((n,), 0.5) for n in SIZES]
+    resid = [[torch.zeros(n) for n in SIZES] for _ in range(world)]
+    states = [[O.ThresholdState() for _ in SIZES] for _ in range(world)]
+    if optimizer == "sgd":
+        cfg, st = O.SGDConfig(lr=0.1, momentum=0.9), [O.SGDState() for _ in SIZES]
+    else:
+        cfg, st = O.AdamConfig(lr=1e-2), [O.AdamState() for _ in SIZES]
+    for step in range(steps):
+        for pi, n in enumerate(SIZES):
+            k = max(1, int(n * ((1.0 - 0.9) / world)))
+            streams = []
+            for node in range(world):
+                g = sum(synthetic_grad(node, l, step, pi, n) for l in range(local_world))
+                idx, val, resid[node][pi] = O.compress_step(method, g, resid[node][pi], k, states[node][pi])
+                keep = idx < n
+                streams.append((idx[keep], val[keep]))
+                resid[node][pi] = resid[node][pi][:n]
+            dense, touched = O.merge_streams(n, streams, [1.0 / world] * world)
+            (O.sparse_sgd if optimizer == "sgd" else O.sparse_adam)(params[pi], dense, touched, cfg, st[pi])
+    return params
+
+
+def _launch(world, local_world, steps, method, optimizer, staleness, mode, join_timeout=90):
+    from _cpu_workers import engine_worker
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port, session = free_port(), (os.getpid() % 10000) * 1000 + np.random.randint(0, 900)
+    procs = []
+    for node in range(world):
+        for local in range(local_world):
+            p = ctx.Process(target=engine_worker, args=(q, port, session, world, node, local_world, local, steps, method,
+                                                        optimizer, staleness, mode))
+            p.start()
+            procs.append(p)
+    results = []
+    deadline = time.time() + join_timeout
+    while len(results) < len(procs) and time.time() < deadline:
+        try:
+            results.append(q.get(timeout=0.5))
+        except Exception:  # noqa: BLE001 - queue.Empty
+            if mode == "die" and sum(p.is_alive() for p in procs) == 0:
+                break
+    for p in procs:
+        p.join(timeout=5)
+        if p.is_alive():
+            p.kill()
+    for node in range(world):
+        ext.ShmManager.unlink_session(session + node)
+    return results
+
+
+@pytest.mark.parametrize("method,optimizer,staleness", [("topk", "sgd", 1), ("thresholdv16", "adam", 0), ("thresholdv", "adam", 1)])
+def test_two_nodes_two_local_processes_match_oracle(method, optimizer, staleness):
+    world, local_world, steps = 2, 2, 6
+    results = _launch(world, local_world, steps, method, optimizer, staleness, "ok")
+    assert len(results) == 4 and all(r[2] == "ok" for r in results), results
+    want = _oracle_run(world, local_world, steps, method, optimizer)
+    for node, local, _, out in results:
+        assert out["drift"] == 0.0
+        assert out["versions"] == [steps] * 3
+        assert out["stats_len"] > 100
+        for got, w in zip(out["params"], want):
+            np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
+
+
+def test_absent_local_process_times_out_instead_of_hanging():
+    t0 = time.time()
+    results = _launch(1, 2, 2, "topk", "sgd", 1, "absent", join_timeout=40)
+    assert time.time() - t0 < 40
+    status = {(n, l): s for n, l, s, _ in results}
+    assert status[(0, 1)] == "absent"
+    assert status[(0, 0)] == "error", results
+    assert "did not all reach configure" in [r[3] for r in results if r[2] == "error"][0]
+
+
+@pytest.mark.parametrize("mode", ["drop", "die"])
+def test_lost_peer_surfaces_as_error(mode):
+    t0 = time.time()
+    results = _launch(2, 1, 5, "topk", "sgd", 0, mode, join_timeout=60)
+    assert time.time() - t0 < 60
+    by_node = {n: (s, info) for n, l, s, info in results}
+    assert by_node[0][0] == "error", results     # node 0 never gets node 1's stream
+    assert any(w in by_node[0][1] for w in ("timed out", "failed", "closed")), by_node[0][1]
