@@ -1,0 +1,224 @@
+"""Centralised controller: receives per-GPU telemetry, answers with instructions.
+
+Role of the reference's ``BatchSizeRateAlloc`` server (backend/src/engine/batch_rate_alloc.py:16-335):
+one connection per GPU, every report is answered with either ``OK`` or a queued ``INSTRUCTION``; a
+scoreboard keeps the latest smoothed measurements per client; a worker fits the per-GPU compute model and
+runs the optimiser; ``DISABLE_RATE_ADAPT`` turns instructions off; ``MODEL_PROFILE`` names the
+convergence profile.  Transport is framed TCP (``messages.py``) instead of ZeroMQ ROUTER/REQ, threads
+talk through queues, and a pid file guards against two controllers on one port.
+
+    python -m stellatrain_b200.control.controller --port 5556
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import queue
+import socket
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import numpy as np
+import pandas as pd
+
+from . import messages as M
+from .gp_profile import load_profile
+from .optimizer import BatchRateOptimizer, TrafficModel, max_batch_for
+
+LOG_PATH = "/tmp/stellatrain-b200-controller.log"
+SMOOTH = 0.9     # scoreboard EWMA
+
+
+@dataclass
+class Client:
+    gpu_id: int
+    rank: int
+    local_rank: int
+    gpu_name: str
+    pending: "queue.Queue[M.Instruction]" = field(default_factory=queue.Queue)
+
+
+class Controller:
+    def __init__(self, port: int = 5556, host: str = "0.0.0.0", adapt: Optional[bool] = None,
+                 profile_path: Optional[str] = None, transport: str = "nvlink") -> None:
+        self.adapt = (os.environ.get("DISABLE_RATE_ADAPT", "0") in ("", "0")) if adapt is None else adapt
+        self.profile = load_profile(profile_path or os.environ.get("MODEL_PROFILE"))
+        self.transport = transport
+        self.sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+        self.sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        self.sock.bind((host, port))
+        self.sock.listen(64)
+        self.port = self.sock.getsockname()[1]
+        self.clients: Dict[int, Client] = {}
+        self.scoreboard = pd.DataFrame(columns=["location", "gpu", "batch_size", "grad_acc", "comp_ratio", "fwd_ms", "bwd_ms",
+                                                "bwd_fwd_gap_ms", "intra_fwd_gap_ms", "send_mbps", "recv_mbps", "uiter"])
+        self.global_init: Optional[M.GlobalInit] = None
+        self.optimizer: Optional[BatchRateOptimizer] = None
+        self.rx: "queue.Queue[M.LocalTelemetry]" = queue.Queue()
+        self.lock = threading.Lock()
+        self.stop = threading.Event()
+        self.latest_iter = 0
+        self.issued: List[M.Instruction] = []
+        self.threads: List[threading.Thread] = []
+
+    # ---------------------------------------------------------------- threads
+    def start(self) -> "Controller":
+        for fn in (self._accept_main, self._logic_main):
+            t = threading.Thread(target=fn, daemon=True, name=fn.__name__)
+            t.start()
+            self.threads.append(t)
+        return self
+
+    def close(self) -> None:
+        self.stop.set()
+        try:
+            self.sock.close()
+        except OSError:
+            pass
+
+    def _accept_main(self) -> None:
+        self.sock.settimeout(0.2)
+        while not self.stop.is_set():
+            try:
+                conn, _ = self.sock.accept()
+            except (socket.timeout, OSError):
+                continue
+            conn.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+            t = threading.Thread(target=self._io_main, args=(conn,), daemon=True, name="controller-io")
+            t.start()
+
+    def _io_main(self, conn: socket.socket) -> None:
+        client: Optional[Client] = None
+        try:
+            while not self.stop.is_set():
+                frame = M.recv_frame(conn)
+                if frame is None:
+                    return
+                mtype, payload = frame
+                reply = M.pack_frame(M.OK)
+                if mtype == M.LOCAL_INIT:
+                    li = M.parse(mtype, payload)
+                    client = Client(li.gpu_id, li.rank, li.local_rank, li.gpu_name)
+                    with self.lock:
+                        self.clients[li.gpu_id] = client
+                        self.scoreboard.loc[li.gpu_id, ["location", "gpu"]] = [f"{li.rank}:{li.local_rank}", li.gpu_name]
+                        if self.optimizer is not None and li.gpu_id < self.optimizer.num_gpus:
+                            self.optimizer.set_max_batch(li.gpu_id, max_batch_for(li.gpu_name))
+                elif mtype == M.LOCAL:
+                    t = M.parse(mtype, payload)
+                    self.rx.put(t)
+                    if client is not None:
+                        try:
+                            reply = M.pack_instruction(client.pending.get_nowait())
+                        except queue.Empty:
+                            pass
+                elif mtype == M.GLOBAL_INIT:
+                    self._on_global_init(M.parse(mtype, payload))
+                elif mtype == M.TERMINATE:
+                    conn.sendall(reply)
+                    self.stop.set()
+                    return
+                conn.sendall(reply)
+        except (OSError, ValueError):
+            return
+        finally:
+            conn.close()
+
+    def _on_global_init(self, gi: M.GlobalInit) -> None:
+        with self.lock:
+            self.global_init = gi
+            traffic = TrafficModel(gi.param_counts, self.transport, gi.grad_fp16, gi.grad_idx_u16)
+            self.optimizer = BatchRateOptimizer(gi.num_gpus, gi.num_nodes, traffic, self.profile,
+                                                latest_iter=lambda: self.latest_iter)
+            for gid, c in self.clients.items():
+                if gid < gi.num_gpus:
+                    self.optimizer.set_max_batch(gid, max_batch_for(c.gpu_name))
+
+    def _update_scoreboard(self, t: M.LocalTelemetry) -> dict:
+        m, c = t.measurement, t.config
+        new = {"batch_size": c.ubatch_size, "grad_acc": c.gradient_accumulation, "comp_ratio": c.compression_rate,
+               "fwd_ms": m.fwd_delay_ms, "bwd_ms": m.bwd_delay_ms, "bwd_fwd_gap_ms": m.bwd_fwd_gap_ms,
+               "intra_fwd_gap_ms": m.intra_fwd_gap_ms, "send_mbps": m.grad_send_thpt_mbps, "recv_mbps": m.grad_recv_thpt_mbps}
+        with self.lock:
+            for k, v in new.items():
+                old = self.scoreboard.at[t.gpu_id, k] if (t.gpu_id in self.scoreboard.index and k in self.scoreboard.columns) else None
+                smooth = k in ("fwd_ms", "bwd_ms", "bwd_fwd_gap_ms", "intra_fwd_gap_ms", "send_mbps", "recv_mbps")
+                if smooth and old is not None and not pd.isna(old) and self.scoreboard.at[t.gpu_id, "batch_size"] == c.ubatch_size:
+                    v = SMOOTH * float(old) + (1.0 - SMOOTH) * float(v)
+                self.scoreboard.at[t.gpu_id, k] = v
+            self.scoreboard.at[t.gpu_id, "uiter"] = t.uiter
+            self.latest_iter = max(self.latest_iter, int(t.uiter) // max(1, c.gradient_accumulation))
+            row = {k: self.scoreboard.at[t.gpu_id, k] for k in new}
+        row["gpu"] = t.gpu_id
+        return row
+
+    def _logic_main(self) -> None:
+        last_dump = 0.0
+        while not self.stop.is_set():
+            try:
+                t = self.rx.get(timeout=0.2)
+            except queue.Empty:
+                continue
+            batch = [t]
+            while True:
+                try:
+                    batch.append(self.rx.get_nowait())
+                except queue.Empty:
+                    break
+            rows = [self._update_scoreboard(x) for x in batch]
+            opt = self.optimizer
+            if opt is None or not self.adapt:
+                continue
+            rows = [r for r in rows if r["gpu"] < opt.num_gpus]
+            opt.update(rows)
+            with self.lock:
+                recv = pd.to_numeric(self.scoreboard["recv_mbps"], errors="coerce").dropna()
+            measured = float(recv.max()) if len(recv) else 0.0
+            inst = opt.step(self.latest_iter, measured)
+            if inst is not None:
+                for gid, c in list(self.clients.items()):
+                    if gid < len(inst.batch):
+                        msg = M.Instruction(inst.iter, M.TrainConfig(int(inst.batch[gid]), 1, float(inst.comp_ratio)))
+                        c.pending.put(msg)
+                        self.issued.append(msg)
+            if time.time() - last_dump > 2.0:
+                last_dump = time.time()
+                try:
+                    with self.lock, open(LOG_PATH, "w") as f:
+                        f.write(self.scoreboard.to_string())
+                except OSError:
+                    pass
+
+
+def _single_instance(port: int) -> None:
+    pid_file = f"/tmp/stellatrain-b200-controller-{port}.pid"
+    try:
+        old = int(open(pid_file).read())
+        if old != os.getpid():
+            os.kill(old, 15)     # the exact pid recorded by the previous controller on this port
+            time.sleep(0.2)
+    except (OSError, ValueError):
+        pass
+    with open(pid_file, "w") as f:
+        f.write(str(os.getpid()))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--port", type=int, default=5556)
+    ap.add_argument("--profile", default=None)
+    ap.add_argument("--transport", default="nvlink", choices=["nvlink", "tcp"])
+    args = ap.parse_args()
+    _single_instance(args.port)
+    c = Controller(args.port, profile_path=args.profile, transport=args.transport).start()
+    try:
+        while not c.stop.is_set():
+            time.sleep(0.2)
+    finally:
+        c.close()
+
+
+if __name__ == "__main__":
+    main()

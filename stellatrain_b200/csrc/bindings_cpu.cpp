@@ -336,7 +336,11 @@ PYBIND11_MODULE(_Ccpu, m) {
         TrainMeasurement tm{meas[0], meas[1], meas[2], meas[3], meas[4], meas[5]};
         InstructionCallback fn;
         if (!cb.is_none()) {
-          auto holder = std::make_shared<py::object>(cb);
+          // the callable is released on the client's thread: take the GIL for that too
+          std::shared_ptr<py::object> holder(new py::object(cb), [](py::object* p) {
+            py::gil_scoped_acquire acq;
+            delete p;
+          });
           fn = [holder](uint64_t since, const TrainConfig& tc) {
             py::gil_scoped_acquire acq;
             (*holder)(since, tc.ubatch_size, tc.gradient_accumulation, tc.compression_rate);

@@ -1,0 +1,157 @@
+"""Control plane on CPU: wire format, profile evaluation, optimiser phases, controller round trip with the
+native telemetry client, shaped-link schedule."""
+import socket
+import threading
+import time
+
+import numpy as np
+import pytest
+
+from stellatrain_b200.control import messages as M
+from stellatrain_b200.control.controller import Controller
+from stellatrain_b200.control.gp_profile import AnalyticProfile, GPProfile, ProfileMeta, fit_profile, load_profile, matern
+from stellatrain_b200.control.optimizer import (BatchRateOptimizer, Phase, TrafficModel, fit_alpha_beta, saturating)
+from stellatrain_b200.control.shaper import BandwidthSchedule, TokenBucket
+
+
+def test_message_roundtrip():
+    lt = M.LocalTelemetry(3, 77, M.TrainConfig(32, 2, 0.97), M.Measurement(1, 2, 3, 4, 5, 6))
+    raw = M.pack_local(lt)
+    magic, mtype, n = M._FRAME.unpack(raw[:12])
+    assert magic == M.MAGIC and mtype == M.LOCAL and n == len(raw) - 12
+    assert M.parse(mtype, raw[12:]) == lt
+    gi = M.GlobalInit(2, 8, False, True, [10, 20, 30])
+    raw = M.pack_global_init(gi)
+    assert M.parse(M.GLOBAL_INIT, raw[12:]) == gi
+    ins = M.Instruction(42, M.TrainConfig(48, 1, 0.9))
+    assert M.parse(M.INSTRUCTION, M.pack_instruction(ins)[12:]) == ins
+    li = M.LocalInit(1, 0, 1, "NVIDIA B200")
+    assert M.parse(M.LOCAL_INIT, M.pack_local_init(li)[12:]) == li
+
+
+def test_gp_profile_fit_and_io(tmp_path):
+    rng = np.random.default_rng(0)
+    tb = rng.uniform(64, 1024, 40); bw = rng.uniform(0.2, 2.0, 40)
+    truth = lambda a, b: 0.01 * np.log1p(a / 256) + 0.02 / (1 + b)
+    prof = fit_profile(tb, bw, truth(tb, bw), ProfileMeta(batch_size=256, max_batch_size=1024, bandwidth=1.0))
+    q_tb, q_bw = np.array([200.0, 800.0]), np.array([0.5, 1.5])
+    np.testing.assert_allclose(prof.h(q_tb, q_bw), truth(q_tb, q_bw), atol=2e-3)
+    prof.save(tmp_path / "p.npz")
+    again = load_profile(str(tmp_path / "p.npz"))
+    np.testing.assert_allclose(again.h(q_tb, q_bw), prof.h(q_tb, q_bw))
+    assert matern(np.array([0.0]), 1.5)[0] == 1.0 and matern(np.array([1.0]), 0.5)[0] == pytest.approx(np.exp(-1))
+    with pytest.raises(ValueError):
+        load_profile("something.pkl")
+    a = AnalyticProfile()
+    assert a.h(1024, 1.0)[0] > a.h(128, 1.0)[0] and a.h(256, 0.1)[0] > a.h(256, 10.0)[0]
+
+
+def test_alpha_beta_fit_recovers_saturation():
+    xs = np.array([4, 8, 16, 32, 64, 128]); ys = saturating(40.0, 900.0, xs)
+    a, b = fit_alpha_beta(list(zip(xs, ys)), (20.0, 500.0), 1.0, 1.0)
+    assert a == pytest.approx(40.0, rel=0.05) and b == pytest.approx(900.0, rel=0.02)
+
+
+def _rows(batches, ms_per_item, gap=0.0, ratio=0.99):
+    return [{"gpu": g, "batch_size": b, "bwd_ms": b * ms_per_item[g] + 2.0, "fwd_ms": 1.0, "comp_ratio": ratio,
+             "bwd_fwd_gap_ms": gap, "intra_fwd_gap_ms": 0.0} for g, b in enumerate(batches)]
+
+
+def test_optimizer_phases_and_heterogeneous_batches():
+    it = {"n": 0}
+    opt = BatchRateOptimizer(2, 2, TrafficModel([1_000_000] * 10, "tcp"), latest_iter=lambda: it["n"], reoptimize_every=5)
+    opt.set_max_batch(0, 64); opt.set_max_batch(1, 64)
+    speed = [0.5, 1.0]          # GPU 1 is twice as slow per item
+    batches = np.array([8.0, 8.0])
+    issued = []
+    for step in range(400):
+        it["n"] = step
+        opt.update(_rows(batches, speed))
+        inst = opt.step(step, measured_mbps=400.0)
+        if inst is not None:
+            issued.append(inst)
+            assert inst.iter == step + 3, "effective three iterations after the latest observed one"
+            batches = inst.batch.copy()
+        if opt.phase == Phase.RUNNING and len(issued) > 12:
+            break
+    assert opt.phase == Phase.RUNNING
+    gaps = np.diff([i.iter for i in issued])
+    assert gaps.min() >= 4, "at most one instruction per four observed iterations"
+    final = issued[-1]
+    assert final.batch[0] > final.batch[1], "the faster GPU gets the larger batch"
+    t = opt.iteration_seconds(final.batch)
+    assert abs(t[0] - t[1]) / t.max() < 0.35
+    assert 0.0 <= final.comp_ratio <= 0.999
+
+
+def test_compression_follows_bandwidth():
+    traffic = TrafficModel([5_000_000] * 20, "nvlink")
+    assert traffic.tx_bytes(0.99) == pytest.approx(8 * 20 * 50_000 + 64, rel=1e-3)
+    assert traffic.tx_bytes(0.9) > 9 * traffic.tx_bytes(0.99)
+    opt = BatchRateOptimizer(2, 2, traffic)
+    x = np.array([32.0, 32.0])
+    tight, loose = opt._min_ratio_for(x, 50.0), opt._min_ratio_for(x, 5000.0)
+    assert tight > loose and tight > 0.9
+
+
+def test_controller_roundtrip_with_native_client():
+    from stellatrain_b200 import cpu_tier
+
+    ext = cpu_tier._load()
+    ctl = Controller(port=0, host="127.0.0.1", adapt=True).start()
+    try:
+        uri = f"tcp://127.0.0.1:{ctl.port}"
+        server = ext.TelemetryServer(uri, False, 3000)
+        clients = [ext.TelemetryClient(uri, g, "NVIDIA B200", 0, g, 3000) for g in range(2)]
+        assert server.send_global_telemetry(1, 2, [1000, 2000, 300000], False, False)
+        got = []
+        cfg = [ext.TrainConfig(8, 1, 0.99), ext.TrainConfig(8, 1, 0.99)]
+        for it in range(120):
+            for g, c in enumerate(clients):
+                bwd = cfg[g].ubatch_size * (0.5 if g == 0 else 1.0) + 2.0
+                c.report(it, cfg[g], [300.0, 300.0, 1.0, bwd, 0.0, 0.0],
+                         lambda since, ub, ga, cr, g=g: (got.append((g, since, ub, cr)), setattr(cfg[g], "ubatch_size", ub)))
+            time.sleep(0.01)
+            if len(got) >= 6:
+                break
+        assert len(got) >= 2, "the controller must have issued instructions"
+        assert all(ub >= 1 and 0.0 <= cr <= 0.999 for _, _, ub, cr in got)
+        assert clients[0].sent() > 0 and clients[0].alive()
+        assert set(ctl.scoreboard.index) == {0, 1} and ctl.scoreboard.at[0, "gpu"] == "NVIDIA B200"
+        assert server.terminate()
+        del clients, server
+    finally:
+        ctl.close()
+
+
+def test_client_survives_controller_loss():
+    from stellatrain_b200 import cpu_tier
+
+    ext = cpu_tier._load()
+    ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
+    c = ext.TelemetryClient(f"127.0.0.1:{ctl.port}", 0, "cpu", 0, 0, 500)
+    c.report(0, ext.TrainConfig(4, 1, 0.9), [0, 0, 1, 2, 0, 0])
+    time.sleep(0.1)
+    ctl.close(); ctl.stop.set()
+    time.sleep(0.5)
+    for i in range(5):
+        c.report(i + 1, ext.TrainConfig(4, 1, 0.9), [0, 0, 1, 2, 0, 0])   # must not raise or block
+    time.sleep(1.2)
+    assert c.queued() <= 5
+    with pytest.raises(RuntimeError):
+        ext.TelemetryClient("127.0.0.1:1", 0, "cpu", 0, 0, 300)
+
+
+def test_schedule_and_token_bucket():
+    s1, s2 = BandwidthSchedule(seed=7), BandwidthSchedule(seed=7)
+    ts = np.linspace(0, 100, 200)
+    v = [s1.gbps_at(t) for t in ts]
+    assert v == [s2.gbps_at(t) for t in ts] and min(v) >= 10.0 and max(v) <= 40.0 and len(set(v)) > 10
+    assert BandwidthSchedule(seed=8).gbps_at(0.0) != s1.gbps_at(0.0)
+    now = {"t": 0.0}
+    tb = TokenBucket(BandwidthSchedule(seed=1, lo_gbps=8.0, hi_gbps=8.0), burst_bytes=1000, clock=lambda: now["t"])
+    assert tb.delay_for(1000) == 0.0
+    w = tb.delay_for(1_000_000)              # 1 MB at 1 GB/s
+    assert w == pytest.approx(1e-3, rel=0.01)
+    now["t"] += w + 0.5
+    assert tb.delay_for(500) == 0.0
