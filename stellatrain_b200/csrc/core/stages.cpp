@@ -21,7 +21,7 @@ enum BarrierStage : int { kAfterCopyIn = 0, kAfterGather = 1, kAfterOptimize = 2
 uint32_t entries_for(uint32_t numel, double ratio, int world) {
   // k = max(min(n, 1), n * (1 - ratio) / W)   (reference compress.cpp:44-52)
   const double k_frac = (1.0 - ratio) / std::max(1, world);
-  const uint32_t k = static_cast<uint32_t>(static_cast<double>(numel) * k_frac);
+  const uint32_t k = static_cast<uint32_t>(static_cast<double>(numel) * k_frac + 1e-6);   // same rounding guard as buckets.py
   return std::min(numel, std::max<uint32_t>(std::min<uint32_t>(numel, 1u), k));
 }
 

@@ -45,7 +45,8 @@ def entries_for(numel: int, ratio: float, world: int) -> int:
     if numel <= 0:
         return 0
     k_frac = (1.0 - float(ratio)) / max(1, int(world))
-    return int(min(numel, max(min(numel, 1), int(numel * k_frac))))
+    # the small epsilon keeps products such as 5000 * (1 - 0.9) = 499.99999999999994 from losing an entry
+    return int(min(numel, max(min(numel, 1), int(numel * k_frac + 1e-6))))
 
 
 @dataclass

@@ -1,0 +1,168 @@
+"""Training driver (role of the reference's backend/test/test_end_to_end.py:15-163).
+
+    python -m stellatrain_b200.train --model resnet152 --dataset dummy --num-epochs 1 --batch-size 32 \
+        --compression 0.99 --optim adam --lr 1e-3 --local-world-size 8
+
+One process per local GPU is spawned (or ``--manual-spawn <local_rank>`` starts exactly one, e.g. under a
+debugger).  Environment, as in the reference's launch scripts (test_script.sh:32-40): MASTER_ADDR,
+MASTER_PORT, WORLD_SIZE (groups / nodes), RANK (group rank).  ``--tier cpu`` trains through the
+CPU-offload tier instead of the GPU-resident engine.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import time
+
+import torch
+import torch.multiprocessing as mp
+import torch.nn.functional as F
+
+
+def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: argparse.Namespace) -> None:
+    import stellatrain_b200 as st
+    from stellatrain_b200.models.registry import build_model, is_language_model
+    from stellatrain_b200.utils import dataloader as D
+    from stellatrain_b200.utils.misc import AverageMeter
+
+    master_addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    master_port = int(os.environ.get("MASTER_PORT", "5555"))
+    world_size = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    use_cuda = torch.cuda.is_available() and args.tier == "gpu"
+    lm = is_language_model(args.model)
+    model = build_model(args.model, args.num_classes)
+    global_rank, global_world = rank * local_world_size + local_rank, world_size * local_world_size
+
+    if args.tier == "gpu":
+        st.configure(master_addr, master_port, world_size, rank, master_pid, local_world_size, local_rank,
+                     args.compressor, args.gradient_accumulation, staleness=args.staleness)
+        st.configure_compression_ratio(args.compression)
+        st.set_optimizer(args.optim)
+        # linear scaling rule of the reference driver (test_end_to_end.py:48-52)
+        lr = args.lr / 256.0 * global_world * args.batch_size if args.scale_lr else args.lr
+        st.configure_optimizer("lr", lr)
+        if args.optim == "sgd":
+            st.configure_optimizer("momentum", args.momentum)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        model = model.to(dev)
+        if args.channels_last and not lm:
+            model = model.to(memory_format=torch.channels_last)
+        net = st.FasterDpModelWrapper(model, sequential=not lm)
+        sync, engine_of = st.synchronize, (lambda: net.engine)
+    else:
+        from stellatrain_b200.cpu_tier import CpuOffloadEngine
+
+        dev = torch.device("cuda", local_rank) if torch.cuda.is_available() else torch.device("cpu")
+        model = model.to(dev)
+        eng = CpuOffloadEngine(model, master_addr=master_addr, master_port=master_port, world_size=world_size, rank=rank,
+                               session=master_pid, local_world_size=local_world_size, local_rank=local_rank,
+                               method=args.compressor, gradient_accumulation=args.gradient_accumulation,
+                               staleness=args.staleness, ratio=args.compression, optimizer=args.optim,
+                               optimizer_options={"lr": args.lr, **({"momentum": args.momentum} if args.optim == "sgd" else {})})
+        net, sync, engine_of = model, eng.synchronize, (lambda: eng)
+
+    builders = {"imagenet": (D.build_imagenet_dataloader, args.imagenet_root), "imagenet100": (D.build_imagenet100_dataloader, args.imagenet_root),
+                "cifar100": (D.build_cifar100_dataloader, args.cifar100_root), "cifar10": (D.build_cifar10_dataloader, args.cifar10_root)}
+    full_batch = args.batch_size * args.gradient_accumulation
+    if args.dataset == "dummy":
+        base = D.DummyTokenGenerator(full_batch, args.seq_len, length=args.dummy_length, seed=global_rank) if lm else \
+            D.DummyInputGenerator(full_batch, length=args.dummy_length, num_class=args.num_classes, seed=global_rank)
+    else:
+        fn, root = builders[args.dataset]
+        base = fn(root, full_batch, args.num_workers, world_size=global_world, rank=global_rank)
+    hook = None
+    if args.telemetry_uri and args.tier == "gpu":
+        from stellatrain_b200.parallel.telemetry import TelemetryHook
+
+        net._ensure_engine()
+        hook = TelemetryHook(net.engine, args.telemetry_uri, args.batch_size)
+
+    meter, global_step, t_start = AverageMeter(), 0, time.time()
+    for epoch in range(args.num_epochs):
+        loader = st.StellaTrainDataLoader(D.PrefetchLoader(base, dev if dev.type == "cuda" else None,
+                                                           channels_last=args.channels_last and not lm),
+                                          gradient_accumulation=args.gradient_accumulation)
+        for idx, (data, target) in enumerate(loader):
+            if args.num_iters is not None and global_step >= args.num_iters:
+                break
+            if dev.type != "cuda":
+                pass
+            if hook is not None:
+                data, target = hook.resize_batch(data, target)
+            ctx = hook.step() if hook is not None else None
+            marker = ctx.__enter__() if ctx is not None else None
+            loss = net(data, target)[1] if lm else F.cross_entropy(net(data), target)
+            if marker is not None:
+                marker.backward_begins()
+            loss.backward()
+            if ctx is not None:
+                ctx.__exit__(None, None, None)
+            if loader.is_eoi:
+                global_step += 1
+                if global_step % args.log_every == 0:
+                    meter.update(float(loss.detach()))
+                    if global_rank == 0:
+                        rate = global_step * args.batch_size * args.gradient_accumulation * global_world / (time.time() - t_start)
+                        print(f"epoch {epoch} step {global_step} loss {meter.val:.4f} ({rate:.0f} samples/s)", flush=True)
+        if args.tier == "gpu":
+            net.step()
+    sync()
+    if args.checkpoint and args.tier == "gpu":
+        from stellatrain_b200.utils import checkpoint
+
+        checkpoint.save(args.checkpoint, net.module, net.engine, {"global_step": global_step})
+    if global_rank == 0:
+        print(f"done: {global_step} iterations in {time.time() - t_start:.1f} s", flush=True)
+    if args.tier == "gpu":
+        st.barrier()
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    p.add_argument("--model", default="resnet18")
+    p.add_argument("--optim", default="sgd", choices=["sgd", "adam"])
+    p.add_argument("--num-classes", type=int, default=100)
+    p.add_argument("--num-iters", type=int, default=None)
+    p.add_argument("--batch-size", type=int, default=72, help="per-device batch size")
+    p.add_argument("--num-epochs", type=int, default=100)
+    p.add_argument("--compression", type=float, default=0.95, help="fraction of gradient entries dropped")
+    p.add_argument("--compressor", default="thresholdv16", choices=["thresholdv16", "thresholdv", "topk", "randomk"])
+    p.add_argument("--staleness", type=int, default=1, choices=[0, 1])
+    p.add_argument("--tier", default="gpu", choices=["gpu", "cpu"])
+    p.add_argument("--manual-spawn", type=int, default=None)
+    p.add_argument("--local-world-size", type=int, default=max(1, torch.cuda.device_count()))
+    p.add_argument("--local-master-pid", type=int, default=os.getpid())
+    p.add_argument("--lr", type=float, default=0.00625)
+    p.add_argument("--scale-lr", action="store_true", help="lr / 256 * world * batch, as the reference driver does")
+    p.add_argument("--momentum", type=float, default=0.9)
+    p.add_argument("--imagenet-root", default="/datasets/imagenet")
+    p.add_argument("--cifar100-root", default="/datasets/cifar100")
+    p.add_argument("--cifar10-root", default="/datasets/cifar10")
+    p.add_argument("--dataset", default="imagenet100", choices=["imagenet", "imagenet100", "cifar100", "cifar10", "dummy"])
+    p.add_argument("--dummy-length", type=int, default=128)
+    p.add_argument("--seq-len", type=int, default=1024)
+    p.add_argument("--num-workers", type=int, default=8)
+    p.add_argument("--gradient-accumulation", type=int, default=1)
+    p.add_argument("--channels-last", action="store_true")
+    p.add_argument("--telemetry-uri", default=None)
+    p.add_argument("--checkpoint", default=None)
+    p.add_argument("--log-every", type=int, default=10)
+    return p
+
+
+def main() -> None:
+    args = build_parser().parse_args()
+    if args.dataset == "imagenet":
+        args.num_classes = 1000
+    elif args.dataset == "cifar10":
+        args.num_classes = 10
+    print(f"per-device batch size is {args.batch_size}", flush=True)
+    if args.manual_spawn is not None:
+        train_worker(args.manual_spawn, args.local_master_pid, args.local_world_size, args)
+    else:
+        mp.spawn(train_worker, args=(os.getpid(), args.local_world_size, args), nprocs=args.local_world_size, join=True)
+
+
+if __name__ == "__main__":
+    main()

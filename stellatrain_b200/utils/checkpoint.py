@@ -1,0 +1,59 @@
+"""Checkpoints in torch ``state_dict`` form (the reference has none; state that must survive is listed in
+backend/src/optim/sgd.h:15-18, backend/src/optim/adam.h:15-18, backend/src/compress/thresholdv16.h:13-14,
+backend/src/engine/core.h:63, 111-127).
+
+Layout of one file per rank, written with ``torch.save``::
+
+    {"model": module.state_dict(), "engine": SparseDPEngine.state_dict(), "extra": {...}, "rank": r, "world": W}
+
+Every rank holds the full optimiser state for its replica (state is replicated, as in the reference), so
+rank 0's file alone restores a job of the same world size; ``save(..., all_ranks=True)`` also keeps the
+per-rank residuals, which differ between ranks.
+"""
+from __future__ import annotations
+
+import os
+from pathlib import Path
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+def _rank_world():
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+def save(path: str, module: torch.nn.Module, engine, extra: Optional[dict] = None, all_ranks: bool = True) -> Optional[str]:
+    rank, world = _rank_world()
+    engine.synchronize()
+    if not all_ranks and rank != 0:
+        return None
+    p = Path(path)
+    if world > 1:
+        p = p.with_name(f"{p.stem}.rank{rank}{p.suffix}")
+    p.parent.mkdir(parents=True, exist_ok=True)
+    tmp = p.with_suffix(p.suffix + ".tmp")
+    torch.save({"model": module.state_dict(), "engine": engine.state_dict(), "extra": extra or {}, "rank": rank,
+                "world": world}, tmp)
+    os.replace(tmp, p)     # a crash never leaves a half-written checkpoint under the final name
+    if world > 1:
+        dist.barrier()
+    return str(p)
+
+
+def load(path: str, module: torch.nn.Module, engine, map_location="cpu") -> dict:
+    rank, world = _rank_world()
+    p = Path(path)
+    if world > 1:
+        mine = p.with_name(f"{p.stem}.rank{rank}{p.suffix}")
+        p = mine if mine.exists() else p.with_name(f"{p.stem}.rank0{p.suffix}")
+    ck = torch.load(p, map_location=map_location, weights_only=False)
+    if ck["world"] != world:
+        raise ValueError(f"checkpoint was written by {ck['world']} ranks, this job has {world}")
+    # buffers (e.g. BatchNorm statistics) come from the model part, parameters from the engine's buckets
+    module.load_state_dict(ck["model"], strict=False)
+    engine.load_state_dict(ck["engine"])
+    return ck["extra"]

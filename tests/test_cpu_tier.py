@@ -13,6 +13,7 @@ import torch
 
 from stellatrain_b200 import cpu_tier
 from stellatrain_b200.ops import oracle as O
+from stellatrain_b200.parallel import buckets as B
 
 ext = cpu_tier._load()
 
@@ -137,7 +138,7 @@ def _oracle_run(world, local_world, steps, method, optimizer):
         cfg, st = O.AdamConfig(lr=1e-2), [O.AdamState() for _ in SIZES]
     for step in range(steps):
         for pi, n in enumerate(SIZES):
-            k = max(1, int(n * ((1.0 - 0.9) / world)))
+            k = B.entries_for(n, 0.9, world)
             streams = []
             for node in range(world):
                 g = sum(synthetic_grad(node, l, step, pi, n) for l in range(local_world))

@@ -1,0 +1,114 @@
+"""Frontend pieces that need no GPU: model cutting, micro-batch loader, bucket planning, CPU-tier driver."""
+import copy
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from stellatrain_b200.models import GPT, build_model, synthetic_batch, to_sequential
+from stellatrain_b200.parallel import buckets as B
+from stellatrain_b200.utils.loader import StellaTrainDataLoader, current_micro_step
+
+
+@pytest.mark.parametrize("name", ["resnet18", "vgg11", "vit_b_32", "swin_t"])
+def test_to_sequential_computes_the_same_function(name):
+    torch.manual_seed(0)
+    m = build_model(name, 10).eval()
+    seq = to_sequential(m).eval()
+    x = torch.randn(2, 3, 224, 224)
+    with torch.no_grad():
+        torch.testing.assert_close(seq(x), m(x), rtol=1e-5, atol=1e-5)
+    assert {id(p) for p in seq.parameters()} == {id(p) for p in m.parameters()}
+
+
+def test_gpt_sequential_and_loss():
+    torch.manual_seed(0)
+    m = GPT.from_name("gpt2-tiny").eval()
+    seq = to_sequential(m).eval()
+    x, y = synthetic_batch("gpt2-tiny", 3, seq_len=32)
+    with torch.no_grad():
+        logits, loss = m(x, y)
+        l2, loss2 = seq((x, y))
+    torch.testing.assert_close(l2, logits)
+    torch.testing.assert_close(loss2, loss)
+    assert abs(float(loss) - np.log(257)) < 0.5
+    assert GPT.from_name("gpt2", vocab_size=50257).num_parameters() == pytest.approx(124.4e6, rel=0.01)
+    with pytest.raises(NotImplementedError):
+        to_sequential(nn.ModuleDict({"a": nn.Linear(2, 2)}))
+
+
+def test_micro_batch_loader():
+    data = [(torch.arange(8).view(8, 1), torch.arange(8), {"m": torch.ones(8, 2)}, "tag")] * 2
+    loader = StellaTrainDataLoader(data, gradient_accumulation=4)
+    seen = []
+    for x, y, d, tag in loader:
+        seen.append((current_micro_step(), x.shape[0], d["m"].shape[0], tag, loader.is_eoi))
+    assert [s[0] for s in seen] == [0, 1, 2, 3] * 2 and all(s[1] == 2 and s[2] == 2 and s[3] == "tag" for s in seen)
+    assert [s[4] for s in seen] == [False, False, False, True] * 2
+    assert current_micro_step() == -1 and len(loader) == 8
+    with pytest.raises(ValueError):
+        list(StellaTrainDataLoader([(torch.zeros(3, 1),)], gradient_accumulation=4))
+
+
+def test_bucket_planning_and_entry_rule():
+    assert B.entries_for(1000, 0.99, 1) == 10 and B.entries_for(1000, 0.99, 8) == 1 and B.entries_for(50, 0.99, 8) == 1
+    assert B.entries_for(0, 0.5, 1) == 0 and B.entries_for(1000, 0.0, 1) == 1000
+    numels = [10, 5000, 17, 70000, 3]
+    groups = B.plan_buckets(numels, 6000)
+    assert [i for g in groups for i in g] == list(range(5)) and groups[0] == [0, 1, 2] and groups[1] == [3]
+    lay = B.BucketLayout([str(i) for i in range(5)], numels, chunk_elems=4096)
+    lay.set_ratio(0.9, 1)
+    offs = [s.off for s in lay.segments]
+    assert all(o % 16 == 0 for o in offs) and lay.n_total % 16 == 0
+    chunks = lay.chunk_table()
+    assert chunks["len"].sum() == lay.n_total and (chunks["len"] % 16 == 0).all() and chunks["len"].max() <= 4096
+    segs = lay.seg_table()
+    assert segs["k"].tolist() == [1, 500, 1, 7000, 1] and segs["out_off"].tolist() == [0, 1, 501, 502, 7502] and lay.cap == 7503
+    covered = np.zeros(lay.n_total, bool)
+    for c in chunks:
+        assert not covered[c["start"]: c["start"] + c["len"]].any()
+        covered[c["start"]: c["start"] + c["len"]] = True
+        s = lay.segments[c["seg"]]
+        assert s.off <= c["start"] and c["start"] + c["len"] <= s.off + s.n_pad
+    assert covered.all()
+
+
+def test_cpu_tier_trains_a_model_on_host_tensors():
+    from stellatrain_b200.cpu_tier import CpuOffloadEngine
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 4))
+    ref = copy.deepcopy(model)
+    eng = CpuOffloadEngine(model, method="topk", ratio=1e-9, optimizer="sgd", optimizer_options={"lr": 0.1}, staleness=0,
+                           data_bytes=8 << 20, workers=2)
+    # ratio ~ 0 keeps (almost) everything: equals dense SGD up to the one entry per tensor it may drop
+    opt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    x, y = torch.randn(64, 16), torch.randint(0, 4, (64,))
+    for _ in range(5):
+        F.cross_entropy(model(x), y).backward()
+        opt.zero_grad(); F.cross_entropy(ref(x), y).backward(); opt.step()
+    eng.synchronize()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        assert (p - q).abs().max() < 5e-2
+    assert "Total" in eng.stats_json()
+    eng.close()
+
+
+def test_train_driver_cpu_tier_end_to_end():
+    out = subprocess.run([sys.executable, "-m", "stellatrain_b200.train", "--tier", "cpu", "--model", "resnet18", "--dataset", "dummy",
+                          "--num-epochs", "1", "--dummy-length", "3", "--batch-size", "2", "--local-world-size", "1",
+                          "--compression", "0.9", "--num-classes", "10", "--log-every", "1"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "done: 3 iterations" in out.stdout
+
+
+def test_reference_arm_reports_unavailable():
+    import json
+
+    out = subprocess.run([sys.executable, "bench.py", "--impl", "reference"], capture_output=True, text=True, timeout=120)
+    d = json.loads(out.stdout.strip().splitlines()[-1])
+    assert d["impl"] == "reference" and "unavailable" in d
