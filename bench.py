@@ -54,6 +54,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--channels-last", type=int, default=1, help="NHWC memory format for vision models")
     ap.add_argument("--amp", default="none", choices=["none", "bf16"])
     ap.add_argument("--no-multicast", action="store_true")
+    ap.add_argument("--grad-mode", default="steal", choices=["steal", "flat"])
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
 
@@ -164,6 +165,7 @@ def main() -> None:
         st.configure_optimizer("lr", args.lr)
         st.state().engine_cfg.bucket_mb = args.bucket_mb
         st.state().engine_cfg.multicast = not args.no_multicast
+        st.state().engine_cfg.grad_mode = args.grad_mode
         net = st.FasterDpModelWrapper(model, sequential=False)
         net._ensure_engine()
         engine = net.engine
@@ -306,7 +308,7 @@ def main() -> None:
                 "lr": args.lr, "staleness": args.staleness, "bucket_mb": args.bucket_mb,
                 "transport": engine.transport if engine is not None else args.impl,
                 "multicast": bool(engine is not None and engine.pool is not None and engine.pool.mc_ptr),
-                "cuda_graph": bool(args.graph), "channels_last": bool(args.channels_last),
+                "cuda_graph": bool(args.graph), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
                 "l2": "per-step working set (233 MB of parameters plus activations) exceeds the 126 MB L2; no flush needed",
             },
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,

@@ -42,13 +42,15 @@ class EngineConfig:
     divide_k_by_world: bool = True        # k per rank = kept budget / world (compress.cpp:44)
     amsgrad: bool = False
     smart_momentum: bool = False
+    grad_mode: str = "steal"              # "steal": kernels read autograd's own gradient tensors through a
+                                          # pointer table; "flat": param.grad are views of a flat buffer
     fine_grained_gating: bool = False     # wait per first-using module instead of at the root
     status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
 
 
 class _BucketRuntime:
     __slots__ = ("bucket", "params", "pending", "full", "grad_ready", "apply_done", "has_pending_apply",
-                 "select_count", "apply_count", "first_module")
+                 "select_count", "apply_count", "first_module", "held", "seg_of")
 
     def __init__(self, bucket: GpuBucket, params: list[nn.Parameter], ga: int):
         self.bucket = bucket
@@ -61,6 +63,8 @@ class _BucketRuntime:
         self.select_count = 0
         self.apply_count = 0
         self.first_module = None
+        self.held: list = []          # gradient tensors the current select reads ("steal" mode)
+        self.seg_of = {id(p): i for i, p in enumerate(params)}
 
 
 class SparseDPEngine:
@@ -93,6 +97,7 @@ class SparseDPEngine:
         self.micro_step = 0
         self._failed: Optional[SparseStepError] = None
         self._capturing = False       # set while a CUDA graph of the step is being captured
+        self._capture_keepalive: list = []
         self._build_buckets(params)
         self._wire()
         self._install_hooks()
@@ -134,7 +139,9 @@ class SparseDPEngine:
                     flat_g = bucket.grad[seg.off : seg.off + seg.numel]
                     flat_p.copy_(_flatten_storage_order(dense))
                     p.data = flat_p.as_strided(dense.shape, dense.stride())
-                    p.grad = flat_g.as_strided(dense.shape, dense.stride())
+                    p.grad = flat_g.as_strided(dense.shape, dense.stride()) if cfg.grad_mode == "flat" else None
+            if cfg.grad_mode != "flat":
+                bucket.use_grad_table()
             rt = _BucketRuntime(bucket, plist, cfg.grad_accumulation)
             self.buckets.append(rt)
             self.param_names.append(names)
@@ -215,13 +222,30 @@ class SparseDPEngine:
     def _make_hook(self, bi: int) -> Callable:
         rt = self.buckets[bi]
 
-        def hook(_param) -> None:
+        steal = self.cfg.grad_mode != "flat"
+
+        def hook(param) -> None:
             rt.pending -= 1
+            if steal and rt.pending < len(rt.params):      # last micro-iteration: the gradient is final
+                self._note_gradient(rt, param)
             if rt.pending == 0:
                 rt.pending = rt.full
                 self._bucket_ready(bi)
 
         return hook
+
+    def _note_gradient(self, rt: _BucketRuntime, p: torch.Tensor) -> None:
+        """Record where autograd left this parameter's gradient.  The tensor must have the parameter's
+        memory layout and a 16-byte aligned start; otherwise it is copied into the flat buffer."""
+        si = rt.seg_of[id(p)]
+        seg = rt.bucket.layout.segments[si]
+        g = p.grad
+        if g.dtype != torch.float32 or g.stride() != p.stride() or (g.data_ptr() & 15):
+            flat = rt.bucket.grad[seg.off : seg.off + seg.numel].as_strided(p.shape, p.stride())
+            flat.copy_(g)
+            g = flat
+        rt.bucket.grad_tab_host[si] = g.data_ptr()
+        rt.held.append(g)
 
     def _make_gate(self, bis: list[int]) -> Callable:
         def pre(_mod, _inp) -> None:
@@ -255,8 +279,19 @@ class SparseDPEngine:
     def _bucket_ready(self, bi: int) -> None:
         rt = self.buckets[bi]
         cur = torch.cuda.current_stream(self.device)
-        rt.grad_ready.record(cur)
         s = self.sparse_stream
+        if self.cfg.grad_mode != "flat":
+            b = rt.bucket
+            b.grad_tab_dev.copy_(b.grad_tab_host, non_blocking=True)    # on the compute stream, before the event
+            held, rt.held = rt.held, []
+            if not self._capturing:
+                for g in held:
+                    g.record_stream(s)          # the allocator must not reuse them before the select has read them
+            else:
+                self._capture_keepalive.extend(held)   # a captured step reads these addresses on every replay
+            for p in rt.params:
+                p.grad = None
+        rt.grad_ready.record(cur)
         s.wait_event(rt.grad_ready)
         if self.cfg.staleness == 1 and rt.has_pending_apply:
             self._apply(rt)

@@ -132,6 +132,10 @@ class GpuBucket:
         self.select_handle = None
         self.select_wiring: Optional[Wiring] = None
         self.zero_grad_in_select = True
+        # "steal" mode: gradients stay where autograd put them; the kernels read them through a
+        # per-segment pointer table that the engine refreshes every iteration
+        self.grad_tab_host: Optional[torch.Tensor] = None
+        self.grad_tab_dev: Optional[torch.Tensor] = None
         self._bind()
 
     # ------------------------------------------------------------------ wiring
@@ -146,7 +150,8 @@ class GpuBucket:
     def _bind_one(self, h, wiring: Optional[Wiring]) -> None:
         L = self.layout
         h.set_data(
-            grad=self.grad.data_ptr(), grad_tab=0, resid=self.resid.data_ptr(), param=self.param.data_ptr(),
+            grad=self.grad.data_ptr(), grad_tab=self._ptr(self.grad_tab_dev), resid=self.resid.data_ptr(),
+            param=self.param.data_ptr(),
             m=self.m.data_ptr(), v=self._ptr(self.v), vmax=self._ptr(self.vmax), last=self._ptr(self.last),
             acc=self.acc.data_ptr(), stamp=self.stamp.data_ptr(), n_total=L.n_total,
         )
@@ -163,6 +168,17 @@ class GpuBucket:
         h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False)
         if wiring is not None:
             self._apply_wiring(h, wiring)
+
+    def use_grad_table(self) -> None:
+        """Switch the select to per-tensor gradient pointers (no flat gradient copy, no zeroing)."""
+        n_segs = len(self.layout.segments)
+        self.grad_tab_host = torch.zeros(n_segs, dtype=torch.int64).pin_memory()
+        self.grad_tab_dev = torch.zeros(n_segs, dtype=torch.int64, device=self.device)
+        for i, seg in enumerate(self.layout.segments):       # default: the flat buffer
+            self.grad_tab_host[i] = self.grad.data_ptr() + 4 * seg.off
+        self.grad_tab_dev.copy_(self.grad_tab_host)
+        self.zero_grad_in_select = False
+        self._bind()
 
     def recv_bytes(self) -> int:
         """Bytes of receive area one rank needs for this bucket (two slots, all sources)."""

@@ -179,6 +179,29 @@ def test_checkpoint_resume_is_bit_exact(monkeypatch):
     eng2.close()
 
 
+@pytest.mark.parametrize("grad_mode", ["flat", "steal"])
+def test_gradient_modes_agree(grad_mode):
+    """Flat-buffer gradients and stolen gradient tensors must train identically."""
+    data = batches(5)
+    model = small_net()
+    eng = make_engine(model, compressor="topk", ratio=0.9, optimizer="adam", staleness=1, grad_mode=grad_mode,
+                      grad_accumulation=2)
+    for x, y in data:
+        for xm, ym in zip(x.chunk(2), y.chunk(2)):
+            F.cross_entropy(model(xm), ym).backward()
+    eng.synchronize()
+    eng.check_status()
+    got = [p.detach().clone() for p in model.parameters()]
+    eng.close()
+    key = "_gradient_modes_reference"
+    ref = globals().get(key)
+    if ref is None:
+        globals()[key] = got
+    else:
+        for p, q in zip(got, ref):
+            torch.testing.assert_close(p, q, rtol=1e-5, atol=1e-6)
+
+
 def test_channels_last_parameters_are_supported():
     model = small_net().to(memory_format=torch.channels_last)
     ref = copy.deepcopy(model)
