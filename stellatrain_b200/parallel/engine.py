@@ -50,7 +50,7 @@ class EngineConfig:
 
 class _BucketRuntime:
     __slots__ = ("bucket", "params", "pending", "full", "grad_ready", "apply_done", "has_pending_apply",
-                 "select_count", "apply_count", "first_module", "held", "seg_of")
+                 "select_count", "apply_count", "first_module", "held", "seg_of", "tab_slot", "tab_events")
 
     def __init__(self, bucket: GpuBucket, params: list[nn.Parameter], ga: int):
         self.bucket = bucket
@@ -65,6 +65,8 @@ class _BucketRuntime:
         self.first_module = None
         self.held: list = []          # gradient tensors the current select reads ("steal" mode)
         self.seg_of = {id(p): i for i, p in enumerate(params)}
+        self.tab_slot = 0             # row of the pinned pointer-table ring the hooks write now
+        self.tab_events: list = [None] * GpuBucket.GRAD_TAB_RING
 
 
 class SparseDPEngine:
@@ -244,7 +246,7 @@ class SparseDPEngine:
             flat = rt.bucket.grad[seg.off : seg.off + seg.numel].as_strided(p.shape, p.stride())
             flat.copy_(g)
             g = flat
-        rt.bucket.grad_tab_host[si] = g.data_ptr()
+        rt.bucket.grad_tab_host[rt.tab_slot, si] = g.data_ptr()
         rt.held.append(g)
 
     def _make_gate(self, bis: list[int]) -> Callable:
@@ -282,7 +284,15 @@ class SparseDPEngine:
         s = self.sparse_stream
         if self.cfg.grad_mode != "flat":
             b = rt.bucket
-            b.grad_tab_dev.copy_(b.grad_tab_host, non_blocking=True)    # on the compute stream, before the event
+            b.grad_tab_dev.copy_(b.grad_tab_host[rt.tab_slot], non_blocking=True)   # compute stream, before the event
+            if not self._capturing:
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                rt.tab_events[rt.tab_slot] = ev
+                rt.tab_slot = (rt.tab_slot + 1) % len(rt.tab_events)
+                nxt = rt.tab_events[rt.tab_slot]
+                if nxt is not None:
+                    nxt.synchronize()       # the copy that last used the next row must be done before it is rewritten
             held, rt.held = rt.held, []
             if not self._capturing:
                 for g in held:

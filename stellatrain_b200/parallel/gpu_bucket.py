@@ -63,6 +63,8 @@ class Wiring:
 
 
 class GpuBucket:
+    GRAD_TAB_RING = 4
+
     def __init__(
         self,
         index: int,
@@ -172,11 +174,13 @@ class GpuBucket:
     def use_grad_table(self) -> None:
         """Switch the select to per-tensor gradient pointers (no flat gradient copy, no zeroing)."""
         n_segs = len(self.layout.segments)
-        self.grad_tab_host = torch.zeros(n_segs, dtype=torch.int64).pin_memory()
+        # a small ring of pinned tables: the copy of iteration i may still be in flight when the
+        # hooks of iteration i+1 write their pointers
+        self.grad_tab_host = torch.zeros(self.GRAD_TAB_RING, n_segs, dtype=torch.int64).pin_memory()
         self.grad_tab_dev = torch.zeros(n_segs, dtype=torch.int64, device=self.device)
         for i, seg in enumerate(self.layout.segments):       # default: the flat buffer
-            self.grad_tab_host[i] = self.grad.data_ptr() + 4 * seg.off
-        self.grad_tab_dev.copy_(self.grad_tab_host)
+            self.grad_tab_host[:, i] = self.grad.data_ptr() + 4 * seg.off
+        self.grad_tab_dev.copy_(self.grad_tab_host[0])
         self.zero_grad_in_select = False
         self._bind()
 
