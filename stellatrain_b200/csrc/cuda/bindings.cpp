@@ -123,6 +123,42 @@ struct BucketHandle {
     sel.skip_ef = skip_ef ? 1u : 0u;
   }
 
+  // grouped mode -------------------------------------------------------------------------------
+  st::GroupArgs grp;
+  bool has_group = false;
+  // mates: addresses of the group-mates' flat gradient buffers; flag areas are [group size] u64 words
+  // indexed by the local rank of the writer.
+  void set_group(uint64_t grad_local, const std::vector<uint64_t>& mate_grad, const std::vector<int>& mate_local,
+                 int my_local, uint64_t ready_local, const std::vector<uint64_t>& mate_ready, uint64_t done_local,
+                 const std::vector<uint64_t>& mate_done, uint64_t group_done_ctr) {
+    if (mate_grad.size() > (size_t)st::kMaxWorld || mate_grad.size() != mate_local.size() ||
+        mate_grad.size() != mate_ready.size() || mate_grad.size() != mate_done.size())
+      throw std::runtime_error("inconsistent group description");
+    std::memset(&grp, 0, sizeof(grp));
+    grp.grad_local = as_ptr<float>(grad_local);
+    grp.n_mates = (int)mate_grad.size();
+    for (int m = 0; m < grp.n_mates; ++m) {
+      grp.grad_peer[m] = as_ptr<const float>(mate_grad[m]);
+      grp.mate_slot[m] = mate_local[m];
+      grp.ready_peer[m] = as_ptr<uint64_t>(mate_ready[m]) + my_local;
+      grp.done_peer[m] = as_ptr<uint64_t>(mate_done[m]) + my_local;
+    }
+    grp.ready_local = as_ptr<const uint64_t>(ready_local);
+    grp.done_local = as_ptr<const uint64_t>(done_local);
+    grp.done_ctr = as_ptr<uint32_t>(group_done_ctr);
+    has_group = grp.n_mates > 0;
+  }
+  void group_reduce(uint64_t stream) {
+    if (!has_group) return;
+    grp.segs = sel.segs;
+    grp.chunks = sel.chunks;
+    grp.n_chunks = sel.n_chunks;
+    grp.epoch = sel.epoch;
+    grp.status = sel.status;
+    grp.timeout_ns = sel.timeout_ns;
+    check(st::launch_group_reduce(grp, as_ptr<CUstream_st>(stream)), "launch_group_reduce");
+  }
+
   void select(uint64_t stream) {
     check(st::launch_select(sel, randomk_seed, as_ptr<CUstream_st>(stream)), "launch_select");
   }
@@ -179,6 +215,10 @@ PYBIND11_MODULE(_C, m) {
            py::arg("skip_ef") = false)
       .def_readwrite("randomk_seed", &BucketHandle::randomk_seed)
       .def_readwrite("max_ctas_per_source", &BucketHandle::max_ctas_per_source)
+      .def("set_group", &BucketHandle::set_group, py::arg("grad_local"), py::arg("mate_grad"), py::arg("mate_local"),
+           py::arg("my_local"), py::arg("ready_local"), py::arg("mate_ready"), py::arg("done_local"), py::arg("mate_done"),
+           py::arg("group_done_ctr"))
+      .def("group_reduce", &BucketHandle::group_reduce, py::arg("stream"))
       .def("select", &BucketHandle::select, py::arg("stream"))
       .def("apply", &BucketHandle::apply, py::arg("stream"));
 
@@ -189,6 +229,13 @@ PYBIND11_MODULE(_C, m) {
   m.def("peer_copy", [](uint64_t dst, uint64_t src, uint64_t n, uint64_t stream) {
     check(st::launch_peer_copy(as_ptr<float>(dst), as_ptr<const float>(src), n, as_ptr<CUstream_st>(stream)),
           "peer_copy");
+  });
+  m.def("delay", [](uint64_t ns_ptr, uint64_t cap_ns, uint64_t stream) {
+    check(st::launch_delay(as_ptr<const uint64_t>(ns_ptr), cap_ns, as_ptr<CUstream_st>(stream)), "delay");
+  });
+  m.def("link_probe", [](uint64_t dst, uint64_t src, uint64_t n, uint64_t out3, uint64_t ctr, uint64_t stream) {
+    check(st::launch_link_probe(as_ptr<float>(dst), as_ptr<const float>(src), n, as_ptr<uint64_t>(out3), as_ptr<uint32_t>(ctr),
+                                as_ptr<CUstream_st>(stream)), "link_probe");
   });
   m.def("ipc_get_handle", &ipc_get_handle);
   m.def("ipc_open_handle", &ipc_open_handle);

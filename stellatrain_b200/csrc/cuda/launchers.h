@@ -18,4 +18,15 @@ cudaError_t launch_max_abs_diff(const float* a, const float* b, uint64_t n, uint
 // dst[0..n) = src[0..n); either side may be peer memory. n % 4 == 0, both 16-byte aligned.
 cudaError_t launch_peer_copy(float* dst, const float* src, uint64_t n, cudaStream_t stream);
 
+// Grouped mode: signal, reduce the owned tensors over the group-mates' buffers, wait until the mates
+// have finished reading this rank's gradients.  Three kernels on `stream`.
+cudaError_t launch_group_reduce(const GroupArgs& args, cudaStream_t stream);
+
+// Holds `stream` for *ns_ptr nanoseconds (at most cap_ns).
+cudaError_t launch_delay(const uint64_t* ns_ptr, uint64_t cap_ns, cudaStream_t stream);
+
+// Device-clock time of a copy of n floats; out3 = {elapsed, min start, max end}; the caller sets
+// out3[1] = UINT64_MAX, out3[2] = 0 and *ctr = 0 beforehand.
+cudaError_t launch_link_probe(float* dst, const float* src, uint64_t n, uint64_t* out3, uint32_t* ctr, cudaStream_t stream);
+
 }  // namespace st

@@ -109,6 +109,16 @@ __global__ void __launch_bounds__(kThreads) k_pass1(SelectArgs A) {
   const HistWindow win = window_of(ss);
 
   if (blockIdx.x == 0 && threadIdx.x == 0) *A.cand_cursor = 0;
+  if (sd.reserved & kSegSkip) {
+    // a tensor another rank of the group is responsible for: only clear the consumed gradient
+    if (A.zero_grad && A.grad_tab == nullptr) {
+      float* gz = A.grad + ch.start;
+      for (uint32_t i = threadIdx.x * 4; i < ch.len; i += kPerIter)
+        *reinterpret_cast<float4*>(gz + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (threadIdx.x == 0) A.chunk_cnt[blockIdx.x] = 0;
+    return;
+  }
   if (need_hist) {
     for (int b = threadIdx.x; b < kHistBins; b += kThreads) s_hist[b] = 0;
   }
@@ -217,6 +227,12 @@ __global__ void __launch_bounds__(kThreads) k_plan(SelectArgs A) {
     }
   }
 
+  uint32_t* gh_skip = A.hist + (size_t)seg * kHistBins;
+  if (sd.reserved & kSegSkip) {
+    if (threadIdx.x == 0) { w->mode = kModeNone; w->k_rem = 0; w->cand_cnt = 0; w->out_cursor = 0; w->found = 0; }
+    for (int b = threadIdx.x; b < kHistBins; b += kThreads) gh_skip[b] = 0;
+    return;
+  }
   uint32_t mode = kModeTop;
   uint32_t found = 0;
   if (A.compressor != kTopk && ss.inited) {

@@ -37,8 +37,10 @@ struct SegDesc {          // static per segment (re-uploaded when the compressio
   uint32_t out_off;       // position of the segment's first entry in the bucket's stream
   uint32_t chunk_begin;   // first chunk of the segment in the chunk table
   uint32_t chunk_cnt;     // number of chunks
-  uint32_t reserved;
+  uint32_t reserved;      // flags: kSegSkip
 };
+
+constexpr uint32_t kSegSkip = 1u;   // this rank does not own the tensor (grouped mode): emit nothing, keep no residual
 
 struct SegState {         // persistent per segment, saved in checkpoints
   float tau;              // threshold (element magnitude or 16-block L1 norm)
@@ -142,6 +144,25 @@ struct ApplyArgs {
   OptState* opt;
   uint32_t* epoch;             // apply epoch of this bucket (starts at 1)
   const uint32_t* sel_epoch;   // select epoch: an apply with epoch >= *sel_epoch has nothing to consume
+  uint32_t* done_ctr;
+  uint32_t* status;
+  uint64_t timeout_ns;
+};
+
+// Intra-group dense reduction (grouped topologies).
+struct GroupArgs {
+  float* grad_local;                     // this rank's flat gradients of the bucket (symmetric memory)
+  const float* grad_peer[kMaxWorld];     // group-mates' flat gradients, same layout
+  int32_t n_mates;
+  int32_t mate_slot[kMaxWorld];          // index of mate m in the [group size] flag arrays
+  const SegDesc* segs;
+  const Chunk* chunks;
+  uint32_t n_chunks;
+  uint64_t* ready_peer[kMaxWorld];       // mate m's ready word for this rank
+  const uint64_t* ready_local;           // [group size] ready words written by the mates
+  uint64_t* done_peer[kMaxWorld];
+  const uint64_t* done_local;
+  const uint32_t* epoch;                 // the bucket's select epoch
   uint32_t* done_ctr;
   uint32_t* status;
   uint64_t timeout_ns;

@@ -59,6 +59,7 @@ class Segment:
     out_off: int = 0
     chunk_begin: int = 0
     chunk_cnt: int = 0
+    skip: bool = False     # grouped mode: another rank of the group owns this tensor
 
 
 @dataclass
@@ -97,13 +98,26 @@ class BucketLayout:
             pos += s.k
         self.cap = pos
 
+    def assign_owners(self, group_size: int, my_local: int) -> list[int]:
+        """Grouped mode: spread the tensors of the bucket over the ranks of a group (largest first onto the
+        least loaded rank, ties towards the lower rank) and mark the ones this rank does not own."""
+        load = [0] * group_size
+        owner = [0] * len(self.segments)
+        for i in sorted(range(len(self.segments)), key=lambda j: (-self.segments[j].numel, j)):
+            r = min(range(group_size), key=lambda q: (load[q], q))
+            owner[i] = r
+            load[r] += self.segments[i].numel
+        for i, s in enumerate(self.segments):
+            s.skip = owner[i] != my_local
+        return owner
+
     def max_cap(self, min_ratio: float, world: int) -> int:
         return sum(entries_for(s.numel, min_ratio, world) for s in self.segments)
 
     def seg_table(self) -> np.ndarray:
         t = np.zeros(len(self.segments), dtype=SEG_DESC_DTYPE)
         for i, s in enumerate(self.segments):
-            t[i] = (s.off, s.numel, s.n_pad, s.k, s.out_off, s.chunk_begin, s.chunk_cnt, 0)
+            t[i] = (s.off, s.numel, s.n_pad, s.k, s.out_off, s.chunk_begin, s.chunk_cnt, 1 if s.skip else 0)
         return t
 
     def chunk_table(self) -> np.ndarray:

@@ -44,6 +44,9 @@ class EngineConfig:
     smart_momentum: bool = False
     grad_mode: str = "steal"              # "steal": kernels read autograd's own gradient tensors through a
                                           # pointer table; "flat": param.grad are views of a flat buffer
+    group_size: int = 1                   # > 1: ranks form groups of this size; gradients are summed densely inside a
+                                          # group (each rank reducing the tensors it owns) and exchanged sparsely
+                                          # between all ranks, with k = kept budget / number of groups per tensor
     fine_grained_gating: bool = False     # wait per first-using module instead of at the root
     status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
 
@@ -93,6 +96,16 @@ class SparseDPEngine:
         if transport == "auto":
             transport = "local" if self.world == 1 else "peer"
         self.transport = transport
+        L = max(1, int(cfg.group_size))
+        if self.world % L:
+            raise ValueError("world size must be a multiple of group_size")
+        self.group_size, self.groups = L, self.world // L
+        self.my_group, self.my_local = self.rank // L, self.rank % L
+        if L > 1:
+            if transport != "peer":
+                raise ValueError("grouped mode needs the peer transport")
+            cfg.grad_mode = "flat"          # group-mates read each other's gradients: they must sit in the pool
+        self.shaper = None
         low, high = torch.cuda.Stream.priority_range()
         self.sparse_stream = torch.cuda.Stream(device=self.device, priority=high)
         self.iteration = 0            # completed optimiser iterations (selects issued per bucket)
@@ -133,7 +146,12 @@ class SparseDPEngine:
                 rank=self.rank, optimizer=cfg.optimizer, amsgrad=cfg.amsgrad,
                 smart_momentum=cfg.smart_momentum, min_ratio=cfg.min_ratio, scratch=self.scratch,
                 timeout_s=cfg.timeout_s, divide_k_by_world=cfg.divide_k_by_world,
+                k_world=(self.groups if (self.group_size > 1 and cfg.divide_k_by_world) else None),
             )
+            if self.group_size > 1:
+                layout.assign_owners(self.group_size, self.my_local)
+                bucket.upload_segments()
+                bucket.set_weights([1.0 / self.groups] * self.world)   # disjoint tensors inside a group, mean over groups
             with torch.no_grad():
                 for seg, p in zip(layout.segments, plist):
                     dense = _dense_like(p)
@@ -161,6 +179,8 @@ class SparseDPEngine:
         W = self.world
         max_n = max(rt.bucket.layout.n_total for rt in self.buckets)
         need = sum(rt.bucket.recv_bytes() + 4 * W * 8 + 1024 for rt in self.buckets) + max_n * 4 + 65536
+        if self.group_size > 1:
+            need += sum(rt.bucket.layout.n_total * 4 + 4 * self.group_size * 8 + 1024 for rt in self.buckets)
         if self.transport == "nccl":
             # library baseline: streams are staged locally and moved by ncclAllGather
             self.pool = symm._alloc_local(need, self.device, 1, 0)
@@ -192,9 +212,43 @@ class SparseDPEngine:
                 peer_ack=[pool.peer_addr(r, a_off) for r in range(W)],
                 recv_mc=pool.mc_addr(r_off), use_flags=True, use_acks=True,
             ))
+            if self.group_size > 1:
+                self._wire_group(rt, r_off)
         if self.dist_on:
             torch.cuda.synchronize(self.device)
             dist.barrier(self.group)
+
+    def _wire_group(self, rt: "_BucketRuntime", recv_off: int) -> None:
+        """Grouped mode: gradients into the pool, ready/done flags, receive areas pre-filled with the
+        'no entry' marker because a source never writes the stream regions of tensors it does not own."""
+        b, pool, L = rt.bucket, self.pool, self.group_size
+        pool.local_view(recv_off, b.recv_bytes()).fill_(0xFF)
+        n = b.layout.n_total
+        g_off = pool.take(n * 4)
+        rdy_off = pool.take(L * 8)
+        done_off = pool.take(L * 8)
+        b.rebind_grad(pool.local_view(g_off, n * 4).view(torch.float32))
+        with torch.no_grad():
+            for seg, p in zip(b.layout.segments, rt.params):
+                p.grad = b.grad[seg.off : seg.off + seg.numel].as_strided(p.shape, p.stride())
+        base = self.my_group * L
+        mates = [l for l in range(L) if l != self.my_local]
+        b._group_ctr = torch.zeros(1, dtype=torch.int32, device=self.device)
+        b.handle.set_group(
+            grad_local=b.grad.data_ptr(), mate_grad=[pool.peer_addr(base + l, g_off) for l in mates], mate_local=mates,
+            my_local=self.my_local, ready_local=pool.peer_addr(self.rank, rdy_off),
+            mate_ready=[pool.peer_addr(base + l, rdy_off) for l in mates], done_local=pool.peer_addr(self.rank, done_off),
+            mate_done=[pool.peer_addr(base + l, done_off) for l in mates], group_done_ctr=b._group_ctr.data_ptr(),
+        )
+
+    def set_link_shaper(self, token_bucket) -> None:
+        """Emulate a constrained cross-group link: before a bucket's streams are pushed, the sparse
+        stream is held for the time the cross-group bytes would need on the shaped link
+        (``control.shaper.TokenBucket``).  Eager mode only."""
+        self.shaper = token_bucket
+        self._delay_host = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self._delay_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.shaped_bytes = 0
 
     def _install_hooks(self) -> None:
         self._hooks = []
@@ -323,6 +377,20 @@ class SparseDPEngine:
             with torch.cuda.stream(s):
                 dist.all_gather_into_tensor(recv, send, group=self.group)
         else:
+            if self.group_size > 1:
+                b.handle.group_reduce(s.cuda_stream)
+                self.stats["kernels"] += 3
+            if self.shaper is not None and not self._capturing:
+                owned = sum(seg.k for seg in b.layout.segments if not seg.skip)
+                nbytes = owned * 8 * (self.world - self.group_size)        # entries stored into other groups
+                self.shaped_bytes += nbytes
+                wait_s = self.shaper.delay_for(nbytes)
+                if wait_s > 0:
+                    from .. import _build
+                    self._delay_host[0] = int(wait_s * 1e9)
+                    with torch.cuda.stream(s):
+                        self._delay_dev.copy_(self._delay_host, non_blocking=False)
+                    _build.load_extension("_C").delay(self._delay_dev.data_ptr(), 2_000_000_000, s.cuda_stream)
             b.select(s)
         rt.select_count += 1
         self.stats["select_launches"] += 1

@@ -81,12 +81,13 @@ class GpuBucket:
         scratch: Optional["CandidateScratch"] = None,
         timeout_s: float = 2.0,
         divide_k_by_world: bool = True,
+        k_world: Optional[int] = None,
     ) -> None:
         self.index = index
         self.layout = layout
         self.device = device
         self.world, self.rank = world, rank
-        self.k_world = world if divide_k_by_world else 1
+        self.k_world = k_world if k_world is not None else (world if divide_k_by_world else 1)
         self.compressor = compressor
         self.ratio = ratio
         self.min_ratio = ratio if min_ratio is None else min(min_ratio, ratio)
@@ -170,6 +171,16 @@ class GpuBucket:
         h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False)
         if wiring is not None:
             self._apply_wiring(h, wiring)
+
+    def rebind_grad(self, storage: torch.Tensor) -> None:
+        """Move the flat gradient buffer into caller-provided (peer-visible) memory."""
+        assert storage.numel() == self.layout.n_total and storage.dtype == torch.float32
+        storage.zero_()
+        self.grad = storage
+        self._bind()
+
+    def upload_segments(self) -> None:
+        self.segs.copy_(_dev_bytes(self.layout.seg_table(), self.device))
 
     def use_grad_table(self) -> None:
         """Switch the select to per-tensor gradient pointers (no flat gradient copy, no zeroing)."""

@@ -152,6 +152,87 @@ def test_sparse_replicas_stay_in_sync(compressor, staleness):
         assert o["first"] == pytest.approx(outs[0]["first"], rel=0.5)
 
 
+def _worker_grouped(rank, world, group_size, sparse):
+    import torch.nn.functional as F
+
+    from stellatrain_b200.control.shaper import BandwidthSchedule, TokenBucket
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+
+    model = _net()
+    lr = 0.05
+    cfg = EngineConfig(compressor="topk", ratio=0.9 if sparse else 0.0, optimizer="sgd", staleness=0 if not sparse else 1,
+                       divide_k_by_world=sparse, bucket_mb=0.02, chunk_elems=1024, group_size=group_size,
+                       optimizer_options={"lr": lr})
+    eng = SparseDPEngine(model, cfg)
+    if sparse:
+        eng.set_link_shaper(TokenBucket(BandwidthSchedule(seed=3, lo_gbps=0.05, hi_gbps=0.2), burst_bytes=1 << 12))
+    steps = 4
+    for x, y in _data(rank, steps):
+        F.cross_entropy(model(x), y).backward()
+    eng.synchronize()
+    eng.check_status()
+    drift = eng.replica_drift()
+    out = {"drift": drift, "owned": [sum(not s.skip for s in rt.bucket.layout.segments) for rt in eng.buckets],
+           "shaped": getattr(eng, "shaped_bytes", 0)}
+    if not sparse:
+        # sum inside a group, mean over groups  ==  group_size * (mean over all ranks)
+        ref = _net()
+        opt = torch.optim.SGD(ref.parameters(), lr=lr * group_size)
+        everyone = [_data(r, steps) for r in range(world)]
+        for s in range(steps):
+            opt.zero_grad()
+            x = torch.cat([everyone[r][s][0] for r in range(world)])
+            y = torch.cat([everyone[r][s][1] for r in range(world)])
+            F.cross_entropy(ref(x), y).backward()
+            opt.step()
+        out["err"] = max(float((p.detach() - q.detach()).abs().max()) for p, q in zip(model.parameters(), ref.parameters()))
+    eng.close()
+    return out
+
+
+@pytest.mark.parametrize("sparse", [False, True])
+def test_grouped_mode(sparse):
+    """Two groups of two ranks: dense reduction inside a group by tensor owners, sparse exchange between all."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    outs = _spawn(_worker_grouped, 4, 2, sparse)
+    for o in outs:
+        assert o["drift"] <= 1e-6, outs
+        if not sparse:
+            assert o["err"] < 1e-4, outs
+        else:
+            assert o["shaped"] > 0
+    # ownership is a partition inside each group
+    assert [a + b for a, b in zip(outs[0]["owned"], outs[1]["owned"])] == [a + b for a, b in zip(outs[2]["owned"], outs[3]["owned"])]
+
+
+def _worker_link_probe(rank, world):
+    from stellatrain_b200 import _build
+    from stellatrain_b200.parallel import symm
+
+    C = _build.load_extension("_C")
+    dev = torch.device("cuda", rank)
+    n = 1 << 24
+    pool = symm.allocate(n * 4 + 4096, dev, None)
+    dst = torch.empty(n, device=dev)
+    out = torch.tensor([0, 2**63 - 1, 0], dtype=torch.int64, device=dev)
+    ctr = torch.zeros(1, dtype=torch.int32, device=dev)
+    peer = (rank + 1) % world
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        out.copy_(torch.tensor([0, 2**63 - 1, 0], dtype=torch.int64))
+        C.link_probe(dst.data_ptr(), pool.peer_addr(peer, 0), n, out.data_ptr(), ctr.data_ptr(), s)
+        torch.cuda.synchronize()
+    ns = int(out[0])
+    return {"gbps": n * 4 * 8 / ns, "backend": pool.backend}
+
+
+def test_link_probe_measures_nvlink():
+    outs = _spawn(_worker_link_probe, 2)
+    for o in outs:
+        assert 100.0 < o["gbps"] < 20000.0, outs      # a peer copy over NVLink: hundreds of GB/s
+
+
 def _worker_missing_peer(rank, world):
     """Rank 1 leaves between steps (host-side decision); rank 0's next step must end with a timeout
     status instead of a hang.  Plain peer stores only (NVLS disabled by the environment)."""
