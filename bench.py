@@ -55,6 +55,10 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--amp", default="none", choices=["none", "bf16"])
     ap.add_argument("--no-multicast", action="store_true")
     ap.add_argument("--grad-mode", default="steal", choices=["steal", "flat"])
+    ap.add_argument("--momentum", type=float, default=0.0)
+    ap.add_argument("--group-size", type=int, default=1, help="ranks per group (grouped two-level mode)")
+    ap.add_argument("--shape-gbps", default=None, help="lo:hi[:seed] emulated cross-group link, e.g. 10:40:0")
+    ap.add_argument("--controller", type=int, default=0, help="run the telemetry controller and apply its instructions")
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
 
@@ -163,12 +167,24 @@ def main() -> None:
         st.configure_compression_ratio(args.ratio)
         st.set_optimizer(args.optimizer)
         st.configure_optimizer("lr", args.lr)
+        if args.optimizer == "sgd" and args.momentum:
+            st.configure_optimizer("momentum", args.momentum)
+        st.state().engine_cfg.group_size = args.group_size
+        if args.controller:
+            st.state().engine_cfg.min_ratio = min(args.ratio, 0.9)      # room for the controller to lower the ratio
         st.state().engine_cfg.bucket_mb = args.bucket_mb
         st.state().engine_cfg.multicast = not args.no_multicast
         st.state().engine_cfg.grad_mode = args.grad_mode
         net = st.FasterDpModelWrapper(model, sequential=False)
         net._ensure_engine()
         engine = net.engine
+        if args.shape_gbps:
+            from stellatrain_b200.control.shaper import BandwidthSchedule, TokenBucket
+
+            parts = args.shape_gbps.split(":")
+            sched = BandwidthSchedule(seed=int(parts[2]) if len(parts) > 2 else 0, lo_gbps=float(parts[0]), hi_gbps=float(parts[1]))
+            engine.set_link_shaper(TokenBucket(sched, burst_bytes=1 << 20))
+            args.graph = 0            # the shaper and the controller act between eager launches
     else:
         if world > 1:
             dist.init_process_group("nccl", init_method=f"tcp://{master_addr}:{master_port}", world_size=world,
@@ -193,16 +209,40 @@ def main() -> None:
     loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
     amp = torch.autocast("cuda", dtype=torch.bfloat16) if args.amp == "bf16" else None
 
-    def fwd_bwd(x, y):
+    def fwd_bwd(x, y, marker=None):
         if amp is not None:
             with amp:
                 loss = net(x, y)[1] if lm else F.cross_entropy(net(x), y)
         else:
             loss = net(x, y)[1] if lm else F.cross_entropy(net(x), y)
+        if marker is not None:
+            marker.backward_begins()
         loss.backward()
         return loss
 
+    hook = None
+    controller = None
+    if args.controller and engine is not None:
+        from stellatrain_b200.control.controller import Controller
+        from stellatrain_b200.parallel.telemetry import TelemetryHook
+
+        args.graph = 0
+        ctl_port = master_port + 17
+        if rank == 0:
+            controller = Controller(port=ctl_port, host="127.0.0.1", adapt=True).start()
+            from stellatrain_b200 import cpu_tier
+            srv = cpu_tier._load().TelemetryServer(f"127.0.0.1:{ctl_port}", False, 5000)
+            srv.send_global_telemetry(max(1, world // max(1, args.group_size)), world,
+                                      [p.numel() for p in model.parameters()], False, False)
+        if world > 1:
+            dist.barrier()
+        hook = TelemetryHook(engine, f"127.0.0.1:{ctl_port}", args.batch, apply_batch=False)
+
     def train_step(x, y):
+        if hook is not None:
+            with hook.step() as marker:
+                loss = fwd_bwd(x, y, marker)
+            return loss
         loss = fwd_bwd(x, y)
         if opt is not None:
             opt.step()
@@ -306,7 +346,11 @@ def main() -> None:
                 "per_gpu_batch": args.batch, "seq_len": args.seq_len if lm else None, "parallelism": f"dp{world}",
                 "compressor": args.compressor, "kept_fraction": 1 - args.ratio, "optimizer": args.optimizer,
                 "lr": args.lr, "staleness": args.staleness, "bucket_mb": args.bucket_mb,
-                "transport": engine.transport if engine is not None else args.impl,
+                "transport": engine.transport if engine is not None else args.impl, "group_size": args.group_size,
+                "shaped_link_gbps": args.shape_gbps,
+                "controller": ({"instructions_applied": len(hook.applied), "final_ratio": engine.cfg.ratio,
+                                "shaped_gbps_achieved": (engine.shaper.achieved_gbps() if engine.shaper else None)}
+                               if hook is not None else None),
                 "multicast": bool(engine is not None and engine.pool is not None and engine.pool.mc_ptr),
                 "cuda_graph": bool(args.graph), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
                 "l2": "per-step working set (233 MB of parameters plus activations) exceeds the 126 MB L2; no flush needed",

@@ -39,6 +39,9 @@ class TelemetryHook:
         self._ev = {k: torch.cuda.Event(enable_timing=True) for k in ("f0", "f1", "b1", "prev_b1")}
         self._have_prev = False
         self.last: Dict[str, float] = {}
+        self._agree_event = None
+        self._agree_dev = torch.zeros(1, dtype=torch.float64, device=engine.device)
+        self._agree_host = torch.zeros(1, dtype=torch.float64).pin_memory()
         if uri:
             from .. import cpu_tier
 
@@ -52,10 +55,36 @@ class TelemetryHook:
         with self.lock:
             self.pending.append((int(since), int(ubatch), float(ratio)))
 
-    def _apply_due(self) -> None:
+    _INF = float(2 ** 40)
+
+    def _agreed_since(self) -> float:
+        """Ranks receive an instruction at slightly different times, but must switch at the same
+        iteration.  Every step each rank contributes the effective iteration of its earliest pending
+        instruction (or "none yet"); the maximum over ranks, read one step later, is an iteration by
+        which every rank holds the instruction."""
+        eng = self.engine
+        if eng.world == 1:
+            with self.lock:
+                return min((p[0] for p in self.pending), default=self._INF)
+        agreed = self._INF
+        if self._agree_event is not None:
+            self._agree_event.synchronize()
+            agreed = float(self._agree_host[0])
         with self.lock:
-            due = [p for p in self.pending if p[0] <= self.iteration]
-            self.pending = [p for p in self.pending if p[0] > self.iteration]
+            mine = min((p[0] for p in self.pending), default=self._INF)
+        self._agree_dev.fill_(mine)
+        dist.all_reduce(self._agree_dev, op=dist.ReduceOp.MAX, group=eng.group)
+        self._agree_host.copy_(self._agree_dev, non_blocking=True)
+        self._agree_event = torch.cuda.Event()
+        self._agree_event.record()
+        return agreed
+
+    def _apply_due(self) -> None:
+        agreed = self._agreed_since()
+        limit = min(agreed, float(self.iteration)) if agreed < self._INF else -1.0
+        with self.lock:
+            due = [p for p in self.pending if p[0] <= limit and agreed <= self.iteration]
+            self.pending = [p for p in self.pending if p not in due]
         for since, ubatch, ratio in due:
             if self.apply_batch and ubatch > 0:
                 self.batch_size = ubatch
