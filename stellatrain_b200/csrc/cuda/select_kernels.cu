@@ -366,6 +366,12 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
   bool emitted = false;
   uint32_t running = 0;
   uint32_t fill_sel = 0, fill_cnd = 0;   // uniform over the CTA
+  // key range of the threshold bin: [key_lo, key_hi); keys are below 2^31, so 2^31 stands for "none above"
+  const uint64_t lo64 = thr_bin == 0u ? 0ull : (uint64_t)win.base + ((uint64_t)thr_bin << win.shift);
+  const uint64_t hi64 = thr_bin == (uint32_t)(kHistBins - 1) ? 0x80000000ull
+                                                              : (uint64_t)win.base + ((uint64_t)(thr_bin + 1u) << win.shift);
+  const uint32_t key_lo = (uint32_t)(lo64 < 0x80000000ull ? lo64 : 0x80000000ull);
+  const uint32_t key_hi = (uint32_t)(hi64 < 0x80000000ull ? hi64 : 0x80000000ull);
 
   auto emit_block = [&](uint32_t pos, uint32_t gi0) {   // one 16-element block at block position pos
 #pragma unroll 4
@@ -427,15 +433,22 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
 
     uint32_t sel_mask = 0, cnd_mask = 0, bkey = 0;
     if (!B16) {
+      // "bin > thr_bin" and "bin == thr_bin" as two key comparisons (bin_of is monotone), and a
+      // whole-thread early out: almost every thread holds nothing at or above the threshold bin
+      const uint32_t cut = (mode == kModeTop) ? key_lo : tau_bits;
+      uint32_t kmax = 0;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const uint32_t key = key_bits(v[j]);
-        if (mode == kModeTop) {
-          const uint32_t bin = bin_of(key, win);
-          sel_mask |= (uint32_t)(act && bin > thr_bin) << j;
-          cnd_mask |= (uint32_t)(act && bin == thr_bin) << j;
-        } else {
-          sel_mask |= (uint32_t)(act && key >= tau_bits) << j;
+      for (int j = 0; j < 16; ++j) kmax = max(kmax, key_bits(v[j]));
+      if (act && kmax >= cut) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t key = key_bits(v[j]);
+          if (mode == kModeTop) {
+            sel_mask |= (uint32_t)(key >= key_hi) << j;
+            cnd_mask |= (uint32_t)(key >= key_lo && key < key_hi) << j;
+          } else {
+            sel_mask |= (uint32_t)(key >= tau_bits) << j;
+          }
         }
       }
     } else {
