@@ -33,8 +33,10 @@ constexpr int kPerIter = kThreads * 4;  // elements one CTA covers per loop iter
 
 __device__ __forceinline__ uint32_t key_bits(float a) { return __float_as_uint(a) & 0x7fffffffu; }
 
+// Gradients are read once: streaming loads and stores (evict-first) keep them from pushing the
+// residual, which pass 2 reads again, out of L2.
 __device__ __forceinline__ float4 load4_guarded(const float* p, uint32_t i, uint32_t valid) {
-  if (i + 4 <= valid) return *reinterpret_cast<const float4*>(p + i);
+  if (i + 4 <= valid) return __ldcs(reinterpret_cast<const float4*>(p + i));
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   if (i + 0 < valid) v.x = p[i + 0];
   if (i + 1 < valid) v.y = p[i + 1];
@@ -44,7 +46,7 @@ __device__ __forceinline__ float4 load4_guarded(const float* p, uint32_t i, uint
 
 __device__ __forceinline__ void store4_guarded(float* p, uint32_t i, uint32_t valid, float4 v) {
   if (i + 4 <= valid) {
-    *reinterpret_cast<float4*>(p + i) = v;
+    __stcs(reinterpret_cast<float4*>(p + i), v);
     return;
   }
   if (i + 0 < valid) p[i + 0] = v.x;
@@ -347,6 +349,9 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
   __shared__ uint32_t s_selb[B16 ? kQueueCap : 1];  // block mode: block ids
   __shared__ uint2 s_cnd[kQueueCap];                // (item id, key)
   __shared__ uint32_t s_base[2];
+  extern __shared__ __align__(128) float s_dyn[];            // two stages of the TMA pipeline
+  float (*s_tile)[kP2PerIter] = reinterpret_cast<float (*)[kP2PerIter]>(s_dyn);
+  __shared__ __align__(8) uint64_t s_bar[2];
   if (ld_volatile_u32(A.status) != kOk) return;
 
   const Chunk ch = A.chunks[blockIdx.x];
@@ -415,14 +420,38 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
     __syncthreads();
   };
 
-  for (uint32_t it = 0; it < ch.len; it += kP2PerIter) {
+  // Tiles of 4096 elements travel global -> shared by TMA bulk copies, two in flight.
+  const uint32_t n_tiles = (ch.len + kP2PerIter - 1) / kP2PerIter;
+  auto issue_tile = [&](uint32_t t) {     // thread 0 only
+    const uint32_t elems = min(kP2PerIter, ch.len - t * kP2PerIter);
+    mbar_expect_tx(&s_bar[t & 1u], elems * 4u);
+    bulk_load(&s_tile[t & 1u][0], r + (size_t)t * kP2PerIter, elems * 4u, &s_bar[t & 1u]);
+  };
+  if (threadIdx.x == 0) {
+    mbar_init(&s_bar[0], 1);
+    mbar_init(&s_bar[1], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    issue_tile(0);
+    if (n_tiles > 1) issue_tile(1);
+  }
+
+  for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+    const uint32_t it = tile * kP2PerIter;
     const uint32_t i = it + threadIdx.x * kP2PerThread;
     const bool act = i < ch.len;   // chunk lengths are multiples of 16: a thread is all in or all out
+    if (!mbar_wait_bounded(&s_bar[tile & 1u], (tile >> 1) & 1u)) {
+      set_status(A.status, kTimeoutFlag);   // cannot happen for a valid source; never spin forever
+      return;
+    }
     float v[16];
     if (act) {
+      const float4* src = reinterpret_cast<const float4*>(&s_tile[tile & 1u][threadIdx.x * kP2PerThread]);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float4 a = *reinterpret_cast<const float4*>(r + i + 4 * q);
+        const float4 a = src[q];
         v[4 * q + 0] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w;
       }
     } else {
@@ -469,6 +498,9 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
     uint32_t total;
     const uint32_t ex = block_excl_scan(n_sel | (n_cnd << 16), s_tmp, total);
     const uint32_t t_sel = total & 0xffffu, t_cnd = total >> 16;
+    // every thread has copied its part of the stage into registers (the scan's barriers are behind
+    // those reads): the stage can take the tile after next
+    if (threadIdx.x == 0 && tile + 2 < n_tiles) issue_tile(tile + 2);
 
     if (mode == kModeTop) {
       if (fill_sel + t_sel > kQueueCap || fill_cnd + t_cnd > kQueueCap) flush();
@@ -837,8 +869,22 @@ cudaError_t launch_select(const SelectArgs& A, uint32_t randomk_seed, cudaStream
   if (b16) k_pass1<true><<<A.n_chunks, kThreads, 0, stream>>>(A);
   else     k_pass1<false><<<A.n_chunks, kThreads, 0, stream>>>(A);
   k_plan<<<A.n_segs, kThreads, 0, stream>>>(A);
-  if (b16) k_pass2<true><<<A.n_chunks, kThreads, 0, stream>>>(A);
-  else     k_pass2<false><<<A.n_chunks, kThreads, 0, stream>>>(A);
+  constexpr int kTileBytes = 2 * kP2PerIter * sizeof(float);
+  {
+    // opt in to more than 48 KB of shared memory, once per device
+    static bool ready[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && !ready[dev]) {
+      e = cudaFuncSetAttribute(k_pass2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(k_pass2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes);
+      if (e != cudaSuccess) return e;
+      ready[dev] = true;
+    }
+  }
+  if (b16) k_pass2<true><<<A.n_chunks, kThreads, kTileBytes, stream>>>(A);
+  else     k_pass2<false><<<A.n_chunks, kThreads, kTileBytes, stream>>>(A);
   k_cand<<<A.n_segs, kCandThreads, 0, stream>>>(A);
   return cudaGetLastError();
 }
