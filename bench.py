@@ -49,7 +49,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--optimizer", default="adam")
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--staleness", type=int, default=1)
-    ap.add_argument("--bucket-mb", type=float, default=32.0)
+    ap.add_argument("--bucket-mb", type=float, default=64.0)
     ap.add_argument("--graph", type=int, default=1, help="capture the training step in a CUDA graph")
     ap.add_argument("--channels-last", type=int, default=1, help="NHWC memory format for vision models")
     ap.add_argument("--amp", default="none", choices=["none", "bf16"])

@@ -48,8 +48,8 @@ def main() -> None:
     ap.add_argument("--compressor", default="thresholdv16")
     ap.add_argument("--optimizer", default="adam")
     ap.add_argument("--ratio", type=float, default=0.99)
-    ap.add_argument("--bucket-mb", type=float, default=32.0)
-    ap.add_argument("--chunk-elems", type=int, default=16384)
+    ap.add_argument("--bucket-mb", type=float, default=64.0)
+    ap.add_argument("--chunk-elems", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()

@@ -68,7 +68,7 @@ class BucketLayout:
 
     names: Sequence[str]
     numels: Sequence[int]
-    chunk_elems: int = 16384
+    chunk_elems: int = 8192
     segments: list[Segment] = field(default_factory=list)
     n_total: int = 0
     cap: int = 0

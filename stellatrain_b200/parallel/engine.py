@@ -33,8 +33,8 @@ class EngineConfig:
     optimizer_options: dict = field(default_factory=dict)
     staleness: int = 1                    # backend/src/engine/core.cpp:80
     grad_accumulation: int = 1
-    bucket_mb: float = 32.0
-    chunk_elems: int = 16384
+    bucket_mb: float = 64.0               # few, large buckets: every chain of six launches has a fixed cost
+    chunk_elems: int = 8192               # work unit of the streaming passes (one CTA); small units balance the tail
     transport: str = "auto"               # auto | peer | nccl | local
     multicast: bool = True                # use the NVLS multicast alias for pushes when available
     timeout_s: float = 10.0               # bound of every device-side wait
