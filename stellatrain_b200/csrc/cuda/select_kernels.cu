@@ -594,7 +594,9 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
     }
   }
   if (mode == kModeTop && (fill_sel | fill_cnd)) flush();
-  if (emitted) __threadfence_system();
+  // No fence here: the arrival flag is published by the last kernel of the chain, and a kernel
+  // boundary on the stream already orders these stores before anything that kernel does.
+  (void)emitted;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -723,7 +725,7 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
         }
       }
     }
-    if (emitted) __threadfence_system();
+    (void)emitted;
     if (tid == 0) {
       SegState ss = A.state[seg];
       // Next select: centre the histogram on the threshold just found, unless it fell off the
@@ -751,13 +753,13 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
     // threshold-v may under-fill (thresholdv.cpp:82): pad the fixed-size stream
     for (uint32_t p = wp->found + tid; p < sd.k; p += kCandThreads)
       emit_entry(A, slot_off, p, kSentinelIdx, 0.f);
-    __threadfence_system();
   }
 
-  // completion: the last CTA publishes the arrival flags and advances the epoch
+  // completion: the last CTA publishes the arrival flags and advances the epoch.  The CTA barrier
+  // orders this CTA's stores before thread 0's system-scope fence, the counter orders the CTAs.
   __syncthreads();
   if (tid == 0) {
-    __threadfence();
+    __threadfence_system();
     const uint32_t prev = atomicAdd(A.done_ctr, 1u);
     if (prev == gridDim.x - 1) {
       *A.done_ctr = 0;
