@@ -49,6 +49,7 @@ class EngineConfig:
                                           # between all ranks, with k = kept budget / number of groups per tensor
     fine_grained_gating: bool = False     # wait per first-using module instead of at the root
     status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
+    profile: bool = False                 # NVTX ranges and CUDA-event timers per bucket and stage (utils/stats.py)
 
 
 class _BucketRuntime:
@@ -124,6 +125,8 @@ class SparseDPEngine:
         self._status_dev = torch.zeros(len(self.buckets), dtype=torch.int32, device=self.device)
         self._status_event: Optional[torch.cuda.Event] = None
         self.stats = {"select_launches": 0, "apply_launches": 0, "kernels": 0}
+        from ..utils.stats import StepTimer
+        self.timer = StepTimer(enabled=cfg.profile)
 
     # ------------------------------------------------------------------ construction
     def _build_buckets(self, params: list[tuple[str, nn.Parameter]]) -> None:
@@ -366,6 +369,21 @@ class SparseDPEngine:
             rt.has_pending_apply = True
 
     def _select(self, rt: _BucketRuntime) -> None:
+        if self.cfg.profile and not self._capturing:
+            with self.timer.stage(f"{rt.select_count}@bucket{rt.bucket.index}", "Select", self.sparse_stream):
+                self._select_impl(rt)
+            self.timer.collect()
+        else:
+            self._select_impl(rt)
+
+    def _apply(self, rt: _BucketRuntime) -> None:
+        if self.cfg.profile and not self._capturing:
+            with self.timer.stage(f"{rt.apply_count}@bucket{rt.bucket.index}", "Apply", self.sparse_stream):
+                self._apply_impl(rt)
+        else:
+            self._apply_impl(rt)
+
+    def _select_impl(self, rt: _BucketRuntime) -> None:
         b = rt.bucket
         s = self.sparse_stream
         if self.transport == "nccl":
@@ -396,7 +414,7 @@ class SparseDPEngine:
         self.stats["select_launches"] += 1
         self.stats["kernels"] += 2 if b.compressor == "randomk" else 4
 
-    def _apply(self, rt: _BucketRuntime) -> None:
+    def _apply_impl(self, rt: _BucketRuntime) -> None:
         s = self.sparse_stream
         rt.bucket.handle.apply(s.cuda_stream)
         ev = torch.cuda.Event()
@@ -419,6 +437,12 @@ class SparseDPEngine:
         cur.wait_stream(self.sparse_stream)
         self.sparse_stream.synchronize()
         self.check_status()
+
+    def export_stats(self, path: Optional[str] = None) -> str:
+        """Per-bucket stage times as JSON ``{"<iteration>@bucket<i>": {"Select": ms, "Apply": ms}}``
+        (the reference writes /tmp/time_log_<timestamp>_<pid>.json, backend/src/engine/core.cpp:1176-1207)."""
+        torch.cuda.synchronize(self.device)
+        return self.timer.export_json(path)
 
     def barrier(self) -> None:
         torch.cuda.synchronize(self.device)
@@ -580,6 +604,26 @@ class SparseDPEngine:
                 w.flag_local.fill_(e)
                 w.ack_local.fill_(e)
             torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+
+    def load_replica_state(self, sd: dict) -> None:
+        """Restore only what does not depend on the world size: parameters, optimiser moments and step
+        counters, thresholds.  Used when a job resumes with a different number of ranks."""
+        self.synchronize()
+        if sd["param_names"] != self.param_names:
+            raise ValueError("checkpoint was written for a different model or bucket plan")
+        for rt, bsd in zip(self.buckets, sd["buckets"]):
+            b = rt.bucket
+            for k in ("param", "m", "v", "vmax", "last"):
+                t = getattr(b, k)
+                if t is not None and k in bsd:
+                    t.copy_(bsd[k])
+            b.opt.copy_(bsd["opt"])
+            b._opt_host = b.opt.cpu().numpy().view(B.OPT_STATE_DTYPE).copy()
+            b.state.copy_(bsd["seg_state"])
+            b.resid.zero_(); b.acc.zero_(); b.grad.zero_(); b.stamp.zero_()
+        torch.cuda.synchronize(self.device)
+        if self.dist_on:
             dist.barrier(self.group)
 
     def close(self) -> None:

@@ -44,15 +44,23 @@ def save(path: str, module: torch.nn.Module, engine, extra: Optional[dict] = Non
     return str(p)
 
 
-def load(path: str, module: torch.nn.Module, engine, map_location="cpu") -> dict:
+def load(path: str, module: torch.nn.Module, engine, map_location="cpu", allow_world_change: bool = False) -> dict:
+    """``allow_world_change``: resume on a different number of ranks (after losing one, or after growing).
+    Parameters, optimiser state and thresholds are replica-independent and are restored; residuals, epochs and
+    exchange counters depend on the world size and start afresh (the unsent gradient mass of the old job is
+    dropped, which costs at most one step's worth of updates)."""
     rank, world = _rank_world()
     p = Path(path)
-    if world > 1:
+    if not p.exists():
         mine = p.with_name(f"{p.stem}.rank{rank}{p.suffix}")
         p = mine if mine.exists() else p.with_name(f"{p.stem}.rank0{p.suffix}")
     ck = torch.load(p, map_location=map_location, weights_only=False)
     if ck["world"] != world:
-        raise ValueError(f"checkpoint was written by {ck['world']} ranks, this job has {world}")
+        if not allow_world_change:
+            raise ValueError(f"checkpoint was written by {ck['world']} ranks, this job has {world}")
+        module.load_state_dict(ck["model"], strict=False)
+        engine.load_replica_state(ck["engine"])
+        return ck["extra"]
     # buffers (e.g. BatchNorm statistics) come from the model part, parameters from the engine's buckets
     module.load_state_dict(ck["model"], strict=False)
     engine.load_state_dict(ck["engine"])
