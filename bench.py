@@ -57,6 +57,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--grad-mode", default="steal", choices=["steal", "flat"])
     ap.add_argument("--momentum", type=float, default=0.0)
     ap.add_argument("--group-size", type=int, default=1, help="ranks per group (grouped two-level mode)")
+    ap.add_argument("--state-partition", default="replicated", choices=["replicated", "owner"],
+                    help="owner: optimiser state of every tensor on one rank, new values stored into all replicas")
     ap.add_argument("--shape-gbps", default=None, help="lo:hi[:seed] emulated cross-group link, e.g. 10:40:0")
     ap.add_argument("--controller", type=int, default=0, help="run the telemetry controller and apply its instructions")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -170,6 +172,7 @@ def main() -> None:
         if args.optimizer == "sgd" and args.momentum:
             st.configure_optimizer("momentum", args.momentum)
         st.state().engine_cfg.group_size = args.group_size
+        st.state().engine_cfg.state_partition = args.state_partition
         if args.controller:
             st.state().engine_cfg.min_ratio = min(args.ratio, 0.9)      # room for the controller to lower the ratio
         st.state().engine_cfg.bucket_mb = args.bucket_mb
@@ -347,7 +350,7 @@ def main() -> None:
                 "compressor": args.compressor, "kept_fraction": 1 - args.ratio, "optimizer": args.optimizer,
                 "lr": args.lr, "staleness": args.staleness, "bucket_mb": args.bucket_mb,
                 "transport": engine.transport if engine is not None else args.impl, "group_size": args.group_size,
-                "shaped_link_gbps": args.shape_gbps,
+                "state_partition": args.state_partition, "shaped_link_gbps": args.shape_gbps,
                 "controller": ({"instructions_applied": len(hook.applied), "final_ratio": engine.cfg.ratio,
                                 "shaped_gbps_achieved": (engine.shaper.achieved_gbps() if engine.shaper else None)}
                                if hook is not None else None),

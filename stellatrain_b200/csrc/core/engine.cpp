@@ -422,6 +422,37 @@ void CpuEngine::copy_out_done(int index, int64_t iter) {
   schedule_terminate(t);
 }
 
+// Where a task currently is: its state and the gate it waits at, for timeout messages.
+std::string CpuEngine::describe_task(const std::string& key) {
+  std::shared_ptr<TrainTask> t;
+  {
+    std::lock_guard<std::mutex> lk(tasks_mu_);
+    auto it = tasks_.find(key);
+    if (it == tasks_.end()) return "no longer tracked";
+    t = it->second;
+  }
+  std::string where = std::string("state ") + task_state_name(t->state());
+  auto holds = [&](const std::list<std::pair<Module*, std::shared_ptr<TrainTask>>>& l) {
+    for (auto& e : l) if (e.second.get() == t.get()) return true;
+    return false;
+  };
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    if (holds(waiting_model_)) where += ", waits for the previous version to be released";
+    if (holds(waiting_prev_)) where += ", waits for the previous iteration of the parameter";
+  }
+  {
+    std::lock_guard<std::mutex> lk(use_mu_);
+    for (auto& kv : use_waiters_) if (holds(kv.second)) where += ", waits for its gradient slot";
+  }
+  {
+    std::lock_guard<std::mutex> lk(barrier_mu_);
+    for (auto& b : pending_barriers_) if (b.task.get() == t.get()) where += ", waits at a node barrier";
+  }
+  where += ", " + std::to_string(pool_->pending()) + " jobs queued";
+  return where;
+}
+
 // ---------------------------------------------------------------- synchronize
 void CpuEngine::synchronize() {
   // release every "previous version still in use" gate (reference core.cpp:910-922)
@@ -449,7 +480,7 @@ void CpuEngine::synchronize() {
         break;
       }
       if (Clock::now() > deadline) {
-        err = "synchronize timed out on " + f.first;
+        err = "synchronize timed out on " + f.first + " (" + describe_task(f.first) + ")";
         break;
       }
     }

@@ -157,6 +157,7 @@ class CpuEngine {
   void barrier_manager_main();
   void start_task(int param_index);
   void notify_layer_usage_finished(ParamLocal& p, int64_t iter);
+  std::string describe_task(const std::string& key);
 
   EngineOptions opt_;
   std::atomic<bool> ready_{false};

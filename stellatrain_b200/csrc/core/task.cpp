@@ -58,15 +58,20 @@ void TrainTask::fail(const std::string& why) {
   state_.store(TaskState::Failed, std::memory_order_release);
 }
 
-void TrainTask::stat_start(const std::string& event) { started_[event] = std::chrono::steady_clock::now(); }
+void TrainTask::stat_start(const std::string& event) {
+  std::lock_guard<std::mutex> lk(stat_mu_);
+  started_[event] = std::chrono::steady_clock::now();
+}
 
 void TrainTask::stat_end(const std::string& event) {
+  std::lock_guard<std::mutex> lk(stat_mu_);
   auto it = started_.find(event);
   if (it == started_.end()) return;
   elapsed_[event] = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - it->second).count();
 }
 
 std::map<std::string, double> TrainTask::stats() const {
+  std::lock_guard<std::mutex> lk(stat_mu_);
   std::map<std::string, double> out = elapsed_;
   for (auto& kv : started_)
     if (!out.count(kv.first)) out[kv.first] = -1.0;

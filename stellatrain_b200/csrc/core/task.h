@@ -10,6 +10,7 @@
 #include <chrono>
 #include <cstdint>
 #include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -55,7 +56,9 @@ struct TrainTask {
   uint32_t k = 0;
   int exchange_round = 0;
 
-  // stage timers in milliseconds, -1 when a stage did not run (reference core.cpp:1151-1207)
+  // stage timers in milliseconds, -1 when a stage did not run (reference core.cpp:1151-1207).
+  // Thread-safe: a stage hands the task to the next one before its own timer is closed, so two
+  // workers can be inside these calls for one task at the same time.
   void stat_start(const std::string& event);
   void stat_end(const std::string& event);
   std::map<std::string, double> stats() const;
@@ -63,6 +66,7 @@ struct TrainTask {
  private:
   std::atomic<TaskState> state_{TaskState::Created};
   std::string error_;
+  mutable std::mutex stat_mu_;
   std::map<std::string, std::chrono::steady_clock::time_point> started_;
   std::map<std::string, double> elapsed_;
 };

@@ -66,6 +66,8 @@ struct BucketHandle {
     sel.n_segs = n_segs;
     sel.n_chunks = n_chunks;
     app.cap = cap;
+    app.segs = sel.segs;
+    app.n_segs = n_segs;
   }
 
   void set_scratch(uint64_t cand, uint64_t cand_cursor, uint32_t cand_cap) {
@@ -115,12 +117,50 @@ struct BucketHandle {
     sel.ack_local = as_ptr<const uint64_t>(ack_local);
     sel.use_acks = app.use_acks = use_acks ? 1u : 0u;
     sel.publish = app.use_flags = use_flags ? 1u : 0u;
+    // replicated optimiser state unless set_owner follows
+    sel.owner_mode = app.owner_mode = 0u;
+    app.ent_lo = 0u;
+    app.ent_hi = (uint32_t)cap;
+    app.state_base = 0u;
+    app.state_len = app.n_total;
   }
 
-  void set_options(uint32_t compressor, bool zero_grad, bool skip_ef) {
+  // Partitioned optimiser state.  bounds: world + 1 stream positions, owner o consumes [bounds[o], bounds[o+1]).
+  // state_base/state_len: element range covered by acc, stamp and the optimiser state of this rank.
+  // Write-back areas have the shape of the receive areas; pflag areas are [2][world] u64 indexed [slot][owner].
+  void set_owner(const std::vector<uint32_t>& bounds, uint32_t state_base, uint32_t state_len, uint64_t wb_local,
+                 const std::vector<uint64_t>& peer_wb, uint64_t wb_mc, uint64_t pflag_local,
+                 const std::vector<uint64_t>& peer_pflag) {
+    const int world = app.world;
+    if (world < 1) throw std::runtime_error("set_comm must come first");
+    if ((int)bounds.size() != world + 1 || (int)peer_wb.size() != world || (int)peer_pflag.size() != world)
+      throw std::runtime_error("set_owner: lists must match the world size");
+    for (int o = 0; o <= world; ++o) {
+      if (bounds[o] > app.cap || (o > 0 && bounds[o] < bounds[o - 1])) throw std::runtime_error("set_owner: bad bounds");
+      app.own_lo[o] = bounds[o];
+    }
+    if ((uint64_t)state_base + state_len > app.n_total) throw std::runtime_error("set_owner: bad state range");
+    sel.owner_mode = app.owner_mode = 1u;
+    app.ent_lo = bounds[app.rank];
+    app.ent_hi = bounds[app.rank + 1];
+    app.state_base = state_base;
+    app.state_len = state_len;
+    app.wb_local = as_ptr<const uint2>(wb_local);
+    app.wb_mc = wb_mc ? as_ptr<uint2>(wb_mc) : nullptr;
+    app.pflag_local = as_ptr<const uint64_t>(pflag_local);
+    app.pflag_slot_stride = world;
+    for (int p = 0; p < world; ++p) {
+      app.wb[p] = as_ptr<uint2>(peer_wb[p]);
+      app.pflag[p] = as_ptr<uint64_t>(peer_pflag[p]) + app.rank;
+    }
+  }
+
+  // narrow: some tensors of the bucket carry the narrow-wire flag in their descriptor
+  void set_options(uint32_t compressor, bool zero_grad, bool skip_ef, bool narrow) {
     sel.compressor = compressor;
     sel.zero_grad = zero_grad ? 1u : 0u;
     sel.skip_ef = skip_ef ? 1u : 0u;
+    app.narrow = narrow ? 1u : 0u;
   }
 
   // grouped mode -------------------------------------------------------------------------------
@@ -162,8 +202,8 @@ struct BucketHandle {
   void select(uint64_t stream) {
     check(st::launch_select(sel, randomk_seed, as_ptr<CUstream_st>(stream)), "launch_select");
   }
-  void apply(uint64_t stream) {
-    check(st::launch_apply(app, max_ctas_per_source, as_ptr<CUstream_st>(stream)), "launch_apply");
+  void apply(uint64_t stream, int phase) {
+    check(st::launch_apply(app, max_ctas_per_source, phase, as_ptr<CUstream_st>(stream)), "launch_apply");
   }
 };
 
@@ -212,7 +252,7 @@ PYBIND11_MODULE(_C, m) {
            py::arg("peer_recv"), py::arg("recv_mc"), py::arg("flag_local"), py::arg("peer_flag"),
            py::arg("ack_local"), py::arg("peer_ack"), py::arg("use_flags"), py::arg("use_acks"))
       .def("set_options", &BucketHandle::set_options, py::arg("compressor"), py::arg("zero_grad"),
-           py::arg("skip_ef") = false)
+           py::arg("skip_ef") = false, py::arg("narrow") = false)
       .def_readwrite("randomk_seed", &BucketHandle::randomk_seed)
       .def_readwrite("max_ctas_per_source", &BucketHandle::max_ctas_per_source)
       .def("set_group", &BucketHandle::set_group, py::arg("grad_local"), py::arg("mate_grad"), py::arg("mate_local"),
@@ -220,7 +260,9 @@ PYBIND11_MODULE(_C, m) {
            py::arg("group_done_ctr"))
       .def("group_reduce", &BucketHandle::group_reduce, py::arg("stream"))
       .def("select", &BucketHandle::select, py::arg("stream"))
-      .def("apply", &BucketHandle::apply, py::arg("stream"));
+      .def("set_owner", &BucketHandle::set_owner, py::arg("bounds"), py::arg("state_base"), py::arg("state_len"),
+           py::arg("wb_local"), py::arg("peer_wb"), py::arg("wb_mc"), py::arg("pflag_local"), py::arg("peer_pflag"))
+      .def("apply", &BucketHandle::apply, py::arg("stream"), py::arg("phase") = 0);
 
   m.def("max_abs_diff", [](uint64_t a, uint64_t b, uint64_t n, uint64_t out_bits, uint64_t stream) {
     check(st::launch_max_abs_diff(as_ptr<const float>(a), as_ptr<const float>(b), n, as_ptr<uint32_t>(out_bits),

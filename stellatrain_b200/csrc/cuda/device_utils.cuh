@@ -53,11 +53,52 @@ __device__ __forceinline__ void multimem_st_pair(uint2* mc_addr, uint2 v) {
                : "memory");
 }
 
-// Store one stream entry into the receive area of every destination.
-__device__ __forceinline__ void emit_entry(const SelectArgs& A, uint64_t slot_off, uint32_t pos,
-                                           uint32_t idx, float val) {
+__device__ __forceinline__ void multimem_st_u32(uint32_t* mc_addr, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+
+// Narrow wire format -----------------------------------------------------------------------------
+// First element of the tensor when its entries travel as 4-byte words, else kNotNarrow.
+__device__ __forceinline__ uint32_t narrow_base_of(const SegDesc& sd) {
+  return (sd.reserved & kSegNarrow) ? sd.off : kNotNarrow;
+}
+
+// The value as it will arrive: unchanged, or rounded to bf16 (nearest even).  The sender keeps
+// x - wire_value(x) in its residual, so the rounding error is fed back like every unsent entry.
+__device__ __forceinline__ float wire_value(uint32_t narrow_base, float x) {
+  if (narrow_base == kNotNarrow) return x;
+  const uint32_t b = __float_as_uint(x);
+  return __uint_as_float((b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u);
+}
+
+// Destination of a segment's entries: one rank when the optimiser state is partitioned, else all (-1).
+__device__ __forceinline__ int dest_of(const SelectArgs& A, const SegDesc& sd) {
+  return A.owner_mode ? (int)((sd.reserved >> kSegOwnerShift) & kSegOwnerMask) : -1;
+}
+
+// Store one stream entry into the receive area of every destination (dest < 0) or of one rank.
+// slot_off: start of the tensor's region in the stream; pos: entry inside the region; val must already
+// be wire_value(narrow_base, .).
+__device__ __forceinline__ void emit_entry(const SelectArgs& A, int dest, uint32_t narrow_base, uint64_t slot_off,
+                                           uint32_t pos, uint32_t idx, float val) {
+  if (narrow_base != kNotNarrow) {
+    const uint32_t w = idx == kSentinelIdx ? 0xFFFFFFFFu : ((idx - narrow_base) | (__float_as_uint(val) & 0xFFFF0000u));
+    if (dest >= 0) {
+      reinterpret_cast<uint32_t*>(A.out[dest] + slot_off)[pos] = w;
+    } else if (A.out_mc != nullptr) {
+      multimem_st_u32(reinterpret_cast<uint32_t*>(A.out_mc + slot_off) + pos, w);
+    } else {
+#pragma unroll
+      for (int p = 0; p < kMaxWorld; ++p) {
+        if (p < A.world) reinterpret_cast<uint32_t*>(A.out[p] + slot_off)[pos] = w;
+      }
+    }
+    return;
+  }
   const uint2 e = make_uint2(idx, __float_as_uint(val));
-  if (A.out_mc != nullptr) {
+  if (dest >= 0) {
+    A.out[dest][slot_off + pos] = e;
+  } else if (A.out_mc != nullptr) {
     multimem_st_pair(A.out_mc + slot_off + pos, e);
   } else {
 #pragma unroll
@@ -65,6 +106,22 @@ __device__ __forceinline__ void emit_entry(const SelectArgs& A, uint64_t slot_of
       if (p < A.world) A.out[p][slot_off + pos] = e;
     }
   }
+}
+
+// Entry at position i of one source's stream (`in` points at position 0), decoded to (bucket index, value).
+__device__ __forceinline__ uint2 load_entry(const ApplyArgs& A, const uint2* in, uint32_t i) {
+  if (!A.narrow) return __ldcg(in + i);   // written by a peer: bypass L1
+  // last tensor whose region starts at or before i
+  uint32_t lo = 0, hi = A.n_segs;
+  while (hi - lo > 1u) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (A.segs[mid].out_off <= i) lo = mid; else hi = mid;
+  }
+  const SegDesc sd = A.segs[lo];
+  if (!(sd.reserved & kSegNarrow)) return __ldcg(in + i);
+  const uint32_t w = __ldcg(reinterpret_cast<const uint32_t*>(in + sd.out_off) + (i - sd.out_off));
+  if (w == 0xFFFFFFFFu) return make_uint2(kSentinelIdx, 0u);
+  return make_uint2(sd.off + (w & 0xFFFFu), w & 0xFFFF0000u);
 }
 
 // ---- TMA bulk copies (cp.async.bulk) with mbarrier completion --------------------------------

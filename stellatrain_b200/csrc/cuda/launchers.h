@@ -8,8 +8,10 @@ namespace st {
 // Error-feedback select + push of one bucket: four kernels on `stream` (two for random-k).
 cudaError_t launch_select(const SelectArgs& args, uint32_t randomk_seed, cudaStream_t stream);
 
-// Bounded wait + scatter-add + sparse optimiser of one bucket: two kernels on `stream`.
-cudaError_t launch_apply(const ApplyArgs& args, int max_ctas_per_source, cudaStream_t stream);
+// Bounded wait + scatter-add + sparse optimiser of one bucket: two kernels on `stream`, plus the copy of
+// the owners' new parameter values when the optimiser state is partitioned.  phase 0 = all, 1 = scatter and
+// apply only, 2 = parameter copy only.
+cudaError_t launch_apply(const ApplyArgs& args, int max_ctas_per_source, int phase, cudaStream_t stream);
 
 // max |a - b| as float bits, atomically folded into *out_bits (caller zeroes it).
 cudaError_t launch_max_abs_diff(const float* a, const float* b, uint64_t n, uint32_t* out_bits,

@@ -365,6 +365,8 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
   const HistWindow win = window_of(A.state[ch.seg]);
   const uint32_t epoch = *A.epoch;
   const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
+  const int dest = dest_of(A, sd);
+  const uint32_t nb = narrow_base_of(sd);
   const uint32_t kk = B16 ? (sd.k + 15u) / 16u : sd.k;
   const uint32_t base_pos = A.chunk_pos[blockIdx.x];
   float* r = A.resid + ch.start;
@@ -383,8 +385,9 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
     for (uint32_t e = 0; e < 16u; ++e) {
       const uint32_t p = pos * 16u + e;
       if (p < sd.k) {
-        emit_entry(A, slot_off, p, gi0 + e, A.resid[gi0 + e]);
-        A.resid[gi0 + e] = 0.f;
+        const float a = A.resid[gi0 + e], sv = wire_value(nb, a);
+        emit_entry(A, dest, nb, slot_off, p, gi0 + e, sv);
+        A.resid[gi0 + e] = a - sv;
       }
     }
   };
@@ -400,7 +403,7 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
     if (!B16) {
       for (uint32_t j = threadIdx.x; j < fill_sel; j += kThreads) {
         const uint2 e = s_sel[j];
-        if (b_sel + j < kk) emit_entry(A, slot_off, b_sel + j, e.x, __uint_as_float(e.y));
+        if (b_sel + j < kk) emit_entry(A, dest, nb, slot_off, b_sel + j, e.x, __uint_as_float(e.y));
       }
     } else {
       for (uint32_t t = threadIdx.x; t < fill_sel * 16u; t += kThreads) {
@@ -408,8 +411,9 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
         const uint32_t gi = s_selb[q] * 16u + e;
         const uint32_t p = (b_sel + q) * 16u + e;
         if (p < sd.k) {
-          emit_entry(A, slot_off, p, gi, A.resid[gi]);
-          A.resid[gi] = 0.f;
+          const float a = A.resid[gi], sv = wire_value(nb, a);
+          emit_entry(A, dest, nb, slot_off, p, gi, sv);
+          A.resid[gi] = a - sv;
         }
       }
     }
@@ -521,10 +525,11 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (sel_mask >> j & 1u) {
-              if (direct) { if (p < kk) emit_entry(A, slot_off, p, gi + j, v[j]); }
-              else s_sel[p] = make_uint2(gi + j, __float_as_uint(v[j]));
+              const float sv = wire_value(nb, v[j]);
+              if (direct) { if (p < kk) emit_entry(A, dest, nb, slot_off, p, gi + j, sv); }
+              else s_sel[p] = make_uint2(gi + j, __float_as_uint(sv));
               ++p;
-              v[j] = 0.f;
+              v[j] -= sv;   // exactly zero unless the wire format rounds
             }
             if (cnd_mask >> j & 1u) {
               const uint2 c = make_uint2(gi + j, key_bits(v[j]));
@@ -563,8 +568,9 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
           for (int j = 0; j < 16; ++j) {
             if (sel_mask >> j & 1u) {
               if (pos < kk) {   // ordered mode truncates at k; the rest stays in the residual
-                emit_entry(A, slot_off, pos, gi + j, v[j]);
-                v[j] = 0.f;
+                const float sv = wire_value(nb, v[j]);
+                emit_entry(A, dest, nb, slot_off, pos, gi + j, sv);
+                v[j] -= sv;
                 any = true;
               }
               ++pos;
@@ -581,8 +587,9 @@ __global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (pos * 16u + j < sd.k) {
-              emit_entry(A, slot_off, pos * 16u + j, gi + j, v[j]);
-              v[j] = 0.f;
+              const float sv = wire_value(nb, v[j]);
+              emit_entry(A, dest, nb, slot_off, pos * 16u + j, gi + j, sv);
+              v[j] -= sv;
             }
           }
 #pragma unroll
@@ -619,6 +626,8 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
   const bool b16 = A.compressor == kThresholdv16;
   const uint32_t kk = b16 ? (sd.k + 15u) / 16u : sd.k;
   const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
+  const int dest = dest_of(A, sd);
+  const uint32_t nb = narrow_base_of(sd);
   const uint32_t mode = wp->mode;
 
   if (ok && mode == kModeTop) {
@@ -708,8 +717,9 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
       if (!b16) {
         const uint32_t pos = atomicAdd(&wp->out_cursor, 1u);
         if (pos < kk) {
-          emit_entry(A, slot_off, pos, e.x, A.resid[e.x]);
-          A.resid[e.x] = 0.f;
+          const float a = A.resid[e.x], sv = wire_value(nb, a);
+          emit_entry(A, dest, nb, slot_off, pos, e.x, sv);
+          A.resid[e.x] = a - sv;
         }
       } else {
         const bool is_last = (e.y == t_key && e.x == last_id);
@@ -718,8 +728,9 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
           const uint32_t base = e.x * 16u;
           for (uint32_t j = 0; j < 16u; ++j) {
             if (pos * 16u + j < sd.k) {
-              emit_entry(A, slot_off, pos * 16u + j, base + j, A.resid[base + j]);
-              A.resid[base + j] = 0.f;
+              const float a = A.resid[base + j], sv = wire_value(nb, a);
+              emit_entry(A, dest, nb, slot_off, pos * 16u + j, base + j, sv);
+              A.resid[base + j] = a - sv;
             }
           }
         }
@@ -752,7 +763,7 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
   } else if (ok && mode == kModeInOrder && !b16 && wp->found < sd.k) {
     // threshold-v may under-fill (thresholdv.cpp:82): pad the fixed-size stream
     for (uint32_t p = wp->found + tid; p < sd.k; p += kCandThreads)
-      emit_entry(A, slot_off, p, kSentinelIdx, 0.f);
+      emit_entry(A, dest, nb, slot_off, p, kSentinelIdx, 0.f);
   }
 
   // completion: the last CTA publishes the arrival flags and advances the epoch.  The CTA barrier
@@ -790,6 +801,8 @@ __global__ void __launch_bounds__(kThreads) k_randomk(SelectArgs A, uint32_t see
   const uint32_t epoch = *A.epoch;
   const bool ok = ld_volatile_u32(A.status) == kOk;
   const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
+  const int dest = dest_of(A, sd);
+  const uint32_t nb = narrow_base_of(sd);
   if (ok) {
     const uint32_t h = mix32(seed ^ mix32(epoch * 0x9E3779B9u + seg));
     const uint32_t start = h % sd.n;
@@ -803,8 +816,9 @@ __global__ void __launch_bounds__(kThreads) k_randomk(SelectArgs A, uint32_t see
     for (uint32_t j = threadIdx.x; j < sd.k; j += kThreads) {
       const uint32_t rel = (uint32_t)(((uint64_t)start + (uint64_t)j * stride) % sd.n);
       const uint32_t gi = sd.off + rel;
-      emit_entry(A, slot_off, j, gi, A.resid[gi]);
-      A.resid[gi] = 0.f;
+      const float a = A.resid[gi], sv = wire_value(nb, a);
+      emit_entry(A, dest, nb, slot_off, j, gi, sv);
+      A.resid[gi] = a - sv;
     }
     __threadfence_system();
   }

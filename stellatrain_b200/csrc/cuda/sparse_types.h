@@ -41,6 +41,17 @@ struct SegDesc {          // static per segment (re-uploaded when the compressio
 };
 
 constexpr uint32_t kSegSkip = 1u;   // this rank does not own the tensor (grouped mode): emit nothing, keep no residual
+// Partitioned optimiser state: bits 8..15 of SegDesc.reserved name the rank that keeps the tensor's
+// optimiser state, receives every rank's entries for it and writes the new parameter values back.
+// Narrow wire format: a tensor of fewer than 65536 (padded) elements whose descriptor carries this flag
+// sends 4-byte entries, (index relative to the tensor : 16 | bf16 value : 16), packed at the start of the
+// tensor's region of the stream; 0xFFFFFFFF is "no entry".  Role of the reference's u16 index and fp16 value
+// wire casts (backend/src/engine/comm_manager.cpp:487-571, 579-583), with an unsigned index.
+constexpr uint32_t kSegNarrow = 2u;
+constexpr uint32_t kNarrowLimit = 65536u;
+constexpr uint32_t kNotNarrow = 0xFFFFFFFFu;
+constexpr uint32_t kSegOwnerShift = 8u;
+constexpr uint32_t kSegOwnerMask = 0xFFu;
 
 struct SegState {         // persistent per segment, saved in checkpoints
   float tau;              // threshold (element magnitude or 16-block L1 norm)
@@ -116,6 +127,7 @@ struct SelectArgs {
   const uint64_t* ack_local;   // [2][world] acknowledgements written by the destinations
   uint32_t use_acks;           // wait for acknowledgements before overwriting a slot
   uint32_t publish;            // publish arrival flags when the stream is complete
+  uint32_t owner_mode;         // 1: a segment's entries go only to the rank named in its descriptor
   uint32_t* epoch;             // select epoch of this bucket (starts at 1)
   uint32_t* done_ctr;          // CTA completion counter of the last kernel of the chain
   uint32_t* status;            // Status
@@ -147,6 +159,27 @@ struct ApplyArgs {
   uint32_t* done_ctr;
   uint32_t* status;
   uint64_t timeout_ns;
+  // Range of stream positions this rank consumes, and the element range its accumulator, stamps and
+  // optimiser state cover (acc, stamp, m, v, vmax, last are indexed by idx - state_base).  Replicated
+  // state: [0, cap) and [0, n_total).
+  uint32_t ent_lo, ent_hi;
+  uint32_t state_base, state_len;
+  // Partitioned state ("owner mode"): the owner of a tensor applies the update and stores, for every
+  // stream position it consumed, either (idx, new parameter value) or the "no entry" marker into the
+  // same position of every rank's write-back area; each rank then copies the values into its replica.
+  uint32_t owner_mode;
+  // Segment table, needed only when some tensors use the narrow wire format (narrow != 0): the receiver
+  // finds the tensor of a stream position by binary search over out_off.
+  uint32_t narrow;
+  uint32_t n_segs;
+  const SegDesc* segs;
+  uint32_t own_lo[kMaxWorld + 1];   // owner o consumes positions [own_lo[o], own_lo[o + 1])
+  uint2* wb[kMaxWorld];             // per rank: its write-back area [2][world][cap], slot 0
+  uint2* wb_mc;                     // multicast alias of the write-back area, or null
+  const uint2* wb_local;            // this rank's write-back area
+  uint64_t* pflag[kMaxWorld];       // per rank: its "parameters of owner `rank` have landed" word, slot 0
+  const uint64_t* pflag_local;      // [2][world] written by the owners
+  uint64_t pflag_slot_stride;
 };
 
 // Intra-group dense reduction (grouped topologies).

@@ -29,6 +29,8 @@ OPT_STATE_DTYPE = np.dtype(
      ("tick", "<u4"), ("first", "<u4"), ("kind", "<u4"), ("reserved1", "<u4")]
 )
 
+NARROW_LIMIT = 65536      # reference: u16 indices when the tensor has fewer than 65536 elements (comm_manager.cpp:579-583)
+
 COMPRESSORS = {"topk": 0, "thresholdv": 1, "thresholdv16": 2, "randomk": 3}
 
 
@@ -60,6 +62,7 @@ class Segment:
     chunk_begin: int = 0
     chunk_cnt: int = 0
     skip: bool = False     # grouped mode: another rank of the group owns this tensor
+    owner: int = 0         # partitioned optimiser state: the rank that keeps this tensor's state
 
 
 @dataclass
@@ -72,6 +75,7 @@ class BucketLayout:
     segments: list[Segment] = field(default_factory=list)
     n_total: int = 0
     cap: int = 0
+    narrow_wire: bool = False   # tensors below NARROW_LIMIT padded elements send 4-byte (u16 index, bf16 value) entries
 
     def __post_init__(self) -> None:
         if self.chunk_elems % 1024:
@@ -111,13 +115,45 @@ class BucketLayout:
             s.skip = owner[i] != my_local
         return owner
 
+    def assign_state_owners(self, world: int) -> list[int]:
+        """Partitioned optimiser state: consecutive tensors go to the same rank so that every rank keeps one
+        contiguous element range of the bucket; a tensor belongs to the rank whose 1/world share of the bucket
+        contains its midpoint.  Returns the owner of every tensor."""
+        for s in self.segments:
+            s.owner = min(world - 1, int((s.off + s.n_pad / 2.0) * world / max(1, self.n_total)))
+        return [s.owner for s in self.segments]
+
+    def state_range(self, rank: int) -> tuple[int, int]:
+        """Element range [lo, hi) of the bucket whose optimiser state ``rank`` keeps (empty: lo == hi)."""
+        mine = [s for s in self.segments if s.owner == rank]
+        if not mine:
+            return (0, 0)
+        return (mine[0].off, mine[-1].off + mine[-1].n_pad)
+
+    def owner_bounds(self, world: int) -> list[int]:
+        """world + 1 stream positions: owner o consumes the entries [bounds[o], bounds[o + 1])."""
+        bounds = [0] * (world + 1)
+        for s in self.segments:
+            bounds[s.owner + 1] += s.k
+        for o in range(world):
+            bounds[o + 1] += bounds[o]
+        return bounds
+
+    def is_narrow(self, s: Segment) -> bool:
+        return self.narrow_wire and s.n_pad < NARROW_LIMIT
+
+    def wire_bytes(self, owned_only: bool = False) -> int:
+        """Bytes one rank stores into one destination for this bucket per step."""
+        return sum(s.k * (4 if self.is_narrow(s) else 8) for s in self.segments if not (owned_only and s.skip))
+
     def max_cap(self, min_ratio: float, world: int) -> int:
         return sum(entries_for(s.numel, min_ratio, world) for s in self.segments)
 
     def seg_table(self) -> np.ndarray:
         t = np.zeros(len(self.segments), dtype=SEG_DESC_DTYPE)
         for i, s in enumerate(self.segments):
-            t[i] = (s.off, s.numel, s.n_pad, s.k, s.out_off, s.chunk_begin, s.chunk_cnt, 1 if s.skip else 0)
+            t[i] = (s.off, s.numel, s.n_pad, s.k, s.out_off, s.chunk_begin, s.chunk_cnt,
+                    (1 if s.skip else 0) | (2 if self.is_narrow(s) else 0) | ((s.owner & 0xFF) << 8))
         return t
 
     def chunk_table(self) -> np.ndarray:

@@ -47,6 +47,11 @@ class EngineConfig:
     group_size: int = 1                   # > 1: ranks form groups of this size; gradients are summed densely inside a
                                           # group (each rank reducing the tensors it owns) and exchanged sparsely
                                           # between all ranks, with k = kept budget / number of groups per tensor
+    state_partition: str = "replicated"   # "owner": every tensor's optimiser state lives on one rank, which receives
+                                          # all ranks' entries for it, applies the update and stores the new values
+                                          # into every replica (1/world of the state memory, bit-equal replicas)
+    wire_format: str = "wide"             # "narrow": tensors below 65536 elements send 4-byte entries (u16 index relative
+                                          # to the tensor, bf16 value; the rounding error stays in the residual)
     fine_grained_gating: bool = False     # wait per first-using module instead of at the root
     status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
     profile: bool = False                 # NVTX ranges and CUDA-event timers per bucket and stage (utils/stats.py)
@@ -106,6 +111,13 @@ class SparseDPEngine:
             if transport != "peer":
                 raise ValueError("grouped mode needs the peer transport")
             cfg.grad_mode = "flat"          # group-mates read each other's gradients: they must sit in the pool
+        if cfg.wire_format not in ("wide", "narrow"):
+            raise ValueError("wire_format must be 'wide' or 'narrow'")
+        if cfg.state_partition not in ("replicated", "owner"):
+            raise ValueError("state_partition must be 'replicated' or 'owner'")
+        self.partitioned = cfg.state_partition == "owner" and self.world > 1
+        if self.partitioned and (transport != "peer" or L > 1):
+            raise ValueError("partitioned optimiser state needs the peer transport and group_size 1")
         self.shaper = None
         low, high = torch.cuda.Stream.priority_range()
         self.sparse_stream = torch.cuda.Stream(device=self.device, priority=high)
@@ -143,13 +155,15 @@ class SparseDPEngine:
             idxs = [order[j] for j in grp]
             names = [params[i][0] for i in idxs]
             plist = [params[i][1] for i in idxs]
-            layout = B.BucketLayout(names, [p.numel() for p in plist], chunk_elems=cfg.chunk_elems)
+            layout = B.BucketLayout(names, [p.numel() for p in plist], chunk_elems=cfg.chunk_elems,
+                                    narrow_wire=(cfg.wire_format == "narrow"))
             bucket = GpuBucket(
                 bi, layout, self.device, compressor=cfg.compressor, ratio=cfg.ratio, world=self.world,
                 rank=self.rank, optimizer=cfg.optimizer, amsgrad=cfg.amsgrad,
                 smart_momentum=cfg.smart_momentum, min_ratio=cfg.min_ratio, scratch=self.scratch,
                 timeout_s=cfg.timeout_s, divide_k_by_world=cfg.divide_k_by_world,
                 k_world=(self.groups if (self.group_size > 1 and cfg.divide_k_by_world) else None),
+                partition_state=self.partitioned,
             )
             if self.group_size > 1:
                 layout.assign_owners(self.group_size, self.my_local)
@@ -184,6 +198,8 @@ class SparseDPEngine:
         need = sum(rt.bucket.recv_bytes() + 4 * W * 8 + 1024 for rt in self.buckets) + max_n * 4 + 65536
         if self.group_size > 1:
             need += sum(rt.bucket.layout.n_total * 4 + 4 * self.group_size * 8 + 1024 for rt in self.buckets)
+        if self.partitioned:
+            need += sum(rt.bucket.recv_bytes() + 2 * W * 8 + 1024 for rt in self.buckets)
         if self.transport == "nccl":
             # library baseline: streams are staged locally and moved by ncclAllGather
             self.pool = symm._alloc_local(need, self.device, 1, 0)
@@ -205,6 +221,15 @@ class SparseDPEngine:
             r_off = pool.take(b.recv_bytes())
             f_off = pool.take(2 * W * 8)
             a_off = pool.take(2 * W * 8)
+            extra = {}
+            if self.partitioned:
+                w_off = pool.take(b.recv_bytes())
+                p_off = pool.take(2 * W * 8)
+                extra = dict(
+                    wb_local=pool.local_view(w_off, b.recv_bytes()), peer_wb=[pool.peer_addr(r, w_off) for r in range(W)],
+                    wb_mc=pool.mc_addr(w_off), pflag_local=pool.local_view(p_off, 2 * W * 8).view(torch.int64),
+                    peer_pflag=[pool.peer_addr(r, p_off) for r in range(W)],
+                )
             b.wire(Wiring(
                 world=W, rank=self.rank,
                 recv_local=pool.local_view(r_off, b.recv_bytes()),
@@ -213,7 +238,7 @@ class SparseDPEngine:
                 peer_flag=[pool.peer_addr(r, f_off) for r in range(W)],
                 ack_local=pool.local_view(a_off, 2 * W * 8).view(torch.int64),
                 peer_ack=[pool.peer_addr(r, a_off) for r in range(W)],
-                recv_mc=pool.mc_addr(r_off), use_flags=True, use_acks=True,
+                recv_mc=pool.mc_addr(r_off), use_flags=True, use_acks=True, **extra,
             ))
             if self.group_size > 1:
                 self._wire_group(rt, r_off)
@@ -399,8 +424,7 @@ class SparseDPEngine:
                 b.handle.group_reduce(s.cuda_stream)
                 self.stats["kernels"] += 3
             if self.shaper is not None and not self._capturing:
-                owned = sum(seg.k for seg in b.layout.segments if not seg.skip)
-                nbytes = owned * 8 * (self.world - self.group_size)        # entries stored into other groups
+                nbytes = b.layout.wire_bytes(owned_only=True) * (self.world - self.group_size)   # stored into other groups
                 self.shaped_bytes += nbytes
                 wait_s = self.shaper.delay_for(nbytes)
                 if wait_s > 0:
@@ -423,7 +447,7 @@ class SparseDPEngine:
         rt.has_pending_apply = False
         rt.apply_count += 1
         self.stats["apply_launches"] += 1
-        self.stats["kernels"] += 2
+        self.stats["kernels"] += rt.bucket.apply_kernels
 
     # ------------------------------------------------------------------ public control
     def synchronize(self) -> None:
@@ -582,6 +606,7 @@ class SparseDPEngine:
             "param_names": self.param_names,
             "buckets": [rt.bucket.state_dict() for rt in self.buckets],
             "world": self.world,
+            "state_partition": "owner" if self.partitioned else "replicated",
         }
 
     def load_state_dict(self, sd: dict) -> None:
@@ -603,6 +628,8 @@ class SparseDPEngine:
                 e = int(sd["iteration"][rt.bucket.index])
                 w.flag_local.fill_(e)
                 w.ack_local.fill_(e)
+                if w.pflag_local is not None:
+                    w.pflag_local.fill_(e)
             torch.cuda.synchronize(self.device)
             dist.barrier(self.group)
 
@@ -614,10 +641,15 @@ class SparseDPEngine:
             raise ValueError("checkpoint was written for a different model or bucket plan")
         for rt, bsd in zip(self.buckets, sd["buckets"]):
             b = rt.bucket
-            for k in ("param", "m", "v", "vmax", "last"):
+            lo, hi = tuple(bsd.get("state_range", (0, b.layout.n_total)))
+            if (lo, hi) != (0, b.layout.n_total):
+                raise ValueError("optimiser state in the checkpoint is a shard: merge the ranks' files first "
+                                 "(utils.checkpoint.load does)")
+            b.param.copy_(bsd["param"])
+            for k in ("m", "v", "vmax", "last"):
                 t = getattr(b, k)
                 if t is not None and k in bsd:
-                    t.copy_(bsd[k])
+                    t[: b.state_hi - b.state_lo].copy_(bsd[k][b.state_lo : b.state_hi])
             b.opt.copy_(bsd["opt"])
             b._opt_host = b.opt.cpu().numpy().view(B.OPT_STATE_DTYPE).copy()
             b.state.copy_(bsd["seg_state"])

@@ -60,6 +60,12 @@ class Wiring:
     recv_mc: int = 0
     use_flags: bool = False
     use_acks: bool = False
+    # partitioned optimiser state: write-back areas (shape of the receive areas) and "values landed" flags
+    wb_local: Optional[torch.Tensor] = None
+    peer_wb: Sequence[int] = ()
+    wb_mc: int = 0
+    pflag_local: Optional[torch.Tensor] = None   # int64 [2][world]
+    peer_pflag: Sequence[int] = ()
 
 
 class GpuBucket:
@@ -82,6 +88,7 @@ class GpuBucket:
         timeout_s: float = 2.0,
         divide_k_by_world: bool = True,
         k_world: Optional[int] = None,
+        partition_state: bool = False,
     ) -> None:
         self.index = index
         self.layout = layout
@@ -98,12 +105,21 @@ class GpuBucket:
         self.grad = torch.zeros(n, **f32)
         self.resid = torch.zeros(n, **f32)
         self.param = torch.zeros(n, **f32)
-        self.acc = torch.zeros(n, **f32)
-        self.stamp = torch.zeros(n, dtype=torch.int32, device=device)
-        self.m = torch.zeros(n, **f32)
-        self.v = torch.zeros(n, **f32) if optimizer == "adam" else None
-        self.vmax = torch.zeros(n, **f32) if (optimizer == "adam" and amsgrad) else None
-        self.last = torch.zeros(n, dtype=torch.int32, device=device) if smart_momentum else None
+        # Accumulator, stamps and optimiser state cover the whole bucket, or with partitioned state only the
+        # contiguous element range of the tensors this rank owns (1/world of the memory).
+        self.partition_state = bool(partition_state) and world > 1
+        if self.partition_state:
+            layout.assign_state_owners(world)
+            self.state_lo, self.state_hi = layout.state_range(rank)
+        else:
+            self.state_lo, self.state_hi = 0, n
+        ns = max(self.state_hi - self.state_lo, B.ALIGN)
+        self.acc = torch.zeros(ns, **f32)
+        self.stamp = torch.zeros(ns, dtype=torch.int32, device=device)
+        self.m = torch.zeros(ns, **f32)
+        self.v = torch.zeros(ns, **f32) if optimizer == "adam" else None
+        self.vmax = torch.zeros(ns, **f32) if (optimizer == "adam" and amsgrad) else None
+        self.last = torch.zeros(ns, dtype=torch.int32, device=device) if smart_momentum else None
 
         layout.set_ratio(ratio, self.k_world)
         self.cap_max = max(layout.max_cap(self.min_ratio, self.k_world), layout.cap, 1)
@@ -168,7 +184,8 @@ class GpuBucket:
             counters=self.counters.data_ptr(), status=self.status.data_ptr(), opt=self.opt.data_ptr(),
             weight=self.weight.data_ptr(), timeout_ns=self.timeout_ns,
         )
-        h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False)
+        h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False,
+                      any(self.layout.is_narrow(s) for s in self.layout.segments))
         if wiring is not None:
             self._apply_wiring(h, wiring)
 
@@ -224,6 +241,14 @@ class GpuBucket:
             ack_local=self._ptr(w.ack_local), peer_ack=list(w.peer_ack), use_flags=w.use_flags,
             use_acks=w.use_acks,
         )
+        if self.partition_state and w.world > 1:
+            if w.wb_local is None or w.pflag_local is None:
+                raise ValueError("partitioned optimiser state needs write-back areas and flags in the wiring")
+            h.set_owner(
+                bounds=self.layout.owner_bounds(w.world), state_base=self.state_lo,
+                state_len=self.state_hi - self.state_lo, wb_local=w.wb_local.data_ptr(), peer_wb=list(w.peer_wb),
+                wb_mc=w.wb_mc, pflag_local=w.pflag_local.data_ptr(), peer_pflag=list(w.peer_pflag),
+            )
 
     # ------------------------------------------------------------------ configuration
     def set_ratio(self, ratio: float) -> None:
@@ -252,9 +277,14 @@ class GpuBucket:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
         (self.select_handle or self.handle).select(s.cuda_stream)
 
-    def apply(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+    def apply(self, stream: Optional[torch.cuda.Stream] = None, phase: int = 0) -> None:
+        """phase 0: the whole chain; 1: scatter + optimiser only; 2: copy of the owners' values only."""
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
-        self.handle.apply(s.cuda_stream)
+        self.handle.apply(s.cuda_stream, phase)
+
+    @property
+    def apply_kernels(self) -> int:
+        return 3 if self.partition_state else 2
 
     def check_status(self) -> None:
         code = int(self.status.item())
@@ -267,12 +297,20 @@ class GpuBucket:
         return buf[s.off : s.off + s.numel]
 
     def stream_of(self, slot: int, src: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """(idx, val) of one received stream, for tests and debugging."""
+        """(idx, val) of one received stream, for tests and debugging; narrow tensors are decoded."""
         cap = self.layout.cap
         w = self.wiring
         pairs = w.recv_local.view(torch.int32)[: 2 * w.world * cap * 2].view(2, w.world, cap, 2)
         e = pairs[slot, src]
-        return e[:, 0].clone(), e[:, 1].clone().view(torch.float32)
+        idx, val = e[:, 0].clone(), e[:, 1].clone().view(torch.float32)
+        for s in self.layout.segments:
+            if self.layout.is_narrow(s) and s.k:
+                # the first s.k 32-bit words of the tensor's region: (relative index : 16 | bf16 value : 16)
+                words = e[s.out_off : s.out_off + s.k].reshape(-1)[: s.k].contiguous()
+                none = words == -1
+                idx[s.out_off : s.out_off + s.k] = torch.where(none, words, (words & 0xFFFF) + s.off)
+                val[s.out_off : s.out_off + s.k] = torch.where(none, torch.zeros_like(words), words & -65536).view(torch.float32)
+        return idx, val
 
     def seg_state(self) -> np.ndarray:
         return self.state.cpu().numpy().view(B.SEG_STATE_DTYPE).copy()
@@ -281,6 +319,7 @@ class GpuBucket:
         d = {
             "resid": self.resid, "param": self.param, "m": self.m, "seg_state": self.state,
             "opt": self.opt, "counters": self.counters, "stamp": self.stamp, "ratio": self.ratio,
+            "state_range": (self.state_lo, self.state_hi),
         }
         for k in ("v", "vmax", "last"):
             t = getattr(self, k)
@@ -289,6 +328,8 @@ class GpuBucket:
         return {k: (v.detach().cpu().clone() if torch.is_tensor(v) else v) for k, v in d.items()}
 
     def load_state_dict(self, d: dict) -> None:
+        if tuple(d.get("state_range", (0, self.layout.n_total))) != (self.state_lo, self.state_hi):
+            raise ValueError("checkpoint was written with a different partition of the optimiser state")
         if abs(d["ratio"] - self.ratio) > 1e-12:
             self.set_ratio(d["ratio"])
         for k in ("resid", "param", "m", "v", "vmax", "last", "stamp", "opt", "counters"):

@@ -6,9 +6,11 @@ Layout of one file per rank, written with ``torch.save``::
 
     {"model": module.state_dict(), "engine": SparseDPEngine.state_dict(), "extra": {...}, "rank": r, "world": W}
 
-Every rank holds the full optimiser state for its replica (state is replicated, as in the reference), so
-rank 0's file alone restores a job of the same world size; ``save(..., all_ranks=True)`` also keeps the
-per-rank residuals, which differ between ranks.
+With replicated optimiser state (the default, as in the reference) every rank holds the full state for its
+replica, so rank 0's file alone restores a job of the same world size; ``save(..., all_ranks=True)`` also keeps
+the per-rank residuals, which differ between ranks.  With partitioned state (``state_partition="owner"``) each
+file holds the moments of the tensors its rank owns; ``merge_state_shards`` reassembles them when a job resumes
+on a different number of ranks.
 """
 from __future__ import annotations
 
@@ -44,6 +46,31 @@ def save(path: str, module: torch.nn.Module, engine, extra: Optional[dict] = Non
     return str(p)
 
 
+def merge_state_shards(engine_sds: list[dict]) -> dict:
+    """One engine ``state_dict`` with full-size moments from the per-rank dicts of a job that ran with
+    partitioned optimiser state.  Every element range is taken from the rank that owned it; parameters,
+    thresholds and step counters are replica-independent and come from the first dict."""
+    out = dict(engine_sds[0])
+    out["buckets"] = []
+    for bi, first in enumerate(engine_sds[0]["buckets"]):
+        merged = dict(first)
+        n = first["param"].numel()
+        for k in ("m", "v", "vmax", "last"):
+            if k not in first:
+                continue
+            full = torch.zeros(n, dtype=first[k].dtype)
+            for sd in engine_sds:
+                b = sd["buckets"][bi]
+                lo, hi = b.get("state_range", (0, n))
+                full[lo:hi] = b[k][: hi - lo]
+            merged[k] = full
+        merged["state_range"] = (0, n)
+        merged.pop("stamp", None)
+        out["buckets"].append(merged)
+    out["state_partition"] = "replicated"
+    return out
+
+
 def load(path: str, module: torch.nn.Module, engine, map_location="cpu", allow_world_change: bool = False) -> dict:
     """``allow_world_change``: resume on a different number of ranks (after losing one, or after growing).
     Parameters, optimiser state and thresholds are replica-independent and are restored; residuals, epochs and
@@ -59,7 +86,16 @@ def load(path: str, module: torch.nn.Module, engine, map_location="cpu", allow_w
         if not allow_world_change:
             raise ValueError(f"checkpoint was written by {ck['world']} ranks, this job has {world}")
         module.load_state_dict(ck["model"], strict=False)
-        engine.load_replica_state(ck["engine"])
+        esd = ck["engine"]
+        if esd.get("state_partition", "replicated") == "owner":
+            base = Path(path)
+            files = [base.with_name(f"{base.stem}.rank{r}{base.suffix}") for r in range(ck["world"])]
+            missing = [str(f) for f in files if not f.exists()]
+            if missing:
+                raise FileNotFoundError(f"partitioned optimiser state needs every rank's file; missing: {missing}")
+            esd = merge_state_shards([torch.load(f, map_location=map_location, weights_only=False)["engine"]
+                                      for f in files])
+        engine.load_replica_state(esd)
         return ck["extra"]
     # buffers (e.g. BatchNorm statistics) come from the model part, parameters from the engine's buckets
     module.load_state_dict(ck["model"], strict=False)

@@ -112,3 +112,24 @@ def test_reference_arm_reports_unavailable():
     out = subprocess.run([sys.executable, "bench.py", "--impl", "reference"], capture_output=True, text=True, timeout=120)
     d = json.loads(out.stdout.strip().splitlines()[-1])
     assert d["impl"] == "reference" and "unavailable" in d
+
+
+def test_merge_state_shards_reassembles_full_moments():
+    import torch
+
+    from stellatrain_b200.utils.checkpoint import merge_state_shards
+
+    n = 64
+    full_m, full_v = torch.arange(n, dtype=torch.float32), torch.arange(n, dtype=torch.float32) * 2
+    ranges = [(0, 16), (16, 48), (48, 48), (48, 64)]
+    sds = []
+    for lo, hi in ranges:
+        pad = max(hi - lo, 16)
+        m, v = torch.zeros(pad), torch.zeros(pad)
+        m[: hi - lo], v[: hi - lo] = full_m[lo:hi], full_v[lo:hi]
+        sds.append({"param_names": [["w"]], "world": 4, "state_partition": "owner",
+                    "buckets": [{"param": torch.ones(n), "m": m, "v": v, "state_range": (lo, hi), "stamp": torch.zeros(pad)}]})
+    out = merge_state_shards(sds)
+    b = out["buckets"][0]
+    assert torch.equal(b["m"], full_m) and torch.equal(b["v"], full_v)
+    assert b["state_range"] == (0, n) and out["state_partition"] == "replicated"

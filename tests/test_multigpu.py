@@ -118,7 +118,7 @@ def test_exchange_equals_dense_data_parallel(transport, multicast):
         assert o["drift"] <= 1e-6, outs      # replicas may differ only by atomic-add rounding order
 
 
-def _worker_sparse_parity(rank, world, compressor, staleness):
+def _worker_sparse_parity(rank, world, compressor, staleness, partition="replicated"):
     import torch.nn.functional as F
 
     from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
@@ -129,7 +129,8 @@ def _worker_sparse_parity(rank, world, compressor, staleness):
             for p in model.parameters():
                 p.add_(1.0)
     eng = SparseDPEngine(model, EngineConfig(compressor=compressor, ratio=0.9, optimizer="adam", staleness=staleness,
-                                             bucket_mb=0.02, chunk_elems=1024, optimizer_options={"lr": 1e-2}))
+                                             bucket_mb=0.02, chunk_elems=1024, optimizer_options={"lr": 1e-2},
+                                             state_partition=partition))
     first = None
     for x, y in _data(rank, 30):
         loss = F.cross_entropy(model(x), y)
@@ -138,8 +139,12 @@ def _worker_sparse_parity(rank, world, compressor, staleness):
     eng.synchronize()
     eng.check_status()
     drift = eng.replica_drift()
+    state_elems = sum(rt.bucket.m.numel() for rt in eng.buckets)
+    total_elems = sum(rt.bucket.layout.n_total for rt in eng.buckets)
+    checksum = float(sum(p.detach().double().sum() for p in model.parameters()))
     eng.close()
-    return {"drift": drift, "first": first, "last": float(loss.detach())}
+    return {"drift": drift, "first": first, "last": float(loss.detach()), "state_elems": state_elems,
+            "total_elems": total_elems, "checksum": checksum}
 
 
 @pytest.mark.parametrize("compressor", ["thresholdv16", "topk", "thresholdv"])
@@ -150,6 +155,25 @@ def test_sparse_replicas_stay_in_sync(compressor, staleness):
     for o in outs:
         assert o["drift"] <= 1e-5, outs
         assert o["first"] == pytest.approx(outs[0]["first"], rel=0.5)
+
+
+@pytest.mark.parametrize("multicast", [True, False])
+@pytest.mark.parametrize("staleness", [0, 1])
+def test_partitioned_optimizer_state(staleness, multicast):
+    """Every tensor's optimiser state on one rank; owners store the new values into all replicas."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    env = {} if multicast else {"STELLATRAIN_NVLS": "0"}
+    par = _spawn(_worker_sparse_parity, world, "thresholdv16", staleness, "owner", env=env)
+    rep = _spawn(_worker_sparse_parity, world, "thresholdv16", staleness, "replicated", env=env)
+    for o in par:
+        assert o["drift"] == 0.0, par                      # values are copied from the owner, never recomputed
+        assert o["state_elems"] < o["total_elems"], par
+    assert sum(o["state_elems"] for o in par) <= par[0]["total_elems"] + 16 * world * 8
+    # same training trajectory as with replicated state, up to the order of floating-point additions
+    assert par[0]["checksum"] == pytest.approx(rep[0]["checksum"], rel=1e-4, abs=1e-3)
+    assert par[0]["last"] == pytest.approx(rep[0]["last"], rel=1e-2, abs=1e-3)
 
 
 def _worker_grouped(rank, world, group_size, sparse):
