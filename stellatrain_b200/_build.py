@@ -168,6 +168,28 @@ def load_extension(name: str, build_if_missing: bool = True):
     return mod
 
 
+def build_selftest(sanitizer: str = "thread", out_dir: Path | None = None) -> Path:
+    """Stand-alone exerciser of the CPU tier (``csrc/selftest/cpu_selftest.cpp``) linked with a sanitizer runtime:
+    ``thread`` (TSAN), ``address`` (ASAN + UBSAN) or ``none``.  The reference has no such target."""
+    out_dir = Path(out_dir) if out_dir is not None else OBJ_DIR
+    out_dir.mkdir(parents=True, exist_ok=True)
+    flags = {"thread": ["-fsanitize=thread"], "address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"],
+             "none": []}[sanitizer]
+    srcs = [s for s in EXTENSIONS["_Ccpu"]["cpp"] if not s.startswith("bindings") and not s.startswith("telemetry")]
+    srcs.append("selftest/cpu_selftest.cpp")
+    exe = out_dir / f"cpu_selftest_{sanitizer}"
+    base = [f for f in CXX_FLAGS if f not in ("-O3", "-fvisibility=hidden")] + ["-O1", "-g", "-fno-omit-frame-pointer"]
+    objs, jobs = [], []
+    for s in srcs:
+        obj = out_dir / (f"selftest_{sanitizer}_" + s.replace("/", "_") + ".o")
+        jobs.append(["g++", *base, *flags, f"-I{CSRC}", "-c", str(CSRC / s), "-o", str(obj)])
+        objs.append(obj)
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+        list(ex.map(_run, jobs))
+    _run(["g++", *flags, "-o", str(exe), *map(str, objs), "-pthread", "-lrt", "-ldl"])
+    return exe
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     for name in EXTENSIONS:
         if _existing(name)["cu"] or _existing(name)["cpp"]:

@@ -1,0 +1,179 @@
+// Stand-alone exerciser of the CPU tier for the sanitizers (no Python, no CUDA).
+//
+// Built by stellatrain_b200/_build.py::build_selftest with -fsanitize=thread or -fsanitize=address and run
+// by tests/test_sanitizers.py.  The reference has no sanitizer target (its CMake build knows only
+// -march=broadwell, backend/CMakeLists.txt:28-29) and its barrier code loses wake-ups; here the thread
+// pool, the task pipeline with both staleness settings, gradient accumulation and a two-node ring over
+// loopback TCP (two engines on two threads of this process) all run under the race detector.
+#include <unistd.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../core/engine.h"
+#include "../core/threadpool.h"
+#include "../cpu/compressors.h"
+#include "../cpu/optimizers.h"
+
+using namespace stc;
+
+namespace {
+
+#define CHECK(cond)                                                                          \
+  do {                                                                                       \
+    if (!(cond)) throw std::runtime_error(std::string("check failed: ") + #cond + " at line " + std::to_string(__LINE__)); \
+  } while (0)
+
+void test_pool() {
+  ThreadPool pool(4);
+  std::atomic<int> sum{0};
+  std::vector<std::future<void>> futs;
+  for (int i = 0; i < 200; ++i) futs.push_back(pool.enqueue(i % 7, [&sum, i] { sum += i; }));
+  for (auto& f : futs) f.get();
+  CHECK(sum == 199 * 200 / 2);
+  // nested parallel_for from inside a worker must not deadlock
+  std::vector<int> hits(1 << 16, 0);
+  auto outer = pool.enqueue(0, [&] {
+    pool.parallel_for(hits.size(), 1024, [&](size_t b, size_t e) {
+      for (size_t i = b; i < e; ++i) hits[i] += 1;
+    });
+  });
+  outer.get();
+  for (int h : hits) CHECK(h == 1);
+}
+
+void test_kernels() {
+  ThreadPool pool(3);
+  const size_t n = 100000;
+  std::vector<float> a(n);
+  uint32_t s = 12345;
+  for (auto& x : a) { s = s * 1664525u + 1013904223u; x = (static_cast<float>(s >> 8) / 8388608.0f - 1.0f) * 1e-2f; }
+  for (const char* method : {"topk", "thresholdv", "thresholdv16", "randomk"}) {
+    auto c = make_compressor(method, &pool);
+    const uint32_t k = 1000;
+    std::vector<uint32_t> idx(k);
+    std::vector<float> val(k);
+    for (int rep = 0; rep < 3; ++rep) {
+      const size_t got = c->compress("t", a.data(), n, k, idx.data(), val.data(), 0);
+      // threshold-v may under-fill, down to nothing, while its threshold adapts (as the reference's does)
+      if (!(got <= k && (got > 0 || std::string(method) == "thresholdv")))
+        throw std::runtime_error(std::string(method) + " returned " + std::to_string(got) + " pairs for k = " + std::to_string(k));
+      for (size_t j = 0; j < got; ++j) CHECK(idx[j] < n && val[j] == a[idx[j]]);
+    }
+  }
+  for (const char* kind : {"sgd", "adam"}) {
+    auto o = make_optimizer(kind);
+    o->configure("lr", 0.1f);
+    std::vector<float> p(1000, 1.0f), g(10, 0.5f);
+    std::vector<uint32_t> idx = {1, 5, 9, 100, 200, 300, 400, 500, 600, 999};
+    o->optimize_raw(p.data(), 1000, "w", g.data(), idx.data(), 10);
+    CHECK(p[1] < 1.0f && p[2] == 1.0f);
+  }
+}
+
+struct Node {
+  CpuEngine engine;
+  std::vector<std::vector<float>> params;
+  std::vector<int> index;
+};
+
+void run_node(Node& node, EngineOptions opt, int iters, std::string* error) {
+  try {
+    node.engine.configure(opt);
+    node.engine.set_optimizer("adam");
+    node.engine.sparse_optimizer()->configure("lr", 1e-2f);
+    const std::vector<uint32_t> sizes = {4096, 17, 70000, 300, 1};
+    node.params.resize(sizes.size());
+    for (size_t i = 0; i < sizes.size(); ++i) {
+      node.params[i].assign(sizes[i], 0.5f);
+      node.index.push_back(node.engine.pre_train_init(static_cast<int>(i), "p" + std::to_string(i), sizes[i], node.params[i].data()));
+    }
+    std::vector<float> grad;
+    for (int it = 0; it < iters; ++it) {
+      for (size_t i = 0; i < sizes.size(); ++i) node.engine.pre_forward_process(node.index[i]);        // forward
+      for (int micro = 0; micro < opt.grad_accumulation; ++micro)
+        for (size_t r = sizes.size(); r-- > 0;) {                                                      // backward
+          grad.assign(sizes[r], 0.f);
+          for (uint32_t j = 0; j < sizes[r]; ++j)
+            grad[j] = 1e-3f * static_cast<float>(((j * 2654435761u) >> 20) % 97 + 1) * (opt.rank + 1);
+          node.engine.post_backward_process(node.index[r], grad.data());
+        }
+    }
+    node.engine.synchronize();
+    for (size_t i = 0; i < sizes.size(); ++i) {
+      CHECK(node.engine.model_version(node.index[i]) == iters);
+      bool moved = false;
+      for (float x : node.params[i]) { CHECK(std::isfinite(x)); moved |= x != 0.5f; }
+      CHECK(moved);
+    }
+  } catch (const std::exception& e) {
+    *error = e.what();
+  }
+}
+
+void test_single_node(int staleness, int accumulation, const char* method) {
+  Node node;
+  EngineOptions o;
+  o.session = static_cast<int64_t>(getpid()) * 100 + staleness * 10 + accumulation;
+  o.staleness = staleness;
+  o.grad_accumulation = accumulation;
+  o.method = method;
+  o.ratio = 0.9;
+  o.workers = 4;
+  o.data_bytes = 16u << 20;
+  o.timeout_ms = 20000;
+  std::string err;
+  run_node(node, o, 12, &err);
+  if (!err.empty()) throw std::runtime_error(std::string("single node (") + method + "): " + err);
+}
+
+void test_two_nodes(uint16_t port) {
+  Node nodes[2];
+  std::string errs[2];
+  std::thread th[2];
+  for (int r = 0; r < 2; ++r) {
+    EngineOptions o;
+    o.master_port = port;
+    o.world = 2;
+    o.rank = r;
+    o.session = static_cast<int64_t>(getpid()) * 100 + 50 + r;
+    o.staleness = 1;
+    o.method = "thresholdv16";
+    o.ratio = 0.9;
+    o.workers = 4;
+    o.data_bytes = 16u << 20;
+    o.timeout_ms = 20000;
+    th[r] = std::thread([&nodes, &errs, o, r] { run_node(nodes[r], o, 10, &errs[r]); });
+  }
+  for (auto& t : th) t.join();
+  for (int r = 0; r < 2; ++r)
+    if (!errs[r].empty()) throw std::runtime_error("two nodes, rank " + std::to_string(r) + ": " + errs[r]);
+  // both nodes applied the same merged updates to the same start values
+  for (size_t i = 0; i < nodes[0].params.size(); ++i)
+    for (size_t j = 0; j < nodes[0].params[i].size(); ++j) CHECK(nodes[0].params[i][j] == nodes[1].params[i][j]);
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  const uint16_t port = argc > 1 ? static_cast<uint16_t>(std::atoi(argv[1])) : 45123;
+  try {
+    test_pool();
+    test_kernels();
+    test_single_node(0, 1, "topk");
+    test_single_node(1, 1, "thresholdv16");
+    test_single_node(1, 2, "thresholdv");
+    test_two_nodes(port);
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "selftest FAILED: %s\n", e.what());
+    return 1;
+  }
+  std::printf("selftest ok\n");
+  return 0;
+}

@@ -47,9 +47,14 @@ def _step(ranks, grads):
         b.apply(phase=2)
 
 
-def _grads(world, n, step, dev):
+def _grads(world, layout, step, dev):
+    """One flat gradient per rank; the padding behind every tensor stays zero, as the engine keeps it."""
+    n = layout.n_total
     g = torch.Generator(device=dev).manual_seed(1000 * step + 1)
-    return [torch.randn(n, device=dev, generator=g) * 1e-2 for _ in range(world)]
+    valid = torch.zeros(n, device=dev)
+    for s in layout.segments:
+        valid[s.off : s.off + s.numel] = 1.0
+    return [torch.randn(n, device=dev, generator=g) * 1e-2 * valid for _ in range(world)]
 
 
 @pytest.mark.parametrize("narrow", [False, True])
@@ -60,14 +65,14 @@ def test_topk_adam_matches_dense_restatement(partition, narrow):
     dev = torch.device("cuda:0")
     world, ratio, lr = 4, 0.9, 1e-2
     ranks = _make_ranks(world, NUMELS, "topk", "adam", partition, ratio, dev, lr, narrow=narrow)
-    L = ranks[0].layout
+    L = LAY = ranks[0].layout
     n = L.n_total
     x = ranks[0].param.double().clone()
     resid = [torch.zeros(n, device=dev) for _ in range(world)]    # fp32 like the device: selection must see equal keys
     m = torch.zeros(n, dtype=torch.float64, device=dev)
     v = torch.zeros(n, dtype=torch.float64, device=dev)
     for step in range(1, 6):
-        grads = _grads(world, n, step, dev)
+        grads = _grads(world, LAY, step, dev)
         _step(ranks, grads)
         merged = torch.zeros(n, dtype=torch.float64, device=dev)
         touched = torch.zeros(n, dtype=torch.bool, device=dev)
@@ -117,9 +122,9 @@ def test_partitioned_state_equals_replicated(compressor, optimizer):
     world = 4
     rep = _make_ranks(world, NUMELS, compressor, optimizer, False, 0.9, dev)
     par = _make_ranks(world, NUMELS, compressor, optimizer, True, 0.9, dev)
-    n = rep[0].layout.n_total
+    LAY = rep[0].layout
     for step in range(1, 9):
-        grads = _grads(world, n, step, dev)
+        grads = _grads(world, LAY, step, dev)
         _step(rep, grads)
         _step(par, grads)
         if step == 4:                       # a change of the compression ratio moves the owners' entry ranges
@@ -143,9 +148,9 @@ def test_ranks_that_own_nothing():
     par = _make_ranks(world, numels, "topk", "adam", True, 0.9, dev)
     owners = [s.owner for s in par[0].layout.segments]
     assert len(set(owners)) < world
-    n = rep[0].layout.n_total
+    LAY = rep[0].layout
     for step in range(1, 5):
-        grads = _grads(world, n, step, dev)
+        grads = _grads(world, LAY, step, dev)
         _step(rep, grads)
         _step(par, grads)
     torch.cuda.synchronize()
