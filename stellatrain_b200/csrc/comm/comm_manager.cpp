@@ -74,6 +74,8 @@ CommManager::~CommManager() {
     send_frame(control_fd_, kBye, "", 0, nullptr, 0, 200);
   }
   if (push_thread_.joinable()) push_thread_.join();
+  // tell the ring successor that the silence that follows is a regular shutdown, not a lost node
+  if (push_fd_ >= 0 && !failed_) send_frame(push_fd_, kBye, "", 0, nullptr, 0, 200);
   if (pull_thread_.joinable()) pull_thread_.join();
   close_fd(push_fd_);
   close_fd(pull_fd_);
@@ -351,6 +353,10 @@ void CommManager::pull_main() {
     std::vector<unsigned char> payload;
     if (!recv_frame(pull_fd_, &h, &key, &payload, timeout_ms_)) {
       if (!stop_) set_failed("the ring predecessor closed the connection or sent a truncated frame");
+      return;
+    }
+    if (h.type == kBye) {
+      LOG_DEBUG("CommManager", "the ring predecessor shut down");
       return;
     }
     if (h.type != kGrad || payload.size() < 4) continue;
