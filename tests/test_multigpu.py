@@ -118,7 +118,7 @@ def test_exchange_equals_dense_data_parallel(transport, multicast):
         assert o["drift"] <= 1e-6, outs      # replicas may differ only by atomic-add rounding order
 
 
-def _worker_sparse_parity(rank, world, compressor, staleness, partition="replicated"):
+def _worker_sparse_parity(rank, world, compressor, staleness, partition="replicated", wire="wide"):
     import torch.nn.functional as F
 
     from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
@@ -130,7 +130,7 @@ def _worker_sparse_parity(rank, world, compressor, staleness, partition="replica
                 p.add_(1.0)
     eng = SparseDPEngine(model, EngineConfig(compressor=compressor, ratio=0.9, optimizer="adam", staleness=staleness,
                                              bucket_mb=0.02, chunk_elems=1024, optimizer_options={"lr": 1e-2},
-                                             state_partition=partition))
+                                             state_partition=partition, wire_format=wire))
     first = None
     for x, y in _data(rank, 30):
         loss = F.cross_entropy(model(x), y)
@@ -174,6 +174,21 @@ def test_partitioned_optimizer_state(staleness, multicast):
     # same training trajectory as with replicated state, up to the order of floating-point additions
     assert par[0]["checksum"] == pytest.approx(rep[0]["checksum"], rel=1e-4, abs=1e-3)
     assert par[0]["last"] == pytest.approx(rep[0]["last"], rel=1e-2, abs=1e-3)
+
+
+@pytest.mark.parametrize("partition", ["replicated", "owner"])
+def test_narrow_wire_format(partition):
+    """4-byte entries (u16 index, bf16 value) for tensors below 65536 elements; the rounding error stays in the
+    sender's residual, so training follows the wide format closely."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    narrow = _spawn(_worker_sparse_parity, world, "topk", 1, partition, "narrow")
+    wide = _spawn(_worker_sparse_parity, world, "topk", 1, partition, "wide")
+    for o in narrow:
+        assert o["drift"] <= (0.0 if partition == "owner" else 1e-5), narrow
+    assert narrow[0]["last"] == pytest.approx(wide[0]["last"], rel=5e-2, abs=5e-3)
+    assert narrow[0]["checksum"] == pytest.approx(wide[0]["checksum"], rel=1e-3, abs=5e-2)
 
 
 def _worker_grouped(rank, world, group_size, sparse):
