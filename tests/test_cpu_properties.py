@@ -1,0 +1,109 @@
+"""Property tests (hypothesis) of the CPU-tier kernels: invariants that must hold for every input, not
+just for the sizes the example-based tests pick."""
+import numpy as np
+import pytest
+import torch
+
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+from stellatrain_b200 import cpu_tier   # noqa: E402
+
+ext = cpu_tier._load()
+
+values = st.one_of(
+    st.floats(min_value=-4.0, max_value=4.0, allow_nan=False, width=32),
+    st.sampled_from([0.0, -0.0, 1.0, -1.0, 0.5, 1e-38, -1e-38, 3.0e38]),      # ties, zeros, a denormal-range and a huge value
+)
+
+
+@st.composite
+def problem(draw, max_n=3000):
+    n = draw(st.integers(min_value=1, max_value=max_n))
+    k = draw(st.integers(min_value=1, max_value=n))
+    seed = draw(st.integers(min_value=0, max_value=2**31 - 1))
+    special = draw(st.lists(values, min_size=0, max_size=min(n, 40)))
+    rng = np.random.default_rng(seed)
+    x = (rng.standard_normal(n) * 1e-2).astype(np.float32)
+    if draw(st.booleans()):
+        x = np.round(x * 200) / 200                      # heavy ties
+    pos = rng.permutation(n)[: len(special)]
+    x[pos] = np.array(special, dtype=np.float32)
+    return torch.from_numpy(x.astype(np.float32)), k
+
+
+def _compress(method, name, grad, resid, k):
+    n = grad.numel()
+    comp = ext.Compressor(method)
+    idx = torch.full((k,), -1, dtype=torch.int32)
+    val = torch.zeros(k)
+    out = []
+    for _ in range(2):        # second call runs with the adapted threshold
+        g = grad.clone()
+        before = resid.clone()
+        cnt = comp.compress_with_feedback(name, g.data_ptr(), resid.data_ptr(), n, k, idx.data_ptr(), val.data_ptr())
+        out.append((cnt, idx[:cnt].long().clone(), val[:cnt].clone(), before, resid.clone()))
+    return out
+
+
+@settings(max_examples=60, deadline=None)
+@given(problem())
+def test_selection_invariants(p):
+    grad, k = p
+    n = grad.numel()
+    for method in ("topk", "thresholdv", "thresholdv16"):
+        resid = torch.zeros(n)
+        for cnt, idx, val, before, after in _compress(method, "t", grad, resid, k):
+            a = grad + before
+            assert 0 <= cnt <= k
+            assert idx.numel() == idx.unique().numel(), "an index was sent twice"
+            assert bool((idx >= 0).all()) and bool((idx < n).all())
+            assert torch.equal(val, a[idx]), "sent values are the accumulated gradient at the sent indices"
+            # mass conservation: every element is either sent or kept, bit for bit
+            kept = a.clone()
+            kept[idx] = 0.0
+            assert torch.equal(after, kept)
+            if method == "topk":
+                assert cnt == k
+                rest = kept.abs()
+                assert float(val.abs().min()) >= float(rest.max()), "something larger than a sent element stayed behind"
+            if method == "thresholdv16":
+                # whole blocks are taken; only the zero padding of the tensor's last block is left out
+                assert k - 15 <= cnt <= k, "threshold-v16 fills the stream"
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 5), st.integers(1, 400), st.integers(0, 2**31 - 1))
+def test_merge_equals_dense_sum(world, n, seed):
+    rng = np.random.default_rng(seed)
+    idxs, vals, cnts, dense = [], [], [], np.zeros(n, dtype=np.float64)
+    weights = rng.random(world).astype(np.float32)
+    for w in range(world):
+        c = int(rng.integers(0, n + 1))
+        i = torch.from_numpy(rng.permutation(n)[:c].astype(np.int32))
+        v = torch.from_numpy(rng.standard_normal(c).astype(np.float32))
+        idxs.append(i); vals.append(v); cnts.append(c)
+        dense[i.numpy()] += (v.numpy() * weights[w]).astype(np.float32)
+    keep = [t if t.numel() else torch.zeros(1, dtype=t.dtype) for t in idxs + vals]          # valid pointers for empty streams
+    got_i, got_v = ext.merge_streams([t.data_ptr() for t in keep[:world]], [t.data_ptr() for t in keep[world:]], cnts,
+                                     [float(x) for x in weights], n)
+    touched = sorted(set(np.concatenate([i.numpy() for i in idxs]).tolist())) if sum(cnts) else []
+    assert sorted(got_i) == touched, "the merge returns the union of the indices, each once"
+    for i, v in zip(got_i, got_v):
+        assert v == pytest.approx(dense[i], rel=1e-5, abs=1e-6)
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.integers(0, 65535), min_size=1, max_size=300), st.lists(values, min_size=1, max_size=300))
+def test_wire_casts_roundtrip(indices, vals):
+    idx = torch.tensor(indices, dtype=torch.int32)
+    n16 = torch.empty(len(indices), dtype=torch.int16); back = torch.empty(len(indices), dtype=torch.int32)
+    ext.narrow_u32_to_u16(idx.data_ptr(), n16.data_ptr(), len(indices))
+    ext.widen_u16_to_u32(n16.data_ptr(), back.data_ptr(), len(indices))
+    assert torch.equal(idx, back)
+    x = torch.tensor(vals, dtype=torch.float32)
+    h = torch.empty(len(vals), dtype=torch.int16); y = torch.empty(len(vals))
+    ext.f32_to_bf16(x.data_ptr(), h.data_ptr(), len(vals)); ext.bf16_to_f32(h.data_ptr(), y.data_ptr(), len(vals))
+    assert torch.equal(y, x.bfloat16().float())
+    ext.f32_to_f16(x.data_ptr(), h.data_ptr(), len(vals)); ext.f16_to_f32(h.data_ptr(), y.data_ptr(), len(vals))
+    assert torch.equal(y, x.half().float())
