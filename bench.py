@@ -134,6 +134,12 @@ def main() -> None:
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return
 
+    # Libraries (NCCL's version banner, for one) write to the process's stdout; the contract is ONE JSON
+    # line there, so everything but that line goes to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -360,7 +366,8 @@ def main() -> None:
             },
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,
         }
-        print(json.dumps(out))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(out) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

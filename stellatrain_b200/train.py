@@ -38,6 +38,8 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
         st.configure(master_addr, master_port, world_size, rank, master_pid, local_world_size, local_rank,
                      args.compressor, args.gradient_accumulation, staleness=args.staleness)
         st.configure_compression_ratio(args.compression)
+        st.state().engine_cfg.state_partition = args.state_partition
+        st.state().engine_cfg.wire_format = args.wire_format
         st.set_optimizer(args.optim)
         # linear scaling rule of the reference driver (test_end_to_end.py:48-52)
         lr = args.lr / 256.0 * global_world * args.batch_size if args.scale_lr else args.lr
@@ -79,6 +81,25 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
         hook = TelemetryHook(net.engine, args.telemetry_uri, args.batch_size)
 
     meter, global_step, t_start = AverageMeter(), 0, time.time()
+    if args.resume and args.tier == "gpu":
+        from stellatrain_b200.utils import checkpoint
+
+        net._ensure_engine()
+        extra = checkpoint.load(args.resume, net.module, net.engine, allow_world_change=args.allow_world_change)
+        global_step = int(extra.get("global_step", 0))
+        if global_rank == 0:
+            print(f"resumed from {args.resume} at iteration {global_step}", flush=True)
+    monitor = None
+    if args.heartbeat and global_world > 1:
+        import datetime
+
+        from torch.distributed import TCPStore
+
+        from stellatrain_b200.parallel.heartbeat import HeartbeatMonitor
+
+        store = TCPStore(master_addr, master_port + 7, global_world, is_master=(global_rank == 0),
+                         timeout=datetime.timedelta(seconds=60), wait_for_workers=False)
+        monitor = HeartbeatMonitor(store, global_rank, global_world, interval_s=args.heartbeat / 4.0, timeout_s=args.heartbeat)
     for epoch in range(args.num_epochs):
         loader = st.StellaTrainDataLoader(D.PrefetchLoader(base, dev if dev.type == "cuda" else None,
                                                            channels_last=args.channels_last and not lm),
@@ -100,6 +121,15 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
                 ctx.__exit__(None, None, None)
             if loader.is_eoi:
                 global_step += 1
+                if monitor is not None:
+                    # between steps, before kernels that would wait for a missing peer are launched; a lost
+                    # peer ends this job with PeerLostError, the survivors restart from the last checkpoint
+                    # with --resume --allow-world-change
+                    monitor.check()
+                if args.checkpoint and args.checkpoint_every and args.tier == "gpu" and global_step % args.checkpoint_every == 0:
+                    from stellatrain_b200.utils import checkpoint
+
+                    checkpoint.save(args.checkpoint, net.module, net.engine, {"global_step": global_step})
                 if global_step % args.log_every == 0:
                     meter.update(float(loss.detach()))
                     if global_rank == 0:
@@ -112,6 +142,8 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
         from stellatrain_b200.utils import checkpoint
 
         checkpoint.save(args.checkpoint, net.module, net.engine, {"global_step": global_step})
+    if monitor is not None:
+        monitor.announce_leave()
     if global_rank == 0:
         print(f"done: {global_step} iterations in {time.time() - t_start:.1f} s", flush=True)
     if args.tier == "gpu":
@@ -146,7 +178,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--gradient-accumulation", type=int, default=1)
     p.add_argument("--channels-last", action="store_true")
     p.add_argument("--telemetry-uri", default=None)
-    p.add_argument("--checkpoint", default=None)
+    p.add_argument("--checkpoint", default=None, help="written at the end and every --checkpoint-every iterations")
+    p.add_argument("--checkpoint-every", type=int, default=0)
+    p.add_argument("--resume", default=None, help="checkpoint to start from")
+    p.add_argument("--allow-world-change", action="store_true", help="resume on a different number of ranks")
+    p.add_argument("--heartbeat", type=float, default=0.0, help="seconds of silence after which a rank counts as lost (0: off)")
+    p.add_argument("--state-partition", default="replicated", choices=["replicated", "owner"])
+    p.add_argument("--wire-format", default="wide", choices=["wide", "narrow"])
     p.add_argument("--log-every", type=int, default=10)
     return p
 

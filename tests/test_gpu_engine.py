@@ -245,3 +245,21 @@ def test_wrapper_and_module_api():
     assert idx.numel() == 100 and val.numel() == 100 and idx.dtype == torch.int32
     assert st.force_model_sync(0, "x", True) == 0.0
     st.detach()
+
+
+def test_train_driver_checkpoints_and_resumes(tmp_path):
+    """The driver on the GPU tier: periodic checkpoint, then a second run that resumes from it."""
+    import subprocess
+    import sys
+
+    ck = str(tmp_path / "ck.pt")
+    base = [sys.executable, "-m", "stellatrain_b200.train", "--tier", "gpu", "--model", "resnet18", "--dataset", "dummy",
+            "--num-epochs", "1", "--dummy-length", "8", "--batch-size", "4", "--local-world-size", "1", "--compression", "0.9",
+            "--num-classes", "10", "--log-every", "1", "--optim", "adam", "--lr", "1e-3", "--checkpoint", ck]
+    first = subprocess.run(base + ["--num-iters", "4", "--checkpoint-every", "2"], capture_output=True, text=True, timeout=600)
+    assert first.returncode == 0, first.stderr[-3000:]
+    assert "done: 4 iterations" in first.stdout
+    second = subprocess.run(base + ["--num-iters", "6", "--resume", ck], capture_output=True, text=True, timeout=600)
+    assert second.returncode == 0, second.stderr[-3000:]
+    assert "resumed from" in second.stdout and "at iteration 4" in second.stdout
+    assert "done: 6 iterations" in second.stdout
