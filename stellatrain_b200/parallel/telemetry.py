@@ -132,9 +132,10 @@ class TelemetryHook:
             gap = e["prev_b1"].elapsed_time(e["f0"]) if self._have_prev else 0.0
             e["prev_b1"], e["b1"] = e["b1"], e["prev_b1"]
             self._have_prev = True
-            entries = sum(rt.bucket.layout.cap for rt in self.engine.buckets)
+            # bytes this rank stored into one peer (4-byte entries for tensors on the narrow wire format)
+            nbytes = sum(rt.bucket.layout.wire_bytes() for rt in self.engine.buckets) * self.bytes_per_entry / 8.0
             step_ms = max(fwd + bwd + gap, 1e-3)
-            mbps = entries * self.bytes_per_entry * 8.0 * max(self.engine.world - 1, 0) / (step_ms * 1000.0)
+            mbps = nbytes * 8.0 * max(self.engine.world - 1, 0) / (step_ms * 1000.0)
             self.last = {"fwd_delay_ms": fwd, "bwd_delay_ms": bwd, "bwd_fwd_gap_ms": gap, "intra_fwd_gap_ms": 0.0,
                          "grad_send_thpt_mbps": mbps, "grad_recv_thpt_mbps": mbps}
             if self.client is not None and self.client.alive():

@@ -263,3 +263,93 @@ def test_train_driver_checkpoints_and_resumes(tmp_path):
     assert second.returncode == 0, second.stderr[-3000:]
     assert "resumed from" in second.stdout and "at iteration 4" in second.stdout
     assert "done: 6 iterations" in second.stdout
+
+
+def test_telemetry_hook_reports_to_the_controller_and_applies_instructions():
+    """Closed loop on one GPU: device-timed measurements reach the controller through the native client, and an
+    instruction takes effect at its effective iteration (batch size and compression ratio)."""
+    import time
+
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from stellatrain_b200 import cpu_tier
+    from stellatrain_b200.control.controller import Controller
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+    from stellatrain_b200.parallel.telemetry import TelemetryHook
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 8)).cuda()
+    eng = SparseDPEngine(model, EngineConfig(compressor="topk", ratio=0.9, min_ratio=0.5, optimizer="sgd", staleness=1,
+                                             bucket_mb=0.01, chunk_elems=1024, optimizer_options={"lr": 0.05}))
+    ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
+    try:
+        srv = cpu_tier._load().TelemetryServer(f"127.0.0.1:{ctl.port}", False, 5000)
+        srv.send_global_telemetry(1, 1, [p.numel() for p in model.parameters()], False, False)
+        hook = TelemetryHook(eng, f"127.0.0.1:{ctl.port}", batch_size=16)
+        x, y = torch.randn(16, 32, device="cuda"), torch.randint(0, 8, (16,), device="cuda")
+        for it in range(30):
+            xb, yb = hook.resize_batch(x, y)
+            with hook.step() as marker:
+                loss = F.cross_entropy(model(xb), yb)
+                marker.backward_begins()
+                loss.backward()
+            if it == 5:
+                hook._on_instruction(since=10, ubatch=24, grad_acc=1, ratio=0.8)    # what the client's callback delivers
+            if it == 12:
+                assert xb.shape[0] == 24 and eng.cfg.ratio == pytest.approx(0.8)
+        eng.synchronize()
+        assert hook.applied == [(10, 24, 0.8)]
+        assert hook.last["fwd_delay_ms"] > 0.0 and hook.last["bwd_delay_ms"] > 0.0
+        deadline = time.time() + 5.0
+        while ctl.latest_iter < 20 and time.time() < deadline:
+            time.sleep(0.05)
+        assert ctl.latest_iter >= 20, "reports did not reach the controller"
+        assert len(ctl.scoreboard) == 1 and float(ctl.scoreboard.iloc[0]["bwd_ms"]) > 0.0
+    finally:
+        ctl.close()
+        eng.close()
+
+
+def test_checkpoint_module_roundtrip_and_world_change(tmp_path):
+    """utils.checkpoint on one GPU: save, load into a fresh replica, continue; a file that claims another world
+    size is refused unless allow_world_change is given, and then restores parameters and moments only."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+    from stellatrain_b200.utils import checkpoint
+
+    def make():
+        torch.manual_seed(3)
+        m = nn.Sequential(nn.Linear(24, 48), nn.ReLU(), nn.Linear(48, 6)).cuda()
+        return m, SparseDPEngine(m, EngineConfig(compressor="thresholdv16", ratio=0.9, optimizer="adam", staleness=0,
+                                                 bucket_mb=0.01, chunk_elems=1024, optimizer_options={"lr": 1e-2}))
+
+    x, y = torch.randn(32, 24, device="cuda"), torch.randint(0, 6, (32,), device="cuda")
+    m1, e1 = make()
+    for _ in range(5):
+        F.cross_entropy(m1(x), y).backward()
+    path = checkpoint.save(str(tmp_path / "ck.pt"), m1, e1, {"global_step": 5})
+    m2, e2 = make()
+    assert checkpoint.load(path, m2, e2)["global_step"] == 5
+    for p, q in zip(m1.parameters(), m2.parameters()):
+        assert torch.equal(p, q)
+    assert torch.equal(e1.buckets[0].bucket.resid, e2.buckets[0].bucket.resid)
+    # a checkpoint from a job of another size
+    ck = torch.load(path, weights_only=False)
+    ck["world"] = ck["engine"]["world"] = 4
+    other = str(tmp_path / "ck4.pt")
+    torch.save(ck, other)
+    m3, e3 = make()
+    with pytest.raises(ValueError):
+        checkpoint.load(other, m3, e3)
+    checkpoint.load(other, m3, e3, allow_world_change=True)
+    for p, q in zip(m1.parameters(), m3.parameters()):
+        assert torch.equal(p, q)
+    assert torch.equal(e3.buckets[0].bucket.m, e1.buckets[0].bucket.m)
+    assert float(e3.buckets[0].bucket.resid.abs().max()) == 0.0        # residuals belong to the old world
+    F.cross_entropy(m3(x), y).backward()
+    e3.synchronize()
+    for e in (e1, e2, e3):
+        e.close()
