@@ -29,7 +29,7 @@ import time
 
 REFERENCE_UNAVAILABLE = (
     "reference is a CMake project without setup.py/pyproject.toml: `pip install --no-index "
-    "--no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref /root/reference` fails with "
+    "--no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref <reference tree>` fails with "
     "\"Neither 'setup.py' nor 'pyproject.toml' found\"; it also ships no GPU kernels and no NCCL path"
 )
 

@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(kThreads) k_plan(SelectArgs A) {
 // ------------------------------------------------------------------------------------------------
 // pass 2
 // ------------------------------------------------------------------------------------------------
-constexpr uint32_t kQueueCap = 2048;   // per-CTA staging of selected / candidate items
+constexpr uint32_t kQueueCap = 1024;   // per-CTA staging of selected / candidate items (16 KB: four CTAs fit one SM)
 constexpr uint32_t kP2PerThread = 16;  // consecutive elements per thread: one block of threshold-v16
 constexpr uint32_t kP2PerIter = kThreads * kP2PerThread;
 
@@ -343,7 +343,7 @@ constexpr uint32_t kP2PerIter = kThreads * kP2PerThread;
 // and reserves positions with ONE global atomic per flush, so that stores into peer memory are
 // consecutive and the per-segment cursor is not hammered by every warp.
 template <bool B16>
-__global__ void __launch_bounds__(kThreads) k_pass2(SelectArgs A) {
+__global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
   __shared__ uint32_t s_tmp[kThreads / 32 + 1];
   __shared__ uint2 s_sel[B16 ? 1 : kQueueCap];      // element mode: (idx, value bits)
   __shared__ uint32_t s_selb[B16 ? kQueueCap : 1];  // block mode: block ids

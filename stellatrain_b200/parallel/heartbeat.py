@@ -1,7 +1,7 @@
 """Host-side failure detection for the GPU-resident engine.
 
 The reference has no failure detection: a dead peer blocks a socket receive or a barrier forever
-(SURVEY of backend/src/engine: no heartbeats, no socket timeouts).  Here three layers cooperate:
+(backend/src/engine/comm_manager.cpp:833-974 and core_module_api.cpp:113-199 have neither heartbeats nor socket timeouts).  Here three layers cooperate:
 
 1. every device-side wait is bounded and leaves a status word (``SparseStepError``);
 2. this module: each rank publishes a heartbeat in the job's key-value store from a small thread, and
