@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
     if (e.x == kSentinelIdx) continue;
     const uint32_t s = e.x - A.state_base;   // wraps to a large value below the base
     if (s >= A.state_len) { set_status(A.status, kBadIndex); continue; }
-    atomicAdd(A.acc + s, __uint_as_float(e.y) * w);
+    atomicAdd(&A.rec[s].x, __uint_as_float(e.y) * w);
   }
 }
 
@@ -107,11 +107,13 @@ __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {
       const uint32_t idx = e.x;
       const uint32_t s = idx - A.state_base;        // sentinel or invalid indices (already reported) fall outside
       // the first thread to stamp an index with this epoch owns it
-      const bool won = s < A.state_len && atomicExch(A.stamp + s, epoch) != epoch;
+      const bool won = s < A.state_len &&
+                       atomicExch(reinterpret_cast<uint32_t*>(&A.rec[s].y), epoch) != epoch;
       float xn = 0.f;
       if (won) {
-        float g = A.acc[s];
-        A.acc[s] = 0.f;
+        const float4 rc = __ldcg(A.rec + s);     // accumulator, stamp, m, v in one 16-byte load
+        float g = rc.x;
+        float m_new = rc.z, v_new = rc.w;
         const float x = A.param[idx];
         if (o.kind == 0) {
           float mu = o.momentum;
@@ -119,17 +121,17 @@ __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {
             mu = powf(o.momentum, (float)(m_iter - A.last[s]));
           if (o.weight_decay != 0.f) g += o.weight_decay * x;
           if (o.momentum != 0.f) {
-            const float b = o.first ? g : A.m[s] * mu + (1.f - o.dampening) * g;
+            const float b = o.first ? g : rc.z * mu + (1.f - o.dampening) * g;
             g = o.nesterov ? g + mu * b : b;
-            A.m[s] = b;
+            m_new = b;
           }
           xn = x - lr * g;
           if (o.smart_momentum && A.last != nullptr) A.last[s] = m_iter;
         } else {
           if (o.maximize) g = -g;
           if (o.weight_decay != 0.f) g += o.weight_decay * x;
-          const float mt = o.beta1 * A.m[s] + (1.f - o.beta1) * g;
-          const float vt = o.beta2 * A.v[s] + (1.f - o.beta2) * g * g;
+          const float mt = o.beta1 * rc.z + (1.f - o.beta1) * g;
+          const float vt = o.beta2 * rc.w + (1.f - o.beta2) * g * g;
           const float mh = mt / bc1;
           float vh = vt / bc2;
           if (o.amsgrad && A.vmax != nullptr) {
@@ -137,9 +139,11 @@ __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {
             A.vmax[s] = vh;
           }
           xn = x - o.lr * mh / (sqrtf(vh) + o.eps);
-          A.m[s] = mt;
-          A.v[s] = vt;
+          m_new = mt;
+          v_new = vt;
         }
+        // accumulator cleared, stamp kept (a late loser's exchange writes the same epoch again)
+        A.rec[s] = make_float4(0.f, __uint_as_float(epoch), m_new, v_new);
         A.param[idx] = xn;
       }
       // every consumed position is rewritten each epoch, so a stale value can never be read back

@@ -38,19 +38,17 @@ struct BucketHandle {
     sel.timeout_ns = app.timeout_ns = 2000000000ull;
   }
 
-  void set_data(uint64_t grad, uint64_t grad_tab, uint64_t resid, uint64_t param, uint64_t m, uint64_t v,
-                uint64_t vmax, uint64_t last, uint64_t acc, uint64_t stamp, uint32_t n_total) {
+  // rec: one float4 {accumulator, stamp, m, v} per element of this rank's state range
+  void set_data(uint64_t grad, uint64_t grad_tab, uint64_t resid, uint64_t param, uint64_t rec, uint64_t vmax,
+                uint64_t last, uint32_t n_total) {
     sel.grad = as_ptr<float>(grad);
     sel.grad_tab = as_ptr<float*>(grad_tab);
     sel.resid = as_ptr<float>(resid);
     sel.n_total = n_total;
     app.param = as_ptr<float>(param);
-    app.m = as_ptr<float>(m);
-    app.v = as_ptr<float>(v);
+    app.rec = as_ptr<float4>(rec);
     app.vmax = as_ptr<float>(vmax);
     app.last = as_ptr<uint32_t>(last);
-    app.acc = as_ptr<float>(acc);
-    app.stamp = as_ptr<uint32_t>(stamp);
     app.n_total = n_total;
   }
 
@@ -240,8 +238,7 @@ PYBIND11_MODULE(_C, m) {
   py::class_<BucketHandle>(m, "BucketHandle")
       .def(py::init<>())
       .def("set_data", &BucketHandle::set_data, py::arg("grad"), py::arg("grad_tab"), py::arg("resid"),
-           py::arg("param"), py::arg("m"), py::arg("v"), py::arg("vmax"), py::arg("last"), py::arg("acc"),
-           py::arg("stamp"), py::arg("n_total"))
+           py::arg("param"), py::arg("rec"), py::arg("vmax"), py::arg("last"), py::arg("n_total"))
       .def("set_tables", &BucketHandle::set_tables, py::arg("segs"), py::arg("state"), py::arg("work"),
            py::arg("chunks"), py::arg("chunk_cnt"), py::arg("chunk_pos"), py::arg("hist"), py::arg("n_segs"),
            py::arg("n_chunks"), py::arg("cap"))

@@ -146,11 +146,12 @@ struct ApplyArgs {
   uint32_t use_flags;          // wait on arrival flags (0 when a library collective filled recv)
   uint32_t use_acks;
   const float* weight;         // [world] weight of each source in the merge (default 1/world)
-  float* acc;                  // dense accumulator, zero outside a scatter/apply pair
-  uint32_t* stamp;             // last epoch at which an element was updated
+  // One 16-byte record per element of the state range: {x: dense accumulator, zero outside a scatter/apply
+  // pair; y: bits of the last epoch at which the element was updated; z: momentum buffer (SGD) or first
+  // moment (Adam); w: second moment (Adam)}.  Interleaved so that an update touches one 32-byte sector of
+  // state instead of four: entries hit random elements and the apply kernel is bound by DRAM transactions.
+  float4* rec;
   float* param;
-  float* m;                    // momentum buffer (SGD) or first moment (Adam)
-  float* v;                    // second moment (Adam)
   float* vmax;                 // AMSGrad maximum, or null
   uint32_t* last;              // smart momentum: step of the last touch, or null
   OptState* opt;

@@ -95,8 +95,8 @@ def main() -> None:
     app = sorted(app_ms)[len(app_ms) // 2]
     sel_bytes = 20.0 * n_total
     entries = sum(b.layout.cap for b in buckets)
-    # apply: per entry read 8 B twice; per touched element acc rmw + stamp + param rw + state rw (sectors of 32 B)
-    app_bytes = entries * (16.0 + 32.0 * (5 if args.optimizer == "adam" else 4))
+    # apply: per entry read 8 B twice; per touched element one 32 B sector of the state record and one of the parameter
+    app_bytes = entries * (16.0 + 32.0 * 2)
     out = {
         "compressor": args.compressor, "optimizer": args.optimizer, "elements": n_total, "buckets": len(buckets),
         "segments": len(numels), "entries_per_step": entries,

@@ -114,10 +114,13 @@ class GpuBucket:
         else:
             self.state_lo, self.state_hi = 0, n
         ns = max(self.state_hi - self.state_lo, B.ALIGN)
-        self.acc = torch.zeros(ns, **f32)
-        self.stamp = torch.zeros(ns, dtype=torch.int32, device=device)
-        self.m = torch.zeros(ns, **f32)
-        self.v = torch.zeros(ns, **f32) if optimizer == "adam" else None
+        # One 16-byte record per element, {accumulator, stamp, m, v}: an update touches one sector of state.
+        # acc / stamp / m / v are strided views of it (v stays unused by SGD).
+        self.rec = torch.zeros(ns, 4, **f32)
+        self.acc = self.rec[:, 0]
+        self.stamp = self.rec[:, 1].view(torch.int32)
+        self.m = self.rec[:, 2]
+        self.v = self.rec[:, 3] if optimizer == "adam" else None
         self.vmax = torch.zeros(ns, **f32) if (optimizer == "adam" and amsgrad) else None
         self.last = torch.zeros(ns, dtype=torch.int32, device=device) if smart_momentum else None
 
@@ -170,9 +173,8 @@ class GpuBucket:
         L = self.layout
         h.set_data(
             grad=self.grad.data_ptr(), grad_tab=self._ptr(self.grad_tab_dev), resid=self.resid.data_ptr(),
-            param=self.param.data_ptr(),
-            m=self.m.data_ptr(), v=self._ptr(self.v), vmax=self._ptr(self.vmax), last=self._ptr(self.last),
-            acc=self.acc.data_ptr(), stamp=self.stamp.data_ptr(), n_total=L.n_total,
+            param=self.param.data_ptr(), rec=self.rec.data_ptr(), vmax=self._ptr(self.vmax), last=self._ptr(self.last),
+            n_total=L.n_total,
         )
         h.set_tables(
             segs=self.segs.data_ptr(), state=self.state.data_ptr(), work=self.work.data_ptr(),
