@@ -273,16 +273,17 @@ def main() -> None:
             return graphed.replay()
         return train_step(dev_x, dev_y)
 
+    # End to end, the way a user feeds the model: the package's PrefetchLoader copies batch i+1 from pinned host
+    # memory on a side stream while step i runs; every step still has its own host-to-device copy and ends with
+    # a device-to-host read of its loss.
+    e2e_iter = None
+
     def run_step_e2e(i):
-        hx, hy = host_batches[i % n_host]
+        x, y = next(e2e_iter)
         if graphed is not None:
-            graphed.copy_inputs(hx, hy)
+            graphed.copy_inputs(x, y)          # device to device, into the graph's input buffers
             loss = graphed.replay()
         else:
-            x = hx.to(dev, non_blocking=True)
-            y = hy.to(dev, non_blocking=True)
-            if args.channels_last and not lm:
-                x = x.contiguous(memory_format=torch.channels_last)
             loss = train_step(x, y)
         loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the step's result is read on the host
@@ -328,7 +329,12 @@ def main() -> None:
 
     e2e = None
     if not args.skip_e2e:
-        for i in range(3):
+        from stellatrain_b200.utils.dataloader import PrefetchLoader
+
+        e2e_warm = 3
+        e2e_iter = iter(PrefetchLoader((host_batches[i % n_host] for i in range(e2e_warm + args.steps + 4)), dev, depth=2,
+                                       channels_last=bool(args.channels_last and not lm)))
+        for i in range(e2e_warm):
             run_step_e2e(i)
         ms2, clocks2, _ = timed(run_step_e2e, args.steps)
         e2e = {"value": unit_per_step / (ms2 / args.steps / 1e3), "unit": "tokens/s" if lm else "images/s",

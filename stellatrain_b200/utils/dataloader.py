@@ -92,8 +92,18 @@ class PrefetchLoader:
             if isinstance(item, Exception):
                 raise item
             if ev is not None:
-                torch.cuda.current_stream(self.device).wait_event(ev)
+                cur = torch.cuda.current_stream(self.device)
+                cur.wait_event(ev)
+                self._record_stream(item, cur)     # allocated on the copy stream, used on this one
             yield item
+
+    def _record_stream(self, obj, stream) -> None:
+        if isinstance(obj, torch.Tensor):
+            if obj.is_cuda:
+                obj.record_stream(stream)
+        elif isinstance(obj, (list, tuple)):
+            for o in obj:
+                self._record_stream(o, stream)
 
 
 SuperFastDataLoader = PrefetchLoader
