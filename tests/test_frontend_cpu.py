@@ -133,3 +133,12 @@ def test_merge_state_shards_reassembles_full_moments():
     b = out["buckets"][0]
     assert torch.equal(b["m"], full_m) and torch.equal(b["v"], full_v)
     assert b["state_range"] == (0, n) and out["state_partition"] == "replicated"
+
+
+def test_package_entry_point_reports_build_state():
+    out = subprocess.run([sys.executable, "-m", "stellatrain_b200"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    import json
+
+    rep = json.loads(out.stdout)
+    assert rep["extensions"]["_Ccpu"]["built"] and rep["cpu_simd"] in ("scalar", "avx2", "avx512")
