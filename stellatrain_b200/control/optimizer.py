@@ -162,6 +162,40 @@ class BatchRateOptimizer:
         self.last_rows: Dict[int, dict] = {}
         self.log: List[str] = []
 
+    # ---------------------------------------------------------------- persistence
+    def state_dict(self) -> dict:
+        """What a restarted controller needs to carry on where it was: the fitted per-GPU throughput curves, the
+        smoothed samples behind them, the phase, the bandwidth estimate and the instruction history (the state the
+        reference keeps only in memory, backend/src/engine/batch_rate_alloc_optim.py:117-162)."""
+        return {
+            "alphas": self.alphas.copy(), "betas": self.betas.copy(), "max_batch": self.max_batch.copy(),
+            "samples": [{"values": dict(s.values), "count": s.count, "momentum": s.momentum} for s in self.samples],
+            "seen": list(self.seen), "initialized": list(self.initialized), "init_batch": self.init_batch.copy(),
+            "init_ratio": self.init_ratio, "phase": int(self.phase.value), "bw_estimate": self.bw_estimate,
+            "prev_x": None if self.prev_x is None else self.prev_x.copy(), "prev_fun": self.prev_fun,
+            "main_iter": self.main_iter, "rng": self.rng.getstate(),
+            "history": [(i.iter, i.batch.copy(), i.comp_ratio) for i in self.history.values()],
+        }
+
+    def load_state_dict(self, sd: dict) -> None:
+        if len(sd["alphas"]) != self.num_gpus:
+            raise ValueError(f"controller state is for {len(sd['alphas'])} GPUs, this job has {self.num_gpus}")
+        self.alphas, self.betas = np.array(sd["alphas"], float), np.array(sd["betas"], float)
+        self.max_batch = np.array(sd["max_batch"], float)
+        self.samples = []
+        for row in sd["samples"]:
+            s = SmoothedSamples(row["momentum"])
+            s.values, s.count = {int(k): float(v) for k, v in row["values"].items()}, int(row["count"])
+            self.samples.append(s)
+        self.seen, self.initialized = list(sd["seen"]), list(sd["initialized"])
+        self.init_batch, self.init_ratio = np.array(sd["init_batch"], float), float(sd["init_ratio"])
+        self.phase = Phase(sd["phase"])
+        self.bw_estimate = sd["bw_estimate"]
+        self.prev_x = None if sd["prev_x"] is None else np.array(sd["prev_x"], float)
+        self.prev_fun, self.main_iter = float(sd["prev_fun"]), int(sd["main_iter"])
+        self.rng.setstate(sd["rng"])
+        self.history = OrderedDict((it, InstructionSet(it, np.array(b, float), float(r))) for it, b, r in sd["history"])
+
     # ---------------------------------------------------------------- telemetry in
     def set_max_batch(self, gpu: int, value: int) -> None:
         self.max_batch[gpu] = value

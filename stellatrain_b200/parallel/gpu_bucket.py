@@ -330,14 +330,27 @@ class GpuBucket:
         return {k: (v.detach().cpu().clone() if torch.is_tensor(v) else v) for k, v in d.items()}
 
     def load_state_dict(self, d: dict) -> None:
-        if tuple(d.get("state_range", (0, self.layout.n_total))) != (self.state_lo, self.state_hi):
+        src_range = tuple(d.get("state_range", (0, self.layout.n_total)))
+        mine = (self.state_lo, self.state_hi)
+        if src_range != mine and src_range != (0, self.layout.n_total):
             raise ValueError("checkpoint was written with a different partition of the optimiser state")
         if abs(d["ratio"] - self.ratio) > 1e-12:
             self.set_ratio(d["ratio"])
-        for k in ("resid", "param", "m", "v", "vmax", "last", "stamp", "opt", "counters"):
+        for k in ("resid", "param", "opt", "counters"):
+            getattr(self, k).copy_(d[k])
+        # per-element state: the checkpoint holds this rank's range, or the whole bucket (a gathered file)
+        off = 0 if src_range == mine else self.state_lo
+        n_state = self.state_hi - self.state_lo
+        for k in ("m", "v", "vmax", "last", "stamp"):
             t = getattr(self, k)
-            if t is not None and k in d:
-                t.copy_(d[k])
+            if t is None:
+                continue
+            if k == "stamp" and (k not in d or src_range != mine):
+                t.zero_()           # no stamps for this layout in the file; epochs start above zero
+                continue
+            if k not in d:
+                continue
+            t[:n_state].copy_(d[k][off : off + n_state])
         self.state.copy_(d["seg_state"])
         self._opt_host = self.opt.cpu().numpy().view(B.OPT_STATE_DTYPE).copy()
         self.acc.zero_()

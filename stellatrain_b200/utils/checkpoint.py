@@ -28,22 +28,44 @@ def _rank_world():
     return 0, 1
 
 
-def save(path: str, module: torch.nn.Module, engine, extra: Optional[dict] = None, all_ranks: bool = True) -> Optional[str]:
+def save(path: str, module: torch.nn.Module, engine, extra: Optional[dict] = None, all_ranks: bool = True,
+         gather: bool = False) -> Optional[str]:
+    """One file per rank (exact resume), or with ``gather=True`` a single file written by rank 0 that holds the
+    whole optimiser state even when it is partitioned over the ranks.  A gathered file keeps rank 0's residual only:
+    the other ranks restart theirs from zero, so use per-rank files when the resume must be bit-exact."""
     rank, world = _rank_world()
     engine.synchronize()
+    esd = engine.state_dict()
+    p = Path(path)
+    if gather and world > 1:
+        if esd.get("state_partition", "replicated") == "owner":
+            keys = ("m", "v", "vmax", "last", "state_range")
+            shard = [{k: b[k] for k in keys if k in b} for b in esd["buckets"]]
+            shards = [None] * world
+            dist.all_gather_object(shards, shard)
+            if rank == 0:
+                per_rank = [dict(esd, buckets=[dict(b, **sh) for b, sh in zip(esd["buckets"], shards[r])]) for r in range(world)]
+                esd = merge_state_shards(per_rank)
+        if rank == 0:
+            esd["gathered"] = True
+            _write(p, {"model": module.state_dict(), "engine": esd, "extra": extra or {}, "rank": 0, "world": world})
+        dist.barrier()
+        return str(p) if rank == 0 else None
     if not all_ranks and rank != 0:
         return None
-    p = Path(path)
     if world > 1:
         p = p.with_name(f"{p.stem}.rank{rank}{p.suffix}")
-    p.parent.mkdir(parents=True, exist_ok=True)
-    tmp = p.with_suffix(p.suffix + ".tmp")
-    torch.save({"model": module.state_dict(), "engine": engine.state_dict(), "extra": extra or {}, "rank": rank,
-                "world": world}, tmp)
-    os.replace(tmp, p)     # a crash never leaves a half-written checkpoint under the final name
+    _write(p, {"model": module.state_dict(), "engine": esd, "extra": extra or {}, "rank": rank, "world": world})
     if world > 1:
         dist.barrier()
     return str(p)
+
+
+def _write(p: Path, payload: dict) -> None:
+    p.parent.mkdir(parents=True, exist_ok=True)
+    tmp = p.with_suffix(p.suffix + ".tmp")
+    torch.save(payload, tmp)
+    os.replace(tmp, p)     # a crash never leaves a half-written checkpoint under the final name
 
 
 def merge_state_shards(engine_sds: list[dict]) -> dict:
@@ -100,4 +122,7 @@ def load(path: str, module: torch.nn.Module, engine, map_location="cpu", allow_w
     # buffers (e.g. BatchNorm statistics) come from the model part, parameters from the engine's buckets
     module.load_state_dict(ck["model"], strict=False)
     engine.load_state_dict(ck["engine"])
+    if ck["engine"].get("gathered") and rank != 0:
+        for rt in engine.buckets:          # the file carries rank 0's residual only
+            rt.bucket.resid.zero_()
     return ck["extra"]

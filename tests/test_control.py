@@ -155,3 +155,37 @@ def test_schedule_and_token_bucket():
     assert w == pytest.approx(1e-3, rel=0.01)
     now["t"] += w + 0.5
     assert tb.delay_for(500) == 0.0
+
+
+def test_optimizer_state_survives_a_restart():
+    """A controller restarted from its state_dict issues the same instructions as one that kept running."""
+    import copy
+    import pickle
+
+    def make(it):
+        o = BatchRateOptimizer(2, 2, TrafficModel([1_000_000] * 10, "tcp"), latest_iter=lambda: it["n"], reoptimize_every=5)
+        o.set_max_batch(0, 64); o.set_max_batch(1, 64)
+        return o
+
+    it_a, it_b = {"n": 0}, {"n": 0}
+    a = make(it_a)
+    speed, batches = [0.5, 1.0], np.array([8.0, 8.0])
+    for step in range(120):
+        it_a["n"] = step
+        a.update(_rows(batches, speed))
+        inst = a.step(step, measured_mbps=400.0)
+        if inst is not None:
+            batches = inst.batch.copy()
+    sd = pickle.loads(pickle.dumps(a.state_dict()))         # what torch.save would do with checkpoint "extra"
+    b = make(it_b)
+    b.load_state_dict(copy.deepcopy(sd))
+    assert b.phase == a.phase and len(b.history) == len(a.history)
+    batches_a, batches_b = batches.copy(), batches.copy()
+    for step in range(120, 200):
+        it_a["n"] = it_b["n"] = step
+        a.update(_rows(batches_a, speed)); b.update(_rows(batches_b, speed))
+        ia, ib = a.step(step, measured_mbps=400.0), b.step(step, measured_mbps=400.0)
+        assert (ia is None) == (ib is None)
+        if ia is not None:
+            assert ia.iter == ib.iter and np.allclose(ia.batch, ib.batch) and ia.comp_ratio == pytest.approx(ib.comp_ratio)
+            batches_a, batches_b = ia.batch.copy(), ib.batch.copy()

@@ -158,3 +158,34 @@ def test_ranks_that_own_nothing():
         par[r].check_status()
         assert torch.equal(par[r].param, par[0].param)
         assert float((par[r].param - rep[r].param).abs().max()) < 1e-5
+
+
+def test_full_state_loads_into_partitioned_buckets():
+    """A checkpoint that holds the whole bucket's moments (replicated state, or a gathered file) restores ranks that
+    keep only their own range; training then continues exactly as the replicated ranks do."""
+    dev = torch.device("cuda:0")
+    world = 4
+    rep = _make_ranks(world, NUMELS, "topk", "adam", False, 0.9, dev)
+    LAY = rep[0].layout
+    for step in range(1, 4):
+        _step(rep, _grads(world, LAY, step, dev))
+    torch.cuda.synchronize()
+    par = _make_ranks(world, NUMELS, "topk", "adam", True, 0.9, dev)
+    for r in range(world):
+        par[r].load_state_dict(rep[r].state_dict())
+        lo, hi = par[r].state_lo, par[r].state_hi
+        assert torch.equal(par[r].m[: hi - lo], rep[r].m[lo:hi]) and torch.equal(par[r].v[: hi - lo], rep[r].v[lo:hi])
+    # flags, acknowledgements and write-back flags restart from the restored epoch
+    e = int(par[0].counters[0]) - 1
+    for b in par:
+        for t in (b.wiring.flag_local, b.wiring.ack_local, b.wiring.pflag_local):
+            t.fill_(e)
+    for step in range(4, 8):
+        grads = _grads(world, LAY, step, dev)
+        _step(rep, grads)
+        _step(par, grads)
+    torch.cuda.synchronize()
+    for r in range(world):
+        par[r].check_status()
+        assert torch.equal(par[r].param, par[0].param)
+        assert float((par[r].param - rep[r].param).abs().max()) < 1e-5

@@ -192,6 +192,50 @@ def test_narrow_wire_format(partition):
     assert narrow[0]["checksum"] == pytest.approx(wide[0]["checksum"], abs=1.0)
 
 
+def _worker_gathered_checkpoint(rank, world, tmp):
+    import torch.nn.functional as F
+
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+    from stellatrain_b200.utils import checkpoint
+
+    def make():
+        model = _net()
+        return model, SparseDPEngine(model, EngineConfig(compressor="topk", ratio=0.9, optimizer="adam", staleness=1,
+                                                         bucket_mb=0.02, chunk_elems=1024, optimizer_options={"lr": 1e-2},
+                                                         state_partition="owner"))
+
+    m1, e1 = make()
+    data = _data(rank, 12)
+    for x, y in data[:6]:
+        F.cross_entropy(m1(x), y).backward()
+    path = checkpoint.save(f"{tmp}/gathered.pt", m1, e1, {"global_step": 6}, gather=True)
+    single = os.path.exists(f"{tmp}/gathered.pt") and not os.path.exists(f"{tmp}/gathered.rank0.pt")
+    m2, e2 = make()
+    extra = checkpoint.load(f"{tmp}/gathered.pt", m2, e2)
+    same_params = all(torch.equal(p, q) for p, q in zip(m1.parameters(), m2.parameters()))
+    same_state = all(torch.equal(a.bucket.m, b.bucket.m) and torch.equal(a.bucket.v, b.bucket.v)
+                     for a, b in zip(e1.buckets, e2.buckets))
+    for x, y in data[6:]:
+        loss = F.cross_entropy(m2(x), y)
+        loss.backward()
+    e2.synchronize()
+    e2.check_status()
+    drift = e2.replica_drift()
+    e1.close(); e2.close()
+    return {"single": single, "step": extra["global_step"], "same_params": same_params, "same_state": same_state,
+            "drift": drift, "wrote": path is not None}
+
+
+def test_gathered_checkpoint_of_partitioned_state(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    outs = _spawn(_worker_gathered_checkpoint, world, str(tmp_path))
+    for r, o in enumerate(outs):
+        assert o["single"] and o["step"] == 6 and o["same_params"] and o["same_state"], outs
+        assert o["drift"] == 0.0 and o["wrote"] == (r == 0), outs
+
+
 def _worker_grouped(rank, world, group_size, sparse):
     import torch.nn.functional as F
 
