@@ -46,13 +46,16 @@ __global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
   if (!s_ok) return;
   const uint2* in = A.recv + (size_t)slot * A.slot_stride + (size_t)src * A.cap;
   const float w = A.weight[src];
+  uint32_t sum = 0;
   for (uint32_t i = A.ent_lo + blockIdx.x * kThreads + threadIdx.x; i < A.ent_hi; i += gridDim.x * kThreads) {
     const uint2 e = load_entry(A, in, i);
     if (e.x == kSentinelIdx) continue;
+    sum += entry_hash(e.x, e.y);
     const uint32_t s = e.x - A.state_base;   // wraps to a large value below the base
     if (s >= A.state_len) { set_status(A.status, kBadIndex); continue; }
     atomicAdd(&A.rec[s].x, __uint_as_float(e.y) * w);
   }
+  if (A.cksum_local != nullptr && sum != 0u) atomicAdd(A.rsum + src, sum);
 }
 
 // Store one write-back entry into the same stream position of every rank's write-back area.
@@ -101,7 +104,13 @@ __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {
     const uint32_t m_iter = o.tick - 1u;
     const float lr = (o.kind == 0 && o.maximize) ? -o.lr : o.lr;
     const uint64_t src_off = (size_t)slot * A.slot_stride + (size_t)src * A.cap;
-    const uint2* in = A.recv + src_off;
+    uint2* in = A.recv + src_off;
+    if (A.cksum_local != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+      // the scatter kernel has read the whole stream of this source: does it add up to what was sent?
+      const uint32_t got = atomicExch(A.rsum + src, 0u);
+      const uint32_t want = __ldcg(A.cksum_local + (size_t)slot * A.world + src);
+      if (got != want) set_status(A.status, kBadChecksum);
+    }
     for (uint32_t i = A.ent_lo + blockIdx.x * kThreads + threadIdx.x; i < A.ent_hi; i += gridDim.x * kThreads) {
       const uint2 e = load_entry(A, in, i);
       const uint32_t idx = e.x;
@@ -148,6 +157,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {
       }
       // every consumed position is rewritten each epoch, so a stale value can never be read back
       if (A.owner_mode) emit_writeback(A, src_off + i, won ? idx : kSentinelIdx, xn);
+      if (A.poison && !A.narrow) in[i] = make_uint2(kSentinelIdx, 0u);
     }
   }
 

@@ -110,7 +110,12 @@ struct BucketHandle {
       app.ack[p] = as_ptr<uint64_t>(peer_ack[p]) + rank;
     }
     sel.out_mc = recv_mc ? as_ptr<uint2>(recv_mc) + (uint64_t)rank * cap : nullptr;
-    app.recv = as_ptr<const uint2>(recv_local);
+    app.recv = as_ptr<uint2>(recv_local);
+    // debug checks are off unless set_debug follows
+    sel.cksum_acc = nullptr;
+    app.cksum_local = nullptr;
+    app.rsum = nullptr;
+    app.poison = 0u;
     app.flag_local = as_ptr<const uint64_t>(flag_local);
     sel.ack_local = as_ptr<const uint64_t>(ack_local);
     sel.use_acks = app.use_acks = use_acks ? 1u : 0u;
@@ -200,6 +205,19 @@ struct BucketHandle {
   void select(uint64_t stream) {
     check(st::launch_select(sel, randomk_seed, as_ptr<CUstream_st>(stream)), "launch_select");
   }
+  // Debug checks.  cksum areas are [2][world] u32 indexed [slot][source]; cksum_acc has MAX_WORLD words, rsum `world`.
+  void set_debug(uint64_t cksum_acc, uint64_t rsum, uint64_t cksum_local, const std::vector<uint64_t>& peer_cksum, bool poison) {
+    const int world = app.world;
+    if (world < 1) throw std::runtime_error("set_comm must come first");
+    if ((int)peer_cksum.size() != world) throw std::runtime_error("set_debug: one checksum area per rank");
+    sel.cksum_acc = as_ptr<uint32_t>(cksum_acc);
+    sel.cksum_slot_stride = world;
+    for (int p = 0; p < world; ++p) sel.cksum[p] = peer_cksum[p] ? as_ptr<uint32_t>(peer_cksum[p]) + app.rank : nullptr;
+    app.cksum_local = as_ptr<const uint32_t>(cksum_local);
+    app.rsum = as_ptr<uint32_t>(rsum);
+    app.poison = poison ? 1u : 0u;
+  }
+
   void apply(uint64_t stream, int phase) {
     check(st::launch_apply(app, max_ctas_per_source, phase, as_ptr<CUstream_st>(stream)), "launch_apply");
   }
@@ -259,6 +277,8 @@ PYBIND11_MODULE(_C, m) {
       .def("select", &BucketHandle::select, py::arg("stream"))
       .def("set_owner", &BucketHandle::set_owner, py::arg("bounds"), py::arg("state_base"), py::arg("state_len"),
            py::arg("wb_local"), py::arg("peer_wb"), py::arg("wb_mc"), py::arg("pflag_local"), py::arg("peer_pflag"))
+      .def("set_debug", &BucketHandle::set_debug, py::arg("cksum_acc"), py::arg("rsum"), py::arg("cksum_local"),
+           py::arg("peer_cksum"), py::arg("poison"))
       .def("apply", &BucketHandle::apply, py::arg("stream"), py::arg("phase") = 0);
 
   m.def("max_abs_diff", [](uint64_t a, uint64_t b, uint64_t n, uint64_t out_bits, uint64_t stream) {

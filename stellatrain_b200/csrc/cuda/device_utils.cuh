@@ -71,6 +71,11 @@ __device__ __forceinline__ float wire_value(uint32_t narrow_base, float x) {
   return __uint_as_float((b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u);
 }
 
+// Order-independent stream checksum: the sum over entries of this hash (debug checks).
+__device__ __forceinline__ uint32_t entry_hash(uint32_t idx, uint32_t val_bits) {
+  return idx * 0x9E3779B1u + (val_bits ^ (val_bits >> 15));
+}
+
 // Destination of a segment's entries: one rank when the optimiser state is partitioned, else all (-1).
 __device__ __forceinline__ int dest_of(const SelectArgs& A, const SegDesc& sd) {
   return A.owner_mode ? (int)((sd.reserved >> kSegOwnerShift) & kSegOwnerMask) : -1;
@@ -81,6 +86,11 @@ __device__ __forceinline__ int dest_of(const SelectArgs& A, const SegDesc& sd) {
 // be wire_value(narrow_base, .).
 __device__ __forceinline__ void emit_entry(const SelectArgs& A, int dest, uint32_t narrow_base, uint64_t slot_off,
                                            uint32_t pos, uint32_t idx, float val) {
+  if (A.cksum_acc != nullptr && idx != kSentinelIdx) {
+    // narrow entries arrive with the low 16 value bits cleared: hash what the receiver will decode
+    const uint32_t vb = narrow_base != kNotNarrow ? (__float_as_uint(val) & 0xFFFF0000u) : __float_as_uint(val);
+    atomicAdd(A.cksum_acc + (dest >= 0 ? dest : 0), entry_hash(idx, vb));
+  }
   if (narrow_base != kNotNarrow) {
     const uint32_t w = idx == kSentinelIdx ? 0xFFFFFFFFu : ((idx - narrow_base) | (__float_as_uint(val) & 0xFFFF0000u));
     if (dest >= 0) {

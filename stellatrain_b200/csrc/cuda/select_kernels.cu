@@ -609,6 +609,19 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
 // ------------------------------------------------------------------------------------------------
 // candidates + completion
 // ------------------------------------------------------------------------------------------------
+// Debug checks: hand every destination the sum over the entries this select stored into it, and clear
+// the accumulators for the next select.  Called by the one thread that publishes the arrival flags, before
+// them (their release orders these stores too).
+__device__ __forceinline__ void publish_checksums(const SelectArgs& A, uint32_t epoch) {
+  if (A.cksum_acc == nullptr) return;
+  for (int p = 0; p < A.world; ++p) {
+    const uint32_t sum = atomicAdd(A.cksum_acc + (A.owner_mode ? p : 0), 0u);
+    if (A.cksum[p] != nullptr) A.cksum[p][(size_t)(epoch & 1u) * A.cksum_slot_stride] = sum;
+  }
+  for (int p = 0; p < kMaxWorld; ++p) A.cksum_acc[p] = 0u;
+  __threadfence_system();
+}
+
 constexpr int kCandThreads = 1024;
 constexpr int kCandIlp = 4;   // independent loads in flight per thread
 
@@ -775,6 +788,7 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
     if (prev == gridDim.x - 1) {
       *A.done_ctr = 0;
       __threadfence_system();
+      publish_checksums(A, epoch);
       if (A.publish && ld_volatile_u32(A.status) == kOk) {
         for (int p = 0; p < A.world; ++p)
           st_release_sys_u64(A.flag[p] + (size_t)(epoch & 1u) * A.flag_slot_stride, (uint64_t)epoch);
@@ -829,6 +843,7 @@ __global__ void __launch_bounds__(kThreads) k_randomk(SelectArgs A, uint32_t see
     if (prev == gridDim.x - 1) {
       *A.done_ctr = 0;
       __threadfence_system();
+      publish_checksums(A, epoch);
       if (A.publish && ld_volatile_u32(A.status) == kOk) {
         for (int p = 0; p < A.world; ++p)
           st_release_sys_u64(A.flag[p] + (size_t)(epoch & 1u) * A.flag_slot_stride, (uint64_t)epoch);

@@ -27,6 +27,7 @@ enum Status : uint32_t {
   kBadIndex = 3,      // a received index is outside the bucket
   kBadCandidate = 4,  // candidate scratch exhausted (cannot happen with a correctly sized scratch)
   kBadSize = 5,       // request exceeds a compiled-in limit
+  kBadChecksum = 6,   // debug checks: a received stream does not add up to what its source sent
 };
 
 struct SegDesc {          // static per segment (re-uploaded when the compression ratio changes)
@@ -128,6 +129,12 @@ struct SelectArgs {
   uint32_t use_acks;           // wait for acknowledgements before overwriting a slot
   uint32_t publish;            // publish arrival flags when the stream is complete
   uint32_t owner_mode;         // 1: a segment's entries go only to the rank named in its descriptor
+  // Debug checks (null = off): every emitted entry adds a hash of (index, value bits) to cksum_acc[dest]
+  // (cksum_acc[0] when the entry goes to everyone); the last kernel of the chain stores the sums into the
+  // destinations' checksum words before it publishes the arrival flags.
+  uint32_t* cksum_acc;         // [kMaxWorld], device memory of this rank
+  uint32_t* cksum[kMaxWorld];  // per destination: its checksum word for source `rank`, slot 0 ([2][world] u32)
+  uint64_t cksum_slot_stride;
   uint32_t* epoch;             // select epoch of this bucket (starts at 1)
   uint32_t* done_ctr;          // CTA completion counter of the last kernel of the chain
   uint32_t* status;            // Status
@@ -135,7 +142,7 @@ struct SelectArgs {
 };
 
 struct ApplyArgs {
-  const uint2* recv;           // [2 slots][world][cap] received streams (local memory)
+  uint2* recv;                 // [2 slots][world][cap] received streams (local memory)
   uint64_t slot_stride;        // entries per slot (= world * cap)
   uint32_t cap;                // entries per source
   uint32_t n_total;            // elements in the bucket
@@ -174,6 +181,13 @@ struct ApplyArgs {
   uint32_t narrow;
   uint32_t n_segs;
   const SegDesc* segs;
+  // Debug checks (null = off): the scatter adds the same hash over what it reads into rsum[source], the apply
+  // compares it with the word the source stored and reports kBadChecksum; with `poison` every consumed entry
+  // of a wide stream is overwritten with the "no entry" marker, so a position a source fails to rewrite
+  // can never be taken for fresh data.
+  const uint32_t* cksum_local;      // [2][world] written by the sources
+  uint32_t* rsum;                   // [world]
+  uint32_t poison;
   uint32_t own_lo[kMaxWorld + 1];   // owner o consumes positions [own_lo[o], own_lo[o + 1])
   uint2* wb[kMaxWorld];             // per rank: its write-back area [2][world][cap], slot 0
   uint2* wb_mc;                     // multicast alias of the write-back area, or null

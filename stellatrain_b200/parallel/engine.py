@@ -54,6 +54,8 @@ class EngineConfig:
                                           # to the tensor, bf16 value; the rounding error stays in the residual)
     fine_grained_gating: bool = False     # wait per first-using module instead of at the root
     status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
+    debug_checks: bool = False            # every stream carries a checksum that the receiver verifies (status 6), consumed
+                                          # entries are overwritten with the "no entry" marker; slower, for debugging
     profile: bool = False                 # NVTX ranges and CUDA-event timers per bucket and stage (utils/stats.py)
 
 
@@ -190,7 +192,7 @@ class SparseDPEngine:
             if self.world != 1:
                 raise ValueError("transport 'local' needs world size 1")
             for rt in self.buckets:
-                rt.bucket.wire_local()
+                rt.bucket.wire_local(debug_checks=self.cfg.debug_checks)
             self.pool = None
             return
         W = self.world
@@ -200,6 +202,8 @@ class SparseDPEngine:
             need += sum(rt.bucket.layout.n_total * 4 + 4 * self.group_size * 8 + 1024 for rt in self.buckets)
         if self.partitioned:
             need += sum(rt.bucket.recv_bytes() + 2 * W * 8 + 1024 for rt in self.buckets)
+        if self.cfg.debug_checks:
+            need += len(self.buckets) * (2 * W * 4 + 1024)
         if self.transport == "nccl":
             # library baseline: streams are staged locally and moved by ncclAllGather
             self.pool = symm._alloc_local(need, self.device, 1, 0)
@@ -230,6 +234,10 @@ class SparseDPEngine:
                     wb_mc=pool.mc_addr(w_off), pflag_local=pool.local_view(p_off, 2 * W * 8).view(torch.int64),
                     peer_pflag=[pool.peer_addr(r, p_off) for r in range(W)],
                 )
+            if self.cfg.debug_checks:
+                c_off = pool.take(2 * W * 4)
+                extra.update(cksum_local=pool.local_view(c_off, 2 * W * 4).view(torch.int32),
+                             peer_cksum=[pool.peer_addr(r, c_off) for r in range(W)], poison=True)
             b.wire(Wiring(
                 world=W, rank=self.rank,
                 recv_local=pool.local_view(r_off, b.recv_bytes()),

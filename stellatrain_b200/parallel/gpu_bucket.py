@@ -22,6 +22,7 @@ STATUS_NAMES = {
     3: "received index outside the bucket",
     4: "candidate scratch exhausted",
     5: "size beyond a compiled-in limit",
+    6: "a received stream does not match its source's checksum",
 }
 
 
@@ -66,6 +67,10 @@ class Wiring:
     wb_mc: int = 0
     pflag_local: Optional[torch.Tensor] = None   # int64 [2][world]
     peer_pflag: Sequence[int] = ()
+    # debug checks: per-source stream checksums (int32 [2][world]) and poisoning of consumed entries
+    cksum_local: Optional[torch.Tensor] = None
+    peer_cksum: Sequence[int] = ()
+    poison: bool = False
 
 
 class GpuBucket:
@@ -218,11 +223,15 @@ class GpuBucket:
         """Bytes of receive area one rank needs for this bucket (two slots, all sources)."""
         return 2 * self.world * self.cap_max * 8
 
-    def wire_local(self) -> None:
+    def wire_local(self, debug_checks: bool = False) -> None:
         """Single-process wiring: the stream goes to this GPU's own receive area, stream order is
         the only synchronisation."""
         recv = torch.zeros(self.recv_bytes(), dtype=torch.uint8, device=self.device)
-        self.wire(Wiring(1, 0, recv, [recv.data_ptr()], None, [0], None, [0]))
+        extra = {}
+        if debug_checks:
+            ck = torch.zeros(2, dtype=torch.int32, device=self.device)
+            extra = dict(cksum_local=ck, peer_cksum=[ck.data_ptr()], poison=True)
+        self.wire(Wiring(1, 0, recv, [recv.data_ptr()], None, [0], None, [0], **extra))
 
     def wire(self, w: Wiring) -> None:
         self.wiring = w
@@ -243,6 +252,12 @@ class GpuBucket:
             ack_local=self._ptr(w.ack_local), peer_ack=list(w.peer_ack), use_flags=w.use_flags,
             use_acks=w.use_acks,
         )
+        if w.cksum_local is not None:
+            if not hasattr(self, "_cksum_acc"):
+                self._cksum_acc = torch.zeros(_ext().MAX_WORLD, dtype=torch.int32, device=self.device)
+                self._rsum = torch.zeros(max(w.world, 1), dtype=torch.int32, device=self.device)
+            h.set_debug(cksum_acc=self._cksum_acc.data_ptr(), rsum=self._rsum.data_ptr(),
+                        cksum_local=w.cksum_local.data_ptr(), peer_cksum=list(w.peer_cksum), poison=w.poison)
         if self.partition_state and w.world > 1:
             if w.wb_local is None or w.pflag_local is None:
                 raise ValueError("partitioned optimiser state needs write-back areas and flags in the wiring")

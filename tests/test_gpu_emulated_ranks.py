@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 NUMELS = [5000, 70000, 130, 40000, 16, 9000]
 
 
-def _make_ranks(world, numels, compressor, optimizer, partition, ratio, dev, lr=1e-2, narrow=False):
+def _make_ranks(world, numels, compressor, optimizer, partition, ratio, dev, lr=1e-2, narrow=False, debug=False):
     from stellatrain_b200.parallel import buckets as B
     from stellatrain_b200.parallel.gpu_bucket import CandidateScratch, GpuBucket, Wiring
 
@@ -25,10 +25,12 @@ def _make_ranks(world, numels, compressor, optimizer, partition, ratio, dev, lr=
     mkf = lambda: torch.zeros(2 * world, dtype=torch.int64, device=dev)    # noqa: E731
     recv, wb = [mk8() for _ in ranks], [mk8() for _ in ranks]
     flag, ack, pflag = [mkf() for _ in ranks], [mkf() for _ in ranks], [mkf() for _ in ranks]
+    cks = [torch.zeros(2 * world, dtype=torch.int32, device=dev) for _ in ranks]
     ptrs = lambda ts: [t.data_ptr() for t in ts]                           # noqa: E731
     for r, b in enumerate(ranks):
+        dbg = dict(cksum_local=cks[r], peer_cksum=ptrs(cks), poison=True) if debug else {}
         b.wire(Wiring(world, r, recv[r], ptrs(recv), flag[r], ptrs(flag), ack[r], ptrs(ack), use_flags=True,
-                      use_acks=True, wb_local=wb[r], peer_wb=ptrs(wb), pflag_local=pflag[r], peer_pflag=ptrs(pflag)))
+                      use_acks=True, wb_local=wb[r], peer_wb=ptrs(wb), pflag_local=pflag[r], peer_pflag=ptrs(pflag), **dbg))
         b.set_optimizer_options(lr=lr, momentum=0.9)
     init = torch.randn(ranks[0].layout.n_total, device=dev, generator=torch.Generator(device=dev).manual_seed(7))
     for b in ranks:
@@ -189,3 +191,46 @@ def test_full_state_loads_into_partitioned_buckets():
         par[r].check_status()
         assert torch.equal(par[r].param, par[0].param)
         assert float((par[r].param - rep[r].param).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("compressor", ["topk", "thresholdv16"])
+@pytest.mark.parametrize("partition,narrow", [(False, False), (True, False), (False, True)])
+def test_debug_checks_accept_good_streams_and_catch_a_corrupted_one(partition, narrow, compressor):
+    """Debug checks: every stream carries the sum of a hash over its entries; the receiver recomputes it.  Clean
+    steps pass and give the same parameters as without the checks; one flipped bit in one received entry is reported by
+    the rank that received it (status 6) and by nobody else."""
+    dev = torch.device("cuda:0")
+    world = 4
+    plain = _make_ranks(world, NUMELS, compressor, "adam", partition, 0.9, dev, narrow=narrow)
+    dbg = _make_ranks(world, NUMELS, compressor, "adam", partition, 0.9, dev, narrow=narrow, debug=True)
+    LAY = dbg[0].layout
+    for step in range(1, 5):
+        grads = _grads(world, LAY, step, dev)
+        _step(plain, grads)
+        _step(dbg, grads)
+    torch.cuda.synchronize()
+    for r in range(world):
+        dbg[r].check_status()
+        assert torch.equal(dbg[r].param, plain[r].param) or float((dbg[r].param - plain[r].param).abs().max()) < 1e-6
+    # step 5 (slot 1): corrupt what rank 1 received from rank 2, between the selects and the applies
+    grads = _grads(world, LAY, 5, dev)
+    for b, g in zip(dbg, grads):
+        b.grad.copy_(g)
+    for b in dbg:
+        b.select()
+    victim, src = dbg[1], 2
+    cap = LAY.cap
+    words = victim.wiring.recv_local.view(torch.int32)[: 2 * world * cap * 2].view(2, world, cap, 2)
+    pos = LAY.owner_bounds(world)[1] if partition else LAY.segments[1].out_off     # an entry of the 70000-element tensor: wide format
+    words[1, src, pos, 1] ^= 0x00010000
+    for b in dbg:
+        b.apply(phase=1)
+    for b in dbg:
+        b.apply(phase=2)
+    torch.cuda.synchronize()
+    codes = [int(b.status.item()) for b in dbg]
+    assert codes[1] == 6, codes
+    # with partitioned state the owner that found the mismatch withholds its parameter values, so the others'
+    # bounded wait for them runs out (status 2) instead of reading values computed from a corrupted stream
+    allowed = (0, 2) if partition else (0,)
+    assert all(c in allowed for i, c in enumerate(codes) if i != 1), codes
