@@ -353,3 +353,28 @@ def test_checkpoint_module_roundtrip_and_world_change(tmp_path):
     e3.synchronize()
     for e in (e1, e2, e3):
         e.close()
+
+
+def test_engine_with_debug_checks_trains_like_without():
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+
+    def run(debug):
+        torch.manual_seed(5)
+        m = nn.Sequential(nn.Linear(40, 80), nn.ReLU(), nn.Linear(80, 5)).cuda()
+        e = SparseDPEngine(m, EngineConfig(compressor="thresholdv16", ratio=0.9, optimizer="adam", staleness=1, bucket_mb=0.01,
+                                           chunk_elems=1024, optimizer_options={"lr": 1e-2}, debug_checks=debug))
+        g = torch.Generator(device="cuda").manual_seed(9)
+        x, y = torch.randn(64, 40, device="cuda", generator=g), torch.randint(0, 5, (64,), device="cuda", generator=g)
+        for _ in range(12):
+            F.cross_entropy(m(x), y).backward()
+        e.synchronize()
+        e.check_status()
+        out = [p.detach().clone() for p in m.parameters()]
+        e.close()
+        return out
+
+    for a, b in zip(run(False), run(True)):
+        assert torch.equal(a, b)
