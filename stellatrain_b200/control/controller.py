@@ -42,10 +42,11 @@ class Client:
 
 class Controller:
     def __init__(self, port: int = 5556, host: str = "0.0.0.0", adapt: Optional[bool] = None,
-                 profile_path: Optional[str] = None, transport: str = "nvlink") -> None:
+                 profile_path: Optional[str] = None, transport: str = "nvlink", state_path: Optional[str] = None) -> None:
         self.adapt = (os.environ.get("DISABLE_RATE_ADAPT", "0") in ("", "0")) if adapt is None else adapt
         self.profile = load_profile(profile_path or os.environ.get("MODEL_PROFILE"))
         self.transport = transport
+        self.state_path = state_path      # optimiser state is written here after every instruction and read back at start
         self.sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
         self.sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
         self.sock.bind((host, port))
@@ -135,6 +136,36 @@ class Controller:
             for gid, c in self.clients.items():
                 if gid < gi.num_gpus:
                     self.optimizer.set_max_batch(gid, max_batch_for(c.gpu_name))
+            self._restore_state()
+
+    # ---------------------------------------------------------------- persistence
+    def save_state(self) -> None:
+        """Atomic write of the optimiser's state (fitted curves, phase, instruction history); the reference keeps
+        all of it in memory only (backend/src/engine/batch_rate_alloc_optim.py:117-162)."""
+        if not self.state_path or self.optimizer is None:
+            return
+        import pickle
+
+        tmp = self.state_path + ".tmp"
+        try:
+            with open(tmp, "wb") as f:
+                pickle.dump({"optimizer": self.optimizer.state_dict(), "latest_iter": self.latest_iter}, f)
+            os.replace(tmp, self.state_path)
+        except OSError:
+            pass
+
+    def _restore_state(self) -> None:
+        if not self.state_path or not os.path.exists(self.state_path) or self.optimizer is None:
+            return
+        import pickle
+
+        try:
+            with open(self.state_path, "rb") as f:
+                sd = pickle.load(f)
+            self.optimizer.load_state_dict(sd["optimizer"])
+            self.latest_iter = max(self.latest_iter, int(sd.get("latest_iter", 0)))
+        except (OSError, ValueError, KeyError, pickle.UnpicklingError):
+            pass      # a state file of another job (different number of GPUs) or a damaged one: start afresh
 
     def _update_scoreboard(self, t: M.LocalTelemetry) -> dict:
         m, c = t.measurement, t.config
@@ -183,6 +214,7 @@ class Controller:
                         msg = M.Instruction(inst.iter, M.TrainConfig(int(inst.batch[gid]), 1, float(inst.comp_ratio)))
                         c.pending.put(msg)
                         self.issued.append(msg)
+                self.save_state()
             if time.time() - last_dump > 2.0:
                 last_dump = time.time()
                 try:
@@ -210,9 +242,10 @@ def main() -> None:
     ap.add_argument("--port", type=int, default=5556)
     ap.add_argument("--profile", default=None)
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "tcp"])
+    ap.add_argument("--state-file", default=None, help="optimiser state is kept here across restarts of the controller")
     args = ap.parse_args()
     _single_instance(args.port)
-    c = Controller(args.port, profile_path=args.profile, transport=args.transport).start()
+    c = Controller(args.port, profile_path=args.profile, transport=args.transport, state_path=args.state_file).start()
     try:
         while not c.stop.is_set():
             time.sleep(0.2)

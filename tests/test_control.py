@@ -189,3 +189,29 @@ def test_optimizer_state_survives_a_restart():
         if ia is not None:
             assert ia.iter == ib.iter and np.allclose(ia.batch, ib.batch) and ia.comp_ratio == pytest.approx(ib.comp_ratio)
             batches_a, batches_b = ia.batch.copy(), ib.batch.copy()
+
+
+def test_controller_keeps_its_state_across_a_restart(tmp_path):
+    from stellatrain_b200.control import messages as M
+    from stellatrain_b200.control.controller import Controller
+
+    path = str(tmp_path / "controller.state")
+    gi = M.GlobalInit(num_nodes=1, num_gpus=2, param_counts=[1000, 2000], grad_fp16=False, grad_idx_u16=False)
+    a = Controller(port=0, host="127.0.0.1", adapt=True, state_path=path)
+    try:
+        a._on_global_init(gi)
+        a.optimizer.alphas[:] = [12.5, 30.0]
+        a.optimizer.phase = Phase.RUNNING
+        a.latest_iter = 77
+        a.save_state()
+    finally:
+        a.close()
+    b = Controller(port=0, host="127.0.0.1", adapt=True, state_path=path)
+    try:
+        b._on_global_init(gi)
+        assert b.optimizer.alphas.tolist() == [12.5, 30.0] and b.optimizer.phase == Phase.RUNNING and b.latest_iter == 77
+        # a state file of a job with another number of GPUs is ignored
+        b._on_global_init(M.GlobalInit(num_nodes=1, num_gpus=3, param_counts=[1000], grad_fp16=False, grad_idx_u16=False))
+        assert len(b.optimizer.alphas) == 3 and b.optimizer.phase == Phase.INIT_WARMUP
+    finally:
+        b.close()
