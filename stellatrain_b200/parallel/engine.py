@@ -94,6 +94,12 @@ class SparseDPEngine:
         params = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
         if not params:
             raise ValueError("module has no trainable parameters")
+        odd = [n for n, p in params if p.dtype != torch.float32]
+        if odd:
+            # residuals, moments and the master copy are fp32, as in the reference (backend/src/engine/core.cpp:807-830);
+            # reduced-precision compute belongs in autocast, which leaves the parameters alone
+            raise TypeError(f"the engine keeps fp32 master parameters; {odd[0]} is {dict(params)[odd[0]].dtype} "
+                            f"({len(odd)} such tensors): use torch.autocast for bf16/fp16 compute")
         self.device = device or params[0][1].device
         if self.device.type != "cuda":
             raise RuntimeError("the GPU-resident engine needs CUDA parameters; use the CPU tier otherwise")
