@@ -364,6 +364,18 @@ class SparseDPEngine:
             # replays of a captured step serialise on their stream, which already orders this
             # forward after every update of the previous replay
             return
+        if torch.is_grad_enabled() and not getattr(self, "_warned_unused", False):
+            for bi, rt in enumerate(self.buckets):
+                if rt.pending % len(rt.params):
+                    # a finished backward leaves every bucket a whole number of micro-iterations short
+                    import warnings
+
+                    self._warned_unused = True
+                    warnings.warn(f"bucket {bi}: {rt.pending % len(rt.params)} of {len(rt.params)} parameters received no "
+                                  f"gradient in the last backward pass; their bucket is exchanged only when all of them "
+                                  f"have one (every parameter must take part in every iteration, as in the reference, "
+                                  f"whose forward gate would wait for such a tensor forever)", RuntimeWarning, stacklevel=3)
+                    break
         cur = torch.cuda.current_stream(self.device)
         for bi, rt in enumerate(self.buckets):
             if bi in self._gated:
