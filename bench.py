@@ -39,7 +39,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_sparse", "ddp", "dense_single"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_sparse", "ddp", "dense_single", "dense_graph"],
+                    help="dense_graph: plain PyTorch step with capturable Adam/SGD captured in one CUDA graph (1 GPU), the "
+                         "strongest dense baseline for the N = 1 point")
     ap.add_argument("--model", default="resnet152")
     ap.add_argument("--batch", type=int, default=32, help="per-GPU batch size")
     ap.add_argument("--num-classes", type=int, default=100)
@@ -201,8 +203,10 @@ def main() -> None:
         net = model
         if args.impl == "ddp" and world > 1:
             net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True)
-        opt = (torch.optim.Adam(model.parameters(), lr=args.lr) if args.optimizer == "adam"
-               else torch.optim.SGD(model.parameters(), lr=args.lr, momentum=0.9))
+        if args.impl == "dense_graph" and world > 1:
+            raise SystemExit("--impl dense_graph is a single-GPU arm")
+        opt = (torch.optim.Adam(model.parameters(), lr=args.lr, capturable=(args.impl == "dense_graph"))
+               if args.optimizer == "adam" else torch.optim.SGD(model.parameters(), lr=args.lr, momentum=0.9))
 
     gen = torch.Generator().manual_seed(100 + rank)
     n_host = 4
@@ -268,9 +272,24 @@ def main() -> None:
             sys.stderr.write(f"[bench] CUDA graph capture failed ({e!r}); running eagerly\n")
             args.graph = 0
 
+    dense_graph, dense_loss = None, None
+    if args.impl == "dense_graph":
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                train_step(dev_x, dev_y)
+        torch.cuda.current_stream().wait_stream(side)
+        dense_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(dense_graph):
+            dense_loss = train_step(dev_x, dev_y)
+
     def run_step_device():
         if graphed is not None:
             return graphed.replay()
+        if dense_graph is not None:
+            dense_graph.replay()
+            return dense_loss
         return train_step(dev_x, dev_y)
 
     # End to end, the way a user feeds the model: the package's PrefetchLoader copies batch i+1 from pinned host
@@ -283,6 +302,11 @@ def main() -> None:
         if graphed is not None:
             graphed.copy_inputs(x, y)          # device to device, into the graph's input buffers
             loss = graphed.replay()
+        elif dense_graph is not None:
+            dev_x.copy_(x, non_blocking=True)
+            dev_y.copy_(y, non_blocking=True)
+            dense_graph.replay()
+            loss = dense_loss
         else:
             loss = train_step(x, y)
         loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
@@ -341,7 +365,7 @@ def main() -> None:
                "ms_per_step": ms2 / args.steps, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
                "clocks": clocks2}
 
-    final_loss = float(train_step(dev_x, dev_y).detach()) if graphed is None else float(graphed.replay().detach())
+    final_loss = float(run_step_device().detach())
     if engine is not None:
         engine.synchronize()
         engine.check_status()
@@ -367,7 +391,7 @@ def main() -> None:
                                 "shaped_gbps_achieved": (engine.shaper.achieved_gbps() if engine.shaper else None)}
                                if hook is not None else None),
                 "multicast": bool(engine is not None and engine.pool is not None and engine.pool.mc_ptr),
-                "cuda_graph": bool(args.graph), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
+                "cuda_graph": bool(args.graph) if engine is not None else (args.impl == "dense_graph"), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
                 "l2": "per-step working set (233 MB of parameters plus activations) exceeds the 126 MB L2; no flush needed",
             },
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,
