@@ -354,11 +354,34 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
   __shared__ __align__(8) uint64_t s_bar[2];
   if (ld_volatile_u32(A.status) != kOk) return;
 
+  // The tiles need nothing but the chunk's place: start their copies first, so that they travel while the
+  // tensor's descriptor, work record and threshold state (a second level of dependent loads) are fetched.
   const Chunk ch = A.chunks[blockIdx.x];
+  float* r = A.resid + ch.start;
+  const uint32_t n_tiles = (ch.len + kP2PerIter - 1) / kP2PerIter;
+  auto issue_tile = [&](uint32_t t) {     // thread 0 only
+    const uint32_t elems = min(kP2PerIter, ch.len - t * kP2PerIter);
+    mbar_expect_tx(&s_bar[t & 1u], elems * 4u);
+    bulk_load(&s_tile[t & 1u][0], r + (size_t)t * kP2PerIter, elems * 4u, &s_bar[t & 1u]);
+  };
+  if (threadIdx.x == 0) {
+    mbar_init(&s_bar[0], 1);
+    mbar_init(&s_bar[1], 1);
+    mbar_init_fence();
+    issue_tile(0);
+    if (n_tiles > 1) issue_tile(1);
+  }
+  __syncthreads();   // the barriers are initialised before anyone waits on them
+
   const SegDesc sd = A.segs[ch.seg];
   SegWork* wp = &A.work[ch.seg];
   const uint32_t mode = wp->mode;
-  if (mode == kModeNone) return;
+  if (mode == kModeNone) {
+    // nothing to do for this tensor, but no copy into this CTA's shared memory may outlive it
+    mbar_wait_bounded(&s_bar[0], 0u);
+    if (n_tiles > 1) mbar_wait_bounded(&s_bar[1], 0u);
+    return;
+  }
   const uint32_t thr_bin = wp->thr_bin;
   const uint32_t tau_bits = wp->tau_bits;
   const uint32_t cand_off = wp->cand_off;
@@ -369,7 +392,6 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
   const uint32_t nb = narrow_base_of(sd);
   const uint32_t kk = B16 ? (sd.k + 15u) / 16u : sd.k;
   const uint32_t base_pos = A.chunk_pos[blockIdx.x];
-  float* r = A.resid + ch.start;
   bool emitted = false;
   uint32_t running = 0;
   uint32_t fill_sel = 0, fill_cnd = 0;   // uniform over the CTA
@@ -424,24 +446,7 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
     __syncthreads();
   };
 
-  // Tiles of 4096 elements travel global -> shared by TMA bulk copies, two in flight.
-  const uint32_t n_tiles = (ch.len + kP2PerIter - 1) / kP2PerIter;
-  auto issue_tile = [&](uint32_t t) {     // thread 0 only
-    const uint32_t elems = min(kP2PerIter, ch.len - t * kP2PerIter);
-    mbar_expect_tx(&s_bar[t & 1u], elems * 4u);
-    bulk_load(&s_tile[t & 1u][0], r + (size_t)t * kP2PerIter, elems * 4u, &s_bar[t & 1u]);
-  };
-  if (threadIdx.x == 0) {
-    mbar_init(&s_bar[0], 1);
-    mbar_init(&s_bar[1], 1);
-    mbar_init_fence();
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    issue_tile(0);
-    if (n_tiles > 1) issue_tile(1);
-  }
-
+  // Tiles of 4096 elements travel global -> shared by TMA bulk copies, two in flight (started above).
   for (uint32_t tile = 0; tile < n_tiles; ++tile) {
     const uint32_t it = tile * kP2PerIter;
     const uint32_t i = it + threadIdx.x * kP2PerThread;
