@@ -1,6 +1,7 @@
 #include "comm_manager.h"
 
 #include <poll.h>
+#include <cstdio>
 #include <unistd.h>
 
 #include <chrono>
@@ -219,7 +220,7 @@ void CommManager::broker_main(int world) {
           res.success = 1;
           res.target_port = succ->req.listen_port;
           res.target_rank = succ->req.rank;
-          std::strncpy(res.target_ip, succ->req.ip, sizeof(res.target_ip) - 1);
+          std::snprintf(res.target_ip, sizeof(res.target_ip), "%s", succ->req.ip);   // always terminated
           send_frame(kv.second->fd, kInitRes, "", 0, &res, sizeof(res), timeout_ms_);
         }
         ring_sent = true;

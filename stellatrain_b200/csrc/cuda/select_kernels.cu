@@ -392,7 +392,6 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
   const uint32_t nb = narrow_base_of(sd);
   const uint32_t kk = B16 ? (sd.k + 15u) / 16u : sd.k;
   const uint32_t base_pos = A.chunk_pos[blockIdx.x];
-  bool emitted = false;
   uint32_t running = 0;
   uint32_t fill_sel = 0, fill_cnd = 0;   // uniform over the CTA
   // key range of the threshold bin: [key_lo, key_hi); keys are below 2^31, so 2^31 stands for "none above"
@@ -440,7 +439,6 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
       }
     }
     for (uint32_t j = threadIdx.x; j < fill_cnd; j += kThreads) A.cand[cand_off + b_cnd + j] = s_cnd[j];
-    if (fill_sel) emitted = true;
     fill_sel = 0;
     fill_cnd = 0;
     __syncthreads();
@@ -546,12 +544,11 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd)
               *reinterpret_cast<float4*>(r + i + 4 * qd) = make_float4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
-            if (direct) emitted = true;
           }
         }
       } else {
         if (sel_mask) {
-          if (direct) { emit_block(p, gi); emitted = true; }
+          if (direct) emit_block(p, gi);
           else s_selb[p] = gi >> 4;
         }
         if (cnd_mask) {
@@ -585,7 +582,6 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd)
               *reinterpret_cast<float4*>(r + i + 4 * qd) = make_float4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
-            emitted = true;
           }
         } else if (pos < kk) {
           // a truncated last block still leaves the residual exact: only emitted elements are zeroed
@@ -600,7 +596,6 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
 #pragma unroll
           for (int qd = 0; qd < 4; ++qd)
             *reinterpret_cast<float4*>(r + i + 4 * qd) = make_float4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
-          emitted = true;
         }
       }
     }
@@ -608,7 +603,6 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
   if (mode == kModeTop && (fill_sel | fill_cnd)) flush();
   // No fence here: the arrival flag is published by the last kernel of the chain, and a kernel
   // boundary on the stream already orders these stores before anything that kernel does.
-  (void)emitted;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -726,12 +720,10 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
       }
       last_id = block_max_u32(mxid, s_tmp);
     }
-    bool emitted = false;
     for (uint32_t i = tid; i < c; i += kCandThreads) {
       const uint2 e = cand[i];
       const bool take = e.y > t_key || (e.y == t_key && e.x <= id_thr);
       if (!take) continue;
-      emitted = true;
       if (!b16) {
         const uint32_t pos = atomicAdd(&wp->out_cursor, 1u);
         if (pos < kk) {
@@ -754,7 +746,6 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
         }
       }
     }
-    (void)emitted;
     if (tid == 0) {
       SegState ss = A.state[seg];
       // Next select: centre the histogram on the threshold just found, unless it fell off the
