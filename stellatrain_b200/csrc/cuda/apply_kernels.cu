@@ -28,7 +28,7 @@ constexpr int kThreads = 256;
 
 __global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
   __shared__ int s_ok;
-  const int src = blockIdx.y;
+  const int src = blockIdx.y + A.src_first;
   const uint32_t epoch = *A.epoch;
   const uint32_t slot = epoch & 1u;
   // Nothing was selected for this epoch yet (e.g. a captured step replayed right after a flush):
@@ -231,7 +231,15 @@ cudaError_t launch_apply(const ApplyArgs& A, int max_ctas_per_source, int phase,
     if (parts < 1) parts = 1;
     if (parts > max_ctas_per_source) parts = max_ctas_per_source;
     dim3 grid(parts, A.world);
-    k_scatter<<<grid, kThreads, 0, stream>>>(A);
+    if (A.deterministic) {
+      ApplyArgs one = A;
+      for (int src = 0; src < A.world; ++src) {   // one launch per source: a fixed order of additions
+        one.src_first = (uint32_t)src;
+        k_scatter<<<dim3(parts, 1), kThreads, 0, stream>>>(one);
+      }
+    } else {
+      k_scatter<<<grid, kThreads, 0, stream>>>(A);
+    }
     k_apply<<<grid, kThreads, 0, stream>>>(A);
   }
   if (A.owner_mode && (phase == 0 || phase == 2)) {

@@ -159,11 +159,13 @@ struct BucketHandle {
   }
 
   // narrow: some tensors of the bucket carry the narrow-wire flag in their descriptor
-  void set_options(uint32_t compressor, bool zero_grad, bool skip_ef, bool narrow) {
+  void set_options(uint32_t compressor, bool zero_grad, bool skip_ef, bool narrow, bool deterministic) {
     sel.compressor = compressor;
     sel.zero_grad = zero_grad ? 1u : 0u;
     sel.skip_ef = skip_ef ? 1u : 0u;
     app.narrow = narrow ? 1u : 0u;
+    app.deterministic = deterministic ? 1u : 0u;   // one scatter launch per source, in rank order
+    app.src_first = 0u;
   }
 
   // grouped mode -------------------------------------------------------------------------------
@@ -267,7 +269,7 @@ PYBIND11_MODULE(_C, m) {
            py::arg("peer_recv"), py::arg("recv_mc"), py::arg("flag_local"), py::arg("peer_flag"),
            py::arg("ack_local"), py::arg("peer_ack"), py::arg("use_flags"), py::arg("use_acks"))
       .def("set_options", &BucketHandle::set_options, py::arg("compressor"), py::arg("zero_grad"),
-           py::arg("skip_ef") = false, py::arg("narrow") = false)
+           py::arg("skip_ef") = false, py::arg("narrow") = false, py::arg("deterministic") = false)
       .def_readwrite("randomk_seed", &BucketHandle::randomk_seed)
       .def_readwrite("max_ctas_per_source", &BucketHandle::max_ctas_per_source)
       .def("set_group", &BucketHandle::set_group, py::arg("grad_local"), py::arg("mate_grad"), py::arg("mate_local"),

@@ -185,6 +185,11 @@ struct ApplyArgs {
   // compares it with the word the source stored and reports kBadChecksum; with `poison` every consumed entry
   // of a wide stream is overwritten with the "no entry" marker, so a position a source fails to rewrite
   // can never be taken for fresh data.
+  // Deterministic merge: the scatter runs once per source, in rank order, so that every replica adds an
+  // element's contributions in the same order and replicas stay bit-equal (three or more contributions to
+  // one element otherwise round differently from GPU to GPU).  src_first is the source of the current launch.
+  uint32_t deterministic;
+  uint32_t src_first;
   const uint32_t* cksum_local;      // [2][world] written by the sources
   uint32_t* rsum;                   // [world]
   uint32_t poison;

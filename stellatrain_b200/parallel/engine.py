@@ -54,6 +54,8 @@ class EngineConfig:
                                           # to the tensor, bf16 value; the rounding error stays in the residual)
     fine_grained_gating: bool = False     # wait per first-using module instead of at the root
     status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
+    deterministic_merge: bool = False     # add the sources' contributions in rank order (one scatter launch per source):
+                                          # replicas with replicated state stay bit-equal; world - 1 more launches per bucket
     debug_checks: bool = False            # every stream carries a checksum that the receiver verifies (status 6), consumed
                                           # entries are overwritten with the "no entry" marker; slower, for debugging
     profile: bool = False                 # NVTX ranges and CUDA-event timers per bucket and stage (utils/stats.py)
@@ -171,7 +173,7 @@ class SparseDPEngine:
                 smart_momentum=cfg.smart_momentum, min_ratio=cfg.min_ratio, scratch=self.scratch,
                 timeout_s=cfg.timeout_s, divide_k_by_world=cfg.divide_k_by_world,
                 k_world=(self.groups if (self.group_size > 1 and cfg.divide_k_by_world) else None),
-                partition_state=self.partitioned,
+                partition_state=self.partitioned, deterministic_merge=cfg.deterministic_merge,
             )
             if self.group_size > 1:
                 layout.assign_owners(self.group_size, self.my_local)

@@ -94,6 +94,7 @@ class GpuBucket:
         divide_k_by_world: bool = True,
         k_world: Optional[int] = None,
         partition_state: bool = False,
+        deterministic_merge: bool = False,
     ) -> None:
         self.index = index
         self.layout = layout
@@ -105,6 +106,7 @@ class GpuBucket:
         self.min_ratio = ratio if min_ratio is None else min(min_ratio, ratio)
         self.optimizer = optimizer
         self.timeout_ns = int(timeout_s * 1e9)
+        self.deterministic_merge = bool(deterministic_merge)   # scatter one source after the other: bit-equal replicas
         n = layout.n_total
         f32 = dict(dtype=torch.float32, device=device)
         self.grad = torch.zeros(n, **f32)
@@ -192,7 +194,7 @@ class GpuBucket:
             weight=self.weight.data_ptr(), timeout_ns=self.timeout_ns,
         )
         h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False,
-                      any(self.layout.is_narrow(s) for s in self.layout.segments))
+                      any(self.layout.is_narrow(s) for s in self.layout.segments), self.deterministic_merge)
         if wiring is not None:
             self._apply_wiring(h, wiring)
 
@@ -301,7 +303,7 @@ class GpuBucket:
 
     @property
     def apply_kernels(self) -> int:
-        return 3 if self.partition_state else 2
+        return (3 if self.partition_state else 2) + (self.world - 1 if self.deterministic_merge else 0)
 
     def check_status(self) -> None:
         code = int(self.status.item())

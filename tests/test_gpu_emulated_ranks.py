@@ -10,7 +10,8 @@ pytestmark = pytest.mark.gpu
 NUMELS = [5000, 70000, 130, 40000, 16, 9000]
 
 
-def _make_ranks(world, numels, compressor, optimizer, partition, ratio, dev, lr=1e-2, narrow=False, debug=False):
+def _make_ranks(world, numels, compressor, optimizer, partition, ratio, dev, lr=1e-2, narrow=False, debug=False,
+                deterministic=False):
     from stellatrain_b200.parallel import buckets as B
     from stellatrain_b200.parallel.gpu_bucket import CandidateScratch, GpuBucket, Wiring
 
@@ -19,7 +20,8 @@ def _make_ranks(world, numels, compressor, optimizer, partition, ratio, dev, lr=
     for r in range(world):
         layout = B.BucketLayout([f"t{i}" for i in range(len(numels))], list(numels), chunk_elems=1024, narrow_wire=narrow)
         ranks.append(GpuBucket(0, layout, dev, compressor=compressor, ratio=ratio, world=world, rank=r,
-                               optimizer=optimizer, scratch=scratch, timeout_s=1.0, partition_state=partition))
+                               optimizer=optimizer, scratch=scratch, timeout_s=1.0, partition_state=partition,
+                               deterministic_merge=deterministic, divide_k_by_world=not deterministic))
     nbytes = ranks[0].recv_bytes()
     mk8 = lambda: torch.zeros(nbytes, dtype=torch.uint8, device=dev)       # noqa: E731
     mkf = lambda: torch.zeros(2 * world, dtype=torch.int64, device=dev)    # noqa: E731
@@ -234,3 +236,19 @@ def test_debug_checks_accept_good_streams_and_catch_a_corrupted_one(partition, n
     # bounded wait for them runs out (status 2) instead of reading values computed from a corrupted stream
     allowed = (0, 2) if partition else (0,)
     assert all(c in allowed for i, c in enumerate(codes) if i != 1), codes
+
+
+def test_deterministic_merge_keeps_replicas_bit_equal():
+    """Every rank keeps half of every tensor (k is not divided by the world size here), so most elements receive three or
+    four contributions; added in rank order they round the same way on every replica."""
+    dev = torch.device("cuda:0")
+    world = 4
+    ranks = _make_ranks(world, NUMELS, "topk", "adam", False, 0.5, dev, deterministic=True)
+    LAY = ranks[0].layout
+    for step in range(1, 7):
+        _step(ranks, _grads(world, LAY, step, dev))
+    torch.cuda.synchronize()
+    for b in ranks:
+        b.check_status()
+        assert torch.equal(b.param, ranks[0].param) and torch.equal(b.m, ranks[0].m) and torch.equal(b.v, ranks[0].v)
+    assert float((ranks[0].param - torch.randn(LAY.n_total, device=dev, generator=torch.Generator(device=dev).manual_seed(7))).abs().max()) > 0
