@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
       if (!ok) set_status(A.status, kTimeoutFlag);
     }
     s_ok = ok;
+    if (A.stamps != nullptr && blockIdx.x == 0 && src == 0) A.stamps[2] = global_timer_ns();
   }
   __syncthreads();
   if (!s_ok) return;
@@ -82,6 +83,10 @@ __device__ __forceinline__ void finish_apply(const ApplyArgs& A, uint32_t epoch,
   A.opt->tick = tick + 1u;
   A.opt->first = 0u;
   *A.epoch = epoch + 1u;
+  if (A.stamps != nullptr) {
+    A.stamps[3] = global_timer_ns();
+    A.stamps[5] = epoch;
+  }
 }
 
 __global__ void __launch_bounds__(kThreads) k_apply(ApplyArgs A) {

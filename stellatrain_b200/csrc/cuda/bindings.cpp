@@ -75,7 +75,7 @@ struct BucketHandle {
   }
 
   // counters: [sel_epoch, app_epoch, sel_done, app_done] as four u32 words; status: one u32 word
-  void set_control(uint64_t counters, uint64_t status, uint64_t opt, uint64_t weight, uint64_t timeout_ns) {
+  void set_control(uint64_t counters, uint64_t status, uint64_t opt, uint64_t weight, uint64_t timeout_ns, uint64_t stamps) {
     uint32_t* c = as_ptr<uint32_t>(counters);
     sel.epoch = c + 0;
     app.epoch = c + 1;
@@ -86,6 +86,7 @@ struct BucketHandle {
     app.opt = as_ptr<st::OptState>(opt);
     app.weight = as_ptr<const float>(weight);
     sel.timeout_ns = app.timeout_ns = timeout_ns;
+    sel.stamps = app.stamps = as_ptr<uint64_t>(stamps);   // 8 u64 words or null
   }
 
   // Exchange wiring.  recv_local: this rank's receive area [2][world][cap] of (idx,val) pairs.
@@ -264,7 +265,7 @@ PYBIND11_MODULE(_C, m) {
            py::arg("n_chunks"), py::arg("cap"))
       .def("set_scratch", &BucketHandle::set_scratch, py::arg("cand"), py::arg("cand_cursor"), py::arg("cand_cap"))
       .def("set_control", &BucketHandle::set_control, py::arg("counters"), py::arg("status"), py::arg("opt"),
-           py::arg("weight"), py::arg("timeout_ns"))
+           py::arg("weight"), py::arg("timeout_ns"), py::arg("stamps") = 0)
       .def("set_comm", &BucketHandle::set_comm, py::arg("world"), py::arg("rank"), py::arg("recv_local"),
            py::arg("peer_recv"), py::arg("recv_mc"), py::arg("flag_local"), py::arg("peer_flag"),
            py::arg("ack_local"), py::arg("peer_ack"), py::arg("use_flags"), py::arg("use_acks"))

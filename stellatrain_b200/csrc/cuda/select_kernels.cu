@@ -110,7 +110,10 @@ __global__ void __launch_bounds__(kThreads) k_pass1(SelectArgs A) {
   const uint32_t tau_bits = __float_as_uint(ss.tau);
   const HistWindow win = window_of(ss);
 
-  if (blockIdx.x == 0 && threadIdx.x == 0) *A.cand_cursor = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *A.cand_cursor = 0;
+    if (A.stamps != nullptr) A.stamps[0] = global_timer_ns();
+  }
   if (sd.reserved & kSegSkip) {
     // a tensor another rank of the group is responsible for: only clear the consumed gradient
     if (A.zero_grad && A.grad_tab == nullptr) {
@@ -612,6 +615,10 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
 // the accumulators for the next select.  Called by the one thread that publishes the arrival flags, before
 // them (their release orders these stores too).
 __device__ __forceinline__ void publish_checksums(const SelectArgs& A, uint32_t epoch) {
+  if (A.stamps != nullptr) {
+    A.stamps[1] = global_timer_ns();
+    A.stamps[4] = epoch;
+  }
   if (A.cksum_acc == nullptr) return;
   for (int p = 0; p < A.world; ++p) {
     const uint32_t sum = atomicAdd(A.cksum_acc + (A.owner_mode ? p : 0), 0u);
@@ -858,6 +865,7 @@ __global__ void __launch_bounds__(kThreads) k_ef_only(SelectArgs A) {
   float* g = tab ? A.grad_tab[ch.seg] + seg_rel : A.grad + ch.start;
   const uint32_t g_valid = tab ? (sd.n > seg_rel ? min(ch.len, sd.n - seg_rel) : 0u) : ch.len;
   float* r = A.resid + ch.start;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && A.stamps != nullptr) A.stamps[0] = global_timer_ns();
   if (blockIdx.x == 0 && threadIdx.x == 0 && A.use_acks) {
     const uint32_t epoch = *A.epoch;
     if (epoch > 2) {

@@ -139,6 +139,10 @@ struct SelectArgs {
   uint32_t* done_ctr;          // CTA completion counter of the last kernel of the chain
   uint32_t* status;            // Status
   uint64_t timeout_ns;
+  // Device clock (globaltimer, ns) of the latest chain, or null: [0] select start, [1] select end (stream
+  // complete, flags published), [2] apply start (first stream seen), [3] apply end, [4] epoch of the
+  // select, [5] epoch of the apply.  Feeds the telemetry (push duration, exposed wait).
+  uint64_t* stamps;
 };
 
 struct ApplyArgs {
@@ -190,6 +194,7 @@ struct ApplyArgs {
   // one element otherwise round differently from GPU to GPU).  src_first is the source of the current launch.
   uint32_t deterministic;
   uint32_t src_first;
+  uint64_t* stamps;                 // see SelectArgs::stamps
   const uint32_t* cksum_local;      // [2][world] written by the sources
   uint32_t* rsum;                   // [world]
   uint32_t poison;

@@ -490,6 +490,11 @@ class SparseDPEngine:
         self.sparse_stream.synchronize()
         self.check_status()
 
+    def device_timeline(self) -> list:
+        """Per bucket: device-clock durations of the latest select + push and apply (``GpuBucket.device_times``)."""
+        self.sparse_stream.synchronize()
+        return [rt.bucket.device_times() for rt in self.buckets]
+
     def export_stats(self, path: Optional[str] = None) -> str:
         """Per-bucket stage times as JSON ``{"<iteration>@bucket<i>": {"Select": ms, "Apply": ms}}``
         (the reference writes /tmp/time_log_<timestamp>_<pid>.json, backend/src/engine/core.cpp:1176-1207)."""

@@ -143,6 +143,7 @@ class GpuBucket:
         self.hist = torch.zeros(n_segs * 2048, dtype=torch.int32, device=device)
         self.counters = torch.tensor([1, 1, 0, 0], dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.stamps = torch.zeros(8, dtype=torch.int64, device=device)    # device clock of the latest chain, see device_times()
         self.weight = torch.full((world,), 1.0 / world, **f32)
         opt = np.zeros(1, dtype=B.OPT_STATE_DTYPE)
         opt["lr"] = 1e-3
@@ -191,7 +192,7 @@ class GpuBucket:
         self.scratch.bind(h)
         h.set_control(
             counters=self.counters.data_ptr(), status=self.status.data_ptr(), opt=self.opt.data_ptr(),
-            weight=self.weight.data_ptr(), timeout_ns=self.timeout_ns,
+            weight=self.weight.data_ptr(), timeout_ns=self.timeout_ns, stamps=self.stamps.data_ptr(),
         )
         h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False,
                       any(self.layout.is_narrow(s) for s in self.layout.segments), self.deterministic_merge)
@@ -304,6 +305,14 @@ class GpuBucket:
     @property
     def apply_kernels(self) -> int:
         return (3 if self.partition_state else 2) + (self.world - 1 if self.deterministic_merge else 0)
+
+    def device_times(self) -> dict:
+        """Device-clock view of the latest select and apply of this bucket, in milliseconds (blocking read):
+        how long select + push took, how long the apply ran, and for which epochs the numbers stand."""
+        t = self.stamps.cpu().tolist()
+        return {"select_ms": max(0, t[1] - t[0]) / 1e6, "apply_ms": max(0, t[3] - t[2]) / 1e6,
+                "select_epoch": t[4], "apply_epoch": t[5],
+                "select_end_to_apply_start_ms": (t[2] - t[1]) / 1e6 if t[4] == t[5] else None}
 
     def check_status(self) -> None:
         code = int(self.status.item())

@@ -372,6 +372,10 @@ def test_engine_with_debug_checks_trains_like_without():
             F.cross_entropy(m(x), y).backward()
         e.synchronize()
         e.check_status()
+        for row in e.device_timeline():      # device clock of the last select + push and apply of every bucket
+            assert 0.0 < row["select_ms"] < 50.0 and 0.0 < row["apply_ms"] < 50.0, row
+            assert row["select_epoch"] == row["apply_epoch"] == 12, row
+            assert row["select_end_to_apply_start_ms"] is not None
         out = [p.detach().clone() for p in m.parameters()]
         e.close()
         return out
