@@ -70,13 +70,20 @@ uint32_t select_top_generic(size_t n, size_t k, ThreadPool* pool, KeyFn key, std
     above += hist[thr_bin];
   }
   const size_t k_rem = k - above;
-  // candidates of the threshold bin
+  // One more pass: positions whose bin lies above the threshold bin (ascending inside a range, ranges are
+  // ascending themselves) and the candidates inside the bin.
+  std::vector<std::vector<uint32_t>> above_parts(parts);
   std::vector<std::vector<std::pair<uint32_t, uint32_t>>> cparts(parts);   // (key, pos)
   run_ranges(pool, n, [&](size_t p, size_t b, size_t e) {
+    auto& up = above_parts[p];
     auto& c = cparts[p];
+    up.reserve((e - b) / 64 + 16);
     for (size_t i = b; i < e; ++i) {
       const uint32_t kx = key(i);
-      if (static_cast<int>(kx >> kShift) == thr_bin) c.emplace_back(kx, static_cast<uint32_t>(i));
+      const int bin = static_cast<int>(kx >> kShift);
+      if (bin < thr_bin) continue;
+      if (bin > thr_bin) up.push_back(static_cast<uint32_t>(i));
+      else c.emplace_back(kx, static_cast<uint32_t>(i));
     }
   }, parts);
   std::vector<std::pair<uint32_t, uint32_t>> cand;
@@ -84,27 +91,17 @@ uint32_t select_top_generic(size_t n, size_t k, ThreadPool* pool, KeyFn key, std
   auto better = [](const std::pair<uint32_t, uint32_t>& a, const std::pair<uint32_t, uint32_t>& b) {
     return a.first != b.first ? a.first > b.first : a.second < b.second;
   };
+  // after nth_element the first k_rem candidates are the k_rem best: larger key first, ties towards the lower position
   std::nth_element(cand.begin(), cand.begin() + (k_rem - 1), cand.end(), better);
-  const uint32_t t_key = cand[k_rem - 1].first, pos_thr = cand[k_rem - 1].second;
-  // ordered compaction
-  std::vector<size_t> counts(parts, 0);
-  auto taken = [&](size_t i) {
-    const uint32_t kx = key(i);
-    return kx > t_key || (kx == t_key && i <= pos_thr);
-  };
-  run_ranges(pool, n, [&](size_t p, size_t b, size_t e) {
-    size_t c = 0;
-    for (size_t i = b; i < e; ++i) c += taken(i);
-    counts[p] = c;
-  }, parts);
-  std::vector<size_t> offs(parts + 1, 0);
-  for (size_t p = 0; p < parts; ++p) offs[p + 1] = offs[p] + counts[p];
-  out_pos.resize(offs[parts]);
-  run_ranges(pool, n, [&](size_t p, size_t b, size_t e) {
-    size_t o = offs[p];
-    for (size_t i = b; i < e; ++i)
-      if (taken(i)) out_pos[o++] = static_cast<uint32_t>(i);
-  }, parts);
+  const uint32_t t_key = cand[k_rem - 1].first;
+  std::vector<uint32_t> from_bin(k_rem);
+  for (size_t j = 0; j < k_rem; ++j) from_bin[j] = cand[j].second;
+  std::sort(from_bin.begin(), from_bin.end());
+  std::vector<uint32_t> from_above;
+  from_above.reserve(above);
+  for (auto& up : above_parts) from_above.insert(from_above.end(), up.begin(), up.end());
+  out_pos.resize(from_above.size() + from_bin.size());
+  std::merge(from_above.begin(), from_above.end(), from_bin.begin(), from_bin.end(), out_pos.begin());
   return t_key;
 }
 
@@ -339,9 +336,14 @@ size_t compress_with_feedback(Compressor& c, const std::string& tensor, const fl
                               uint32_t k, uint32_t* dst_idx, float* dst_val, ThreadPool* pool) {
   size_t parts = 1;
   run_ranges(pool, n, [&](size_t, size_t b, size_t e) {
-    add_arrays_to(resid + b, resid + b, grad + b, e - b);
-    for (size_t i = b; i < e; ++i)
-      if (resid[i] != resid[i]) resid[i] = 0.f;
+    // block by block, so that the NaN scan finds the sums still in the first-level cache
+    constexpr size_t kBlock = 4096;
+    for (size_t i0 = b; i0 < e; i0 += kBlock) {
+      const size_t i1 = std::min(e, i0 + kBlock);
+      add_arrays_to(resid + i0, resid + i0, grad + i0, i1 - i0);
+      for (size_t i = i0; i < i1; ++i)
+        if (resid[i] != resid[i]) resid[i] = 0.f;
+    }
   }, parts);
   const size_t cnt = c.compress(tensor, resid, n, k, dst_idx, dst_val, 0);
   for (size_t j = 0; j < cnt; ++j) resid[dst_idx[j]] = 0.f;
