@@ -7,8 +7,8 @@
 //   sparse SGD / sparse Adam        backend/src/optim/sgd.cpp:221-262, backend/src/optim/adam.cpp:19-87
 //   H2D copy of updated parameters  backend/src/engine/modules/h2d_copy.cpp:31-56  (no longer needed)
 // by two kernels per bucket (three when the optimiser state is partitioned over the ranks):
-//   scatter  each CTA waits (bounded) for the arrival flag of the source it serves, then adds the
-//            source's weighted values into a dense accumulator with red.global.add.f32
+//   wait     one warp waits (bounded) for the arrival flags of all sources (only when flags are in use)
+//   scatter  adds every source's weighted values into a dense accumulator with red.global.add.f32
 //   apply    walks the same streams again; the first thread to stamp an index with the current epoch
 //            owns it, reads and clears the accumulator and applies the optimiser rule once, which
 //            is the "apply once at the union of indices" contract without building the union; the
@@ -26,25 +26,32 @@ namespace {
 constexpr int kThreads = 256;
 }
 
-__global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
-  __shared__ int s_ok;
-  const int src = blockIdx.y + A.src_first;
+// One warp waits (bounded) for the arrival flags of all sources, one lane per source, and leaves the outcome
+// in the status word.  The wide scatter grid that follows in the stream therefore never sits on the SMs
+// spinning while a peer is late, which would keep the backward pass of the lower-priority compute stream out.
+__global__ void k_wait_streams(ApplyArgs A) {
   const uint32_t epoch = *A.epoch;
   const uint32_t slot = epoch & 1u;
   // Nothing was selected for this epoch yet (e.g. a captured step replayed right after a flush):
   // the chain of kernels is a no-op and leaves every counter untouched.
   if (epoch >= ld_volatile_u32(A.sel_epoch)) return;
-  if (threadIdx.x == 0) {
-    int ok = ld_volatile_u32(A.status) == kOk;
-    if (ok && A.use_flags) {
-      ok = wait_ge_bounded(A.flag_local + (size_t)slot * A.world + src, (uint64_t)epoch, A.timeout_ns);
-      if (!ok) set_status(A.status, kTimeoutFlag);
+  if (ld_volatile_u32(A.status) == kOk) {
+    for (int src = threadIdx.x; src < A.world; src += 32) {
+      if (!wait_ge_bounded(A.flag_local + (size_t)slot * A.world + src, (uint64_t)epoch, A.timeout_ns))
+        set_status(A.status, kTimeoutFlag);
     }
-    s_ok = ok;
-    if (A.stamps != nullptr && blockIdx.x == 0 && src == 0) A.stamps[2] = global_timer_ns();
   }
-  __syncthreads();
-  if (!s_ok) return;
+  __syncwarp();
+  if (threadIdx.x == 0 && A.stamps != nullptr) A.stamps[2] = global_timer_ns();
+}
+
+__global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
+  const int src = blockIdx.y + A.src_first;
+  const uint32_t epoch = *A.epoch;
+  const uint32_t slot = epoch & 1u;
+  if (epoch >= ld_volatile_u32(A.sel_epoch)) return;
+  if (ld_volatile_u32(A.status) != kOk) return;   // includes "a stream did not arrive in time"
+  if (!A.use_flags && A.stamps != nullptr && blockIdx.x == 0 && src == 0 && threadIdx.x == 0) A.stamps[2] = global_timer_ns();
   const uint2* in = A.recv + (size_t)slot * A.slot_stride + (size_t)src * A.cap;
   const float w = A.weight[src];
   uint32_t sum = 0;
@@ -236,6 +243,7 @@ cudaError_t launch_apply(const ApplyArgs& A, int max_ctas_per_source, int phase,
     if (parts < 1) parts = 1;
     if (parts > max_ctas_per_source) parts = max_ctas_per_source;
     dim3 grid(parts, A.world);
+    if (A.use_flags) k_wait_streams<<<1, 32, 0, stream>>>(A);
     if (A.deterministic) {
       ApplyArgs one = A;
       for (int src = 0; src < A.world; ++src) {   // one launch per source: a fixed order of additions

@@ -304,7 +304,8 @@ class GpuBucket:
 
     @property
     def apply_kernels(self) -> int:
-        return (3 if self.partition_state else 2) + (self.world - 1 if self.deterministic_merge else 0)
+        waits = 1 if (self.wiring is not None and self.wiring.use_flags) else 0     # the one-warp flag wait
+        return (3 if self.partition_state else 2) + (self.world - 1 if self.deterministic_merge else 0) + waits
 
     def device_times(self) -> dict:
         """Device-clock view of the latest select and apply of this bucket, in milliseconds (blocking read):
