@@ -344,6 +344,33 @@ void CpuEngine::mark_sequenced(const std::shared_ptr<TrainTask>& t) {
   if (next.first) schedule(next.first, next.second);
 }
 
+void CpuEngine::schedule_after_master_free(Module* next, const std::shared_ptr<TrainTask>& t) {
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    if (params_[t->param_index].master_read_iter < t->iter - 1) {
+      waiting_master_.emplace_back(next, t);
+      return;
+    }
+  }
+  schedule(next, t);
+}
+
+void CpuEngine::mark_master_read(const std::shared_ptr<TrainTask>& t) {
+  std::pair<Module*, std::shared_ptr<TrainTask>> next{nullptr, nullptr};
+  {
+    std::lock_guard<std::mutex> lk(version_mu_);
+    auto& p = params_[t->param_index];
+    p.master_read_iter = std::max(p.master_read_iter, t->iter);
+    for (auto it = waiting_master_.begin(); it != waiting_master_.end(); ++it)
+      if (it->second->param_index == t->param_index && it->second->iter <= p.master_read_iter + 1) {
+        next = *it;
+        waiting_master_.erase(it);
+        break;
+      }
+  }
+  if (next.first) schedule(next.first, next.second);
+}
+
 void CpuEngine::schedule_after_use(Module* next, const std::shared_ptr<TrainTask>& t) {
   const std::string slot_key = t->persistent_key + "#" + std::to_string(t->iter % 2);
   {
@@ -416,10 +443,8 @@ void CpuEngine::copy_out_done(int index, int64_t iter) {
     if (it == tasks_.end()) throw std::runtime_error("copy_out_done for an unknown task");
     t = it->second;
   }
-  t->advance(TaskState::Finished);
-  update_model_version(t);
-  return_after_use(t);
-  schedule_terminate(t);
+  // the caller has copied the master parameter out; the rest happens once every local process has
+  schedule_after_barrier(module("CopyOutDone"), t, kAfterCopyOut);
 }
 
 // Where a task currently is: its state and the gate it waits at, for timeout messages.
@@ -440,6 +465,7 @@ std::string CpuEngine::describe_task(const std::string& key) {
     std::lock_guard<std::mutex> lk(version_mu_);
     if (holds(waiting_model_)) where += ", waits for the previous version to be released";
     if (holds(waiting_prev_)) where += ", waits for the previous iteration of the parameter";
+    if (holds(waiting_master_)) where += ", waits for the previous copy-out of the parameter";
   }
   {
     std::lock_guard<std::mutex> lk(use_mu_);

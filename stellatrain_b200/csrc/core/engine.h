@@ -60,6 +60,9 @@ struct EngineOptions {
 
 struct SharedParamEntry;       // row of the parameter table in shared memory
 
+// Stage ids of the node-wide task barriers.
+enum BarrierStage : int { kAfterCopyIn = 0, kAfterGather = 1, kAfterOptimize = 2, kAfterCopyOut = 3, kCheckerBase = 16 };
+
 class CpuEngine;
 
 // A pipeline stage ("module" in the reference, backend/src/engine/modules/module.h:18-34).
@@ -119,6 +122,11 @@ class CpuEngine {
   // see as iteration i left it.
   void schedule_after_previous(Module* m, const std::shared_ptr<TrainTask>& t);
   void mark_sequenced(const std::shared_ptr<TrainTask>& t);
+  // Runs `m` (the optimise stage, the only writer of the master parameter) once the copy-out of the previous
+  // iteration has finished reading the master: otherwise the copy handed to the framework could mix two updates,
+  // differently in every local process.  mark_master_read is called when that copy is complete.
+  void schedule_after_master_free(Module* m, const std::shared_ptr<TrainTask>& t);
+  void mark_master_read(const std::shared_ptr<TrainTask>& t);
   void schedule_after_use(Module* m, const std::shared_ptr<TrainTask>& t);
   void return_after_use(const std::shared_ptr<TrainTask>& t);
   void schedule_terminate(const std::shared_ptr<TrainTask>& t);
@@ -143,6 +151,7 @@ class CpuEngine {
     int64_t alloc_cnt = 0;                   // backwards (tasks) created
     int64_t completed_version = -1;
     int64_t sequenced_iter = -1;             // last iteration that left the optimise stage
+    int64_t master_read_iter = -1;           // last iteration whose copy-out has finished reading the master
     int micro = 0;
     bool checked_barrier = false;
     std::vector<float> merge_scratch;        // node master: dense accumulator of the merge
@@ -189,6 +198,7 @@ class CpuEngine {
   std::condition_variable version_cv_;
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_model_;
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_prev_;
+  std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_master_;
 
   // exclusive use of (parameter, slot)
   std::mutex use_mu_;

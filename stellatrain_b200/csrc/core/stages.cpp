@@ -16,8 +16,6 @@ namespace stc {
 
 namespace {
 
-enum BarrierStage : int { kAfterCopyIn = 0, kAfterGather = 1, kAfterOptimize = 2, kCheckerBase = 16 };
-
 uint32_t entries_for(uint32_t numel, double ratio, int world) {
   // k = max(min(n, 1), n * (1 - ratio) / W)   (reference compress.cpp:44-52)
   const double k_frac = (1.0 - ratio) / std::max(1, world);
@@ -136,7 +134,8 @@ class ModuleCompress : public Module {
     for (size_t j = 0; j < cnt; ++j) acc[t->idx[j]] = 0.f;
     std::memcpy(p.resid, acc, static_cast<size_t>(p.numel) * sizeof(float));
     t->stat_end("CRIT_PATH_save_residual");
-    e.schedule(e.module(W == 1 ? "Optimize" : "GradExchange"), t);
+    if (W == 1) e.schedule_after_master_free(e.module("Optimize"), t);
+    else e.schedule(e.module("GradExchange"), t);
   }
 };
 
@@ -148,7 +147,7 @@ class ModuleGradExchange : public Module {
     const int W = e.options().world;
     const int round = t->exchange_round;
     if (round >= W - 1) {
-      e.schedule(e.module("Optimize"), t);
+      e.schedule_after_master_free(e.module("Optimize"), t);
       return;
     }
     // ring all-gather: forward slot `round` to the successor, expect slot `round + 1` from the predecessor
@@ -216,7 +215,18 @@ class ModuleCopyOut : public Module {
       return;
     }
     std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
+    e.schedule_after_barrier(e.module("CopyOutDone"), t, kAfterCopyOut);
+  }
+};
+
+// Every local process has copied the master parameter out: the optimise stage of the next iteration may
+// write it again, the forward pass may use the copy, the gradient slot is free.
+class ModuleCopyOutDone : public Module {
+ public:
+  const char* name() const override { return "CopyOutDone"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
     t->advance(TaskState::Finished);
+    e.mark_master_read(t);
     e.update_model_version(t);
     e.return_after_use(t);
     e.schedule_terminate(t);
@@ -240,6 +250,7 @@ void CpuEngine::load_modules() {
   add(std::make_unique<ModuleOptimize>());
   add(std::make_unique<ModuleWaitModel>());
   add(std::make_unique<ModuleCopyOut>());
+  add(std::make_unique<ModuleCopyOutDone>());
 }
 
 }  // namespace stc
