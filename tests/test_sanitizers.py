@@ -25,8 +25,9 @@ def test_cpu_tier_selftest_is_clean(sanitizer, marker, tmp_path):
         if "sanitize" in str(e) and ("cannot find" in str(e) or "unrecognized" in str(e)):
             pytest.skip("sanitizer runtime not installed")
         raise
-    out = subprocess.run([str(exe), str(_free_port())], capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stderr[-4000:]
-    assert "selftest ok" in out.stdout
-    assert marker not in out.stderr, out.stderr[-4000:]
-    assert "runtime error:" not in out.stderr, out.stderr[-4000:]      # UBSan
+    for _ in range(3 if sanitizer == "thread" else 1):      # races depend on the schedule: several runs
+        out = subprocess.run([str(exe), str(_free_port())], capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, out.stderr[-4000:]
+        assert "selftest ok" in out.stdout
+        assert marker not in out.stderr, out.stderr[-4000:]
+        assert "runtime error:" not in out.stderr, out.stderr[-4000:]      # UBSan
