@@ -142,3 +142,14 @@ def test_package_entry_point_reports_build_state():
 
     rep = json.loads(out.stdout)
     assert rep["extensions"]["_Ccpu"]["built"] and rep["cpu_simd"] in ("scalar", "avx2", "avx512")
+
+
+def test_train_driver_two_local_ranks_with_heartbeat():
+    """Two processes of one node share gradients and the master copy through shared memory; the heartbeat monitor
+    runs between steps and every rank announces that it leaves at the end."""
+    out = subprocess.run([sys.executable, "-m", "stellatrain_b200.train", "--tier", "cpu", "--model", "resnet18", "--dataset", "dummy",
+                          "--num-epochs", "1", "--dummy-length", "3", "--batch-size", "2", "--local-world-size", "2",
+                          "--compression", "0.9", "--num-classes", "10", "--log-every", "1", "--heartbeat", "5"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "done: 3 iterations" in out.stdout
