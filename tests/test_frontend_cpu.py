@@ -153,3 +153,35 @@ def test_train_driver_two_local_ranks_with_heartbeat():
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "done: 3 iterations" in out.stdout
+
+
+def test_state_partition_and_narrow_wire_layout():
+    """Layout rules of the partitioned optimiser state and of the narrow wire format (pure Python)."""
+    import numpy as np
+
+    from stellatrain_b200.parallel import buckets as B
+
+    lay = B.BucketLayout(["a", "b", "c", "d", "e", "f"], [5000, 70000, 130, 40000, 16, 9000], chunk_elems=1024, narrow_wire=True)
+    lay.set_ratio(0.9, 4)
+    owners = lay.assign_state_owners(4)
+    assert owners == sorted(owners) and set(owners) <= set(range(4))            # consecutive tensors, one range per rank
+    ranges = [lay.state_range(r) for r in range(4)]
+    assert ranges[0][0] == 0 and ranges[-1][1] == lay.n_total
+    assert all(ranges[r][1] == ranges[r + 1][0] for r in range(3) if ranges[r + 1] != (0, 0))
+    bounds = lay.owner_bounds(4)
+    assert bounds[0] == 0 and bounds[-1] == lay.cap and bounds == sorted(bounds)
+    for r in range(4):                                                           # entry ranges match the tensors owned
+        assert bounds[r + 1] - bounds[r] == sum(s.k for s in lay.segments if s.owner == r)
+    segs = lay.seg_table()
+    assert [(int(x) >> 8) & 0xFF for x in segs["reserved"]] == owners
+    assert [bool(int(x) & 2) for x in segs["reserved"]] == [True, False, True, True, True, True]   # 70000 elements stay wide
+    assert lay.wire_bytes() == sum(s.k * (4 if s.n_pad < 65536 else 8) for s in lay.segments)
+    wide = B.BucketLayout(["a"], [1000], chunk_elems=1024)
+    wide.set_ratio(0.9, 1)
+    assert wide.wire_bytes() == 8 * wide.cap and not any(int(x) & 2 for x in wide.seg_table()["reserved"])
+    # more ranks than tensors: some ranks own nothing, the bounds still tile the stream
+    few = B.BucketLayout(["a", "b"], [100000, 50], chunk_elems=1024)
+    few.set_ratio(0.9, 4)
+    few.assign_state_owners(4)
+    assert [few.state_range(r) for r in range(4)].count((0, 0)) == 2 and few.owner_bounds(4)[-1] == few.cap
+    assert isinstance(np.asarray(few.owner_bounds(4)), np.ndarray)
