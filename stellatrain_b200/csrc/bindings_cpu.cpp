@@ -66,7 +66,11 @@ struct CompressorBox {
 template <typename Opt>
 void bind_optimizer(py::module_& m, const char* name) {
   py::class_<Opt>(m, name)
-      .def(py::init<>())
+      .def(py::init([] {
+        auto o = std::make_unique<Opt>();
+        o->set_pool(&shared_pool());
+        return o;
+      }))
       .def("optimize", [](Opt& o, uint64_t param, uint32_t n, const std::string& tname, uint64_t grad, uint64_t idx, uint32_t cnt) {
         py::gil_scoped_release rel;
         o.optimize_raw(P<float>(param), n, tname, P<const float>(grad), P<const uint32_t>(idx), cnt);

@@ -63,6 +63,7 @@ void CpuEngine::configure(const EngineOptions& o) {
   if (o.pin_cuda) shm_->pin_for_cuda();
   compressor_ = make_compressor(o.method, pool_.get());
   optimizer_ = make_optimizer("sgd");
+  optimizer_->set_pool(pool_.get());
   load_modules();
   if (o.world > 1 && node_master()) {
     comm_ = std::make_unique<CommManager>(o.master_addr, o.master_port, o.timeout_ms);
@@ -74,7 +75,10 @@ void CpuEngine::configure(const EngineOptions& o) {
   ready_ = true;
 }
 
-void CpuEngine::set_optimizer(const std::string& name) { optimizer_ = make_optimizer(name); }
+void CpuEngine::set_optimizer(const std::string& name) {
+  optimizer_ = make_optimizer(name);
+  optimizer_->set_pool(pool_.get());
+}
 
 void CpuEngine::configure_compression(const std::string& method) { compressor_ = make_compressor(method, pool_.get()); }
 

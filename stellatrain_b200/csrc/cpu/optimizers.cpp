@@ -52,28 +52,28 @@ void SGD::optimize_raw(float* param, uint32_t param_len, const std::string& name
   State& s = state_for(name, param_len);
   const float lr = maximize_ ? -lr_ : lr_;
   const bool first = s.first;
-  uint32_t j0 = 0;
-  if (best_isa() == Isa::Avx512 && !smart_momentum_ && !nesterov_ && param_len < (1u << 31)) {
-    for (uint32_t j = 0; j < grad_len; ++j)
-      if (idx[j] >= param_len) throw std::out_of_range("sparse SGD: index beyond the parameter");
-    j0 = sgd_avx512(param, s.b.data(), grad, idx, grad_len, lr, momentum_, dampening_, weight_decay_, first);
-  }
-  for (uint32_t j = j0; j < grad_len; ++j) {
-    const uint32_t i = idx[j];
-    if (i >= param_len) throw std::out_of_range("sparse SGD: index beyond the parameter");
-    const float x = param[i];
-    float g = grad[j];
-    float mu = momentum_;
-    if (smart_momentum_ && s.iter != 0) mu = std::pow(momentum_, static_cast<float>(s.iter - s.last[i]));
-    if (weight_decay_ != 0.f) g += weight_decay_ * x;
-    if (momentum_ != 0.f) {
-      const float b = first ? g : s.b[i] * mu + (1.f - dampening_) * g;
-      g = nesterov_ ? g + mu * b : b;
-      s.b[i] = b;
+  for (uint32_t j = 0; j < grad_len; ++j)
+    if (idx[j] >= param_len) throw std::out_of_range("sparse SGD: index beyond the parameter");
+  const bool simd = best_isa() == Isa::Avx512 && !smart_momentum_ && !nesterov_ && param_len < (1u << 31);
+  for_ranges(grad_len, [&](uint32_t jb, uint32_t je) {
+    uint32_t j0 = jb;
+    if (simd) j0 = jb + sgd_avx512(param, s.b.data(), grad + jb, idx + jb, je - jb, lr, momentum_, dampening_, weight_decay_, first);
+    for (uint32_t j = j0; j < je; ++j) {
+      const uint32_t i = idx[j];
+      const float x = param[i];
+      float g = grad[j];
+      float mu = momentum_;
+      if (smart_momentum_ && s.iter != 0) mu = std::pow(momentum_, static_cast<float>(s.iter - s.last[i]));
+      if (weight_decay_ != 0.f) g += weight_decay_ * x;
+      if (momentum_ != 0.f) {
+        const float b = first ? g : s.b[i] * mu + (1.f - dampening_) * g;
+        g = nesterov_ ? g + mu * b : b;
+        s.b[i] = b;
+      }
+      param[i] = x - lr * g;
+      if (smart_momentum_) s.last[i] = s.iter;
     }
-    param[i] = x - lr * g;
-    if (smart_momentum_) s.last[i] = s.iter;
-  }
+  });
   s.first = false;
   ++s.iter;
 }
@@ -141,25 +141,28 @@ void Adam::optimize_raw(float* param, uint32_t param_len, const std::string& nam
   const double b1 = b1_, b2 = b2_, lr = lr_, eps = eps_;
   const double c1 = 1.0 - std::pow(b1, static_cast<double>(s.tick));
   const double c2 = 1.0 - std::pow(b2, static_cast<double>(s.tick));
-  for (uint32_t j = 0; j < grad_len; ++j) {
-    const uint32_t i = idx[j];
-    if (i >= param_len) throw std::out_of_range("sparse Adam: index beyond the parameter");
-    const float x = param[i];
-    float g = grad[j];
-    if (maximize_) g = -g;
-    if (weight_decay_ != 0.f) g += weight_decay_ * x;
-    const double mt = b1 * s.m[i] + (1.0 - b1) * g;
-    const double vt = b2 * s.v[i] + (1.0 - b2) * static_cast<double>(g) * g;
-    const double mh = mt / c1;
-    double vh = vt / c2;
-    if (amsgrad_) {
-      vh = std::max(static_cast<double>(s.vmax[i]), vh);
-      s.vmax[i] = static_cast<float>(vh);
+  for (uint32_t j = 0; j < grad_len; ++j)
+    if (idx[j] >= param_len) throw std::out_of_range("sparse Adam: index beyond the parameter");
+  for_ranges(grad_len, [&](uint32_t jb, uint32_t je) {
+    for (uint32_t j = jb; j < je; ++j) {
+      const uint32_t i = idx[j];
+      const float x = param[i];
+      float g = grad[j];
+      if (maximize_) g = -g;
+      if (weight_decay_ != 0.f) g += weight_decay_ * x;
+      const double mt = b1 * s.m[i] + (1.0 - b1) * g;
+      const double vt = b2 * s.v[i] + (1.0 - b2) * static_cast<double>(g) * g;
+      const double mh = mt / c1;
+      double vh = vt / c2;
+      if (amsgrad_) {
+        vh = std::max(static_cast<double>(s.vmax[i]), vh);
+        s.vmax[i] = static_cast<float>(vh);
+      }
+      param[i] = static_cast<float>(x - lr * mh / (std::sqrt(vh) + eps));
+      s.m[i] = static_cast<float>(mt);
+      s.v[i] = static_cast<float>(vt);
     }
-    param[i] = static_cast<float>(x - lr * mh / (std::sqrt(vh) + eps));
-    s.m[i] = static_cast<float>(mt);
-    s.v[i] = static_cast<float>(vt);
-  }
+  });
   ++s.tick;
 }
 

@@ -14,6 +14,8 @@
 #include <string>
 #include <vector>
 
+#include "../core/threadpool.h"
+
 namespace stc {
 
 class SparseOptimizer {
@@ -33,8 +35,20 @@ class SparseOptimizer {
   virtual std::map<std::string, TensorState> export_state() = 0;
   virtual void import_state(const std::map<std::string, TensorState>& st) = 0;
   float lr() const { return lr_; }
+  // Long index lists are split over this pool (indices of one call are unique, so the ranges touch disjoint
+  // elements); without a pool, or for short lists, the calling thread does all the work.  The reference runs
+  // its Adam loop under one global mutex (backend/src/optim/adam.cpp:47).
+  void set_pool(ThreadPool* pool) { pool_ = pool; }
 
  protected:
+  template <typename F>
+  void for_ranges(uint32_t n, F&& fn) {
+    if (pool_ != nullptr && n >= (1u << 15))
+      pool_->parallel_for(n, 1u << 13, [&](size_t b, size_t e) { fn(static_cast<uint32_t>(b), static_cast<uint32_t>(e)); });
+    else
+      fn(0u, n);
+  }
+  ThreadPool* pool_ = nullptr;
   float lr_ = 1e-3f;   // backend/src/optim/sparse_optimizer.h:30
 };
 
