@@ -97,8 +97,15 @@ class ModuleGather : public Module {
     const size_t b = len * static_cast<size_t>(r) / N, en = len * static_cast<size_t>(r + 1) / N;
     float* dst = p.slot[t->iter % 2][0] + b;
     t->stat_start("CRIT_PATH_gather");
-    add_arrays(dst, p.resid + b, en - b);                       // error feedback (shared residual)
-    for (int g = 1; g < N; ++g) add_arrays(dst, p.slot[t->iter % 2][g] + b, en - b);
+    // error feedback (shared residual) and the other local processes' gradients; the last addition also applies the
+    // NaN policy shared with the GPU tier: a NaN is dropped (neither sent nor kept)
+    if (N == 1) {
+      add_arrays_nan_to_zero(dst, dst, p.resid + b, en - b);
+    } else {
+      add_arrays(dst, p.resid + b, en - b);
+      for (int g = 1; g + 1 < N; ++g) add_arrays(dst, p.slot[t->iter % 2][g] + b, en - b);
+      add_arrays_nan_to_zero(dst, dst, p.slot[t->iter % 2][N - 1] + b, en - b);
+    }
     t->stat_end("CRIT_PATH_gather");
     e.schedule_after_barrier(e.module("Compress"), t, kAfterGather);
   }
@@ -115,9 +122,7 @@ class ModuleCompress : public Module {
     }
     auto& p = e.param(t->param_index);
     const int W = e.options().world;
-    float* acc = p.slot[t->iter % 2][0];
-    for (uint32_t i = 0; i < p.numel; ++i)
-      if (acc[i] != acc[i]) acc[i] = 0.f;                        // NaN policy shared with the GPU tier
+    float* acc = p.slot[t->iter % 2][0];                         // NaN already dropped by the gather stage
     const uint32_t k = entries_for(p.numel, e.compression_ratio(), W);
     t->k = k;
     t->idx.assign(static_cast<size_t>(k) * W, 0xFFFFFFFFu);

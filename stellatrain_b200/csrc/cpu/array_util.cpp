@@ -70,6 +70,42 @@ void add_arrays_to(float* dst, const float* a, const float* b, size_t n) {
 
 void add_arrays(float* dst, const float* src, size_t n) { add_arrays_to(dst, dst, src, n); }
 
+__attribute__((target("avx512f"))) static void add_nan0_avx512(float* dst, const float* a, const float* b, size_t n) {
+  size_t i = 0;
+  for (; i + 16 <= n; i += 16) {
+    const __m512 s = _mm512_add_ps(_mm512_loadu_ps(a + i), _mm512_loadu_ps(b + i));
+    _mm512_storeu_ps(dst + i, _mm512_maskz_mov_ps(_mm512_cmp_ps_mask(s, s, _CMP_ORD_Q), s));   // NaN lanes become 0
+  }
+  for (; i < n; ++i) {
+    const float s = a[i] + b[i];
+    dst[i] = s == s ? s : 0.f;
+  }
+}
+
+__attribute__((target("avx2"))) static void add_nan0_avx2(float* dst, const float* a, const float* b, size_t n) {
+  size_t i = 0;
+  for (; i + 8 <= n; i += 8) {
+    const __m256 s = _mm256_add_ps(_mm256_loadu_ps(a + i), _mm256_loadu_ps(b + i));
+    _mm256_storeu_ps(dst + i, _mm256_and_ps(s, _mm256_cmp_ps(s, s, _CMP_ORD_Q)));
+  }
+  for (; i < n; ++i) {
+    const float s = a[i] + b[i];
+    dst[i] = s == s ? s : 0.f;
+  }
+}
+
+void add_arrays_nan_to_zero(float* dst, const float* a, const float* b, size_t n) {
+  switch (best_isa()) {
+    case Isa::Avx512: add_nan0_avx512(dst, a, b, n); return;
+    case Isa::Avx2: add_nan0_avx2(dst, a, b, n); return;
+    default:
+      for (size_t i = 0; i < n; ++i) {
+        const float s = a[i] + b[i];
+        dst[i] = s == s ? s : 0.f;
+      }
+  }
+}
+
 // ---------------------------------------------------------------- block L1 norms
 // The reduction tree matches the GPU kernel: ((|x0|+|x1|)+(|x2|+|x3|)) per group of four, then
 // (g0+g1)+(g2+g3); scores are therefore bit-identical across tiers.

@@ -17,6 +17,9 @@ const char* isa_name(Isa isa);
 void add_arrays(float* dst, const float* src, size_t n);
 // dst[i] = a[i] + b[i]
 void add_arrays_to(float* dst, const float* a, const float* b, size_t n);
+// dst = a + b with every NaN replaced by zero (the accumulate step of error feedback: a NaN gradient is
+// dropped instead of poisoning the residual).
+void add_arrays_nan_to_zero(float* dst, const float* a, const float* b, size_t n);
 // sum of |x[i]| over aligned blocks of 16: out[b] = sum_{j<16} |x[16 b + j]| (tail block zero padded)
 void block_l1_norms(const float* x, size_t n, float* out);
 float max_abs(const float* x, size_t n);

@@ -336,14 +336,7 @@ size_t compress_with_feedback(Compressor& c, const std::string& tensor, const fl
                               uint32_t k, uint32_t* dst_idx, float* dst_val, ThreadPool* pool) {
   size_t parts = 1;
   run_ranges(pool, n, [&](size_t, size_t b, size_t e) {
-    // block by block, so that the NaN scan finds the sums still in the first-level cache
-    constexpr size_t kBlock = 4096;
-    for (size_t i0 = b; i0 < e; i0 += kBlock) {
-      const size_t i1 = std::min(e, i0 + kBlock);
-      add_arrays_to(resid + i0, resid + i0, grad + i0, i1 - i0);
-      for (size_t i = i0; i < i1; ++i)
-        if (resid[i] != resid[i]) resid[i] = 0.f;
-    }
+    add_arrays_nan_to_zero(resid + b, resid + b, grad + b, e - b);     // a = g + r in one pass, NaN dropped
   }, parts);
   const size_t cnt = c.compress(tensor, resid, n, k, dst_idx, dst_val, 0);
   for (size_t j = 0; j < cnt; ++j) resid[dst_idx[j]] = 0.f;

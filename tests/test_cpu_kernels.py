@@ -186,3 +186,23 @@ def test_flat_gradient_benchmark_small():
         assert out["sent_fraction"] == pytest.approx(0.01, rel=0.15)
         assert out["rel_l2_to_dense"] < 1.0 and out["cos_to_dense"] > 0.1
         assert out["residual_mass_conserved"]
+
+
+@pytest.mark.parametrize("method", ["topk", "thresholdv", "thresholdv16"])
+def test_nan_gradients_are_dropped(method):
+    """A NaN in the gradient is neither sent nor kept: the accumulate step writes zero in its place."""
+    n, k = 1003, 50
+    g = torch.Generator().manual_seed(3)
+    grad = torch.randn(n, generator=g)
+    bad = torch.tensor([0, 15, 16, 17, 500, 1001, 1002])
+    grad[bad] = float("nan")
+    resid = torch.randn(n, generator=g) * 0.1
+    want = resid + grad
+    want[bad] = 0.0
+    comp = ext.Compressor(method)
+    idx = torch.empty(k, dtype=torch.int32); val = torch.empty(k)
+    cnt = comp.compress_with_feedback("t", grad.data_ptr(), resid.data_ptr(), n, k, idx.data_ptr(), val.data_ptr())
+    assert not torch.isnan(resid).any() and not torch.isnan(val[:cnt]).any()
+    rebuilt = resid.clone()
+    rebuilt[idx[:cnt].long()] = val[:cnt]
+    assert torch.equal(rebuilt, want)          # sent + kept = g + r with the NaN positions at zero

@@ -185,3 +185,25 @@ def test_state_partition_and_narrow_wire_layout():
     few.assign_state_owners(4)
     assert [few.state_range(r) for r in range(4)].count((0, 0)) == 2 and few.owner_bounds(4)[-1] == few.cap
     assert isinstance(np.asarray(few.owner_bounds(4)), np.ndarray)
+
+
+def test_cpu_tier_drops_nan_gradients():
+    """A step whose gradients are NaN leaves parameters and residuals untouched (the NaN is dropped in the gather
+    stage); training continues normally afterwards."""
+    from stellatrain_b200.cpu_tier import CpuOffloadEngine
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 4))
+    eng = CpuOffloadEngine(model, method="topk", ratio=0.5, optimizer="sgd", optimizer_options={"lr": 0.1}, staleness=0,
+                           data_bytes=8 << 20, workers=2)
+    x, y = torch.randn(32, 16), torch.randint(0, 4, (32,))
+    before = [p.detach().clone() for p in model.parameters()]
+    (F.cross_entropy(model(x), y) * float("nan")).backward()
+    eng.synchronize()
+    for p, q in zip(model.parameters(), before):
+        assert torch.equal(p, q) and torch.isfinite(p).all()
+    F.cross_entropy(model(x), y).backward()
+    eng.synchronize()
+    assert any(not torch.equal(p, q) for p, q in zip(model.parameters(), before))
+    assert all(torch.isfinite(p).all() for p in model.parameters())
+    eng.close()
