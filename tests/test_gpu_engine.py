@@ -382,3 +382,31 @@ def test_engine_with_debug_checks_trains_like_without():
 
     for a, b in zip(run(False), run(True)):
         assert torch.equal(a, b)
+
+
+def test_cpu_offload_tier_with_a_cuda_model():
+    """The CPU-offload tier under a model on the GPU: gradients go to pinned shared slots on a copy stream, the
+    C++ pipeline compresses and optimises on the host, updated parameters come back by asynchronous copies."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from stellatrain_b200.cpu_tier import CpuOffloadEngine
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(64, 128), nn.ReLU(), nn.Linear(128, 10)).cuda()
+    before = [p.detach().clone() for p in model.parameters()]
+    eng = CpuOffloadEngine(model, method="thresholdv16", ratio=0.9, optimizer="adam", optimizer_options={"lr": 1e-2},
+                           staleness=1, data_bytes=16 << 20, workers=4)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x, y = torch.randn(128, 64, device="cuda", generator=g), torch.randint(0, 10, (128,), device="cuda", generator=g)
+    losses = []
+    for _ in range(25):
+        loss = F.cross_entropy(model(x), y)
+        loss.backward()
+        losses.append(float(loss.detach()))
+    eng.synchronize()
+    assert all(torch.isfinite(p).all() for p in model.parameters())
+    assert any(not torch.equal(p, q) for p, q in zip(model.parameters(), before))
+    assert losses[-1] < losses[0]
+    assert "Total" in eng.stats_json()
+    eng.close()
