@@ -112,6 +112,7 @@ class TrafficModel:
     grad_fp16: bool = False
     grad_idx_u16: bool = False
     buckets: int = 8
+    grad_block16: bool = False       # "tcp" only: entries travel as whole blocks of 16 behind one block id
 
     def tx_bytes(self, ratio: float) -> int:
         ratio = min(max(ratio, 0.0), 0.999999)
@@ -123,7 +124,12 @@ class TrafficModel:
             if self.transport == "nvlink":
                 total += 8 * k if not (self.grad_fp16 or self.grad_idx_u16) else (idx_b + val_b) * k
             else:
-                payload = 24 + 16 + 4 + (idx_b + val_b) * k              # frame header, key, count, arrays
+                if self.grad_block16 and k >= 16:
+                    blk_b = 2 if n <= (1 << 20) else 4
+                    arrays = 4 + (k // 16) * blk_b + (k % 16) * idx_b + val_b * k
+                else:
+                    arrays = (idx_b + val_b) * k
+                payload = 24 + 16 + 4 + arrays                           # frame header, key, count, arrays
                 mss = 1538 - 0x42
                 total += payload + math.ceil(payload / mss) * 0x42       # Ethernet/IP/TCP per segment
         if self.transport == "nvlink":

@@ -88,7 +88,8 @@ class CpuOffloadEngine:
                  rank: int = 0, session: Optional[int] = None, local_world_size: int = 1, local_rank: int = 0,
                  method: str = "thresholdv16", gradient_accumulation: int = 1, staleness: int = 1, ratio: float = 0.99,
                  optimizer: str = "sgd", optimizer_options: Optional[dict] = None, data_bytes: int = 0,
-                 timeout_ms: int = 30000, workers: int = 0, debug_accuracy: bool = False, debug_barrier: bool = False):
+                 timeout_ms: int = 30000, workers: int = 0, debug_accuracy: bool = False, debug_barrier: bool = False,
+                 wire_blocks: bool = True, wire_values: str = "fp32"):
         ext = _load()
         self.module = module
         self.engine = ext.CpuEngine()
@@ -101,6 +102,9 @@ class CpuOffloadEngine:
         self.engine.configure(master_addr, master_port, world_size, rank, os.getpid() if session is None else session,
                               local_world_size, local_rank, method, gradient_accumulation, staleness, ratio,
                               data_bytes, timeout_ms, workers, self.cuda, debug_accuracy, debug_barrier)
+        # messages between nodes: block ids for whole aligned runs of 16 indices, optionally 16-bit values whose
+        # rounding error stays in the sender's residual
+        self.engine.configure_wire(wire_blocks, {"fp32": 0, "fp16": 1, "bf16": 2}[wire_values])
         self.engine.set_optimizer(optimizer)
         for k, v in (optimizer_options or {}).items():
             self.engine.configure_optimizer(k, v)

@@ -126,6 +126,22 @@ PYBIND11_MODULE(_Ccpu, m) {
   m.def("best_isa", [] { return std::string(isa_name(best_isa())); });
   m.def("add_arrays", [](uint64_t dst, uint64_t src, size_t n) { add_arrays(P<float>(dst), P<const float>(src), n); });
   m.def("block_l1_norms", [](uint64_t x, size_t n, uint64_t out) { block_l1_norms(P<const float>(x), n, P<float>(out)); });
+  m.def("encode_sparse", [](const std::vector<uint32_t>& idx, const std::vector<float>& val, uint32_t numel, bool allow_u16,
+                            int value_format, bool allow_blocks) {
+    if (idx.size() != val.size()) throw std::invalid_argument("idx and val differ in length");
+    EncodedSparse e = encode_sparse(idx.data(), val.data(), idx.size(), numel, allow_u16, value_format, allow_blocks);
+    return py::make_tuple(static_cast<int>(e.flags), py::bytes(reinterpret_cast<const char*>(e.payload.data()), e.payload.size()));
+  }, py::arg("idx"), py::arg("val"), py::arg("tensor_numel"), py::arg("allow_u16") = true, py::arg("value_format") = 0,
+        py::arg("allow_blocks") = true,
+        "Payload of one gradient message: (flags, bytes).  Whole aligned runs of 16 indices become block ids.");
+  m.def("decode_sparse", [](int flags, const std::string& payload, uint32_t numel) {
+    std::vector<uint32_t> idx;
+    std::vector<float> val;
+    if (!decode_sparse(static_cast<uint8_t>(flags), reinterpret_cast<const unsigned char*>(payload.data()), payload.size(),
+                       numel, &idx, &val))
+      throw std::invalid_argument("malformed sparse payload");
+    return py::make_tuple(idx, val);
+  }, py::arg("flags"), py::arg("payload"), py::arg("tensor_numel") = 0);
   m.def("narrow_u32_to_u16", [](uint64_t s, uint64_t d, size_t n) { narrow_u32_to_u16(P<const uint32_t>(s), P<uint16_t>(d), n); });
   m.def("widen_u16_to_u32", [](uint64_t s, uint64_t d, size_t n) { widen_u16_to_u32(P<const uint16_t>(s), P<uint32_t>(d), n); });
   m.def("f32_to_f16", [](uint64_t s, uint64_t d, size_t n) { f32_to_f16(P<const float>(s), P<uint16_t>(d), n); });
@@ -225,10 +241,11 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def("start_client", [](CommBox& b, int rank, int world, int gpus) { return b.c->start_client(rank, world, gpus); },
            py::call_guard<py::gil_scoped_release>())
       .def("queue_tx", [](CommBox& b, int64_t prio, const std::string& key, const std::vector<uint32_t>& idx,
-                          const std::vector<float>& val, uint32_t numel, bool allow_u16, int value_format) {
-        b.c->queue_tx(prio, key, idx.data(), val.data(), idx.size(), numel, allow_u16, value_format);
+                          const std::vector<float>& val, uint32_t numel, bool allow_u16, int value_format,
+                          bool allow_blocks) {
+        b.c->queue_tx(prio, key, idx.data(), val.data(), idx.size(), numel, allow_u16, value_format, allow_blocks);
       }, py::arg("priority"), py::arg("key"), py::arg("idx"), py::arg("val"), py::arg("tensor_numel"),
-           py::arg("allow_u16") = true, py::arg("value_format") = 0)
+           py::arg("allow_u16") = true, py::arg("value_format") = 0, py::arg("allow_blocks") = true)
       .def("post_recv", &CommBox::post)
       .def("drain", &CommBox::drain)
       .def("stashed", [](CommBox& b) { return b.c->stashed(); })
@@ -290,6 +307,7 @@ PYBIND11_MODULE(_Ccpu, m) {
       })
       .def("configure_compression", &CpuEngine::configure_compression)
       .def("configure_compression_ratio", &CpuEngine::configure_compression_ratio)
+      .def("configure_wire", &CpuEngine::configure_wire, py::arg("blocks") = true, py::arg("value_format") = 0)
       .def("gradient_accumulation", &CpuEngine::gradient_accumulation)
       .def("is_debug_accuracy_mode", [](CpuEngine& e) { return e.options().debug_accuracy; })
       .def("barrier", &CpuEngine::barrier, py::call_guard<py::gil_scoped_release>())

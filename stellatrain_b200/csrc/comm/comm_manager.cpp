@@ -274,38 +274,162 @@ void CommManager::set_tx_fault_hook(std::function<bool(const std::string&, int*)
   tx_hook_ = std::move(hook);
 }
 
+namespace {
+
+void put_values(const float* val, size_t n, int value_format, unsigned char* out) {
+  if (value_format == 1) f32_to_f16(val, reinterpret_cast<uint16_t*>(out), n);
+  else if (value_format == 2) f32_to_bf16(val, reinterpret_cast<uint16_t*>(out), n);
+  else std::memcpy(out, val, n * 4);
+}
+
+// true when idx[j .. j+15] is one aligned block: starts at a multiple of 16 and counts up by one
+inline bool whole_block_at(const uint32_t* idx, size_t j, size_t count) {
+  if (j + 16 > count || (idx[j] & 15u) != 0) return false;
+  for (uint32_t d = 1; d < 16; ++d)
+    if (idx[j + d] != idx[j] + d) return false;
+  return true;
+}
+
+}  // namespace
+
+EncodedSparse encode_sparse(const uint32_t* idx, const float* val, size_t count, uint32_t tensor_numel, bool allow_u16,
+                            int value_format, bool allow_blocks) {
+  EncodedSparse e;
+  e.count = static_cast<uint32_t>(count);
+  const size_t vsz = value_format == 0 ? 4 : 2;
+  if (value_format == 1) e.flags |= kFlagValF16;
+  else if (value_format == 2) e.flags |= kFlagValBF16;
+
+  // pass over the indices: where the whole blocks are, and whether the rest fits 16 bits (reference:
+  // tensor_numel < 65536, comm_manager.cpp:579-583; the sentinel index used for padding does not fit and
+  // keeps the stream wide)
+  std::vector<uint32_t> block_at;      // positions j of whole blocks
+  bool narrow = allow_u16 && tensor_numel <= 65536;
+  bool narrow_blocks = true;
+  for (size_t j = 0; j < count;) {
+    if (allow_blocks && whole_block_at(idx, j, count)) {
+      block_at.push_back(static_cast<uint32_t>(j));
+      narrow_blocks = narrow_blocks && (idx[j] >> 4) < 65536u;
+      j += 16;
+    } else {
+      narrow = narrow && idx[j] < 65536u;
+      ++j;
+    }
+  }
+  const size_t nb = block_at.size();
+  const size_t loose = count - 16 * nb;
+  const size_t isz = narrow ? 2 : 4;
+  if (narrow) e.flags |= kFlagIdxU16;
+
+  if (nb == 0) {
+    e.payload.resize(4 + count * isz + count * vsz);
+    unsigned char* p = e.payload.data();
+    std::memcpy(p, &e.count, 4);
+    p += 4;
+    if (narrow) narrow_u32_to_u16(idx, reinterpret_cast<uint16_t*>(p), count);
+    else std::memcpy(p, idx, count * 4);
+    put_values(val, count, value_format, p + count * isz);
+    return e;
+  }
+
+  e.flags |= kFlagBlock16;
+  if (narrow_blocks) e.flags |= kFlagBlockU16;
+  const size_t bsz = narrow_blocks ? 2 : 4;
+  e.payload.resize(8 + nb * bsz + loose * isz + count * vsz);
+  unsigned char* p = e.payload.data();
+  const uint32_t nb32 = static_cast<uint32_t>(nb);
+  std::memcpy(p, &e.count, 4);
+  std::memcpy(p + 4, &nb32, 4);
+  unsigned char* pb = p + 8;
+  unsigned char* pi = pb + nb * bsz;
+  unsigned char* pv = pi + loose * isz;
+  unsigned char* pvl = pv + 16 * nb * vsz;   // values of the loose entries follow those of the blocks
+  std::vector<uint32_t> loose_idx;
+  std::vector<float> loose_val;
+  loose_idx.reserve(loose);
+  loose_val.reserve(loose);
+  size_t next_block = 0;
+  for (size_t j = 0; j < count;) {
+    if (next_block < nb && block_at[next_block] == j) {
+      const uint32_t id = idx[j] >> 4;
+      if (narrow_blocks) {
+        const uint16_t id16 = static_cast<uint16_t>(id);
+        std::memcpy(pb + next_block * 2, &id16, 2);
+      } else {
+        std::memcpy(pb + next_block * 4, &id, 4);
+      }
+      put_values(val + j, 16, value_format, pv + next_block * 16 * vsz);
+      ++next_block;
+      j += 16;
+    } else {
+      loose_idx.push_back(idx[j]);
+      loose_val.push_back(val[j]);
+      ++j;
+    }
+  }
+  if (loose) {
+    if (narrow) narrow_u32_to_u16(loose_idx.data(), reinterpret_cast<uint16_t*>(pi), loose);
+    else std::memcpy(pi, loose_idx.data(), loose * 4);
+    put_values(loose_val.data(), loose, value_format, pvl);
+  }
+  return e;
+}
+
+bool decode_sparse(uint8_t flags, const unsigned char* payload, size_t len, uint32_t tensor_numel,
+                   std::vector<uint32_t>* idx, std::vector<float>* val) {
+  if (len < 4) return false;
+  uint32_t count;
+  std::memcpy(&count, payload, 4);
+  const size_t isz = (flags & kFlagIdxU16) ? 2 : 4;
+  const size_t vsz = (flags & (kFlagValF16 | kFlagValBF16)) ? 2 : 4;
+  uint32_t nb = 0;
+  size_t head = 4, bsz = 0;
+  if (flags & kFlagBlock16) {
+    if (len < 8) return false;
+    std::memcpy(&nb, payload + 4, 4);
+    head = 8;
+    bsz = (flags & kFlagBlockU16) ? 2 : 4;
+    if (static_cast<uint64_t>(nb) * 16 > count) return false;
+  }
+  const size_t loose = count - static_cast<size_t>(nb) * 16;
+  if (len != head + nb * bsz + loose * isz + static_cast<size_t>(count) * vsz) return false;
+  idx->resize(count);
+  val->resize(count);
+  const unsigned char* pb = payload + head;
+  const unsigned char* pi = pb + nb * bsz;
+  const unsigned char* pv = pi + loose * isz;
+  for (uint32_t b = 0; b < nb; ++b) {
+    uint32_t id;
+    if (bsz == 2) {
+      uint16_t id16;
+      std::memcpy(&id16, pb + b * 2, 2);
+      id = id16;
+    } else {
+      std::memcpy(&id, pb + b * 4, 4);
+      if (id > 0x0FFFFFFFu) return false;
+    }
+    for (uint32_t d = 0; d < 16; ++d) (*idx)[static_cast<size_t>(b) * 16 + d] = id * 16 + d;
+  }
+  uint32_t* li = idx->data() + static_cast<size_t>(nb) * 16;
+  if (isz == 2) widen_u16_to_u32(reinterpret_cast<const uint16_t*>(pi), li, loose);
+  else if (loose) std::memcpy(li, pi, loose * 4);
+  if (flags & kFlagValF16) f16_to_f32(reinterpret_cast<const uint16_t*>(pv), val->data(), count);
+  else if (flags & kFlagValBF16) bf16_to_f32(reinterpret_cast<const uint16_t*>(pv), val->data(), count);
+  else if (count) std::memcpy(val->data(), pv, static_cast<size_t>(count) * 4);
+  if (tensor_numel)
+    for (uint32_t j = 0; j < count; ++j)
+      if ((*idx)[j] >= tensor_numel && (*idx)[j] != 0xFFFFFFFFu) return false;   // the padding sentinel may travel
+  return true;
+}
+
 void CommManager::queue_tx(int64_t priority, const std::string& key, const uint32_t* idx, const float* val, size_t count,
-                           uint32_t tensor_numel, bool allow_u16, int value_format) {
+                           uint32_t tensor_numel, bool allow_u16, int value_format, bool allow_blocks) {
   auto item = std::make_shared<TxItem>();
   item->priority = priority;
   item->key = key;
-  item->count = static_cast<uint32_t>(count);
-  item->flags = 0;
-  // index narrowing when every index fits (reference: tensor_numel < 65536, comm_manager.cpp:579-583);
-  // the sentinel index used for padding does not fit and keeps the stream wide
-  bool narrow = allow_u16 && tensor_numel <= 65536;
-  if (narrow)
-    for (size_t i = 0; i < count && narrow; ++i) narrow = idx[i] < 65536u;
-  if (narrow) {
-    item->flags |= kFlagIdxU16;
-    item->idx_bytes.resize(count * 2);
-    narrow_u32_to_u16(idx, reinterpret_cast<uint16_t*>(item->idx_bytes.data()), count);
-  } else {
-    item->idx_bytes.resize(count * 4);
-    std::memcpy(item->idx_bytes.data(), idx, count * 4);
-  }
-  if (value_format == 1) {
-    item->flags |= kFlagValF16;
-    item->val_bytes.resize(count * 2);
-    f32_to_f16(val, reinterpret_cast<uint16_t*>(item->val_bytes.data()), count);
-  } else if (value_format == 2) {
-    item->flags |= kFlagValBF16;
-    item->val_bytes.resize(count * 2);
-    f32_to_bf16(val, reinterpret_cast<uint16_t*>(item->val_bytes.data()), count);
-  } else {
-    item->val_bytes.resize(count * 4);
-    std::memcpy(item->val_bytes.data(), val, count * 4);
-  }
+  EncodedSparse enc = encode_sparse(idx, val, count, tensor_numel, allow_u16, value_format, allow_blocks);
+  item->flags = enc.flags;
+  item->payload = std::move(enc.payload);
   {
     std::lock_guard<std::mutex> lk(tx_mu_);
     item->seq = tx_seq_++;
@@ -333,10 +457,7 @@ void CommManager::push_main() {
       if (hook(item->key, &delay)) continue;   // dropped on purpose by a test
       if (delay > 0) std::this_thread::sleep_for(std::chrono::milliseconds(delay));
     }
-    std::vector<unsigned char> payload(4 + item->idx_bytes.size() + item->val_bytes.size());
-    std::memcpy(payload.data(), &item->count, 4);
-    std::memcpy(payload.data() + 4, item->idx_bytes.data(), item->idx_bytes.size());
-    std::memcpy(payload.data() + 4 + item->idx_bytes.size(), item->val_bytes.data(), item->val_bytes.size());
+    const std::vector<unsigned char>& payload = item->payload;
     if (!send_frame(push_fd_, kGrad, item->key, item->flags, payload.data(), payload.size(), timeout_ms_)) {
       if (!stop_) set_failed("send to the ring successor failed for " + item->key);
       return;
@@ -364,23 +485,10 @@ void CommManager::pull_main() {
     SparseMessage m;
     m.key = key;
     m.flags = static_cast<uint8_t>(h.flags);
-    uint32_t count;
-    std::memcpy(&count, payload.data(), 4);
-    const size_t idx_bytes = static_cast<size_t>(count) * ((m.flags & kFlagIdxU16) ? 2 : 4);
-    const size_t val_bytes = static_cast<size_t>(count) * ((m.flags & (kFlagValF16 | kFlagValBF16)) ? 2 : 4);
-    if (payload.size() != 4 + idx_bytes + val_bytes) {
+    if (!decode_sparse(m.flags, payload.data(), payload.size(), 0, &m.idx, &m.val)) {
       set_failed("malformed gradient frame for " + key);
       return;
     }
-    m.idx.resize(count);
-    m.val.resize(count);
-    const unsigned char* pi = payload.data() + 4;
-    const unsigned char* pv = pi + idx_bytes;
-    if (m.flags & kFlagIdxU16) widen_u16_to_u32(reinterpret_cast<const uint16_t*>(pi), m.idx.data(), count);
-    else std::memcpy(m.idx.data(), pi, idx_bytes);
-    if (m.flags & kFlagValF16) f16_to_f32(reinterpret_cast<const uint16_t*>(pv), m.val.data(), count);
-    else if (m.flags & kFlagValBF16) bf16_to_f32(reinterpret_cast<const uint16_t*>(pv), m.val.data(), count);
-    else std::memcpy(m.val.data(), pv, val_bytes);
     m.wire_bytes = sizeof(FrameHeader) + key.size() + payload.size();
     bytes_recv_ += m.wire_bytes;
     rx_mon_.add(m.wire_bytes);

@@ -29,6 +29,8 @@ namespace stc {
 constexpr uint8_t kFlagIdxU16 = 0x01;   // reference comm_manager.h:24
 constexpr uint8_t kFlagValF16 = 0x02;   // reference comm_manager.h:25
 constexpr uint8_t kFlagValBF16 = 0x04;
+constexpr uint8_t kFlagBlock16 = 0x08;  // part of the entries travels as whole aligned blocks of 16
+constexpr uint8_t kFlagBlockU16 = 0x10; // block ids are 16 bits wide (tensors of up to 1,048,576 elements)
 
 struct SparseMessage {
   std::string key;
@@ -37,6 +39,30 @@ struct SparseMessage {
   std::vector<float> val;
   size_t wire_bytes = 0;
 };
+
+// Payload of one gradient message.
+//
+//   plain:  count:u32 | idx[count] (u32, or u16 with kFlagIdxU16) | val[count] (f32, f16 or bf16)
+//   blocks: count:u32 | nblocks:u32 | block_id[nblocks] (u32, or u16 with kFlagBlockU16)
+//           | idx[count - 16 nblocks] | val[count]
+//
+// The block form is what threshold-v16 produces most of the time: 16 consecutive indices that start at a
+// multiple of 16.  Such a run is sent as one block id (index / 16) followed by its 16 values, which removes
+// 15 of 16 indices: 68 bytes instead of 128 for a block of fp32 values (the reference always sends
+// (index, value) pairs, backend/src/engine/comm_manager.cpp:748-764).  The encoder moves the whole blocks to
+// the front of the message and the loose entries behind them; a receiver that merges by index does not depend
+// on the order.  A message without a single whole block is sent in the plain form.
+struct EncodedSparse {
+  uint8_t flags = 0;
+  uint32_t count = 0;
+  std::vector<unsigned char> payload;
+};
+EncodedSparse encode_sparse(const uint32_t* idx, const float* val, size_t count, uint32_t tensor_numel, bool allow_u16,
+                            int value_format, bool allow_blocks);
+// Returns false when the payload does not have the size its header implies or names an index outside the tensor
+// (tensor_numel 0: not checked).
+bool decode_sparse(uint8_t flags, const unsigned char* payload, size_t len, uint32_t tensor_numel,
+                   std::vector<uint32_t>* idx, std::vector<float>* val);
 
 struct PeerStat {       // one line of the broker's link report
   int rank;
@@ -58,7 +84,8 @@ class CommManager {
 
   // ---- gradient data (ring)
   void queue_tx(int64_t priority, const std::string& key, const uint32_t* idx, const float* val, size_t count,
-                uint32_t tensor_numel, bool allow_u16 = true, int value_format = 0 /*0 f32, 1 f16, 2 bf16*/);
+                uint32_t tensor_numel, bool allow_u16 = true, int value_format = 0 /*0 f32, 1 f16, 2 bf16*/,
+                bool allow_blocks = true);
   // `cb` runs on the pull thread (or immediately on the caller when the message is already here).
   void post_recv(const std::string& key, std::function<void(SparseMessage&&)> cb);
   bool cancel_recv(const std::string& key);
@@ -87,8 +114,7 @@ class CommManager {
     uint64_t seq;
     std::string key;
     uint8_t flags;
-    std::vector<unsigned char> idx_bytes, val_bytes;
-    uint32_t count;
+    std::vector<unsigned char> payload;
   };
   struct TxLater {
     bool operator()(const std::shared_ptr<TxItem>& a, const std::shared_ptr<TxItem>& b) const {

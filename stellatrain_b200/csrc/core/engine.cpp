@@ -87,6 +87,12 @@ void CpuEngine::configure_compression_ratio(double ratio) {
   ratio_ = ratio;
 }
 
+void CpuEngine::configure_wire(bool blocks, int value_format) {
+  if (value_format < 0 || value_format > 2) throw std::invalid_argument("value format must be 0 (fp32), 1 (fp16) or 2 (bf16)");
+  wire_blocks_ = blocks;
+  wire_values_ = value_format;
+}
+
 void CpuEngine::barrier() {
   if (!shm_->barrier(opt_.timeout_ms)) throw std::runtime_error("node barrier timed out");
   if (comm_ && !comm_->global_barrier()) throw std::runtime_error("global barrier timed out");

@@ -88,6 +88,13 @@ class CpuEngine {
   void configure_compression(const std::string& method);
   void configure_compression_ratio(double ratio);
   double compression_ratio() const { return ratio_; }
+  // Wire format of the gradient messages between nodes.  `blocks`: whole aligned runs of 16 indices travel as one
+  // block id (what threshold-v16 selects).  `value_format`: 0 fp32, 1 fp16, 2 bf16; with 1 or 2 the compress stage
+  // keeps the rounding error of every sent value in the residual, so narrow values delay mass instead of losing it.
+  // Every node must use the same value format (the block form is self-describing).
+  void configure_wire(bool blocks, int value_format);
+  bool wire_blocks() const { return wire_blocks_; }
+  int wire_value_format() const { return wire_values_; }
   int gradient_accumulation() const { return opt_.grad_accumulation; }
   void barrier();               // all processes of all nodes
   void synchronize();           // flush the pipeline (throws on failed tasks)
@@ -172,6 +179,8 @@ class CpuEngine {
   std::atomic<bool> ready_{false};
   std::atomic<bool> stop_{false};
   double ratio_ = 0.99;
+  std::atomic<bool> wire_blocks_{true};
+  std::atomic<int> wire_values_{0};
   std::unique_ptr<ThreadPool> pool_;
   std::unique_ptr<ShmManager> shm_;
   std::unique_ptr<CommManager> comm_;

@@ -136,7 +136,21 @@ class ModuleCompress : public Module {
       for (size_t j = 0; j < cnt; ++j)
         if (t->idx[j] >= p.numel || t->val[j] != acc[t->idx[j]]) throw std::runtime_error("compressor output is inconsistent");
     t->stat_start("CRIT_PATH_save_residual");
-    for (size_t j = 0; j < cnt; ++j) acc[t->idx[j]] = 0.f;
+    const int vf = W > 1 ? e.wire_value_format() : 0;
+    if (vf == 0) {
+      for (size_t j = 0; j < cnt; ++j) acc[t->idx[j]] = 0.f;
+    } else {
+      // narrow values on the wire: send what the receiver will decode and keep the rounding error here
+      std::vector<uint16_t> half(cnt);
+      std::vector<float> sent(cnt);
+      if (vf == 1) { f32_to_f16(t->val.data(), half.data(), cnt); f16_to_f32(half.data(), sent.data(), cnt); }
+      else { f32_to_bf16(t->val.data(), half.data(), cnt); bf16_to_f32(half.data(), sent.data(), cnt); }
+      for (size_t j = 0; j < cnt; ++j) {
+        const float s = std::isfinite(sent[j]) ? sent[j] : 0.f;   // fp16 overflow: keep the whole value for later
+        acc[t->idx[j]] = t->val[j] - s;
+        t->val[j] = s;
+      }
+    }
     std::memcpy(p.resid, acc, static_cast<size_t>(p.numel) * sizeof(float));
     t->stat_end("CRIT_PATH_save_residual");
     if (W == 1) e.schedule_after_master_free(e.module("Optimize"), t);
@@ -158,7 +172,8 @@ class ModuleGradExchange : public Module {
     // ring all-gather: forward slot `round` to the successor, expect slot `round + 1` from the predecessor
     const std::string key = t->key + "!" + std::to_string(round);
     const size_t off = static_cast<size_t>(round) * t->k;
-    e.comm()->queue_tx(t->priority(), key, t->idx.data() + off, t->val.data() + off, t->counts[round], t->numel);
+    e.comm()->queue_tx(t->priority(), key, t->idx.data() + off, t->val.data() + off, t->counts[round], t->numel,
+                       true, e.wire_value_format(), e.wire_blocks());
     e.schedule_after_comm(this, t, key, round + 1);
   }
 };

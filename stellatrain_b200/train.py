@@ -61,6 +61,7 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
                                session=master_pid, local_world_size=local_world_size, local_rank=local_rank,
                                method=args.compressor, gradient_accumulation=args.gradient_accumulation,
                                staleness=args.staleness, ratio=args.compression, optimizer=args.optim,
+                               wire_blocks=not args.no_wire_blocks, wire_values=args.wire_values,
                                optimizer_options={"lr": args.lr, **({"momentum": args.momentum} if args.optim == "sgd" else {})})
         net, sync, engine_of = model, eng.synchronize, (lambda: eng)
 
@@ -185,6 +186,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--heartbeat", type=float, default=0.0, help="seconds of silence after which a rank counts as lost (0: off)")
     p.add_argument("--state-partition", default="replicated", choices=["replicated", "owner"])
     p.add_argument("--wire-format", default="wide", choices=["wide", "narrow"])
+    p.add_argument("--wire-values", default="fp32", choices=["fp32", "fp16", "bf16"],
+                   help="CPU tier: value type of the messages between nodes (the rounding error stays in the residual)")
+    p.add_argument("--no-wire-blocks", action="store_true",
+                   help="CPU tier: send (index, value) pairs even where 16 aligned indices could travel as one block id")
     p.add_argument("--log-every", type=int, default=10)
     return p
 

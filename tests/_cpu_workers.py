@@ -17,7 +17,8 @@ def synthetic_grad(node, local, step, pi, n):
 
 
 def engine_worker(q, port, session_base, world, node, local_world, local, steps, method, optimizer, staleness, mode):
-    """mode: 'ok' | 'absent' (never configures) | 'drop' (node 1 drops its gradient sends) | 'die' (node 1 exits mid-run)"""
+    """mode: 'ok' | 'ok_bf16' (bf16 values on the wire) | 'ok_pairs' (no block ids on the wire) | 'absent' (never
+    configures) | 'drop' (node 1 drops its gradient sends) | 'die' (node 1 exits mid-run)"""
     try:
         from stellatrain_b200 import cpu_tier
 
@@ -27,9 +28,14 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
             q.put((node, local, "absent", None))
             return
         eng = ext.CpuEngine()
+        wire = {"ok_bf16": (True, 2), "ok_pairs": (False, 0)}.get(mode)
+        if mode.startswith("ok"):
+            mode = "ok"
         timeout_ms = 4000 if mode != "ok" else 30000
         eng.configure("127.0.0.1", port, world, node, session_base + node, local_world, local, method, 1, staleness,
                       0.9, 32 << 20, timeout_ms, 4, False, True, mode == "ok")
+        if wire is not None:
+            eng.configure_wire(*wire)
         eng.set_optimizer(optimizer)
         eng.configure_optimizer("lr", 0.1 if optimizer == "sgd" else 1e-2)
         if optimizer == "sgd":
@@ -51,7 +57,8 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
         stats = eng.stats_json(False)
         eng.barrier()
         q.put((node, local, "ok", {"params": [p.numpy().copy() for p in params], "drift": drift,
-                                   "versions": [eng.model_version(pi) for pi in idxs], "stats_len": len(stats)}))
+                                   "versions": [eng.model_version(pi) for pi in idxs], "stats_len": len(stats),
+                                   "tx_bytes": eng.comm_bytes()[0]}))
         del eng
     except Exception as e:  # noqa: BLE001
         q.put((node, local, "error", f"{type(e).__name__}: {e}\n{traceback.format_exc()[-600:]}"))

@@ -215,3 +215,21 @@ def test_controller_keeps_its_state_across_a_restart(tmp_path):
         assert len(b.optimizer.alphas) == 3 and b.optimizer.phase == Phase.INIT_WARMUP
     finally:
         b.close()
+
+
+def test_traffic_model_matches_the_block_wire_format():
+    """The controller's byte model of the framed TCP transport follows the encoder: whole blocks of 16 entries behind
+    one block id, loose entries as pairs."""
+    from stellatrain_b200 import cpu_tier
+
+    ext = cpu_tier._load()
+    n, ratio = 400_000, 0.99
+    k = 4000
+    idx = [j for b in range(0, k // 16) for j in range(64 * b, 64 * b + 16)]
+    _, payload = ext.encode_sparse(idx, [1.0] * len(idx), n)
+    pairs = TrafficModel([n], "tcp").tx_bytes(ratio)
+    blocks = TrafficModel([n], "tcp", grad_block16=True).tx_bytes(ratio)
+    header = 24 + 16
+    assert abs((blocks - header) - len(payload)) <= 0.05 * len(payload) + 0x42 * 12   # payload + per-segment headers
+    assert blocks < 0.56 * pairs
+    assert TrafficModel([8], "tcp", grad_block16=True).tx_bytes(0.5) == TrafficModel([8], "tcp").tx_bytes(0.5)
