@@ -2,9 +2,10 @@
 
 * ``FastDataLoader``: a ``DataLoader`` whose worker processes survive across epochs (repeat sampler).
 * ``PrefetchLoader``: produces batches in a background thread and copies them to the device from pinned
-  memory on a side stream, so that the host-to-device copy of batch i+1 overlaps step i (the reference
-  moves its loader into a subprocess, ``SuperFastDataLoader``; on one GPU per process the copy overlap is
-  what matters).
+  memory on a side stream, so that the host-to-device copy of batch i+1 overlaps step i.
+* ``SuperFastDataLoader``: runs a whole loader in a child process and hands batches over through shared
+  memory (util/dataloader.py:41-71), for pipelines whose Python-side decoding would otherwise compete
+  with the training loop for the interpreter lock; wrap it in a ``PrefetchLoader`` for the device copy.
 * ``DummyInputGenerator``: one fixed random batch repeated ``length`` times (images N(0,1), labels uniform).
 * builders for ImageNet, ImageNet-100, CIFAR-10/100 and dummy data with a ``DistributedSampler``.
 """
@@ -106,7 +107,95 @@ class PrefetchLoader:
                 self._record_stream(o, stream)
 
 
-SuperFastDataLoader = PrefetchLoader
+def _loader_process(factory: Callable, out, stop, epochs: int) -> None:
+    """Body of the child process of ``SuperFastDataLoader``."""
+    torch.set_num_threads(1)
+    try:
+        loader = factory()
+        out.put(("len", len(loader) if hasattr(loader, "__len__") else -1))
+        for _ in range(epochs):
+            for batch in loader:
+                if stop.is_set():
+                    return
+                out.put(("batch", batch))
+            out.put(("end", None))
+    except Exception as e:  # noqa: BLE001 - reported to the parent
+        out.put(("error", f"{type(e).__name__}: {e}"))
+    # tensors travel as file descriptors that the parent fetches from this process when it unpickles a batch:
+    # stay until the parent says it is done
+    stop.wait()
+
+
+class SuperFastDataLoader:
+    """A loader that lives in a child process.
+
+    ``factory`` is a picklable callable that builds the loader inside the child (a loader with worker processes
+    cannot be pickled once it runs).  Batches come back through a bounded queue; tensors travel in shared memory,
+    so the parent does not copy them.  ``len()`` is the child's loader length.  Every wait has a limit: a child that
+    dies or stalls raises ``RuntimeError`` in the parent instead of blocking the training loop forever.
+    """
+
+    def __init__(self, factory: Callable, depth: int = 4, epochs: int = 1 << 30, timeout_s: float = 300.0,
+                 start_method: str = "spawn") -> None:
+        import torch.multiprocessing as tmp
+
+        ctx = tmp.get_context(start_method)
+        self._q = ctx.Queue(maxsize=depth)
+        self._stop = ctx.Event()
+        self._timeout = timeout_s
+        self._proc = ctx.Process(target=_loader_process, args=(factory, self._q, self._stop, epochs), daemon=True,
+                                 name="SuperFastDataLoader")
+        self._proc.start()
+        kind, value = self._get(max(timeout_s, 120.0))     # starting an interpreter and importing torch takes a while
+        if kind == "error":
+            self.close()
+            raise RuntimeError(f"the loader process failed to start: {value}")
+        self._len = int(value)
+
+    def _get(self, limit: Optional[float] = None):
+        waited, limit = 0.0, (self._timeout if limit is None else limit)
+        while True:
+            try:
+                return self._q.get(timeout=0.5)
+            except queue.Empty:
+                waited += 0.5
+                if not self._proc.is_alive() and self._q.empty():
+                    raise RuntimeError("the loader process exited") from None
+                if waited >= limit:
+                    raise RuntimeError(f"no batch from the loader process within {limit:.0f} s") from None
+
+    def __len__(self) -> int:
+        if self._len < 0:
+            raise TypeError("the wrapped loader has no length")
+        return self._len
+
+    def __iter__(self) -> Iterator:
+        while True:
+            kind, value = self._get()
+            if kind == "end":
+                return
+            if kind == "error":
+                raise RuntimeError(f"the loader process failed: {value}")
+            yield value
+
+    def close(self) -> None:
+        self._stop.set()
+        try:
+            while True:                      # unblock a child that waits for room in the queue
+                self._q.get_nowait()
+        except (queue.Empty, OSError, ValueError):
+            pass
+        self._proc.join(timeout=5)
+        if self._proc.is_alive():
+            self._proc.terminate()           # this exact child, by handle
+            self._proc.join(timeout=5)
+
+    def __del__(self) -> None:
+        try:
+            if self._proc.is_alive():
+                self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
 
 
 class DummyInputGenerator:

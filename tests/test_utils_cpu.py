@@ -117,3 +117,45 @@ def test_imagenet100_keeps_only_listed_classes(tmp_path):
     (tmp_path / "imagenet100.txt").write_text("n99 nothing\n")
     with pytest.raises(FileNotFoundError):
         ImageNet100(str(tmp_path), "train")                  # none of the listed classes is present
+
+
+def _small_loader():
+    ds = torch.utils.data.TensorDataset(torch.arange(24, dtype=torch.float32).view(12, 2), torch.arange(12))
+    return torch.utils.data.DataLoader(ds, batch_size=4)
+
+
+def _broken_loader():
+    raise OSError("no such dataset")
+
+
+class _Stalls:
+    def __len__(self):
+        return 1
+
+    def __iter__(self):
+        import time
+
+        time.sleep(60)
+        yield None
+
+
+def test_loader_in_a_child_process():
+    sub = D.SuperFastDataLoader(_small_loader, depth=2, epochs=2)
+    try:
+        assert len(sub) == 3
+        for _ in range(2):                                   # two epochs come from the same child
+            got = list(sub)
+            assert [b[1].tolist() for b in got] == [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9, 10, 11]]
+            assert got[2][0].tolist() == [[16.0, 17.0], [18.0, 19.0], [20.0, 21.0], [22.0, 23.0]]
+    finally:
+        sub.close()
+    assert not sub._proc.is_alive()
+    with pytest.raises(RuntimeError, match="no such dataset"):
+        D.SuperFastDataLoader(_broken_loader)
+    stalled = D.SuperFastDataLoader(_Stalls, timeout_s=1.0)   # a child that never delivers: an error, not a hang
+    try:
+        with pytest.raises(RuntimeError, match="no batch"):
+            next(iter(stalled))
+    finally:
+        stalled.close()
+    assert not stalled._proc.is_alive()
