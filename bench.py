@@ -39,7 +39,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_sparse", "ddp", "dense_single", "dense_graph"],
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_sparse", "ddp", "dense_single", "dense_graph", "cpu_offload"],
                     help="dense_graph: plain PyTorch step with capturable Adam/SGD captured in one CUDA graph (1 GPU), the "
                          "strongest dense baseline for the N = 1 point")
     ap.add_argument("--model", default="resnet152")
@@ -164,14 +164,42 @@ def main() -> None:
     torch.backends.cudnn.benchmark = True
 
     lm = is_language_model(args.model)
+    if args.impl == "cpu_offload":
+        args.channels_last, args.graph = 0, 0      # the CPU tier reads and writes contiguous parameters, eagerly
     model = build_model(args.model, args.num_classes).to(dev)
     if args.channels_last and not lm:
         model = model.to(memory_format=torch.channels_last)
     n_params = sum(p.numel() for p in model.parameters())
 
     engine = None
+    cpu_engine = None
     opt = None
-    if args.impl in ("ours", "nccl_sparse"):
+    if args.impl == "cpu_offload":
+        # The reference's own pipeline shape, built from this package's CPU tier: gradients leave the GPU into
+        # pinned shared memory, are reduced, sparsified and applied by the sparse optimiser on the host, and the
+        # parameters come back; one node, one process per GPU.
+        from stellatrain_b200.cpu_tier import CpuOffloadEngine
+
+        if world > 1:
+            dist.init_process_group("nccl", init_method=f"tcp://{master_addr}:{master_port}", world_size=world,
+                                    rank=rank, device_id=dev)
+        session = (os.getppid() if world > 1 else os.getpid()) % 1000000 + 1000000
+        need = int(n_params * 4 * (2 + 2 * world) * 1.25) + (72 << 20)
+        vfs = os.statvfs("/dev/shm")
+        if vfs.f_bavail * vfs.f_frsize < need + (256 << 20):
+            if rank == 0:
+                os.write(json_fd, (json.dumps({"impl": "cpu_offload", "unavailable":
+                         f"/dev/shm has {vfs.f_bavail * vfs.f_frsize >> 20} MiB free, the pinned pool needs {need >> 20} MiB"}) + "\n").encode())
+            return
+        options = {"lr": args.lr}
+        if args.optimizer == "sgd" and args.momentum:
+            options["momentum"] = args.momentum
+        cpu_engine = CpuOffloadEngine(model, master_addr=master_addr, master_port=master_port + 23, world_size=1, rank=0,
+                                      session=session, local_world_size=world, local_rank=rank, method=args.compressor,
+                                      staleness=args.staleness, ratio=args.ratio, optimizer=args.optimizer,
+                                      optimizer_options=options, timeout_ms=120000)
+        net = model
+    elif args.impl in ("ours", "nccl_sparse"):
         st.configure(master_addr, master_port, 1, 0, os.getpid(), world, rank, args.compressor, 1,
                      staleness=args.staleness, transport=("nccl" if args.impl == "nccl_sparse" else None))
         st.configure_compression_ratio(args.ratio)
@@ -316,6 +344,8 @@ def main() -> None:
     def sync_all():
         if engine is not None:
             engine.synchronize()
+        if cpu_engine is not None:
+            cpu_engine.synchronize()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
@@ -332,6 +362,8 @@ def main() -> None:
             fn(i)
         if engine is not None:
             engine.synchronize()     # the last updates are part of the measured work
+        if cpu_engine is not None:
+            cpu_engine.synchronize()
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
@@ -369,6 +401,9 @@ def main() -> None:
     if engine is not None:
         engine.synchronize()
         engine.check_status()
+    if cpu_engine is not None:
+        cpu_engine.synchronize()
+        cpu_engine.close()
 
     if rank == 0:
         out = {
@@ -385,7 +420,8 @@ def main() -> None:
                 "per_gpu_batch": args.batch, "seq_len": args.seq_len if lm else None, "parallelism": f"dp{world}",
                 "compressor": args.compressor, "kept_fraction": 1 - args.ratio, "optimizer": args.optimizer,
                 "lr": args.lr, "staleness": args.staleness, "bucket_mb": args.bucket_mb,
-                "transport": engine.transport if engine is not None else args.impl, "group_size": args.group_size,
+                "transport": engine.transport if engine is not None else
+                             ("pinned shared memory, host pipeline" if cpu_engine is not None else args.impl), "group_size": args.group_size,
                 "state_partition": args.state_partition, "shaped_link_gbps": args.shape_gbps,
                 "controller": ({"instructions_applied": len(hook.applied), "final_ratio": engine.cfg.ratio,
                                 "shaped_gbps_achieved": (engine.shaper.achieved_gbps() if engine.shaper else None)}
