@@ -63,6 +63,8 @@ def parse_args() -> argparse.Namespace:
                     help="owner: optimiser state of every tensor on one rank, new values stored into all replicas")
     ap.add_argument("--shape-gbps", default=None, help="lo:hi[:seed] emulated cross-group link, e.g. 10:40:0")
     ap.add_argument("--controller", type=int, default=0, help="run the telemetry controller and apply its instructions")
+    ap.add_argument("--native-copies", type=int, default=0,
+                    help="cpu_offload arm: 1 lets the native engine issue the device copies itself")
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
 
@@ -197,7 +199,8 @@ def main() -> None:
         cpu_engine = CpuOffloadEngine(model, master_addr=master_addr, master_port=master_port + 23, world_size=1, rank=0,
                                       session=session, local_world_size=world, local_rank=rank, method=args.compressor,
                                       staleness=args.staleness, ratio=args.ratio, optimizer=args.optimizer,
-                                      optimizer_options=options, timeout_ms=120000)
+                                      optimizer_options=options, timeout_ms=120000,
+                                      native_copies=bool(args.native_copies))
         net = model
     elif args.impl in ("ours", "nccl_sparse"):
         st.configure(master_addr, master_port, 1, 0, os.getpid(), world, rank, args.compressor, 1,
@@ -421,7 +424,8 @@ def main() -> None:
                 "compressor": args.compressor, "kept_fraction": 1 - args.ratio, "optimizer": args.optimizer,
                 "lr": args.lr, "staleness": args.staleness, "bucket_mb": args.bucket_mb,
                 "transport": engine.transport if engine is not None else
-                             ("pinned shared memory, host pipeline" if cpu_engine is not None else args.impl), "group_size": args.group_size,
+                             ("pinned shared memory, host pipeline, copies by the " + ("native engine" if args.native_copies else "Python class")
+                              if cpu_engine is not None else args.impl), "group_size": args.group_size,
                 "state_partition": args.state_partition, "shaped_link_gbps": args.shape_gbps,
                 "controller": ({"instructions_applied": len(hook.applied), "final_ratio": engine.cfg.ratio,
                                 "shaped_gbps_achieved": (engine.shaper.achieved_gbps() if engine.shaper else None)}

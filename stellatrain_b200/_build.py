@@ -58,7 +58,7 @@ EXTENSIONS = {
         "cu": [],
         "cpp": [
             "cpu/compressors.cpp", "cpu/optimizers.cpp", "cpu/array_util.cpp", "cpu/xorshift.cpp",
-            "core/threadpool.cpp", "core/task.cpp", "core/shm_manager.cpp", "core/engine.cpp",
+            "core/threadpool.cpp", "core/task.cpp", "core/shm_manager.cpp", "core/engine.cpp", "core/cuda_api.cpp", "core/fake_cuda.cpp",
             "core/stages.cpp", "comm/comm_manager.cpp", "comm/net_util.cpp",
             "telemetry/telemetry.cpp", "bindings_cpu.cpp",
         ],

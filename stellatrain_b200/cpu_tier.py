@@ -89,7 +89,7 @@ class CpuOffloadEngine:
                  method: str = "thresholdv16", gradient_accumulation: int = 1, staleness: int = 1, ratio: float = 0.99,
                  optimizer: str = "sgd", optimizer_options: Optional[dict] = None, data_bytes: int = 0,
                  timeout_ms: int = 30000, workers: int = 0, debug_accuracy: bool = False, debug_barrier: bool = False,
-                 wire_blocks: bool = True, wire_values: str = "fp32"):
+                 wire_blocks: bool = True, wire_values: str = "fp32", native_copies: bool = False):
         ext = _load()
         self.module = module
         self.engine = ext.CpuEngine()
@@ -114,20 +114,35 @@ class CpuOffloadEngine:
         for li, (name, p) in enumerate(params):
             if not p.is_contiguous():
                 raise ValueError(f"parameter {name} must be contiguous")
-            user = 0 if self.cuda else p.data.data_ptr()
-            idx = self.engine.pre_train_init(li, name[-40:], p.numel(), user)
+            if self.cuda:
+                # the engine never writes device memory through `user_param`; it starts the master copy from a host copy
+                # of the initial values
+                init = p.detach().reshape(-1).to("cpu", torch.float32).contiguous()
+                idx = self.engine.pre_train_init(li, name[-40:], p.numel(), 0, init.data_ptr())
+            else:
+                idx = self.engine.pre_train_init(li, name[-40:], p.numel(), p.data.data_ptr())
             self.params.append(p)
             self._index[id(p)] = idx
             if self.cuda:
                 master = _from_ptr(self.engine.master_param(idx), p.numel())
                 p.data.copy_(master.view_as(p), non_blocking=False)
+        # CUDA parameters, two ways to move data: copies issued by this class with torch streams and two helper threads,
+        # or by the native engine itself (event, stream wait, asynchronous copy and a host callback per tensor, its
+        # D2H_Copy / H2D_Copy stages); the second needs no Python thread on the path of a task
+        self.native_copies = bool(native_copies and self.cuda)
+        if self.native_copies:
+            if not self.engine.device_copies_available():
+                raise RuntimeError("native_copies=True needs the CUDA runtime in this process")
+            self._native_streams = [torch.cuda.Stream() for _ in range(4)]
+            for idx, p in enumerate(self.params):
+                self.engine.attach_device_param(self._index[id(p)], p.data.data_ptr())
         self._hooks = [p.register_post_accumulate_grad_hook(self._on_grad) for p in self.params]
         self._hooks.append(module.register_forward_pre_hook(self._pre_forward))
         self._stop = False
         self._copy_stream = torch.cuda.Stream() if self.cuda else None
         self._h2d_thread = None
         self._pending_events: list = []
-        if self.cuda:
+        if self.cuda and not self.native_copies:
             self._h2d_thread = threading.Thread(target=self._h2d_main, name="H2DCopy", daemon=True)
             self._h2d_thread.start()
             self._d2h_thread = threading.Thread(target=self._d2h_main, name="D2HCopy", daemon=True)
@@ -150,8 +165,14 @@ class CpuOffloadEngine:
         else:
             # device accumulation across micro-iterations, one D2H at the end (core.cpp:781-788)
             last = (self._micro == self.grad_accumulation - 1)
-            if last:
-                slot = _from_ptr(self.engine.grad_slot(idx), p.numel())
+            if last and self.native_copies:
+                g = g if (g.is_contiguous() and g.dtype == torch.float32) else g.contiguous().float()
+                stream = self._native_streams[idx % len(self._native_streams)]
+                self.engine.post_backward_device(idx, g.data_ptr(), torch.cuda.current_stream().cuda_stream, stream.cuda_stream)
+                g.record_stream(stream)          # the allocator must not reuse the gradient before the copy has read it
+                p.grad = None
+            elif last:
+                slot = _from_ptr(self.engine.claim_grad_slot(idx), p.numel())   # one per iteration, in turn
                 ev = torch.cuda.Event()
                 cur = torch.cuda.current_stream()
                 self._copy_stream.wait_stream(cur)
@@ -195,7 +216,9 @@ class CpuOffloadEngine:
 
     # ------------------------------------------------------------------ control
     def synchronize(self) -> None:
-        if self.cuda:
+        if self.cuda and self.native_copies:
+            torch.cuda.synchronize()
+        elif self.cuda:
             torch.cuda.synchronize()
             import time
             while True:

@@ -15,6 +15,7 @@
 #include "comm/comm_manager.h"
 #include "comm/net_util.h"
 #include "core/config.h"
+#include "core/cuda_api.h"
 #include "core/engine.h"
 #include "core/logger.h"
 #include "core/shm_manager.h"
@@ -142,6 +143,14 @@ PYBIND11_MODULE(_Ccpu, m) {
       throw std::invalid_argument("malformed sparse payload");
     return py::make_tuple(idx, val);
   }, py::arg("flags"), py::arg("payload"), py::arg("tensor_numel") = 0);
+  m.def("install_fake_cuda", &install_fake_cuda, py::arg("delay_ms") = 0,
+        "Replace the CUDA runtime calls of the engine's device copies by worker threads over host memory (tests).");
+  m.def("remove_fake_cuda", &remove_fake_cuda);
+  m.def("fake_cuda_counters", [] {
+    long a, b, c;
+    fake_cuda_counters(&a, &b, &c);
+    return py::make_tuple(a, b, c);
+  });
   m.def("narrow_u32_to_u16", [](uint64_t s, uint64_t d, size_t n) { narrow_u32_to_u16(P<const uint32_t>(s), P<uint16_t>(d), n); });
   m.def("widen_u16_to_u32", [](uint64_t s, uint64_t d, size_t n) { widen_u16_to_u32(P<const uint16_t>(s), P<uint32_t>(d), n); });
   m.def("f32_to_f16", [](uint64_t s, uint64_t d, size_t n) { f32_to_f16(P<const float>(s), P<uint16_t>(d), n); });
@@ -312,10 +321,11 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def("is_debug_accuracy_mode", [](CpuEngine& e) { return e.options().debug_accuracy; })
       .def("barrier", &CpuEngine::barrier, py::call_guard<py::gil_scoped_release>())
       .def("synchronize", &CpuEngine::synchronize, py::call_guard<py::gil_scoped_release>())
-      .def("pre_train_init", [](CpuEngine& e, int layer, const std::string& name, uint32_t numel, uint64_t user_param) {
+      .def("pre_train_init", [](CpuEngine& e, int layer, const std::string& name, uint32_t numel, uint64_t user_param,
+                                uint64_t init_values) {
         py::gil_scoped_release rel;
-        return e.pre_train_init(layer, name, numel, P<float>(user_param));
-      })
+        return e.pre_train_init(layer, name, numel, P<float>(user_param), P<const float>(init_values));
+      }, py::arg("layer"), py::arg("name"), py::arg("numel"), py::arg("user_param"), py::arg("init_values") = 0)
       .def("pre_forward_process", &CpuEngine::pre_forward_process, py::call_guard<py::gil_scoped_release>())
       .def("post_backward_process", [](CpuEngine& e, int index, uint64_t grad) {
         py::gil_scoped_release rel;
@@ -334,6 +344,12 @@ PYBIND11_MODULE(_Ccpu, m) {
         const uint64_t tx = e.comm() ? e.comm()->bytes_sent() : 0, rx = e.comm() ? e.comm()->bytes_received() : 0;
         return py::make_tuple(tx, rx);
       })
+      .def("claim_grad_slot", [](CpuEngine& e, int i) { return reinterpret_cast<uint64_t>(e.claim_grad_slot(i)); })
+      .def("device_copies_available", &CpuEngine::device_copies_available)
+      .def("attach_device_param", [](CpuEngine& e, int i, uint64_t dev) { e.attach_device_param(i, P<void>(dev)); })
+      .def("post_backward_device", [](CpuEngine& e, int i, uint64_t grad, uint64_t producer_stream, uint64_t copy_stream) {
+        e.post_backward_device(i, P<const void>(grad), P<void>(producer_stream), P<void>(copy_stream));
+      }, py::arg("param_index"), py::arg("device_grad"), py::arg("producer_stream"), py::arg("copy_stream") = 0)
       .def("drop_tx_containing", [](CpuEngine& e, const std::string& needle) {
         if (!e.comm()) return;
         e.comm()->set_tx_fault_hook([needle](const std::string& key, int*) { return key.find(needle) != std::string::npos; });

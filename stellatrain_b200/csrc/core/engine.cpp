@@ -9,6 +9,7 @@
 
 #include "../cpu/array_util.h"
 #include "config.h"
+#include "cuda_api.h"
 #include "logger.h"
 
 namespace stc {
@@ -32,6 +33,13 @@ CpuEngine::~CpuEngine() {
     version_cv_.notify_all();
   }
   if (barrier_thread_.joinable()) barrier_thread_.join();
+  if (const CudaApi* api = cuda_api()) {
+    // host callbacks still queued in a copy stream refer to this object
+    for (void* s : copy_streams_) api->stream_synchronize(s);
+    for (int i = 0; i < 2000 && callbacks_in_flight_.load() > 0; ++i) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    for (void* s : copy_streams_) api->stream_destroy(s);
+    for (auto& p : params_) if (p.grad_event) api->event_destroy(p.grad_event);
+  }
   pool_.reset();      // joins the workers before the memory they use goes away
   comm_.reset();
   shm_.reset();
@@ -100,7 +108,7 @@ void CpuEngine::barrier() {
 }
 
 // ---------------------------------------------------------------- registration
-int CpuEngine::pre_train_init(int layer, const std::string& name, uint32_t numel, float* user_param) {
+int CpuEngine::pre_train_init(int layer, const std::string& name, uint32_t numel, float* user_param, const float* init_values) {
   if (!ready_) throw std::runtime_error("configure() first");
   const int index = static_cast<int>(params_.size());
   if (index >= cfg::kMaxParams) throw std::runtime_error("too many parameters");
@@ -115,7 +123,8 @@ int CpuEngine::pre_train_init(int layer, const std::string& name, uint32_t numel
     float* master = static_cast<float*>(shm_->alloc(bytes));
     float* resid = static_cast<float*>(shm_->alloc(bytes));
     std::memset(resid, 0, bytes);
-    if (user_param) std::memcpy(master, user_param, bytes); else std::memset(master, 0, bytes);
+    const float* init = init_values ? init_values : user_param;
+    if (init) std::memcpy(master, init, bytes); else std::memset(master, 0, bytes);
     e->master_off = shm_->offset_of(master);
     e->resid_off = shm_->offset_of(resid);
     for (int s = 0; s < 2; ++s)
@@ -178,6 +187,94 @@ void CpuEngine::pre_forward_process(int index) {
 float* CpuEngine::grad_slot(int index) {
   ParamLocal& p = params_.at(index);
   return p.slot[p.alloc_cnt % 2][opt_.local_rank];
+}
+
+float* CpuEngine::claim_grad_slot(int index) {
+  ParamLocal& p = params_.at(index);
+  return p.slot[p.claim_cnt++ % 2][opt_.local_rank];
+}
+
+// ---------------------------------------------------------------- device copies
+namespace {
+constexpr int kCopyStreams = 4;
+
+struct AfterCuda {
+  CpuEngine* engine;
+  std::function<void()> fn;
+  std::atomic<int>* in_flight;
+};
+
+// Runs on a thread of the CUDA runtime, in stream order: it must not call the runtime and should be short.  The
+// continuations only create a task or put a stage into the pool's queue; running them here, not in the pool, keeps
+// two callbacks of one parameter in the order of their copies.
+void after_cuda_trampoline(void* user) {
+  std::unique_ptr<AfterCuda> a(static_cast<AfterCuda*>(user));
+  try {
+    a->fn();
+  } catch (const std::exception& e) {
+    LOG_ERROR("CpuEngine", "continuation behind a device copy failed: " << e.what());
+  }
+  a->in_flight->fetch_sub(1);
+}
+}  // namespace
+
+bool CpuEngine::device_copies_available() const { return cuda_api() != nullptr; }
+
+void* CpuEngine::copy_stream_for(int index) {
+  const CudaApi* api = cuda_api();
+  if (!api) return nullptr;
+  std::lock_guard<std::mutex> lk(copy_mu_);
+  if (copy_streams_.empty()) {
+    for (int i = 0; i < kCopyStreams; ++i) {
+      void* s = nullptr;
+      if (api->stream_create(&s) != 0) throw std::runtime_error("could not create a copy stream");
+      copy_streams_.push_back(s);
+    }
+  }
+  return copy_streams_[static_cast<size_t>(index) % copy_streams_.size()];
+}
+
+void CpuEngine::attach_device_param(int index, void* device_param) {
+  if (!cuda_api()) throw std::runtime_error("attach_device_param: no CUDA runtime in this process");
+  params_.at(index).device_param = device_param;
+}
+
+void CpuEngine::post_backward_device(int index, const void* device_grad, void* producer_stream, void* copy_stream) {
+  const CudaApi* api = cuda_api();
+  if (!api) throw std::runtime_error("post_backward_device: no CUDA runtime in this process");
+  ParamLocal& p = params_.at(index);
+  if (!copy_stream) copy_stream = copy_stream_for(index);
+  if (!p.grad_event && api->event_create(&p.grad_event) != 0) throw std::runtime_error("could not create an event");
+  float* slot = claim_grad_slot(index);
+  p.last_copy_stream = copy_stream;
+  const int reps = opt_.grad_accumulation;   // the device accumulated the micro-iterations: one copy stands for all
+  auto* after = new AfterCuda{this, [this, index, reps] {
+    try {
+      for (int i = 0; i < reps; ++i) post_backward_in_slot(index);
+    } catch (const std::exception& e) {
+      LOG_ERROR("CpuEngine", "starting the task of parameter " << index << " failed: " << e.what());
+    }
+  }, &callbacks_in_flight_};
+  callbacks_in_flight_.fetch_add(1);
+  const int rc = api->event_record(p.grad_event, producer_stream) | api->stream_wait_event(copy_stream, p.grad_event) |
+                 api->memcpy_d2h_async(slot, device_grad, static_cast<size_t>(p.numel) * sizeof(float), copy_stream) |
+                 api->launch_host_func(copy_stream, after_cuda_trampoline, after);
+  if (rc != 0) throw std::runtime_error("a CUDA runtime call of the gradient copy failed");
+}
+
+void CpuEngine::schedule_after_cuda(Module* next, const std::shared_ptr<TrainTask>& t, void* stream) {
+  const CudaApi* api = cuda_api();
+  if (!api) {
+    schedule(next, t);
+    return;
+  }
+  auto* after = new AfterCuda{this, [this, next, t] { schedule(next, t); }, &callbacks_in_flight_};
+  callbacks_in_flight_.fetch_add(1);
+  if (api->launch_host_func(stream, after_cuda_trampoline, after) != 0) {
+    callbacks_in_flight_.fetch_sub(1);
+    delete after;
+    fail_task(t, "cudaLaunchHostFunc failed before " + std::string(next->name()));
+  }
 }
 
 void CpuEngine::post_backward_process(int index, const float* grad) {
@@ -491,6 +588,15 @@ std::string CpuEngine::describe_task(const std::string& key) {
 
 // ---------------------------------------------------------------- synchronize
 void CpuEngine::synchronize() {
+  // gradient copies still in a stream have not started their tasks yet: wait for them first
+  if (const CudaApi* api = cuda_api()) {
+    std::vector<void*> streams;
+    for (auto& p : params_)
+      if (p.last_copy_stream && std::find(streams.begin(), streams.end(), p.last_copy_stream) == streams.end())
+        streams.push_back(p.last_copy_stream);
+    for (void* st : streams)
+      if (api->stream_synchronize(st) != 0) throw std::runtime_error("a copy stream did not finish");
+  }
   // release every "previous version still in use" gate (reference core.cpp:910-922)
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> runnable;
   {

@@ -102,19 +102,37 @@ class CpuEngine {
 
   // ---- per-parameter protocol
   // Registers a parameter (same order in every process).  `user_param` may be null when the caller
-  // moves data itself.  Returns the parameter index.
-  int pre_train_init(int layer, const std::string& name, uint32_t numel, float* user_param);
+  // moves data itself; the master copy then starts from `init_values` (numel floats, read during the call; zeros
+  // when null too).  With more than one node every node's master copy takes rank 0's values.  Returns the
+  // parameter index.
+  int pre_train_init(int layer, const std::string& name, uint32_t numel, float* user_param,
+                     const float* init_values = nullptr);
   void pre_forward_process(int param_index);
   // `grad` is a host pointer with numel floats; it is accumulated into this process's slot of the
   // current iteration.  The last micro-iteration starts the pipeline.
   void post_backward_process(int param_index, const float* grad);
   // Callers that copy by themselves:
   float* grad_slot(int param_index);              // where to put this iteration's gradient (zeroed by the engine)
+  // Same, for a caller whose copy into the slot completes later (an asynchronous device copy): hands out the slots
+  // of successive iterations in turn, so a second backward pass that is issued before the first copy has been
+  // reported cannot be given the same slot.  One claim per iteration, followed by post_backward_in_slot().
+  float* claim_grad_slot(int param_index);
   void post_backward_in_slot(int param_index);    // gradient already is in grad_slot()
   const float* master_param(int param_index) const;
   // Updates whose parameters are ready to be copied out by the caller: (param_index, iteration)
   std::vector<std::pair<int, int64_t>> pop_ready_updates(int max_wait_ms);
   void copy_out_done(int param_index, int64_t iter);
+  // ---- device copies done by the engine itself (the reference's D2H_Copy and H2D_Copy stages)
+  // True when a CUDA runtime (or a replacement table, see cuda_api.h) is available.
+  bool device_copies_available() const;
+  // The parameter's copy on the device: CopyOut then writes the master copy there on one of the engine's copy streams
+  // and the task goes on when the stream has reached that point (schedule_after_cuda).
+  void attach_device_param(int param_index, void* device_param);
+  // The accumulated gradient of the last micro-iteration, on the device.  An event on `producer_stream` orders
+  // the copy after the kernels that wrote the gradient; the copy runs on the parameter's copy stream into the pinned
+  // slot and the pipeline starts from a host callback behind it.  The caller keeps `device_grad` alive until that
+  // stream has passed the copy.  `copy_stream` may be null: the engine then uses a stream of its own.
+  void post_backward_device(int param_index, const void* device_grad, void* producer_stream, void* copy_stream);
   double force_model_sync(int param_index, bool dry_run);
   int64_t model_version(int param_index) const;
   int num_params() const { return static_cast<int>(params_.size()); }
@@ -124,6 +142,10 @@ class CpuEngine {
   void schedule_after_barrier(Module* m, const std::shared_ptr<TrainTask>& t, int stage_id);
   void schedule_after_comm(Module* m, const std::shared_ptr<TrainTask>& t, const std::string& key, int slot);
   void schedule_after_model_complete(Module* m, const std::shared_ptr<TrainTask>& t);
+  // Runs `m` once `stream` has finished the work enqueued so far (a host callback in the stream; reference
+  // core_module_api.cpp:201-277).  Without a CUDA runtime the stage runs at once.
+  void schedule_after_cuda(Module* m, const std::shared_ptr<TrainTask>& t, void* stream);
+  void* copy_stream_for(int param_index);
   // Runs `m` once the previous iteration of the same parameter has left its optimise stage:
   // residual, optimiser state and master parameter are per-parameter state that iteration i+1 must
   // see as iteration i left it.
@@ -160,6 +182,10 @@ class CpuEngine {
     int64_t sequenced_iter = -1;             // last iteration that left the optimise stage
     int64_t master_read_iter = -1;           // last iteration whose copy-out has finished reading the master
     int micro = 0;
+    int64_t claim_cnt = 0;                   // gradient slots handed out by claim_grad_slot
+    void* device_param = nullptr;            // set by attach_device_param
+    void* grad_event = nullptr;              // orders the device-to-host copy after the backward kernels
+    void* last_copy_stream = nullptr;        // stream of the latest device-to-host copy of this parameter
     bool checked_barrier = false;
     std::vector<float> merge_scratch;        // node master: dense accumulator of the merge
     std::vector<uint8_t> merge_touched;
@@ -222,6 +248,11 @@ class CpuEngine {
   std::string first_error_;
   std::mutex stats_mu_;
   std::list<std::pair<std::string, std::map<std::string, double>>> stat_ring_;   // bounded history
+
+  // device copies
+  std::mutex copy_mu_;
+  std::vector<void*> copy_streams_;
+  std::atomic<int> callbacks_in_flight_{0};
 
   std::mutex ready_mu_;
   std::condition_variable ready_cv_;

@@ -9,6 +9,7 @@
 
 #include "../cpu/array_util.h"
 #include "config.h"
+#include "cuda_api.h"
 #include "engine.h"
 #include "logger.h"
 
@@ -230,11 +231,33 @@ class ModuleCopyOut : public Module {
     auto& p = e.param(t->param_index);
     // the slot is consumed: clear this process's part for the next use
     std::memset(p.slot[t->iter % 2][e.options().local_rank], 0, static_cast<size_t>(p.numel) * sizeof(float));
+    if (p.device_param != nullptr) {
+      // host-to-device copy on the stream that carried this parameter's latest gradient copy: that copy waited for the
+      // backward kernels that last read the parameter, so stream order keeps the write behind every reader
+      const CudaApi* api = cuda_api();
+      void* stream = p.last_copy_stream ? p.last_copy_stream : e.copy_stream_for(t->param_index);
+      if (!api || api->memcpy_h2d_async(p.device_param, p.master, static_cast<size_t>(p.numel) * sizeof(float), stream) != 0) {
+        e.fail_task(t, "host-to-device copy of the parameter failed");
+        return;
+      }
+      e.schedule_after_cuda(e.module("CopyOutPost"), t, stream);
+      return;
+    }
     if (p.user_param == nullptr) {
       e.push_ready_update(t->param_index, t->iter);   // the caller copies and reports copy_out_done()
       return;
     }
     std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
+    e.schedule_after_barrier(e.module("CopyOutDone"), t, kAfterCopyOut);
+  }
+};
+
+// Behind the asynchronous host-to-device copy (reference H2D_Copy_Post, h2d_copy.cpp:59-72): wait for the other local
+// processes, then finish.
+class ModuleCopyOutPost : public Module {
+ public:
+  const char* name() const override { return "CopyOutPost"; }
+  void run(CpuEngine& e, const std::shared_ptr<TrainTask>& t) override {
     e.schedule_after_barrier(e.module("CopyOutDone"), t, kAfterCopyOut);
   }
 };
@@ -270,6 +293,7 @@ void CpuEngine::load_modules() {
   add(std::make_unique<ModuleOptimize>());
   add(std::make_unique<ModuleWaitModel>());
   add(std::make_unique<ModuleCopyOut>());
+  add(std::make_unique<ModuleCopyOutPost>());
   add(std::make_unique<ModuleCopyOutDone>());
 }
 

@@ -278,3 +278,58 @@ def test_lost_peer_surfaces_as_error(mode):
     by_node = {n: (s, info) for n, l, s, info in results}
     assert by_node[0][0] == "error", results     # node 0 never gets node 1's stream
     assert any(w in by_node[0][1] for w in ("timed out", "failed", "closed")), by_node[0][1]
+
+
+def _run_single_process_engine(device_copies, staleness, delay_ms=0, steps=6):
+    from _cpu_workers import SIZES, synthetic_grad
+
+    session = (os.getpid() % 10000) * 1000 + np.random.randint(0, 900)
+    if device_copies:
+        ext.install_fake_cuda(delay_ms)
+    try:
+        eng = ext.CpuEngine()
+        eng.configure("127.0.0.1", free_port(), 1, 0, session, 1, 0, "thresholdv16", 1, staleness, 0.9, 32 << 20, 20000, 4,
+                      False, True, False)
+        eng.set_optimizer("adam")
+        eng.configure_optimizer("lr", 1e-2)
+        params = [torch.full((n,), 0.5) for n in SIZES]            # with device copies these play the device memory
+        idxs = [eng.pre_train_init(pi, f"p{pi}", p.numel(), 0, p.data_ptr()) if device_copies else
+                eng.pre_train_init(pi, f"p{pi}", p.numel(), p.data_ptr()) for pi, p in enumerate(params)]
+        keep = []
+        if device_copies:
+            assert eng.device_copies_available()
+            for pi, p in zip(idxs, params):
+                eng.attach_device_param(pi, p.data_ptr())
+        for step in range(steps):
+            for pi in idxs:
+                eng.pre_forward_process(pi)
+            for pi in reversed(idxs):
+                g = synthetic_grad(0, 0, step, pi, SIZES[pi])
+                if device_copies:
+                    keep.append(g)                                 # alive until the copy stream has read it
+                    eng.post_backward_device(pi, g.data_ptr(), 0)
+                else:
+                    eng.post_backward_process(pi, g.data_ptr())
+        eng.synchronize()
+        versions = [eng.model_version(pi) for pi in idxs]
+        counters = ext.fake_cuda_counters() if device_copies else None
+        del eng
+        return [p.clone() for p in params], versions, counters
+    finally:
+        if device_copies:
+            ext.remove_fake_cuda()
+        ext.ShmManager.unlink_session(session)
+
+
+@pytest.mark.parametrize("staleness,delay_ms", [(0, 0), (1, 0), (1, 3)])
+def test_engine_device_copies_against_a_fake_runtime(staleness, delay_ms):
+    """The engine's own gradient and parameter copies (event, stream wait, asynchronous copy, host callback) give the
+    same parameters as the host path, also when the copy streams lag behind the host by whole iterations."""
+    steps = 6
+    want, _, _ = _run_single_process_engine(False, staleness, steps=steps)
+    got, versions, (d2h, h2d, funcs) = _run_single_process_engine(True, staleness, delay_ms, steps=steps)
+    assert versions == [steps] * 3
+    assert d2h == 3 * steps and h2d == 3 * steps and funcs == 2 * 3 * steps   # one callback behind every copy
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert any(float((a - 0.5).abs().max()) > 0 for a in got)

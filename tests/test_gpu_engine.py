@@ -384,9 +384,11 @@ def test_engine_with_debug_checks_trains_like_without():
         assert torch.equal(a, b)
 
 
-def test_cpu_offload_tier_with_a_cuda_model():
+@pytest.mark.parametrize("native_copies", [False, True])
+def test_cpu_offload_tier_with_a_cuda_model(native_copies):
     """The CPU-offload tier under a model on the GPU: gradients go to pinned shared slots on a copy stream, the
-    C++ pipeline compresses and optimises on the host, updated parameters come back by asynchronous copies."""
+    C++ pipeline compresses and optimises on the host, updated parameters come back by asynchronous copies, issued
+    either by the Python class or by the native engine itself."""
     import torch.nn as nn
     import torch.nn.functional as F
 
@@ -396,7 +398,8 @@ def test_cpu_offload_tier_with_a_cuda_model():
     model = nn.Sequential(nn.Linear(64, 128), nn.ReLU(), nn.Linear(128, 10)).cuda()
     before = [p.detach().clone() for p in model.parameters()]
     eng = CpuOffloadEngine(model, method="thresholdv16", ratio=0.9, optimizer="adam", optimizer_options={"lr": 1e-2},
-                           staleness=1, data_bytes=16 << 20, workers=4)
+                           staleness=1, data_bytes=16 << 20, workers=4, native_copies=native_copies)
+    assert all(torch.equal(p, q) for p, q in zip(model.parameters(), before)), "attaching must keep the initial values"
     g = torch.Generator(device="cuda").manual_seed(1)
     x, y = torch.randn(128, 64, device="cuda", generator=g), torch.randint(0, 10, (128,), device="cuda", generator=g)
     losses = []
@@ -407,6 +410,6 @@ def test_cpu_offload_tier_with_a_cuda_model():
     eng.synchronize()
     assert all(torch.isfinite(p).all() for p in model.parameters())
     assert any(not torch.equal(p, q) for p, q in zip(model.parameters(), before))
-    assert losses[-1] < losses[0]
+    assert losses[-1] < 0.9 * losses[0]        # the hidden layer has to learn for this, not only the output bias
     assert "Total" in eng.stats_json()
     eng.close()
