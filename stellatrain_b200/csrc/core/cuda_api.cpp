@@ -17,6 +17,8 @@ using EventRecordFn = int (*)(void*, void*);
 using StreamWaitFn = int (*)(void*, void*, unsigned);
 using MemcpyAsyncFn = int (*)(void*, const void*, size_t, int, void*);
 using HostFuncFn = int (*)(void*, void (*)(void*), void*);
+using GetDeviceFn = int (*)(int*);
+using SetDeviceFn = int (*)(int);
 
 struct Runtime {
   StreamCreateFn stream_create = nullptr;
@@ -26,6 +28,8 @@ struct Runtime {
   StreamWaitFn stream_wait = nullptr;
   MemcpyAsyncFn memcpy_async = nullptr;
   HostFuncFn host_func = nullptr;
+  GetDeviceFn get_device = nullptr;
+  SetDeviceFn set_device = nullptr;
 } rt;
 
 int w_stream_create(void** s) { return rt.stream_create(s, 0x01 /* cudaStreamNonBlocking */); }
@@ -38,18 +42,23 @@ int w_stream_wait(void* s, void* e) { return rt.stream_wait(s, e, 0); }
 int w_d2h(void* d, const void* s, size_t n, void* st) { return rt.memcpy_async(d, s, n, 2 /* cudaMemcpyDeviceToHost */, st); }
 int w_h2d(void* d, const void* s, size_t n, void* st) { return rt.memcpy_async(d, s, n, 1 /* cudaMemcpyHostToDevice */, st); }
 int w_host_func(void* s, void (*fn)(void*), void* u) { return rt.host_func(s, fn, u); }
+int w_get_device(int* d) { return rt.get_device(d); }
+int w_set_device(int d) { return rt.set_device(d); }
 
 const CudaApi kRuntimeTable = {w_stream_create, w_stream_destroy, w_stream_sync, w_event_create, w_event_destroy,
-                               w_event_record,  w_stream_wait,    w_d2h,         w_h2d,          w_host_func};
+                               w_event_record,  w_stream_wait,    w_d2h,         w_h2d,          w_host_func,
+                               w_get_device,    w_set_device};
 
 std::atomic<const CudaApi*> installed{nullptr};
 std::once_flag load_once;
 bool runtime_ok = false;
 
 void load_runtime() {
-  // the framework that owns the GPU has loaded the runtime already; fall back to the versioned name
-  void* lib = dlopen("libcudart.so", RTLD_NOW | RTLD_GLOBAL);
+  // The framework that owns the GPU has loaded a runtime already: use that copy (streams and events are shared with
+  // it), and only load one when there is none.
+  void* lib = dlopen("libcudart.so.12", RTLD_NOW | RTLD_NOLOAD);
   if (!lib) lib = dlopen("libcudart.so.12", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("libcudart.so", RTLD_NOW | RTLD_GLOBAL);
   if (!lib) return;
   auto sym = [lib](const char* name) { return dlsym(lib, name); };
   rt.stream_create = reinterpret_cast<StreamCreateFn>(sym("cudaStreamCreateWithFlags"));
@@ -61,8 +70,10 @@ void load_runtime() {
   rt.stream_wait = reinterpret_cast<StreamWaitFn>(sym("cudaStreamWaitEvent"));
   rt.memcpy_async = reinterpret_cast<MemcpyAsyncFn>(sym("cudaMemcpyAsync"));
   rt.host_func = reinterpret_cast<HostFuncFn>(sym("cudaLaunchHostFunc"));
+  rt.get_device = reinterpret_cast<GetDeviceFn>(sym("cudaGetDevice"));
+  rt.set_device = reinterpret_cast<SetDeviceFn>(sym("cudaSetDevice"));
   runtime_ok = rt.stream_create && rt.stream_destroy && rt.stream_sync && rt.event_create && rt.event_destroy &&
-               rt.event_record && rt.stream_wait && rt.memcpy_async && rt.host_func;
+               rt.event_record && rt.stream_wait && rt.memcpy_async && rt.host_func && rt.get_device && rt.set_device;
 }
 
 }  // namespace

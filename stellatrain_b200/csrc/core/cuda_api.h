@@ -23,6 +23,8 @@ struct CudaApi {
   int (*memcpy_d2h_async)(void* dst, const void* src, size_t bytes, void* stream);
   int (*memcpy_h2d_async)(void* dst, const void* src, size_t bytes, void* stream);
   int (*launch_host_func)(void* stream, void (*fn)(void*), void* user);
+  int (*get_device)(int* device);                                       // device of the calling thread
+  int (*set_device)(int device);
 };
 
 // The table in use: an installed one, else the dlopen'ed runtime, else nullptr (no CUDA runtime in this process).

@@ -223,6 +223,7 @@ bool CpuEngine::device_copies_available() const { return cuda_api() != nullptr; 
 void* CpuEngine::copy_stream_for(int index) {
   const CudaApi* api = cuda_api();
   if (!api) return nullptr;
+  use_engine_device();
   std::lock_guard<std::mutex> lk(copy_mu_);
   if (copy_streams_.empty()) {
     for (int i = 0; i < kCopyStreams; ++i) {
@@ -235,8 +236,17 @@ void* CpuEngine::copy_stream_for(int index) {
 }
 
 void CpuEngine::attach_device_param(int index, void* device_param) {
-  if (!cuda_api()) throw std::runtime_error("attach_device_param: no CUDA runtime in this process");
+  const CudaApi* api = cuda_api();
+  if (!api) throw std::runtime_error("attach_device_param: no CUDA runtime in this process");
+  if (device_ < 0 && api->get_device(&device_) != 0) throw std::runtime_error("cudaGetDevice failed");
   params_.at(index).device_param = device_param;
+}
+
+void CpuEngine::use_engine_device() {
+  thread_local int current = -1;
+  if (device_ < 0 || current == device_) return;
+  if (const CudaApi* api = cuda_api())
+    if (api->set_device(device_) == 0) current = device_;
 }
 
 void CpuEngine::post_backward_device(int index, const void* device_grad, void* producer_stream, void* copy_stream) {

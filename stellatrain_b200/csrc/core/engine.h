@@ -146,6 +146,8 @@ class CpuEngine {
   // core_module_api.cpp:201-277).  Without a CUDA runtime the stage runs at once.
   void schedule_after_cuda(Module* m, const std::shared_ptr<TrainTask>& t, void* stream);
   void* copy_stream_for(int param_index);
+  // Makes the engine's CUDA device current in the calling thread (pool workers start on device 0).
+  void use_engine_device();
   // Runs `m` once the previous iteration of the same parameter has left its optimise stage:
   // residual, optimiser state and master parameter are per-parameter state that iteration i+1 must
   // see as iteration i left it.
@@ -252,6 +254,7 @@ class CpuEngine {
   // device copies
   std::mutex copy_mu_;
   std::vector<void*> copy_streams_;
+  int device_ = -1;                          // CUDA device of the thread that attached the first device parameter
   std::atomic<int> callbacks_in_flight_{0};
 
   std::mutex ready_mu_;

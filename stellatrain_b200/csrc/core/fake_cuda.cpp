@@ -129,8 +129,13 @@ int f_host_func(void* s, void (*fn)(void*), void* user) {
   return 0;
 }
 
+std::atomic<int> fake_device{0};
+int f_get_device(int* d) { *d = fake_device.load(); return 0; }
+int f_set_device(int d) { fake_device = d; return 0; }
+
 const CudaApi kFakeTable = {f_stream_create, f_stream_destroy, f_stream_sync, f_event_create, f_event_destroy,
-                            f_event_record,  f_stream_wait,    f_d2h,         f_h2d,          f_host_func};
+                            f_event_record,  f_stream_wait,    f_d2h,         f_h2d,          f_host_func,
+                            f_get_device,    f_set_device};
 
 }  // namespace
 

@@ -134,10 +134,8 @@ ShmManager::ShmManager(bool master, int64_t session, int local_rank, int local_w
 
 ShmManager::~ShmManager() {
   if (pinned_) {
-    if (void* lib = dlopen("libcudart.so", RTLD_NOW | RTLD_NOLOAD)) {
-      using Fn = int (*)(void*);
-      if (auto fn = reinterpret_cast<Fn>(dlsym(lib, "cudaHostUnregister"))) fn(data_);
-    }
+    using Fn = int (*)(void*);
+    if (auto fn = cudart_ ? reinterpret_cast<Fn>(dlsym(cudart_, "cudaHostUnregister")) : nullptr) fn(data_);
   }
   if (data_) munmap(data_, data_bytes_);
   if (meta_) munmap(meta_, meta_bytes_);
@@ -278,14 +276,16 @@ void ShmManager::wait_change(int timeout_ms) {
 
 bool ShmManager::pin_for_cuda() {
   if (pinned_) return true;
-  void* lib = dlopen("libcudart.so", RTLD_NOW | RTLD_GLOBAL);
+  void* lib = dlopen("libcudart.so.12", RTLD_NOW | RTLD_NOLOAD);   // the copy the framework already uses
   if (!lib) lib = dlopen("libcudart.so.12", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("libcudart.so", RTLD_NOW | RTLD_GLOBAL);
   if (!lib) return false;
   using Fn = int (*)(void*, size_t, unsigned int);
   auto fn = reinterpret_cast<Fn>(dlsym(lib, "cudaHostRegister"));
   if (!fn) return false;
   const int rc = fn(data_, data_bytes_, 0x02 /* cudaHostRegisterMapped */);
   pinned_ = rc == 0;
+  if (pinned_) cudart_ = lib;
   if (!pinned_) LOG_WARN("ShmManager", "cudaHostRegister failed with code " << rc << "; copies will be pageable");
   return pinned_;
 }

@@ -67,6 +67,7 @@ class ShmManager {
   unsigned char* meta_ = nullptr;
   unsigned char* data_ = nullptr;
   bool pinned_ = false;
+  void* cudart_ = nullptr;      // runtime library that registered the data segment
 };
 
 }  // namespace stc

@@ -235,6 +235,7 @@ class ModuleCopyOut : public Module {
       // host-to-device copy on the stream that carried this parameter's latest gradient copy: that copy waited for the
       // backward kernels that last read the parameter, so stream order keeps the write behind every reader
       const CudaApi* api = cuda_api();
+      e.use_engine_device();
       void* stream = p.last_copy_stream ? p.last_copy_stream : e.copy_stream_for(t->param_index);
       if (!api || api->memcpy_h2d_async(p.device_param, p.master, static_cast<size_t>(p.numel) * sizeof(float), stream) != 0) {
         e.fail_task(t, "host-to-device copy of the parameter failed");

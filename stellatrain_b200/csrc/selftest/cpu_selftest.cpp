@@ -16,6 +16,7 @@
 #include <thread>
 #include <vector>
 
+#include "../core/cuda_api.h"
 #include "../core/engine.h"
 #include "../core/threadpool.h"
 #include "../cpu/compressors.h"
@@ -133,6 +134,62 @@ void test_single_node(int staleness, int accumulation, const char* method) {
   if (!err.empty()) throw std::runtime_error(std::string("single node (") + method + "): " + err);
 }
 
+// The engine's own device copies against the stand-in runtime (streams are threads, device memory is host memory):
+// gradient copies with host callbacks that start the tasks, parameter copies behind CopyOut, copy streams that lag.
+void test_device_copies(int staleness) {
+  install_fake_cuda(1);
+  std::string err;
+  {
+    CpuEngine engine;
+    EngineOptions o;
+    o.session = static_cast<int64_t>(getpid()) * 100 + 70 + staleness;
+    o.staleness = staleness;
+    o.method = "thresholdv16";
+    o.ratio = 0.9;
+    o.workers = 4;
+    o.data_bytes = 16u << 20;
+    o.timeout_ms = 20000;
+    try {
+      engine.configure(o);
+      engine.set_optimizer("adam");
+      engine.sparse_optimizer()->configure("lr", 1e-2f);
+      const std::vector<uint32_t> sizes = {4096, 17, 70000};
+      std::vector<std::vector<float>> device(sizes.size());
+      std::vector<std::vector<std::vector<float>>> grads(sizes.size());
+      const int iters = 8;
+      for (size_t i = 0; i < sizes.size(); ++i) {
+        device[i].assign(sizes[i], 0.5f);
+        const int idx = engine.pre_train_init(static_cast<int>(i), "d" + std::to_string(i), sizes[i], nullptr, device[i].data());
+        CHECK(idx == static_cast<int>(i));
+        engine.attach_device_param(idx, device[i].data());
+        grads[i].assign(iters, std::vector<float>(sizes[i]));
+      }
+      for (int it = 0; it < iters; ++it) {
+        for (size_t i = 0; i < sizes.size(); ++i) engine.pre_forward_process(static_cast<int>(i));
+        for (size_t r = sizes.size(); r-- > 0;) {
+          std::vector<float>& g = grads[r][it];                  // stays alive until the copy stream has read it
+          for (uint32_t j = 0; j < sizes[r]; ++j) g[j] = 1e-3f * static_cast<float>(((j * 2654435761u) >> 20) % 97 + 1 + it);
+          engine.post_backward_device(static_cast<int>(r), g.data(), nullptr, nullptr);
+        }
+      }
+      engine.synchronize();
+      for (size_t i = 0; i < sizes.size(); ++i) {
+        CHECK(engine.model_version(static_cast<int>(i)) == iters);
+        bool moved = false;
+        for (float x : device[i]) { CHECK(std::isfinite(x)); moved |= x != 0.5f; }
+        CHECK(moved);
+      }
+      long d2h, h2d, funcs;
+      fake_cuda_counters(&d2h, &h2d, &funcs);
+      CHECK(d2h == 3 * iters && h2d == 3 * iters);
+    } catch (const std::exception& e) {
+      err = e.what();
+    }
+  }   // the engine (and its copy streams) goes away before the stand-in runtime is removed
+  remove_fake_cuda();
+  if (!err.empty()) throw std::runtime_error("device copies, staleness " + std::to_string(staleness) + ": " + err);
+}
+
 void test_two_nodes(uint16_t port) {
   Node nodes[2];
   std::string errs[2];
@@ -169,6 +226,8 @@ int main(int argc, char** argv) {
     test_single_node(0, 1, "topk");
     test_single_node(1, 1, "thresholdv16");
     test_single_node(1, 2, "thresholdv");
+    test_device_copies(0);
+    test_device_copies(1);
     test_two_nodes(port);
   } catch (const std::exception& e) {
     std::fprintf(stderr, "selftest FAILED: %s\n", e.what());
