@@ -63,7 +63,7 @@ def parse_args() -> argparse.Namespace:
                     help="owner: optimiser state of every tensor on one rank, new values stored into all replicas")
     ap.add_argument("--shape-gbps", default=None, help="lo:hi[:seed] emulated cross-group link, e.g. 10:40:0")
     ap.add_argument("--controller", type=int, default=0, help="run the telemetry controller and apply its instructions")
-    ap.add_argument("--native-copies", type=int, default=0,
+    ap.add_argument("--native-copies", type=int, default=1,
                     help="cpu_offload arm: 1 lets the native engine issue the device copies itself")
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()

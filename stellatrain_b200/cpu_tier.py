@@ -8,9 +8,10 @@ benchmark, and a way to train when optimiser state should not live in HBM.
 ``CpuOffloadEngine`` drives the native ``CpuEngine`` for an ``nn.Module``:
 
 * host parameters: the engine reads gradients from and writes parameters to the tensors directly;
-* CUDA parameters: gradients are copied into the pinned shared slots on a side stream, the native
-  pipeline starts when the copy's event has fired, and updated parameters are copied back by a small
-  completion thread (the reference's D2H_Copy / H2D_Copy stages, d2h_copy.cpp:20-66, h2d_copy.cpp:31-56).
+* CUDA parameters: the native engine copies gradients into the pinned shared slots on copy streams (event on the
+  backward stream, stream wait, asynchronous copy, host callback that starts the task) and copies updated parameters
+  back behind its CopyOut stage (the reference's D2H_Copy / H2D_Copy stages, d2h_copy.cpp:20-66, h2d_copy.cpp:31-56).
+  ``native_copies=False`` keeps the older route: torch copies issued by this class and two helper threads.
 """
 from __future__ import annotations
 
@@ -89,7 +90,7 @@ class CpuOffloadEngine:
                  method: str = "thresholdv16", gradient_accumulation: int = 1, staleness: int = 1, ratio: float = 0.99,
                  optimizer: str = "sgd", optimizer_options: Optional[dict] = None, data_bytes: int = 0,
                  timeout_ms: int = 30000, workers: int = 0, debug_accuracy: bool = False, debug_barrier: bool = False,
-                 wire_blocks: bool = True, wire_values: str = "fp32", native_copies: bool = False):
+                 wire_blocks: bool = True, wire_values: str = "fp32", native_copies: Optional[bool] = None):
         ext = _load()
         self.module = module
         self.engine = ext.CpuEngine()
@@ -129,6 +130,8 @@ class CpuOffloadEngine:
         # CUDA parameters, two ways to move data: copies issued by this class with torch streams and two helper threads,
         # or by the native engine itself (event, stream wait, asynchronous copy and a host callback per tensor, its
         # D2H_Copy / H2D_Copy stages); the second needs no Python thread on the path of a task
+        if native_copies is None:
+            native_copies = self.cuda and self.engine.device_copies_available()
         self.native_copies = bool(native_copies and self.cuda)
         if self.native_copies:
             if not self.engine.device_copies_available():
