@@ -17,7 +17,8 @@ def synthetic_grad(node, local, step, pi, n):
 
 
 def engine_worker(q, port, session_base, world, node, local_world, local, steps, method, optimizer, staleness, mode):
-    """mode: 'ok' | 'ok_bf16' (bf16 values on the wire) | 'ok_pairs' (no block ids on the wire) | 'absent' (never
+    """mode: 'ok' | 'ok_bf16' (bf16 values on the wire) | 'ok_pairs' (no block ids on the wire) | 'ok_device' (the
+    engine copies gradients and parameters itself, through the stand-in CUDA runtime) | 'absent' (never
     configures) | 'drop' (node 1 drops its gradient sends) | 'die' (node 1 exits mid-run)"""
     try:
         from stellatrain_b200 import cpu_tier
@@ -29,6 +30,9 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
             return
         eng = ext.CpuEngine()
         wire = {"ok_bf16": (True, 2), "ok_pairs": (False, 0)}.get(mode)
+        device = mode == "ok_device"
+        if device:
+            ext.install_fake_cuda(1)
         if mode.startswith("ok"):
             mode = "ok"
         timeout_ms = 4000 if mode != "ok" else 30000
@@ -41,7 +45,15 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
         if optimizer == "sgd":
             eng.configure_optimizer("momentum", 0.9)
         params = [torch.full((n,), 0.5 + node + local) for n in SIZES]   # only node 0 / local 0 values must survive
-        idxs = [eng.pre_train_init(pi, f"p{pi}", p.numel(), p.data_ptr()) for pi, p in enumerate(params)]
+        if device:
+            idxs = [eng.pre_train_init(pi, f"p{pi}", p.numel(), 0, p.data_ptr()) for pi, p in enumerate(params)]
+            for pi, p in zip(idxs, params):
+                p.copy_(torch.frombuffer((__import__("ctypes").c_float * p.numel()).from_address(eng.master_param(pi)),
+                                         dtype=torch.float32))      # what a framework does after registration
+                eng.attach_device_param(pi, p.data_ptr())
+        else:
+            idxs = [eng.pre_train_init(pi, f"p{pi}", p.numel(), p.data_ptr()) for pi, p in enumerate(params)]
+        keep = []
         if mode == "drop" and node == 1:
             eng.drop_tx_containing("@")
         for step in range(steps):
@@ -51,7 +63,11 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
                 eng.pre_forward_process(pi)
             for pi in reversed(idxs):
                 g = synthetic_grad(node, local, step, pi, SIZES[pi])
-                eng.post_backward_process(pi, g.data_ptr())
+                if device:
+                    keep.append(g)
+                    eng.post_backward_device(pi, g.data_ptr(), 0)
+                else:
+                    eng.post_backward_process(pi, g.data_ptr())
         eng.synchronize()
         drift = max(eng.force_model_sync(pi, True) for pi in idxs)
         stats = eng.stats_json(False)

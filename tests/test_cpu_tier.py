@@ -260,6 +260,19 @@ def test_wire_formats_block_ids_and_bf16_values():
         assert float(np.abs(a - b).mean()) < 0.1 * float(np.abs(a - 0.5).mean())
 
 
+def test_two_nodes_two_local_processes_with_engine_device_copies():
+    """Same pipeline, but every process lets the engine copy gradients in and parameters out through the stand-in
+    CUDA runtime (copy streams that lag, host callbacks that start the tasks and end the copy-out)."""
+    world, local_world, steps = 2, 2, 5
+    results = _launch(world, local_world, steps, "thresholdv16", "adam", 1, "ok_device")
+    assert len(results) == 4 and all(r[2] == "ok" for r in results), results
+    want = _oracle_run(world, local_world, steps, "thresholdv16", "adam")
+    for node, local, _, out in results:
+        assert out["drift"] == 0.0 and out["versions"] == [steps] * 3
+        for got, w in zip(out["params"], want):
+            np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
+
+
 def test_absent_local_process_times_out_instead_of_hanging():
     t0 = time.time()
     results = _launch(1, 2, 2, "topk", "sgd", 1, "absent", join_timeout=40)
