@@ -106,6 +106,10 @@ class CpuOffloadEngine:
         # messages between nodes: block ids for whole aligned runs of 16 indices, optionally 16-bit values whose
         # rounding error stays in the sender's residual
         self.engine.configure_wire(wire_blocks, {"fp32": 0, "fp16": 1, "bf16": 2}[wire_values])
+        self._meta = {"method": method, "ratio": ratio, "staleness": staleness, "gradient_accumulation": gradient_accumulation,
+                      "optimizer": optimizer, "optimizer_options": dict(optimizer_options or {}), "world_size": world_size,
+                      "local_world_size": local_world_size}
+        self._local_rank = local_rank
         self.engine.set_optimizer(optimizer)
         for k, v in (optimizer_options or {}).items():
             self.engine.configure_optimizer(k, v)
@@ -235,6 +239,50 @@ class CpuOffloadEngine:
 
     def barrier(self) -> None:
         self.engine.barrier()
+
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self) -> dict:
+        """Everything a later run needs to continue bit for bit, in torch's plain-container form (``torch.save``-able):
+        the module's ``state_dict``, the sparse optimiser's per-tensor state (moments and step counters, or momentum
+        buffers), the error-feedback residuals, the thresholds of the compressor and the engine's settings.  Flushes
+        the pipeline first.  Optimiser state and thresholds live in the node master (local rank 0): save its dictionary.
+        The reference keeps all of this only in memory (backend/src/optim/adam.h:15-18, sgd.h:15-18,
+        compress/thresholdv16.h:13-14, engine/core.h:63)."""
+        self.synchronize()
+        names = [n for n, p in self.module.named_parameters() if p.requires_grad]
+        resid = {n: _from_ptr(self.engine.grad_residual(i), p.numel()).clone()
+                 for i, (n, p) in enumerate(zip(names, self.params))}
+        opt = {}
+        for tensor, (arrays, counters) in self.engine.optimizer_state().items():
+            opt[tensor] = {"arrays": {k: torch.frombuffer(bytearray(v), dtype=torch.float32).clone() if len(v) else
+                                      torch.zeros(0) for k, v in arrays.items()},
+                           "counters": dict(counters)}
+        return {"model": {k: v.detach().to("cpu").clone() for k, v in self.module.state_dict().items()},
+                "optimizer": {"kind": self.engine.optimizer_kind(), "options": dict(self._meta["optimizer_options"]), "state": opt},
+                "sparsifier": {"residual": resid,
+                               "threshold": {k: tuple(v) for k, v in self.engine.compressor_state().items()}},
+                "engine": dict(self._meta)}
+
+    def load_state_dict(self, sd: dict) -> None:
+        """Inverse of :meth:`state_dict` on an engine built with the same settings around the same architecture.
+        Every local process calls it (each loads its module); the node master also restores the shared master copy,
+        the residuals, the optimiser state and the thresholds."""
+        if sd["optimizer"]["kind"] != self.engine.optimizer_kind():
+            raise ValueError(f"checkpoint was written by the {sd['optimizer']['kind']} optimiser")
+        self.synchronize()
+        self.module.load_state_dict(sd["model"])
+        if self._local_rank == 0:
+            names = [n for n, p in self.module.named_parameters() if p.requires_grad]
+            for i, (n, p) in enumerate(zip(names, self.params)):
+                _from_ptr(self.engine.master_param(i), p.numel()).copy_(p.detach().reshape(-1).to("cpu", torch.float32))
+                _from_ptr(self.engine.grad_residual(i), p.numel()).copy_(sd["sparsifier"]["residual"][n])
+            self.engine.set_optimizer_state({t: ({k: v.contiguous().numpy().tobytes() for k, v in st["arrays"].items()},
+                                                 {k: int(c) for k, c in st["counters"].items()})
+                                             for t, st in sd["optimizer"]["state"].items()})
+            self.engine.set_compressor_state({k: (float(v[0]), float(v[1]), bool(v[2]))
+                                              for k, v in sd["sparsifier"]["threshold"].items()})
+        if self._meta["local_world_size"] > 1 or self._meta["world_size"] > 1:
+            self.engine.barrier()
 
     def stats_json(self, clear: bool = False) -> str:
         return self.engine.stats_json(clear)

@@ -354,6 +354,41 @@ PYBIND11_MODULE(_Ccpu, m) {
         if (!e.comm()) return;
         e.comm()->set_tx_fault_hook([needle](const std::string& key, int*) { return key.find(needle) != std::string::npos; });
       })
+      .def("grad_residual", [](CpuEngine& e, int i) { return reinterpret_cast<uint64_t>(e.grad_residual(i)); })
+      .def("optimizer_kind", [](CpuEngine& e) { return std::string(e.sparse_optimizer()->kind()); })
+      .def("optimizer_state", [](CpuEngine& e) {
+        // {tensor: ({array name: [float]}, {counter name: int})}
+        py::dict out;
+        for (auto& kv : e.sparse_optimizer()->export_state()) {
+          py::dict arrays, counters;
+          for (auto& a : kv.second.arrays)
+            arrays[py::str(a.first)] = py::bytes(reinterpret_cast<const char*>(a.second.data()), a.second.size() * sizeof(float));
+          for (auto& c : kv.second.counters) counters[py::str(c.first)] = c.second;
+          out[py::str(kv.first)] = py::make_tuple(arrays, counters);
+        }
+        return out;
+      }, "Per-tensor optimiser state: {tensor: ({array: bytes of float32}, {counter: int})}")
+      .def("set_optimizer_state", [](CpuEngine& e, const std::map<std::string, std::pair<std::map<std::string, std::string>,
+                                                                                         std::map<std::string, int64_t>>>& st) {
+        std::map<std::string, SparseOptimizer::TensorState> m;
+        for (auto& kv : st) {
+          SparseOptimizer::TensorState ts;
+          for (auto& a : kv.second.first) {
+            if (a.second.size() % sizeof(float)) throw std::invalid_argument("array " + a.first + " is not a whole number of floats");
+            std::vector<float> v(a.second.size() / sizeof(float));
+            std::memcpy(v.data(), a.second.data(), a.second.size());
+            ts.arrays[a.first] = std::move(v);
+          }
+          ts.counters = kv.second.second;
+          m[kv.first] = std::move(ts);
+        }
+        e.sparse_optimizer()->import_state(m);
+      })
+      .def("set_compressor_state", [](CpuEngine& e, const std::map<std::string, std::tuple<float, float, bool>>& st) {
+        std::map<std::string, ThresholdState> m;
+        for (auto& kv : st) m[kv.first] = ThresholdState{std::get<0>(kv.second), std::get<1>(kv.second), std::get<2>(kv.second)};
+        e.compressor().import_state(m);
+      })
       .def("compressor_state", [](CpuEngine& e) {
         py::dict d;
         for (auto& kv : e.compressor().export_state()) d[py::str(kv.first)] = py::make_tuple(kv.second.tau, kv.second.tau_inc, kv.second.inited);

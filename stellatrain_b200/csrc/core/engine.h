@@ -119,6 +119,12 @@ class CpuEngine {
   float* claim_grad_slot(int param_index);
   void post_backward_in_slot(int param_index);    // gradient already is in grad_slot()
   const float* master_param(int param_index) const;
+  // Error-feedback residual of a parameter in shared memory (reference get_grad_residual, core_module_api.cpp:516-526);
+  // written by the node master's compress stage, readable by every local process.
+  float* grad_residual(int param_index) { return params_.at(param_index).resid; }
+  // Stage timers of a task, as the stages themselves use them (reference record_stat_start/end, core_module_api.cpp:504-514)
+  void record_stat_start(const std::shared_ptr<TrainTask>& t, const std::string& event) { t->stat_start(event); }
+  void record_stat_end(const std::shared_ptr<TrainTask>& t, const std::string& event) { t->stat_end(event); }
   // Updates whose parameters are ready to be copied out by the caller: (param_index, iteration)
   std::vector<std::pair<int, int64_t>> pop_ready_updates(int max_wait_ms);
   void copy_out_done(int param_index, int64_t iter);

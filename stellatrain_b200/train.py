@@ -90,6 +90,22 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
         global_step = int(extra.get("global_step", 0))
         if global_rank == 0:
             print(f"resumed from {args.resume} at iteration {global_step}", flush=True)
+    def save_cpu_tier(step: int) -> None:
+        # optimiser state and thresholds live in each node's master process; one file per node
+        sd = eng.state_dict()
+        if local_rank == 0:
+            sd["extra"] = {"global_step": step}
+            target = args.checkpoint if world_size == 1 else f"{args.checkpoint}.node{rank}"
+            torch.save(sd, target + ".tmp")
+            os.replace(target + ".tmp", target)
+
+    if args.resume and args.tier == "cpu":
+        source = args.resume if world_size == 1 else f"{args.resume}.node{rank}"
+        sd = torch.load(source, map_location="cpu", weights_only=False)
+        eng.load_state_dict(sd)
+        global_step = int(sd.get("extra", {}).get("global_step", 0))
+        if global_rank == 0:
+            print(f"resumed from {args.resume} at iteration {global_step}", flush=True)
     monitor = None
     if args.heartbeat and global_world > 1:
         import datetime
@@ -131,6 +147,8 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
                     from stellatrain_b200.utils import checkpoint
 
                     checkpoint.save(args.checkpoint, net.module, net.engine, {"global_step": global_step})
+                if args.checkpoint and args.checkpoint_every and args.tier == "cpu" and global_step % args.checkpoint_every == 0:
+                    save_cpu_tier(global_step)
                 if global_step % args.log_every == 0:
                     meter.update(float(loss.detach()))
                     if global_rank == 0:
@@ -143,6 +161,8 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
         from stellatrain_b200.utils import checkpoint
 
         checkpoint.save(args.checkpoint, net.module, net.engine, {"global_step": global_step})
+    if args.checkpoint and args.tier == "cpu":
+        save_cpu_tier(global_step)
     if monitor is not None:
         monitor.announce_leave()
     if global_rank == 0:

@@ -346,3 +346,50 @@ def test_engine_device_copies_against_a_fake_runtime(staleness, delay_ms):
     for a, b in zip(got, want):
         assert torch.equal(a, b)
     assert any(float((a - 0.5).abs().max()) > 0 for a in got)
+
+
+@pytest.mark.parametrize("method,optimizer", [("thresholdv16", "adam"), ("topk", "sgd")])
+def test_cpu_tier_checkpoint_resumes_bit_for_bit(method, optimizer, tmp_path):
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    def make():
+        torch.manual_seed(3)
+        model = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 8))
+        opts = {"lr": 1e-2} if optimizer == "adam" else {"lr": 0.05, "momentum": 0.9}
+        return model, cpu_tier.CpuOffloadEngine(model, method=method, ratio=0.9, optimizer=optimizer, optimizer_options=opts,
+                                                staleness=1, data_bytes=8 << 20, workers=2)
+
+    def steps(model, lo, hi):
+        for i in range(lo, hi):
+            g = torch.Generator().manual_seed(50 + i)
+            x, y = torch.randn(16, 32, generator=g), torch.randint(0, 8, (16,), generator=g)
+            F.cross_entropy(model(x), y).backward()
+
+    model, eng = make()
+    steps(model, 0, 5)
+    sd = eng.state_dict()
+    path = tmp_path / "cpu_tier.pt"
+    torch.save(sd, path)
+    steps(model, 5, 9)
+    eng.synchronize()
+    want = [p.detach().clone() for p in model.parameters()]
+    eng.close()
+
+    model2, eng2 = make()
+    with torch.no_grad():
+        for p in model2.parameters():
+            p.add_(1.0)                                  # anything but the saved values
+    loaded = torch.load(path, weights_only=False)
+    assert set(loaded) == {"model", "optimizer", "sparsifier", "engine"} and loaded["optimizer"]["kind"] == optimizer
+    assert any(float(r.abs().sum()) > 0 for r in loaded["sparsifier"]["residual"].values())
+    eng2.load_state_dict(loaded)
+    steps(model2, 5, 9)
+    eng2.synchronize()
+    for a, b in zip(model2.parameters(), want):
+        assert torch.equal(a.detach(), b)
+    other = cpu_tier.CpuOffloadEngine(nn.Linear(4, 4), optimizer="sgd" if optimizer == "adam" else "adam", data_bytes=1 << 20, workers=1)
+    with pytest.raises(ValueError, match="optimiser"):
+        other.load_state_dict(loaded)
+    other.close()
+    eng2.close()

@@ -106,6 +106,19 @@ def test_train_driver_cpu_tier_end_to_end():
     assert "done: 3 iterations" in out.stdout
 
 
+def test_train_driver_cpu_tier_checkpoint_and_resume(tmp_path):
+    ck = str(tmp_path / "cpu.pt")
+    base = [sys.executable, "-m", "stellatrain_b200.train", "--tier", "cpu", "--model", "resnet18", "--dataset", "dummy",
+            "--num-epochs", "1", "--dummy-length", "4", "--batch-size", "2", "--local-world-size", "1", "--compression", "0.9",
+            "--num-classes", "10", "--log-every", "1", "--checkpoint", ck]
+    out = subprocess.run(base + ["--num-iters", "2"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "done: 2 iterations" in out.stdout
+    out = subprocess.run(base + ["--resume", ck, "--num-iters", "4"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "resumed from" in out.stdout and "at iteration 2" in out.stdout and "done: 4 iterations" in out.stdout
+
+
 def test_reference_arm_reports_unavailable():
     import json
 
