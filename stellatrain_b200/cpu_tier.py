@@ -295,3 +295,122 @@ class CpuOffloadEngine:
             self._h2d_thread.join(timeout=2)
             self._d2h_thread.join(timeout=2)
         self.engine = None
+
+
+class CpuTierTelemetry:
+    """Closes the control loop for the CPU tier: times every step on the host, reports to the controller through the
+    native telemetry client and applies the instructions that come back.
+
+    The reference ships the client, the server and the controller but never connects them to its engine
+    (backend/src/engine/telemetry_client.cpp:39-110, batch_rate_alloc.py:194-215).  Usage::
+
+        hook = CpuTierTelemetry(engine, "127.0.0.1:5556", batch_size=32, rank=node_rank, local_rank=local_rank)
+        for x, y in loader:
+            x, y = hook.resize_batch(x, y)              # per-GPU batch size the controller asked for
+            with hook.step() as marker:
+                loss = criterion(model(x), y); marker.backward_begins(); loss.backward()
+
+    A new compression ratio is handed to the engine together with the iteration from which it counts
+    (``configure_compression_ratio_from``), so every node switches at the same task even though the instruction
+    reaches the nodes at different moments.  Throughput fields are the bytes the node's comm manager sent and
+    received during the step.
+    """
+
+    def __init__(self, engine: "CpuOffloadEngine", uri: Optional[str], batch_size: int, gpu_id: int = 0, rank: int = 0,
+                 local_rank: int = 0, gpu_name: Optional[str] = None, apply_batch: bool = True, apply_ratio: bool = True,
+                 timeout_ms: int = 5000) -> None:
+        import time
+
+        self._now = time.perf_counter
+        self.engine = engine
+        self.batch_size = int(batch_size)
+        self.apply_batch, self.apply_ratio = apply_batch, apply_ratio
+        self.iteration = 0
+        self.ratio = float(engine._meta["ratio"])
+        self.pending: list = []         # (effective_since, ubatch, ratio), written by the client's thread
+        self.applied: list = []
+        self.last: dict = {}
+        self._lock = threading.Lock()
+        self._prev_end: Optional[float] = None
+        self._prev_bytes = engine.engine.comm_bytes()
+        self.client = None
+        if uri:
+            ext = _load()
+            name = gpu_name or (torch.cuda.get_device_name(0) if engine.cuda else "cpu")
+            self._TrainConfig = ext.TrainConfig
+            self.client = ext.TelemetryClient(uri, gpu_id, name, rank, local_rank, timeout_ms)
+
+    def _on_instruction(self, since: int, ubatch: int, grad_acc: int, ratio: float) -> None:
+        with self._lock:
+            self.pending.append((int(since), int(ubatch), float(ratio)))
+
+    def _take_instructions(self) -> None:
+        with self._lock:
+            new, self.pending = self.pending, []
+        for since, ubatch, ratio in new:
+            # a switch that would lie in the past on this node counts from the next iteration
+            since = max(since, self.iteration)
+            if self.apply_ratio and 0.0 < ratio <= 1.0:
+                self.engine.engine.configure_compression_ratio_from(since, ratio)
+            self.applied.append((since, ubatch, ratio))
+        for since, ubatch, ratio in self.applied:
+            if since == self.iteration:
+                if self.apply_batch and ubatch > 0:
+                    self.batch_size = ubatch
+                if self.apply_ratio and 0.0 < ratio <= 1.0:
+                    self.ratio = ratio
+
+    def resize_batch(self, *tensors: torch.Tensor):
+        """Cut or tile a batch along dim 0 to the size the controller asked for."""
+        self._take_instructions()      # a size that counts from this iteration applies to this batch already
+        out = []
+        for t in tensors:
+            n = t.shape[0]
+            if n >= self.batch_size:
+                out.append(t[: self.batch_size])
+            else:
+                reps = (self.batch_size + n - 1) // n
+                out.append(t.repeat(reps, *([1] * (t.dim() - 1)))[: self.batch_size])
+        return tuple(out)
+
+    def step(self):
+        import contextlib
+
+        @contextlib.contextmanager
+        def _ctx():
+            self._take_instructions()
+            t0 = self._now()
+            marker = _HostBackwardStart(self._now)
+            try:
+                yield marker
+            finally:
+                if self.engine.cuda:
+                    torch.cuda.current_stream().synchronize()      # the step's kernels, not only their launches
+                t1 = self._now()
+                fwd = (marker.at - t0) * 1e3 if marker.at is not None else 0.0
+                bwd = (t1 - marker.at) * 1e3 if marker.at is not None else (t1 - t0) * 1e3
+                gap = (t0 - self._prev_end) * 1e3 if self._prev_end is not None else 0.0
+                self._prev_end = t1
+                tx, rx = self.engine.engine.comm_bytes()
+                step_ms = max(fwd + bwd + gap, 1e-3)
+                send = (tx - self._prev_bytes[0]) * 8.0 / (step_ms * 1000.0)
+                recv = (rx - self._prev_bytes[1]) * 8.0 / (step_ms * 1000.0)
+                self._prev_bytes = (tx, rx)
+                self.last = {"fwd_delay_ms": fwd, "bwd_delay_ms": bwd, "bwd_fwd_gap_ms": gap, "intra_fwd_gap_ms": 0.0,
+                             "grad_send_thpt_mbps": send, "grad_recv_thpt_mbps": recv}
+                if self.client is not None and self.client.alive():
+                    cfg = self._TrainConfig(self.batch_size, self.engine.grad_accumulation, self.ratio)
+                    self.client.report(self.iteration, cfg, [send, recv, fwd, bwd, gap, 0.0], self._on_instruction)
+                self.iteration += 1
+
+        return _ctx()
+
+
+class _HostBackwardStart:
+    """``marker.backward_begins()`` between forward and backward splits the two host times."""
+
+    def __init__(self, now) -> None:
+        self._now, self.at = now, None
+
+    def backward_begins(self) -> None:
+        self.at = self._now()

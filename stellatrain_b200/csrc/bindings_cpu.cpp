@@ -316,6 +316,8 @@ PYBIND11_MODULE(_Ccpu, m) {
       })
       .def("configure_compression", &CpuEngine::configure_compression)
       .def("configure_compression_ratio", &CpuEngine::configure_compression_ratio)
+      .def("configure_compression_ratio_from", &CpuEngine::configure_compression_ratio_from, py::arg("iteration"), py::arg("ratio"))
+      .def("compression_ratio_at", &CpuEngine::compression_ratio_at)
       .def("configure_wire", &CpuEngine::configure_wire, py::arg("blocks") = true, py::arg("value_format") = 0)
       .def("gradient_accumulation", &CpuEngine::gradient_accumulation)
       .def("is_debug_accuracy_mode", [](CpuEngine& e) { return e.options().debug_accuracy; })

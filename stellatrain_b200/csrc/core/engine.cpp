@@ -51,7 +51,10 @@ void CpuEngine::configure(const EngineOptions& o) {
   if (o.local_world < 1 || o.local_world > cfg::kMaxLocalRanks) throw std::invalid_argument("local_world out of range");
   if (o.staleness < 0 || o.staleness > 1) throw std::invalid_argument("staleness must be 0 or 1");
   opt_ = o;
-  ratio_ = o.ratio;
+  {
+    std::lock_guard<std::mutex> lk(ratio_mu_);
+    ratio_ = o.ratio;
+  }
   const int workers = o.workers > 0 ? o.workers : (node_master() ? cfg::kWorkersNodeMaster : cfg::kWorkersOther);
   pool_ = std::make_unique<ThreadPool>(static_cast<size_t>(workers));
   const size_t data_bytes = o.data_bytes ? o.data_bytes : static_cast<size_t>(cfg::env_long("STELLATRAIN_SHM_BYTES", static_cast<long>(cfg::kShmDataBytes)));
@@ -92,7 +95,30 @@ void CpuEngine::configure_compression(const std::string& method) { compressor_ =
 
 void CpuEngine::configure_compression_ratio(double ratio) {
   if (!(ratio > 0.0 && ratio <= 1.0)) throw std::invalid_argument("compression ratio must be in (0, 1]");
+  std::lock_guard<std::mutex> lk(ratio_mu_);
   ratio_ = ratio;
+  ratio_from_.clear();
+}
+
+double CpuEngine::compression_ratio() const {
+  std::lock_guard<std::mutex> lk(ratio_mu_);
+  return ratio_;
+}
+
+void CpuEngine::configure_compression_ratio_from(int64_t iter, double ratio) {
+  if (!(ratio > 0.0 && ratio <= 1.0)) throw std::invalid_argument("compression ratio must be in (0, 1]");
+  std::lock_guard<std::mutex> lk(ratio_mu_);
+  ratio_from_[iter] = ratio;
+}
+
+double CpuEngine::compression_ratio_at(int64_t iter) const {
+  std::lock_guard<std::mutex> lk(ratio_mu_);
+  double r = ratio_;
+  for (auto& kv : ratio_from_) {       // ordered by iteration: the last switch at or before `iter` wins
+    if (kv.first > iter) break;
+    r = kv.second;
+  }
+  return r;
 }
 
 void CpuEngine::configure_wire(bool blocks, int value_format) {
@@ -316,6 +342,7 @@ void CpuEngine::start_task(int index) {
   auto task = std::make_shared<TrainTask>(iter, p.layer, p.name);
   task->numel = p.numel;
   task->param_index = index;
+  task->ratio = compression_ratio_at(iter);
   task->stat_start("Total");
   auto prom = std::make_shared<std::promise<void>>();
   {

@@ -87,7 +87,13 @@ class CpuEngine {
   SparseOptimizer* sparse_optimizer() { return optimizer_.get(); }
   void configure_compression(const std::string& method);
   void configure_compression_ratio(double ratio);
-  double compression_ratio() const { return ratio_; }
+  double compression_ratio() const;
+  // The ratio that tasks of iteration `iter` and later will use (iterations count per parameter from 0 and agree
+  // between nodes, so every node switches at the same task: the instruction protocol of the controller, effective a
+  // few iterations after issue, backend/src/engine/batch_rate_alloc_optim.py:454-479).  A task's ratio is fixed when
+  // the task is created; configure_compression_ratio() changes it for every task created afterwards.
+  void configure_compression_ratio_from(int64_t iter, double ratio);
+  double compression_ratio_at(int64_t iter) const;
   // Wire format of the gradient messages between nodes.  `blocks`: whole aligned runs of 16 indices travel as one
   // block id (what threshold-v16 selects).  `value_format`: 0 fp32, 1 fp16, 2 bf16; with 1 or 2 the compress stage
   // keeps the rounding error of every sent value in the residual, so narrow values delay mass instead of losing it.
@@ -212,7 +218,9 @@ class CpuEngine {
   EngineOptions opt_;
   std::atomic<bool> ready_{false};
   std::atomic<bool> stop_{false};
+  mutable std::mutex ratio_mu_;
   double ratio_ = 0.99;
+  std::map<int64_t, double> ratio_from_;     // first iteration -> ratio, for switches that lie ahead
   std::atomic<bool> wire_blocks_{true};
   std::atomic<int> wire_values_{0};
   std::unique_ptr<ThreadPool> pool_;

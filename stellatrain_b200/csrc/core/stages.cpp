@@ -124,7 +124,7 @@ class ModuleCompress : public Module {
     auto& p = e.param(t->param_index);
     const int W = e.options().world;
     float* acc = p.slot[t->iter % 2][0];                         // NaN already dropped by the gather stage
-    const uint32_t k = entries_for(p.numel, e.compression_ratio(), W);
+    const uint32_t k = entries_for(p.numel, t->ratio, W);
     t->k = k;
     t->idx.assign(static_cast<size_t>(k) * W, 0xFFFFFFFFu);
     t->val.assign(static_cast<size_t>(k) * W, 0.f);

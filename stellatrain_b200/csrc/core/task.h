@@ -54,6 +54,7 @@ struct TrainTask {
   std::vector<float> val;
   std::vector<size_t> counts;          // valid entries per slot
   uint32_t k = 0;
+  double ratio = 0.99;                 // compression ratio of this iteration, fixed when the task is created
   int exchange_round = 0;
 
   // stage timers in milliseconds, -1 when a stage did not run (reference core.cpp:1151-1207).

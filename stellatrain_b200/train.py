@@ -80,6 +80,10 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
 
         net._ensure_engine()
         hook = TelemetryHook(net.engine, args.telemetry_uri, args.batch_size)
+    elif args.telemetry_uri:
+        from stellatrain_b200.cpu_tier import CpuTierTelemetry
+
+        hook = CpuTierTelemetry(eng, args.telemetry_uri, args.batch_size, gpu_id=global_rank, rank=rank, local_rank=local_rank)
 
     meter, global_step, t_start = AverageMeter(), 0, time.time()
     if args.resume and args.tier == "gpu":

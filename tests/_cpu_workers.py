@@ -17,7 +17,8 @@ def synthetic_grad(node, local, step, pi, n):
 
 
 def engine_worker(q, port, session_base, world, node, local_world, local, steps, method, optimizer, staleness, mode):
-    """mode: 'ok' | 'ok_bf16' (bf16 values on the wire) | 'ok_pairs' (no block ids on the wire) | 'ok_device' (the
+    """mode: 'ok' | 'ok_bf16' (bf16 values on the wire) | 'ok_pairs' (no block ids on the wire) | 'ok_switch' (the compression ratio changes from iteration 3 on; the nodes learn
+    of it at different steps) | 'ok_device' (the
     engine copies gradients and parameters itself, through the stand-in CUDA runtime) | 'absent' (never
     configures) | 'drop' (node 1 drops its gradient sends) | 'die' (node 1 exits mid-run)"""
     try:
@@ -33,7 +34,7 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
         device = mode == "ok_device"
         if device:
             ext.install_fake_cuda(1)
-        if mode.startswith("ok"):
+        if mode.startswith("ok") and mode != "ok_switch":
             mode = "ok"
         timeout_ms = 4000 if mode != "ok" else 30000
         eng.configure("127.0.0.1", port, world, node, session_base + node, local_world, local, method, 1, staleness,
@@ -56,7 +57,12 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
         keep = []
         if mode == "drop" and node == 1:
             eng.drop_tx_containing("@")
+        switch = mode == "ok_switch"
+        if switch:
+            mode = "ok"
         for step in range(steps):
+            if switch and step == 1 + node:
+                eng.configure_compression_ratio_from(3, 0.5)
             if mode == "die" and node == 1 and step == 2:
                 os._exit(0)
             for pi in idxs:

@@ -172,7 +172,7 @@ def test_bandwidth_monitor_and_interfaces():
         del os.environ["PUBLIC_IP"]
 
 
-def _oracle_run(world, local_world, steps, method, optimizer):
+def _oracle_run(world, local_world, steps, method, optimizer, ratio_from=None):
     from _cpu_workers import SIZES, synthetic_grad
 
     params = [torch.full((n,), 0.5) for n in SIZES]
@@ -184,7 +184,7 @@ def _oracle_run(world, local_world, steps, method, optimizer):
         cfg, st = O.AdamConfig(lr=1e-2), [O.AdamState() for _ in SIZES]
     for step in range(steps):
         for pi, n in enumerate(SIZES):
-            k = B.entries_for(n, 0.9, world)
+            k = B.entries_for(n, 0.9 if ratio_from is None or step < ratio_from[0] else ratio_from[1], world)
             streams = []
             for node in range(world):
                 g = sum(synthetic_grad(node, l, step, pi, n) for l in range(local_world))
@@ -271,6 +271,57 @@ def test_two_nodes_two_local_processes_with_engine_device_copies():
         assert out["drift"] == 0.0 and out["versions"] == [steps] * 3
         for got, w in zip(out["params"], want):
             np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
+
+
+def test_ratio_switch_takes_effect_at_the_same_iteration_on_every_node():
+    """An instruction names the iteration from which its compression ratio counts; nodes that learn of it at different
+    steps still switch at the same task, so replicas stay equal and match the oracle with the same schedule."""
+    world, steps = 2, 6
+    results = _launch(world, 1, steps, "topk", "adam", 1, "ok_switch")
+    assert len(results) == 2 and all(r[2] == "ok" for r in results), results
+    want = _oracle_run(world, 1, steps, "topk", "adam", ratio_from=(3, 0.5))
+    for node, local, _, out in results:
+        assert out["drift"] == 0.0 and out["versions"] == [steps] * 3
+        for got, w in zip(out["params"], want):
+            np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
+
+
+def test_cpu_tier_telemetry_closes_the_loop_with_the_controller():
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from stellatrain_b200.control.controller import Controller
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 8))
+    eng = cpu_tier.CpuOffloadEngine(model, method="topk", ratio=0.9, optimizer="sgd", optimizer_options={"lr": 0.05},
+                                    staleness=1, data_bytes=8 << 20, workers=2)
+    ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
+    try:
+        srv = ext.TelemetryServer(f"127.0.0.1:{ctl.port}", False, 5000)
+        srv.send_global_telemetry(1, 1, [p.numel() for p in model.parameters()], False, False)
+        hook = cpu_tier.CpuTierTelemetry(eng, f"127.0.0.1:{ctl.port}", batch_size=16)
+        x, y = torch.randn(16, 32), torch.randint(0, 8, (16,))
+        shapes = []
+        for it in range(20):
+            xb, yb = hook.resize_batch(x, y)
+            shapes.append(xb.shape[0])
+            with hook.step() as marker:
+                loss = F.cross_entropy(model(xb), yb)
+                marker.backward_begins()
+                loss.backward()
+            if it == 4:
+                hook._on_instruction(since=8, ubatch=24, grad_acc=1, ratio=0.6)     # what the client's callback delivers
+        eng.synchronize()
+        assert hook.applied == [(8, 24, 0.6)]
+        assert shapes[7] == 16 and shapes[8] == 24 and hook.ratio == pytest.approx(0.6)
+        assert eng.engine.compression_ratio_at(7) == pytest.approx(0.9) and eng.engine.compression_ratio_at(8) == pytest.approx(0.6)
+        assert hook.last["fwd_delay_ms"] > 0.0 and hook.last["bwd_delay_ms"] > 0.0
+        assert _wait_for(lambda: ctl.latest_iter >= 15), "reports did not reach the controller"
+        assert len(ctl.scoreboard) == 1 and float(ctl.scoreboard.iloc[0]["bwd_ms"]) > 0.0
+    finally:
+        ctl.close()
+        eng.close()
 
 
 def test_absent_local_process_times_out_instead_of_hanging():
