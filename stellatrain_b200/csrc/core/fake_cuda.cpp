@@ -123,8 +123,8 @@ int f_d2h(void* dst, const void* src, size_t n, void* s) { return f_copy(dst, sr
 int f_h2d(void* dst, const void* src, size_t n, void* s) { return f_copy(dst, src, n, s, &copies_h2d); }
 int f_host_func(void* s, void (*fn)(void*), void* user) {
   on_stream(s, [fn, user] {
+    host_funcs.fetch_add(1);   // before the call: what the callback starts may finish before it returns
     fn(user);
-    host_funcs.fetch_add(1);
   });
   return 0;
 }
