@@ -85,8 +85,11 @@ class _SafeUnpickler(pickle._Unpickler):  # the pure-Python implementation: its 
 
     def find_class(self, module: str, name: str) -> Any:
         if (module, name) in _NUMPY_OK:
-            mod = np.core.multiarray if "multiarray" in module else np
-            return getattr(mod, name)
+            if "multiarray" in module:
+                import numpy._core.multiarray as multiarray
+
+                return getattr(multiarray, name)
+            return getattr(np, name)
         if (module, name) == ("copyreg", "_reconstructor"):
             import copyreg
 
@@ -144,3 +147,88 @@ def read_records(path: str) -> Any:
     if raw[:1] == b"x":                      # joblib's zlib container
         raw = zlib.decompressobj().decompress(raw, _MAX_BYTES)
     return _SafeUnpickler(io.BytesIO(raw)).load()
+
+
+def _find_kernel_parts(kernel: Any) -> dict:
+    """Constant, length scales and smoothness of ``Constant * Matern [+ White]`` (any nesting order)."""
+    out: dict = {}
+
+    def walk(k: Any) -> None:
+        if not isinstance(k, Record):
+            return
+        leaf = k._name.rsplit(".", 1)[-1]
+        if leaf in ("Sum", "Product"):
+            walk(k.attr("k1"))
+            walk(k.attr("k2"))
+        elif leaf == "ConstantKernel":
+            out["constant"] = float(k.attr("constant_value"))
+        elif leaf == "Matern":
+            out["length_scale"] = np.atleast_1d(np.asarray(k.attr("length_scale"), dtype=float))
+            out["nu"] = float(k.attr("nu"))
+        elif leaf == "RBF":
+            out["length_scale"] = np.atleast_1d(np.asarray(k.attr("length_scale"), dtype=float))
+            out["nu"] = float("inf")
+        elif leaf == "WhiteKernel":
+            out["noise"] = float(k.attr("noise_level", 0.0))
+        else:
+            raise ValueError(f"unsupported kernel component {k._name}")
+
+    walk(kernel)
+    if "length_scale" not in out:
+        raise ValueError("no Matern or RBF component in the kernel")
+    out.setdefault("constant", 1.0)
+    return out
+
+
+def profile_from_records(result: Any) -> GPProfile:
+    """Build a ``GPProfile`` from the record tree of a scikit-optimize result."""
+    if not isinstance(result, Record) or "models" not in result:
+        raise ValueError("not a scikit-optimize result: no 'models' entry")
+    models = result["models"]
+    if not models:
+        raise ValueError("the result holds no fitted model")
+    gp = models[-1]
+    x_train = np.asarray(gp.attr("X_train_"), dtype=float)
+    alpha = np.asarray(gp.attr("alpha_"), dtype=float).reshape(-1)
+    if x_train.ndim != 2 or x_train.shape[1] != 2 or x_train.shape[0] != alpha.shape[0]:
+        raise ValueError(f"unexpected training set: X {x_train.shape}, alpha {alpha.shape}")
+    parts = _find_kernel_parts(gp.attr("kernel_"))
+    ls = parts["length_scale"]
+    ls = np.repeat(ls, 2) if ls.shape[0] == 1 else ls
+    y_mean = gp.attr("_y_train_mean", gp.attr("y_train_mean_", 0.0))
+    y_std = gp.attr("_y_train_std", gp.attr("y_train_std_", 1.0))
+    md = result.get("metadata") or {}
+    if isinstance(md, Record):
+        md = dict(md)
+    known = {k: md[k] for k in ("batch_size", "max_batch_size", "min_batch_size", "bandwidth", "compression") if k in md}
+    meta = ProfileMeta(**{k: float(v) for k, v in known.items()}, model=str(md.get("model", "")))
+    return GPProfile(x_train, alpha, ls, parts["constant"], parts["nu"], float(np.asarray(y_mean)), float(np.asarray(y_std)), meta)
+
+
+def convert(src: str, dst: Optional[str] = None) -> GPProfile:
+    prof = profile_from_records(read_records(src))
+    if dst:
+        if dst.endswith(".json"):
+            import json
+
+            Path(dst).write_text(json.dumps({
+                "x_train": prof.x_train.tolist(), "alpha": prof.alpha.tolist(), "length_scale": prof.length_scale.tolist(),
+                "constant": prof.constant, "nu": prof.nu, "y_mean": prof.y_mean, "y_std": prof.y_std,
+                "metadata": prof.meta.__dict__}))
+        else:
+            prof.save(dst)
+    return prof
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("src", help="scikit-optimize result written by skopt.dump / joblib.dump")
+    ap.add_argument("dst", help=".npz or .json profile for MODEL_PROFILE")
+    a = ap.parse_args()
+    prof = convert(a.src, a.dst)
+    print(f"{a.dst}: {len(prof.alpha)} training points, kernel {prof.constant:.4g} * Matern(nu={prof.nu}, "
+          f"length_scale={prof.length_scale.tolist()}), metadata {prof.meta.__dict__}")
+
+
+if __name__ == "__main__":
+    main()

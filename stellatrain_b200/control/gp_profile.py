@@ -4,8 +4,10 @@ The reference loads scikit-optimize pickles whose last model is a Gaussian proce
 Constant x Matern + White over (total batch / max batch, bandwidth / reference bandwidth) and uses the
 posterior mean as a multiplicative "iterations needed" penalty, ``1 + 50 h``
 (backend/src/engine/batch_rate_alloc_optim.py:139-172, 190).  Those pickles are foreign code-bearing
-files and are never loaded here.  Instead:
+files and are never loaded by the controller.  Instead:
 
+* ``python -m stellatrain_b200.control.convert_profile in.pkl out.npz`` turns such a pickle into plain arrays
+  offline, reading it with an allow-list unpickler that runs nothing the file names;
 * ``GPProfile`` evaluates the posterior mean of a Matern GP from plain arrays (``.npz`` or JSON):
   ``mean(x) = K(x, X) @ alpha * y_std + y_mean``;
 * ``fit_profile`` builds such a profile from measured (batch, bandwidth, penalty) points;
@@ -125,5 +127,6 @@ def load_profile(path: Optional[str]):
         return AnalyticProfile()
     p = Path(path)
     if p.suffix in (".pkl", ".pickle"):
-        raise ValueError("pickled scikit-optimize profiles are not loaded; export X_train/alpha/length_scale to .npz or .json")
+        raise ValueError("pickled scikit-optimize profiles are not loaded here; convert them once with "
+                         "`python -m stellatrain_b200.control.convert_profile in.pkl out.npz`")
     return GPProfile.load(p)

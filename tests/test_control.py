@@ -1,5 +1,6 @@
 """Control plane on CPU: wire format, profile evaluation, optimiser phases, controller round trip with the
 native telemetry client, shaped-link schedule."""
+import os
 import socket
 import threading
 import time
@@ -233,3 +234,83 @@ def test_traffic_model_matches_the_block_wire_format():
     assert abs((blocks - header) - len(payload)) <= 0.05 * len(payload) + 0x42 * 12   # payload + per-segment headers
     assert blocks < 0.56 * pairs
     assert TrafficModel([8], "tcp", grad_block16=True).tx_bytes(0.5) == TrafficModel([8], "tcp").tx_bytes(0.5)
+
+
+class _FakeKernel:                       # stand-ins whose pickles look like scikit-optimize's to the converter
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+class Sum(_FakeKernel): pass             # noqa: E701
+class Product(_FakeKernel): pass         # noqa: E701
+class ConstantKernel(_FakeKernel): pass  # noqa: E701
+class Matern(_FakeKernel): pass          # noqa: E701
+class WhiteKernel(_FakeKernel): pass     # noqa: E701
+class GaussianProcessRegressor(_FakeKernel): pass   # noqa: E701
+
+
+class OptimizeResult(dict):
+    pass
+
+
+class _Boom:
+    def __reduce__(self):
+        import os
+
+        return (os.system, ("touch /dev/null/should_never_run",))
+
+
+def test_profile_converter_reads_a_result_pickle_without_running_it(tmp_path):
+    import joblib
+
+    from stellatrain_b200.control import convert_profile as C
+    from stellatrain_b200.control.gp_profile import GPProfile, ProfileMeta, fit_profile, load_profile
+
+    meta = ProfileMeta(batch_size=256, max_batch_size=1024, min_batch_size=64, bandwidth=1.0, compression=0.9, model="toy")
+    rng = np.random.default_rng(0)
+    tb, bw = rng.uniform(64, 1024, 20), rng.uniform(0.1, 1.0, 20)
+    want = fit_profile(tb, bw, 0.05 + 0.1 * tb / 1024 + 0.02 / bw, meta, length_scale=(0.4, 0.7), nu=1.5)
+    gp = GaussianProcessRegressor(
+        X_train_=np.asfortranarray(want.x_train), alpha_=want.alpha, _y_train_mean=np.float64(want.y_mean), _y_train_std=np.float64(want.y_std),
+        kernel_=Sum(k1=Product(k1=ConstantKernel(constant_value=1.0), k2=Matern(length_scale=np.array([0.4, 0.7]), nu=1.5)),
+                    k2=WhiteKernel(noise_level=0.0)))
+    res = OptimizeResult(models=[None, gp], metadata=dict(meta.__dict__), x=[0.1, 0.2], trap=_Boom())
+    src = tmp_path / "toy.pkl"
+    joblib.dump(res, src, compress=3)          # the container scikit-optimize writes: zlib, arrays as raw payloads
+
+    records = C.read_records(str(src))
+    assert isinstance(records["trap"], C.Record) and records["trap"]._name.endswith("system")   # recorded, not called
+    got = C.convert(str(src), str(tmp_path / "toy.npz"))
+    assert got.nu == 1.5 and got.meta.model == "toy" and got.meta.max_batch_size == 1024
+    q_tb, q_bw = np.array([100.0, 512.0, 900.0]), np.array([0.2, 0.5, 1.0])
+    np.testing.assert_allclose(got.h(q_tb, q_bw), want.h(q_tb, q_bw), rtol=1e-12)
+    np.testing.assert_allclose(load_profile(str(tmp_path / "toy.npz")).h(q_tb, q_bw), want.h(q_tb, q_bw), rtol=1e-12)
+    C.convert(str(src), str(tmp_path / "toy.json"))
+    np.testing.assert_allclose(GPProfile.load(tmp_path / "toy.json").h(q_tb, q_bw), want.h(q_tb, q_bw), rtol=1e-9)
+    with pytest.raises(ValueError):
+        load_profile(str(src))                 # the controller itself still refuses pickles
+    bad = tmp_path / "bad.pkl"
+    joblib.dump({"models": []}, bad)
+    with pytest.raises(ValueError):
+        C.convert(str(bad))
+
+
+@pytest.mark.parametrize("name", ["resnet152_frac50_368", "resnet50_frac50_256", "vitb16_frac25_512.v2", "swinb_frac25_512"])
+def test_profile_converter_on_published_profiles(name):
+    """Where the upstream tree is at hand: its profiles convert, and the converted Gaussian process reproduces its own
+    training targets through (K + noise I) alpha = y, which pins kernel, length scales and constant."""
+    from pathlib import Path
+
+    from stellatrain_b200.control import convert_profile as C
+
+    src = Path(os.environ.get("STELLATRAIN_REFERENCE", "/root/reference")) / "bayesian" / "profile" / f"{name}.pkl"
+    if not src.exists():
+        pytest.skip("upstream profiles not available")
+    rec = C.read_records(str(src))
+    prof = C.profile_from_records(rec)
+    gp = rec["models"][-1]
+    y = np.asarray(gp.attr("y_train_"), float)
+    fit = prof._k(prof.x_train) @ prof.alpha + float(gp.attr("noise_")) * prof.alpha
+    np.testing.assert_allclose(fit, y, atol=1e-6)
+    assert prof.meta.bandwidth == 1.0 and prof.meta.compression == 0.9 and prof.meta.max_batch_size in (1024.0, 2048.0)
+    assert np.isfinite(prof.h(prof.meta.batch_size, 1.0)).all()
