@@ -30,7 +30,7 @@ import time
 REFERENCE_UNAVAILABLE = (
     "reference is a CMake project without setup.py/pyproject.toml: `pip install --no-index "
     "--no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref <reference tree>` fails with "
-    "\"Neither 'setup.py' nor 'pyproject.toml' found\"; it also ships no GPU kernels and no NCCL path"
+    "\"Neither 'setup.py' nor 'pyproject.toml' found\"; baseline/build_reference.sh builds it with CMake instead"
 )
 
 
@@ -131,11 +131,129 @@ def arm_watchdog(seconds: float) -> None:
     t.start()
 
 
+def run_reference_arm(args: argparse.Namespace) -> None:
+    """The unmodified reference, built out of tree into ``baseline/_ref`` (recipe in ``baseline/build_reference.sh``),
+    driven through its own API by ``baseline/reference_arm.py``: one node, one process per GPU, started by rank 0 the way
+    the reference's driver starts its local ranks (backend/test/test_end_to_end.py:160-163).  Any failure, a time-out
+    included, ends in the ``unavailable`` line."""
+    import glob
+    import signal
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return                      # the other launcher ranks have nothing to do: rank 0 owns all local processes
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref_dir = os.path.join(here, "baseline", "_ref")
+
+    def unavailable(why: str) -> None:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:600]}), flush=True)
+
+    if not glob.glob(os.path.join(ref_dir, "fasterdp*.so")) or not os.path.exists(os.path.join(ref_dir, "model_wrapper.py")):
+        unavailable(REFERENCE_UNAVAILABLE + "; no out-of-tree build under baseline/_ref either")
+        return
+    lm = args.model.startswith("gpt")
+    if lm or args.amp != "none" or args.compressor != "thresholdv16":
+        unavailable("the reference's driver path is torchvision models in fp32 with its thresholdv16 compressor "
+                    "(backend/test/test_end_to_end.py:21-45); this configuration is outside it")
+        return
+    try:
+        import torch
+
+        have = torch.cuda.device_count()
+    except Exception as e:  # noqa: BLE001
+        have = 0
+        sys.stderr.write(f"[bench] torch: {e!r}\n")
+    if have < world:
+        unavailable(f"{world} GPUs asked for, {have} visible")
+        return
+    session = os.getpid()
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 31
+    env = dict(os.environ)
+    env["LD_LIBRARY_PATH"] = ref_dir + os.pathsep + env.get("LD_LIBRARY_PATH", "")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT", "MASTER_ADDR", "OMP_NUM_THREADS"):
+        env.pop(k, None)            # the reference reads the first ones as NODE rank and NODE count; the launcher's
+                                    # OMP_NUM_THREADS=1 would slow the ATen calls of its host pipeline
+    env.update(WORLD_SIZE="1", RANK="0", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sampler = ClockSampler(0)
+    sampler.start()
+    procs, logs = [], []
+    for lr in range(world):
+        log = open(os.path.join(here, "baseline", f".reference_arm_{lr}.log"), "w+")
+        logs.append(log)
+        procs.append(subprocess.Popen(
+            [sys.executable, os.path.join(here, "baseline", "reference_arm.py"), "--ref-dir", ref_dir, "--local-rank", str(lr),
+             "--local-world", str(world), "--session", str(session), "--port", str(port), "--model", args.model,
+             "--batch", str(args.batch), "--num-classes", str(args.num_classes), "--ratio", str(args.ratio),
+             "--optimizer", args.optimizer, "--lr", str(args.lr), "--momentum", str(args.momentum),
+             "--steps", str(args.steps), "--warmup", str(max(3, args.warmup))],
+            stdout=log, stderr=subprocess.STDOUT, env=env, start_new_session=True))
+    deadline = time.time() + float(os.environ.get("REFERENCE_ARM_TIMEOUT_S", "330"))
+    timed_out = False
+    while any(p.poll() is None for p in procs):
+        if time.time() > deadline:
+            timed_out = True
+            break
+        if any(p.poll() not in (None, 0) for p in procs):
+            time.sleep(2.0)         # one rank failed: the others would wait for it forever
+            break
+        time.sleep(0.2)
+    for p in procs:
+        if p.poll() is None:
+            try:
+                os.killpg(p.pid, signal.SIGKILL)      # exactly the process group this call started
+            except ProcessLookupError:
+                pass
+            p.wait()
+    clocks = sampler.stop()
+    for f in glob.glob(f"/dev/shm/fasterdp-shm-*-{session}*") + glob.glob(f"/dev/shm/sem.fasterdp-sem-{session}*"):
+        try:
+            os.unlink(f)
+        except OSError:
+            pass
+    results, tails = [], []
+    for log in logs:
+        log.seek(0)
+        text = log.read()
+        log.close()
+        first_error = next((ln for ln in text.splitlines() if "Error" in ln or "error" in ln or "Assertion" in ln), "")
+        tails.append((first_error[:240] + " ... " if first_error else "") + text[-160:])
+        for line in text.splitlines():
+            if line.startswith("REFERENCE_ARM_RESULT "):
+                results.append(json.loads(line[len("REFERENCE_ARM_RESULT "):]))
+    if len(results) != world:
+        unavailable(("timed out; " if timed_out else "") + f"{len(results)} of {world} reference processes finished; last output: "
+                    + " | ".join(tails))
+        return
+    ms = max(r["ms"] for r in results)
+    per_step = ms / args.steps
+    value = args.batch * world / (per_step / 1e3)
+    h2d = args.batch * 3 * 224 * 224 * 4 + args.batch * 8
+    out = {
+        "metric": f"{args.model} training throughput, sparse data parallel (thresholdv16 keeping {(1 - args.ratio) * 100:g}% of "
+                  f"gradient entries, error feedback, sparse {args.optimizer})",
+        "impl": "reference", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32 (torch defaults: TF32 cuDNN convolutions)",
+        "data": "synthetic N(0,1) images / uniform labels, random-init weights",
+        "config": {"model": args.model, "global_batch": args.batch * world, "per_gpu_batch": args.batch, "seq_len": None,
+                   "parallelism": f"dp{world}", "compressor": "thresholdv16", "kept_fraction": 1 - args.ratio,
+                   "optimizer": args.optimizer, "lr": args.lr, "staleness": 1,
+                   "transport": "reference: one node, pinned shared memory, CPU pipeline",
+                   "build": "unmodified sources, CMake RelWithDebInfo, out of tree (baseline/build_reference.sh)",
+                   "l2": "per-step working set exceeds the 126 MB L2; no flush needed"},
+        "clocks": clocks,
+        # the reference's loop copies every batch from pinned host memory itself; it reads no loss back
+        "e2e": {"value": value, "unit": "images/s", "ms_per_step": per_step, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "final_loss": results[0]["loss"],
+    }
+    print(json.dumps(out), flush=True)
+
+
 def main() -> None:
     args = parse_args()
     arm_watchdog(float(os.environ.get("BENCH_WATCHDOG_S", "420")))
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        run_reference_arm(args)
         return
 
     # Libraries (NCCL's version banner, for one) write to the process's stdout; the contract is ONE JSON
