@@ -122,9 +122,12 @@ def test_train_driver_cpu_tier_checkpoint_and_resume(tmp_path):
 def test_reference_arm_reports_unavailable():
     import json
 
-    out = subprocess.run([sys.executable, "bench.py", "--impl", "reference"], capture_output=True, text=True, timeout=120)
+    out = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--steps", "3", "--warmup", "3"],
+                         capture_output=True, text=True, timeout=400)
+    assert out.returncode == 0
     d = json.loads(out.stdout.strip().splitlines()[-1])
-    assert d["impl"] == "reference" and "unavailable" in d
+    # without a GPU (or without the out-of-tree build) the arm says why it cannot run; with both it reports a number
+    assert d["impl"] == "reference" and ("unavailable" in d or d["value"] > 0)
 
 
 def test_merge_state_shards_reassembles_full_moments():
