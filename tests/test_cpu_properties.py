@@ -107,3 +107,58 @@ def test_wire_casts_roundtrip(indices, vals):
     assert torch.equal(y, x.bfloat16().float())
     ext.f32_to_f16(x.data_ptr(), h.data_ptr(), len(vals)); ext.f16_to_f32(h.data_ptr(), y.data_ptr(), len(vals))
     assert torch.equal(y, x.half().float())
+
+
+@st.composite
+def sparse_stream(draw):
+    """Unique indices with a mix of whole aligned blocks of 16, runs that only look like blocks and loose entries."""
+    numel = draw(st.sampled_from([40, 4096, 65536, 70000, 1 << 20, (1 << 20) + 64, 5_000_000]))
+    n_blocks = draw(st.integers(min_value=0, max_value=min(12, numel // 16)))
+    blocks = draw(st.lists(st.integers(min_value=0, max_value=numel // 16 - 1), min_size=n_blocks, max_size=n_blocks, unique=True))
+    used = set()
+    idx = []
+    for b in blocks:
+        keep = draw(st.sampled_from([16, 16, 16, 15, 9]))          # some blocks arrive truncated
+        run = list(range(16 * b, 16 * b + keep))
+        if draw(st.booleans()) and keep == 16:
+            run = run[1:] + run[:1]                                # all 16 present, but not in counting order
+        idx += run
+        used.update(run)
+        for j in draw(st.lists(st.integers(min_value=0, max_value=numel - 1), max_size=3)):
+            if j not in used:
+                idx.append(j)
+                used.add(j)
+    seed = draw(st.integers(min_value=0, max_value=2**31 - 1))
+    val = np.random.default_rng(seed).standard_normal(len(idx)).astype(np.float32).tolist()
+    return numel, idx, val, draw(st.booleans()), draw(st.sampled_from([0, 1, 2])), draw(st.booleans())
+
+
+@settings(max_examples=150, deadline=None)
+@given(sparse_stream())
+def test_wire_payload_round_trip_for_any_mix_of_blocks_and_loose_entries(case):
+    numel, idx, val, allow_u16, value_format, allow_blocks = case
+    flags, payload = ext.encode_sparse(idx, val, numel, allow_u16, value_format, allow_blocks)
+    got_idx, got_val = ext.decode_sparse(flags, payload, numel)
+    want = torch.tensor(val, dtype=torch.float32)
+    if value_format == 1:
+        want = want.half().float()
+    elif value_format == 2:
+        want = want.bfloat16().float()
+    assert sorted(zip(got_idx, got_val)) == sorted(zip(idx, want.tolist()))
+    pairs = 4 + len(idx) * ((2 if (flags & 1) else 4) + (2 if value_format else 4))
+    assert len(payload) <= pairs + 4                       # the block form is only chosen when a block exists
+    if not allow_blocks:
+        assert not flags & 0x08
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.integers(min_value=0, max_value=31), st.binary(max_size=200), st.sampled_from([0, 100, 70000]))
+def test_wire_decoder_refuses_or_decodes_arbitrary_bytes(flags, payload, numel):
+    """What arrives from the network is untrusted: the decoder either returns entries inside the tensor or raises."""
+    try:
+        idx, val = ext.decode_sparse(flags, payload, numel)
+    except ValueError:
+        return
+    assert len(idx) == len(val)
+    if numel:
+        assert all(i < numel or i == 0xFFFFFFFF for i in idx)
