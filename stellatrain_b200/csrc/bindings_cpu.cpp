@@ -277,6 +277,8 @@ PYBIND11_MODULE(_Ccpu, m) {
         for (auto& s : b.c->broker_stats()) out.append(py::make_tuple(s.rank, s.send_mbps, s.recv_mbps));
         return out;
       })
+      .def("set_tx_rate_limit", [](CommBox& b, double bytes_per_s, size_t burst) { b.c->set_tx_rate_limit(bytes_per_s, burst); },
+           py::arg("bytes_per_s"), py::arg("burst_bytes") = 64 << 10)
       .def("drop_keys_containing", [](CommBox& b, const std::string& needle, int delay_ms) {
         b.c->set_tx_fault_hook([needle, delay_ms](const std::string& key, int* delay) {
           if (key.find(needle) == std::string::npos) return false;
@@ -352,6 +354,10 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def("post_backward_device", [](CpuEngine& e, int i, uint64_t grad, uint64_t producer_stream, uint64_t copy_stream) {
         e.post_backward_device(i, P<const void>(grad), P<void>(producer_stream), P<void>(copy_stream));
       }, py::arg("param_index"), py::arg("device_grad"), py::arg("producer_stream"), py::arg("copy_stream") = 0)
+      .def("set_tx_rate_limit", [](CpuEngine& e, double bytes_per_s, size_t burst) {
+        if (e.comm()) e.comm()->set_tx_rate_limit(bytes_per_s, burst);
+      }, py::arg("bytes_per_s"), py::arg("burst_bytes") = 64 << 10,
+           "Pace this node's gradient sends (a software stand-in for a slow link between nodes); 0 lifts the limit.")
       .def("drop_tx_containing", [](CpuEngine& e, const std::string& needle) {
         if (!e.comm()) return;
         e.comm()->set_tx_fault_hook([needle](const std::string& key, int*) { return key.find(needle) != std::string::npos; });

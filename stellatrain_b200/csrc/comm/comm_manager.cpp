@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <unistd.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstring>
 #include <stdexcept>
@@ -438,6 +439,11 @@ void CommManager::queue_tx(int64_t priority, const std::string& key, const uint3
   tx_cv_.notify_one();
 }
 
+void CommManager::set_tx_rate_limit(double bytes_per_s, size_t burst_bytes) {
+  tx_burst_ = std::max<size_t>(burst_bytes, 1);
+  tx_rate_ = bytes_per_s > 0 ? bytes_per_s : 0.0;
+}
+
 void CommManager::push_main() {
   pthread_setname_np(pthread_self(), "CommPushThread");
   while (!stop_) {
@@ -458,6 +464,25 @@ void CommManager::push_main() {
       if (delay > 0) std::this_thread::sleep_for(std::chrono::milliseconds(delay));
     }
     const std::vector<unsigned char>& payload = item->payload;
+    if (const double rate = tx_rate_.load()) {
+      // token bucket: the message leaves when the bucket holds its bytes (or is as full as it gets)
+      const double need = static_cast<double>(sizeof(FrameHeader) + item->key.size() + payload.size());
+      const double burst = static_cast<double>(tx_burst_.load());
+      const auto now = std::chrono::steady_clock::now();
+      if (tx_last_.time_since_epoch().count() == 0) { tx_last_ = now; tx_tokens_ = burst; }
+      tx_tokens_ = std::min(burst, tx_tokens_ + std::chrono::duration<double>(now - tx_last_).count() * rate);
+      tx_last_ = now;
+      if (tx_tokens_ < need) {
+        const double wait_s = (need - tx_tokens_) / rate;
+        const auto until = now + std::chrono::duration_cast<std::chrono::steady_clock::duration>(std::chrono::duration<double>(wait_s));
+        while (!stop_ && std::chrono::steady_clock::now() < until)
+          std::this_thread::sleep_for(std::min<std::chrono::steady_clock::duration>(until - std::chrono::steady_clock::now(), std::chrono::milliseconds(20)));
+        tx_last_ = std::chrono::steady_clock::now();
+        tx_tokens_ = 0.0;       // a message larger than the bucket leaves once the bucket's worth plus the rest has accrued
+      } else {
+        tx_tokens_ -= need;
+      }
+    }
     if (!send_frame(push_fd_, kGrad, item->key, item->flags, payload.data(), payload.size(), timeout_ms_)) {
       if (!stop_) set_failed("send to the ring successor failed for " + item->key);
       return;

@@ -11,6 +11,7 @@
 // host-side hook so that failure handling is testable without breaking real links.
 #pragma once
 #include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdint>
 #include <functional>
@@ -103,6 +104,10 @@ class CommManager {
   uint64_t bytes_sent() const { return bytes_sent_; }
   uint64_t bytes_received() const { return bytes_recv_; }
   size_t stashed() const;
+  // Paces the gradient sends of this node to `bytes_per_s` (0: unlimited) with a token bucket of `burst_bytes`: a
+  // software stand-in for a slow link between nodes, so that the regime the reference was written for (about
+  // 1 Gbit/s between machines) can be reproduced on one host.  Control-plane messages are not paced.
+  void set_tx_rate_limit(double bytes_per_s, size_t burst_bytes = 64 << 10);
   // return true to drop the message; positive delay_ms stalls the sender before the send
   void set_tx_fault_hook(std::function<bool(const std::string& key, int* delay_ms)> hook);
   bool failed() const { return failed_; }
@@ -156,6 +161,10 @@ class CommManager {
   std::map<std::string, std::function<void(SparseMessage&&)>> posted_;
   std::map<std::string, SparseMessage> stash_;
   std::function<bool(const std::string&, int*)> tx_hook_;
+  std::atomic<double> tx_rate_{0.0};            // bytes per second, 0 = unlimited
+  std::atomic<size_t> tx_burst_{64 << 10};
+  double tx_tokens_ = 0.0;                       // push thread only
+  std::chrono::steady_clock::time_point tx_last_{};
   BandwidthMonitor rx_mon_;
   std::atomic<uint64_t> bytes_sent_{0}, bytes_recv_{0};
 };

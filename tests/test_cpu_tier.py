@@ -159,6 +159,36 @@ def test_sparse_payload_block_form_round_trip():
     assert ext.decode_sparse(*ext.encode_sparse([], [], 10)) == ([], [])
 
 
+def test_paced_sends_hold_the_configured_rate():
+    boxes = _ring(2, free_port())
+    try:
+        n = 4000                                             # 32 KB per message as pairs
+        idx, val = list(range(1, 2 * n, 2)), [1.0] * n       # odd indices: no whole block
+        boxes[0].set_tx_rate_limit(1_000_000.0, 16 << 10)    # 1 MB/s
+        for i in range(8):
+            boxes[1].post_recv(f"m{i}")
+        t0 = time.time()
+        for i in range(8):
+            boxes[0].queue_tx(i, f"m{i}", idx, val, 100000)
+        got = []
+        while len(got) < 8 and time.time() - t0 < 10:
+            got += boxes[1].drain()
+            time.sleep(0.005)
+        dt = time.time() - t0
+        assert len(got) == 8
+        sent = boxes[0].bytes_sent()
+        assert sent > 8 * 32000
+        assert 0.7 * (sent - (16 << 10)) / 1e6 <= dt <= 2.5 * sent / 1e6, (dt, sent)     # ~0.26 s at 1 MB/s
+        boxes[0].set_tx_rate_limit(0.0)
+        boxes[1].post_recv("fast")
+        t1 = time.time()
+        boxes[0].queue_tx(0, "fast", idx, val, 100000)
+        assert _wait_for(lambda: boxes[1].drain()) and time.time() - t1 < 0.2
+    finally:
+        for b in boxes[::-1]:
+            b.close()
+
+
 def test_bandwidth_monitor_and_interfaces():
     m = ext.BandwidthMonitor()
     for _ in range(5):
@@ -444,3 +474,12 @@ def test_cpu_tier_checkpoint_resumes_bit_for_bit(method, optimizer, tmp_path):
         other.load_state_dict(loaded)
     other.close()
     eng2.close()
+
+
+def test_ring_benchmark_smoke():
+    from stellatrain_b200 import bench_cpu_ring as R
+
+    sizes = [65536, 20000]
+    pairs = R.run(nodes=2, gbps=0.0, steps=3, warmup=1, wire="pairs", sizes=sizes, ratio=0.9)
+    blocks = R.run(nodes=2, gbps=0.0, steps=3, warmup=1, wire="blocks+bf16", sizes=sizes, ratio=0.9)
+    assert pairs["ms_per_step"] > 0 and blocks["tx_bytes_per_step_per_node"] < 0.5 * pairs["tx_bytes_per_step_per_node"]
