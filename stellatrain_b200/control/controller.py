@@ -42,10 +42,14 @@ class Client:
 
 class Controller:
     def __init__(self, port: int = 5556, host: str = "0.0.0.0", adapt: Optional[bool] = None,
-                 profile_path: Optional[str] = None, transport: str = "nvlink", state_path: Optional[str] = None) -> None:
+                 profile_path: Optional[str] = None, transport: str = "nvlink", state_path: Optional[str] = None,
+                 wire_blocks: Optional[bool] = None) -> None:
         self.adapt = (os.environ.get("DISABLE_RATE_ADAPT", "0") in ("", "0")) if adapt is None else adapt
         self.profile = load_profile(profile_path or os.environ.get("MODEL_PROFILE"))
         self.transport = transport
+        # the CPU tier's TCP messages carry whole blocks of 16 entries behind one block id by default: the byte model
+        # that turns a compression ratio into required goodput has to know
+        self.wire_blocks = (transport == "tcp") if wire_blocks is None else wire_blocks
         self.state_path = state_path      # optimiser state is written here after every instruction and read back at start
         self.sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
         self.sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
@@ -130,7 +134,7 @@ class Controller:
     def _on_global_init(self, gi: M.GlobalInit) -> None:
         with self.lock:
             self.global_init = gi
-            traffic = TrafficModel(gi.param_counts, self.transport, gi.grad_fp16, gi.grad_idx_u16)
+            traffic = TrafficModel(gi.param_counts, self.transport, gi.grad_fp16, gi.grad_idx_u16, grad_block16=self.wire_blocks)
             self.optimizer = BatchRateOptimizer(gi.num_gpus, gi.num_nodes, traffic, self.profile,
                                                 latest_iter=lambda: self.latest_iter)
             for gid, c in self.clients.items():
