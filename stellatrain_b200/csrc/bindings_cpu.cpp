@@ -320,6 +320,8 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def("configure_compression_ratio", &CpuEngine::configure_compression_ratio)
       .def("configure_compression_ratio_from", &CpuEngine::configure_compression_ratio_from, py::arg("iteration"), py::arg("ratio"))
       .def("compression_ratio_at", &CpuEngine::compression_ratio_at)
+      .def("set_node_weights", &CpuEngine::set_node_weights, py::arg("weights"), py::arg("from_iteration") = 0)
+      .def("node_weights_at", &CpuEngine::node_weights_at)
       .def("configure_wire", &CpuEngine::configure_wire, py::arg("blocks") = true, py::arg("value_format") = 0)
       .def("gradient_accumulation", &CpuEngine::gradient_accumulation)
       .def("is_debug_accuracy_mode", [](CpuEngine& e) { return e.options().debug_accuracy; })

@@ -121,6 +121,24 @@ double CpuEngine::compression_ratio_at(int64_t iter) const {
   return r;
 }
 
+void CpuEngine::set_node_weights(const std::vector<float>& weights, int64_t from_iter) {
+  if (static_cast<int>(weights.size()) != opt_.world) throw std::invalid_argument("one weight per node is needed");
+  for (float w : weights)
+    if (!(w >= 0.f) || !std::isfinite(w)) throw std::invalid_argument("weights must be finite and not negative");
+  std::lock_guard<std::mutex> lk(ratio_mu_);
+  weights_from_[from_iter] = weights;
+}
+
+std::vector<float> CpuEngine::node_weights_at(int64_t iter) const {
+  std::lock_guard<std::mutex> lk(ratio_mu_);
+  std::vector<float> w(static_cast<size_t>(std::max(1, opt_.world)), 1.0f / static_cast<float>(std::max(1, opt_.world)));
+  for (auto& kv : weights_from_) {
+    if (kv.first > iter) break;
+    w = kv.second;
+  }
+  return w;
+}
+
 void CpuEngine::configure_wire(bool blocks, int value_format) {
   if (value_format < 0 || value_format > 2) throw std::invalid_argument("value format must be 0 (fp32), 1 (fp16) or 2 (bf16)");
   wire_blocks_ = blocks;

@@ -98,6 +98,12 @@ class CpuEngine {
   // block id (what threshold-v16 selects).  `value_format`: 0 fp32, 1 fp16, 2 bf16; with 1 or 2 the compress stage
   // keeps the rounding error of every sent value in the residual, so narrow values delay mass instead of losing it.
   // Every node must use the same value format (the block form is self-describing).
+  // Weight of every node's stream in the merge, indexed by node rank (default: 1 / nodes each, the reference's mean,
+  // backend/src/engine/modules/cpu_optimize.cpp:55).  With unequal batch sizes per node the share of the global batch
+  // keeps the merged gradient unbiased.  Counts from iteration `from_iter` on (same rule as the ratio switch); every
+  // node must be given the same weights for the same iteration.
+  void set_node_weights(const std::vector<float>& weights, int64_t from_iter = 0);
+  std::vector<float> node_weights_at(int64_t iter) const;
   void configure_wire(bool blocks, int value_format);
   bool wire_blocks() const { return wire_blocks_; }
   int wire_value_format() const { return wire_values_; }
@@ -221,6 +227,7 @@ class CpuEngine {
   mutable std::mutex ratio_mu_;
   double ratio_ = 0.99;
   std::map<int64_t, double> ratio_from_;     // first iteration -> ratio, for switches that lie ahead
+  std::map<int64_t, std::vector<float>> weights_from_;   // first iteration -> per-node merge weights
   std::atomic<bool> wire_blocks_{true};
   std::atomic<int> wire_values_{0};
   std::unique_ptr<ThreadPool> pool_;

@@ -192,7 +192,11 @@ class ModuleOptimize : public Module {
     }
     std::vector<const uint32_t*> idx(W);
     std::vector<const float*> val(W);
-    std::vector<float> weights(W, 1.0f / static_cast<float>(W));   // mean over nodes (cpu_optimize.cpp:55)
+    // mean over nodes (cpu_optimize.cpp:55) unless the nodes were given their shares of the global batch; slot 0 is this
+    // node's own stream, slot s the stream that started s hops up the ring
+    const std::vector<float> by_node = e.node_weights_at(t->iter);
+    std::vector<float> weights(W);
+    for (int s = 0; s < W; ++s) weights[s] = by_node[static_cast<size_t>(((e.options().rank - s) % W + W) % W)];
     size_t total = 0;
     for (int s = 0; s < W; ++s) {
       idx[s] = t->idx.data() + static_cast<size_t>(s) * t->k;

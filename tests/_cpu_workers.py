@@ -18,7 +18,7 @@ def synthetic_grad(node, local, step, pi, n):
 
 def engine_worker(q, port, session_base, world, node, local_world, local, steps, method, optimizer, staleness, mode):
     """mode: 'ok' | 'ok_bf16' (bf16 values on the wire) | 'ok_pairs' (no block ids on the wire) | 'ok_switch' (the compression ratio changes from iteration 3 on; the nodes learn
-    of it at different steps) | 'ok_device' (the
+    of it at different steps) | 'ok_weights' (node 0 counts a quarter, node 1 three quarters in the merge) | 'ok_device' (the
     engine copies gradients and parameters itself, through the stand-in CUDA runtime) | 'absent' (never
     configures) | 'drop' (node 1 drops its gradient sends) | 'die' (node 1 exits mid-run)"""
     try:
@@ -34,7 +34,7 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
         device = mode == "ok_device"
         if device:
             ext.install_fake_cuda(1)
-        if mode.startswith("ok") and mode != "ok_switch":
+        if mode.startswith("ok") and mode not in ("ok_switch", "ok_weights"):
             mode = "ok"
         timeout_ms = 4000 if mode != "ok" else 30000
         eng.configure("127.0.0.1", port, world, node, session_base + node, local_world, local, method, 1, staleness,
@@ -57,6 +57,9 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
         keep = []
         if mode == "drop" and node == 1:
             eng.drop_tx_containing("@")
+        if mode == "ok_weights":
+            eng.set_node_weights([0.25, 0.75])
+            mode = "ok"
         switch = mode == "ok_switch"
         if switch:
             mode = "ok"

@@ -202,7 +202,7 @@ def test_bandwidth_monitor_and_interfaces():
         del os.environ["PUBLIC_IP"]
 
 
-def _oracle_run(world, local_world, steps, method, optimizer, ratio_from=None):
+def _oracle_run(world, local_world, steps, method, optimizer, ratio_from=None, weights=None):
     from _cpu_workers import SIZES, synthetic_grad
 
     params = [torch.full((n,), 0.5) for n in SIZES]
@@ -222,7 +222,7 @@ def _oracle_run(world, local_world, steps, method, optimizer, ratio_from=None):
                 keep = idx < n
                 streams.append((idx[keep], val[keep]))
                 resid[node][pi] = resid[node][pi][:n]
-            dense, touched = O.merge_streams(n, streams, [1.0 / world] * world)
+            dense, touched = O.merge_streams(n, streams, weights or [1.0 / world] * world)
             (O.sparse_sgd if optimizer == "sgd" else O.sparse_adam)(params[pi], dense, touched, cfg, st[pi])
     return params
 
@@ -312,6 +312,19 @@ def test_ratio_switch_takes_effect_at_the_same_iteration_on_every_node():
     want = _oracle_run(world, 1, steps, "topk", "adam", ratio_from=(3, 0.5))
     for node, local, _, out in results:
         assert out["drift"] == 0.0 and out["versions"] == [steps] * 3
+        for got, w in zip(out["params"], want):
+            np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
+
+
+def test_node_weights_follow_the_ring_order():
+    """Unequal batch sizes per node: every node merges the streams with the same per-node weights, whichever slot a
+    stream arrived in."""
+    world, steps = 2, 5
+    results = _launch(world, 1, steps, "topk", "sgd", 1, "ok_weights")
+    assert len(results) == 2 and all(r[2] == "ok" for r in results), results
+    want = _oracle_run(world, 1, steps, "topk", "sgd", weights=[0.25, 0.75])
+    for node, local, _, out in results:
+        assert out["drift"] == 0.0
         for got, w in zip(out["params"], want):
             np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
 
