@@ -73,7 +73,14 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
             D.DummyInputGenerator(full_batch, length=args.dummy_length, num_class=args.num_classes, seed=global_rank)
     else:
         fn, root = builders[args.dataset]
-        base = fn(root, full_batch, args.num_workers, world_size=global_world, rank=global_rank)
+        if args.loader == "subprocess":
+            # the whole input pipeline in a child process (the reference's SuperFastDataLoader, util/dataloader.py:41-71)
+            import functools
+
+            base = D.SuperFastDataLoader(functools.partial(fn, root, full_batch, args.num_workers, world_size=global_world,
+                                                           rank=global_rank), epochs=args.num_epochs)
+        else:
+            base = fn(root, full_batch, args.num_workers, world_size=global_world, rank=global_rank)
     hook = None
     if args.telemetry_uri and args.tier == "gpu":
         from stellatrain_b200.parallel.telemetry import TelemetryHook
@@ -209,6 +216,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--allow-world-change", action="store_true", help="resume on a different number of ranks")
     p.add_argument("--heartbeat", type=float, default=0.0, help="seconds of silence after which a rank counts as lost (0: off)")
     p.add_argument("--state-partition", default="replicated", choices=["replicated", "owner"])
+    p.add_argument("--loader", default="inline", choices=["inline", "subprocess"],
+                   help="real datasets: build and run the DataLoader in this process or in a child process")
     p.add_argument("--wire-format", default="wide", choices=["wide", "narrow"])
     p.add_argument("--wire-values", default="fp32", choices=["fp32", "fp16", "bf16"],
                    help="CPU tier: value type of the messages between nodes (the rounding error stays in the residual)")
