@@ -167,6 +167,8 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
                         print(f"epoch {epoch} step {global_step} loss {meter.val:.4f} ({rate:.0f} samples/s)", flush=True)
         if args.tier == "gpu":
             net.step()
+    if hasattr(base, "close"):
+        base.close()       # a loader in a child process: this process cannot exit while that child lives
     sync()
     if args.checkpoint and args.tier == "gpu":
         from stellatrain_b200.utils import checkpoint

@@ -107,8 +107,10 @@ class PrefetchLoader:
                 self._record_stream(o, stream)
 
 
-def _loader_process(factory: Callable, out, stop, epochs: int) -> None:
+def _loader_process(factory: Callable, out, stop, epochs: int, parent_pid: int) -> None:
     """Body of the child process of ``SuperFastDataLoader``."""
+    import os
+
     torch.set_num_threads(1)
     try:
         loader = factory()
@@ -122,15 +124,18 @@ def _loader_process(factory: Callable, out, stop, epochs: int) -> None:
     except Exception as e:  # noqa: BLE001 - reported to the parent
         out.put(("error", f"{type(e).__name__}: {e}"))
     # tensors travel as file descriptors that the parent fetches from this process when it unpickles a batch:
-    # stay until the parent says it is done
-    stop.wait()
+    # stay until the parent says it is done (or is gone: this process is not a daemon, its loader may have workers)
+    while not stop.wait(timeout=1.0):
+        if os.getppid() != parent_pid:
+            return
 
 
 class SuperFastDataLoader:
     """A loader that lives in a child process.
 
     ``factory`` is a picklable callable that builds the loader inside the child (a loader with worker processes
-    cannot be pickled once it runs).  Batches come back through a bounded queue; tensors travel in shared memory,
+    cannot be pickled once it runs).  The child is not a daemon, because a loader inside it needs worker processes of
+    its own; ``close()`` ends it, and a finalizer does the same when this process exits.  Batches come back through a bounded queue; tensors travel in shared memory,
     so the parent does not copy them.  ``len()`` is the child's loader length.  Every wait has a limit: a child that
     dies or stalls raises ``RuntimeError`` in the parent instead of blocking the training loop forever.
     """
@@ -143,9 +148,17 @@ class SuperFastDataLoader:
         self._q = ctx.Queue(maxsize=depth)
         self._stop = ctx.Event()
         self._timeout = timeout_s
-        self._proc = ctx.Process(target=_loader_process, args=(factory, self._q, self._stop, epochs), daemon=True,
-                                 name="SuperFastDataLoader")
+        import multiprocessing.util as mp_util
+        import os
+
+        # not a daemon: a DataLoader inside the child needs worker processes of its own
+        self._proc = ctx.Process(target=_loader_process, args=(factory, self._q, self._stop, epochs, os.getpid()),
+                                 daemon=False, name="SuperFastDataLoader")
         self._proc.start()
+        # runs when this process ends, before multiprocessing waits for its non-daemonic children, also in a process
+        # that multiprocessing itself started (those skip atexit handlers)
+        self._finalizer = mp_util.Finalize(self, SuperFastDataLoader._shutdown, args=(self._proc, self._q, self._stop),
+                                           exitpriority=20)
         kind, value = self._get(max(timeout_s, 120.0))     # starting an interpreter and importing torch takes a while
         if kind == "error":
             self.close()
@@ -178,24 +191,24 @@ class SuperFastDataLoader:
                 raise RuntimeError(f"the loader process failed: {value}")
             yield value
 
-    def close(self) -> None:
-        self._stop.set()
+    @staticmethod
+    def _shutdown(proc, q, stop) -> None:
+        if not proc.is_alive():
+            return
+        stop.set()
         try:
             while True:                      # unblock a child that waits for room in the queue
-                self._q.get_nowait()
+                q.get_nowait()
         except (queue.Empty, OSError, ValueError):
             pass
-        self._proc.join(timeout=5)
-        if self._proc.is_alive():
-            self._proc.terminate()           # this exact child, by handle
-            self._proc.join(timeout=5)
+        proc.join(timeout=5)
+        if proc.is_alive():
+            proc.terminate()                 # this exact child, by handle
+            proc.join(timeout=5)
 
-    def __del__(self) -> None:
-        try:
-            if self._proc.is_alive():
-                self.close()
-        except Exception:  # noqa: BLE001 - interpreter shutdown
-            pass
+    def close(self) -> None:
+        self._finalizer()                    # runs _shutdown once
+
 
 
 class DummyInputGenerator:

@@ -119,6 +119,25 @@ def test_train_driver_cpu_tier_checkpoint_and_resume(tmp_path):
     assert "resumed from" in out.stdout and "at iteration 2" in out.stdout and "done: 4 iterations" in out.stdout
 
 
+def test_train_driver_real_dataset_through_a_loader_process(tmp_path):
+    """ImageNet-100 builder (class list next to the data), the loader in a child process, CPU tier."""
+    np = pytest.importorskip("numpy")
+    Image = pytest.importorskip("PIL.Image")
+    classes = ["n01440764", "n01443537"]
+    for c in classes + ["n09999999"]:                       # the third class is not on the list and must be ignored
+        d = tmp_path / "train" / c
+        d.mkdir(parents=True)
+        for i in range(4):
+            Image.fromarray((np.random.rand(40, 40, 3) * 255).astype("uint8")).save(d / f"{i}.jpg")
+    (tmp_path / "imagenet100.txt").write_text("\n".join(classes) + "\n")
+    out = subprocess.run([sys.executable, "-m", "stellatrain_b200.train", "--tier", "cpu", "--model", "resnet18", "--dataset",
+                          "imagenet100", "--imagenet-root", str(tmp_path), "--num-epochs", "1", "--batch-size", "2",
+                          "--local-world-size", "1", "--compression", "0.9", "--num-classes", "2", "--log-every", "1",
+                          "--num-workers", "1", "--loader", "subprocess"], capture_output=True, text=True, timeout=400)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "done: 4 iterations" in out.stdout               # 8 listed images, batches of 2
+
+
 def test_reference_arm_reports_unavailable():
     import json
 
