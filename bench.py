@@ -526,6 +526,30 @@ def main() -> None:
         cpu_engine.synchronize()
         cpu_engine.close()
 
+    # The sparse path inside the step, from the device-clock stamps that the kernels of the last step wrote themselves:
+    # select + push and scatter + apply of every bucket, and the select chain against the memory roofline (it moves 20
+    # bytes per element: read gradient and residual, write residual and zeros, re-read the residual) at the measured
+    # copy bandwidth.  In the step these kernels share the GPU with the backward pass, so the fraction is a lower bound
+    # of what the kernels reach alone (profiles/ has those numbers).  Never allowed to break the result line.
+    sparse_path = None
+    if engine is not None:
+        try:
+            rows = engine.device_timeline()
+            sel, app = sum(r["select_ms"] for r in rows), sum(r["apply_ms"] for r in rows)
+            hbm_gbs, peaks_src = 6650.0, "fallback"
+            peaks_file = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+            if os.path.exists(peaks_file):
+                with open(peaks_file) as f:
+                    hbm_gbs, peaks_src = float(json.load(f)["hbm_gbs"]), "measured"
+            sparse_path = {"buckets": len(rows), "select_push_ms": sel, "scatter_apply_ms": app,
+                           "share_of_step": (sel + app) / per_step if per_step > 0 else None,
+                           "select_bytes": 20 * n_params,
+                           "select_fraction_of_copy_bandwidth": (20 * n_params / (sel * 1e-3) / (hbm_gbs * 1e9)) if sel > 0 else None,
+                           "copy_bandwidth_gbs": hbm_gbs, "of": peaks_src,
+                           "nvlink_bytes_per_step": int(sum(rt.bucket.layout.wire_bytes() for rt in engine.buckets) * max(world - 1, 0))}
+        except Exception as e:  # noqa: BLE001
+            sparse_path = {"error": repr(e)}
+
     if rank == 0:
         out = {
             "metric": f"{args.model} training throughput, sparse data parallel ({args.compressor} keeping "
@@ -552,7 +576,7 @@ def main() -> None:
                 "cuda_graph": bool(args.graph) if engine is not None else (args.impl == "dense_graph"), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
                 "l2": "per-step working set (233 MB of parameters plus activations) exceeds the 126 MB L2; no flush needed",
             },
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss, "sparse_path": sparse_path,
         }
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(out) + "\n").encode())

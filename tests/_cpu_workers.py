@@ -1,4 +1,5 @@
 """Worker entry points for multi-process tests of the CPU tier (importable for the spawn start method)."""
+import ctypes
 import os
 import sys
 import traceback
@@ -49,7 +50,7 @@ def engine_worker(q, port, session_base, world, node, local_world, local, steps,
         if device:
             idxs = [eng.pre_train_init(pi, f"p{pi}", p.numel(), 0, p.data_ptr()) for pi, p in enumerate(params)]
             for pi, p in zip(idxs, params):
-                p.copy_(torch.frombuffer((__import__("ctypes").c_float * p.numel()).from_address(eng.master_param(pi)),
+                p.copy_(torch.frombuffer((ctypes.c_float * p.numel()).from_address(eng.master_param(pi)),
                                          dtype=torch.float32))      # what a framework does after registration
                 eng.attach_device_param(pi, p.data_ptr())
         else:
