@@ -11,8 +11,12 @@
 // Workload: 11,689,512 fp32 elements ~ N(0, 1e-2), k = 1 %, Adam lr 1e-3, 20 steps, one tensor, world size 1; the
 // reference's thread pool has 32 workers as on its node master (backend/src/engine/config.h:7).
 // Prints one JSON line per compressor with the median milliseconds per step.
+//
+// With a third argument (a directory) it also writes the input of the first step (input.f32) and what each compressor
+// selected from it (<method>.idx.u32, <method>.val.f32), so that another implementation can be compared on the same data.
 #include <algorithm>
 #include <chrono>
+#include <fstream>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -31,6 +35,11 @@ int main(int argc, char** argv) {
   const size_t n = argc > 1 ? std::stoull(argv[1]) : 11689512ull;
   const int steps = argc > 2 ? std::atoi(argv[2]) : 20;
   const uint32_t k = static_cast<uint32_t>(std::max<size_t>(1, n / 100));
+  const std::string dump = argc > 3 ? argv[3] : "";
+  auto write = [&dump](const std::string& name, const void* data, size_t bytes) {
+    std::ofstream f(dump + "/" + name, std::ios::binary);
+    f.write(static_cast<const char*>(data), static_cast<std::streamsize>(bytes));
+  };
   std::unique_ptr<ThreadPool> pool = std::make_unique<ThreadPool>(32);
 
   for (const std::string method : {"thresholdv16", "thresholdv", "topk"}) {
@@ -54,6 +63,11 @@ int main(int argc, char** argv) {
       const auto t0 = std::chrono::steady_clock::now();
       add_arrays(acc.data(), resid.data(), n);
       const size_t cnt = comp->compress("flat", {acc.data(), n}, k, {idx.data(), k}, {val.data(), k}, 0);
+      if (s == 0 && !dump.empty()) {
+        write("input.f32", grad.data(), n * sizeof(float));
+        write(method + ".idx.u32", idx.data(), cnt * sizeof(uint32_t));
+        write(method + ".val.f32", val.data(), cnt * sizeof(float));
+      }
       for (size_t j = 0; j < cnt; ++j) acc[idx[j]] = 0.f;
       std::memcpy(resid.data(), acc.data(), n * sizeof(float));
       adam.optimize_raw(param.data(), static_cast<uint32_t>(n), "flat", val.data(), idx.data(), static_cast<uint32_t>(cnt));
