@@ -30,6 +30,7 @@
 #include "engine/threadpool.h"
 #include "misc/array_util.h"
 #include "optim/adam.h"
+#include "optim/sgd.h"
 
 int main(int argc, char** argv) {
   const size_t n = argc > 1 ? std::stoull(argv[1]) : 11689512ull;
@@ -67,6 +68,25 @@ int main(int argc, char** argv) {
         write("input.f32", grad.data(), n * sizeof(float));
         write(method + ".idx.u32", idx.data(), cnt * sizeof(uint32_t));
         write(method + ".val.f32", val.data(), cnt * sizeof(float));
+        if (method == "thresholdv") {
+          // the reference's optimisers on this selection, two calls each from zero parameters (the second call
+          // exercises Adam's step counter and SGD's momentum buffer): parameter values at the selected indices
+          std::string opt_lr = "lr", opt_mom = "momentum";
+          Adam a2;
+          a2.configure(opt_lr, 1e-3f);
+          SGD s2;
+          s2.configure(opt_lr, 0.1f);
+          s2.configure(opt_mom, 0.9f);
+          std::vector<float> pa(n, 0.f), ps(n, 0.f), out(cnt);
+          for (int rep = 0; rep < 2; ++rep) {
+            a2.optimize_raw(pa.data(), static_cast<uint32_t>(n), "parity", val.data(), idx.data(), static_cast<uint32_t>(cnt));
+            s2.optimize_raw(ps.data(), static_cast<uint32_t>(n), "parity", val.data(), idx.data(), static_cast<uint32_t>(cnt));
+          }
+          for (size_t j = 0; j < cnt; ++j) out[j] = pa[idx[j]];
+          write("adam.param.f32", out.data(), cnt * sizeof(float));
+          for (size_t j = 0; j < cnt; ++j) out[j] = ps[idx[j]];
+          write("sgd.param.f32", out.data(), cnt * sizeof(float));
+        }
       }
       for (size_t j = 0; j < cnt; ++j) acc[idx[j]] = 0.f;
       std::memcpy(resid.data(), acc.data(), n * sizeof(float));

@@ -73,3 +73,25 @@ def test_top_k_is_exact_where_the_reference_is_not(dump):
     # (backend/src/compress/topk.cpp:28-46): its values are not the input's values at its indices and carry less mass
     assert not np.array_equal(x[ri], rv)
     assert np.abs(rv).sum() < np.abs(ov).sum()
+
+
+def test_sparse_optimisers_match_the_reference_numerically(dump):
+    """Two calls of the reference's sparse Adam (lr 1e-3) and SGD (lr 0.1, momentum 0.9) on one selection, from zero
+    parameters, against this package's CPU optimisers on the same (index, value) pairs."""
+    from stellatrain_b200 import cpu_tier
+
+    x, ri, rv = _load(dump, "thresholdv")
+    idx = torch.from_numpy(ri.astype(np.int32)).contiguous()
+    val = torch.from_numpy(rv.copy())
+    for kind, options, file, tol in (("adam", {"lr": 1e-3}, "adam.param.f32", 2e-6), ("sgd", {"lr": 0.1, "momentum": 0.9}, "sgd.param.f32", 1e-6)):
+        want = np.fromfile(dump / file, dtype=np.float32)
+        opt = cpu_tier.make_optimizer(kind)
+        for k, v in options.items():
+            opt.configure(k, v)
+        param = torch.zeros(len(x))
+        for _ in range(2):
+            opt.optimize(param.data_ptr(), len(x), "parity", val.data_ptr(), idx.data_ptr(), len(ri))
+        got = param.numpy()[ri]
+        assert np.abs(want).max() > 0
+        np.testing.assert_allclose(got, want, rtol=tol, atol=1e-9)
+        assert float(param.abs().sum()) == pytest.approx(float(np.abs(got).sum()), rel=1e-6)      # nothing else moved
