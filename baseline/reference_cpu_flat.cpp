@@ -60,6 +60,10 @@ int main(int argc, char** argv) {
     size_t sent = 0;
     for (int s = 0; s < steps; ++s) {
       for (auto& g : grad) g = dist(rng);
+      if (!dump.empty() && method == "thresholdv16") {
+        std::ofstream f(dump + "/grads.f32", s == 0 ? std::ios::binary : std::ios::binary | std::ios::app);
+        f.write(reinterpret_cast<const char*>(grad.data()), static_cast<std::streamsize>(n * sizeof(float)));
+      }
       std::memcpy(acc.data(), grad.data(), n * sizeof(float));      // the gradient as it lands in the shared slot (not timed)
       const auto t0 = std::chrono::steady_clock::now();
       add_arrays(acc.data(), resid.data(), n);
@@ -93,6 +97,10 @@ int main(int argc, char** argv) {
       adam.optimize_raw(param.data(), static_cast<uint32_t>(n), "flat", val.data(), idx.data(), static_cast<uint32_t>(cnt));
       ms.push_back(std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
       sent += cnt;
+    }
+    if (!dump.empty()) {
+      write(method + ".final_param.f32", param.data(), n * sizeof(float));
+      write(method + ".final_resid.f32", resid.data(), n * sizeof(float));
     }
     std::sort(ms.begin(), ms.end());
     std::printf("{\"impl\": \"reference\", \"method\": \"%s\", \"numel\": %zu, \"steps\": %d, \"k\": %u, "

@@ -21,7 +21,7 @@ def dump(tmp_path_factory):
         pytest.skip("the reference is not built or its tree is not at hand")
     out = tmp_path_factory.mktemp("refdump")
     env = dict(os.environ, TMPDIR=str(out))
-    run = subprocess.run(["bash", str(ROOT / "baseline" / "run_reference_cpu_flat.sh"), str(REF_TREE), "200000", "1", str(out)],
+    run = subprocess.run(["bash", str(ROOT / "baseline" / "run_reference_cpu_flat.sh"), str(REF_TREE), "200000", "8", str(out)],
                          capture_output=True, text=True, timeout=600, env=env)
     if run.returncode != 0:
         pytest.skip("the harness did not build here: " + run.stderr[-300:])
@@ -95,3 +95,32 @@ def test_sparse_optimisers_match_the_reference_numerically(dump):
         assert np.abs(want).max() > 0
         np.testing.assert_allclose(got, want, rtol=tol, atol=1e-9)
         assert float(param.abs().sum()) == pytest.approx(float(np.abs(got).sum()), rel=1e-6)      # nothing else moved
+
+
+def test_eight_steps_of_error_feedback_and_sparse_adam_track_the_reference(dump):
+    """The whole per-tensor pipeline (accumulate with the residual, threshold-v16 with its adapting threshold, residual
+    save, sparse Adam) for eight steps on the reference's gradients: selections may differ by a block per step, so the
+    comparison is on what matters downstream."""
+    from stellatrain_b200 import cpu_tier
+
+    n, steps = 200000, 8
+    grads = np.fromfile(dump / "grads.f32", dtype=np.float32).reshape(steps, n)
+    want_p = np.fromfile(dump / "thresholdv16.final_param.f32", dtype=np.float32)
+    want_r = np.fromfile(dump / "thresholdv16.final_resid.f32", dtype=np.float32)
+    opt = cpu_tier.make_optimizer("adam")
+    opt.configure("lr", 1e-3)
+    param, resid, k = torch.zeros(n), torch.zeros(n), n // 100
+    name = f"parity-pipeline-{os.getpid()}"
+    for s in range(steps):
+        idx, val = cpu_tier.compress_with_feedback(name, torch.from_numpy(grads[s].copy()), resid, k, "thresholdv16")
+        assert idx.numel() == k
+        opt.optimize(param.data_ptr(), n, "pipeline", val.data_ptr(), idx.data_ptr(), idx.numel())
+    got_p, got_r = param.numpy(), resid.numpy()
+    cos = float(np.dot(got_p, want_p) / (np.linalg.norm(got_p) * np.linalg.norm(want_p)))
+    assert cos > 0.97, cos
+    touched_both = np.count_nonzero((got_p != 0) & (want_p != 0)) / max(1, np.count_nonzero((got_p != 0) | (want_p != 0)))
+    assert touched_both > 0.95
+    # nothing is lost in either: what was not sent sits in the residual
+    total = grads.astype(np.float64).sum()
+    assert abs(float(got_r.astype(np.float64).sum()) - float(want_r.astype(np.float64).sum())) < 0.05 * abs(total) + 1.0
+    assert np.linalg.norm(got_r - want_r) / np.linalg.norm(want_r) < 0.1
