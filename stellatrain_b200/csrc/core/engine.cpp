@@ -309,11 +309,20 @@ void CpuEngine::post_backward_device(int index, const void* device_grad, void* p
       LOG_ERROR("CpuEngine", "starting the task of parameter " << index << " failed: " << e.what());
     }
   }, &callbacks_in_flight_};
-  callbacks_in_flight_.fetch_add(1);
-  const int rc = api->event_record(p.grad_event, producer_stream) | api->stream_wait_event(copy_stream, p.grad_event) |
-                 api->memcpy_d2h_async(slot, device_grad, static_cast<size_t>(p.numel) * sizeof(float), copy_stream) |
-                 api->launch_host_func(copy_stream, after_cuda_trampoline, after);
-  if (rc != 0) throw std::runtime_error("a CUDA runtime call of the gradient copy failed");
+  // in order, stopping at the first failure: a callback that was never enqueued must not be waited for
+  int rc = api->event_record(p.grad_event, producer_stream);
+  if (rc == 0) rc = api->stream_wait_event(copy_stream, p.grad_event);
+  if (rc == 0) rc = api->memcpy_d2h_async(slot, device_grad, static_cast<size_t>(p.numel) * sizeof(float), copy_stream);
+  if (rc == 0) {
+    callbacks_in_flight_.fetch_add(1);
+    rc = api->launch_host_func(copy_stream, after_cuda_trampoline, after);
+    if (rc != 0) callbacks_in_flight_.fetch_sub(1);
+  }
+  if (rc != 0) {
+    delete after;
+    --p.claim_cnt;      // the slot was not used
+    throw std::runtime_error("a CUDA runtime call of the gradient copy failed with code " + std::to_string(rc));
+  }
 }
 
 void CpuEngine::schedule_after_cuda(Module* next, const std::shared_ptr<TrainTask>& t, void* stream) {
