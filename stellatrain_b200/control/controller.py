@@ -28,6 +28,9 @@ from .gp_profile import load_profile
 from .optimizer import BatchRateOptimizer, TrafficModel, max_batch_for
 
 LOG_PATH = "/tmp/stellatrain-b200-controller.log"
+# one line per issued instruction set (the reference appends to instruction_history_log.txt,
+# backend/src/engine/batch_rate_alloc_optim.py:474-477)
+INSTRUCTION_LOG_PATH = "/tmp/stellatrain-b200-instructions.log"
 SMOOTH = 0.9     # scoreboard EWMA
 
 
@@ -218,6 +221,13 @@ class Controller:
                         msg = M.Instruction(inst.iter, M.TrainConfig(int(inst.batch[gid]), 1, float(inst.comp_ratio)))
                         c.pending.put(msg)
                         self.issued.append(msg)
+                try:
+                    with open(INSTRUCTION_LOG_PATH, "a") as f:
+                        f.write(f"{time.time():.3f} observed_iter={self.latest_iter} effective_iter={inst.iter} "
+                                f"ratio={float(inst.comp_ratio):.6f} batch={[int(b) for b in inst.batch]} "
+                                f"measured_mbps={measured:.1f}\n")
+                except OSError:
+                    pass
                 self.save_state()
             if time.time() - last_dump > 2.0:
                 last_dump = time.time()
