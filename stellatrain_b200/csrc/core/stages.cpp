@@ -96,17 +96,14 @@ class ModuleGather : public Module {
     const int N = e.options().local_world, r = e.options().local_rank;
     const size_t len = p.numel;
     const size_t b = len * static_cast<size_t>(r) / N, en = len * static_cast<size_t>(r + 1) / N;
-    float* dst = p.slot[t->iter % 2][0] + b;
+    // The slice of the residual takes the sum: r <- r + g_0 + ... + g_{N-1}.  Accumulating into the residual instead of
+    // into a gradient slot lets the compress stage work in place, so no copy back into the residual is needed afterwards
+    // (the reference sums into slot 0 and copies the whole tensor back, cpu_gather.cpp:63-82, compress.cpp:172-188).
+    float* dst = p.resid + b;
     t->stat_start("CRIT_PATH_gather");
-    // error feedback (shared residual) and the other local processes' gradients; the last addition also applies the
-    // NaN policy shared with the GPU tier: a NaN is dropped (neither sent nor kept)
-    if (N == 1) {
-      add_arrays_nan_to_zero(dst, dst, p.resid + b, en - b);
-    } else {
-      add_arrays(dst, p.resid + b, en - b);
-      for (int g = 1; g + 1 < N; ++g) add_arrays(dst, p.slot[t->iter % 2][g] + b, en - b);
-      add_arrays_nan_to_zero(dst, dst, p.slot[t->iter % 2][N - 1] + b, en - b);
-    }
+    // the last addition also applies the NaN policy shared with the GPU tier: a NaN is dropped (neither sent nor kept)
+    for (int g = 0; g + 1 < N; ++g) add_arrays(dst, p.slot[t->iter % 2][g] + b, en - b);
+    add_arrays_nan_to_zero(dst, dst, p.slot[t->iter % 2][N - 1] + b, en - b);
     t->stat_end("CRIT_PATH_gather");
     e.schedule_after_barrier(e.module("Compress"), t, kAfterGather);
   }
@@ -123,7 +120,7 @@ class ModuleCompress : public Module {
     }
     auto& p = e.param(t->param_index);
     const int W = e.options().world;
-    float* acc = p.slot[t->iter % 2][0];                         // NaN already dropped by the gather stage
+    float* acc = p.resid;                                        // gradient sum plus residual, NaN dropped, left by the gather stage
     const uint32_t k = entries_for(p.numel, t->ratio, W);
     t->k = k;
     t->idx.assign(static_cast<size_t>(k) * W, 0xFFFFFFFFu);
@@ -152,8 +149,7 @@ class ModuleCompress : public Module {
         t->val[j] = s;
       }
     }
-    std::memcpy(p.resid, acc, static_cast<size_t>(p.numel) * sizeof(float));
-    t->stat_end("CRIT_PATH_save_residual");
+    t->stat_end("CRIT_PATH_save_residual");      // what was not sent already sits in the residual
     if (W == 1) e.schedule_after_master_free(e.module("Optimize"), t);
     else e.schedule(e.module("GradExchange"), t);
   }
