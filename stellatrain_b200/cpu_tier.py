@@ -333,6 +333,9 @@ class CpuTierTelemetry:
         self._lock = threading.Lock()
         self._prev_end: Optional[float] = None
         self._prev_bytes = engine.engine.comm_bytes()
+        from .parallel.telemetry import _WeakInstruction
+
+        self._callback = _WeakInstruction(self)
         self.client = None
         if uri:
             ext = _load()
@@ -400,7 +403,7 @@ class CpuTierTelemetry:
                              "grad_send_thpt_mbps": send, "grad_recv_thpt_mbps": recv}
                 if self.client is not None and self.client.alive():
                     cfg = self._TrainConfig(self.batch_size, self.engine.grad_accumulation, self.ratio)
-                    self.client.report(self.iteration, cfg, [send, recv, fwd, bwd, gap, 0.0], self._on_instruction)
+                    self.client.report(self.iteration, cfg, [send, recv, fwd, bwd, gap, 0.0], self._callback)
                 self.iteration += 1
 
         return _ctx()

@@ -39,12 +39,13 @@ static bool recv_msg(int fd, uint32_t* type, std::vector<unsigned char>* payload
 
 TelemetryClient::TelemetryClient(const std::string& uri, uint32_t gpu_id, const std::string& gpu_name, uint32_t rank,
                                  uint32_t local_rank, int timeout_ms)
-    : gpu_id_(gpu_id), timeout_ms_(timeout_ms) {
+    : st_(std::make_shared<State>()), gpu_id_(gpu_id) {
+  st_->timeout_ms = timeout_ms;
   std::string host;
   uint16_t port;
   if (!parse_uri(uri, &host, &port)) throw std::invalid_argument("bad telemetry uri: " + uri);
-  fd_ = tcp_connect(host, port, timeout_ms);
-  if (fd_ < 0) throw std::runtime_error("telemetry: cannot reach the controller at " + uri);
+  st_->fd = tcp_connect(host, port, timeout_ms);
+  if (st_->fd < 0) throw std::runtime_error("telemetry: cannot reach the controller at " + uri);
   LocalTelemetryInit init{};
   init.gpu_id = gpu_id;
   init.rank = rank;
@@ -52,18 +53,24 @@ TelemetryClient::TelemetryClient(const std::string& uri, uint32_t gpu_id, const 
   std::strncpy(init.gpu_name, gpu_name.c_str(), sizeof(init.gpu_name) - 1);
   uint32_t type;
   std::vector<unsigned char> reply;
-  if (!send_msg(fd_, kTelLocalInit, &init, sizeof(init), timeout_ms) || !recv_msg(fd_, &type, &reply, timeout_ms)) {
-    close_fd(fd_);
+  if (!send_msg(st_->fd, kTelLocalInit, &init, sizeof(init), timeout_ms) || !recv_msg(st_->fd, &type, &reply, timeout_ms)) {
+    close_fd(st_->fd);
     throw std::runtime_error("telemetry: the controller did not acknowledge the registration");
   }
-  worker_ = std::thread([this] { worker_main(); });
+  worker_ = std::thread(worker_main, st_);
 }
 
 TelemetryClient::~TelemetryClient() {
-  stop_ = true;
-  cv_.notify_all();
-  if (worker_.joinable()) worker_.join();
-  close_fd(fd_);
+  st_->stop = true;
+  st_->cv.notify_all();
+  if (worker_.joinable()) {
+    if (worker_.get_id() == std::this_thread::get_id()) {
+      worker_.detach();          // destroyed from the worker itself (see State): it closes the socket on its way out
+      return;
+    }
+    worker_.join();
+  }
+  close_fd(st_->fd);
 }
 
 void TelemetryClient::report(uint64_t uiter, const TrainConfig& cfg, const TrainMeasurement& m, InstructionCallback cb) {
@@ -73,44 +80,57 @@ void TelemetryClient::report(uint64_t uiter, const TrainConfig& cfg, const Train
   t.config = cfg;
   t.measurement = m;
   {
-    std::lock_guard<std::mutex> lk(mu_);
-    if (queue_.size() > 4096) queue_.pop_front();   // a stalled controller must not grow memory
-    queue_.emplace_back(t, std::move(cb));
+    std::lock_guard<std::mutex> lk(st_->mu);
+    if (st_->queue.size() > 4096) st_->queue.pop_front();   // a stalled controller must not grow memory
+    st_->queue.emplace_back(t, std::move(cb));
   }
-  cv_.notify_one();
+  st_->cv.notify_one();
 }
 
 size_t TelemetryClient::queued() {
-  std::lock_guard<std::mutex> lk(mu_);
-  return queue_.size();
+  std::lock_guard<std::mutex> lk(st_->mu);
+  return st_->queue.size();
 }
 
-void TelemetryClient::worker_main() {
+void TelemetryClient::worker_main(std::shared_ptr<State> st) {
   pthread_setname_np(pthread_self(), "TelemetryClient");
-  while (!stop_) {
-    std::pair<LocalTelemetry, InstructionCallback> item;
+  bool detached = false;
+  while (!st->stop) {
     {
-      std::unique_lock<std::mutex> lk(mu_);
-      cv_.wait_for(lk, std::chrono::milliseconds(100), [this] { return stop_ || !queue_.empty(); });
-      if (stop_) return;
-      if (queue_.empty()) continue;
-      item = std::move(queue_.front());
-      queue_.pop_front();
-    }
-    uint32_t type;
-    std::vector<unsigned char> reply;
-    if (!send_msg(fd_, kTelLocal, &item.first, sizeof(item.first), timeout_ms_) || !recv_msg(fd_, &type, &reply, timeout_ms_)) {
-      LOG_WARN("TelemetryClient", "controller connection lost; telemetry stops, training continues");
-      dead_ = true;
-      return;
-    }
-    ++sent_;
-    if (type == kTelInstruction && reply.size() == sizeof(Instruction) && item.second) {
-      Instruction ins;
-      std::memcpy(&ins, reply.data(), sizeof(ins));
-      item.second(ins.iter_effective_since, ins.config);
-    }
+      std::pair<LocalTelemetry, InstructionCallback> item;
+      {
+        std::unique_lock<std::mutex> lk(st->mu);
+        st->cv.wait_for(lk, std::chrono::milliseconds(100), [&st] { return st->stop || !st->queue.empty(); });
+        if (st->stop) break;
+        if (st->queue.empty()) continue;
+        item = std::move(st->queue.front());
+        st->queue.pop_front();
+      }
+      uint32_t type;
+      std::vector<unsigned char> reply;
+      if (!send_msg(st->fd, kTelLocal, &item.first, sizeof(item.first), st->timeout_ms) ||
+          !recv_msg(st->fd, &type, &reply, st->timeout_ms)) {
+        LOG_WARN("TelemetryClient", "controller connection lost; telemetry stops, training continues");
+        st->dead = true;
+        break;
+      }
+      ++st->sent;
+      if (type == kTelInstruction && reply.size() == sizeof(Instruction) && item.second) {
+        Instruction ins;
+        std::memcpy(&ins, reply.data(), sizeof(ins));
+        item.second(ins.iter_effective_since, ins.config);
+      }
+    }   // the callback is released here, which may destroy the client on this very thread
+    if (st->stop && st.use_count() == 1) detached = true;
   }
+  // queued callbacks may own the client as well: release them before deciding who closes the socket
+  std::deque<std::pair<LocalTelemetry, InstructionCallback>> rest;
+  {
+    std::lock_guard<std::mutex> lk(st->mu);
+    rest.swap(st->queue);
+  }
+  rest.clear();
+  if (detached || st.use_count() == 1) close_fd(st->fd);   // the client is gone and could not close it itself
 }
 
 TelemetryServer::TelemetryServer(const std::string& uri, bool launch_controller, int timeout_ms) : timeout_ms_(timeout_ms) {

@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <deque>
 #include <functional>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <thread>
@@ -65,20 +66,27 @@ class TelemetryClient {
   // Non-blocking: queues one report; `cb` runs on the client's thread if the reply is an instruction.
   void report(uint64_t uiter, const TrainConfig& cfg, const TrainMeasurement& m, InstructionCallback cb = nullptr);
   size_t queued();
-  uint64_t sent() const { return sent_; }
-  bool alive() const { return !dead_; }
+  uint64_t sent() const { return st_->sent; }
+  bool alive() const { return !st_->dead; }
 
  private:
-  void worker_main();
-  int fd_ = -1;
+  // Everything the worker thread touches lives in a block that the thread shares with this object.  A callback may
+  // hold the last reference to whatever owns this client (a Python hook whose bound method was passed to report());
+  // when the worker releases that callback, this object is destroyed ON the worker thread.  The destructor then cannot
+  // join the thread it runs on: it lets the thread go, and the thread finishes on the shared block alone.
+  struct State {
+    int fd = -1;
+    int timeout_ms = 5000;
+    std::mutex mu;
+    std::condition_variable cv;
+    std::deque<std::pair<LocalTelemetry, InstructionCallback>> queue;
+    std::atomic<bool> stop{false}, dead{false};
+    std::atomic<uint64_t> sent{0};
+  };
+  static void worker_main(std::shared_ptr<State> st);
+  std::shared_ptr<State> st_;
   uint32_t gpu_id_;
-  int timeout_ms_;
   std::thread worker_;
-  std::mutex mu_;
-  std::condition_variable cv_;
-  std::deque<std::pair<LocalTelemetry, InstructionCallback>> queue_;
-  std::atomic<bool> stop_{false}, dead_{false};
-  std::atomic<uint64_t> sent_{0};
 };
 
 class TelemetryServer {

@@ -36,6 +36,7 @@ class TelemetryHook:
         self.applied: List[Tuple[int, int, float]] = []
         self.lock = threading.Lock()
         self.client = None
+        self._callback = _WeakInstruction(self)
         self._ev = {k: torch.cuda.Event(enable_timing=True) for k in ("f0", "f1", "b1", "prev_b1")}
         self._have_prev = False
         self.last: Dict[str, float] = {}
@@ -140,8 +141,23 @@ class TelemetryHook:
                          "grad_send_thpt_mbps": mbps, "grad_recv_thpt_mbps": mbps}
             if self.client is not None and self.client.alive():
                 cfg = self._TrainConfig(self.batch_size, self.engine.cfg.grad_accumulation, self.engine.cfg.ratio)
-                self.client.report(self.iteration, cfg, [mbps, mbps, fwd, bwd, gap, 0.0], self._on_instruction)
+                self.client.report(self.iteration, cfg, [mbps, mbps, fwd, bwd, gap, 0.0], self._callback)
             self.iteration += 1
+
+
+class _WeakInstruction:
+    """Callback handed to the native client: holds the hook weakly, so that reports still queued in the client's
+    thread never keep the hook (and through it the client itself) alive."""
+
+    def __init__(self, hook) -> None:
+        import weakref
+
+        self._ref = weakref.ref(hook)
+
+    def __call__(self, since: int, ubatch: int, grad_acc: int, ratio: float) -> None:
+        hook = self._ref()
+        if hook is not None:
+            hook._on_instruction(since, ubatch, grad_acc, ratio)
 
 
 class _BackwardStart:

@@ -314,3 +314,37 @@ def test_profile_converter_on_published_profiles(name):
     np.testing.assert_allclose(fit, y, atol=1e-6)
     assert prof.meta.bandwidth == 1.0 and prof.meta.compression == 0.9 and prof.meta.max_batch_size in (1024.0, 2048.0)
     assert np.isfinite(prof.h(prof.meta.batch_size, 1.0)).all()
+
+
+def test_client_may_be_destroyed_from_its_own_thread():
+    """A callback can own the client (a bound method of the object that holds it).  When the reports still queued in the
+    client's thread are the last owners, the client is destroyed on that thread; it must let the thread go instead of
+    joining itself (which ends the process with 'Resource deadlock avoided')."""
+    import gc
+
+    from stellatrain_b200 import cpu_tier
+
+    ext = cpu_tier._load()
+    ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
+    try:
+        class Holder:
+            def __init__(self):
+                self.client = ext.TelemetryClient(f"127.0.0.1:{ctl.port}", 0, "cpu", 0, 0, 2000)
+                self.seen = 0
+
+            def on_instruction(self, since, ubatch, grad_acc, ratio):
+                self.seen += 1
+
+        for _ in range(5):
+            h = Holder()
+            for i in range(300):
+                h.client.report(i, ext.TrainConfig(4, 1, 0.9), [0, 0, 1, 2, 0, 0], h.on_instruction)
+            del h                                       # the queue inside the client's thread now owns the holder
+            gc.collect()
+        time.sleep(1.0)
+        deadline = time.time() + 10
+        while ctl.latest_iter < 250 and time.time() < deadline:
+            time.sleep(0.05)
+        assert ctl.latest_iter >= 250
+    finally:
+        ctl.close()
