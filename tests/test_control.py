@@ -303,7 +303,9 @@ def test_profile_converter_on_published_profiles(name):
 
     from stellatrain_b200.control import convert_profile as C
 
-    src = Path(os.environ.get("STELLATRAIN_REFERENCE", "/root/reference")) / "bayesian" / "profile" / f"{name}.pkl"
+    here = Path(__file__).resolve().parent.parent
+    tree = Path(os.environ.get("STELLATRAIN_REFERENCE") or here.parent / "reference")    # named, else beside this repository
+    src = tree / "bayesian" / "profile" / f"{name}.pkl"
     if not src.exists():
         pytest.skip("upstream profiles not available")
     rec = C.read_records(str(src))

@@ -12,7 +12,8 @@ import pytest
 import torch
 
 ROOT = Path(__file__).resolve().parent.parent
-REF_TREE = Path(os.environ.get("STELLATRAIN_REFERENCE", "/root/reference"))
+# the upstream tree: named by the environment, else a checkout called "reference" beside this repository
+REF_TREE = Path(os.environ.get("STELLATRAIN_REFERENCE") or ROOT.parent / "reference")
 
 
 @pytest.fixture(scope="module")
