@@ -410,6 +410,7 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def_readwrite("ubatch_size", &TrainConfig::ubatch_size)
       .def_readwrite("gradient_accumulation", &TrainConfig::gradient_accumulation)
       .def_readwrite("compression_rate", &TrainConfig::compression_rate);
+  m.def("telemetry_clients_destroyed_on_own_thread", &TelemetryClient::destroyed_on_own_thread);
   py::class_<TelemetryClient>(m, "TelemetryClient")
       .def(py::init<const std::string&, uint32_t, const std::string&, uint32_t, uint32_t, int>(), py::arg("uri"), py::arg("gpu_id"),
            py::arg("gpu_name"), py::arg("rank"), py::arg("local_rank"), py::arg("timeout_ms") = 5000,

@@ -60,11 +60,17 @@ TelemetryClient::TelemetryClient(const std::string& uri, uint32_t gpu_id, const 
   worker_ = std::thread(worker_main, st_);
 }
 
+namespace {
+std::atomic<uint64_t> g_destroyed_on_own_thread{0};
+}
+uint64_t TelemetryClient::destroyed_on_own_thread() { return g_destroyed_on_own_thread.load(); }
+
 TelemetryClient::~TelemetryClient() {
   st_->stop = true;
   st_->cv.notify_all();
   if (worker_.joinable()) {
     if (worker_.get_id() == std::this_thread::get_id()) {
+      ++g_destroyed_on_own_thread;
       worker_.detach();          // destroyed from the worker itself (see State): it closes the socket on its way out
       return;
     }

@@ -68,6 +68,8 @@ class TelemetryClient {
   size_t queued();
   uint64_t sent() const { return st_->sent; }
   bool alive() const { return !st_->dead; }
+  // How many clients of this process were destroyed on their own worker thread so far (see State below); for tests.
+  static uint64_t destroyed_on_own_thread();
 
  private:
   // Everything the worker thread touches lives in a block that the thread shares with this object.  A callback may

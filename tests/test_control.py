@@ -329,6 +329,8 @@ def test_client_may_be_destroyed_from_its_own_thread():
     ext = cpu_tier._load()
     ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
     try:
+        before = ext.telemetry_clients_destroyed_on_own_thread()
+
         class Holder:
             def __init__(self):
                 self.client = ext.TelemetryClient(f"127.0.0.1:{ctl.port}", 0, "cpu", 0, 0, 2000)
@@ -348,5 +350,9 @@ def test_client_may_be_destroyed_from_its_own_thread():
         while ctl.latest_iter < 250 and time.time() < deadline:
             time.sleep(0.05)
         assert ctl.latest_iter >= 250
+        deadline = time.time() + 30
+        while ext.telemetry_clients_destroyed_on_own_thread() == before and time.time() < deadline:
+            time.sleep(0.1)
+        assert ext.telemetry_clients_destroyed_on_own_thread() > before      # the situation did arise
     finally:
         ctl.close()
