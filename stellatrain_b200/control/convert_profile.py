@@ -78,6 +78,17 @@ _NUMPY_OK = {
 }
 
 
+def _safe_scalar(dtype: Any, data: Any) -> Any:
+    """numpy's scalar constructor, refused for object dtypes: for those numpy itself unpickles ``data`` with the
+    ordinary, unrestricted unpickler."""
+    dt = np.dtype(dtype)
+    if dt.hasobject or not isinstance(data, (bytes, bytearray)):
+        raise pickle.UnpicklingError("object-typed numpy scalars are not read")
+    import numpy._core.multiarray as multiarray
+
+    return multiarray.scalar(dt, bytes(data))
+
+
 class _SafeUnpickler(pickle._Unpickler):  # the pure-Python implementation: its dispatch table can be extended
     def __init__(self, file: io.BufferedIOBase) -> None:
         super().__init__(file)
@@ -85,6 +96,8 @@ class _SafeUnpickler(pickle._Unpickler):  # the pure-Python implementation: its 
 
     def find_class(self, module: str, name: str) -> Any:
         if (module, name) in _NUMPY_OK:
+            if name == "scalar":
+                return _safe_scalar
             if "multiarray" in module:
                 import numpy._core.multiarray as multiarray
 

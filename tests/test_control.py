@@ -356,3 +356,35 @@ def test_client_may_be_destroyed_from_its_own_thread():
         assert ext.telemetry_clients_destroyed_on_own_thread() > before      # the situation did arise
     finally:
         ctl.close()
+
+
+def test_profile_reader_refuses_the_numpy_scalar_detour(tmp_path):
+    """numpy's scalar constructor unpickles its payload itself when the dtype is object: a pickle can smuggle a second,
+    unrestricted pickle through it.  The reader refuses object-typed scalars and still reads ordinary ones."""
+    import pickle
+
+    from stellatrain_b200.control import convert_profile as C
+
+    marker = tmp_path / "ran"
+
+    class Inner:
+        def __reduce__(self):
+            return (open, (str(marker), "w"))
+
+    inner = pickle.dumps(Inner())
+
+    class Outer:
+        def __reduce__(self):
+            import numpy._core.multiarray as ma
+
+            return (ma.scalar, (np.dtype("O"), inner))
+
+    bad = tmp_path / "bad.pkl"
+    bad.write_bytes(pickle.dumps({"models": [Outer()]}))
+    with pytest.raises(pickle.UnpicklingError):
+        C.read_records(str(bad))
+    assert not marker.exists()
+    good = tmp_path / "good.pkl"
+    good.write_bytes(pickle.dumps({"x": np.float64(2.5), "n": np.int32(7)}))
+    rec = C.read_records(str(good))
+    assert float(rec["x"]) == 2.5 and int(rec["n"]) == 7
