@@ -240,6 +240,26 @@ class CpuOffloadEngine:
     def barrier(self) -> None:
         self.engine.barrier()
 
+    # the calls the ``fasterdp``-named frontend makes on whichever engine is attached
+    def set_compression_ratio(self, ratio: float) -> None:
+        self.engine.configure_compression_ratio(float(ratio))
+        self._meta["ratio"] = float(ratio)
+
+    def configure_optimizer(self, **options) -> None:
+        for k, v in options.items():
+            self.engine.configure_optimizer(k, v)
+            self._meta["optimizer_options"][k] = v
+
+    def replica_drift(self) -> float:
+        """Largest difference between this node's master copy and node 0's (0.0 on one node)."""
+        self.synchronize()
+        return max((self.engine.force_model_sync(i, True) for i in range(len(self.params))), default=0.0)
+
+    def broadcast_parameters(self) -> None:
+        self.synchronize()
+        for i in range(len(self.params)):
+            self.engine.force_model_sync(i, False)
+
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self) -> dict:
         """Everything a later run needs to continue bit for bit, in torch's plain-container form (``torch.save``-able):

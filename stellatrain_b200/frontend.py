@@ -59,8 +59,17 @@ def global_world() -> int:
 def configure(master_addr: str, master_port: int, world_size: int, rank: int, local_session_id: int,
               local_world_size: int = 1, local_rank: int = 0, method: str = "thresholdv16",
               gradient_accumulation: int = 1, *, backend: Optional[str] = None, staleness: Optional[int] = None,
-              transport: Optional[str] = None, timeout_s: float = 600.0) -> None:
-    """Bind the process to its GPU and join the job (backend/src/engine/core.cpp:64-183)."""
+              transport: Optional[str] = None, timeout_s: float = 600.0, tier: Optional[str] = None) -> None:
+    """Bind the process to its GPU and join the job (backend/src/engine/core.cpp:64-183).
+
+    ``tier="cpu"`` selects the CPU-offload tier: the same calls then drive the native host pipeline (pinned shared
+    memory, gather, compress, TCP ring between nodes, sparse optimiser) with the reference's meaning of the arguments:
+    ``world_size`` nodes of ``local_world_size`` processes each.  That tier brings its own transport, so no
+    ``torch.distributed`` group is created."""
+    if tier is not None:
+        if tier not in ("gpu", "cpu"):
+            raise ValueError("tier must be 'gpu' or 'cpu'")
+        _S.tier = tier
     if method and method not in _COMPRESSORS:
         raise ValueError(f"unknown compression method {method!r}")
     _S.master_addr, _S.master_port = master_addr, int(master_port)
@@ -77,7 +86,7 @@ def configure(master_addr: str, master_port: int, world_size: int, rank: int, lo
     use_cuda = torch.cuda.is_available()
     if use_cuda:
         torch.cuda.set_device(_S.local_rank % torch.cuda.device_count())
-    if global_world() > 1 and not dist.is_initialized():
+    if _S.tier == "gpu" and global_world() > 1 and not dist.is_initialized():
         be = backend or ("nccl" if use_cuda else "gloo")
         kwargs = {}
         if be == "nccl":
@@ -168,6 +177,17 @@ def attach(module: torch.nn.Module, **overrides) -> SparseDPEngine:
     cfg = _S.engine_cfg
     for k, v in overrides.items():
         setattr(cfg, k, v)
+    if _S.tier == "cpu":
+        from .cpu_tier import CpuOffloadEngine
+
+        _S.engine = CpuOffloadEngine(
+            module, master_addr=_S.master_addr, master_port=_S.master_port, world_size=_S.world_size, rank=_S.rank,
+            session=_S.session_id, local_world_size=_S.local_world_size, local_rank=_S.local_rank, method=cfg.compressor,
+            gradient_accumulation=cfg.grad_accumulation, staleness=cfg.staleness, ratio=cfg.ratio, optimizer=cfg.optimizer,
+            optimizer_options=dict(cfg.optimizer_options), timeout_ms=max(30000, int(cfg.timeout_s * 1000)),
+            debug_accuracy=_S.debug_accuracy)
+        _S.pending_params.clear()
+        return _S.engine
     _S.engine = SparseDPEngine(module, cfg)
     _S.pending_params.clear()
     return _S.engine
@@ -194,7 +214,7 @@ def pre_forward_process(layer_idx: int, name: str) -> None:
     """Make the compute stream wait for the update the coming forward must see
     (backend/src/engine/core.cpp:712-758); the wait is an event on the stream, the host never blocks."""
     eng = _S.engine
-    if eng is None:
+    if eng is None or _S.tier == "cpu":      # the CPU tier waits in its own forward hook
         return
     cur = torch.cuda.current_stream(eng.device)
     for rt in eng.buckets:

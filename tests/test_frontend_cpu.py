@@ -138,6 +138,41 @@ def test_train_driver_real_dataset_through_a_loader_process(tmp_path):
     assert "done: 4 iterations" in out.stdout               # 8 listed images, batches of 2
 
 
+def test_fasterdp_named_calls_drive_the_cpu_tier(tmp_path):
+    """The reference's call sequence (configure, ratio, optimiser, wrapper, loader, backward, synchronize) with
+    tier="cpu": the native host pipeline does the update."""
+    script = tmp_path / "run.py"
+    script.write_text("""
+import os, torch, torchvision, torch.nn.functional as F
+import stellatrain_b200 as fasterdp
+fasterdp.configure("127.0.0.1", 5555, 1, 0, os.getpid(), 1, 0, "thresholdv16", 2, tier="cpu")
+fasterdp.configure_compression_ratio(0.9)
+fasterdp.set_optimizer("adam"); fasterdp.configure_optimizer("lr", 1e-2)
+torch.manual_seed(0)
+model = fasterdp.FasterDpModelWrapper(torchvision.models.resnet18(num_classes=10))
+before = [p.detach().clone() for p in model.parameters()]
+x, y = torch.randn(8, 3, 32, 32), torch.randint(0, 10, (8,))
+losses = []
+for _ in range(6):
+    for xb, yb in fasterdp.StellaTrainDataLoader([(x, y)]):       # two micro-batches of four
+        loss = F.cross_entropy(model(xb), yb); loss.backward(); losses.append(float(loss.detach()))
+fasterdp.synchronize()
+assert type(model.engine).__name__ == "CpuOffloadEngine"
+assert any(not torch.equal(a, b.detach()) for a, b in zip(before, model.parameters()))
+assert losses[-1] < losses[0], losses
+assert model.step() is None or True
+fasterdp.configure_compression_ratio(0.8)                          # reaches the running engine
+assert abs(model.engine.engine.compression_ratio_at(10**6) - 0.8) < 1e-9
+sd = model.engine.state_dict(); assert set(sd) == {"model", "optimizer", "sparsifier", "engine"}
+fasterdp.detach()
+print("ok", losses[0], losses[-1])
+""")
+    out = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=300,
+                         env={**__import__("os").environ, "PYTHONPATH": str(__import__("pathlib").Path(__file__).resolve().parent.parent)})
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.strip().splitlines()[-1].startswith("ok")
+
+
 def test_reference_arm_reports_unavailable():
     import json
 
