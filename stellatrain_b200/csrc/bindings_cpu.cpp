@@ -411,7 +411,15 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def_readwrite("gradient_accumulation", &TrainConfig::gradient_accumulation)
       .def_readwrite("compression_rate", &TrainConfig::compression_rate);
   m.def("telemetry_clients_destroyed_on_own_thread", &TelemetryClient::destroyed_on_own_thread);
-  py::class_<TelemetryClient>(m, "TelemetryClient")
+  // The destructor joins the client's thread, and that thread takes the interpreter lock whenever it calls or releases a
+  // Python callback: destroying the client with the lock held would wait for a thread that waits for the lock.
+  struct DeleteWithoutGil {
+    void operator()(TelemetryClient* c) const {
+      py::gil_scoped_release rel;
+      delete c;
+    }
+  };
+  py::class_<TelemetryClient, std::unique_ptr<TelemetryClient, DeleteWithoutGil>>(m, "TelemetryClient")
       .def(py::init<const std::string&, uint32_t, const std::string&, uint32_t, uint32_t, int>(), py::arg("uri"), py::arg("gpu_id"),
            py::arg("gpu_name"), py::arg("rank"), py::arg("local_rank"), py::arg("timeout_ms") = 5000,
            py::call_guard<py::gil_scoped_release>())

@@ -388,3 +388,22 @@ def test_profile_reader_refuses_the_numpy_scalar_detour(tmp_path):
     good.write_bytes(pickle.dumps({"x": np.float64(2.5), "n": np.int32(7)}))
     rec = C.read_records(str(good))
     assert float(rec["x"]) == 2.5 and int(rec["n"]) == 7
+
+
+def test_client_destroyed_with_callbacks_still_queued_does_not_wait_for_itself():
+    """Dropping the client on the Python thread while its thread still holds Python callbacks: the destructor joins
+    that thread, which needs the interpreter lock to release the callbacks, so the lock must not be held meanwhile."""
+    from stellatrain_b200 import cpu_tier
+
+    ext = cpu_tier._load()
+    ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
+    try:
+        t0 = time.time()
+        for _ in range(10):
+            c = ext.TelemetryClient(f"127.0.0.1:{ctl.port}", 0, "cpu", 0, 0, 2000)
+            for i in range(200):
+                c.report(i, ext.TrainConfig(4, 1, 0.9), [0, 0, 1, 2, 0, 0], lambda *a: None)
+            del c
+        assert time.time() - t0 < 30
+    finally:
+        ctl.close()
