@@ -2,7 +2,7 @@
 
 Runs the unmodified reference (kaist-ina/stellatrain, built out of tree into ``baseline/_ref``) through its own
 public API, the way its driver does (backend/test/test_end_to_end.py:15-85): ``fasterdp.configure`` with the
-``thresholdv16`` compressor, ``configure_compression_ratio``, ``FasterDpModelWrapper`` around the torchvision model,
+``thresholdv16`` compressor (or another one it accepts), ``configure_compression_ratio``, ``FasterDpModelWrapper`` around the torchvision model,
 ``set_optimizer`` / ``configure_optimizer``, ``StellaTrainDataLoader`` around the batches, forward, cross entropy,
 backward, and ``fasterdp.synchronize`` at the end.  Nothing of this package is imported here.
 
@@ -30,6 +30,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--num-classes", type=int, default=100)
     ap.add_argument("--ratio", type=float, default=0.99)
+    ap.add_argument("--method", default="thresholdv16", help="compressor name given to fasterdp.configure")
     ap.add_argument("--optimizer", default="adam")
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--momentum", type=float, default=0.0)
@@ -46,7 +47,7 @@ def main() -> None:
     from model_wrapper import FasterDpModelWrapper, StellaTrainDataLoader   # the reference's frontend
 
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    fasterdp.configure("127.0.0.1", a.port, 1, 0, a.session, a.local_world, a.local_rank, "thresholdv16", 1)
+    fasterdp.configure("127.0.0.1", a.port, 1, 0, a.session, a.local_world, a.local_rank, a.method, 1)
     torch.cuda.set_device(a.local_rank)
     fasterdp.configure_compression_ratio(a.ratio)
 

@@ -152,9 +152,10 @@ def run_reference_arm(args: argparse.Namespace) -> None:
         unavailable(REFERENCE_UNAVAILABLE + "; no out-of-tree build under baseline/_ref either")
         return
     lm = args.model.startswith("gpt")
-    if lm or args.amp != "none" or args.compressor != "thresholdv16":
-        unavailable("the reference's driver path is torchvision models in fp32 with its thresholdv16 compressor "
-                    "(backend/test/test_end_to_end.py:21-45); this configuration is outside it")
+    if lm or args.amp != "none" or args.compressor not in ("thresholdv16", "thresholdv", "topk"):
+        unavailable("the reference's driver path is torchvision models in fp32 with one of its compressors thresholdv16, "
+                    "thresholdv, topk (backend/test/test_end_to_end.py:21-45, backend/src/engine/core.cpp:110-118); this "
+                    "configuration is outside it")
         return
     try:
         import torch
@@ -184,7 +185,7 @@ def run_reference_arm(args: argparse.Namespace) -> None:
             [sys.executable, os.path.join(here, "baseline", "reference_arm.py"), "--ref-dir", ref_dir, "--local-rank", str(lr),
              "--local-world", str(world), "--session", str(session), "--port", str(port), "--model", args.model,
              "--batch", str(args.batch), "--num-classes", str(args.num_classes), "--ratio", str(args.ratio),
-             "--optimizer", args.optimizer, "--lr", str(args.lr), "--momentum", str(args.momentum),
+             "--optimizer", args.optimizer, "--lr", str(args.lr), "--momentum", str(args.momentum), "--method", args.compressor,
              "--steps", str(args.steps), "--warmup", str(max(3, args.warmup))],
             stdout=log, stderr=subprocess.STDOUT, env=env, start_new_session=True))
     deadline = time.time() + float(os.environ.get("REFERENCE_ARM_TIMEOUT_S", "330"))
@@ -229,14 +230,14 @@ def run_reference_arm(args: argparse.Namespace) -> None:
     value = args.batch * world / (per_step / 1e3)
     h2d = args.batch * 3 * 224 * 224 * 4 + args.batch * 8
     out = {
-        "metric": f"{args.model} training throughput, sparse data parallel (thresholdv16 keeping {(1 - args.ratio) * 100:g}% of "
+        "metric": f"{args.model} training throughput, sparse data parallel ({args.compressor} keeping {(1 - args.ratio) * 100:g}% of "
                   f"gradient entries, error feedback, sparse {args.optimizer})",
         "impl": "reference", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32 (torch defaults: TF32 cuDNN convolutions)",
         "data": "synthetic N(0,1) images / uniform labels, random-init weights",
         "config": {"model": args.model, "global_batch": args.batch * world, "per_gpu_batch": args.batch, "seq_len": None,
-                   "parallelism": f"dp{world}", "compressor": "thresholdv16", "kept_fraction": 1 - args.ratio,
+                   "parallelism": f"dp{world}", "compressor": args.compressor, "kept_fraction": 1 - args.ratio,
                    "optimizer": args.optimizer, "lr": args.lr, "staleness": 1,
                    "transport": "reference: one node, pinned shared memory, CPU pipeline",
                    "build": "unmodified sources, CMake RelWithDebInfo, out of tree (baseline/build_reference.sh)",
