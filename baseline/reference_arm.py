@@ -2,8 +2,8 @@
 
 Runs the unmodified reference (kaist-ina/stellatrain, built out of tree into ``baseline/_ref``) through its own
 public API, the way its driver does (backend/test/test_end_to_end.py:15-85): ``fasterdp.configure`` with the
-``thresholdv16`` compressor (or another one it accepts), ``configure_compression_ratio``, ``FasterDpModelWrapper`` around the torchvision model,
-``set_optimizer`` / ``configure_optimizer``, ``StellaTrainDataLoader`` around the batches, forward, cross entropy,
+``thresholdv16`` compressor (or another one it accepts), ``configure_compression_ratio``,
+``FasterDpModelWrapper`` around the torchvision model, ``set_optimizer`` / ``configure_optimizer``, ``StellaTrainDataLoader`` around the batches, forward, cross entropy,
 backward, and ``fasterdp.synchronize`` at the end.  Nothing of this package is imported here.
 
 One node (``WORLD_SIZE=1``) with ``--local-world`` processes, one per GPU, which is the reference's single-machine
