@@ -21,3 +21,12 @@ from .models.wrapper import FasterDpModelWrapper, SparseDPModelWrapper, to_seque
 from .parallel.engine import EngineConfig, SparseDPEngine  # noqa: F401
 from .parallel.gpu_bucket import SparseStepError  # noqa: F401
 from .utils.loader import StellaTrainDataLoader  # noqa: F401
+
+
+def __getattr__(name: str):
+    # the CPU-offload tier is imported on first use: its native module is not needed by GPU-only runs
+    if name in ("CpuOffloadEngine", "CpuTierTelemetry"):
+        from . import cpu_tier
+
+        return getattr(cpu_tier, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
