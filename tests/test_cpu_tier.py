@@ -178,12 +178,12 @@ def test_paced_sends_hold_the_configured_rate():
         assert len(got) == 8
         sent = boxes[0].bytes_sent()
         assert sent > 8 * 32000
-        assert 0.7 * (sent - (16 << 10)) / 1e6 <= dt <= 2.5 * sent / 1e6, (dt, sent)     # ~0.26 s at 1 MB/s
+        assert 0.7 * (sent - (16 << 10)) / 1e6 <= dt <= 8 * sent / 1e6, (dt, sent)     # ~0.26 s at 1 MB/s; generous above for busy hosts
         boxes[0].set_tx_rate_limit(0.0)
         boxes[1].post_recv("fast")
         t1 = time.time()
         boxes[0].queue_tx(0, "fast", idx, val, 100000)
-        assert _wait_for(lambda: boxes[1].drain()) and time.time() - t1 < 0.2
+        assert _wait_for(lambda: boxes[1].drain()) and time.time() - t1 < 1.0
     finally:
         for b in boxes[::-1]:
             b.close()
