@@ -175,7 +175,7 @@ def build_selftest(sanitizer: str = "thread", out_dir: Path | None = None) -> Pa
     out_dir.mkdir(parents=True, exist_ok=True)
     flags = {"thread": ["-fsanitize=thread"], "address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"],
              "none": []}[sanitizer]
-    srcs = [s for s in EXTENSIONS["_Ccpu"]["cpp"] if not s.startswith("bindings") and not s.startswith("telemetry")]
+    srcs = [s for s in EXTENSIONS["_Ccpu"]["cpp"] if not s.startswith("bindings")]
     srcs.append("selftest/cpu_selftest.cpp")
     exe = out_dir / f"cpu_selftest_{sanitizer}"
     base = [f for f in CXX_FLAGS if f not in ("-O3", "-fvisibility=hidden")] + ["-O1", "-g", "-fno-omit-frame-pointer"]

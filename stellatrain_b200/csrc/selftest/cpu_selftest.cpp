@@ -21,6 +21,8 @@
 #include "../core/threadpool.h"
 #include "../cpu/compressors.h"
 #include "../cpu/optimizers.h"
+#include "../telemetry/telemetry.h"
+#include "../comm/net_util.h"
 
 using namespace stc;
 
@@ -190,6 +192,74 @@ void test_device_copies(int staleness) {
   if (!err.empty()) throw std::runtime_error("device copies, staleness " + std::to_string(staleness) + ": " + err);
 }
 
+// Telemetry client against a stand-in controller (a thread that acknowledges every frame and answers every fifth
+// report with an instruction): ordinary shutdown with reports still queued, and a client whose last owner is a
+// callback queued in its own thread, so that it is destroyed on that thread.
+void test_telemetry(uint16_t port) {
+  uint16_t bound = 0;
+  int lfd = tcp_listen(port, &bound, true);
+  CHECK(lfd >= 0);
+  std::atomic<bool> stop{false};
+  std::atomic<int> reports{0};
+  std::thread server([&] {
+    std::vector<std::thread> conns;
+    while (!stop) {
+      const int fd = tcp_accept(lfd, 100);
+      if (fd < 0) continue;
+      conns.emplace_back([fd, &stop, &reports] {
+        int cfd = fd;
+        while (!stop) {
+          if (!wait_readable(cfd, 100)) continue;
+          TelemetryFrame f;
+          if (!recv_all(cfd, &f, sizeof(f), 1000) || f.magic != kTelemetryMagic) break;
+          std::vector<unsigned char> payload(f.payload_len);
+          if (f.payload_len && !recv_all(cfd, payload.data(), f.payload_len, 1000)) break;
+          if (f.type == kTelLocal && ++reports % 5 == 0) {
+            Instruction ins{};
+            ins.iter_effective_since = 42;
+            ins.config = TrainConfig{8, 1, 0.95};
+            TelemetryFrame r{kTelemetryMagic, kTelInstruction, sizeof(ins)};
+            if (!send_all(cfd, &r, sizeof(r), 1000) || !send_all(cfd, &ins, sizeof(ins), 1000)) break;
+          } else {
+            TelemetryFrame r{kTelemetryMagic, kTelOk, 0};
+            if (!send_all(cfd, &r, sizeof(r), 1000)) break;
+          }
+        }
+        close_fd(cfd);
+      });
+    }
+    for (auto& c : conns) c.join();
+  });
+  const std::string uri = "127.0.0.1:" + std::to_string(bound);
+  std::atomic<int> instructions{0};
+  {
+    TelemetryClient client(uri, 0, "cpu", 0, 0, 2000);
+    for (int i = 0; i < 50; ++i)
+      client.report(i, TrainConfig{4, 1, 0.9}, TrainMeasurement{1, 1, 1, 1, 0, 0},
+                    [&instructions](uint64_t since, const TrainConfig& c) { if (since == 42 && c.ubatch_size == 8) ++instructions; });
+    const auto t0 = std::chrono::steady_clock::now();
+    while (client.sent() < 50 && std::chrono::steady_clock::now() - t0 < std::chrono::seconds(10))
+      std::this_thread::sleep_for(std::chrono::milliseconds(5));
+    CHECK(client.sent() == 50 && instructions == 10);
+    for (int i = 0; i < 200; ++i) client.report(100 + i, TrainConfig{4, 1, 0.9}, TrainMeasurement{}, nullptr);
+  }   // destroyed with reports still queued: joins its thread
+  const uint64_t before = TelemetryClient::destroyed_on_own_thread();
+  for (int round = 0; round < 3; ++round) {
+    auto owner = std::make_shared<std::unique_ptr<TelemetryClient>>(std::make_unique<TelemetryClient>(uri, 1, "cpu", 0, 1, 2000));
+    for (int i = 0; i < 100; ++i)
+      (*owner)->report(i, TrainConfig{4, 1, 0.9}, TrainMeasurement{}, [owner](uint64_t, const TrainConfig&) {});
+    owner.reset();   // the queued callbacks are now the only owners
+  }
+  const auto t1 = std::chrono::steady_clock::now();
+  while (TelemetryClient::destroyed_on_own_thread() < before + 3 && std::chrono::steady_clock::now() - t1 < std::chrono::seconds(20))
+    std::this_thread::sleep_for(std::chrono::milliseconds(10));
+  CHECK(TelemetryClient::destroyed_on_own_thread() == before + 3);
+  std::this_thread::sleep_for(std::chrono::milliseconds(200));   // the released threads finish on their shared blocks
+  stop = true;
+  server.join();
+  close_fd(lfd);
+}
+
 void test_two_nodes(uint16_t port) {
   Node nodes[2];
   std::string errs[2];
@@ -229,6 +299,7 @@ int main(int argc, char** argv) {
     test_device_copies(0);
     test_device_copies(1);
     test_two_nodes(port);
+    test_telemetry(static_cast<uint16_t>(port + 7));
   } catch (const std::exception& e) {
     std::fprintf(stderr, "selftest FAILED: %s\n", e.what());
     return 1;
