@@ -325,6 +325,7 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def("configure_wire", &CpuEngine::configure_wire, py::arg("blocks") = true, py::arg("value_format") = 0)
       .def("gradient_accumulation", &CpuEngine::gradient_accumulation)
       .def("is_debug_accuracy_mode", [](CpuEngine& e) { return e.options().debug_accuracy; })
+      .def("skips_critical_paths", [](CpuEngine& e) { return e.options().skip_critical_paths; })
       .def("barrier", &CpuEngine::barrier, py::call_guard<py::gil_scoped_release>())
       .def("synchronize", &CpuEngine::synchronize, py::call_guard<py::gil_scoped_release>())
       .def("pre_train_init", [](CpuEngine& e, int layer, const std::string& name, uint32_t numel, uint64_t user_param,

@@ -51,6 +51,7 @@ void CpuEngine::configure(const EngineOptions& o) {
   if (o.local_world < 1 || o.local_world > cfg::kMaxLocalRanks) throw std::invalid_argument("local_world out of range");
   if (o.staleness < 0 || o.staleness > 1) throw std::invalid_argument("staleness must be 0 or 1");
   opt_ = o;
+  if (cfg::env_long("STELLATRAIN_SKIP_CRITICAL_PATHS", 0) != 0) opt_.skip_critical_paths = true;
   {
     std::lock_guard<std::mutex> lk(ratio_mu_);
     ratio_ = o.ratio;

@@ -56,6 +56,11 @@ struct EngineOptions {
   bool pin_cuda = false;      // cudaHostRegister the data segment
   bool debug_accuracy = false;
   bool debug_barrier = false; // run the barrier self-check before the first task of every parameter
+  // Leave out the arithmetic of the critical path (gradient accumulation, selection, optimiser step) so that what
+  // remains is the cost of the pipeline itself: copies, barriers, scheduling, exchange of empty streams.  The
+  // reference has this as the compile-time switch SKIP_SOME_CRITICAL_PATHS (backend/src/engine/config.h:35-67).
+  // Also set by STELLATRAIN_SKIP_CRITICAL_PATHS=1.  Parameters do not change in this mode.
+  bool skip_critical_paths = false;
 };
 
 struct SharedParamEntry;       // row of the parameter table in shared memory

@@ -100,6 +100,10 @@ class ModuleGather : public Module {
     // into a gradient slot lets the compress stage work in place, so no copy back into the residual is needed afterwards
     // (the reference sums into slot 0 and copies the whole tensor back, cpu_gather.cpp:63-82, compress.cpp:172-188).
     float* dst = p.resid + b;
+    if (e.options().skip_critical_paths) {
+      e.schedule_after_barrier(e.module("Compress"), t, kAfterGather);
+      return;
+    }
     t->stat_start("CRIT_PATH_gather");
     // the last addition also applies the NaN policy shared with the GPU tier: a NaN is dropped (neither sent nor kept)
     for (int g = 0; g + 1 < N; ++g) add_arrays(dst, p.slot[t->iter % 2][g] + b, en - b);
@@ -127,7 +131,9 @@ class ModuleCompress : public Module {
     t->val.assign(static_cast<size_t>(k) * W, 0.f);
     t->counts.assign(W, 0);
     t->stat_start("CRIT_PATH_compress");
-    const size_t cnt = e.compressor().compress(t->persistent_key, acc, p.numel, k, t->idx.data(), t->val.data(), 0);
+    const size_t cnt = e.options().skip_critical_paths
+                           ? 0
+                           : e.compressor().compress(t->persistent_key, acc, p.numel, k, t->idx.data(), t->val.data(), 0);
     t->stat_end("CRIT_PATH_compress");
     t->counts[0] = cnt;
     if (e.options().debug_accuracy)

@@ -496,3 +496,33 @@ def test_ring_benchmark_smoke():
     pairs = R.run(nodes=2, gbps=0.0, steps=3, warmup=1, wire="pairs", sizes=sizes, ratio=0.9)
     blocks = R.run(nodes=2, gbps=0.0, steps=3, warmup=1, wire="blocks+bf16", sizes=sizes, ratio=0.9)
     assert pairs["ms_per_step"] > 0 and blocks["tx_bytes_per_step_per_node"] < 0.5 * pairs["tx_bytes_per_step_per_node"]
+
+
+def test_pipeline_overhead_mode_leaves_the_arithmetic_out():
+    """STELLATRAIN_SKIP_CRITICAL_PATHS=1: tasks run through every stage, barrier and copy, but nothing is accumulated,
+    selected or applied, so the parameters stay as they were and the run measures the pipeline alone."""
+    import subprocess
+    import sys
+
+    code = """
+import os, torch
+from stellatrain_b200 import cpu_tier
+ext = cpu_tier._load()
+eng = ext.CpuEngine()
+eng.configure("127.0.0.1", 5555, 1, 0, os.getpid(), 1, 0, "thresholdv16", 1, 1, 0.9, 8 << 20, 20000, 2, False, False, False)
+assert eng.skips_critical_paths()
+eng.set_optimizer("adam"); eng.configure_optimizer("lr", 1e-2)
+p = torch.full((5000,), 0.5)
+i = eng.pre_train_init(0, "p", p.numel(), p.data_ptr())
+for step in range(4):
+    eng.pre_forward_process(i)
+    g = torch.randn(5000)
+    eng.post_backward_process(i, g.data_ptr())
+eng.synchronize()
+assert eng.model_version(i) == 4 and bool((p == 0.5).all())
+print("ok")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120,
+                         env={**os.environ, "STELLATRAIN_SKIP_CRITICAL_PATHS": "1", "PYTHONPATH": root})
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-1500:]
