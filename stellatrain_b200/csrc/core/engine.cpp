@@ -383,13 +383,15 @@ void CpuEngine::start_task(int index) {
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> runnable;
   {
     std::lock_guard<std::mutex> lk(version_mu_);
-    for (auto it = waiting_model_.begin(); it != waiting_model_.end();) {
-      ParamLocal& q = params_[it->second->param_index];
-      if (q.completed_version >= it->second->iter) {
-        runnable.push_back(*it);
-        it = waiting_model_.erase(it);
-      } else {
-        ++it;
+    auto mine = waiting_model_.find(index);
+    if (mine != waiting_model_.end()) {
+      for (auto it = mine->second.begin(); it != mine->second.end();) {
+        if (p.completed_version >= it->second->iter) {
+          runnable.push_back(*it);
+          it = mine->second.erase(it);
+        } else {
+          ++it;
+        }
       }
     }
   }
@@ -483,7 +485,7 @@ void CpuEngine::schedule_after_model_complete(Module* next, const std::shared_pt
   {
     std::lock_guard<std::mutex> lk(version_mu_);
     if (params_[t->param_index].completed_version < t->iter) {
-      waiting_model_.emplace_back(next, t);
+      waiting_model_[t->param_index].emplace_back(next, t);
       return;
     }
   }
@@ -635,7 +637,8 @@ std::string CpuEngine::describe_task(const std::string& key) {
   };
   {
     std::lock_guard<std::mutex> lk(version_mu_);
-    if (holds(waiting_model_)) where += ", waits for the previous version to be released";
+    for (auto& kv : waiting_model_)
+      if (holds(kv.second)) where += ", waits for the previous version to be released";
     if (holds(waiting_prev_)) where += ", waits for the previous iteration of the parameter";
     if (holds(waiting_master_)) where += ", waits for the previous copy-out of the parameter";
   }
@@ -667,7 +670,7 @@ void CpuEngine::synchronize() {
   {
     std::lock_guard<std::mutex> lk(version_mu_);
     for (auto& p : params_) p.completed_version = p.alloc_cnt - 1;
-    runnable.swap(waiting_model_);
+    for (auto& kv : waiting_model_) runnable.splice(runnable.end(), kv.second);
   }
   for (auto& r : runnable) schedule(r.first, r.second);
   std::list<std::pair<std::string, std::shared_future<void>>> futs;

@@ -259,7 +259,9 @@ class CpuEngine {
   // model-version gates
   std::mutex version_mu_;
   std::condition_variable version_cv_;
-  std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_model_;
+  // by parameter: a new backward pass of a parameter can only release tasks of that parameter, so start_task looks at
+  // one short list instead of at every waiting task of the model
+  std::map<int, std::list<std::pair<Module*, std::shared_ptr<TrainTask>>>> waiting_model_;
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_prev_;
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> waiting_master_;
 
