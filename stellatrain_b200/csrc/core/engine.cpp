@@ -1,5 +1,7 @@
 #include "engine.h"
 
+#include <pthread.h>
+
 #include <algorithm>
 #include <chrono>
 #include <cmath>
@@ -40,6 +42,12 @@ CpuEngine::~CpuEngine() {
     for (void* s : copy_streams_) api->stream_destroy(s);
     for (auto& p : params_) if (p.grad_event) api->event_destroy(p.grad_event);
   }
+  {
+    std::lock_guard<std::mutex> lk(after_cuda_mu_);
+    after_cuda_stop_ = true;
+  }
+  after_cuda_cv_.notify_all();
+  if (after_cuda_thread_.joinable()) after_cuda_thread_.join();
   pool_.reset();      // joins the workers before the memory they use goes away
   comm_.reset();
   shm_.reset();
@@ -249,19 +257,48 @@ struct AfterCuda {
   std::atomic<int>* in_flight;
 };
 
-// Runs on a thread of the CUDA runtime, in stream order: it must not call the runtime and should be short.  The
-// continuations only create a task or put a stage into the pool's queue; running them here, not in the pool, keeps
-// two callbacks of one parameter in the order of their copies.
+// Runs on a thread of the CUDA runtime, in stream order, and the stream does not go on until it returns: it must not
+// call the runtime and has to be short.  It only hands the continuation to the engine's own thread, which runs the
+// continuations in the order in which they were handed over (two callbacks of one parameter keep the order of their
+// copies).
 void after_cuda_trampoline(void* user) {
   std::unique_ptr<AfterCuda> a(static_cast<AfterCuda*>(user));
-  try {
-    a->fn();
-  } catch (const std::exception& e) {
-    LOG_ERROR("CpuEngine", "continuation behind a device copy failed: " << e.what());
-  }
-  a->in_flight->fetch_sub(1);
+  std::atomic<int>* in_flight = a->in_flight;
+  std::function<void()> fn = std::move(a->fn);
+  a->engine->run_after_cuda([fn = std::move(fn), in_flight] {
+    try {
+      fn();
+    } catch (const std::exception& e) {
+      LOG_ERROR("CpuEngine", "continuation behind a device copy failed: " << e.what());
+    }
+    in_flight->fetch_sub(1);
+  });
 }
 }  // namespace
+
+void CpuEngine::run_after_cuda(std::function<void()> fn) {
+  {
+    std::lock_guard<std::mutex> lk(after_cuda_mu_);
+    if (!after_cuda_thread_.joinable()) after_cuda_thread_ = std::thread([this] { after_cuda_main(); });
+    after_cuda_q_.push_back(std::move(fn));
+  }
+  after_cuda_cv_.notify_one();
+}
+
+void CpuEngine::after_cuda_main() {
+  pthread_setname_np(pthread_self(), "AfterCuda");
+  for (;;) {
+    std::function<void()> fn;
+    {
+      std::unique_lock<std::mutex> lk(after_cuda_mu_);
+      after_cuda_cv_.wait(lk, [this] { return after_cuda_stop_ || !after_cuda_q_.empty(); });
+      if (after_cuda_q_.empty()) return;       // stop requested and nothing left
+      fn = std::move(after_cuda_q_.front());
+      after_cuda_q_.pop_front();
+    }
+    fn();
+  }
+}
 
 bool CpuEngine::device_copies_available() const { return cuda_api() != nullptr; }
 
@@ -309,6 +346,7 @@ void CpuEngine::post_backward_device(int index, const void* device_grad, void* p
     } catch (const std::exception& e) {
       LOG_ERROR("CpuEngine", "starting the task of parameter " << index << " failed: " << e.what());
     }
+    grad_copies_pending_.fetch_sub(1);
   }, &callbacks_in_flight_};
   // in order, stopping at the first failure: a callback that was never enqueued must not be waited for
   int rc = api->event_record(p.grad_event, producer_stream);
@@ -316,8 +354,12 @@ void CpuEngine::post_backward_device(int index, const void* device_grad, void* p
   if (rc == 0) rc = api->memcpy_d2h_async(slot, device_grad, static_cast<size_t>(p.numel) * sizeof(float), copy_stream);
   if (rc == 0) {
     callbacks_in_flight_.fetch_add(1);
+    grad_copies_pending_.fetch_add(1);
     rc = api->launch_host_func(copy_stream, after_cuda_trampoline, after);
-    if (rc != 0) callbacks_in_flight_.fetch_sub(1);
+    if (rc != 0) {
+      callbacks_in_flight_.fetch_sub(1);
+      grad_copies_pending_.fetch_sub(1);
+    }
   }
   if (rc != 0) {
     delete after;
@@ -664,6 +706,12 @@ void CpuEngine::synchronize() {
         streams.push_back(p.last_copy_stream);
     for (void* st : streams)
       if (api->stream_synchronize(st) != 0) throw std::runtime_error("a copy stream did not finish");
+    // the host callbacks have fired; the tasks are created by the engine's own thread just behind them
+    const auto limit = Clock::now() + std::chrono::milliseconds(opt_.timeout_ms);
+    while (grad_copies_pending_.load() > 0) {
+      if (Clock::now() > limit) throw std::runtime_error("tasks behind finished gradient copies were not created in time");
+      std::this_thread::sleep_for(std::chrono::microseconds(100));
+    }
   }
   // release every "previous version still in use" gate (reference core.cpp:910-922)
   std::list<std::pair<Module*, std::shared_ptr<TrainTask>>> runnable;

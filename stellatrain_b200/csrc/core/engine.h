@@ -18,6 +18,7 @@
 #include <atomic>
 #include <condition_variable>
 #include <cstdint>
+#include <deque>
 #include <functional>
 #include <future>
 #include <list>
@@ -284,6 +285,18 @@ class CpuEngine {
   std::vector<void*> copy_streams_;
   int device_ = -1;                          // CUDA device of the thread that attached the first device parameter
   std::atomic<int> callbacks_in_flight_{0};
+  std::atomic<int> grad_copies_pending_{0};    // gradient copies whose task has not been created yet
+  // Continuations behind device copies run here, in the order in which their host callbacks fired: the callback itself
+  // (a thread of the CUDA runtime, which holds back the stream while it runs) only appends to this queue.
+  std::thread after_cuda_thread_;
+  std::mutex after_cuda_mu_;
+  std::condition_variable after_cuda_cv_;
+  std::deque<std::function<void()>> after_cuda_q_;
+  bool after_cuda_stop_ = false;
+ public:
+  void run_after_cuda(std::function<void()> fn);      // called by the host callback
+ private:
+  void after_cuda_main();
 
   std::mutex ready_mu_;
   std::condition_variable ready_cv_;
