@@ -131,11 +131,65 @@ def arm_watchdog(seconds: float) -> None:
     t.start()
 
 
+def _exit_text(rc) -> str:
+    """A child's return code in words: 'exit 0', 'signal SIGBUS', 'still running (killed at the limit)'."""
+    import signal
+
+    if rc is None:
+        return "still running (killed at the limit)"
+    if rc < 0:
+        try:
+            return f"signal {signal.Signals(-rc).name}"
+        except ValueError:
+            return f"signal {-rc}"
+    return f"exit {rc}"
+
+
+def _host_limits() -> str:
+    """What the machine offers to a pipeline that lives in host memory: shared-memory file system, RAM, cores."""
+    parts = []
+    try:
+        v = os.statvfs("/dev/shm")
+        parts.append(f"/dev/shm {v.f_bavail * v.f_frsize >> 20} MiB free of {v.f_blocks * v.f_frsize >> 20} MiB")
+    except OSError as e:
+        parts.append(f"/dev/shm: {e}")
+    try:
+        with open("/proc/meminfo") as f:
+            mem = {ln.split(":")[0]: ln.split()[1] for ln in f if ln.startswith(("MemTotal", "MemAvailable"))}
+        parts.append(f"RAM {int(mem.get('MemAvailable', 0)) >> 10} MiB available of {int(mem.get('MemTotal', 0)) >> 10} MiB")
+    except (OSError, ValueError):
+        pass
+    for path in ("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory/memory.limit_in_bytes"):
+        try:
+            with open(path) as f:
+                parts.append(f"cgroup memory limit {f.read().strip()}")
+            break
+        except OSError:
+            continue
+    parts.append(f"{len(os.sched_getaffinity(0))} cores")
+    return ", ".join(parts)
+
+
+# Pinned pool the reference carves its tensors from: ONE chunk of 4 GiB that never grows
+# (backend/src/engine/config.h:24, backend/src/engine/shm_manager.cpp:217-219, 330-370).
+REFERENCE_POOL_BYTES = 4 << 30
+
+
+def reference_pool_need(n_params: int, local_world: int) -> int:
+    """Bytes the reference takes from its pool for one model: the master copy of every parameter
+    (backend/src/engine/core.cpp:807-830) plus, per local GPU, two gradient slots of every tensor
+    (backend/src/engine/core.cpp:963-1008), each start rounded up to 16 bytes."""
+    return n_params * 4 * (1 + 2 * local_world) + 16 * 1024 * (1 + 2 * local_world)
+
+
 def run_reference_arm(args: argparse.Namespace) -> None:
     """The unmodified reference, built out of tree into ``baseline/_ref`` (recipe in ``baseline/build_reference.sh``),
-    driven through its own API by ``baseline/reference_arm.py``: one node, one process per GPU, started by rank 0 the way
-    the reference's driver starts its local ranks (backend/test/test_end_to_end.py:160-163).  Any failure, a time-out
-    included, ends in the ``unavailable`` line."""
+    driven through its own API by ``baseline/reference_arm.py``: one node, one process per GPU.  Local rank 0 is
+    started first and the others only once its shared-memory pool exists, the order in which the reference's own
+    driver brings its local ranks up (backend/test/test_end_to_end.py:160-163): a local rank that finds the metadata
+    segment before rank 0 has filled it in reads a chunk count of zero and stops at
+    backend/src/engine/shm_manager.cpp:186.  Any failure, a time-out included, ends in the ``unavailable`` line,
+    which carries every rank's exit code or signal, the head and tail of its log, and the host's limits."""
     import glob
     import signal
 
@@ -146,7 +200,7 @@ def run_reference_arm(args: argparse.Namespace) -> None:
     ref_dir = os.path.join(here, "baseline", "_ref")
 
     def unavailable(why: str) -> None:
-        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:600]}), flush=True)
+        print(json.dumps({"impl": "reference", "n_gpus": world, "unavailable": " ".join(why.split())[:6000]}), flush=True)
 
     if not glob.glob(os.path.join(ref_dir, "fasterdp*.so")) or not os.path.exists(os.path.join(ref_dir, "model_wrapper.py")):
         unavailable(REFERENCE_UNAVAILABLE + "; no out-of-tree build under baseline/_ref either")
@@ -164,8 +218,31 @@ def run_reference_arm(args: argparse.Namespace) -> None:
     except Exception as e:  # noqa: BLE001
         have = 0
         sys.stderr.write(f"[bench] torch: {e!r}\n")
+    have = int(os.environ.get("REFERENCE_ARM_ASSUME_GPUS", have))    # tests of the launch and failure path on a CPU box
     if have < world:
         unavailable(f"{world} GPUs asked for, {have} visible")
+        return
+    # The pool is a file in /dev/shm that the reference sizes to 4 GiB without reserving it: where the file system is
+    # smaller than what the run touches, the process that touches the first missing page dies of SIGBUS without a word.
+    try:
+        import torchvision
+
+        n_params = sum(p.numel() for p in getattr(torchvision.models, args.model)(num_classes=args.num_classes).parameters())
+    except Exception as e:  # noqa: BLE001
+        unavailable(f"cannot size the model: {e!r}")
+        return
+    need = reference_pool_need(n_params, world)
+    if need > REFERENCE_POOL_BYTES:
+        unavailable(f"{args.model} on {world} local GPUs needs {need >> 20} MiB of the reference's pinned pool (one parameter "
+                    f"copy and two gradient slots per GPU, backend/src/engine/core.cpp:807-830, 963-1008); the pool is one "
+                    f"chunk of {REFERENCE_POOL_BYTES >> 20} MiB that never grows (backend/src/engine/config.h:24, "
+                    f"backend/src/engine/shm_manager.cpp:217-219) and its allocator throws when it is full (shm_manager.cpp:355-367)")
+        return
+    vfs = os.statvfs("/dev/shm")
+    shm_free = vfs.f_bavail * vfs.f_frsize
+    if shm_free < need + (64 << 20) + (64 << 20):      # 64 MiB metadata segment (config.h:23) and some slack
+        unavailable(f"{args.model} on {world} local GPUs touches {need >> 20} MiB of the reference's pool in /dev/shm "
+                    f"(+64 MiB of metadata); this box: {_host_limits()}")
         return
     session = os.getpid()
     port = int(os.environ.get("MASTER_PORT", "29500")) + 31
@@ -178,7 +255,9 @@ def run_reference_arm(args: argparse.Namespace) -> None:
     sampler = ClockSampler(0)
     sampler.start()
     procs, logs = [], []
-    for lr in range(world):
+    deadline = time.time() + float(os.environ.get("REFERENCE_ARM_TIMEOUT_S", "330"))
+
+    def start(lr: int) -> None:
         log = open(os.path.join(here, "baseline", f".reference_arm_{lr}.log"), "w+")
         logs.append(log)
         procs.append(subprocess.Popen(
@@ -188,9 +267,25 @@ def run_reference_arm(args: argparse.Namespace) -> None:
              "--optimizer", args.optimizer, "--lr", str(args.lr), "--momentum", str(args.momentum), "--method", args.compressor,
              "--steps", str(args.steps), "--warmup", str(max(3, args.warmup))],
             stdout=log, stderr=subprocess.STDOUT, env=env, start_new_session=True))
-    deadline = time.time() + float(os.environ.get("REFERENCE_ARM_TIMEOUT_S", "330"))
+
+    def log_text(i: int) -> str:
+        logs[i].flush()
+        with open(logs[i].name) as f:
+            return f.read()
+
+    start(0)
+    pool_file = f"/dev/shm/fasterdp-shm-data-{session}-0"
+    master_up = False
+    while time.time() < deadline and procs[0].poll() is None:
+        if os.path.exists(pool_file) and "Starting SHM Master OK" in log_text(0):
+            master_up = True
+            break
+        time.sleep(0.1)
+    if master_up:
+        for lr in range(1, world):
+            start(lr)
     timed_out = False
-    while any(p.poll() is None for p in procs):
+    while master_up and any(p.poll() is None for p in procs):
         if time.time() > deadline:
             timed_out = True
             break
@@ -198,6 +293,7 @@ def run_reference_arm(args: argparse.Namespace) -> None:
             time.sleep(2.0)         # one rank failed: the others would wait for it forever
             break
         time.sleep(0.2)
+    codes = [p.poll() for p in procs]
     for p in procs:
         if p.poll() is None:
             try:
@@ -206,24 +302,28 @@ def run_reference_arm(args: argparse.Namespace) -> None:
                 pass
             p.wait()
     clocks = sampler.stop()
+    limits = _host_limits()         # before the pool's files go: what was left while the run had its pages
     for f in glob.glob(f"/dev/shm/fasterdp-shm-*-{session}*") + glob.glob(f"/dev/shm/sem.fasterdp-sem-{session}*"):
         try:
             os.unlink(f)
         except OSError:
             pass
     results, tails = [], []
-    for log in logs:
+    for i, log in enumerate(logs):
         log.seek(0)
         text = log.read()
         log.close()
-        first_error = next((ln for ln in text.splitlines() if "Error" in ln or "error" in ln or "Assertion" in ln), "")
-        tails.append((first_error[:240] + " ... " if first_error else "") + text[-160:])
+        body = text if len(text) <= 2048 else text[:1024] + " [...] " + text[-1024:]
+        tails.append(f"[local rank {i}: {_exit_text(codes[i])}] {body}")
         for line in text.splitlines():
             if line.startswith("REFERENCE_ARM_RESULT "):
                 results.append(json.loads(line[len("REFERENCE_ARM_RESULT "):]))
     if len(results) != world:
-        unavailable(("timed out; " if timed_out else "") + f"{len(results)} of {world} reference processes finished; last output: "
-                    + " | ".join(tails))
+        why = "timed out; " if timed_out else ""
+        if not master_up:
+            why += "local rank 0 did not bring its shared-memory pool up; "
+        unavailable(why + f"{len(results)} of {world} reference processes finished; pool need {need >> 20} MiB; host at the end: "
+                    f"{limits}; " + " | ".join(tails))
         return
     ms = max(r["ms"] for r in results)
     per_step = ms / args.steps
@@ -528,10 +628,11 @@ def main() -> None:
         cpu_engine.close()
 
     # The sparse path inside the step, from the device-clock stamps that the kernels of the last step wrote themselves:
-    # select + push and scatter + apply of every bucket, and the select chain against the memory roofline (it moves 20
-    # bytes per element: read gradient and residual, write residual and zeros, re-read the residual) at the measured
-    # copy bandwidth.  In the step these kernels share the GPU with the backward pass, so the fraction is a lower bound
-    # of what the kernels reach alone (profiles/ has those numbers).  Never allowed to break the result line.
+    # select + push and scatter + apply of every bucket, and the select chain against the memory roofline at the measured
+    # copy bandwidth.  Bytes per element: the one-pass chain reads gradient and residual and writes the residual (12), the
+    # two-pass chain reads the residual once more (16); 4 more where the consumed gradients are zeroed ("flat" gradient
+    # mode).  In the step these kernels share the GPU with the backward pass, so the fraction is a lower bound of what the
+    # kernels reach alone (profiles/ has those numbers).  Never allowed to break the result line.
     sparse_path = None
     if engine is not None:
         try:
@@ -542,10 +643,13 @@ def main() -> None:
             if os.path.exists(peaks_file):
                 with open(peaks_file) as f:
                     hbm_gbs, peaks_src = float(json.load(f)["hbm_gbs"]), "measured"
+            one_pass = all(getattr(rt.bucket, "last_select_fused", False) for rt in engine.buckets)
+            per_elem = (12 if one_pass else 16) + (4 if engine.cfg.grad_mode == "flat" else 0)
             sparse_path = {"buckets": len(rows), "select_push_ms": sel, "scatter_apply_ms": app,
                            "share_of_step": (sel + app) / per_step if per_step > 0 else None,
-                           "select_bytes": 20 * n_params,
-                           "select_fraction_of_copy_bandwidth": (20 * n_params / (sel * 1e-3) / (hbm_gbs * 1e9)) if sel > 0 else None,
+                           "select_chain": "one-pass" if one_pass else "two-pass", "select_bytes_per_element": per_elem,
+                           "select_bytes": per_elem * n_params,
+                           "select_fraction_of_copy_bandwidth": (per_elem * n_params / (sel * 1e-3) / (hbm_gbs * 1e9)) if sel > 0 else None,
                            "copy_bandwidth_gbs": hbm_gbs, "of": peaks_src,
                            "nvlink_bytes_per_step": int(sum(rt.bucket.layout.wire_bytes() for rt in engine.buckets) * max(world - 1, 0))}
         except Exception as e:  # noqa: BLE001

@@ -52,8 +52,13 @@ struct BucketHandle {
     app.n_total = n_total;
   }
 
+  uint32_t max_chunk_len = 0;   // longest chunk of the chunk table (decides whether the one-pass select may run)
+
   void set_tables(uint64_t segs, uint64_t state, uint64_t work, uint64_t chunks, uint64_t chunk_cnt,
-                  uint64_t chunk_pos, uint64_t hist, uint32_t n_segs, uint32_t n_chunks, uint32_t cap) {
+                  uint64_t chunk_pos, uint64_t hist, uint32_t n_segs, uint32_t n_chunks, uint32_t cap,
+                  uint64_t chunk_state, uint32_t max_chunk) {
+    sel.chunk_state = as_ptr<uint64_t>(chunk_state);
+    max_chunk_len = max_chunk;
     sel.segs = as_ptr<const st::SegDesc>(segs);
     sel.state = as_ptr<st::SegState>(state);
     sel.work = as_ptr<st::SegWork>(work);
@@ -205,9 +210,17 @@ struct BucketHandle {
     check(st::launch_group_reduce(grp, as_ptr<CUstream_st>(stream)), "launch_group_reduce");
   }
 
-  void select(uint64_t stream) {
+  // fused: the one-pass chain of the threshold compressors; every tensor of the bucket must have its threshold
+  // (one select through the four-kernel chain, or a restored checkpoint)
+  void select(uint64_t stream, bool fused) {
+    if (fused) {
+      if (!st::fused_select_possible(sel, max_chunk_len)) throw std::runtime_error("one-pass select is not available for this bucket");
+      check(st::launch_select_fused(sel, as_ptr<CUstream_st>(stream)), "launch_select_fused");
+      return;
+    }
     check(st::launch_select(sel, randomk_seed, as_ptr<CUstream_st>(stream)), "launch_select");
   }
+  bool can_fuse() const { return st::fused_select_possible(sel, max_chunk_len); }
   // Debug checks.  cksum areas are [2][world] u32 indexed [slot][source]; cksum_acc has MAX_WORLD words, rsum `world`.
   void set_debug(uint64_t cksum_acc, uint64_t rsum, uint64_t cksum_local, const std::vector<uint64_t>& peer_cksum, bool poison) {
     const int world = app.world;
@@ -262,7 +275,7 @@ PYBIND11_MODULE(_C, m) {
            py::arg("param"), py::arg("rec"), py::arg("vmax"), py::arg("last"), py::arg("n_total"))
       .def("set_tables", &BucketHandle::set_tables, py::arg("segs"), py::arg("state"), py::arg("work"),
            py::arg("chunks"), py::arg("chunk_cnt"), py::arg("chunk_pos"), py::arg("hist"), py::arg("n_segs"),
-           py::arg("n_chunks"), py::arg("cap"))
+           py::arg("n_chunks"), py::arg("cap"), py::arg("chunk_state") = 0, py::arg("max_chunk") = 0)
       .def("set_scratch", &BucketHandle::set_scratch, py::arg("cand"), py::arg("cand_cursor"), py::arg("cand_cap"))
       .def("set_control", &BucketHandle::set_control, py::arg("counters"), py::arg("status"), py::arg("opt"),
            py::arg("weight"), py::arg("timeout_ns"), py::arg("stamps") = 0)
@@ -277,7 +290,8 @@ PYBIND11_MODULE(_C, m) {
            py::arg("my_local"), py::arg("ready_local"), py::arg("mate_ready"), py::arg("done_local"), py::arg("mate_done"),
            py::arg("group_done_ctr"))
       .def("group_reduce", &BucketHandle::group_reduce, py::arg("stream"))
-      .def("select", &BucketHandle::select, py::arg("stream"))
+      .def("select", &BucketHandle::select, py::arg("stream"), py::arg("fused") = false)
+      .def("can_fuse", &BucketHandle::can_fuse)
       .def("set_owner", &BucketHandle::set_owner, py::arg("bounds"), py::arg("state_base"), py::arg("state_len"),
            py::arg("wb_local"), py::arg("peer_wb"), py::arg("wb_mc"), py::arg("pflag_local"), py::arg("peer_pflag"))
       .def("set_debug", &BucketHandle::set_debug, py::arg("cksum_acc"), py::arg("rsum"), py::arg("cksum_local"),

@@ -8,6 +8,11 @@ namespace st {
 // Error-feedback select + push of one bucket: four kernels on `stream` (two for random-k).
 cudaError_t launch_select(const SelectArgs& args, uint32_t randomk_seed, cudaStream_t stream);
 
+// One-pass variant for threshold-v and threshold-v16 once every tensor has its threshold: two kernels.  Usable
+// when fused_select_possible() says so (max_chunk_len: the longest chunk of the bucket's chunk table).
+bool fused_select_possible(const SelectArgs& args, uint32_t max_chunk_len);
+cudaError_t launch_select_fused(const SelectArgs& args, cudaStream_t stream);
+
 // Bounded wait + scatter-add + sparse optimiser of one bucket: two kernels on `stream`, plus the copy of
 // the owners' new parameter values when the optimiser state is partitioned.  phase 0 = all, 1 = scatter and
 // apply only, 2 = parameter copy only.

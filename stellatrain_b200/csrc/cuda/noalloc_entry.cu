@@ -89,6 +89,25 @@ int fail(int code, const char* what, cudaError_t e = cudaSuccess) {
 
 extern "C" const char* st_noalloc_last_error(void) { return g_err; }
 
+extern "C" int st_noalloc_status(uint32_t* status_out, cudaStream_t stream) {
+  if (status_out == nullptr) return fail(ST_NOALLOC_ERR_BAD_ARG, "status_out must not be null");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ST_NOALLOC_ERR_CUDA, "cudaGetDevice", e);
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (dev >= 0 && dev < kMaxDevices) base = g_base[dev];
+  }
+  if (base == nullptr) return fail(ST_NOALLOC_ERR_BAD_ARG, "no selection has run on this device yet");
+  // a plain copy into the caller's memory: nothing is allocated here either
+  e = cudaMemcpyAsync(status_out, base + Layout::control + 2 * sizeof(uint32_t), sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(ST_NOALLOC_ERR_CUDA, "reading the status word", e);
+  g_err[0] = 0;
+  return ST_NOALLOC_OK;
+}
+
 extern "C" int st_topk_select_noalloc(const float* values, uint32_t n, uint32_t k, void* out_pairs,
                                       cudaStream_t stream) {
   if (n > kMaxElems) {

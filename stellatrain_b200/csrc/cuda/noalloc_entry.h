@@ -41,6 +41,14 @@ extern "C" {
 __attribute__((visibility("default")))
 int st_topk_select_noalloc(const float* values, uint32_t n, uint32_t k, void* out_pairs, cudaStream_t stream);
 
+// The selection runs asynchronously, so st_topk_select_noalloc returns before its kernels have run and cannot say
+// how they fared.  This call waits for `stream` and copies the device-side status word of the latest selection on
+// the current GPU into *status_out (host memory): 0 = the k pairs were written, anything else = the kernels gave
+// up and out_pairs is not valid (values of st::Status in sparse_types.h; with well-formed arguments this does not
+// happen).  It allocates nothing.  Returns one of the ST_NOALLOC_* codes.
+__attribute__((visibility("default")))
+int st_noalloc_status(uint32_t* status_out, cudaStream_t stream);
+
 // Human-readable reason of the calling thread's last non-zero return value.
 __attribute__((visibility("default")))
 const char* st_noalloc_last_error(void);

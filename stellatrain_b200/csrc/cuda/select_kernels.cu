@@ -452,8 +452,17 @@ __global__ void __launch_bounds__(kThreads, 4) k_pass2(SelectArgs A) {
     const uint32_t it = tile * kP2PerIter;
     const uint32_t i = it + threadIdx.x * kP2PerThread;
     const bool act = i < ch.len;   // chunk lengths are multiples of 16: a thread is all in or all out
-    if (!mbar_wait_bounded(&s_bar[tile & 1u], (tile >> 1) & 1u)) {
-      set_status(A.status, kTimeoutFlag);   // cannot happen for a valid source; never spin forever
+    // The exit on a copy that never lands is taken by the whole CTA or by nobody: the scans below contain
+    // barriers, and a copy into this CTA's shared memory must not be in flight when the CTA retires.
+    const bool landed = mbar_wait_bounded(&s_bar[tile & 1u], (tile >> 1) & 1u);
+    if (!__syncthreads_and(landed)) {
+      if (threadIdx.x == 0) {
+        set_status(A.status, kTimeoutFlag);   // cannot happen for a valid source; never spin forever
+        // tile + 1 was started together with this one (or when tile - 1 was consumed): wait for it too, bounded
+        if (tile + 1 < n_tiles) mbar_wait_bounded(&s_bar[(tile + 1) & 1u], ((tile + 1) >> 1) & 1u);
+        if (!landed) mbar_wait_bounded(&s_bar[tile & 1u], (tile >> 1) & 1u);
+      }
+      __syncthreads();
       return;
     }
     float v[16];
@@ -631,6 +640,137 @@ __device__ __forceinline__ void publish_checksums(const SelectArgs& A, uint32_t 
 constexpr int kCandThreads = 1024;
 constexpr int kCandIlp = 4;   // independent loads in flight per thread
 
+// Called by a whole CTA of kCandThreads threads.  Among cand[0..c) takes the `rem` largest keys (equal keys: lowest
+// item id first; 1 <= rem <= c) and emits them: stream positions come from wp->out_cursor, except that the
+// lowest-ranked taken block of threshold-v16 goes to `last_pos`, where it may be cut off at sd.k.  Returns the key
+// of the lowest-ranked taken item.  s_hist: 2048 words, s_tmp: kCandThreads / 32 + 1 words, s_res: 4 words.
+__device__ __forceinline__ uint32_t take_top(const SelectArgs& A, const SegDesc& sd, SegWork* wp, const uint2* cand,
+                                             uint32_t c, uint32_t rem, bool b16, uint32_t kk, uint32_t last_pos,
+                                             uint64_t slot_off, int dest, uint32_t nb, uint32_t* s_hist,
+                                             uint32_t* s_tmp, uint32_t* s_res) {
+  const uint32_t tid = threadIdx.x;
+  uint32_t ties = 0;
+  uint32_t prefix = 0, mask = 0;
+  // radix select over the full 31-bit key, largest first: digits of 11, 11 and 9 bits
+  const int shifts[3] = {20, 9, 0};
+  const uint32_t widths[3] = {2048u, 2048u, 512u};
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = shifts[pass];
+    const uint32_t nbins = widths[pass];
+    for (uint32_t b = tid; b < nbins; b += kCandThreads) s_hist[b] = 0;
+    __syncthreads();
+    for (uint32_t i0 = tid; i0 < c; i0 += kCandThreads * kCandIlp) {
+      uint32_t key[kCandIlp];
+#pragma unroll
+      for (int u = 0; u < kCandIlp; ++u) {
+        const uint32_t i = i0 + u * kCandThreads;
+        key[u] = i < c ? cand[i].y : 0xFFFFFFFFu;
+      }
+#pragma unroll
+      for (int u = 0; u < kCandIlp; ++u)
+        if (key[u] != 0xFFFFFFFFu && (key[u] & mask) == prefix) atomicAdd(&s_hist[(key[u] >> shift) & (nbins - 1)], 1u);
+    }
+    __syncthreads();
+    // thread t owns bins nbins-1-2t and nbins-2-2t (descending)
+    const uint32_t h0 = 2 * tid < nbins ? s_hist[nbins - 1 - 2 * tid] : 0u;
+    const uint32_t h1 = 2 * tid + 1 < nbins ? s_hist[nbins - 2 - 2 * tid] : 0u;
+    uint32_t total;
+    const uint32_t ex = block_excl_scan(h0 + h1, s_tmp, total);
+    if (ex < rem && ex + h0 >= rem) {
+      s_res[0] = nbins - 1 - 2 * tid; s_res[1] = rem - ex; s_res[2] = h0;
+    } else if (ex + h0 < rem && ex + h0 + h1 >= rem) {
+      s_res[0] = nbins - 2 - 2 * tid; s_res[1] = rem - ex - h0; s_res[2] = h1;
+    }
+    __syncthreads();
+    prefix |= s_res[0] << shift;
+    mask |= (nbins - 1) << shift;
+    rem = s_res[1];
+    ties = s_res[2];
+    __syncthreads();
+  }
+  const uint32_t t_key = prefix;
+  // among equal keys take the lowest item ids: radix select on the id, smallest first
+  uint32_t id_thr = 0xFFFFFFFFu;
+  if (rem < ties) {
+    uint32_t ipre = 0, imask = 0, irem = rem;
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (uint32_t b = tid; b < 256; b += kCandThreads) s_hist[b] = 0;
+      __syncthreads();
+      for (uint32_t i = tid; i < c; i += kCandThreads) {
+        const uint2 e = cand[i];
+        if (e.y == t_key && (e.x & imask) == ipre) atomicAdd(&s_hist[(e.x >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      const uint32_t h = tid < 256 ? s_hist[tid] : 0u;
+      uint32_t total;
+      const uint32_t ex = block_excl_scan(h, s_tmp, total);
+      if (tid < 256 && ex < irem && ex + h >= irem) { s_res[0] = tid; s_res[1] = irem - ex; }
+      __syncthreads();
+      ipre |= s_res[0] << shift;
+      imask |= 255u << shift;
+      irem = s_res[1];
+      __syncthreads();
+    }
+    id_thr = ipre;
+  }
+  // threshold-v16: the lowest-ranked taken block goes last and may be truncated
+  uint32_t last_id = id_thr;
+  if (b16 && rem >= ties) {
+    uint32_t mxid = 0;
+    for (uint32_t i = tid; i < c; i += kCandThreads) {
+      const uint2 e = cand[i];
+      if (e.y == t_key) mxid = max(mxid, e.x);
+    }
+    last_id = block_max_u32(mxid, s_tmp);
+  }
+  for (uint32_t i = tid; i < c; i += kCandThreads) {
+    const uint2 e = cand[i];
+    const bool take = e.y > t_key || (e.y == t_key && e.x <= id_thr);
+    if (!take) continue;
+    if (!b16) {
+      const uint32_t pos = atomicAdd(&wp->out_cursor, 1u);
+      if (pos < kk) {
+        const float a = A.resid[e.x], sv = wire_value(nb, a);
+        emit_entry(A, dest, nb, slot_off, pos, e.x, sv);
+        A.resid[e.x] = a - sv;
+      }
+    } else {
+      const bool is_last = (e.y == t_key && e.x == last_id);
+      const uint32_t pos = is_last ? last_pos : atomicAdd(&wp->out_cursor, 1u);
+      if (pos < kk) {
+        const uint32_t base = e.x * 16u;
+        for (uint32_t j = 0; j < 16u; ++j) {
+          if (pos * 16u + j < sd.k) {
+            const float a = A.resid[base + j], sv = wire_value(nb, a);
+            emit_entry(A, dest, nb, slot_off, pos * 16u + j, base + j, sv);
+            A.resid[base + j] = a - sv;
+          }
+        }
+      }
+    }
+  }
+  return t_key;
+}
+
+// Completion of a select chain, called by thread 0 of every CTA of its last kernel after a CTA barrier: the last
+// CTA publishes the arrival flags and advances the epoch.  The CTA barrier orders the CTA's stores before this
+// thread's system-scope fence, the counter orders the CTAs.
+__device__ __forceinline__ void finish_select(const SelectArgs& A, uint32_t epoch) {
+  __threadfence_system();
+  const uint32_t prev = atomicAdd(A.done_ctr, 1u);
+  if (prev == gridDim.x - 1) {
+    *A.done_ctr = 0;
+    __threadfence_system();
+    publish_checksums(A, epoch);
+    if (A.publish && ld_volatile_u32(A.status) == kOk) {
+      for (int p = 0; p < A.world; ++p)
+        st_release_sys_u64(A.flag[p] + (size_t)(epoch & 1u) * A.flag_slot_stride, (uint64_t)epoch);
+    }
+    *A.epoch = epoch + 1;
+  }
+}
+
 __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
   __shared__ uint32_t s_hist[2048];
   __shared__ uint32_t s_tmp[kCandThreads / 32 + 1];
@@ -650,109 +790,8 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
   const uint32_t mode = wp->mode;
 
   if (ok && mode == kModeTop) {
-    const uint32_t c = wp->cand_cnt;
-    const uint2* cand = A.cand + wp->cand_off;
-    uint32_t rem = wp->k_rem, ties = 0;
-    uint32_t prefix = 0, mask = 0;
-    // radix select over the full 31-bit key, largest first: digits of 11, 11 and 9 bits
-    const int shifts[3] = {20, 9, 0};
-    const uint32_t widths[3] = {2048u, 2048u, 512u};
-    for (int pass = 0; pass < 3; ++pass) {
-      const int shift = shifts[pass];
-      const uint32_t nb = widths[pass];
-      for (uint32_t b = tid; b < nb; b += kCandThreads) s_hist[b] = 0;
-      __syncthreads();
-      for (uint32_t i0 = tid; i0 < c; i0 += kCandThreads * kCandIlp) {
-        uint32_t key[kCandIlp];
-#pragma unroll
-        for (int u = 0; u < kCandIlp; ++u) {
-          const uint32_t i = i0 + u * kCandThreads;
-          key[u] = i < c ? cand[i].y : 0xFFFFFFFFu;
-        }
-#pragma unroll
-        for (int u = 0; u < kCandIlp; ++u)
-          if (key[u] != 0xFFFFFFFFu && (key[u] & mask) == prefix) atomicAdd(&s_hist[(key[u] >> shift) & (nb - 1)], 1u);
-      }
-      __syncthreads();
-      // thread t owns bins nb-1-2t and nb-2-2t (descending)
-      const uint32_t h0 = 2 * tid < nb ? s_hist[nb - 1 - 2 * tid] : 0u;
-      const uint32_t h1 = 2 * tid + 1 < nb ? s_hist[nb - 2 - 2 * tid] : 0u;
-      uint32_t total;
-      const uint32_t ex = block_excl_scan(h0 + h1, s_tmp, total);
-      if (ex < rem && ex + h0 >= rem) {
-        s_res[0] = nb - 1 - 2 * tid; s_res[1] = rem - ex; s_res[2] = h0;
-      } else if (ex + h0 < rem && ex + h0 + h1 >= rem) {
-        s_res[0] = nb - 2 - 2 * tid; s_res[1] = rem - ex - h0; s_res[2] = h1;
-      }
-      __syncthreads();
-      prefix |= s_res[0] << shift;
-      mask |= (nb - 1) << shift;
-      rem = s_res[1];
-      ties = s_res[2];
-      __syncthreads();
-    }
-    const uint32_t t_key = prefix;
-    // among equal keys take the lowest item ids: radix select on the id, smallest first
-    uint32_t id_thr = 0xFFFFFFFFu;
-    if (rem < ties) {
-      uint32_t ipre = 0, imask = 0, irem = rem;
-      for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        for (uint32_t b = tid; b < 256; b += kCandThreads) s_hist[b] = 0;
-        __syncthreads();
-        for (uint32_t i = tid; i < c; i += kCandThreads) {
-          const uint2 e = cand[i];
-          if (e.y == t_key && (e.x & imask) == ipre) atomicAdd(&s_hist[(e.x >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        const uint32_t h = tid < 256 ? s_hist[tid] : 0u;
-        uint32_t total;
-        const uint32_t ex = block_excl_scan(h, s_tmp, total);
-        if (tid < 256 && ex < irem && ex + h >= irem) { s_res[0] = tid; s_res[1] = irem - ex; }
-        __syncthreads();
-        ipre |= s_res[0] << shift;
-        imask |= 255u << shift;
-        irem = s_res[1];
-        __syncthreads();
-      }
-      id_thr = ipre;
-    }
-    // threshold-v16: the lowest-ranked taken block goes last and may be truncated
-    uint32_t last_id = id_thr;
-    if (b16 && rem >= ties) {
-      uint32_t mxid = 0;
-      for (uint32_t i = tid; i < c; i += kCandThreads) {
-        const uint2 e = cand[i];
-        if (e.y == t_key) mxid = max(mxid, e.x);
-      }
-      last_id = block_max_u32(mxid, s_tmp);
-    }
-    for (uint32_t i = tid; i < c; i += kCandThreads) {
-      const uint2 e = cand[i];
-      const bool take = e.y > t_key || (e.y == t_key && e.x <= id_thr);
-      if (!take) continue;
-      if (!b16) {
-        const uint32_t pos = atomicAdd(&wp->out_cursor, 1u);
-        if (pos < kk) {
-          const float a = A.resid[e.x], sv = wire_value(nb, a);
-          emit_entry(A, dest, nb, slot_off, pos, e.x, sv);
-          A.resid[e.x] = a - sv;
-        }
-      } else {
-        const bool is_last = (e.y == t_key && e.x == last_id);
-        const uint32_t pos = is_last ? kk - 1 : atomicAdd(&wp->out_cursor, 1u);
-        if (pos < kk) {
-          const uint32_t base = e.x * 16u;
-          for (uint32_t j = 0; j < 16u; ++j) {
-            if (pos * 16u + j < sd.k) {
-              const float a = A.resid[base + j], sv = wire_value(nb, a);
-              emit_entry(A, dest, nb, slot_off, pos * 16u + j, base + j, sv);
-              A.resid[base + j] = a - sv;
-            }
-          }
-        }
-      }
-    }
+    const uint32_t t_key = take_top(A, sd, wp, A.cand + wp->cand_off, wp->cand_cnt, wp->k_rem, b16, kk, kk - 1u, slot_off,
+                                    dest, nb, s_hist, s_tmp, s_res);
     if (tid == 0) {
       SegState ss = A.state[seg];
       // Next select: centre the histogram on the threshold just found, unless it fell off the
@@ -782,23 +821,380 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
       emit_entry(A, dest, nb, slot_off, p, kSentinelIdx, 0.f);
   }
 
-  // completion: the last CTA publishes the arrival flags and advances the epoch.  The CTA barrier
-  // orders this CTA's stores before thread 0's system-scope fence, the counter orders the CTAs.
   __syncthreads();
   if (tid == 0) {
-    __threadfence_system();
-    const uint32_t prev = atomicAdd(A.done_ctr, 1u);
-    if (prev == gridDim.x - 1) {
-      *A.done_ctr = 0;
-      __threadfence_system();
-      publish_checksums(A, epoch);
-      if (A.publish && ld_volatile_u32(A.status) == kOk) {
-        for (int p = 0; p < A.world; ++p)
-          st_release_sys_u64(A.flag[p] + (size_t)(epoch & 1u) * A.flag_slot_stride, (uint64_t)epoch);
+    wp->cand_cnt = 0;      // the one-pass select appends its near-miss blocks behind a zero count
+    wp->found = 0;
+    finish_select(A, epoch);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// one-pass select of the threshold modes
+// ------------------------------------------------------------------------------------------------
+// Threshold-v and threshold-v16 know their threshold before they look at the data (it persists per tensor,
+// backend/src/compress/thresholdv.cpp:44-52, backend/src/compress/thresholdv16.cpp:81-97), so once a tensor has
+// one the select needs a single pass over gradient and residual:
+//   fused   a = g + r, r <- a; items at or over the threshold are counted per chunk, the chunks of a tensor chain
+//           their counts (decoupled look-back, one 64-bit word per chunk) so that every item learns its position in
+//           index order, and the first k of them go straight into the destinations' receive areas and are cleared
+//           in r.  Blocks of large tensors just under the threshold are noted as candidates for the fill.
+//   finish  per tensor: threshold-v pads an under-filled stream; threshold-v16 completes it with the best of
+//           the rejected blocks (backend/src/compress/thresholdv16.cpp:261-293: its heap), taken from the noted
+//           candidates or, when those do not suffice or the tensor is small, from a scan of the whole tensor by
+//           this CTA, so the stream always holds exactly what the two-pass chain would have chosen; then the
+//           threshold steps (AIMD) and the last CTA publishes the arrival flags.
+// 12 bytes per element cross HBM (read g, read r, write r) against 16 to 20 of the two-pass chain.
+constexpr int kFusedMaxIter = 16;                              // iterations of kPerIter elements per chunk
+constexpr uint32_t kFusedMaxChunk = kFusedMaxIter * kPerIter;  // 16384 elements
+constexpr uint32_t kSmallSegBlocks = 4096;                     // up to 65536 elements the finishing CTA scans the tensor itself
+constexpr uint32_t kLookbackPolls = 1u << 20;                  // bound of every wait on a predecessor chunk
+constexpr float kWindowDefault = 0.05f;                        // candidates: keys in [tau * (1 - window), tau)
+
+__device__ __forceinline__ uint64_t ld_relaxed_gpu_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_relaxed_gpu_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// State word of a chunk: select epoch (so that a word of an earlier select never counts) | kind | item count.
+// kind 1: the chunk's own count; kind 2: the count of the chunk and of all chunks of the tensor before it.
+__device__ __forceinline__ uint64_t chunk_word(uint32_t epoch, uint32_t kind, uint32_t value) {
+  return ((uint64_t)epoch << 32) | ((uint64_t)kind << 30) | (uint64_t)value;
+}
+
+// Run by warp 0 of a chunk's CTA.  Publishes the chunk's count, then walks back over the chunks of the tensor,
+// 32 at a time, adding counts until one carries an inclusive prefix.  Returns the number of items of the tensor
+// in front of this chunk.  Every wait is bounded: *good is false when a predecessor never published, and the
+// chunk then still publishes a prefix so that the chunks behind it do not wait for it in turn.
+__device__ __forceinline__ uint32_t chunk_lookback(uint64_t* state, uint32_t first, uint32_t mine, uint32_t epoch,
+                                                   uint32_t total, bool* good) {
+  const uint32_t lane = threadIdx.x & 31u;
+  if (mine == first) {
+    if (lane == 0) st_relaxed_gpu_u64(state + mine, chunk_word(epoch, 2u, total));
+    *good = true;
+    return 0u;
+  }
+  if (lane == 0) st_relaxed_gpu_u64(state + mine, chunk_word(epoch, 1u, total));
+  uint32_t base = 0;
+  bool ok = true;
+  uint32_t j = mine;   // chunks [first, j) are not accounted for yet
+  while (j > first) {
+    uint32_t kind = 2u, val = 0u;   // lanes that reach past the tensor's first chunk stand for "prefix 0"
+    if (j - first > lane) {
+      const uint64_t* p = state + (j - 1u - lane);
+      uint64_t w = ld_relaxed_gpu_u64(p);
+      for (uint32_t polls = 0; (uint32_t)(w >> 32) != epoch && polls < kLookbackPolls; ++polls) {
+        __nanosleep(64);
+        w = ld_relaxed_gpu_u64(p);
       }
-      *A.epoch = epoch + 1;
+      if ((uint32_t)(w >> 32) != epoch) ok = false;
+      else { kind = (uint32_t)(w >> 30) & 3u; val = (uint32_t)w & 0x3FFFFFFFu; }
+    }
+    const uint32_t has_prefix = __ballot_sync(0xffffffffu, kind == 2u);
+    const uint32_t upto = has_prefix ? (uint32_t)__ffs((int)has_prefix) - 1u : 31u;
+    base += __reduce_add_sync(0xffffffffu, lane <= upto ? val : 0u);
+    if (has_prefix) break;
+    j -= 32u;
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (lane == 0) st_relaxed_gpu_u64(state + mine, chunk_word(epoch, 2u, base + total));
+  *good = ok;
+  return base;
+}
+
+// The receive slot about to be overwritten was last used two epochs ago; every destination must have consumed
+// it.  One thread calls this right before its CTA stores into the destinations.
+__device__ __forceinline__ bool acks_arrived(const SelectArgs& A, uint32_t epoch) {
+  if (!A.use_acks || epoch <= 2u) return true;
+  const uint64_t want = (uint64_t)epoch - 2u;
+  for (int p = 0; p < A.world; ++p) {
+    if (!wait_ge_bounded(A.ack_local + (size_t)(epoch & 1u) * A.world + p, want, A.timeout_ns)) {
+      set_status(A.status, kTimeoutAck);
+      return false;
     }
   }
+  return true;
+}
+
+template <bool B16>
+__global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
+  constexpr int kWarps = kThreads / 32;
+  __shared__ uint32_t s_cnt[kFusedMaxIter * kWarps];        // items over the threshold per (iteration, warp)
+  __shared__ uint32_t s_tmp[kWarps + 1];
+  __shared__ uint2 s_cnd[B16 ? kFusedMaxChunk / 16 : 1];    // near-miss blocks of this chunk: (block id, key)
+  __shared__ uint32_t s_word[4];   // [0] candidates staged, [1] items in front of the chunk, [2] candidate base, [3] may emit
+
+  const Chunk ch = A.chunks[blockIdx.x];
+  const SegDesc sd = A.segs[ch.seg];
+  const SegState ss = A.state[ch.seg];
+  SegWork* wp = &A.work[ch.seg];
+  const uint32_t epoch = *A.epoch;
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+
+  if (blockIdx.x == 0 && threadIdx.x == 0 && A.stamps != nullptr) A.stamps[0] = global_timer_ns();
+  if (sd.reserved & kSegSkip) {
+    // a tensor another rank of the group is responsible for: only clear the consumed gradient
+    if (A.zero_grad && A.grad_tab == nullptr) {
+      float* gz = A.grad + ch.start;
+      for (uint32_t i = threadIdx.x * 4; i < ch.len; i += kPerIter)
+        *reinterpret_cast<float4*>(gz + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    return;
+  }
+  if (threadIdx.x == 0) s_word[0] = 0;
+  __syncthreads();
+
+  const uint32_t seg_rel = ch.start - sd.off;
+  const bool tab = A.grad_tab != nullptr;
+  float* g = tab ? A.grad_tab[ch.seg] + seg_rel : A.grad + ch.start;
+  const uint32_t g_valid = tab ? (sd.n > seg_rel ? min(ch.len, sd.n - seg_rel) : 0u) : ch.len;
+  float* r = A.resid + ch.start;
+  // a tensor without a threshold yet selects nothing here: the finishing kernel then takes the exact top items
+  const uint32_t tau_bits = ss.inited ? __float_as_uint(ss.tau) : 0xFFFFFFFFu;
+  const uint32_t kk = B16 ? (sd.k + 15u) / 16u : sd.k;
+  const bool collect = B16 && ss.inited && sd.n_pad / 16u > kSmallSegBlocks;
+  float window = __uint_as_float(ss.reserved[0]);
+  if (!(window > 0.f && window <= 1.f)) window = kWindowDefault;
+  const uint32_t lo_bits = collect ? __float_as_uint(fmaxf(ss.tau * (1.f - window), 0.f)) : 0xFFFFFFFFu;
+  const uint32_t n_iter = (ch.len + kPerIter - 1) / kPerIter;   // the launcher guarantees <= kFusedMaxIter
+
+  uint32_t selbits = 0;   // B16: bit `it` = this lane's block of iteration `it` is over the threshold
+  uint64_t selmask = 0;   // element mode: 4 bits per iteration
+  uint32_t mx = 0;
+  for (uint32_t it = 0; it < n_iter; ++it) {
+    const uint32_t i = it * kPerIter + threadIdx.x * 4;
+    const bool act = i < ch.len;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (act) {
+      a = *reinterpret_cast<const float4*>(r + i);
+      if (!A.skip_ef) {
+        const float4 gv = load4_guarded(g, i, g_valid);
+        a.x += gv.x; a.y += gv.y; a.z += gv.z; a.w += gv.w;
+        // NaN policy: a NaN is dropped (neither sent nor kept), so it cannot poison the residual.
+        if (!(a.x == a.x)) a.x = 0.f;
+        if (!(a.y == a.y)) a.y = 0.f;
+        if (!(a.z == a.z)) a.z = 0.f;
+        if (!(a.w == a.w)) a.w = 0.f;
+        *reinterpret_cast<float4*>(r + i) = a;
+        if (A.zero_grad) store4_guarded(g, i, g_valid, make_float4(0.f, 0.f, 0.f, 0.f));
+      }
+    }
+    if (B16) {
+      const uint32_t key = __float_as_uint(quad_l1(a));   // the same value in the four lanes of a block
+      const bool sel = act && key >= tau_bits;
+      const uint32_t leaders = __ballot_sync(0xffffffffu, sel) & 0x11111111u;
+      if (lane == 0) s_cnt[it * kWarps + warp] = __popc(leaders);
+      selbits |= (uint32_t)sel << it;
+      if (collect && act && !sel && (lane & 3u) == 0u && key >= lo_bits && key != 0u) {
+        const uint32_t slot = atomicAdd(&s_word[0], 1u);
+        s_cnd[slot] = make_uint2((ch.start + i) >> 4, key);
+      }
+    } else {
+      const uint32_t key[4] = {key_bits(a.x), key_bits(a.y), key_bits(a.z), key_bits(a.w)};
+      uint32_t m4 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // the zero padding behind the tensor never counts, whatever the threshold
+        if (act && seg_rel + i + j < sd.n) {
+          m4 |= (uint32_t)(key[j] >= tau_bits) << j;
+          mx = max(mx, key[j]);
+        }
+      }
+      const uint32_t n = __reduce_add_sync(0xffffffffu, (uint32_t)__popc(m4));
+      if (lane == 0) s_cnt[it * kWarps + warp] = n;
+      selmask |= (uint64_t)m4 << (4u * it);
+    }
+  }
+  __syncthreads();
+
+  // positions: exclusive prefix over (iteration, warp) cells in index order, then over the chunks of the tensor
+  const uint32_t n_cells = n_iter * kWarps;
+  uint32_t total;
+  const uint32_t cell = threadIdx.x < n_cells ? s_cnt[threadIdx.x] : 0u;
+  const uint32_t cell_ex = block_excl_scan(cell, s_tmp, total);
+  if (threadIdx.x < n_cells) s_cnt[threadIdx.x] = cell_ex;
+  if (!B16) {
+    mx = block_max_u32(mx, s_tmp);
+    if (threadIdx.x == 0 && mx) atomicMax(&wp->max_bits, mx);
+  }
+  if (warp == 0) {
+    bool good;
+    const uint32_t base = chunk_lookback(A.chunk_state, sd.chunk_begin, blockIdx.x, epoch, total, &good);
+    if (lane == 0) {
+      if (!good) set_status(A.status, kTimeoutScan);
+      s_word[1] = base;
+      if (B16) s_word[2] = s_word[0] ? atomicAdd(&wp->cand_cnt, s_word[0]) : 0u;
+      if (blockIdx.x == sd.chunk_begin + sd.chunk_cnt - 1u) wp->found = base + total;
+      bool may = total != 0u && base < kk && ld_volatile_u32(A.status) == kOk;
+      if (may) may = acks_arrived(A, epoch);
+      s_word[3] = may ? 1u : 0u;
+    }
+  }
+  __syncthreads();
+
+  if (B16 && s_word[0]) {
+    uint2* region = A.cand + (sd.off >> 4);   // one slot per block of the tensor: can never overflow
+    const uint32_t cb = s_word[2];
+    for (uint32_t j = threadIdx.x; j < s_word[0]; j += kThreads) region[cb + j] = s_cnd[j];
+  }
+  if (!s_word[3]) return;
+
+  const uint32_t base = s_word[1];
+  const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
+  const int dest = dest_of(A, sd);
+  const uint32_t nb = narrow_base_of(sd);
+  for (uint32_t it = 0; it < n_iter; ++it) {
+    const uint32_t i = it * kPerIter + threadIdx.x * 4;
+    if (B16) {
+      const bool sel = (selbits >> it) & 1u;
+      const uint32_t leaders = __ballot_sync(0xffffffffu, sel) & 0x11111111u;
+      if (!sel) continue;
+      const uint32_t before = __popc(leaders & ((1u << (lane & ~3u)) - 1u));   // blocks of lower lanes
+      const uint32_t pos = base + s_cnt[it * kWarps + warp] + before;
+      if (pos >= kk) continue;   // beyond the budget: the block stays in the residual
+      float4 a = *reinterpret_cast<const float4*>(r + i);
+      float v[4] = {a.x, a.y, a.z, a.w};
+      const uint32_t p0 = pos * 16u + (lane & 3u) * 4u;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (p0 + e < sd.k) {   // a truncated last block leaves the residual exact: only emitted elements are cleared
+          const float sv = wire_value(nb, v[e]);
+          emit_entry(A, dest, nb, slot_off, p0 + e, ch.start + i + e, sv);
+          v[e] -= sv;
+        }
+      }
+      *reinterpret_cast<float4*>(r + i) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      const uint32_t m4 = (uint32_t)(selmask >> (4u * it)) & 15u;
+      const uint32_t n = __popc(m4);
+      uint32_t pos = base + s_cnt[it * kWarps + warp] + warp_incl_scan(n) - n;
+      if (!m4 || pos >= kk) continue;
+      float4 a = *reinterpret_cast<const float4*>(r + i);
+      float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (m4 >> j & 1u) {
+          if (pos < kk) {   // ordered mode truncates at k; the rest stays in the residual
+            const float sv = wire_value(nb, v[j]);
+            emit_entry(A, dest, nb, slot_off, pos, ch.start + i + j, sv);
+            v[j] -= sv;
+          }
+          ++pos;
+        }
+      }
+      // the padding of the tensor's last float4 is zero and stays zero
+      *reinterpret_cast<float4*>(r + i) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
+  __shared__ uint32_t s_hist[2048];
+  __shared__ uint32_t s_tmp[kCandThreads / 32 + 1];
+  __shared__ uint32_t s_res[4];
+  __shared__ uint32_t s_n[2];   // [0] candidates found by the scan, [1] acknowledgements arrived
+
+  const uint32_t seg = blockIdx.x;
+  const uint32_t tid = threadIdx.x;
+  const SegDesc sd = A.segs[seg];
+  SegWork* wp = &A.work[seg];
+  const uint32_t epoch = *A.epoch;
+  const bool ok = ld_volatile_u32(A.status) == kOk;
+  const bool b16 = A.compressor == kThresholdv16;
+  const uint32_t kk = b16 ? (sd.k + 15u) / 16u : sd.k;
+  const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
+  const int dest = dest_of(A, sd);
+  const uint32_t nb = narrow_base_of(sd);
+
+  if (ok && !(sd.reserved & kSegSkip)) {
+    SegState ss = A.state[seg];
+    const uint32_t found = wp->found;          // items at or over the threshold in the whole tensor
+    const uint32_t c_win = wp->cand_cnt;       // near-miss blocks the one-pass kernel noted
+    const bool short_of = found < kk;
+    uint32_t t_key = 0;
+    bool scanned = false;
+    if (short_of) {
+      if (tid == 0) s_n[1] = acks_arrived(A, epoch) ? 1u : 0u;
+      __syncthreads();
+      if (s_n[1]) {
+        if (!b16) {
+          // threshold-v may under-fill (thresholdv.cpp:82): pad the fixed-size stream
+          for (uint32_t p = found + tid; p < sd.k; p += kCandThreads)
+            emit_entry(A, dest, nb, slot_off, p, kSentinelIdx, 0.f);
+        } else {
+          const uint32_t need = kk - found, n_blocks = sd.n_pad / 16u;
+          uint2* cand = A.cand + (sd.off >> 4);
+          uint32_t c = c_win;
+          if (n_blocks <= kSmallSegBlocks || !ss.inited || c < need) {
+            // every block that still holds something is a candidate: the blocks over the threshold were all
+            // emitted (the stream is short of them) and are zero in the residual by now
+            scanned = true;
+            if (tid == 0) s_n[0] = 0;
+            __syncthreads();
+            for (uint32_t b0 = 0; b0 < n_blocks; b0 += kCandThreads / 4) {
+              const uint32_t b = b0 + (tid >> 2);
+              float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (b < n_blocks) a = *reinterpret_cast<const float4*>(A.resid + sd.off + b * 16u + (tid & 3u) * 4u);
+              const uint32_t key = __float_as_uint(quad_l1(a));
+              if (b < n_blocks && (tid & 3u) == 0u && key != 0u) {
+                const uint32_t slot = atomicAdd(&s_n[0], 1u);
+                cand[slot] = make_uint2((sd.off >> 4) + b, key);
+              }
+            }
+            __syncthreads();
+            c = s_n[0];
+          }
+          const uint32_t take = min(need, c);
+          if (tid == 0) wp->out_cursor = found;
+          __syncthreads();
+          if (take) t_key = take_top(A, sd, wp, cand, c, take, true, kk, found + take - 1u, slot_off, dest, nb, s_hist, s_tmp, s_res);
+          // fewer blocks with anything in them than the budget: the rest of the stream says "no entry"
+          for (uint32_t p = (found + take) * 16u + tid; p < sd.k; p += kCandThreads)
+            emit_entry(A, dest, nb, slot_off, p, kSentinelIdx, 0.f);
+        }
+      }
+    }
+    if (tid == 0) {
+      if (!b16) {
+        const float max_abs = __uint_as_float(wp->max_bits);
+        if (ss.inited) {   // AIMD of thresholdv.cpp:70-76
+          if (sd.k > found) ss.tau *= 0.99f;
+          else if (sd.k < found) ss.tau = ss.tau + 0.01f * ((float)found / (float)sd.k) * max_abs;
+        }
+      } else if (!ss.inited) {
+        if (short_of && s_n[1]) {   // first threshold: the smallest selected key plus the first additive step
+          const float t0 = __uint_as_float(t_key);
+          ss.tau_inc = 0.01f * t0;
+          ss.tau = t0 + ss.tau_inc;
+          ss.inited = 1;
+        }
+      } else {
+        if (short_of) ss.tau *= 0.99f;      // "must drop less" (thresholdv16.cpp:245-248)
+        else ss.tau += ss.tau_inc;          // thresholdv16.cpp:249-252
+        if (sd.n_pad / 16u > kSmallSegBlocks) {
+          // keep about as many near-miss blocks as the budget: few enough to be cheap, enough to fill from
+          float w = __uint_as_float(ss.reserved[0]);
+          if (!(w > 0.f && w <= 1.f)) w = kWindowDefault;
+          if (scanned) w *= 2.f;
+          else if (c_win > 2u * kk) w *= 0.75f;
+          else if (c_win < kk / 2u + 1u) w *= 1.5f;
+          ss.reserved[0] = __float_as_uint(fminf(fmaxf(w, 1e-3f), 1.f));
+        }
+      }
+      A.state[seg] = ss;
+      wp->cand_cnt = 0;
+      wp->found = 0;
+      wp->max_bits = 0;
+    }
+  }
+
+  __syncthreads();
+  if (tid == 0) finish_select(A, epoch);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -892,6 +1288,21 @@ __global__ void __launch_bounds__(kThreads) k_ef_only(SelectArgs A) {
 // ------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------
+bool fused_select_possible(const SelectArgs& A, uint32_t max_chunk_len) {
+  return (A.compressor == kThresholdv || A.compressor == kThresholdv16) && A.chunk_state != nullptr &&
+         max_chunk_len <= kFusedMaxChunk && A.n_total < (1u << 30);
+}
+
+cudaError_t launch_select_fused(const SelectArgs& A, cudaStream_t stream) {
+  if (A.n_chunks == 0 || A.n_segs == 0) return cudaSuccess;
+  if (A.world > kMaxWorld || A.chunk_state == nullptr) return cudaErrorInvalidValue;
+  if (A.compressor == kThresholdv16) k_fused<true><<<A.n_chunks, kThreads, 0, stream>>>(A);
+  else if (A.compressor == kThresholdv) k_fused<false><<<A.n_chunks, kThreads, 0, stream>>>(A);
+  else return cudaErrorInvalidValue;
+  k_finish<<<A.n_segs, kCandThreads, 0, stream>>>(A);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_select(const SelectArgs& A, uint32_t randomk_seed, cudaStream_t stream) {
   if (A.n_chunks == 0 || A.n_segs == 0) return cudaSuccess;
   if (A.world > kMaxWorld) return cudaErrorInvalidValue;

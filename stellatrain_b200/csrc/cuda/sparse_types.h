@@ -28,6 +28,7 @@ enum Status : uint32_t {
   kBadCandidate = 4,  // candidate scratch exhausted (cannot happen with a correctly sized scratch)
   kBadSize = 5,       // request exceeds a compiled-in limit
   kBadChecksum = 6,   // debug checks: a received stream does not add up to what its source sent
+  kTimeoutScan = 7,   // one-pass select: a chunk never saw the item count of the chunk in front of it
 };
 
 struct SegDesc {          // static per segment (re-uploaded when the compression ratio changes)
@@ -64,6 +65,8 @@ struct SegState {         // persistent per segment, saved in checkpoints
   // holds the next threshold is 2^-10 wide (relative) and the candidate set is tiny.
   uint32_t hist_base;
   uint32_t hist_shift;
+  // reserved[0]: float bits of the one-pass select's candidate window (blocks with a key in
+  // [tau * (1 - window), tau) are noted for the fill); 0 = not set yet.
   uint32_t reserved[3];
 };
 
@@ -110,6 +113,7 @@ struct SelectArgs {
   const Chunk* chunks;
   uint32_t* chunk_cnt;         // items over the threshold per chunk
   uint32_t* chunk_pos;         // exclusive prefix of chunk_cnt inside the segment
+  uint64_t* chunk_state;       // one-pass select: per chunk (epoch | kind | items), see chunk_word(); or null
   uint32_t* hist;              // [n_segs][kHistBins]
   uint2* cand;                 // candidate scratch: (item id, key)
   uint32_t* cand_cursor;       // bump pointer into cand

@@ -3,12 +3,15 @@
     python -m stellatrain_b200.ops.bench_kernels --model resnet152 --compressor thresholdv16
     python -m stellatrain_b200.ops.bench_kernels --elems 40000000 --segments 64 --compressor topk
 
-Times, with CUDA events after warm-up, the select chain (pass1, plan, pass2, cand) and the apply chain
-(scatter, apply) over all buckets of a parameter-size list, and reports achieved HBM bandwidth against
-the measured copy bandwidth of the machine (``MEASURED_PEAKS.json`` next to the repository root when
-present).  Algorithmic traffic of one select: read g, read r, write r, write g (zeroing) in pass 1 and
-read r in pass 2 = 20 bytes per element; the sparse outputs are below 1 % of that.  Between iterations
-the gradient buffers are refilled, which also evicts the previous iteration's lines from L2.
+Times, with CUDA events after warm-up, the select chain and the apply chain (scatter, apply) over all buckets
+of a parameter-size list, and reports achieved HBM bandwidth against the measured copy bandwidth of the
+machine (``MEASURED_PEAKS.json`` next to the repository root when present).  Algorithmic traffic of one select,
+per element: the two-pass chain (pass1, plan, pass2, cand) reads g and r and writes r in pass 1 and reads r
+again in pass 2 = 16 bytes; the one-pass chain of the threshold compressors (fused, finish) reads g and r and
+writes r = 12 bytes; both write 4 more when the consumed gradient is zeroed (``--zero-grad 1``, the engine's
+"flat" gradient mode; its default mode hands the kernels autograd's own tensors and zeroes nothing).  The sparse
+outputs are below 1 % of that.  Between iterations the gradient buffers are refilled, which also evicts the
+previous iteration's lines from L2.
 """
 from __future__ import annotations
 
@@ -50,6 +53,8 @@ def main() -> None:
     ap.add_argument("--ratio", type=float, default=0.99)
     ap.add_argument("--bucket-mb", type=float, default=64.0)
     ap.add_argument("--chunk-elems", type=int, default=8192)
+    ap.add_argument("--zero-grad", type=int, default=0, help="1: the select also writes zeros over the gradients it consumed")
+    ap.add_argument("--fused", type=int, default=1, help="0: keep the threshold compressors on the two-pass chain")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -62,8 +67,10 @@ def main() -> None:
     for bi, grp in enumerate(groups):
         layout = B.BucketLayout([f"t{i}" for i in grp], [numels[i] for i in grp], chunk_elems=args.chunk_elems)
         b = GpuBucket(bi, layout, dev, compressor=args.compressor, ratio=args.ratio, optimizer=args.optimizer,
-                      scratch=scratch)
+                      scratch=scratch, fused_select=bool(args.fused))
         b.wire_local()
+        b.zero_grad_in_select = bool(args.zero_grad)
+        b._bind()
         buckets.append(b)
     n_total = sum(b.layout.n_total for b in buckets)
     gen = torch.Generator(device=dev).manual_seed(0)
@@ -93,18 +100,21 @@ def main() -> None:
     peaks = measured_peaks()
     sel = sorted(sel_ms)[len(sel_ms) // 2]
     app = sorted(app_ms)[len(app_ms) // 2]
-    sel_bytes = 20.0 * n_total
+    one_pass = bool(getattr(buckets[0], "last_select_fused", False))
+    sel_bytes = ((12.0 if one_pass else 16.0) + (4.0 if args.zero_grad else 0.0)) * n_total
     entries = sum(b.layout.cap for b in buckets)
     # apply: per entry read 8 B twice; per touched element one 32 B sector of the state record and one of the parameter
     app_bytes = entries * (16.0 + 32.0 * 2)
     out = {
         "compressor": args.compressor, "optimizer": args.optimizer, "elements": n_total, "buckets": len(buckets),
         "segments": len(numels), "entries_per_step": entries,
+        "select_chain": "one-pass (fused, finish)" if one_pass else "two-pass (pass1, plan, pass2, cand)",
+        "select_bytes_per_element": sel_bytes / n_total,
         "select_ms": sel, "select_GBps": sel_bytes / sel / 1e6,
         "select_frac_of_measured_copy": sel_bytes / sel / 1e6 / peaks["hbm_gbs"],
         "apply_ms": app, "apply_sector_GBps": app_bytes / app / 1e6,
         "hbm_gbs_measured": peaks["hbm_gbs"], "peaks_are_fallback": bool(peaks.get("fallback", False)),
-        "kernel_launches_per_step": len(buckets) * 6,
+        "kernel_launches_per_step": len(buckets) * (4 if one_pass else 6),
     }
     print(json.dumps(out))
 

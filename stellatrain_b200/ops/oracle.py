@@ -80,8 +80,14 @@ def block_scores(a_pad: torch.Tensor) -> torch.Tensor:
     return (lane[:, 0] + lane[:, 1]) + (lane[:, 2] + lane[:, 3])
 
 
-def select_thresholdv16(a: torch.Tensor, k: int, st: ThresholdState) -> torch.Tensor:
-    """Element indices sent (exactly k, some may point into the zero padding of the last block)."""
+def select_thresholdv16(a: torch.Tensor, k: int, st: ThresholdState, one_pass: bool = False) -> torch.Tensor:
+    """Element indices sent (k of them; some may point into the zero padding of the last block).
+
+    ``one_pass`` states the rule of the one-pass kernel chain for a tensor that already has a threshold: the
+    blocks at or over the threshold go first, in index order; when they fall short of the budget, the best of
+    the others complete it (the reference's heap fill, backend/src/compress/thresholdv16.cpp:261-293), but a
+    block that holds nothing is never sent, so a tensor with fewer non-zero blocks than the budget yields
+    fewer than k indices (the rest of its stream says "no entry").  The two-pass chain sends such blocks."""
     n = a.numel()
     n_pad = (n + 15) // 16 * 16
     a_pad = torch.zeros(n_pad, dtype=torch.float32, device=a.device)
@@ -91,6 +97,8 @@ def select_thresholdv16(a: torch.Tensor, k: int, st: ThresholdState) -> torch.Te
     last_len = k - 16 * (kb - 1)
 
     def expand(blocks: torch.Tensor) -> torch.Tensor:
+        if blocks.numel() < kb:         # short stream: whole blocks only
+            return (blocks[:, None] * 16 + torch.arange(16, device=a.device)[None, :]).flatten()
         full = (blocks[:-1, None] * 16 + torch.arange(16, device=a.device)[None, :]).flatten()
         tail = blocks[-1] * 16 + torch.arange(last_len, device=a.device)
         return torch.cat([full, tail])
@@ -110,12 +118,14 @@ def select_thresholdv16(a: torch.Tensor, k: int, st: ThresholdState) -> torch.Te
         st.tau = f32(f32(st.tau) + f32(st.tau_inc))
     else:
         blocks = _top_indices(score, kb)
+        if one_pass:
+            blocks = blocks[score[blocks] > 0]
         st.tau = f32(f32(st.tau) * f32(0.99))
     return expand(blocks)
 
 
 def compress_step(kind: str, grad: torch.Tensor, resid: torch.Tensor, k: int,
-                  st: Optional[ThresholdState] = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                  st: Optional[ThresholdState] = None, one_pass: bool = False) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """One error-feedback compression of one tensor: returns (idx, val, new_residual).
 
     For threshold-v16 the residual and the indices refer to the zero-padded tensor."""
@@ -129,7 +139,7 @@ def compress_step(kind: str, grad: torch.Tensor, resid: torch.Tensor, k: int,
         n_pad = (n + 15) // 16 * 16
         if n_pad != n:
             a = torch.cat([a, torch.zeros(n_pad - n, dtype=a.dtype, device=a.device)])
-        idx = select_thresholdv16(a[:n], k, st)
+        idx = select_thresholdv16(a[:n], k, st, one_pass=one_pass)
     else:
         raise ValueError(kind)
     val = a[idx]

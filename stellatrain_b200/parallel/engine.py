@@ -56,6 +56,8 @@ class EngineConfig:
     status_poll_interval: int = 16        # forwards between non-blocking looks at the status words
     deterministic_merge: bool = False     # add the sources' contributions in rank order (one scatter launch per source):
                                           # replicas with replicated state stay bit-equal; world - 1 more launches per bucket
+    fused_select: bool = True             # threshold compressors: one pass over gradient and residual once every tensor
+                                          # has its threshold (12 bytes per element instead of 16 to 20)
     debug_checks: bool = False            # every stream carries a checksum that the receiver verifies (status 6), consumed
                                           # entries are overwritten with the "no entry" marker; slower, for debugging
     profile: bool = False                 # NVTX ranges and CUDA-event timers per bucket and stage (utils/stats.py)
@@ -174,6 +176,7 @@ class SparseDPEngine:
                 timeout_s=cfg.timeout_s, divide_k_by_world=cfg.divide_k_by_world,
                 k_world=(self.groups if (self.group_size > 1 and cfg.divide_k_by_world) else None),
                 partition_state=self.partitioned, deterministic_merge=cfg.deterministic_merge,
+                fused_select=cfg.fused_select,
             )
             if self.group_size > 1:
                 layout.assign_owners(self.group_size, self.my_local)
@@ -464,7 +467,7 @@ class SparseDPEngine:
             b.select(s)
         rt.select_count += 1
         self.stats["select_launches"] += 1
-        self.stats["kernels"] += 2 if b.compressor == "randomk" else 4
+        self.stats["kernels"] += 2 if (b.compressor == "randomk" or getattr(b, "last_select_fused", False)) else 4
 
     def _apply_impl(self, rt: _BucketRuntime) -> None:
         s = self.sparse_stream
@@ -686,6 +689,7 @@ class SparseDPEngine:
             b.opt.copy_(bsd["opt"])
             b._opt_host = b.opt.cpu().numpy().view(B.OPT_STATE_DTYPE).copy()
             b.state.copy_(bsd["seg_state"])
+            b.thresholds_ready = b._all_thresholds_set()
             b.resid.zero_(); b.acc.zero_(); b.grad.zero_(); b.stamp.zero_()
         torch.cuda.synchronize(self.device)
         if self.dist_on:

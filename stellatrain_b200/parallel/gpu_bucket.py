@@ -23,6 +23,7 @@ STATUS_NAMES = {
     4: "candidate scratch exhausted",
     5: "size beyond a compiled-in limit",
     6: "a received stream does not match its source's checksum",
+    7: "one-pass select: a chunk never saw the count of the chunk before it",
 }
 
 
@@ -95,6 +96,7 @@ class GpuBucket:
         k_world: Optional[int] = None,
         partition_state: bool = False,
         deterministic_merge: bool = False,
+        fused_select: bool = True,
     ) -> None:
         self.index = index
         self.layout = layout
@@ -140,6 +142,11 @@ class GpuBucket:
         self.chunks = _dev_bytes(layout.chunk_table(), device)
         self.chunk_cnt = torch.zeros(layout.n_chunks, dtype=torch.int32, device=device)
         self.chunk_pos = torch.zeros(layout.n_chunks, dtype=torch.int32, device=device)
+        # One-pass select of the threshold compressors: one state word per chunk (epoch | kind | count).  It takes
+        # over once every tensor has a threshold: after the first select, or after a checkpoint that carries them.
+        self.chunk_state = torch.zeros(layout.n_chunks, dtype=torch.int64, device=device)
+        self.fused_select = bool(fused_select)
+        self.thresholds_ready = False
         self.hist = torch.zeros(n_segs * 2048, dtype=torch.int32, device=device)
         self.counters = torch.tensor([1, 1, 0, 0], dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -188,6 +195,7 @@ class GpuBucket:
             segs=self.segs.data_ptr(), state=self.state.data_ptr(), work=self.work.data_ptr(),
             chunks=self.chunks.data_ptr(), chunk_cnt=self.chunk_cnt.data_ptr(), chunk_pos=self.chunk_pos.data_ptr(),
             hist=self.hist.data_ptr(), n_segs=len(L.segments), n_chunks=L.n_chunks, cap=L.cap,
+            chunk_state=self.chunk_state.data_ptr(), max_chunk=min(L.chunk_elems, max(s.n_pad for s in L.segments)),
         )
         self.scratch.bind(h)
         h.set_control(
@@ -295,7 +303,11 @@ class GpuBucket:
     # ------------------------------------------------------------------ execution
     def select(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
-        (self.select_handle or self.handle).select(s.cuda_stream)
+        h = self.select_handle or self.handle
+        fused = self.fused_select and self.thresholds_ready and h.can_fuse()
+        h.select(s.cuda_stream, fused)
+        self.thresholds_ready = True      # the four-kernel chain leaves every tensor with a threshold
+        self.last_select_fused = fused
 
     def apply(self, stream: Optional[torch.cuda.Stream] = None, phase: int = 0) -> None:
         """phase 0: the whole chain; 1: scatter + optimiser only; 2: copy of the owners' values only."""
@@ -341,6 +353,10 @@ class GpuBucket:
                 val[s.out_off : s.out_off + s.k] = torch.where(none, torch.zeros_like(words), words & -65536).view(torch.float32)
         return idx, val
 
+    def _all_thresholds_set(self) -> bool:
+        inited = self.seg_state()["inited"]
+        return all(bool(inited[i]) for i, s in enumerate(self.layout.segments) if not s.skip)
+
     def seg_state(self) -> np.ndarray:
         return self.state.cpu().numpy().view(B.SEG_STATE_DTYPE).copy()
 
@@ -379,6 +395,7 @@ class GpuBucket:
                 continue
             t[:n_state].copy_(d[k][off : off + n_state])
         self.state.copy_(d["seg_state"])
+        self.thresholds_ready = self._all_thresholds_set()
         self._opt_host = self.opt.cpu().numpy().view(B.OPT_STATE_DTYPE).copy()
         self.acc.zero_()
         self.grad.zero_()

@@ -32,12 +32,15 @@ class HeartbeatMonitor:
     missing key and supports ``check([keys])`` or ``num_keys`` - a ``torch.distributed.TCPStore`` does."""
 
     def __init__(self, store, rank: int, world: int, interval_s: float = 0.5, timeout_s: float = 5.0,
-                 prefix: str = "hb") -> None:
+                 prefix: str = "hb", startup_timeout_s: Optional[float] = None) -> None:
         self.store, self.rank, self.world = store, rank, world
         self.interval_s, self.timeout_s, self.prefix = interval_s, timeout_s, prefix
+        # a peer that has not published anything yet is still starting (processes of one job come up seconds
+        # apart): it gets a longer limit than a peer that was heard and then fell silent
+        self.startup_timeout_s = max(timeout_s, 30.0) if startup_timeout_s is None else startup_timeout_s
         self._stop = threading.Event()
         self._beat(0)
-        self._last_seen = {r: (0, time.monotonic()) for r in range(world)}
+        self._last_seen = {r: (-1, time.monotonic()) for r in range(world)}
         self._thread = threading.Thread(target=self._main, daemon=True, name="Heartbeat")
         self._thread.start()
 
@@ -81,7 +84,7 @@ class HeartbeatMonitor:
             prev, when = self._last_seen[r]
             if count > prev:
                 self._last_seen[r] = (count, now)
-            elif now - when > self.timeout_s:
+            elif now - when > (self.timeout_s if prev >= 0 else self.startup_timeout_s):
                 lost.append(r)
                 reason = reason or f"no heartbeat for {now - when:.1f} s"
         if lost:

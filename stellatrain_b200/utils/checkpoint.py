@@ -51,14 +51,14 @@ def save(path: str, module: torch.nn.Module, engine, extra: Optional[dict] = Non
             _write(p, {"model": module.state_dict(), "engine": esd, "extra": extra or {}, "rank": 0, "world": world})
         dist.barrier()
         return str(p) if rank == 0 else None
-    if not all_ranks and rank != 0:
-        return None
+    writes = all_ranks or rank == 0
     if world > 1:
         p = p.with_name(f"{p.stem}.rank{rank}{p.suffix}")
-    _write(p, {"model": module.state_dict(), "engine": esd, "extra": extra or {}, "rank": rank, "world": world})
+    if writes:
+        _write(p, {"model": module.state_dict(), "engine": esd, "extra": extra or {}, "rank": rank, "world": world})
     if world > 1:
-        dist.barrier()
-    return str(p)
+        dist.barrier()      # every rank takes part, also the ones that wrote nothing
+    return str(p) if writes else None
 
 
 def _write(p: Path, payload: dict) -> None:

@@ -184,6 +184,43 @@ def test_reference_arm_reports_unavailable():
     assert d["impl"] == "reference" and ("unavailable" in d or d["value"] > 0)
 
 
+def test_reference_arm_starts_local_rank_0_first_and_reports_every_rank():
+    """Failure path of the arm on a box without GPUs: local rank 0 brings the pool up, only then the second rank
+    starts; both fail at their first CUDA call and the line names each rank's exit and the host's limits."""
+    import json
+    import os
+    from pathlib import Path
+
+    import torch
+
+    root = Path(__file__).resolve().parent.parent
+    if torch.cuda.is_available() or not list((root / "baseline" / "_ref").glob("fasterdp*.so")):
+        pytest.skip("needs the out-of-tree build of the reference and no GPU")
+    env = {**os.environ, "WORLD_SIZE": "2", "RANK": "0", "REFERENCE_ARM_ASSUME_GPUS": "2", "REFERENCE_ARM_TIMEOUT_S": "120"}
+    out = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=300, cwd=root, env=env)
+    assert out.returncode == 0
+    d = json.loads(out.stdout.strip().splitlines()[-1])
+    why = d["unavailable"]
+    assert d["impl"] == "reference" and d["n_gpus"] == 2
+    assert "Starting SHM Master OK" in why and "[local rank 0:" in why and "[local rank 1:" in why
+    assert "/dev/shm" in why and "pool need" in why
+
+
+def test_reference_pool_arithmetic():
+    """ResNet-152 (58.3 M parameters): one master copy and two gradient slots per GPU fit the reference's 4 GiB chunk
+    up to 8 local GPUs, and no further."""
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("bench_mod", Path(__file__).resolve().parent.parent / "bench.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    n = 58_348_708
+    assert mod.reference_pool_need(n, 8) < mod.REFERENCE_POOL_BYTES < mod.reference_pool_need(n, 9)
+    assert mod.reference_pool_need(n, 4) < 2.3e9
+
+
 def test_merge_state_shards_reassembles_full_moments():
     import torch
 

@@ -47,21 +47,33 @@ def fill_grads(b, gen, scale=1e-2, mode="normal"):
 
 
 @pytest.mark.parametrize("compressor", ["topk", "thresholdv", "thresholdv16"])
-@pytest.mark.parametrize("mode", ["normal", "ties", "zero"])
-def test_select_matches_oracle(compressor, mode):
+@pytest.mark.parametrize("mode", ["normal", "ties", "zero", "shrinking"])
+@pytest.mark.parametrize("fused", [True, False])
+def test_select_matches_oracle(compressor, mode, fused):
+    """Bit-equal streams, residuals and thresholds against the plain-PyTorch rule, for the two-pass chain and
+    for the one-pass chain that takes over once a threshold compressor has its thresholds.  "shrinking" halves
+    the gradient scale every step, so the threshold is far too high and the one-pass chain has to complete
+    the stream from a scan of the tensor."""
+    if compressor == "topk" and fused:
+        pytest.skip("top-k has no persistent threshold: always the two-pass chain")
     torch.manual_seed(0)
     gen = torch.Generator(device="cuda").manual_seed(1234)
-    b = make_bucket(compressor, 0.99)
+    b = make_bucket(compressor, 0.99, fused_select=fused)
     resid_ref = torch.zeros_like(b.resid)
-    steps = 5 if mode == "normal" else 3
+    steps = 3 if mode in ("ties", "zero") else 6
     for step in range(steps):
         epoch = step + 1
-        fill_grads(b, gen, mode=mode if not (mode == "zero" and step == 1) else "normal")
+        if mode == "shrinking":
+            fill_grads(b, gen, scale=1e-2 * 0.5 ** step)
+        else:
+            fill_grads(b, gen, mode=mode if not (mode == "zero" and step == 1) else "normal")
         grad = b.grad.clone()
         states = oracle_states(b)
         b.select()
         torch.cuda.synchronize()
         b.check_status()
+        one_pass = fused and step > 0
+        assert b.last_select_fused == one_pass
         assert float(b.grad.abs().max()) == 0.0, "consumed gradients must be zeroed"
         idx_all, val_all = read_stream(b, epoch)
         new_states = b.seg_state()
@@ -73,7 +85,7 @@ def test_select_matches_oracle(compressor, mode):
             pad = compressor == "thresholdv16"
             g = grad[slp] if pad else grad[sl]
             r = resid_ref[slp] if pad else resid_ref[sl]
-            want_idx, want_val, new_r = O.compress_step(compressor, g, r, k, st)
+            want_idx, want_val, new_r = O.compress_step(compressor, g, r, k, st, one_pass=one_pass)
             want_idx = want_idx.cpu().numpy() + s.off
             valid = got_idx != O.SENTINEL
             order_g = np.argsort(got_idx[valid], kind="stable")

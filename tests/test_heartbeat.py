@@ -69,3 +69,57 @@ def test_peer_loss_is_detected_and_survivors_agree(behaviour):
         what, (lost, members, elapsed) = results[r]
         assert what == "lost" and lost == [2] and members == [0, 1], results
         assert elapsed < 10.0
+
+
+def _ckpt_rank_main(rank, world, port, q, tmp):
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    from stellatrain_b200.utils import checkpoint
+
+    class _Engine:           # what save() needs of an engine
+        def synchronize(self):
+            pass
+
+        def state_dict(self):
+            return {"world": world, "buckets": [], "param_names": [], "state_partition": "replicated"}
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", world_size=world, rank=rank,
+                            timeout=datetime.timedelta(seconds=30))
+    model = torch.nn.Linear(3, 2)
+    path = checkpoint.save(f"{tmp}/only0.pt", model, _Engine(), {"step": 1}, all_ranks=False)
+    # a collective right behind it: with an unmatched barrier inside save() the ranks would pair this one wrongly or block
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t)
+    dist.barrier()
+    q.put((rank, path, float(t)))
+    dist.destroy_process_group()
+
+
+def test_checkpoint_written_by_rank_0_only_keeps_the_ranks_in_step(tmp_path):
+    import os
+
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ckpt_rank_main, args=(r, world, port, q, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    deadline = time.time() + 90
+    while len(results) < world and time.time() < deadline:
+        try:
+            r, path, total = q.get(timeout=0.5)
+            results[r] = (path, total)
+        except Exception:  # noqa: BLE001
+            pass
+    for p in procs:
+        p.join(timeout=20)
+        if p.is_alive():
+            p.kill()
+    assert sorted(results) == [0, 1], results
+    assert results[0][0] is not None and os.path.exists(results[0][0]) and results[1][0] is None
+    assert results[0][1] == results[1][1] == 3.0
+    assert not os.path.exists(tmp_path / "only0.rank1.pt")

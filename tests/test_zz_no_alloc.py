@@ -26,6 +26,8 @@ def _lib():
     lib.st_topk_select_noalloc.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
                                            ctypes.c_void_p]
     lib.st_noalloc_last_error.restype = ctypes.c_char_p
+    lib.st_noalloc_status.restype = ctypes.c_int
+    lib.st_noalloc_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), ctypes.c_void_p]
     return lib
 
 
@@ -34,6 +36,9 @@ def _call(lib, values: torch.Tensor, k: int):
     stream = torch.cuda.current_stream().cuda_stream
     rc = lib.st_topk_select_noalloc(values.data_ptr(), values.numel(), k, out.data_ptr(), stream)
     assert rc == 0, lib.st_noalloc_last_error().decode()
+    status = ctypes.c_uint32(99)
+    assert lib.st_noalloc_status(ctypes.byref(status), stream) == 0, lib.st_noalloc_last_error().decode()
+    assert status.value == 0, "the kernels must report success on the device as well"
     torch.cuda.synchronize()
     idx = out[:, 0].cpu().numpy().view(np.uint32).astype(np.int64)
     val = out[:, 1].contiguous().view(torch.float32).cpu().numpy()
@@ -64,6 +69,30 @@ def test_noalloc_topk_matches_engine_path_twice():
         assert np.array_equal(got_idx, want_idx)
         np.testing.assert_allclose(got_val, want_val, rtol=0, atol=0)
         assert np.array_equal(values[torch.from_numpy(got_idx).cuda()].cpu().numpy(), got_val), "input must stay intact"
+
+
+def _plain_topk(values: torch.Tensor, k: int):
+    """Independent oracle in plain PyTorch: largest magnitudes, equal ones towards the lower index, NaN as 0."""
+    clean = torch.where(torch.isnan(values), torch.zeros_like(values), values)
+    order = torch.sort(clean.abs(), descending=True, stable=True).indices[:k]
+    idx = np.sort(order.cpu().numpy().astype(np.int64), kind="stable")
+    return idx, clean.cpu().numpy()[idx]
+
+
+def test_noalloc_topk_matches_plain_pytorch_with_odd_sizes_ties_and_nan():
+    lib = _lib()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for n, k in [(100_003, 1001), (17, 5), (65_537, 7)]:        # none a multiple of 16
+        values = torch.randn(n, device="cuda", generator=g)
+        values[::13] = values[1]                                 # exact ties, some of them across the k-th place
+        values[3] = float("nan")
+        values[n - 1] = float("nan")
+        before = values.clone()
+        got_idx, got_val = _call(lib, values, k)
+        want_idx, want_val = _plain_topk(values, k)
+        assert np.array_equal(got_idx, want_idx), (n, k)
+        np.testing.assert_array_equal(got_val, want_val)
+        assert torch.equal(torch.nan_to_num(values), torch.nan_to_num(before)) and bool(torch.isnan(values[3])), "input must stay intact"
 
 
 def test_noalloc_rejects_oversized_and_bad_arguments():
