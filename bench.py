@@ -13,9 +13,11 @@ gradient entries with error feedback, sparse Adam lr 1e-3, bounded staleness 1, 
 Rank 0 prints ONE JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with inputs already
 on the device; ``e2e`` is the same loop through the public API with, every step, the host-to-device copy
 of the batch from pinned memory and a device-to-host read of the loss inside the timed region.
-Other arms: ``--impl reference`` (the unmodified reference; not installable here, prints why),
-``--impl nccl_sparse`` (same kernels, streams moved by ncclAllGather) and ``--impl ddp`` (dense
-all-reduce + torch.optim.Adam) as library baselines.
+Other arms: ``--impl reference`` (the unmodified reference, built out of tree by ``baseline/build_reference.sh`` and
+driven through its own API; prints an ``unavailable`` line with the cause when it cannot run), ``--impl nccl_sparse``
+(same kernels, streams moved by ncclAllGather), ``--impl ddp`` (dense all-reduce + torch.optim.Adam),
+``--impl dense_single`` / ``dense_graph`` (plain PyTorch on one GPU) and ``--impl cpu_offload`` (this package's CPU tier)
+as baselines.
 """
 from __future__ import annotations
 
@@ -28,9 +30,9 @@ import sys
 import time
 
 REFERENCE_UNAVAILABLE = (
-    "reference is a CMake project without setup.py/pyproject.toml: `pip install --no-index "
-    "--no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref <reference tree>` fails with "
-    "\"Neither 'setup.py' nor 'pyproject.toml' found\"; baseline/build_reference.sh builds it with CMake instead"
+    "the reference is a CMake project without setup.py/pyproject.toml, so `pip install --target baseline/_ref "
+    "<reference tree>` fails with \"Neither 'setup.py' nor 'pyproject.toml' found\"; "
+    "baseline/build_reference.sh builds it with CMake instead"
 )
 
 
@@ -63,6 +65,9 @@ def parse_args() -> argparse.Namespace:
                     help="owner: optimiser state of every tensor on one rank, new values stored into all replicas")
     ap.add_argument("--shape-gbps", default=None, help="lo:hi[:seed] emulated cross-group link, e.g. 10:40:0")
     ap.add_argument("--controller", type=int, default=0, help="run the telemetry controller and apply its instructions")
+    ap.add_argument("--adapt-batch", type=int, default=0, help="with --controller: also apply the per-GPU batch sizes it assigns")
+    ap.add_argument("--slow-ranks-ms", type=float, default=0.0,
+                    help="hold the upper half of the ranks for this long in every iteration (unequal GPUs for --adapt-batch)")
     ap.add_argument("--native-copies", type=int, default=1,
                     help="cpu_offload arm: 1 lets the native engine issue the device copies itself")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -436,16 +441,29 @@ def main() -> None:
         st.state().engine_cfg.bucket_mb = args.bucket_mb
         st.state().engine_cfg.multicast = not args.no_multicast
         st.state().engine_cfg.grad_mode = args.grad_mode
-        net = st.FasterDpModelWrapper(model, sequential=False)
+        if args.impl == "nccl_sparse":
+            args.graph = 0            # the library collective between the kernel chains is not captured
+        net = st.FasterDpModelWrapper(model, sequential=False, graph=bool(args.graph), graph_warmup=max(3, args.warmup - 2),
+                                      autocast_dtype=(torch.bfloat16 if args.amp == "bf16" else None))
         net._ensure_engine()
         engine = net.engine
         if args.shape_gbps:
-            from stellatrain_b200.control.shaper import BandwidthSchedule, TokenBucket
+            from stellatrain_b200.control.shaper import BandwidthSchedule
 
             parts = args.shape_gbps.split(":")
             sched = BandwidthSchedule(seed=int(parts[2]) if len(parts) > 2 else 0, lo_gbps=float(parts[0]), hi_gbps=float(parts[1]))
-            engine.set_link_shaper(TokenBucket(sched, burst_bytes=1 << 20))
-            args.graph = 0            # the shaper and the controller act between eager launches
+            engine.set_link_shaper(sched)      # token bucket on the device: works inside the captured step too
+        if args.slow_ranks_ms > 0 and rank >= (world + 1) // 2:
+            from stellatrain_b200 import _build
+
+            hold = torch.tensor([int(args.slow_ranks_ms * 1e6)], dtype=torch.int64, device=dev)
+            plain = net._loss_of
+
+            def slowed(*inputs):
+                _build.load_extension("_C").delay(hold.data_ptr(), 1_000_000_000, torch.cuda.current_stream().cuda_stream)
+                return plain(*inputs)
+
+            net._loss_of = slowed
     else:
         if world > 1:
             dist.init_process_group("nccl", init_method=f"tcp://{master_addr}:{master_port}", world_size=world,
@@ -489,7 +507,6 @@ def main() -> None:
         from stellatrain_b200.control.controller import Controller
         from stellatrain_b200.parallel.telemetry import TelemetryHook
 
-        args.graph = 0
         ctl_port = master_port + 17
         if rank == 0:
             controller = Controller(port=ctl_port, host="127.0.0.1", adapt=True).start()
@@ -499,28 +516,22 @@ def main() -> None:
                                       [p.numel() for p in model.parameters()], False, False)
         if world > 1:
             dist.barrier()
-        hook = TelemetryHook(engine, f"127.0.0.1:{ctl_port}", args.batch, apply_batch=False)
+        hook = TelemetryHook(engine, f"127.0.0.1:{ctl_port}", args.batch, apply_batch=bool(args.adapt_batch))
+
+    sparse_arm = engine is not None      # this package's engine: the wrapper owns the iteration (eager or captured)
 
     def train_step(x, y):
-        if hook is not None:
-            with hook.step() as marker:
-                loss = fwd_bwd(x, y, marker)
-            return loss
+        if sparse_arm:
+            if hook is not None:
+                if args.adapt_batch:
+                    x, y = hook.resize_batch(x, y)
+                return hook.run(net, x, y)
+            return net.train_step(x, y)
         loss = fwd_bwd(x, y)
         if opt is not None:
             opt.step()
             opt.zero_grad(set_to_none=False)
         return loss
-
-    graphed = None
-    if args.graph and engine is not None:
-        from stellatrain_b200.parallel.graphs import GraphedStep
-
-        try:
-            graphed = GraphedStep(engine, lambda x, y: fwd_bwd(x, y), (dev_x, dev_y), warmup=max(3, args.warmup))
-        except Exception as e:  # noqa: BLE001 - fall back to eager launches, and say so in the result
-            sys.stderr.write(f"[bench] CUDA graph capture failed ({e!r}); running eagerly\n")
-            args.graph = 0
 
     dense_graph, dense_loss = None, None
     if args.impl == "dense_graph":
@@ -535,8 +546,6 @@ def main() -> None:
             dense_loss = train_step(dev_x, dev_y)
 
     def run_step_device():
-        if graphed is not None:
-            return graphed.replay()
         if dense_graph is not None:
             dense_graph.replay()
             return dense_loss
@@ -549,10 +558,7 @@ def main() -> None:
 
     def run_step_e2e(i):
         x, y = next(e2e_iter)
-        if graphed is not None:
-            graphed.copy_inputs(x, y)          # device to device, into the graph's input buffers
-            loss = graphed.replay()
-        elif dense_graph is not None:
+        if dense_graph is not None:
             dev_x.copy_(x, non_blocking=True)
             dev_y.copy_(y, non_blocking=True)
             dense_graph.replay()
@@ -600,6 +606,15 @@ def main() -> None:
 
     for i in range(max(3, args.warmup)):
         run_step_device()
+    if sparse_arm and net.graph:
+        # the wrapper captures the iteration after its eager warm-up: make sure that lies before the timed region
+        for i in range(8):
+            if net._graphs:
+                break
+            run_step_device()
+        if not net._graphs:
+            sys.stderr.write("[bench] the step was not captured; running eagerly\n")
+            args.graph = 0
     ms, clocks, launches = timed(lambda i: run_step_device(), args.steps)
     per_step = ms / args.steps
     unit_per_step = args.batch * world * (args.seq_len if lm else 1)
@@ -674,11 +689,16 @@ def main() -> None:
                              ("pinned shared memory, host pipeline, copies by the " + ("native engine" if args.native_copies else "Python class")
                               if cpu_engine is not None else args.impl), "group_size": args.group_size,
                 "state_partition": args.state_partition, "shaped_link_gbps": args.shape_gbps,
-                "controller": ({"instructions_applied": len(hook.applied), "final_ratio": engine.cfg.ratio,
-                                "shaped_gbps_achieved": (engine.shaper.achieved_gbps() if engine.shaper else None)}
-                               if hook is not None else None),
+                "controller": ({"instructions_applied": len(hook.applied), "initial_ratio": args.ratio, "final_ratio": engine.cfg.ratio,
+                                "ratio_trajectory": [(s_, r_) for s_, _b, r_ in hook.applied][-12:],
+                                "final_batch": hook.batch_size} if hook is not None else None),
+                "shaper": ({"gbps_achieved_this_rank": engine.shaper.achieved_gbps(),
+                            "gbps_scheduled_mean_this_rank": engine.shaper.scheduled_mean_gbps(),
+                            "ranks_sharing_the_link": engine.group_size, "waited_s": engine.shaper.stats()["waited_s"],
+                            "bytes_per_step_this_rank": engine.shaped_bytes_per_step()}
+                           if engine is not None and engine.shaper is not None else None),
                 "multicast": bool(engine is not None and engine.pool is not None and engine.pool.mc_ptr),
-                "cuda_graph": bool(args.graph) if engine is not None else (args.impl == "dense_graph"), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
+                "cuda_graph": bool(args.graph and net._graphs) if engine is not None else (args.impl == "dense_graph"), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
                 "l2": "per-step working set (233 MB of parameters plus activations) exceeds the 126 MB L2; no flush needed",
             },
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss, "sparse_path": sparse_path,

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kThreads) k_scatter(ApplyArgs A) {
   if (ld_volatile_u32(A.status) != kOk) return;   // includes "a stream did not arrive in time"
   if (!A.use_flags && A.stamps != nullptr && blockIdx.x == 0 && src == 0 && threadIdx.x == 0) A.stamps[2] = global_timer_ns();
   const uint2* in = A.recv + (size_t)slot * A.slot_stride + (size_t)src * A.cap;
-  const float w = A.weight[src];
+  const float w = A.weight[(size_t)slot * A.world + src];
   uint32_t sum = 0;
   for (uint32_t i = A.ent_lo + blockIdx.x * kThreads + threadIdx.x; i < A.ent_hi; i += gridDim.x * kThreads) {
     const uint2 e = load_entry(A, in, i);

@@ -4,8 +4,11 @@
 //                  tensors it owns by reading its group-mates' buffers over NVLink.  GPU form of the
 //                  reference's slice-parallel CPU gather (backend/src/engine/modules/cpu_gather.cpp:58-82),
 //                  partitioned by tensor instead of by slice so that per-tensor selection stays whole.
-//   delay          holds a stream for a number of nanoseconds read from device memory: the serialisation
-//                  time of a payload on an emulated slow link (token bucket on the host decides the value).
+//   delay          holds a stream for a number of nanoseconds read from device memory.
+//   shape          token bucket of an emulated slow link, kept on the device: a payload that the bucket cannot
+//                  cover holds the stream for its serialisation time at the scheduled rate.  Because the state
+//                  and the clock are the GPU's own, the shaper also works inside a captured step.
+//   stamp          writes the device clock into a slot (step timing that survives CUDA-graph replay).
 //   link probe     times a peer-to-peer copy with the device clock (the reference's bandwidth monitor
 //                  counts bytes on a socket, backend/src/misc/bandwidth_monitor.h:8-84).
 // Handshake of the group reduce, all flags are epochs in symmetric memory and every wait is bounded:
@@ -105,6 +108,55 @@ __global__ void k_delay(const uint64_t* ns_ptr, uint64_t cap_ns) {
 
 cudaError_t launch_delay(const uint64_t* ns_ptr, uint64_t cap_ns, cudaStream_t stream) {
   k_delay<<<1, 32, 0, stream>>>(ns_ptr, cap_ns);
+  return cudaGetLastError();
+}
+
+// Token bucket whose fill rate follows a piecewise-constant schedule (ShaperState::rate, one level per period,
+// origin at the first use).  Takes `nbytes`; when the bucket goes negative the stream is held for the time the
+// debt needs at the current rate, at most cap_ns (a bound, so that a mis-set schedule cannot hold a GPU).
+__global__ void k_shape(ShaperState* s, uint64_t nbytes, uint64_t cap_ns) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const uint64_t now = global_timer_ns();
+  if (s->last_ns == 0) {
+    s->t0_ns = now;
+    s->last_ns = now;
+    s->tokens = (double)s->burst_bytes;
+  }
+  const uint32_t levels = s->levels ? s->levels : 1u;
+  const double period_ns = (double)s->period_s * 1e9;
+  auto rate_at = [&](uint64_t t) -> double {
+    const uint64_t lvl = period_ns > 0.0 ? (uint64_t)((double)(t - s->t0_ns) / period_ns) : 0ull;
+    const double r = (double)s->rate[lvl % levels];
+    return r > 1.0 ? r : 1.0;
+  };
+  const double dt = (double)(now - s->last_ns) * 1e-9;
+  double tokens = s->tokens + dt * rate_at(s->last_ns);
+  if (tokens > (double)s->burst_bytes) tokens = (double)s->burst_bytes;
+  tokens -= (double)nbytes;
+  s->tokens = tokens;
+  s->last_ns = now;
+  s->sent_bytes += nbytes;
+  if (tokens >= 0.0) return;
+  double wait = -tokens / rate_at(now) * 1e9;
+  if (wait > (double)cap_ns) wait = (double)cap_ns;
+  const uint64_t ns = (uint64_t)wait;
+  s->waited_ns += ns;
+  while (global_timer_ns() - now < ns) __nanosleep(1000);
+}
+
+cudaError_t launch_shape(ShaperState* state, uint64_t nbytes, uint64_t cap_ns, cudaStream_t stream) {
+  if (state == nullptr) return cudaErrorInvalidValue;
+  k_shape<<<1, 32, 0, stream>>>(state, nbytes, cap_ns);
+  return cudaGetLastError();
+}
+
+__global__ void k_stamp(uint64_t* slot) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *slot = global_timer_ns();
+}
+
+cudaError_t launch_stamp(uint64_t* slot, cudaStream_t stream) {
+  if (slot == nullptr) return cudaErrorInvalidValue;
+  k_stamp<<<1, 32, 0, stream>>>(slot);
   return cudaGetLastError();
 }
 

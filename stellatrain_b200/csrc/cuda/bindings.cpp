@@ -309,6 +309,14 @@ PYBIND11_MODULE(_C, m) {
   m.def("delay", [](uint64_t ns_ptr, uint64_t cap_ns, uint64_t stream) {
     check(st::launch_delay(as_ptr<const uint64_t>(ns_ptr), cap_ns, as_ptr<CUstream_st>(stream)), "delay");
   });
+  m.attr("SIZEOF_SHAPER_STATE") = sizeof(st::ShaperState);
+  m.attr("SHAPER_LEVELS") = st::kShaperLevels;
+  m.def("shape", [](uint64_t state, uint64_t nbytes, uint64_t cap_ns, uint64_t stream) {
+    check(st::launch_shape(as_ptr<st::ShaperState>(state), nbytes, cap_ns, as_ptr<CUstream_st>(stream)), "shape");
+  });
+  m.def("stamp", [](uint64_t slot, uint64_t stream) {
+    check(st::launch_stamp(as_ptr<uint64_t>(slot), as_ptr<CUstream_st>(stream)), "stamp");
+  });
   m.def("link_probe", [](uint64_t dst, uint64_t src, uint64_t n, uint64_t out3, uint64_t ctr, uint64_t stream) {
     check(st::launch_link_probe(as_ptr<float>(dst), as_ptr<const float>(src), n, as_ptr<uint64_t>(out3), as_ptr<uint32_t>(ctr),
                                 as_ptr<CUstream_st>(stream)), "link_probe");

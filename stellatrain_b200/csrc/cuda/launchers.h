@@ -32,6 +32,12 @@ cudaError_t launch_group_reduce(const GroupArgs& args, cudaStream_t stream);
 // Holds `stream` for *ns_ptr nanoseconds (at most cap_ns).
 cudaError_t launch_delay(const uint64_t* ns_ptr, uint64_t cap_ns, cudaStream_t stream);
 
+// Takes nbytes from the device-resident token bucket; holds `stream` while the bucket is in debt (at most cap_ns).
+cudaError_t launch_shape(ShaperState* state, uint64_t nbytes, uint64_t cap_ns, cudaStream_t stream);
+
+// *slot = device clock (ns) when `stream` reaches this point.
+cudaError_t launch_stamp(uint64_t* slot, cudaStream_t stream);
+
 // Device-clock time of a copy of n floats; out3 = {elapsed, min start, max end}; the caller sets
 // out3[1] = UINT64_MAX, out3[2] = 0 and *ctr = 0 beforehand.
 cudaError_t launch_link_probe(float* dst, const float* src, uint64_t n, uint64_t* out3, uint32_t* ctr, cudaStream_t stream);

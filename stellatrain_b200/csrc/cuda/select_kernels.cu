@@ -838,16 +838,15 @@ __global__ void __launch_bounds__(kCandThreads) k_cand(SelectArgs A) {
 //   fused   a = g + r, r <- a; items at or over the threshold are counted per chunk, the chunks of a tensor chain
 //           their counts (decoupled look-back, one 64-bit word per chunk) so that every item learns its position in
 //           index order, and the first k of them go straight into the destinations' receive areas and are cleared
-//           in r.  Blocks of large tensors just under the threshold are noted as candidates for the fill.
+//           in r.  Blocks just under the threshold are noted as candidates for the fill.
 //   finish  per tensor: threshold-v pads an under-filled stream; threshold-v16 completes it with the best of
 //           the rejected blocks (backend/src/compress/thresholdv16.cpp:261-293: its heap), taken from the noted
-//           candidates or, when those do not suffice or the tensor is small, from a scan of the whole tensor by
-//           this CTA, so the stream always holds exactly what the two-pass chain would have chosen; then the
+//           candidates or, when those do not suffice, from a scan of the whole tensor by this CTA, so the
+//           stream always holds exactly what the two-pass chain would have chosen; then the
 //           threshold steps (AIMD) and the last CTA publishes the arrival flags.
 // 12 bytes per element cross HBM (read g, read r, write r) against 16 to 20 of the two-pass chain.
 constexpr int kFusedMaxIter = 16;                              // iterations of kPerIter elements per chunk
 constexpr uint32_t kFusedMaxChunk = kFusedMaxIter * kPerIter;  // 16384 elements
-constexpr uint32_t kSmallSegBlocks = 4096;                     // up to 65536 elements the finishing CTA scans the tensor itself
 constexpr uint32_t kLookbackPolls = 1u << 20;                  // bound of every wait on a predecessor chunk
 constexpr float kWindowDefault = 0.05f;                        // candidates: keys in [tau * (1 - window), tau)
 
@@ -929,7 +928,13 @@ __global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
   __shared__ uint2 s_cnd[B16 ? kFusedMaxChunk / 16 : 1];    // near-miss blocks of this chunk: (block id, key)
   __shared__ uint32_t s_word[4];   // [0] candidates staged, [1] items in front of the chunk, [2] candidate base, [3] may emit
 
+  // The chunk's place is all the first loads need: they are on their way while the tensor's descriptor, threshold
+  // and gradient pointer (a second level of dependent loads) are fetched.
   const Chunk ch = A.chunks[blockIdx.x];
+  float* r = A.resid + ch.start;
+  const uint32_t i0 = threadIdx.x * 4;
+  float4 r_next = make_float4(0.f, 0.f, 0.f, 0.f), g_next = r_next;
+  if (i0 < ch.len) r_next = *reinterpret_cast<const float4*>(r + i0);
   const SegDesc sd = A.segs[ch.seg];
   const SegState ss = A.state[ch.seg];
   SegWork* wp = &A.work[ch.seg];
@@ -947,21 +952,22 @@ __global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
     return;
   }
   if (threadIdx.x == 0) s_word[0] = 0;
-  __syncthreads();
 
   const uint32_t seg_rel = ch.start - sd.off;
   const bool tab = A.grad_tab != nullptr;
   float* g = tab ? A.grad_tab[ch.seg] + seg_rel : A.grad + ch.start;
   const uint32_t g_valid = tab ? (sd.n > seg_rel ? min(ch.len, sd.n - seg_rel) : 0u) : ch.len;
-  float* r = A.resid + ch.start;
+  const bool add = !A.skip_ef;
+  if (add && i0 < ch.len) g_next = load4_guarded(g, i0, g_valid);
   // a tensor without a threshold yet selects nothing here: the finishing kernel then takes the exact top items
   const uint32_t tau_bits = ss.inited ? __float_as_uint(ss.tau) : 0xFFFFFFFFu;
   const uint32_t kk = B16 ? (sd.k + 15u) / 16u : sd.k;
-  const bool collect = B16 && ss.inited && sd.n_pad / 16u > kSmallSegBlocks;
+  const bool collect = B16 && ss.inited;
   float window = __uint_as_float(ss.reserved[0]);
   if (!(window > 0.f && window <= 1.f)) window = kWindowDefault;
   const uint32_t lo_bits = collect ? __float_as_uint(fmaxf(ss.tau * (1.f - window), 0.f)) : 0xFFFFFFFFu;
   const uint32_t n_iter = (ch.len + kPerIter - 1) / kPerIter;   // the launcher guarantees <= kFusedMaxIter
+  __syncthreads();   // s_word[0] is cleared before anyone stages a candidate
 
   uint32_t selbits = 0;   // B16: bit `it` = this lane's block of iteration `it` is over the threshold
   uint64_t selmask = 0;   // element mode: 4 bits per iteration
@@ -969,21 +975,27 @@ __global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
   for (uint32_t it = 0; it < n_iter; ++it) {
     const uint32_t i = it * kPerIter + threadIdx.x * 4;
     const bool act = i < ch.len;
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (act) {
-      a = *reinterpret_cast<const float4*>(r + i);
-      if (!A.skip_ef) {
-        const float4 gv = load4_guarded(g, i, g_valid);
-        a.x += gv.x; a.y += gv.y; a.z += gv.z; a.w += gv.w;
-        // NaN policy: a NaN is dropped (neither sent nor kept), so it cannot poison the residual.
-        if (!(a.x == a.x)) a.x = 0.f;
-        if (!(a.y == a.y)) a.y = 0.f;
-        if (!(a.z == a.z)) a.z = 0.f;
-        if (!(a.w == a.w)) a.w = 0.f;
-        *reinterpret_cast<float4*>(r + i) = a;
-        if (A.zero_grad) store4_guarded(g, i, g_valid, make_float4(0.f, 0.f, 0.f, 0.f));
+    float4 a = r_next;
+    const float4 gv = g_next;
+    {
+      // the loads of the next iteration leave before this iteration's values are touched
+      const uint32_t in = i + kPerIter;
+      if (it + 1 < n_iter && in < ch.len) {
+        r_next = *reinterpret_cast<const float4*>(r + in);
+        if (add) g_next = load4_guarded(g, in, g_valid);
       }
     }
+    if (act && add) {
+      a.x += gv.x; a.y += gv.y; a.z += gv.z; a.w += gv.w;
+      // NaN policy: a NaN is dropped (neither sent nor kept), so it cannot poison the residual.
+      if (!(a.x == a.x)) a.x = 0.f;
+      if (!(a.y == a.y)) a.y = 0.f;
+      if (!(a.z == a.z)) a.z = 0.f;
+      if (!(a.w == a.w)) a.w = 0.f;
+      *reinterpret_cast<float4*>(r + i) = a;
+      if (A.zero_grad) store4_guarded(g, i, g_valid, make_float4(0.f, 0.f, 0.f, 0.f));
+    }
+    if (!act) a = make_float4(0.f, 0.f, 0.f, 0.f);
     if (B16) {
       const uint32_t key = __float_as_uint(quad_l1(a));   // the same value in the four lanes of a block
       const bool sel = act && key >= tau_bits;
@@ -1098,6 +1110,7 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
   __shared__ uint32_t s_tmp[kCandThreads / 32 + 1];
   __shared__ uint32_t s_res[4];
   __shared__ uint32_t s_n[2];   // [0] candidates found by the scan, [1] acknowledgements arrived
+  __shared__ uint32_t s_in[3];  // found, noted candidates, "has a threshold" as read by thread 0
 
   const uint32_t seg = blockIdx.x;
   const uint32_t tid = threadIdx.x;
@@ -1112,9 +1125,18 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
   const uint32_t nb = narrow_base_of(sd);
 
   if (ok && !(sd.reserved & kSegSkip)) {
+    // Thread 0 rewrites the tensor's state and work record at the end: everything the CTA branches on is read
+    // once, handed out through shared memory, and a barrier stands between the last read and the first write.
+    if (tid == 0) {
+      s_in[0] = wp->found;
+      s_in[1] = wp->cand_cnt;
+      s_in[2] = A.state[seg].inited;
+    }
+    __syncthreads();
     SegState ss = A.state[seg];
-    const uint32_t found = wp->found;          // items at or over the threshold in the whole tensor
-    const uint32_t c_win = wp->cand_cnt;       // near-miss blocks the one-pass kernel noted
+    ss.inited = s_in[2];
+    const uint32_t found = s_in[0];            // items at or over the threshold in the whole tensor
+    const uint32_t c_win = s_in[1];            // near-miss blocks the one-pass kernel noted
     const bool short_of = found < kk;
     uint32_t t_key = 0;
     bool scanned = false;
@@ -1129,36 +1151,78 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
         } else {
           const uint32_t need = kk - found, n_blocks = sd.n_pad / 16u;
           uint2* cand = A.cand + (sd.off >> 4);
-          uint32_t c = c_win;
-          if (n_blocks <= kSmallSegBlocks || !ss.inited || c < need) {
+          uint32_t c = min(c_win, n_blocks);   // the candidate region holds one slot per block of the tensor
+          if (!ss.inited || c < need) {
             // every block that still holds something is a candidate: the blocks over the threshold were all
             // emitted (the stream is short of them) and are zero in the residual by now
             scanned = true;
             if (tid == 0) s_n[0] = 0;
             __syncthreads();
-            for (uint32_t b0 = 0; b0 < n_blocks; b0 += kCandThreads / 4) {
-              const uint32_t b = b0 + (tid >> 2);
-              float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (b < n_blocks) a = *reinterpret_cast<const float4*>(A.resid + sd.off + b * 16u + (tid & 3u) * 4u);
-              const uint32_t key = __float_as_uint(quad_l1(a));
-              if (b < n_blocks && (tid & 3u) == 0u && key != 0u) {
-                const uint32_t slot = atomicAdd(&s_n[0], 1u);
-                cand[slot] = make_uint2((sd.off >> 4) + b, key);
+            constexpr uint32_t kRound = kCandThreads / 4;   // blocks per round, four lanes each
+            const float* src = A.resid + sd.off + (tid & 3u) * 4u;
+            for (uint32_t b0 = 0; b0 < n_blocks; b0 += 4u * kRound) {
+              float4 a[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {   // four independent loads in flight
+                const uint32_t b = b0 + u * kRound + (tid >> 2);
+                a[u] = b < n_blocks ? *reinterpret_cast<const float4*>(src + (size_t)b * 16u) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const uint32_t b = b0 + u * kRound + (tid >> 2);
+                const uint32_t key = __float_as_uint(quad_l1(a[u]));
+                if (b < n_blocks && (tid & 3u) == 0u && key != 0u) {
+                  const uint32_t slot = atomicAdd(&s_n[0], 1u);
+                  cand[slot] = make_uint2((sd.off >> 4) + b, key);
+                }
               }
             }
             __syncthreads();
             c = s_n[0];
           }
           const uint32_t take = min(need, c);
-          if (tid == 0) wp->out_cursor = found;
-          __syncthreads();
-          if (take) t_key = take_top(A, sd, wp, cand, c, take, true, kk, found + take - 1u, slot_off, dest, nb, s_hist, s_tmp, s_res);
+          if (take && c <= (uint32_t)kCandThreads) {
+            // few candidates: every thread ranks one of them against all others in shared memory (larger key
+            // first, equal keys by lower block id), and rank q goes to stream position found + q
+            uint2* s_one = reinterpret_cast<uint2*>(s_hist);       // kCandThreads pairs
+            uint32_t* s_take = s_hist;                              // reused once the ranks are known
+            const uint2 mine = tid < c ? __ldcg(cand + tid) : make_uint2(0u, 0u);
+            s_one[tid] = mine;
+            __syncthreads();
+            uint32_t rank = 0;
+            if (tid < c) {
+              for (uint32_t j = 0; j < c; ++j) {
+                const uint2 o = s_one[j];
+                rank += (o.y > mine.y || (o.y == mine.y && o.x < mine.x)) ? 1u : 0u;
+              }
+            }
+            __syncthreads();
+            if (tid < c && rank < take) s_take[rank] = mine.x;
+            if (tid < c && rank == take - 1u) s_res[0] = mine.y;
+            __syncthreads();
+            t_key = s_res[0];
+            for (uint32_t e = tid; e < take * 16u; e += kCandThreads) {
+              const uint32_t q = e >> 4, j = e & 15u;
+              const uint32_t p = (found + q) * 16u + j;
+              if (p < sd.k) {   // only the lowest-ranked block can be cut off
+                const uint32_t gi = s_take[q] * 16u + j;
+                const float a = A.resid[gi], sv = wire_value(nb, a);
+                emit_entry(A, dest, nb, slot_off, p, gi, sv);
+                A.resid[gi] = a - sv;
+              }
+            }
+          } else if (take) {
+            if (tid == 0) wp->out_cursor = found;
+            __syncthreads();
+            t_key = take_top(A, sd, wp, cand, c, take, true, kk, found + take - 1u, slot_off, dest, nb, s_hist, s_tmp, s_res);
+          }
           // fewer blocks with anything in them than the budget: the rest of the stream says "no entry"
           for (uint32_t p = (found + take) * 16u + tid; p < sd.k; p += kCandThreads)
             emit_entry(A, dest, nb, slot_off, p, kSentinelIdx, 0.f);
         }
       }
     }
+    __syncthreads();   // every thread is past its reads of the state and of the work record
     if (tid == 0) {
       if (!b16) {
         const float max_abs = __uint_as_float(wp->max_bits);
@@ -1176,7 +1240,7 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
       } else {
         if (short_of) ss.tau *= 0.99f;      // "must drop less" (thresholdv16.cpp:245-248)
         else ss.tau += ss.tau_inc;          // thresholdv16.cpp:249-252
-        if (sd.n_pad / 16u > kSmallSegBlocks) {
+        {
           // keep about as many near-miss blocks as the budget: few enough to be cheap, enough to fill from
           float w = __uint_as_float(ss.reserved[0]);
           if (!(w > 0.f && w <= 1.f)) w = kWindowDefault;

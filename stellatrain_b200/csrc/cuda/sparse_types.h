@@ -160,7 +160,9 @@ struct ApplyArgs {
   uint64_t ack_slot_stride;
   uint32_t use_flags;          // wait on arrival flags (0 when a library collective filled recv)
   uint32_t use_acks;
-  const float* weight;         // [world] weight of each source in the merge (default 1/world)
+  const float* weight;         // [2][world] weight of each source in the merge (default 1/world), row = epoch & 1:
+                               // two rows let the host switch weights at a named iteration without draining the
+                               // pipeline (the row of an epoch is rewritten between the applies of epochs e - 2 and e)
   // One 16-byte record per element of the state range: {x: dense accumulator, zero outside a scatter/apply
   // pair; y: bits of the last epoch at which the element was updated; z: momentum buffer (SGD) or first
   // moment (Adam); w: second moment (Adam)}.  Interleaved so that an update touches one 32-byte sector of
@@ -209,6 +211,22 @@ struct ApplyArgs {
   uint64_t* pflag[kMaxWorld];       // per rank: its "parameters of owner `rank` have landed" word, slot 0
   const uint64_t* pflag_local;      // [2][world] written by the owners
   uint64_t pflag_slot_stride;
+};
+
+// Token bucket of an emulated slow link, resident on the device (k_shape).  The host fills in burst, period and
+// the schedule once and zeroes the rest; it reads sent_bytes, waited_ns and the clock origin back for telemetry.
+constexpr int kShaperLevels = 64;
+struct ShaperState {
+  double tokens;            // bytes that may go out without waiting; negative: debt being repaid
+  uint64_t last_ns;         // device clock of the last refill, 0 before the first use
+  uint64_t t0_ns;           // device clock of the first use: origin of the schedule
+  uint64_t sent_bytes;
+  uint64_t waited_ns;
+  float burst_bytes;
+  float period_s;           // duration of one level of the schedule
+  uint32_t levels;          // levels in use, <= kShaperLevels
+  uint32_t reserved;
+  float rate[kShaperLevels];   // bytes per second
 };
 
 // Intra-group dense reduction (grouped topologies).

@@ -172,9 +172,18 @@ class SparseDPModelWrapper(nn.Module):
     """``model = SparseDPModelWrapper(torchvision.models.resnet152(num_classes=100)).cuda()``
 
     ``sequential=True`` reproduces the reference's layer sequence; ``False`` keeps the module as is
-    (needed for models whose forward takes several arguments)."""
+    (needed for models whose forward takes several arguments).
 
-    def __init__(self, module: nn.Module, sequential: bool = True, **engine_overrides) -> None:
+    Two ways to run an iteration.  The reference's: ``loss = criterion(model(x), y); loss.backward()``
+    (backend/test/test_end_to_end.py:62-76).  Or ``loss = model.train_step(x, y)``, which does the same and, with
+    ``graph=True``, captures the whole iteration (forward, loss, backward and the sparse kernels of every bucket)
+    in a CUDA graph after ``graph_warmup`` eager iterations and replays it from then on: one launch per iteration
+    instead of one host round trip per parameter tensor.  A change of the compression ratio, of the batch shape
+    or of the input types makes the capture stale; the next iterations run eagerly and a new capture follows."""
+
+    def __init__(self, module: nn.Module, sequential: bool = True, graph: bool = False, graph_warmup: int = 3,
+                 loss_fn: Optional[Callable] = None, autocast_dtype: Optional[torch.dtype] = None,
+                 **engine_overrides) -> None:
         super().__init__()
         if sequential:
             try:
@@ -185,6 +194,15 @@ class SparseDPModelWrapper(nn.Module):
         self.sequential = sequential
         self._overrides = engine_overrides
         self.engine = None
+        self.graph = bool(graph)
+        self.graph_warmup = max(1, int(graph_warmup))
+        self.loss_fn = loss_fn
+        self.autocast_dtype = autocast_dtype
+        self._graphs: Dict[tuple, object] = {}       # input signature -> GraphedStep
+        self._eager_by_key: Dict[tuple, int] = {}
+        self._ever_captured = False
+        self._seen_version = -1
+        self._side_stream = None
 
     def _ensure_engine(self) -> None:
         if self.engine is not None:
@@ -201,6 +219,81 @@ class SparseDPModelWrapper(nn.Module):
             raise RuntimeError("gradient accumulation needs StellaTrainDataLoader around the data iterable")
         self._ensure_engine()
         return self.module(*args, **kwargs)
+
+    # ------------------------------------------------------------------ whole iterations
+    def _loss_of(self, *inputs: torch.Tensor) -> torch.Tensor:
+        """Forward and loss.  Default rule: a module that computes its own loss from (input, target) and returns
+        (output, loss) is called with both (the GPT path of the reference, model_wrapper.py:175-182); any other module
+        gets the first tensor and its output meets the second in cross entropy."""
+        if self.loss_fn is not None:
+            return self.loss_fn(self, *inputs)
+        if self.sequential and getattr(self.module[-1], "__class__", type(None)).__name__ == "GPTHeadStage":
+            return self((inputs[0], inputs[1]))[1]
+        if self.module.__class__.__name__ == "GPT":
+            return self(*inputs)[1]
+        return F.cross_entropy(self(inputs[0]), inputs[1])
+
+    def _iteration(self, *inputs: torch.Tensor) -> torch.Tensor:
+        eng = self.engine
+        if eng is not None and not eng.cfg.step_clock:
+            eng.stamp(0)                # with the step clock on, the engine stamps behind its forward gate
+        if self.autocast_dtype is not None:
+            with torch.autocast("cuda", dtype=self.autocast_dtype):
+                loss = self._loss_of(*inputs)
+        else:
+            loss = self._loss_of(*inputs)
+        if self.engine is not None and eng is None:
+            eng = self.engine           # attached by the first forward
+        if eng is not None:
+            eng.stamp(1)
+        loss.backward()
+        if eng is not None:
+            eng.stamp(2)
+        return loss
+
+    def train_step(self, *inputs: torch.Tensor) -> torch.Tensor:
+        """One iteration (forward, loss, backward; the engine updates the parameters).  Returns the loss tensor; with
+        ``graph=True`` it is the captured step's output buffer, overwritten by the next replay."""
+        self._ensure_engine()
+        eng = self.engine
+        if not (self.graph and eng.device.type == "cuda") or frontend.gradient_accumulation() > 1:
+            return self._iteration(*inputs)
+        if self._seen_version != eng.capture_version:       # the ratio changed: captured steps are stale
+            self._graphs.clear()
+            self._eager_by_key.clear()
+            self._seen_version = eng.capture_version
+        key = tuple((tuple(t.shape), t.dtype, t.is_contiguous(memory_format=torch.channels_last) if t.dim() == 4 else False)
+                    for t in inputs)
+        g = self._graphs.get(key)
+        if g is not None:
+            g.copy_inputs(*inputs)
+            return g.replay()
+        # Eager iterations run on the stream the capture will use, so that library handles, tuned kernels and the
+        # allocator's blocks of that stream are warm when the capture begins.  The first capture waits for
+        # ``graph_warmup`` of them; a later one (new ratio, new batch shape) for one, which also brings the engine
+        # back to its steady state after the drain that a ratio change implies.
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=eng.device)
+        cur = torch.cuda.current_stream(eng.device)
+        done = self._eager_by_key.get(key, 0)
+        if done < (1 if self._ever_captured else self.graph_warmup):
+            self._side_stream.wait_stream(cur)
+            with torch.cuda.stream(self._side_stream):
+                loss = self._iteration(*inputs)
+            cur.wait_stream(self._side_stream)
+            for t in inputs:
+                t.record_stream(self._side_stream)
+            loss.record_stream(cur)
+            self._eager_by_key[key] = done + 1
+            return loss
+        from ..parallel.graphs import GraphedStep
+
+        while len(self._graphs) >= 2:                         # every capture owns a private memory pool
+            self._graphs.pop(next(iter(self._graphs)))
+        g = GraphedStep(eng, self._iteration, inputs, warmup=0, stream=self._side_stream)
+        self._graphs[key] = g
+        self._ever_captured = True
+        return g.replay()
 
     def step(self) -> Optional[float]:
         """In debug-accuracy mode, measure how far replicas drifted (must be exactly 0)."""

@@ -60,6 +60,8 @@ class EngineConfig:
                                           # has its threshold (12 bytes per element instead of 16 to 20)
     debug_checks: bool = False            # every stream carries a checksum that the receiver verifies (status 6), consumed
                                           # entries are overwritten with the "no entry" marker; slower, for debugging
+    step_clock: bool = False              # stamp the device clock at the start of every forward (behind the gate that
+                                          # waits for outstanding updates); the telemetry hook switches it on
     profile: bool = False                 # NVTX ranges and CUDA-event timers per bucket and stage (utils/stats.py)
 
 
@@ -137,7 +139,10 @@ class SparseDPEngine:
         self.micro_step = 0
         self._failed: Optional[SparseStepError] = None
         self._capturing = False       # set while a CUDA graph of the step is being captured
+        self._pending_weights: list = []   # [from_iteration, device weights, rows written]
+        self.capture_version = 0      # bumped by everything that makes a captured step stale (ratio, hyper-parameters are not)
         self._capture_keepalive: list = []
+        self._capture_rows: dict = {}     # bucket index -> pinned row of gradient addresses of the running capture
         self._build_buckets(params)
         self._wire()
         self._install_hooks()
@@ -288,14 +293,34 @@ class SparseDPEngine:
             mate_done=[pool.peer_addr(base + l, done_off) for l in mates], group_done_ctr=b._group_ctr.data_ptr(),
         )
 
-    def set_link_shaper(self, token_bucket) -> None:
-        """Emulate a constrained cross-group link: before a bucket's streams are pushed, the sparse
-        stream is held for the time the cross-group bytes would need on the shaped link
-        (``control.shaper.TokenBucket``).  Eager mode only."""
-        self.shaper = token_bucket
-        self._delay_host = torch.zeros(1, dtype=torch.int64).pin_memory()
-        self._delay_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
+    def set_link_shaper(self, shaper) -> None:
+        """Emulate a constrained cross-group link: before a bucket's streams are pushed, a one-thread kernel takes
+        the bytes that leave the group from a token bucket in device memory and holds the sparse stream while the
+        bucket is in debt (``control.shaper.DeviceTokenBucket``; a host ``TokenBucket`` or a ``BandwidthSchedule`` is
+        turned into one, the ranks of a group sharing the scheduled rate).  Works in eager and in captured steps."""
+        from ..control.shaper import BandwidthSchedule, DeviceTokenBucket, TokenBucket
+
+        if isinstance(shaper, TokenBucket):
+            shaper = DeviceTokenBucket(shaper.schedule, self.device, burst_bytes=int(shaper.burst), share=1.0 / self.group_size)
+        elif isinstance(shaper, BandwidthSchedule):
+            shaper = DeviceTokenBucket(shaper, self.device, share=1.0 / self.group_size)
+        self.shaper = shaper
         self.shaped_bytes = 0
+
+    def shaped_bytes_per_step(self) -> int:
+        """Bytes this rank stores into other groups per iteration (what the shaper charges)."""
+        return sum(rt.bucket.layout.wire_bytes(owned_only=True) for rt in self.buckets) * (self.world - self.group_size)
+
+    # ------------------------------------------------------------------ step clock
+    def stamp(self, slot: int) -> None:
+        """Write the device clock into slot 0..7 of ``step_stamps`` when the current stream gets here (capturable):
+        0 forward begins, 1 backward begins, 2 backward ended.  Step timing that survives CUDA-graph replay."""
+        from .. import _build
+
+        if not hasattr(self, "step_stamps"):
+            self.step_stamps = torch.zeros(8, dtype=torch.int64, device=self.device)
+        _build.load_extension("_C").stamp(self.step_stamps.data_ptr() + 8 * int(slot),
+                                          torch.cuda.current_stream(self.device).cuda_stream)
 
     def _install_hooks(self) -> None:
         self._hooks = []
@@ -347,8 +372,21 @@ class SparseDPEngine:
             flat = rt.bucket.grad[seg.off : seg.off + seg.numel].as_strided(p.shape, p.stride())
             flat.copy_(g)
             g = flat
-        rt.bucket.grad_tab_host[rt.tab_slot, si] = g.data_ptr()
+        self._table_row(rt)[si] = g.data_ptr()
         rt.held.append(g)
+
+    def _table_row(self, rt: _BucketRuntime) -> torch.Tensor:
+        """Pinned row of gradient addresses the hooks of the running step write: a row of the bucket's ring in eager
+        mode; under capture a row of the capture's own, which no eager step ever writes (the captured copy reads it
+        on every replay, long after eager steps have moved on through the ring)."""
+        if not self._capturing:
+            return rt.bucket.grad_tab_host[rt.tab_slot]
+        row = self._capture_rows.get(rt.bucket.index)
+        if row is None:
+            row = rt.bucket.grad_tab_host[0].clone().pin_memory()
+            self._capture_rows[rt.bucket.index] = row
+            self._capture_keepalive.append(row)
+        return row
 
     def _make_gate(self, bis: list[int]) -> Callable:
         def pre(_mod, _inp) -> None:
@@ -368,6 +406,8 @@ class SparseDPEngine:
         if self._capturing:
             # replays of a captured step serialise on their stream, which already orders this
             # forward after every update of the previous replay
+            if self.cfg.step_clock:
+                self.stamp(0)
             return
         if torch.is_grad_enabled() and not getattr(self, "_warned_unused", False):
             for bi, rt in enumerate(self.buckets):
@@ -381,12 +421,16 @@ class SparseDPEngine:
                                   f"have one (every parameter must take part in every iteration, as in the reference, "
                                   f"whose forward gate would wait for such a tensor forever)", RuntimeWarning, stacklevel=3)
                     break
+        if all(rt.pending == rt.full for rt in self.buckets):     # first micro-step of an iteration
+            self.before_iteration()
         cur = torch.cuda.current_stream(self.device)
         for bi, rt in enumerate(self.buckets):
             if bi in self._gated:
                 continue
             if rt.apply_done is not None:
                 cur.wait_event(rt.apply_done)
+        if self.cfg.step_clock:
+            self.stamp(0)             # behind the waits: time spent blocked on updates counts as gap, not as forward
         self._forward_count = getattr(self, "_forward_count", 0) + 1
         if self.cfg.status_poll_interval and self._forward_count % self.cfg.status_poll_interval == 0:
             self._poll_status()
@@ -397,7 +441,7 @@ class SparseDPEngine:
         s = self.sparse_stream
         if self.cfg.grad_mode != "flat":
             b = rt.bucket
-            b.grad_tab_dev.copy_(b.grad_tab_host[rt.tab_slot], non_blocking=True)   # compute stream, before the event
+            b.grad_tab_dev.copy_(self._table_row(rt), non_blocking=True)   # compute stream, before the event
             if not self._capturing:
                 ev = torch.cuda.Event()
                 ev.record(cur)
@@ -454,16 +498,11 @@ class SparseDPEngine:
             if self.group_size > 1:
                 b.handle.group_reduce(s.cuda_stream)
                 self.stats["kernels"] += 3
-            if self.shaper is not None and not self._capturing:
+            if self.shaper is not None:
                 nbytes = b.layout.wire_bytes(owned_only=True) * (self.world - self.group_size)   # stored into other groups
                 self.shaped_bytes += nbytes
-                wait_s = self.shaper.delay_for(nbytes)
-                if wait_s > 0:
-                    from .. import _build
-                    self._delay_host[0] = int(wait_s * 1e9)
-                    with torch.cuda.stream(s):
-                        self._delay_dev.copy_(self._delay_host, non_blocking=False)
-                    _build.load_extension("_C").delay(self._delay_dev.data_ptr(), 2_000_000_000, s.cuda_stream)
+                self.shaper.take(nbytes, s)
+                self.stats["kernels"] += 1
             b.select(s)
         rt.select_count += 1
         self.stats["select_launches"] += 1
@@ -559,16 +598,55 @@ class SparseDPEngine:
         for rt in self.buckets:
             rt.bucket.set_ratio(ratio)
         self.cfg.ratio = ratio
+        self.capture_version += 1     # stream sizes are launch arguments: a captured step is stale now
 
-    def set_rank_weights(self, weights: Iterable[float]) -> None:
-        """Weight of each rank's gradient in the merge, e.g. batch_r / sum(batch) for unequal
-        per-GPU batch sizes (the reference averages with 1/W, cpu_optimize.cpp:55)."""
-        w = list(weights)
+    def set_rank_weights(self, weights: Iterable[float], from_iteration: Optional[int] = None) -> None:
+        """Weight of each rank's gradient in the merge, e.g. batch_r / sum(batch) for unequal per-GPU batch sizes
+        (the reference averages with 1/W, cpu_optimize.cpp:55).  Without ``from_iteration`` the pipeline is drained
+        and the weights count at once.  With it they count from that iteration on (0-based count of backward passes;
+        every rank must name the same one, not earlier than the coming iteration) and nothing is drained: the
+        scatter of epoch e reads row e & 1 of a two-row table, and each row is rewritten in stream order between the
+        last apply that wants the old weights and the first that wants the new ones."""
+        w = [float(x) for x in weights]
         if len(w) != self.world:
             raise ValueError("one weight per rank")
-        self.synchronize()
-        for rt in self.buckets:
-            rt.bucket.set_weights(w)
+        if from_iteration is None:
+            self.synchronize()
+            for rt in self.buckets:
+                rt.bucket.set_weights(w)
+            return
+        now = self.iterations_started()
+        if from_iteration < now:
+            raise ValueError(f"iteration {from_iteration} has begun already (the coming one is {now})")
+        dev_w = torch.tensor(w, dtype=torch.float32, device=self.device)
+        self._pending_weights.append([int(from_iteration), dev_w, 0])
+
+    def iterations_started(self) -> int:
+        """Backward passes begun so far = index of the coming iteration."""
+        return self.buckets[-1].select_count if self.buckets else 0
+
+    def before_iteration(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Host work at the start of an iteration (first forward of its micro-steps, or a graph replay): rows of
+        the merge-weight table that become due.  Iteration i selects with epoch i + 1; its streams are applied one
+        iteration later (staleness 1) or in the same one (staleness 0).  The row of parity (i + 1) & 1 is free once
+        the apply of epoch i - 1 has been enqueued, which is the case when iteration i begins."""
+        if not self._pending_weights:
+            return
+        it = self.iterations_started()
+        # eager: the sparse stream carries the applies; a replayed graph carries them on the stream it is launched on
+        stream = stream if stream is not None else self.sparse_stream
+        keep = []
+        for entry in self._pending_weights:
+            since, w, done = entry
+            for step in (0, 1):
+                if it == since + step and done == step:
+                    with torch.cuda.stream(stream):
+                        for rt in self.buckets:
+                            rt.bucket.set_weight_row((since + step + 1) & 1, w)
+                    entry[2] = done = step + 1
+            if done < 2:
+                keep.append(entry)
+        self._pending_weights = keep
 
     # ------------------------------------------------------------------ replicas
     def broadcast_parameters(self, src: int = 0) -> None:

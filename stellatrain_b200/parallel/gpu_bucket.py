@@ -151,7 +151,8 @@ class GpuBucket:
         self.counters = torch.tensor([1, 1, 0, 0], dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.stamps = torch.zeros(8, dtype=torch.int64, device=device)    # device clock of the latest chain, see device_times()
-        self.weight = torch.full((world,), 1.0 / world, **f32)
+        # merge weight of every source, one row per epoch parity (the scatter of epoch e reads row e & 1)
+        self.weight = torch.full((2, world), 1.0 / world, **f32)
         opt = np.zeros(1, dtype=B.OPT_STATE_DTYPE)
         opt["lr"] = 1e-3
         opt["beta1"], opt["beta2"], opt["eps"] = 0.9, 0.999, 1e-8
@@ -298,7 +299,12 @@ class GpuBucket:
         self.opt[:48].copy_(torch.from_numpy(raw), non_blocking=False)
 
     def set_weights(self, weights: Sequence[float]) -> None:
-        self.weight.copy_(torch.tensor(list(weights), dtype=torch.float32))
+        """Both rows at once; the caller guarantees that no apply is in flight."""
+        self.weight.copy_(torch.tensor([list(weights)] * 2, dtype=torch.float32))
+
+    def set_weight_row(self, parity: int, weights: torch.Tensor) -> None:
+        """Stream-ordered update of the row that epochs of the given parity read (``weights``: device tensor [world])."""
+        self.weight[parity & 1].copy_(weights, non_blocking=True)
 
     # ------------------------------------------------------------------ execution
     def select(self, stream: Optional[torch.cuda.Stream] = None) -> None:

@@ -10,9 +10,16 @@ but never instantiates them in its engine.  Here the loop is closed:
         with hook.step():                       # times forward/backward, reports, applies instructions
             loss = criterion(model(x), y); loss.backward()
 
-Measurements are device times from CUDA events: forward, backward, the gap between the end of backward
-and the start of the next forward, and the time a forward spent blocked on outstanding updates (exposed
-communication).  Throughput fields come from the bytes the engine pushed during the step.
+    # or, with the wrapper's whole-iteration call (eager or replayed from a CUDA graph):
+    loss = hook.run(model, x, y)
+
+Measurements are device times: three one-thread kernels write the GPU's clock when the compute stream reaches
+the start of the forward pass (behind the wait for the updates this forward must see), the start of backward and
+its end, so the numbers are the same whether the iteration is launched kernel by kernel or replayed from a graph.
+They give forward, backward and the gap between the end of one backward and the start of the next forward, which
+holds the exposed communication: the time the stream was blocked on outstanding updates or on the shaped link.
+The stamps of iteration i are read while iteration i + 1 runs, so nothing here makes the host wait for the GPU.
+Throughput fields come from the bytes the engine pushed during the step.
 """
 from __future__ import annotations
 
@@ -37,8 +44,10 @@ class TelemetryHook:
         self.lock = threading.Lock()
         self.client = None
         self._callback = _WeakInstruction(self)
-        self._ev = {k: torch.cuda.Event(enable_timing=True) for k in ("f0", "f1", "b1", "prev_b1")}
-        self._have_prev = False
+        self._ring = [torch.zeros(3, dtype=torch.int64).pin_memory() for _ in range(4)]   # stamps of the last iterations
+        self._ring_events: List[Optional[torch.cuda.Event]] = [None] * 4
+        self._prev_b1 = 0             # device clock at the end of the previous measured backward
+        engine.cfg.step_clock = True  # the engine stamps the start of every forward behind its gate
         self.last: Dict[str, float] = {}
         self._agree_event = None
         self._agree_dev = torch.zeros(1, dtype=torch.float64, device=engine.device)
@@ -100,7 +109,8 @@ class TelemetryHook:
             all_b = [torch.zeros_like(t) for _ in range(self.engine.world)]
             dist.all_gather(all_b, t, group=self.engine.group)
             b = torch.cat(all_b)
-            self.engine.set_rank_weights((b / b.sum()).tolist())
+            # from the coming iteration on, which is the same one on every rank; nothing is drained
+            self.engine.set_rank_weights((b / b.sum()).tolist(), from_iteration=self.engine.iterations_started())
 
     def resize_batch(self, *tensors: torch.Tensor):
         """Cut or tile a batch along dim 0 to the size the controller asked for."""
@@ -117,32 +127,75 @@ class TelemetryHook:
         return tuple(out)
 
     # ------------------------------------------------------------------ per step
+    def begin(self) -> None:
+        """Start of an iteration: instructions whose effective iteration has come are applied."""
+        self._apply_due()
+
+    def end(self) -> None:
+        """End of an iteration (everything enqueued): its stamps travel to pinned memory behind it, and the
+        iteration before it, whose stamps have landed, is measured and reported."""
+        eng = self.engine
+        slot = self.iteration % len(self._ring)
+        if hasattr(eng, "step_stamps"):
+            self._ring[slot].copy_(eng.step_stamps[:3], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._ring_events[slot] = ev
+        if self.iteration > 0:
+            self._measure(self.iteration - 1)
+        self.iteration += 1
+
+    def flush(self) -> None:
+        """Measure and report the latest iteration too (end of training)."""
+        if self.iteration > 0:
+            self._measure(self.iteration - 1)
+
+    def _measure(self, it: int) -> None:
+        slot = it % len(self._ring)
+        ev = self._ring_events[slot]
+        if ev is None:
+            return
+        ev.synchronize()
+        self._ring_events[slot] = None
+        f0, f1, b1 = (int(v) for v in self._ring[slot])
+        if not (f0 and b1):
+            return
+        split = f0 <= f1 <= b1                 # the start of backward was stamped in this iteration
+        fwd = (f1 - f0) / 1e6 if split else 0.0
+        bwd = (b1 - f1) / 1e6 if split else (b1 - f0) / 1e6
+        gap = max(0.0, (f0 - self._prev_b1) / 1e6) if self._prev_b1 else 0.0
+        self._prev_b1 = b1
+        # bytes this rank stored into one peer (4-byte entries for tensors on the narrow wire format)
+        nbytes = sum(rt.bucket.layout.wire_bytes() for rt in self.engine.buckets) * self.bytes_per_entry / 8.0
+        step_ms = max(fwd + bwd + gap, 1e-3)
+        mbps = nbytes * 8.0 * max(self.engine.world - 1, 0) / (step_ms * 1000.0)
+        if self.engine.shaper is not None:
+            # a shaped cross-group link: what the controller has to fit is the traffic that crosses it
+            mbps = self.engine.shaped_bytes_per_step() * 8.0 / (step_ms * 1000.0)
+        self.last = {"fwd_delay_ms": fwd, "bwd_delay_ms": bwd, "bwd_fwd_gap_ms": gap, "intra_fwd_gap_ms": 0.0,
+                     "grad_send_thpt_mbps": mbps, "grad_recv_thpt_mbps": mbps}
+        if self.client is not None and self.client.alive():
+            cfg = self._TrainConfig(self.batch_size, self.engine.cfg.grad_accumulation, self.engine.cfg.ratio)
+            self.client.report(it, cfg, [mbps, mbps, fwd, bwd, gap, 0.0], self._callback)
+
     @contextlib.contextmanager
     def step(self):
-        self._apply_due()
-        e = self._ev
-        e["f0"].record()
-        marker = _BackwardStart(e["f1"])
+        """Around a hand-written iteration: ``marker.backward_begins()`` between forward and backward."""
+        self.begin()
+        marker = _BackwardStart(self.engine)
         try:
             yield marker
         finally:
-            e["b1"].record()
-            e["b1"].synchronize()
-            fwd = e["f0"].elapsed_time(e["f1"]) if marker.recorded else 0.0
-            bwd = e["f1"].elapsed_time(e["b1"]) if marker.recorded else e["f0"].elapsed_time(e["b1"])
-            gap = e["prev_b1"].elapsed_time(e["f0"]) if self._have_prev else 0.0
-            e["prev_b1"], e["b1"] = e["b1"], e["prev_b1"]
-            self._have_prev = True
-            # bytes this rank stored into one peer (4-byte entries for tensors on the narrow wire format)
-            nbytes = sum(rt.bucket.layout.wire_bytes() for rt in self.engine.buckets) * self.bytes_per_entry / 8.0
-            step_ms = max(fwd + bwd + gap, 1e-3)
-            mbps = nbytes * 8.0 * max(self.engine.world - 1, 0) / (step_ms * 1000.0)
-            self.last = {"fwd_delay_ms": fwd, "bwd_delay_ms": bwd, "bwd_fwd_gap_ms": gap, "intra_fwd_gap_ms": 0.0,
-                         "grad_send_thpt_mbps": mbps, "grad_recv_thpt_mbps": mbps}
-            if self.client is not None and self.client.alive():
-                cfg = self._TrainConfig(self.batch_size, self.engine.cfg.grad_accumulation, self.engine.cfg.ratio)
-                self.client.report(self.iteration, cfg, [mbps, mbps, fwd, bwd, gap, 0.0], self._callback)
-            self.iteration += 1
+            self.engine.stamp(2)
+            self.end()
+
+    def run(self, net, *inputs: torch.Tensor) -> torch.Tensor:
+        """One whole iteration through the wrapper (``net.train_step``), eager or replayed from a CUDA graph."""
+        self.begin()
+        try:
+            return net.train_step(*inputs)
+        finally:
+            self.end()
 
 
 class _WeakInstruction:
@@ -163,9 +216,9 @@ class _WeakInstruction:
 class _BackwardStart:
     """``marker.backward_begins()`` between forward and backward splits the two device times."""
 
-    def __init__(self, ev: torch.cuda.Event) -> None:
-        self.ev, self.recorded = ev, False
+    def __init__(self, engine) -> None:
+        self.engine, self.recorded = engine, False
 
     def backward_begins(self) -> None:
-        self.ev.record()
+        self.engine.stamp(1)
         self.recorded = True

@@ -50,7 +50,7 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
         model = model.to(dev)
         if args.channels_last and not lm:
             model = model.to(memory_format=torch.channels_last)
-        net = st.FasterDpModelWrapper(model, sequential=not lm)
+        net = st.FasterDpModelWrapper(model, sequential=not lm, graph=args.graph, graph_warmup=args.graph_warmup)
         sync, engine_of = st.synchronize, (lambda: net.engine)
     else:
         from stellatrain_b200.cpu_tier import CpuOffloadEngine
@@ -139,14 +139,18 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
                 pass
             if hook is not None:
                 data, target = hook.resize_batch(data, target)
-            ctx = hook.step() if hook is not None else None
-            marker = ctx.__enter__() if ctx is not None else None
-            loss = net(data, target)[1] if lm else F.cross_entropy(net(data), target)
-            if marker is not None:
-                marker.backward_begins()
-            loss.backward()
-            if ctx is not None:
-                ctx.__exit__(None, None, None)
+            if args.tier == "gpu" and args.graph and args.gradient_accumulation == 1:
+                # the wrapper owns the whole iteration: eager at first, then captured once and replayed
+                loss = hook.run(net, data, target) if hook is not None else net.train_step(data, target)
+            else:
+                ctx = hook.step() if hook is not None else None
+                marker = ctx.__enter__() if ctx is not None else None
+                loss = net(data, target)[1] if lm else F.cross_entropy(net(data), target)
+                if marker is not None:
+                    marker.backward_begins()
+                loss.backward()
+                if ctx is not None:
+                    ctx.__exit__(None, None, None)
             if loader.is_eoi:
                 global_step += 1
                 if monitor is not None:
@@ -211,6 +215,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--num-workers", type=int, default=8)
     p.add_argument("--gradient-accumulation", type=int, default=1)
     p.add_argument("--channels-last", action="store_true")
+    p.add_argument("--graph", action="store_true",
+                   help="GPU tier: capture the iteration in a CUDA graph after --graph-warmup eager iterations and replay it")
+    p.add_argument("--graph-warmup", type=int, default=3)
     p.add_argument("--telemetry-uri", default=None)
     p.add_argument("--checkpoint", default=None, help="written at the end and every --checkpoint-every iterations")
     p.add_argument("--checkpoint-every", type=int, default=0)

@@ -413,3 +413,128 @@ def test_cpu_offload_tier_with_a_cuda_model(native_copies):
     assert losses[-1] < 0.9 * losses[0]        # the hidden layer has to learn for this, not only the output bias
     assert "Total" in eng.stats_json()
     eng.close()
+
+
+def _wrapper_run(graph, data, ratio_change_at=None, eager_detour_at=None):
+    """Train small_net through the wrapper's whole-iteration call; returns the final parameters."""
+    import stellatrain_b200 as st
+
+    st.detach()
+    st.configure("127.0.0.1", 29541, 1, 0, 0, 1, 0, "thresholdv16", 1, staleness=1)
+    st.configure_compression_ratio(0.9)
+    torch.backends.cudnn.deterministic = True       # weight-gradient kernels may otherwise sum in a run-dependent order
+    st.state().engine_cfg.min_ratio = 0.5
+    st.state().engine_cfg.bucket_mb = 0.004
+    st.state().engine_cfg.chunk_elems = 1024
+    st.set_optimizer("adam")
+    st.configure_optimizer("lr", 1e-2)
+    net = st.FasterDpModelWrapper(small_net(), sequential=False, graph=graph, graph_warmup=2)
+    losses = []
+    for i, (x, y) in enumerate(data):
+        if ratio_change_at is not None and i == ratio_change_at:
+            net.engine.set_compression_ratio(0.8)
+        if eager_detour_at is not None and i == eager_detour_at:
+            F.cross_entropy(net(x), y).backward()          # the reference's way of running an iteration, in between replays
+            continue
+        losses.append(float(net.train_step(x, y)))
+    st.synchronize()
+    net.engine.check_status()
+    out = [p.detach().clone() for p in net.parameters()], losses, bool(net._graphs), net.engine.stats.get("graph_replays", 0)
+    st.detach()
+    from stellatrain_b200.parallel.engine import EngineConfig
+
+    st.state().engine_cfg = EngineConfig()          # the frontend's configuration is process-wide: leave it as found
+    return out
+
+
+@pytest.mark.parametrize("scenario", ["plain", "ratio_change", "eager_detour"])
+def test_wrapper_train_step_graph_equals_eager(scenario):
+    """The captured iteration is the product path of the wrapper: same parameters as eager launches, also across a
+    change of the compression ratio (the capture goes stale, one eager iteration, a new capture) and across an
+    iteration run the reference's way between replays (gradient addresses of eager steps never reach a replay)."""
+    data = batches(12)
+    kw = {"ratio_change": dict(ratio_change_at=7), "eager_detour": dict(eager_detour_at=8)}.get(scenario, {})
+    p_eager, l_eager, captured_e, _ = _wrapper_run(False, data, **kw)
+    p_graph, l_graph, captured_g, replays = _wrapper_run(True, data, **kw)
+    assert not captured_e and captured_g and replays >= 5
+    for p, q in zip(p_eager, p_graph):
+        torch.testing.assert_close(p, q, rtol=1e-5, atol=1e-6)
+    assert l_graph[-1] == pytest.approx(l_eager[-1], rel=1e-4)
+
+
+def test_device_token_bucket_paces_a_stream_also_inside_a_graph():
+    """The shaper on the device: payloads beyond the burst hold the stream for bytes / rate, measured with the GPU's
+    own clock, both launched directly and replayed from a captured graph."""
+    from stellatrain_b200 import _build
+    from stellatrain_b200.control.shaper import BandwidthSchedule, DeviceTokenBucket
+
+    C = _build.load_extension("_C")
+    dev = torch.device("cuda:0")
+    sched = BandwidthSchedule(seed=1, lo_gbps=8.0, hi_gbps=8.0, period_s=10.0)      # 1 GB/s flat
+    stamps = torch.zeros(2, dtype=torch.int64, device=dev)
+    s = torch.cuda.Stream()
+    for captured in (False, True):
+        tb = DeviceTokenBucket(sched, dev, burst_bytes=1 << 16)
+        def burst():
+            C.stamp(stamps.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            for _ in range(10):
+                tb.take(1_000_000, torch.cuda.current_stream())       # 10 MB at 1 GB/s: about 10 ms
+            C.stamp(stamps.data_ptr() + 8, torch.cuda.current_stream().cuda_stream)
+        with torch.cuda.stream(s):
+            if captured:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s):
+                    burst()
+                g.replay()
+            else:
+                burst()
+        torch.cuda.synchronize()
+        ms = float(stamps[1] - stamps[0]) / 1e6
+        st = tb.stats()
+        assert st["sent_bytes"] == 10_000_000
+        assert 8.0 < ms < 14.0, (captured, ms)
+        assert tb.achieved_gbps() == pytest.approx(8.0, rel=0.25)
+
+
+class _CoefficientNet(nn.Module):
+    """loss = sum <p, c>: the gradient is the coefficient tensor, independent of the parameters."""
+
+    def __init__(self):
+        super().__init__()
+        g = torch.Generator().manual_seed(3)
+        self.ps = nn.ParameterList([nn.Parameter(torch.randn(n, generator=g)) for n in (3000, 700, 64)])
+
+    def forward(self, coeffs):
+        return sum((p * c).sum() for p, c in zip(self.ps, coeffs))
+
+
+@pytest.mark.parametrize("staleness", [0, 1])
+def test_rank_weights_switch_at_a_named_iteration_without_draining(staleness):
+    """Merge weights that count from iteration s on: with learning rate 1 and gradients that do not depend on the
+    parameters, the run that halves its weight at s ends exactly halfway between the run that stops at s and the
+    run that never switches."""
+    steps, since = 9, 4
+
+    def run(n_steps, switch):
+        model = _CoefficientNet().cuda()
+        eng = make_engine(model, compressor="topk", ratio=0.9, optimizer="sgd", staleness=staleness,
+                          optimizer_options={"lr": 1.0}, bucket_mb=0.008)
+        g = torch.Generator(device="cuda").manual_seed(77)
+        for i in range(n_steps):
+            if switch and i == 2:
+                eng.set_rank_weights([0.5], from_iteration=since)      # announced early, counts from `since`
+            model([torch.randn(p.numel(), device="cuda", generator=g) for p in model.ps]).backward()
+        eng.synchronize()
+        eng.check_status()
+        out = [p.detach().clone() for p in model.ps]
+        eng.close()
+        return out
+
+    full, half, head = run(steps, False), run(steps, True), run(since, False)
+    for a, b, c in zip(full, half, head):
+        torch.testing.assert_close(b - c, 0.5 * (a - c), rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError):
+        model = _CoefficientNet().cuda()
+        eng = make_engine(model, compressor="topk", ratio=0.9, optimizer="sgd")
+        model([torch.randn(p.numel(), device="cuda") for p in model.ps]).backward()
+        eng.set_rank_weights([1.0], from_iteration=0)
