@@ -52,6 +52,10 @@ EXTENSIONS = {
     "_C": {
         "cu": ["cuda/select_kernels.cu", "cuda/apply_kernels.cu", "cuda/aux_kernels.cu", "cuda/noalloc_entry.cu"],
         "cpp": ["cuda/bindings.cpp"],
+        # compiled against the torch headers and linked with the torch libraries: the native step engine registers
+        # C++ hooks on autograd's accumulation nodes (the reference links its engine against torch the same way,
+        # backend/CMakeLists.txt:12-16, 84-100)
+        "torch_cpp": ["cuda/native_engine.cpp"],
         "link": "nvcc",
     },
     "_Ccpu": {
@@ -67,11 +71,23 @@ EXTENSIONS = {
 }
 
 
+def _torch_paths() -> dict:
+    """Include and library directories of the installed torch (found without importing it)."""
+    spec = importlib.util.find_spec("torch")
+    if spec is None or not spec.submodule_search_locations:
+        raise RuntimeError("the native step engine needs torch's headers and libraries")
+    root = Path(list(spec.submodule_search_locations)[0])
+    version = (root / "version.py").read_text() if (root / "version.py").exists() else ""
+    return {"include": [root / "include", root / "include" / "torch" / "csrc" / "api" / "include"], "lib": root / "lib",
+            "version": version}
+
+
 def _existing(name: str) -> dict:
     spec = EXTENSIONS[name]
     return {
         "cu": [s for s in spec["cu"] if (CSRC / s).exists()],
         "cpp": [s for s in spec["cpp"] if (CSRC / s).exists()],
+        "torch_cpp": [s for s in spec.get("torch_cpp", []) if (CSRC / s).exists()],
         "link": spec["link"],
     }
 
@@ -80,7 +96,9 @@ def _source_hash(name: str) -> str:
     spec = _existing(name)
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + CXX_FLAGS).encode())
-    files = [CSRC / s for s in spec["cu"] + spec["cpp"]]
+    files = [CSRC / s for s in spec["cu"] + spec["cpp"] + spec["torch_cpp"]]
+    if spec["torch_cpp"]:
+        h.update(_torch_paths()["version"].encode())
     files += sorted(CSRC.rglob("*.h")) + sorted(CSRC.rglob("*.cuh")) + sorted(CSRC.rglob("*.hpp"))
     for f in files:
         h.update(str(f.relative_to(CSRC)).encode())
@@ -134,6 +152,18 @@ def build_extension(name: str, force: bool = False, verbose: bool = False) -> Pa
         obj = OBJ_DIR / (name + "_" + s.replace("/", "_") + ".o")
         jobs.append(["g++", *CXX_FLAGS, *inc, "-c", str(CSRC / s), "-o", str(obj)])
         objs.append(obj)
+    link_extra = []
+    if spec["torch_cpp"]:
+        tp = _torch_paths()
+        tinc = [f"-I{CSRC}", f"-I{CSRC / 'cuda'}", *[f"-I{d}" for d in tp["include"]], f"-I{sysconfig.get_paths()['include']}",
+                f"-I{CUDA_HOME / 'include'}"]
+        for s in spec["torch_cpp"]:
+            obj = OBJ_DIR / (name + "_" + s.replace("/", "_") + ".o")
+            jobs.append(["g++", *[f for f in CXX_FLAGS if f != "-Wall"], "-D_GLIBCXX_USE_CXX11_ABI=1", *tinc, "-c", str(CSRC / s),
+                         "-o", str(obj)])
+            objs.append(obj)
+        link_extra = [f"-L{tp['lib']}", "-ltorch_python", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10_cuda", "-lc10",
+                      "-Xlinker", f"-rpath={tp['lib']}"]
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
         outs = list(ex.map(_run, jobs))
     if verbose:
@@ -142,7 +172,7 @@ def build_extension(name: str, force: bool = False, verbose: bool = False) -> Pa
                 print(o)
     so = so_path(name)
     if spec["link"] == "nvcc":
-        _run([nvcc, "-shared", "-o", str(so), *map(str, objs)])
+        _run([nvcc, "-shared", "-o", str(so), *map(str, objs), *link_extra])
     else:
         _run(["g++", "-shared", "-o", str(so), *map(str, objs), "-pthread", "-lrt", "-ldl"])
     _stamp_path(name).write_text(json.dumps({"hash": _source_hash(name)}))

@@ -8,7 +8,8 @@
 #include <string>
 #include <vector>
 
-#include "launchers.h"
+#include "bucket_handle.h"
+#include "native_engine.h"
 
 namespace py = pybind11;
 using st::ApplyArgs;
@@ -26,15 +27,11 @@ void check(cudaError_t e, const char* what) {
 
 // One bucket's pre-filled kernel arguments.  Filled once at set-up; `select` and `apply` are then
 // a handful of kernel launches without any per-call marshalling.
-struct BucketHandle {
-  SelectArgs sel;
-  ApplyArgs app;
-  uint32_t randomk_seed = 0x5DEECE66u;
-  int max_ctas_per_source = 148 * 16;
-
+struct BucketHandle : public st::BucketHandle {
   BucketHandle() {
     std::memset(&sel, 0, sizeof(sel));
     std::memset(&app, 0, sizeof(app));
+    std::memset(&grp, 0, sizeof(grp));
     sel.timeout_ns = app.timeout_ns = 2000000000ull;
   }
 
@@ -51,8 +48,6 @@ struct BucketHandle {
     app.last = as_ptr<uint32_t>(last);
     app.n_total = n_total;
   }
-
-  uint32_t max_chunk_len = 0;   // longest chunk of the chunk table (decides whether the one-pass select may run)
 
   void set_tables(uint64_t segs, uint64_t state, uint64_t work, uint64_t chunks, uint64_t chunk_cnt,
                   uint64_t chunk_pos, uint64_t hist, uint32_t n_segs, uint32_t n_chunks, uint32_t cap,
@@ -79,7 +74,7 @@ struct BucketHandle {
     sel.cand_cap = cand_cap;
   }
 
-  // counters: [sel_epoch, app_epoch, sel_done, app_done] as four u32 words; status: one u32 word
+  // counters: [sel_epoch, app_epoch, sel_done, app_done, chunk ticket, 3 spare] as eight u32 words; status: one u32 word
   void set_control(uint64_t counters, uint64_t status, uint64_t opt, uint64_t weight, uint64_t timeout_ns, uint64_t stamps) {
     uint32_t* c = as_ptr<uint32_t>(counters);
     sel.epoch = c + 0;
@@ -87,6 +82,7 @@ struct BucketHandle {
     app.sel_epoch = c + 0;
     sel.done_ctr = c + 2;
     app.done_ctr = c + 3;
+    sel.chunk_ticket = c + 4;    // counters holds eight words
     sel.status = app.status = as_ptr<uint32_t>(status);
     app.opt = as_ptr<st::OptState>(opt);
     app.weight = as_ptr<const float>(weight);
@@ -175,8 +171,6 @@ struct BucketHandle {
   }
 
   // grouped mode -------------------------------------------------------------------------------
-  st::GroupArgs grp;
-  bool has_group = false;
   // mates: addresses of the group-mates' flat gradient buffers; flag areas are [group size] u64 words
   // indexed by the local rank of the writer.
   void set_group(uint64_t grad_local, const std::vector<uint64_t>& mate_grad, const std::vector<int>& mate_local,
@@ -199,28 +193,15 @@ struct BucketHandle {
     grp.done_ctr = as_ptr<uint32_t>(group_done_ctr);
     has_group = grp.n_mates > 0;
   }
-  void group_reduce(uint64_t stream) {
-    if (!has_group) return;
-    grp.segs = sel.segs;
-    grp.chunks = sel.chunks;
-    grp.n_chunks = sel.n_chunks;
-    grp.epoch = sel.epoch;
-    grp.status = sel.status;
-    grp.timeout_ns = sel.timeout_ns;
-    check(st::launch_group_reduce(grp, as_ptr<CUstream_st>(stream)), "launch_group_reduce");
+  void py_group_reduce(uint64_t stream) {
+    check(st::BucketHandle::group_reduce(as_ptr<CUstream_st>(stream)), "launch_group_reduce");
   }
 
-  // fused: the one-pass chain of the threshold compressors; every tensor of the bucket must have its threshold
-  // (one select through the four-kernel chain, or a restored checkpoint)
-  void select(uint64_t stream, bool fused) {
-    if (fused) {
-      if (!st::fused_select_possible(sel, max_chunk_len)) throw std::runtime_error("one-pass select is not available for this bucket");
-      check(st::launch_select_fused(sel, as_ptr<CUstream_st>(stream)), "launch_select_fused");
-      return;
-    }
-    check(st::launch_select(sel, randomk_seed, as_ptr<CUstream_st>(stream)), "launch_select");
+  // The one-pass chain of the threshold compressors runs when it is enabled, possible for this bucket and every
+  // tensor has its threshold; otherwise the four-kernel chain.
+  void py_select(uint64_t stream) {
+    check(st::BucketHandle::select(as_ptr<CUstream_st>(stream)), "launch_select");
   }
-  bool can_fuse() const { return st::fused_select_possible(sel, max_chunk_len); }
   // Debug checks.  cksum areas are [2][world] u32 indexed [slot][source]; cksum_acc has MAX_WORLD words, rsum `world`.
   void set_debug(uint64_t cksum_acc, uint64_t rsum, uint64_t cksum_local, const std::vector<uint64_t>& peer_cksum, bool poison) {
     const int world = app.world;
@@ -234,8 +215,8 @@ struct BucketHandle {
     app.poison = poison ? 1u : 0u;
   }
 
-  void apply(uint64_t stream, int phase) {
-    check(st::launch_apply(app, max_ctas_per_source, phase, as_ptr<CUstream_st>(stream)), "launch_apply");
+  void py_apply(uint64_t stream, int phase) {
+    check(st::BucketHandle::apply(as_ptr<CUstream_st>(stream), phase), "launch_apply");
   }
 };
 
@@ -289,14 +270,61 @@ PYBIND11_MODULE(_C, m) {
       .def("set_group", &BucketHandle::set_group, py::arg("grad_local"), py::arg("mate_grad"), py::arg("mate_local"),
            py::arg("my_local"), py::arg("ready_local"), py::arg("mate_ready"), py::arg("done_local"), py::arg("mate_done"),
            py::arg("group_done_ctr"))
-      .def("group_reduce", &BucketHandle::group_reduce, py::arg("stream"))
-      .def("select", &BucketHandle::select, py::arg("stream"), py::arg("fused") = false)
-      .def("can_fuse", &BucketHandle::can_fuse)
+      .def("group_reduce", &BucketHandle::py_group_reduce, py::arg("stream"))
+      .def("select", &BucketHandle::py_select, py::arg("stream"))
+      .def("can_fuse", [](const BucketHandle& h) { return h.can_fuse(); })
+      .def_readwrite("fused_enabled", &BucketHandle::fused_enabled)
+      .def_readwrite("thresholds_ready", &BucketHandle::thresholds_ready)
+      .def_readonly("last_select_fused", &BucketHandle::last_select_fused)
+      .def_property_readonly("select_kernels", [](const BucketHandle& h) { return h.select_kernels(); })
+      .def_property_readonly("apply_kernels", [](const BucketHandle& h) { return h.apply_kernels(); })
       .def("set_owner", &BucketHandle::set_owner, py::arg("bounds"), py::arg("state_base"), py::arg("state_len"),
            py::arg("wb_local"), py::arg("peer_wb"), py::arg("wb_mc"), py::arg("pflag_local"), py::arg("peer_pflag"))
       .def("set_debug", &BucketHandle::set_debug, py::arg("cksum_acc"), py::arg("rsum"), py::arg("cksum_local"),
            py::arg("peer_cksum"), py::arg("poison"))
-      .def("apply", &BucketHandle::apply, py::arg("stream"), py::arg("phase") = 0);
+      .def("apply", &BucketHandle::py_apply, py::arg("stream"), py::arg("phase") = 0);
+
+  // Native step engine: C++ hooks on the parameters, bucket bookkeeping, stream and event choreography.
+  py::class_<st::NativeEngine>(m, "NativeEngine")
+      .def(py::init<int, uint64_t, int, int>(), py::arg("device"), py::arg("sparse_stream"), py::arg("staleness"),
+           py::arg("grad_accumulation"))
+      .def("add_bucket",
+           [](st::NativeEngine& e, BucketHandle& h, py::object select_handle, int n_params, bool steal, uint64_t table_host,
+              int table_ring, uint64_t table_dev, py::object flat_grad, const std::vector<uint32_t>& seg_off,
+              const std::vector<uint32_t>& seg_numel, uint64_t shaped_bytes) {
+             st::NativeBucketSpec spec;
+             spec.handle = &h;
+             spec.select_handle = select_handle.is_none() ? nullptr : static_cast<st::BucketHandle*>(&select_handle.cast<BucketHandle&>());
+             spec.n_params = n_params;
+             spec.steal = steal;
+             spec.table_host = as_ptr<uint64_t>(table_host);
+             spec.table_ring = table_ring;
+             spec.table_dev = as_ptr<uint64_t>(table_dev);
+             spec.flat_grad = flat_grad.is_none() ? nullptr : flat_grad.ptr();
+             spec.seg_off = seg_off;
+             spec.seg_numel = seg_numel;
+             spec.shaped_bytes = shaped_bytes;
+             return e.add_bucket(spec);
+           },
+           py::arg("handle"), py::arg("select_handle"), py::arg("n_params"), py::arg("steal"), py::arg("table_host"),
+           py::arg("table_ring"), py::arg("table_dev"), py::arg("flat_grad"), py::arg("seg_off"), py::arg("seg_numel"),
+           py::arg("shaped_bytes") = 0, py::keep_alive<1, 2>())
+      .def("add_param", [](st::NativeEngine& e, int bucket, int seg, py::handle p) { e.add_param(bucket, seg, p.ptr()); })
+      .def("remove_hooks", &st::NativeEngine::remove_hooks)
+      .def("set_shaper", [](st::NativeEngine& e, uint64_t state, uint64_t cap_ns) { e.set_shaper(as_ptr<void>(state), cap_ns); })
+      .def("set_shaped_bytes", &st::NativeEngine::set_shaped_bytes)
+      .def("wait_applies", &st::NativeEngine::wait_applies, py::arg("stream"), py::arg("bucket") = -1)
+      .def("flush", &st::NativeEngine::flush, py::arg("stream"))
+      .def("begin_capture", &st::NativeEngine::begin_capture)
+      .def("end_capture", [](st::NativeEngine& e) { return py::reinterpret_steal<py::object>(e.end_capture()); })
+      .def("select_count", &st::NativeEngine::select_count)
+      .def("apply_count", &st::NativeEngine::apply_count)
+      .def("pending_apply", &st::NativeEngine::pending_apply)
+      .def("pending_hooks", &st::NativeEngine::pending_hooks)
+      .def("set_counts", &st::NativeEngine::set_counts)
+      .def("kernels_launched", &st::NativeEngine::kernels_launched)
+      .def("shaped_bytes", &st::NativeEngine::shaped_bytes)
+      .def("last_error", &st::NativeEngine::last_error);
 
   m.def("max_abs_diff", [](uint64_t a, uint64_t b, uint64_t n, uint64_t out_bits, uint64_t stream) {
     check(st::launch_max_abs_diff(as_ptr<const float>(a), as_ptr<const float>(b), n, as_ptr<uint32_t>(out_bits),

@@ -60,30 +60,88 @@ class EngineConfig:
                                           # has its threshold (12 bytes per element instead of 16 to 20)
     debug_checks: bool = False            # every stream carries a checksum that the receiver verifies (status 6), consumed
                                           # entries are overwritten with the "no entry" marker; slower, for debugging
+    native_hooks: bool = True             # C++ hooks on the parameters and C++ bucket scheduling (csrc/cuda/native_engine.cpp);
+                                          # False: the same protocol from Python hooks (needed by profile=True and by the
+                                          # library-collective baseline transport)
     step_clock: bool = False              # stamp the device clock at the start of every forward (behind the gate that
                                           # waits for outstanding updates); the telemetry hook switches it on
     profile: bool = False                 # NVTX ranges and CUDA-event timers per bucket and stage (utils/stats.py)
 
 
 class _BucketRuntime:
-    __slots__ = ("bucket", "params", "pending", "full", "grad_ready", "apply_done", "has_pending_apply",
-                 "select_count", "apply_count", "first_module", "held", "seg_of", "tab_slot", "tab_events")
+    """Host-side state of one bucket.  With the native step engine the counters live there and these fields read
+    and write through to it."""
 
     def __init__(self, bucket: GpuBucket, params: list[nn.Parameter], ga: int):
         self.bucket = bucket
+        self.index = bucket.index
         self.params = params
         self.full = len(params) * ga
-        self.pending = self.full
+        self._pending = self.full
         self.grad_ready = torch.cuda.Event()
         self.apply_done: Optional[torch.cuda.Event] = None
-        self.has_pending_apply = False
-        self.select_count = 0
-        self.apply_count = 0
+        self._has_pending_apply = False
+        self._select_count = 0
+        self._apply_count = 0
         self.first_module = None
         self.held: list = []          # gradient tensors the current select reads ("steal" mode)
         self.seg_of = {id(p): i for i, p in enumerate(params)}
         self.tab_slot = 0             # row of the pinned pointer-table ring the hooks write now
         self.tab_events: list = [None] * GpuBucket.GRAD_TAB_RING
+        self.native = None            # the C++ step engine, when it drives this bucket
+
+    def _push(self, selects=None, applies=None, pending_apply=None) -> None:
+        n = self.native
+        n.set_counts(self.index, n.select_count(self.index) if selects is None else int(selects),
+                     n.apply_count(self.index) if applies is None else int(applies),
+                     n.pending_apply(self.index) if pending_apply is None else bool(pending_apply))
+
+    @property
+    def select_count(self) -> int:
+        return self.native.select_count(self.index) if self.native is not None else self._select_count
+
+    @select_count.setter
+    def select_count(self, v: int) -> None:
+        if self.native is not None:
+            self._push(selects=v)
+        else:
+            self._select_count = int(v)
+
+    @property
+    def apply_count(self) -> int:
+        return self.native.apply_count(self.index) if self.native is not None else self._apply_count
+
+    @apply_count.setter
+    def apply_count(self, v: int) -> None:
+        if self.native is not None:
+            self._push(applies=v)
+        else:
+            self._apply_count = int(v)
+
+    @property
+    def has_pending_apply(self) -> bool:
+        return self.native.pending_apply(self.index) if self.native is not None else self._has_pending_apply
+
+    @has_pending_apply.setter
+    def has_pending_apply(self, v: bool) -> None:
+        if self.native is not None:
+            self._push(pending_apply=v)
+        else:
+            self._has_pending_apply = bool(v)
+
+    @property
+    def pending(self) -> int:
+        """Gradient hooks still to come before the bucket is ready (``full`` between iterations)."""
+        return self.native.pending_hooks(self.index) if self.native is not None else self._pending
+
+    @pending.setter
+    def pending(self, v: int) -> None:
+        if self.native is not None:
+            if int(v) != self.full:
+                raise ValueError("the native engine only resets the hook counter")
+            self._push()
+        else:
+            self._pending = int(v)
 
 
 class SparseDPEngine:
@@ -133,6 +191,7 @@ class SparseDPEngine:
         if self.partitioned and (transport != "peer" or L > 1):
             raise ValueError("partitioned optimiser state needs the peer transport and group_size 1")
         self.shaper = None
+        self._shaped_bytes = 0
         low, high = torch.cuda.Stream.priority_range()
         self.sparse_stream = torch.cuda.Stream(device=self.device, priority=high)
         self.iteration = 0            # completed optimiser iterations (selects issued per bucket)
@@ -305,7 +364,44 @@ class SparseDPEngine:
         elif isinstance(shaper, BandwidthSchedule):
             shaper = DeviceTokenBucket(shaper, self.device, share=1.0 / self.group_size)
         self.shaper = shaper
-        self.shaped_bytes = 0
+        self._shaped_bytes = 0
+        self._push_shaper()
+
+    def _push_shaper(self) -> None:
+        if self.native is None or self.shaper is None:
+            return
+        self.native.set_shaper(self.shaper.state.data_ptr(), self.shaper.MAX_HOLD_NS)
+        for bi, rt in enumerate(self.buckets):
+            self.native.set_shaped_bytes(bi, rt.bucket.layout.wire_bytes(owned_only=True) * (self.world - self.group_size))
+
+    @property
+    def shaped_bytes(self) -> int:
+        """Bytes charged to the link shaper so far."""
+        return self._shaped_bytes + (self.native.shaped_bytes() if self.native is not None else 0)
+
+    @shaped_bytes.setter
+    def shaped_bytes(self, v: int) -> None:
+        self._shaped_bytes = int(v) - (self.native.shaped_bytes() if self.native is not None else 0)
+
+    def kernels_launched(self) -> int:
+        """Kernels of this package launched so far (or, for a captured step, replayed)."""
+        return self.stats["kernels"] + (self.native.kernels_launched() if self.native is not None else 0)
+
+    def begin_capture(self) -> None:
+        """A CUDA graph of the iteration is about to be captured: gradients of the captured step stay referenced,
+        their addresses go to pinned rows of the capture's own."""
+        self._capturing = True
+        self._capture_keepalive, self._capture_rows = [], {}
+        if self.native is not None:
+            self.native.begin_capture()
+
+    def end_capture(self) -> list:
+        """Returns what the captured step reads on every replay and must therefore outlive it."""
+        self._capturing = False
+        keep, self._capture_keepalive, self._capture_rows = self._capture_keepalive, [], {}
+        if self.native is not None:
+            keep = keep + list(self.native.end_capture())
+        return keep
 
     def shaped_bytes_per_step(self) -> int:
         """Bytes this rank stores into other groups per iteration (what the shaper charges)."""
@@ -322,11 +418,40 @@ class SparseDPEngine:
         _build.load_extension("_C").stamp(self.step_stamps.data_ptr() + 8 * int(slot),
                                           torch.cuda.current_stream(self.device).cuda_stream)
 
+    def _use_native(self) -> bool:
+        return bool(self.cfg.native_hooks) and self.transport != "nccl" and not self.cfg.profile
+
+    def _install_native(self) -> None:
+        """C++ hooks and C++ bucket scheduling (role of backend/src/engine/core.cpp:775-797 and 1025-1095): from the
+        moment autograd has a gradient to the moment the bucket's kernels are in the sparse stream the interpreter is
+        not involved.  Buffers, tables and wiring stay where the Python side created them."""
+        from .. import _build
+
+        C = _build.load_extension("_C")
+        steal = self.cfg.grad_mode != "flat"
+        self.native = C.NativeEngine(self.device.index if self.device.index is not None else torch.cuda.current_device(),
+                                     self.sparse_stream.cuda_stream, self.cfg.staleness, self.cfg.grad_accumulation)
+        for bi, rt in enumerate(self.buckets):
+            b = rt.bucket
+            segs = b.layout.segments
+            got = self.native.add_bucket(
+                b.handle, b.select_handle, len(rt.params), steal,
+                b.grad_tab_host.data_ptr() if steal else 0, GpuBucket.GRAD_TAB_RING if steal else 0,
+                b.grad_tab_dev.data_ptr() if steal else 0, b.grad, [s.off for s in segs], [s.numel for s in segs], 0)
+            assert got == bi
+            for si, p in enumerate(rt.params):
+                self.native.add_param(bi, si, p)
+            rt.native = self.native
+
     def _install_hooks(self) -> None:
         self._hooks = []
-        for bi, rt in enumerate(self.buckets):
-            for p in rt.params:
-                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(bi)))
+        self.native = None
+        if self._use_native():
+            self._install_native()
+        else:
+            for bi, rt in enumerate(self.buckets):
+                for p in rt.params:
+                    self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(bi)))
         # forward gating: wait for the updates this forward must see
         first_owner: dict[int, nn.Module] = {}
         if self.cfg.fine_grained_gating:
@@ -394,6 +519,9 @@ class SparseDPEngine:
                 return
             cur = torch.cuda.current_stream(self.device)
             for bi in bis:
+                if self.native is not None:
+                    self.native.wait_applies(cur.cuda_stream, bi)
+                    continue
                 ev = self.buckets[bi].apply_done
                 if ev is not None:
                     cur.wait_event(ev)
@@ -424,11 +552,22 @@ class SparseDPEngine:
         if all(rt.pending == rt.full for rt in self.buckets):     # first micro-step of an iteration
             self.before_iteration()
         cur = torch.cuda.current_stream(self.device)
-        for bi, rt in enumerate(self.buckets):
-            if bi in self._gated:
-                continue
-            if rt.apply_done is not None:
-                cur.wait_event(rt.apply_done)
+        if self.native is not None:
+            if self._gated:
+                for bi in range(len(self.buckets)):
+                    if bi not in self._gated:
+                        self.native.wait_applies(cur.cuda_stream, bi)
+            else:
+                self.native.wait_applies(cur.cuda_stream, -1)
+            err = self.native.last_error()
+            if err:
+                raise RuntimeError(f"a CUDA call of the native step engine failed with error {err}")
+        else:
+            for bi, rt in enumerate(self.buckets):
+                if bi in self._gated:
+                    continue
+                if rt.apply_done is not None:
+                    cur.wait_event(rt.apply_done)
         if self.cfg.step_clock:
             self.stamp(0)             # behind the waits: time spent blocked on updates counts as gap, not as forward
         self._forward_count = getattr(self, "_forward_count", 0) + 1
@@ -500,13 +639,13 @@ class SparseDPEngine:
                 self.stats["kernels"] += 3
             if self.shaper is not None:
                 nbytes = b.layout.wire_bytes(owned_only=True) * (self.world - self.group_size)   # stored into other groups
-                self.shaped_bytes += nbytes
+                self._shaped_bytes += nbytes
                 self.shaper.take(nbytes, s)
                 self.stats["kernels"] += 1
             b.select(s)
         rt.select_count += 1
         self.stats["select_launches"] += 1
-        self.stats["kernels"] += 2 if (b.compressor == "randomk" or getattr(b, "last_select_fused", False)) else 4
+        self.stats["kernels"] += (b.select_handle or b.handle).select_kernels
 
     def _apply_impl(self, rt: _BucketRuntime) -> None:
         s = self.sparse_stream
@@ -524,11 +663,17 @@ class SparseDPEngine:
         """Flush every pending update and wait for the sparse stream
         (role of backend/src/engine/core.cpp:1097-1140)."""
         cur = torch.cuda.current_stream(self.device)
-        self.sparse_stream.wait_stream(cur)
-        for rt in self.buckets:
-            if rt.has_pending_apply:
-                self._apply(rt)
-        cur.wait_stream(self.sparse_stream)
+        if self.native is not None:
+            self.native.flush(cur.cuda_stream)
+            err = self.native.last_error()
+            if err:
+                raise RuntimeError(f"a CUDA call of the native step engine failed with error {err}")
+        else:
+            self.sparse_stream.wait_stream(cur)
+            for rt in self.buckets:
+                if rt.has_pending_apply:
+                    self._apply(rt)
+            cur.wait_stream(self.sparse_stream)
         self.sparse_stream.synchronize()
         self.check_status()
 
@@ -598,6 +743,7 @@ class SparseDPEngine:
         for rt in self.buckets:
             rt.bucket.set_ratio(ratio)
         self.cfg.ratio = ratio
+        self._push_shaper()
         self.capture_version += 1     # stream sizes are launch arguments: a captured step is stale now
 
     def set_rank_weights(self, weights: Iterable[float], from_iteration: Optional[int] = None) -> None:
@@ -777,6 +923,8 @@ class SparseDPEngine:
         for h in self._hooks:
             h.remove()
         self._hooks = []
+        if self.native is not None:
+            self.native.remove_hooks()
 
 
 def _is_dense(t: torch.Tensor) -> bool:

@@ -146,9 +146,9 @@ class GpuBucket:
         # over once every tensor has a threshold: after the first select, or after a checkpoint that carries them.
         self.chunk_state = torch.zeros(layout.n_chunks, dtype=torch.int64, device=device)
         self.fused_select = bool(fused_select)
-        self.thresholds_ready = False
         self.hist = torch.zeros(n_segs * 2048, dtype=torch.int32, device=device)
-        self.counters = torch.tensor([1, 1, 0, 0], dtype=torch.int32, device=device)
+        # [select epoch, apply epoch, select CTAs done, apply CTAs done, chunk ticket of the persistent select, 3 spare]
+        self.counters = torch.tensor([1, 1, 0, 0, 0, 0, 0, 0], dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.stamps = torch.zeros(8, dtype=torch.int64, device=device)    # device clock of the latest chain, see device_times()
         # merge weight of every source, one row per epoch parity (the scatter of epoch e reads row e & 1)
@@ -205,6 +205,7 @@ class GpuBucket:
         )
         h.set_options(B.COMPRESSORS[self.compressor], self.zero_grad_in_select, False,
                       any(self.layout.is_narrow(s) for s in self.layout.segments), self.deterministic_merge)
+        h.fused_enabled = self.fused_select
         if wiring is not None:
             self._apply_wiring(h, wiring)
 
@@ -307,13 +308,26 @@ class GpuBucket:
         self.weight[parity & 1].copy_(weights, non_blocking=True)
 
     # ------------------------------------------------------------------ execution
+    @property
+    def _select_h(self):
+        return self.select_handle or self.handle
+
+    @property
+    def thresholds_ready(self) -> bool:
+        """Every tensor has its threshold: the one-pass chain of the threshold compressors may take over."""
+        return bool(self._select_h.thresholds_ready)
+
+    @thresholds_ready.setter
+    def thresholds_ready(self, v: bool) -> None:
+        self._select_h.thresholds_ready = bool(v)
+
+    @property
+    def last_select_fused(self) -> bool:
+        return bool(self._select_h.last_select_fused)
+
     def select(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
-        h = self.select_handle or self.handle
-        fused = self.fused_select and self.thresholds_ready and h.can_fuse()
-        h.select(s.cuda_stream, fused)
-        self.thresholds_ready = True      # the four-kernel chain leaves every tensor with a threshold
-        self.last_select_fused = fused
+        self._select_h.select(s.cuda_stream)
 
     def apply(self, stream: Optional[torch.cuda.Stream] = None, phase: int = 0) -> None:
         """phase 0: the whole chain; 1: scatter + optimiser only; 2: copy of the owners' values only."""
@@ -385,8 +399,9 @@ class GpuBucket:
             raise ValueError("checkpoint was written with a different partition of the optimiser state")
         if abs(d["ratio"] - self.ratio) > 1e-12:
             self.set_ratio(d["ratio"])
-        for k in ("resid", "param", "opt", "counters"):
+        for k in ("resid", "param", "opt"):
             getattr(self, k).copy_(d[k])
+        self.counters[:4].copy_(d["counters"][:4])       # epochs and completion counters; the rest is scratch
         # per-element state: the checkpoint holds this rank's range, or the whole bucket (a gathered file)
         off = 0 if src_range == mine else self.state_lo
         n_state = self.state_hi - self.state_lo

@@ -43,31 +43,28 @@ class GraphedStep:
         if engine.cfg.staleness == 1 and not all(rt.has_pending_apply for rt in engine.buckets):
             raise RuntimeError("capture needs a steady-state step: run at least one eager step first")
         before = [(rt.select_count, rt.apply_count) for rt in engine.buckets]
-        kernels0, shaped0 = engine.stats["kernels"], getattr(engine, "shaped_bytes", 0)
+        kernels0, shaped0 = engine.kernels_launched(), engine.shaped_bytes
         self.version = engine.capture_version
         self.graph = torch.cuda.CUDAGraph()
-        engine._capturing = True
-        engine._capture_keepalive, engine._capture_rows = [], {}
+        engine.begin_capture()
         try:
             with torch.cuda.graph(self.graph, stream=side):
                 self.loss = step_fn(*self.static_inputs)
                 torch.cuda.current_stream(dev).wait_stream(engine.sparse_stream)
         finally:
-            engine._capturing = False
-        # A replay reads the captured gradient addresses from pinned rows of its own and reads the gradients
-        # themselves at those addresses: both stay alive as long as this object does.
-        self._keepalive, engine._capture_keepalive, engine._capture_rows = engine._capture_keepalive, [], {}
+            # A replay reads the captured gradient addresses from pinned rows of its own and reads the gradients
+            # themselves at those addresses: both stay alive as long as this object does.
+            self._keepalive = engine.end_capture()
         # capture only records: undo the host-side bookkeeping of the captured (not executed) step
         self._per_replay = []
         for rt, (s0, a0) in zip(engine.buckets, before):
             self._per_replay.append((rt.select_count - s0, rt.apply_count - a0))
             rt.select_count, rt.apply_count = s0, a0
             rt.apply_done = None          # events recorded under capture are not waitable outside
-        self._kernels_per_replay = engine.stats["kernels"] - kernels0
-        engine.stats["kernels"] = kernels0
-        self._shaped_per_replay = getattr(engine, "shaped_bytes", 0) - shaped0
-        if hasattr(engine, "shaped_bytes"):
-            engine.shaped_bytes = shaped0
+        self._kernels_per_replay = engine.kernels_launched() - kernels0
+        engine.stats["kernels"] -= self._kernels_per_replay
+        self._shaped_per_replay = engine.shaped_bytes - shaped0
+        engine.shaped_bytes = shaped0
         torch.cuda.synchronize(dev)
 
     @property
@@ -92,8 +89,7 @@ class GraphedStep:
             rt.apply_count += da
         eng.stats["kernels"] += self._kernels_per_replay
         eng.stats["graph_replays"] = eng.stats.get("graph_replays", 0) + 1
-        if hasattr(eng, "shaped_bytes"):
-            eng.shaped_bytes += self._shaped_per_replay
+        eng.shaped_bytes = eng.shaped_bytes + self._shaped_per_replay
         n = eng.stats["graph_replays"]
         if eng.cfg.status_poll_interval and n % eng.cfg.status_poll_interval == 0:
             eng._poll_status()
