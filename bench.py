@@ -70,6 +70,7 @@ def parse_args() -> argparse.Namespace:
                     help="hold the upper half of the ranks for this long in every iteration (unequal GPUs for --adapt-batch)")
     ap.add_argument("--native-copies", type=int, default=1,
                     help="cpu_offload arm: 1 lets the native engine issue the device copies itself")
+    ap.add_argument("--native-hooks", type=int, default=1, help="0: Python hooks instead of the native step engine (eager mode comparison)")
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
 
@@ -471,6 +472,7 @@ def main() -> None:
         st.state().engine_cfg.bucket_mb = args.bucket_mb
         st.state().engine_cfg.multicast = not args.no_multicast
         st.state().engine_cfg.grad_mode = args.grad_mode
+        st.state().engine_cfg.native_hooks = bool(args.native_hooks)
         if args.impl == "nccl_sparse":
             args.graph = 0            # the library collective between the kernel chains is not captured
         net = st.FasterDpModelWrapper(model, sequential=False, graph=bool(args.graph), graph_warmup=max(3, args.warmup - 2),
@@ -728,6 +730,7 @@ def main() -> None:
                             "bytes_per_step_this_rank": engine.shaped_bytes_per_step()}
                            if engine is not None and engine.shaper is not None else None),
                 "multicast": bool(engine is not None and engine.pool is not None and engine.pool.mc_ptr),
+                "native_step_engine": bool(engine is not None and engine.native is not None),
                 "cuda_graph": bool(args.graph and net._graphs) if engine is not None else (args.impl == "dense_graph"), "channels_last": bool(args.channels_last), "grad_mode": args.grad_mode,
                 "l2": "per-step working set (233 MB of parameters plus activations) exceeds the 126 MB L2; no flush needed",
             },

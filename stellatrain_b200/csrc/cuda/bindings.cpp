@@ -74,7 +74,7 @@ struct BucketHandle : public st::BucketHandle {
     sel.cand_cap = cand_cap;
   }
 
-  // counters: [sel_epoch, app_epoch, sel_done, app_done, chunk ticket, 3 spare] as eight u32 words; status: one u32 word
+  // counters: [sel_epoch, app_epoch, sel_done, app_done, 4 spare] as eight u32 words; status: one u32 word
   void set_control(uint64_t counters, uint64_t status, uint64_t opt, uint64_t weight, uint64_t timeout_ns, uint64_t stamps) {
     uint32_t* c = as_ptr<uint32_t>(counters);
     sel.epoch = c + 0;
@@ -82,7 +82,6 @@ struct BucketHandle : public st::BucketHandle {
     app.sel_epoch = c + 0;
     sel.done_ctr = c + 2;
     app.done_ctr = c + 3;
-    sel.chunk_ticket = c + 4;    // counters holds eight words
     sel.status = app.status = as_ptr<uint32_t>(status);
     app.opt = as_ptr<st::OptState>(opt);
     app.weight = as_ptr<const float>(weight);

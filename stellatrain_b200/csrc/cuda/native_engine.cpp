@@ -337,10 +337,7 @@ PyObject* NativeEngine::end_capture() {
 int64_t NativeEngine::select_count(int bucket) const { return impl_->buckets.at(bucket).select_count; }
 int64_t NativeEngine::apply_count(int bucket) const { return impl_->buckets.at(bucket).apply_count; }
 bool NativeEngine::pending_apply(int bucket) const { return impl_->buckets.at(bucket).has_pending_apply; }
-int NativeEngine::pending_hooks(int bucket) const {
-  const BucketRec& b = impl_->buckets.at(bucket);
-  return b.pending % b.spec.n_params;
-}
+int NativeEngine::pending_hooks(int bucket) const { return impl_->buckets.at(bucket).pending; }
 void NativeEngine::set_counts(int bucket, int64_t selects, int64_t applies, bool pending_apply) {
   std::lock_guard<std::mutex> lock(impl_->mu);
   BucketRec& b = impl_->buckets.at(bucket);

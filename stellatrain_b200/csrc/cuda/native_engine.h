@@ -67,7 +67,8 @@ class NativeEngine {
   int64_t apply_count(int bucket) const;
   void set_counts(int bucket, int64_t selects, int64_t applies, bool pending_apply);
   bool pending_apply(int bucket) const;
-  int pending_hooks(int bucket) const;          // parameters of the running micro-iteration still without a gradient
+  int pending_hooks(int bucket) const;          // gradient hooks still to come before the bucket is ready
+                                                // (parameters x accumulation steps between iterations)
   int64_t kernels_launched() const;
   uint64_t shaped_bytes() const;
   // First CUDA error a hook met (hooks cannot raise through autograd's thread), or 0.

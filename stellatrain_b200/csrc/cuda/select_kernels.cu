@@ -761,7 +761,6 @@ __device__ __forceinline__ void finish_select(const SelectArgs& A, uint32_t epoc
   const uint32_t prev = atomicAdd(A.done_ctr, 1u);
   if (prev == gridDim.x - 1) {
     *A.done_ctr = 0;
-    if (A.chunk_ticket != nullptr) *A.chunk_ticket = 0;   // the persistent one-pass kernel hands chunks out from zero
     __threadfence_system();
     publish_checksums(A, epoch);
     if (A.publish && ld_volatile_u32(A.status) == kOk) {
@@ -1106,326 +1105,12 @@ __global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// threshold-v16, one pass, persistent and warp-specialised
-// ------------------------------------------------------------------------------------------------
-// Same work as k_fused<true>, organised so that memory never waits for bookkeeping: a fixed number of CTAs per SM
-// take chunks from a ticket counter (in chunk order, so a chunk only ever waits for chunks held by CTAs that are
-// running) and split into three roles.
-//   producer  one thread.  Fetches the next chunk's tables, then asks the copy engine (cp.async.bulk, completion on
-//             an mbarrier) for its residual and gradient tiles, kStreamStages tiles ahead of the consumers.
-//   consumers eight warps.  Wait for a tile, a = g + r from shared memory, store r, block norms, ballots of the blocks
-//             at or over the threshold and near-miss candidates into the chunk's bookkeeping buffer, free the stage.
-//   epilogue  one warp, one chunk behind.  Scans the chunk's counts, chains them with the chunks before it
-//             (look-back), stores the selected blocks of the chunk into the destinations' receive areas and clears
-//             them in r.  Its global round trips overlap the next chunk's streaming instead of stalling it.
-// Every wait (stage, bookkeeping buffer, predecessor chunk, acknowledgement) is bounded; a wait that runs out sets
-// the status word and an abort flag that ends all three roles.
-constexpr int kStreamStages = 4;
-constexpr int kStreamConsumerWarps = 8;
-constexpr int kStreamConsumers = kStreamConsumerWarps * 32;
-constexpr int kStreamThreads = kStreamConsumers + 64;      // + producer warp + epilogue warp
-constexpr int kStreamCtasPerSm = 3;
-constexpr uint32_t kStreamTile = kPerIter;                 // elements per stage and array
-constexpr uint32_t kStreamWarpCand = 16;                   // near-miss blocks a consumer warp can note per chunk
-constexpr uint32_t kStreamDescRing = 8;                    // >= stages + 2 chunks of lead, see the producer
-constexpr uint32_t kNoChunk = 0xFFFFFFFFu;
-constexpr uint32_t kDescCollect = 1u, kDescSkip = 2u, kDescAdd = 4u, kDescZeroGrad = 8u;
-
-struct StreamDesc {
-  uint32_t chunk;        // kNoChunk: the tickets are used up
-  uint32_t seg, start, len, n_tiles;
-  uint32_t tau_bits, lo_bits;
-  uint32_t flags;
-  uint32_t g_valid;      // gradient elements that exist behind g (a tensor's tail is not padded)
-  float* g;              // gradient of the chunk
-};
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-
-// Bounded wait for a phase that also gives up when another role of the CTA has given up.
-__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, const volatile uint32_t* abort_flag) {
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((it & 255u) == 255u && *abort_flag) return false;
-  }
-  return false;
-}
-
-__global__ void __launch_bounds__(kStreamThreads, kStreamCtasPerSm) k_stream16(SelectArgs A) {
-  __shared__ __align__(128) float s_r[kStreamStages][kStreamTile];
-  __shared__ __align__(128) float s_g[kStreamStages][kStreamTile];
-  __shared__ __align__(8) uint64_t s_full[kStreamStages], s_empty[kStreamStages], s_done[2], s_free[2];
-  __shared__ StreamDesc s_desc[kStreamDescRing];
-  __shared__ uint32_t s_cnt[2][kFusedMaxIter * kStreamConsumerWarps];    // blocks over the threshold per (tile, warp)
-  __shared__ uint32_t s_bal[2][kFusedMaxIter * kStreamConsumerWarps];    // which ones: ballot of the blocks' first lanes
-  __shared__ uint2 s_cnd[2][kStreamConsumerWarps][kStreamWarpCand];
-  __shared__ uint32_t s_ncnd[2][kStreamConsumerWarps];
-  __shared__ uint16_t s_list[kFusedMaxChunk / 16];                       // epilogue: selected blocks of the chunk, in order
-  __shared__ uint32_t s_abort;
-
-  const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-  if (tid == 0) {
-    for (int s = 0; s < kStreamStages; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], kStreamConsumerWarps);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&s_done[b], kStreamConsumerWarps);
-      mbar_init(&s_free[b], 1);
-    }
-    mbar_init_fence();
-    s_abort = 0;
-    if (blockIdx.x == 0 && A.stamps != nullptr) A.stamps[0] = global_timer_ns();
-  }
-  __syncthreads();
-  const volatile uint32_t* abort_flag = &s_abort;
-  auto give_up = [&]() {
-    set_status(A.status, kTimeoutScan);
-    s_abort = 1;
-  };
-
-  // ---------------------------------------------------------------------------------------------- producer
-  if (warp == kStreamConsumerWarps) {
-    if (lane != 0) return;
-    const bool tab = A.grad_tab != nullptr;
-    uint32_t t = 0;
-    // the tables of the coming chunk are requested one chunk early, so that their latency (ticket, chunk, tensor
-    // descriptor, threshold, gradient pointer: a chain of dependent loads) hides behind the tiles in flight
-    uint32_t c_next = atomicAdd(A.chunk_ticket, 1u);
-    Chunk ch_next = c_next < A.n_chunks ? A.chunks[c_next] : Chunk{0u, 0u, 0u, 0u};
-    for (uint32_t k = 0;; ++k) {
-      const uint32_t c = c_next;
-      const Chunk ch = ch_next;
-      StreamDesc d;
-      d.chunk = kNoChunk; d.seg = 0; d.start = 0; d.len = 0; d.n_tiles = 0; d.tau_bits = 0xFFFFFFFFu; d.lo_bits = 0xFFFFFFFFu;
-      d.flags = 0; d.g_valid = 0; d.g = nullptr;
-      if (c < A.n_chunks) {
-        const SegDesc sd = A.segs[ch.seg];
-        const SegState ss = A.state[ch.seg];
-        float* gseg = tab ? A.grad_tab[ch.seg] : nullptr;
-        c_next = atomicAdd(A.chunk_ticket, 1u);
-        if (c_next < A.n_chunks) ch_next = A.chunks[c_next];
-        const uint32_t seg_rel = ch.start - sd.off;
-        d.chunk = c; d.seg = ch.seg; d.start = ch.start; d.len = ch.len;
-        d.g = tab ? gseg + seg_rel : A.grad + ch.start;
-        d.g_valid = tab ? (sd.n > seg_rel ? min(ch.len, sd.n - seg_rel) : 0u) : ch.len;
-        if (sd.reserved & kSegSkip) {
-          d.flags = kDescSkip | (A.zero_grad && !tab ? kDescZeroGrad : 0u);
-        } else {
-          d.n_tiles = (ch.len + kStreamTile - 1) / kStreamTile;
-          float window = __uint_as_float(ss.reserved[0]);
-          if (!(window > 0.f && window <= 1.f)) window = kWindowDefault;
-          if (ss.inited) {
-            d.tau_bits = __float_as_uint(ss.tau);
-            d.lo_bits = __float_as_uint(fmaxf(ss.tau * (1.f - window), 0.f));
-            d.flags |= kDescCollect;
-          }
-          if (!A.skip_ef) d.flags |= kDescAdd;
-          if (A.zero_grad) d.flags |= kDescZeroGrad;
-        }
-      }
-      // The ring slot is free: the consumers are at most kStreamStages chunks behind (a chunk takes at least one
-      // stage) and the epilogue at most two behind them.
-      s_desc[k % kStreamDescRing] = d;
-      const uint32_t slots = d.n_tiles ? d.n_tiles : 1u;
-      for (uint32_t j = 0; j < slots; ++j, ++t) {
-        const uint32_t s = t % kStreamStages;
-        if (!mbar_wait_or_abort(&s_empty[s], ((t / kStreamStages) & 1u) ^ 1u, abort_flag)) { give_up(); return; }
-        if (j < d.n_tiles) {
-          const uint32_t off = j * kStreamTile;
-          const uint32_t tl = min(kStreamTile, d.len - off);
-          const uint32_t gl = (d.flags & kDescAdd) ? (min(tl, d.g_valid > off ? d.g_valid - off : 0u) & ~3u) : 0u;
-          mbar_expect_tx(&s_full[s], (tl + gl) * 4u);
-          bulk_load(&s_r[s][0], A.resid + d.start + off, tl * 4u, &s_full[s]);
-          if (gl) bulk_load(&s_g[s][0], d.g + off, gl * 4u, &s_full[s]);
-        } else {
-          mbar_arrive(&s_full[s]);   // a chunk without tiles still passes through the pipeline, in order
-        }
-      }
-      if (c >= A.n_chunks) return;
-    }
-  }
-
-  // ---------------------------------------------------------------------------------------------- epilogue
-  if (warp == kStreamConsumerWarps + 1) {
-    const uint32_t epoch = *A.epoch;
-    for (uint32_t k = 0;; ++k) {
-      const uint32_t cb = k & 1u;
-      if (!mbar_wait_or_abort(&s_done[cb], (k >> 1) & 1u, abort_flag)) { if (lane == 0) give_up(); return; }
-      const StreamDesc d = s_desc[k % kStreamDescRing];
-      if (d.chunk == kNoChunk) return;
-      if (!(d.flags & kDescSkip)) {
-        const SegDesc sd = A.segs[d.seg];
-        SegWork* wp = &A.work[d.seg];
-        const uint32_t kk = (sd.k + 15u) / 16u;
-        // exclusive prefix over the (tile, warp) cells in index order: four cells per lane
-        const uint32_t n_cells = d.n_tiles * kStreamConsumerWarps;
-        uint32_t v[4], mine = 0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t cell = lane * 4u + q;
-          v[q] = cell < n_cells ? s_cnt[cb][cell] : 0u;
-          mine += v[q];
-        }
-        const uint32_t incl = warp_incl_scan(mine);
-        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-        uint32_t at = incl - mine;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t cell = lane * 4u + q;
-          if (cell < n_cells) {
-            uint32_t bits = s_bal[cb][cell];
-            const uint32_t tile = cell / kStreamConsumerWarps, w = cell % kStreamConsumerWarps;
-            while (bits) {
-              const uint32_t b = (uint32_t)__ffs((int)bits) - 1u;
-              bits &= bits - 1u;
-              s_list[at++] = (uint16_t)(tile * (kStreamTile / 16u) + w * 8u + (b >> 2));
-            }
-          }
-        }
-        bool good;
-        const uint32_t base = chunk_lookback(A.chunk_state, sd.chunk_begin, d.chunk, epoch, total, &good);
-        // near-miss blocks of the chunk -> the tensor's candidate region
-        {
-          const uint32_t n_w = lane < kStreamConsumerWarps ? s_ncnd[cb][lane] : 0u;
-          const uint32_t n_c = min(n_w, kStreamWarpCand);
-          const uint32_t c_incl = warp_incl_scan(n_c);
-          const uint32_t c_total = __shfl_sync(0xffffffffu, c_incl, 31);
-          uint32_t c_base = 0;
-          if (lane == 0 && c_total) c_base = atomicAdd(&wp->cand_cnt, c_total);
-          c_base = __shfl_sync(0xffffffffu, c_base, 0);
-          if (lane < kStreamConsumerWarps) {
-            uint2* region = A.cand + (sd.off >> 4);
-            for (uint32_t i = 0; i < n_c; ++i) region[c_base + c_incl - n_c + i] = s_cnd[cb][lane][i];
-            if (n_w > kStreamWarpCand) atomicOr(&wp->reserved[0], 1u);   // some were not noted: the finish must scan
-          }
-        }
-        uint32_t may = 0;
-        if (lane == 0) {
-          if (!good) set_status(A.status, kTimeoutScan);
-          if (d.chunk == sd.chunk_begin + sd.chunk_cnt - 1u) wp->found = base + total;
-          bool m = total != 0u && base < kk && ld_volatile_u32(A.status) == kOk;
-          if (m) m = acks_arrived(A, epoch);
-          may = m ? 1u : 0u;
-        }
-        may = __shfl_sync(0xffffffffu, may, 0);
-        __syncwarp();
-        if (may) {
-          const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
-          const int dest = dest_of(A, sd);
-          const uint32_t nb = narrow_base_of(sd);
-          const uint32_t n_emit = min(total, kk - base);        // blocks beyond the budget stay in the residual
-          const uint32_t items = n_emit * 16u;
-          for (uint32_t w0 = 0; w0 < items; w0 += 128u) {       // four independent loads per lane in flight
-            float a[4];
-            uint32_t gi[4], p[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const uint32_t w = w0 + u * 32u + lane;
-              const uint32_t j = w >> 4, e = w & 15u;
-              p[u] = w < items ? (base + j) * 16u + e : 0xFFFFFFFFu;
-              gi[u] = w < items ? d.start + (uint32_t)s_list[j] * 16u + e : 0u;
-              a[u] = (p[u] < sd.k) ? __ldcg(A.resid + gi[u]) : 0.f;
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              if (p[u] < sd.k) {   // a truncated last block leaves the residual exact: only emitted elements are cleared
-                const float sv = wire_value(nb, a[u]);
-                emit_entry(A, dest, nb, slot_off, p[u], gi[u], sv);
-                A.resid[gi[u]] = a[u] - sv;
-              }
-            }
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[cb]);
-    }
-  }
-
-  // ---------------------------------------------------------------------------------------------- consumers
-  uint32_t t = 0;
-  for (uint32_t k = 0;; ++k) {
-    const uint32_t cb = k & 1u;
-    if (!mbar_wait_or_abort(&s_full[t % kStreamStages], (t / kStreamStages) & 1u, abort_flag)) { if (lane == 0) give_up(); return; }
-    const StreamDesc d = s_desc[k % kStreamDescRing];
-    // the bookkeeping buffer of this parity is free once the epilogue is through with the chunk before last
-    if (!mbar_wait_or_abort(&s_free[cb], ((k >> 1) & 1u) ^ 1u, abort_flag)) { if (lane == 0) give_up(); return; }
-    if (d.chunk == kNoChunk) {
-      if (lane == 0) mbar_arrive(&s_done[cb]);
-      return;
-    }
-    if (lane == 0) s_ncnd[cb][warp] = 0;
-    __syncwarp();
-    if (d.flags & kDescSkip) {
-      // a tensor another rank of the group is responsible for: only clear the consumed gradient
-      if (d.flags & kDescZeroGrad) {
-        for (uint32_t i = tid * 4; i < d.len; i += kStreamConsumers * 4)
-          *reinterpret_cast<float4*>(d.g + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[t % kStreamStages]);
-      ++t;
-    } else {
-      const bool add = d.flags & kDescAdd;
-      float* r = A.resid + d.start;
-      for (uint32_t j = 0; j < d.n_tiles; ++j, ++t) {
-        const uint32_t s = t % kStreamStages;
-        if (j && !mbar_wait_or_abort(&s_full[s], (t / kStreamStages) & 1u, abort_flag)) { if (lane == 0) give_up(); return; }
-        const uint32_t off = j * kStreamTile, o = tid * 4u, i = off + o;
-        const bool act = i < d.len;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (act) {
-          a = *reinterpret_cast<const float4*>(&s_r[s][o]);
-          if (add) {
-            const uint32_t tl = min(kStreamTile, d.len - off);
-            const uint32_t gl = min(tl, d.g_valid > off ? d.g_valid - off : 0u) & ~3u;   // what the bulk copy brought
-            const float4 gv = (o + 4u <= gl) ? *reinterpret_cast<const float4*>(&s_g[s][o]) : load4_guarded(d.g, i, d.g_valid);
-            a.x += gv.x; a.y += gv.y; a.z += gv.z; a.w += gv.w;
-            // NaN policy: a NaN is dropped (neither sent nor kept), so it cannot poison the residual.
-            if (!(a.x == a.x)) a.x = 0.f;
-            if (!(a.y == a.y)) a.y = 0.f;
-            if (!(a.z == a.z)) a.z = 0.f;
-            if (!(a.w == a.w)) a.w = 0.f;
-            *reinterpret_cast<float4*>(r + i) = a;
-            if (d.flags & kDescZeroGrad) store4_guarded(d.g, i, d.g_valid, make_float4(0.f, 0.f, 0.f, 0.f));
-          }
-        }
-        const uint32_t key = __float_as_uint(quad_l1(a));   // the same value in the four lanes of a block
-        const bool sel = act && key >= d.tau_bits;
-        const uint32_t leaders = __ballot_sync(0xffffffffu, sel) & 0x11111111u;
-        if (lane == 0) {
-          s_cnt[cb][j * kStreamConsumerWarps + warp] = __popc(leaders);
-          s_bal[cb][j * kStreamConsumerWarps + warp] = leaders;
-        }
-        if ((d.flags & kDescCollect) && act && !sel && (lane & 3u) == 0u && key >= d.lo_bits && key != 0u) {
-          const uint32_t slot = atomicAdd(&s_ncnd[cb][warp], 1u);
-          if (slot < kStreamWarpCand) s_cnd[cb][warp][slot] = make_uint2((d.start + i) >> 4, key);
-        }
-        __syncwarp();   // every lane has read its part of the stage
-        if (lane == 0) mbar_arrive(&s_empty[s]);
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&s_done[cb]);   // the chunk's stores and bookkeeping are visible to the epilogue behind this
-  }
-}
-
 __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
   __shared__ uint32_t s_hist[2048];
   __shared__ uint32_t s_tmp[kCandThreads / 32 + 1];
   __shared__ uint32_t s_res[4];
   __shared__ uint32_t s_n[2];   // [0] candidates found by the scan, [1] acknowledgements arrived
-  __shared__ uint32_t s_in[4];  // found, noted candidates, "has a threshold", "candidates incomplete" as read by thread 0
+  __shared__ uint32_t s_in[3];  // found, noted candidates, "has a threshold" as read by thread 0
 
   const uint32_t seg = blockIdx.x;
   const uint32_t tid = threadIdx.x;
@@ -1446,7 +1131,6 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
       s_in[0] = wp->found;
       s_in[1] = wp->cand_cnt;
       s_in[2] = A.state[seg].inited;
-      s_in[3] = wp->reserved[0];     // the one-pass kernel could not note every near-miss block of this tensor
     }
     __syncthreads();
     SegState ss = A.state[seg];
@@ -1468,7 +1152,7 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
           const uint32_t need = kk - found, n_blocks = sd.n_pad / 16u;
           uint2* cand = A.cand + (sd.off >> 4);
           uint32_t c = min(c_win, n_blocks);   // the candidate region holds one slot per block of the tensor
-          if (!ss.inited || c < need || s_in[3]) {
+          if (!ss.inited || c < need) {
             // every block that still holds something is a candidate: the blocks over the threshold were all
             // emitted (the stream is short of them) and are zero in the residual by now
             scanned = true;
@@ -1570,7 +1254,6 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
       wp->cand_cnt = 0;
       wp->found = 0;
       wp->max_bits = 0;
-      wp->reserved[0] = 0;
     }
   }
 
@@ -1677,14 +1360,7 @@ bool fused_select_possible(const SelectArgs& A, uint32_t max_chunk_len) {
 cudaError_t launch_select_fused(const SelectArgs& A, cudaStream_t stream) {
   if (A.n_chunks == 0 || A.n_segs == 0) return cudaSuccess;
   if (A.world > kMaxWorld || A.chunk_state == nullptr) return cudaErrorInvalidValue;
-  if (A.compressor == kThresholdv16 && A.chunk_ticket != nullptr) {
-    // persistent: a fixed number of CTAs per SM take the chunks in order from a ticket counter
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    uint32_t grid = (uint32_t)sms * kStreamCtasPerSm;
-    if (grid > A.n_chunks) grid = A.n_chunks;
-    k_stream16<<<grid, kStreamThreads, 0, stream>>>(A);
-  } else if (A.compressor == kThresholdv16) k_fused<true><<<A.n_chunks, kThreads, 0, stream>>>(A);
+  if (A.compressor == kThresholdv16) k_fused<true><<<A.n_chunks, kThreads, 0, stream>>>(A);
   else if (A.compressor == kThresholdv) k_fused<false><<<A.n_chunks, kThreads, 0, stream>>>(A);
   else return cudaErrorInvalidValue;
   k_finish<<<A.n_segs, kCandThreads, 0, stream>>>(A);

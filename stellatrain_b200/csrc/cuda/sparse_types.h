@@ -81,7 +81,7 @@ struct SegWork {          // scratch per segment, valid within one select
   uint32_t max_bits;      // running max |x| of the segment as float bits (reset by plan)
   uint32_t max_saved;     // max |x| of the current select
   uint32_t tau_bits;      // threshold the current select was counted with
-  uint32_t reserved[2];   // [0]: one-pass select: not every near-miss block was noted (the finish scans the tensor)
+  uint32_t reserved[2];
 };
 
 struct Chunk {            // unit of work of the streaming passes; never spans two segments
@@ -114,7 +114,6 @@ struct SelectArgs {
   uint32_t* chunk_cnt;         // items over the threshold per chunk
   uint32_t* chunk_pos;         // exclusive prefix of chunk_cnt inside the segment
   uint64_t* chunk_state;       // one-pass select: per chunk (epoch | kind | items), see chunk_word(); or null
-  uint32_t* chunk_ticket;      // persistent one-pass select: next chunk to hand out (zero between selects); or null
   uint32_t* hist;              // [n_segs][kHistBins]
   uint2* cand;                 // candidate scratch: (item id, key)
   uint32_t* cand_cursor;       // bump pointer into cand

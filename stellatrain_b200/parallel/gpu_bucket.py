@@ -147,7 +147,7 @@ class GpuBucket:
         self.chunk_state = torch.zeros(layout.n_chunks, dtype=torch.int64, device=device)
         self.fused_select = bool(fused_select)
         self.hist = torch.zeros(n_segs * 2048, dtype=torch.int32, device=device)
-        # [select epoch, apply epoch, select CTAs done, apply CTAs done, chunk ticket of the persistent select, 3 spare]
+        # [select epoch, apply epoch, select CTAs done, apply CTAs done, 4 spare]
         self.counters = torch.tensor([1, 1, 0, 0, 0, 0, 0, 0], dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.stamps = torch.zeros(8, dtype=torch.int64, device=device)    # device clock of the latest chain, see device_times()
