@@ -541,7 +541,8 @@ def main() -> None:
 
         ctl_port = master_port + 17
         if rank == 0:
-            controller = Controller(port=ctl_port, host="127.0.0.1", adapt=True).start()
+            controller = Controller(port=ctl_port, host="127.0.0.1", adapt=True,
+                                    max_batch=(2 * args.batch if args.adapt_batch else args.batch)).start()
             from stellatrain_b200 import cpu_tier
             srv = cpu_tier._load().TelemetryServer(f"127.0.0.1:{ctl_port}", False, 5000)
             srv.send_global_telemetry(max(1, world // max(1, args.group_size)), world,

@@ -46,10 +46,11 @@ class Client:
 class Controller:
     def __init__(self, port: int = 5556, host: str = "0.0.0.0", adapt: Optional[bool] = None,
                  profile_path: Optional[str] = None, transport: str = "nvlink", state_path: Optional[str] = None,
-                 wire_blocks: Optional[bool] = None) -> None:
+                 wire_blocks: Optional[bool] = None, max_batch: Optional[int] = None) -> None:
         self.adapt = (os.environ.get("DISABLE_RATE_ADAPT", "0") in ("", "0")) if adapt is None else adapt
         self.profile = load_profile(profile_path or os.environ.get("MODEL_PROFILE"))
         self.transport = transport
+        self.max_batch = max_batch        # per-GPU batch ceiling of this job; None: by device name (MAX_BATCH_SIZE_MAP)
         # the CPU tier's TCP messages carry whole blocks of 16 entries behind one block id by default: the byte model
         # that turns a compression ratio into required goodput has to know
         self.wire_blocks = (transport == "tcp") if wire_blocks is None else wire_blocks
@@ -113,7 +114,7 @@ class Controller:
                         self.clients[li.gpu_id] = client
                         self.scoreboard.loc[li.gpu_id, ["location", "gpu"]] = [f"{li.rank}:{li.local_rank}", li.gpu_name]
                         if self.optimizer is not None and li.gpu_id < self.optimizer.num_gpus:
-                            self.optimizer.set_max_batch(li.gpu_id, max_batch_for(li.gpu_name))
+                            self.optimizer.set_max_batch(li.gpu_id, self.max_batch or max_batch_for(li.gpu_name))
                 elif mtype == M.LOCAL:
                     t = M.parse(mtype, payload)
                     self.rx.put(t)
@@ -142,7 +143,7 @@ class Controller:
                                                 latest_iter=lambda: self.latest_iter)
             for gid, c in self.clients.items():
                 if gid < gi.num_gpus:
-                    self.optimizer.set_max_batch(gid, max_batch_for(c.gpu_name))
+                    self.optimizer.set_max_batch(gid, self.max_batch or max_batch_for(c.gpu_name))
             self._restore_state()
 
     # ---------------------------------------------------------------- persistence
@@ -257,9 +258,11 @@ def main() -> None:
     ap.add_argument("--profile", default=None)
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "tcp"])
     ap.add_argument("--state-file", default=None, help="optimiser state is kept here across restarts of the controller")
+    ap.add_argument("--max-batch", type=int, default=None, help="per-GPU batch ceiling (default: by device name)")
     args = ap.parse_args()
     _single_instance(args.port)
-    c = Controller(args.port, profile_path=args.profile, transport=args.transport, state_path=args.state_file).start()
+    c = Controller(args.port, profile_path=args.profile, transport=args.transport, state_path=args.state_file,
+                   max_batch=args.max_batch).start()
     try:
         while not c.stop.is_set():
             time.sleep(0.2)

@@ -33,11 +33,16 @@ import torch.distributed as dist
 
 class TelemetryHook:
     def __init__(self, engine, uri: Optional[str], batch_size: int, gpu_name: Optional[str] = None,
-                 apply_batch: bool = True, apply_ratio: bool = True, link_bytes_per_entry: int = 8) -> None:
+                 apply_batch: bool = True, apply_ratio: bool = True, link_bytes_per_entry: int = 8,
+                 ratio_tolerance: float = 0.15) -> None:
         self.engine = engine
         self.batch_size = int(batch_size)
         self.apply_batch, self.apply_ratio = apply_batch, apply_ratio
         self.bytes_per_entry = link_bytes_per_entry
+        # A new ratio drains the pipeline and makes a captured step stale, so one that moves the kept fraction by
+        # less than this (relative) is not worth applying; the controller re-issues its current view every few
+        # iterations anyway (backend/src/engine/batch_rate_alloc_optim.py:454-472).
+        self.ratio_tolerance = float(ratio_tolerance)
         self.iteration = 0
         self.pending: List[Tuple[int, int, float]] = []      # (effective_since, ubatch, ratio)
         self.applied: List[Tuple[int, int, float]] = []
@@ -101,7 +106,10 @@ class TelemetryHook:
             if self.apply_ratio and 0.0 < ratio <= 1.0:
                 # every rank receives the same ratio for the same effective iteration
                 lo = self.engine.buckets[0].bucket.min_ratio
-                self.engine.set_compression_ratio(max(ratio, lo))
+                target, now = max(ratio, lo), self.engine.cfg.ratio
+                kept_now, kept_new = max(1.0 - now, 1e-9), max(1.0 - target, 1e-9)
+                if abs(kept_new - kept_now) > self.ratio_tolerance * kept_now:
+                    self.engine.set_compression_ratio(target)
             self.applied.append((since, ubatch, ratio))
         if due and self.apply_batch and self.engine.world > 1:
             # unequal batches: weight each rank's gradient by its share of the global batch
