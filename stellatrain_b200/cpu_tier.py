@@ -84,14 +84,38 @@ def _from_ptr(ptr: int, numel: int) -> torch.Tensor:
     return torch.frombuffer(buf, dtype=torch.float32, count=numel)
 
 
+def bundled_libzmq() -> str:
+    """Path of the libzmq that ships inside pyzmq ('' when that package is not installed)."""
+    import glob
+    import importlib.util
+
+    spec = importlib.util.find_spec("zmq")
+    if spec is None or not spec.submodule_search_locations:
+        return ""
+    root = os.path.dirname(list(spec.submodule_search_locations)[0])
+    found = sorted(glob.glob(os.path.join(root, "pyzmq.libs", "libzmq*.so*")))
+    return found[0] if found else ""
+
+
 class CpuOffloadEngine:
     def __init__(self, module: nn.Module, *, master_addr: str = "127.0.0.1", master_port: int = 5555, world_size: int = 1,
                  rank: int = 0, session: Optional[int] = None, local_world_size: int = 1, local_rank: int = 0,
                  method: str = "thresholdv16", gradient_accumulation: int = 1, staleness: int = 1, ratio: float = 0.99,
                  optimizer: str = "sgd", optimizer_options: Optional[dict] = None, data_bytes: int = 0,
                  timeout_ms: int = 30000, workers: int = 0, debug_accuracy: bool = False, debug_barrier: bool = False,
-                 wire_blocks: bool = True, wire_values: str = "fp32", native_copies: Optional[bool] = None):
+                 wire_blocks: bool = True, wire_values: str = "fp32", native_copies: Optional[bool] = None,
+                 data_transport: str = "tcp"):
         ext = _load()
+        if data_transport == "zmq":
+            # the ring between nodes over ZeroMQ PUSH/PULL sockets, the reference's transport; the native comm manager
+            # opens the library at run time and is told where pyzmq keeps its copy
+            os.environ["STELLATRAIN_DATA_TRANSPORT"] = "zmq"
+            if not os.environ.get("STELLATRAIN_LIBZMQ"):
+                found = bundled_libzmq()
+                if found:
+                    os.environ["STELLATRAIN_LIBZMQ"] = found
+        elif data_transport != "tcp":
+            raise ValueError("data_transport must be 'tcp' or 'zmq'")
         self.module = module
         self.engine = ext.CpuEngine()
         params = [(n, p) for n, p in module.named_parameters() if p.requires_grad]

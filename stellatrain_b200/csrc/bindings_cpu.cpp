@@ -247,6 +247,10 @@ PYBIND11_MODULE(_Ccpu, m) {
   py::class_<CommBox>(m, "CommManager")
       .def(py::init<const std::string&, uint16_t, int>())
       .def("start_server", [](CommBox& b, int world) { b.c->start_server(world); })
+      .def("set_data_transport", [](CommBox& b, const std::string& name, const std::string& libzmq) {
+        return b.c->set_data_transport(name, libzmq);
+      }, py::arg("name"), py::arg("libzmq") = "")
+      .def("data_transport", [](CommBox& b) { return std::string(b.c->data_transport()); })
       .def("start_client", [](CommBox& b, int rank, int world, int gpus) { return b.c->start_client(rank, world, gpus); },
            py::call_guard<py::gil_scoped_release>())
       .def("queue_tx", [](CommBox& b, int64_t prio, const std::string& key, const std::vector<uint32_t>& idx,

@@ -1,5 +1,7 @@
 #include "comm_manager.h"
 
+#include <cstdlib>
+
 #include <poll.h>
 #include <cstdio>
 #include <unistd.h>
@@ -79,6 +81,7 @@ CommManager::~CommManager() {
   // tell the ring successor that the silence that follows is a regular shutdown, not a lost node
   if (push_fd_ >= 0 && !failed_) send_frame(push_fd_, kBye, "", 0, nullptr, 0, 200);
   if (pull_thread_.joinable()) pull_thread_.join();
+  if (zmq_) zmq_->close();     // both threads are gone: no socket is in use any more
   close_fd(push_fd_);
   close_fd(pull_fd_);
   close_fd(data_listen_fd_);
@@ -232,21 +235,48 @@ void CommManager::broker_main(int world) {
 }
 
 // ---------------------------------------------------------------- client
+bool CommManager::set_data_transport(const std::string& name, const std::string& libzmq_hint) {
+  if (name == "tcp") {
+    zmq_.reset();
+    return true;
+  }
+  if (name != "zmq") return false;
+  std::string why;
+  if (!ZmqLibrary::load(libzmq_hint, &why)) {
+    LOG_WARN("CommManager", why);
+    return false;
+  }
+  zmq_ = std::make_unique<ZmqLink>();
+  return true;
+}
+
 bool CommManager::start_client(int rank, int world, int num_gpus) {
   rank_ = rank;
   world_ = world;
+  if (!zmq_) {
+    const char* env = std::getenv("STELLATRAIN_DATA_TRANSPORT");
+    if (env != nullptr && std::string(env) == "zmq" && !set_data_transport("zmq")) {
+      set_failed("STELLATRAIN_DATA_TRANSPORT=zmq, but no ZeroMQ library could be loaded (STELLATRAIN_LIBZMQ names one)");
+      return false;
+    }
+  }
   control_fd_ = tcp_connect(master_addr_, master_port_, timeout_ms_);
   if (control_fd_ < 0) { set_failed("cannot reach the broker at " + master_addr_); return false; }
+  const std::string my_ip = master_addr_ == "127.0.0.1" || master_addr_ == "localhost" ? "127.0.0.1" : pick_local_ip();
   uint16_t port = 0;
-  data_listen_fd_ = tcp_listen(0, &port, true);
-  if (data_listen_fd_ < 0) { set_failed("cannot open a data port"); return false; }
+  if (zmq_) {
+    port = zmq_->bind_pull(my_ip == "127.0.0.1" ? my_ip : "*");
+    if (port == 0) { set_failed("cannot bind a ZeroMQ PULL socket"); return false; }
+  } else {
+    data_listen_fd_ = tcp_listen(0, &port, true);
+    if (data_listen_fd_ < 0) { set_failed("cannot open a data port"); return false; }
+  }
   InitReq req{};
   req.rank = static_cast<uint16_t>(rank);
   req.listen_port = port;
   req.num_gpus = static_cast<uint16_t>(num_gpus);
   req.timestamp_ns = now_ns();
-  const std::string ip = master_addr_ == "127.0.0.1" || master_addr_ == "localhost" ? "127.0.0.1" : pick_local_ip();
-  std::strncpy(req.ip, ip.c_str(), sizeof(req.ip) - 1);
+  std::strncpy(req.ip, my_ip.c_str(), sizeof(req.ip) - 1);
   FrameHeader h;
   std::string key;
   std::vector<unsigned char> payload;
@@ -261,9 +291,13 @@ bool CommManager::start_client(int rank, int world, int num_gpus) {
   }
   InitRes res;
   std::memcpy(&res, payload.data(), sizeof(res));
-  push_fd_ = tcp_connect(res.target_ip, res.target_port, timeout_ms_);
-  pull_fd_ = tcp_accept(data_listen_fd_, timeout_ms_);
-  if (push_fd_ < 0 || pull_fd_ < 0) { set_failed("cannot establish the data ring"); return false; }
+  if (zmq_) {
+    if (!zmq_->connect_push(res.target_ip, res.target_port)) { set_failed("cannot connect the ZeroMQ PUSH socket"); return false; }
+  } else {
+    push_fd_ = tcp_connect(res.target_ip, res.target_port, timeout_ms_);
+    pull_fd_ = tcp_accept(data_listen_fd_, timeout_ms_);
+    if (push_fd_ < 0 || pull_fd_ < 0) { set_failed("cannot establish the data ring"); return false; }
+  }
   LOG_INFO("CommManager", "rank " << rank << " -> rank " << res.target_rank << " at " << res.target_ip << ":" << res.target_port);
   push_thread_ = std::thread([this] { push_main(); });
   pull_thread_ = std::thread([this] { pull_main(); });
@@ -483,7 +517,9 @@ void CommManager::push_main() {
         tx_tokens_ -= need;
       }
     }
-    if (!send_frame(push_fd_, kGrad, item->key, item->flags, payload.data(), payload.size(), timeout_ms_)) {
+    const bool sent = zmq_ ? zmq_->send(item->key, item->flags, payload.data(), payload.size(), timeout_ms_)
+                           : send_frame(push_fd_, kGrad, item->key, item->flags, payload.data(), payload.size(), timeout_ms_);
+    if (!sent) {
       if (!stop_) set_failed("send to the ring successor failed for " + item->key);
       return;
     }
@@ -494,13 +530,24 @@ void CommManager::push_main() {
 void CommManager::pull_main() {
   pthread_setname_np(pthread_self(), "CommPullThread");
   while (!stop_) {
-    if (!wait_readable(pull_fd_, 100)) continue;
-    FrameHeader h;
+    FrameHeader h{};
     std::string key;
     std::vector<unsigned char> payload;
-    if (!recv_frame(pull_fd_, &h, &key, &payload, timeout_ms_)) {
-      if (!stop_) set_failed("the ring predecessor closed the connection or sent a truncated frame");
-      return;
+    if (zmq_) {
+      uint8_t flags = 0;
+      bool malformed = false;
+      if (!zmq_->recv(&key, &flags, &payload, 100, &malformed)) {
+        if (malformed && !stop_) { set_failed("malformed ZeroMQ gradient message"); return; }
+        continue;     // nothing within the poll interval (ZeroMQ hides connection loss; the engine's own deadlines catch it)
+      }
+      h.type = kGrad;
+      h.flags = flags;
+    } else {
+      if (!wait_readable(pull_fd_, 100)) continue;
+      if (!recv_frame(pull_fd_, &h, &key, &payload, timeout_ms_)) {
+        if (!stop_) set_failed("the ring predecessor closed the connection or sent a truncated frame");
+        return;
+      }
     }
     if (h.type == kBye) {
       LOG_DEBUG("CommManager", "the ring predecessor shut down");

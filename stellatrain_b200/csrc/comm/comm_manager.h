@@ -24,6 +24,7 @@
 #include <vector>
 
 #include "net_util.h"
+#include "zmq_link.h"
 
 namespace stc {
 
@@ -82,6 +83,13 @@ class CommManager {
   bool start_client(int rank, int world, int num_gpus);
   int rank() const { return rank_; }
   int world() const { return world_; }
+
+  // Transport of the gradient ring, chosen before start_client: "tcp" (length-prefixed frames on plain sockets, the
+  // default) or "zmq" (ZeroMQ PUSH/PULL sockets as in the reference, backend/src/engine/comm_manager.cpp:369-477; the
+  // library is opened at run time, `libzmq_hint` may name it).  The control plane stays on framed TCP either way.
+  // Also selected by STELLATRAIN_DATA_TRANSPORT=zmq.  Returns false when ZeroMQ cannot be loaded.
+  bool set_data_transport(const std::string& name, const std::string& libzmq_hint = "");
+  const char* data_transport() const { return zmq_ ? "zmq" : "tcp"; }
 
   // ---- gradient data (ring)
   void queue_tx(int64_t priority, const std::string& key, const uint32_t* idx, const float* val, size_t count,
@@ -167,6 +175,7 @@ class CommManager {
   std::chrono::steady_clock::time_point tx_last_{};
   BandwidthMonitor rx_mon_;
   std::atomic<uint64_t> bytes_sent_{0}, bytes_recv_{0};
+  std::unique_ptr<ZmqLink> zmq_;                 // set: the ring runs over ZeroMQ PUSH/PULL instead of plain sockets
 };
 
 }  // namespace stc

@@ -51,8 +51,28 @@ def test_shm_manager_offsets_and_barriers():
     del other, master
 
 
-def _ring(world, port):
+def _libzmq_path():
+    """The libzmq that ships inside pyzmq, if that package is installed."""
+    import glob
+    import importlib.util
+
+    spec = importlib.util.find_spec("zmq")
+    if spec is None or not spec.submodule_search_locations:
+        return ""
+    root = os.path.dirname(list(spec.submodule_search_locations)[0])
+    found = sorted(glob.glob(os.path.join(root, "pyzmq.libs", "libzmq*.so*")))
+    return found[0] if found else ""
+
+
+def _ring(world, port, transport="tcp"):
     boxes = [ext.CommManager("127.0.0.1", port, 5000) for _ in range(world)]
+    if transport != "tcp":
+        for b in boxes:
+            if not b.set_data_transport(transport, _libzmq_path()):
+                for x in boxes:
+                    x.close()
+                pytest.skip("no ZeroMQ library on this machine")
+            assert b.data_transport() == transport
     boxes[0].start_server(world)
     oks = [None] * world
     ths = [threading.Thread(target=lambda r=r: oks.__setitem__(r, boxes[r].start_client(r, world, 1))) for r in range(world)]
@@ -114,6 +134,38 @@ def test_comm_ring_stash_narrowing_and_control_plane():
         assert abs(boxes[1].sync_time(4)) < 50.0
         assert boxes[1].report_stat(100.0, 90.0) and _wait_for(lambda: boxes[0].broker_stats()) == [(1, 100.0, 90.0)]
         assert boxes[0].bytes_sent() > 0 and boxes[1].bytes_received() > 0 and boxes[1].rx_peak_bytes_per_s() > 0
+    finally:
+        for b in boxes[::-1]:
+            b.close()
+
+
+def test_comm_ring_over_zeromq_push_pull_sockets():
+    """The reference's data transport: the ring runs over ZeroMQ PUSH/PULL sockets (library opened at run time), with the
+    same keyed messages, the stash for early arrivals, block and 16-bit wire forms and priority order."""
+    boxes = _ring(3, free_port(), "zmq")
+    try:
+        boxes[0].queue_tx(5, "3@1@w!0", [1, 40000, 65535], [0.5, -2.0, 1024.0], 65536, True, 1)
+        assert _wait_for(lambda: boxes[1].stashed() == 1)
+        boxes[1].post_recv("3@1@w!0")
+        (key, flags, idx, val), = boxes[1].drain()
+        assert key == "3@1@w!0" and flags == 0x03 and idx == [1, 40000, 65535] and val == [0.5, -2.0, 1024.0]
+        blk = list(range(64, 80)) + [3] + list(range(160, 176))
+        boxes[2].post_recv("blk")
+        boxes[1].queue_tx(0, "blk", blk, [float(i) for i in blk], 100000)
+        (key, flags, idx, val), = _wait_for(lambda: boxes[2].drain())
+        assert flags == 0x18 and sorted(idx) == sorted(blk) and val == [float(i) for i in idx]
+        # a large message (1 MB of entries) and the ring's last hop back to rank 0
+        n = 120000
+        boxes[0].post_recv("big")
+        boxes[2].queue_tx(0, "big", list(range(0, 2 * n, 2)), [1.0] * n, 1 << 20, True, 0, False)
+        (key, flags, idx, val), = _wait_for(lambda: boxes[0].drain(), timeout=10.0)
+        assert key == "big" and len(idx) == n and idx[-1] == 2 * n - 2
+        assert boxes[2].bytes_sent() > 8 * n and boxes[0].bytes_received() > 8 * n
+        # the control plane next to it is unchanged
+        res = {}
+        ths = [threading.Thread(target=lambda b=b: res.__setitem__(id(b), b.global_barrier())) for b in boxes]
+        [t.start() for t in ths]; [t.join() for t in ths]
+        assert all(res[id(b)] for b in boxes)
     finally:
         for b in boxes[::-1]:
             b.close()
@@ -269,6 +321,23 @@ def test_two_nodes_two_local_processes_match_oracle(method, optimizer, staleness
         assert out["stats_len"] > 100
         for got, w in zip(out["params"], want):
             np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
+
+
+def test_two_nodes_exchange_over_zeromq_like_over_tcp(monkeypatch):
+    """The whole host pipeline with the ring on ZeroMQ PUSH/PULL sockets: same parameters as the oracle."""
+    lib = _libzmq_path()
+    if not lib:
+        pytest.skip("no ZeroMQ library on this machine")
+    monkeypatch.setenv("STELLATRAIN_DATA_TRANSPORT", "zmq")       # the spawned node processes inherit it
+    monkeypatch.setenv("STELLATRAIN_LIBZMQ", lib)
+    world, local_world, steps = 2, 1, 5
+    results = _launch(world, local_world, steps, "thresholdv16", "adam", 1, "ok")
+    assert len(results) == 2 and all(r[2] == "ok" for r in results), results
+    want = _oracle_run(world, local_world, steps, "thresholdv16", "adam")
+    for node, local, _, out in results:
+        assert out["drift"] == 0.0
+        for got, w in zip(out["params"], want):
+            np.testing.assert_allclose(np.asarray(got), w.numpy(), rtol=2e-5, atol=1e-6)
 
 
 def test_wire_formats_block_ids_and_bf16_values():
