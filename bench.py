@@ -64,6 +64,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--state-partition", default="replicated", choices=["replicated", "owner"],
                     help="owner: optimiser state of every tensor on one rank, new values stored into all replicas")
     ap.add_argument("--shape-gbps", default=None, help="lo:hi[:seed] emulated cross-group link, e.g. 10:40:0")
+    ap.add_argument("--shape-destinations", type=int, default=None,
+                    help="charge every stream for this many ranks outside the own group (rehearsal of a shaped link on fewer GPUs)")
+    ap.add_argument("--shape-share", type=float, default=None, help="this rank's share of the scheduled rate (default 1 / group size)")
     ap.add_argument("--controller", type=int, default=0, help="run the telemetry controller and apply its instructions")
     ap.add_argument("--adapt-batch", type=int, default=0, help="with --controller: also apply the per-GPU batch sizes it assigns")
     ap.add_argument("--slow-ranks-ms", type=float, default=0.0,
@@ -484,7 +487,11 @@ def main() -> None:
 
             parts = args.shape_gbps.split(":")
             sched = BandwidthSchedule(seed=int(parts[2]) if len(parts) > 2 else 0, lo_gbps=float(parts[0]), hi_gbps=float(parts[1]))
-            engine.set_link_shaper(sched)      # token bucket on the device: works inside the captured step too
+            if args.shape_share is not None:
+                from stellatrain_b200.control.shaper import DeviceTokenBucket
+
+                sched = DeviceTokenBucket(sched, dev, share=args.shape_share)
+            engine.set_link_shaper(sched, destinations=args.shape_destinations)   # token bucket on the device: works inside the captured step too
         if args.slow_ranks_ms > 0 and rank >= (world + 1) // 2:
             from stellatrain_b200 import _build
 

@@ -352,11 +352,13 @@ class SparseDPEngine:
             mate_done=[pool.peer_addr(base + l, done_off) for l in mates], group_done_ctr=b._group_ctr.data_ptr(),
         )
 
-    def set_link_shaper(self, shaper) -> None:
+    def set_link_shaper(self, shaper, destinations: Optional[int] = None) -> None:
         """Emulate a constrained cross-group link: before a bucket's streams are pushed, a one-thread kernel takes
         the bytes that leave the group from a token bucket in device memory and holds the sparse stream while the
         bucket is in debt (``control.shaper.DeviceTokenBucket``; a host ``TokenBucket`` or a ``BandwidthSchedule`` is
-        turned into one, the ranks of a group sharing the scheduled rate).  Works in eager and in captured steps."""
+        turned into one, the ranks of a group sharing the scheduled rate).  Works in eager and in captured steps.
+        ``destinations`` overrides the number of ranks outside the own group that every stream is charged for (a job
+        without a second group can rehearse a shaped link that way)."""
         from ..control.shaper import BandwidthSchedule, DeviceTokenBucket, TokenBucket
 
         if isinstance(shaper, TokenBucket):
@@ -365,6 +367,7 @@ class SparseDPEngine:
             shaper = DeviceTokenBucket(shaper, self.device, share=1.0 / self.group_size)
         self.shaper = shaper
         self._shaped_bytes = 0
+        self._shaped_destinations = destinations
         self._push_shaper()
 
     def _push_shaper(self) -> None:
@@ -372,7 +375,7 @@ class SparseDPEngine:
             return
         self.native.set_shaper(self.shaper.state.data_ptr(), self.shaper.MAX_HOLD_NS)
         for bi, rt in enumerate(self.buckets):
-            self.native.set_shaped_bytes(bi, rt.bucket.layout.wire_bytes(owned_only=True) * (self.world - self.group_size))
+            self.native.set_shaped_bytes(bi, rt.bucket.layout.wire_bytes(owned_only=True) * self._remote_ranks())
 
     @property
     def shaped_bytes(self) -> int:
@@ -405,12 +408,18 @@ class SparseDPEngine:
 
     def shaped_bytes_per_step(self) -> int:
         """Bytes this rank stores into other groups per iteration (what the shaper charges)."""
-        return sum(rt.bucket.layout.wire_bytes(owned_only=True) for rt in self.buckets) * (self.world - self.group_size)
+        return sum(rt.bucket.layout.wire_bytes(owned_only=True) for rt in self.buckets) * self._remote_ranks()
+
+    def _remote_ranks(self) -> int:
+        d = getattr(self, "_shaped_destinations", None)
+        return (self.world - self.group_size) if d is None else int(d)
 
     # ------------------------------------------------------------------ step clock
     def stamp(self, slot: int) -> None:
         """Write the device clock into slot 0..7 of ``step_stamps`` when the current stream gets here (capturable):
-        0 forward begins, 1 backward begins, 2 backward ended.  Step timing that survives CUDA-graph replay."""
+        0 forward begins (behind the wait for outstanding updates), 1 backward begins, 2 backward ended, 3 in front of
+        that wait (eager launches), 4 behind the join of a captured iteration with its bucket chains.  Step timing
+        that survives CUDA-graph replay."""
         from .. import _build
 
         if not hasattr(self, "step_stamps"):
@@ -552,6 +561,8 @@ class SparseDPEngine:
         if all(rt.pending == rt.full for rt in self.buckets):     # first micro-step of an iteration
             self.before_iteration()
         cur = torch.cuda.current_stream(self.device)
+        if self.cfg.step_clock:
+            self.stamp(3)             # in front of the waits: (0) - (3) is the time this forward was held back by updates
         if self.native is not None:
             if self._gated:
                 for bi in range(len(self.buckets)):
@@ -638,7 +649,7 @@ class SparseDPEngine:
                 b.handle.group_reduce(s.cuda_stream)
                 self.stats["kernels"] += 3
             if self.shaper is not None:
-                nbytes = b.layout.wire_bytes(owned_only=True) * (self.world - self.group_size)   # stored into other groups
+                nbytes = b.layout.wire_bytes(owned_only=True) * self._remote_ranks()   # stored into other groups
                 self._shaped_bytes += nbytes
                 self.shaper.take(nbytes, s)
                 self.stats["kernels"] += 1

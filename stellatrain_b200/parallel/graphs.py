@@ -51,6 +51,8 @@ class GraphedStep:
             with torch.cuda.graph(self.graph, stream=side):
                 self.loss = step_fn(*self.static_inputs)
                 torch.cuda.current_stream(dev).wait_stream(engine.sparse_stream)
+                if engine.cfg.step_clock:
+                    engine.stamp(4)      # behind the join: (4) - (2) is the time the iteration waited for its bucket chains
         finally:
             # A replay reads the captured gradient addresses from pinned rows of its own and reads the gradients
             # themselves at those addresses: both stay alive as long as this object does.

@@ -16,8 +16,8 @@ but never instantiates them in its engine.  Here the loop is closed:
 Measurements are device times: three one-thread kernels write the GPU's clock when the compute stream reaches
 the start of the forward pass (behind the wait for the updates this forward must see), the start of backward and
 its end, so the numbers are the same whether the iteration is launched kernel by kernel or replayed from a graph.
-They give forward, backward and the gap between the end of one backward and the start of the next forward, which
-holds the exposed communication: the time the stream was blocked on outstanding updates or on the shaped link.
+They give forward, backward and the exposed communication: the time the stream was blocked on outstanding updates or on
+the shaped link (the wait in front of an eagerly launched forward, or the join behind a captured iteration).
 The stamps of iteration i are read while iteration i + 1 runs, so nothing here makes the host wait for the GPU.
 Throughput fields come from the bytes the engine pushed during the step.
 """
@@ -49,7 +49,7 @@ class TelemetryHook:
         self.lock = threading.Lock()
         self.client = None
         self._callback = _WeakInstruction(self)
-        self._ring = [torch.zeros(3, dtype=torch.int64).pin_memory() for _ in range(4)]   # stamps of the last iterations
+        self._ring = [torch.zeros(5, dtype=torch.int64).pin_memory() for _ in range(4)]   # stamps of the last iterations
         self._ring_events: List[Optional[torch.cuda.Event]] = [None] * 4
         self._prev_b1 = 0             # device clock at the end of the previous measured backward
         engine.cfg.step_clock = True  # the engine stamps the start of every forward behind its gate
@@ -145,7 +145,7 @@ class TelemetryHook:
         eng = self.engine
         slot = self.iteration % len(self._ring)
         if hasattr(eng, "step_stamps"):
-            self._ring[slot].copy_(eng.step_stamps[:3], non_blocking=True)
+            self._ring[slot].copy_(eng.step_stamps[:5], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
             self._ring_events[slot] = ev
@@ -165,13 +165,22 @@ class TelemetryHook:
             return
         ev.synchronize()
         self._ring_events[slot] = None
-        f0, f1, b1 = (int(v) for v in self._ring[slot])
+        f0, f1, b1, pre, joined = (int(v) for v in self._ring[slot])
         if not (f0 and b1):
             return
         split = f0 <= f1 <= b1                 # the start of backward was stamped in this iteration
         fwd = (f1 - f0) / 1e6 if split else 0.0
         bwd = (b1 - f1) / 1e6 if split else (b1 - f0) / 1e6
-        gap = max(0.0, (f0 - self._prev_b1) / 1e6) if self._prev_b1 else 0.0
+        # Exposed communication, on the device's clock: a captured iteration ends with a join of its bucket chains
+        # (stamp 4 behind it), an eagerly launched one waits at the start of the next forward (stamp 3 in front).
+        # Host-side pauses (a new capture, a slow launch loop) are in neither, unlike in the distance between the end
+        # of one backward and the start of the next forward.
+        if joined >= b1:
+            gap = (joined - b1) / 1e6
+        elif 0 < pre <= f0:
+            gap = (f0 - pre) / 1e6
+        else:
+            gap = 0.0
         self._prev_b1 = b1
         # bytes this rank stored into one peer (4-byte entries for tensors on the narrow wire format)
         nbytes = sum(rt.bucket.layout.wire_bytes() for rt in self.engine.buckets) * self.bytes_per_entry / 8.0
