@@ -560,13 +560,18 @@ def main() -> None:
 
     sparse_arm = engine is not None      # this package's engine: the wrapper owns the iteration (eager or captured)
 
+    samples = [0]       # samples this rank really processed (the controller may change the per-GPU batch)
+
     def train_step(x, y):
         if sparse_arm:
             if hook is not None:
                 if args.adapt_batch:
                     x, y = hook.resize_batch(x, y)
+                samples[0] += x.shape[0]
                 return hook.run(net, x, y)
+            samples[0] += x.shape[0]
             return net.train_step(x, y)
+        samples[0] += x.shape[0]
         loss = fwd_bwd(x, y)
         if opt is not None:
             opt.step()
@@ -655,9 +660,16 @@ def main() -> None:
         if not net._graphs:
             sys.stderr.write("[bench] the step was not captured; running eagerly\n")
             args.graph = 0
+    samples0 = samples[0]
     ms, clocks, launches = timed(lambda i: run_step_device(), args.steps)
     per_step = ms / args.steps
     unit_per_step = args.batch * world * (args.seq_len if lm else 1)
+    if args.adapt_batch and world >= 1:
+        # unequal, changing batches: count what was processed
+        done = torch.tensor([float(samples[0] - samples0)], device=dev)
+        if world > 1:
+            dist.all_reduce(done)
+        unit_per_step = float(done.item()) / args.steps * (args.seq_len if lm else 1)
     value = unit_per_step / (per_step / 1e3)
 
     e2e = None
