@@ -39,6 +39,6 @@ class BuildPy(build_py):
 
 setup(
     packages=find_packages(include=["stellatrain_b200", "stellatrain_b200.*"]),
-    package_data={"stellatrain_b200": ["*.so", "*.pyi", "csrc/**/*", "utils/*.txt"]},
+    package_data={"stellatrain_b200": ["*.so", "*.pyi", "csrc/**/*", "utils/*.txt", "control/profiles/*.json"]},
     cmdclass={"build_ext": BuildExt, "build_py": BuildPy},
 )

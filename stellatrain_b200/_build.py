@@ -133,9 +133,28 @@ def _run(cmd: list[str]) -> str:
 
 
 def build_extension(name: str, force: bool = False, verbose: bool = False) -> Path:
-    """Compile and link one extension; returns the path of the shared object."""
+    """Compile and link one extension; returns the path of the shared object.
+
+    Several ranks of one job may find the extension stale at the same moment (sources newer than the shipped
+    objects): one of them builds while the others wait on a lock file and then find the result current.  Objects go
+    to a directory of the building process and the shared object is renamed into place, so nobody ever loads a
+    half-written file."""
     if not force and is_current(name):
         return so_path(name)
+    import fcntl
+
+    OBJ_DIR.mkdir(exist_ok=True)
+    with open(OBJ_DIR / f"{name}.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and is_current(name):
+                return so_path(name)
+            return _build_locked(name, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(name: str, verbose: bool) -> Path:
     spec = _existing(name)
     if not spec["cu"] and not spec["cpp"]:
         raise RuntimeError(f"extension {name} has no sources")
@@ -171,10 +190,12 @@ def build_extension(name: str, force: bool = False, verbose: bool = False) -> Pa
             if o.strip():
                 print(o)
     so = so_path(name)
+    tmp = so.with_name(so.name + f".tmp{os.getpid()}")
     if spec["link"] == "nvcc":
-        _run([nvcc, "-shared", "-o", str(so), *map(str, objs), *link_extra])
+        _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), *link_extra])
     else:
-        _run(["g++", "-shared", "-o", str(so), *map(str, objs), "-pthread", "-lrt", "-ldl"])
+        _run(["g++", "-shared", "-o", str(tmp), *map(str, objs), "-pthread", "-lrt", "-ldl"])
+    os.replace(tmp, so)
     _stamp_path(name).write_text(json.dumps({"hash": _source_hash(name)}))
     return so
 

@@ -24,7 +24,7 @@ import numpy as np
 import pandas as pd
 
 from . import messages as M
-from .gp_profile import load_profile
+from .gp_profile import AnalyticProfile, load_profile
 from .optimizer import BatchRateOptimizer, TrafficModel, max_batch_for
 
 LOG_PATH = "/tmp/stellatrain-b200-controller.log"
@@ -48,7 +48,10 @@ class Controller:
                  profile_path: Optional[str] = None, transport: str = "nvlink", state_path: Optional[str] = None,
                  wire_blocks: Optional[bool] = None, max_batch: Optional[int] = None) -> None:
         self.adapt = (os.environ.get("DISABLE_RATE_ADAPT", "0") in ("", "0")) if adapt is None else adapt
-        self.profile = load_profile(profile_path or os.environ.get("MODEL_PROFILE"))
+        # Without a named profile (argument or MODEL_PROFILE, batch_rate_alloc_optim.py:139-141) the one that ships for the
+        # clients' kind of GPU is taken once their names are known, and the analytic surrogate when none ships.
+        self.profile_path = profile_path or os.environ.get("MODEL_PROFILE")
+        self.profile = load_profile(self.profile_path)
         self.transport = transport
         self.max_batch = max_batch        # per-GPU batch ceiling of this job; None: by device name (MAX_BATCH_SIZE_MAP)
         # the CPU tier's TCP messages carry whole blocks of 16 entries behind one block id by default: the byte model
@@ -115,6 +118,7 @@ class Controller:
                         self.scoreboard.loc[li.gpu_id, ["location", "gpu"]] = [f"{li.rank}:{li.local_rank}", li.gpu_name]
                         if self.optimizer is not None and li.gpu_id < self.optimizer.num_gpus:
                             self.optimizer.set_max_batch(li.gpu_id, self.max_batch or max_batch_for(li.gpu_name))
+                        self._choose_profile()
                 elif mtype == M.LOCAL:
                     t = M.parse(mtype, payload)
                     self.rx.put(t)
@@ -135,10 +139,23 @@ class Controller:
         finally:
             conn.close()
 
+    def _choose_profile(self) -> None:
+        """Called with the lock held, whenever a client or the job description arrives."""
+        if self.profile_path:
+            return
+        for c in self.clients.values():
+            chosen = load_profile(None, c.gpu_name)
+            if isinstance(self.profile, AnalyticProfile) and not isinstance(chosen, AnalyticProfile):
+                self.profile = chosen
+                if self.optimizer is not None:
+                    self.optimizer.profile = chosen
+                return
+
     def _on_global_init(self, gi: M.GlobalInit) -> None:
         with self.lock:
             self.global_init = gi
             traffic = TrafficModel(gi.param_counts, self.transport, gi.grad_fp16, gi.grad_idx_u16, grad_block16=self.wire_blocks)
+            self._choose_profile()
             self.optimizer = BatchRateOptimizer(gi.num_gpus, gi.num_nodes, traffic, self.profile,
                                                 latest_iter=lambda: self.latest_iter)
             for gid, c in self.clients.items():

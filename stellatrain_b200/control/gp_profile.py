@@ -122,9 +122,27 @@ class AnalyticProfile:
         return batch_term + bw_term
 
 
-def load_profile(path: Optional[str]):
+# Profiles that ship with the package, by a substring of the device name a client reports.
+SHIPPED_PROFILES = {"B200": "b200_gpt2_small.json"}
+
+
+def shipped_profile_path(gpu_name: Optional[str]) -> Optional[Path]:
+    """The fitted profile that ships for this kind of GPU (``sweep_profile.py`` produced it), or None."""
+    for needle, fname in SHIPPED_PROFILES.items():
+        if gpu_name and needle in gpu_name:
+            path = Path(__file__).parent / "profiles" / fname
+            if path.exists():
+                return path
+    return None
+
+
+def load_profile(path: Optional[str], gpu_name: Optional[str] = None):
+    """``path`` (or, without one, the profile that ships for ``gpu_name``; the analytic surrogate when there is none)."""
     if not path:
-        return AnalyticProfile()
+        shipped = shipped_profile_path(gpu_name)
+        if shipped is None:
+            return AnalyticProfile()
+        return GPProfile.load(shipped)
     p = Path(path)
     if p.suffix in (".pkl", ".pickle"):
         raise ValueError("pickled scikit-optimize profiles are not loaded here; convert them once with "

@@ -15,6 +15,12 @@ entry, ``--step-ms`` per iteration at ``--ref-batch``, iteration time growing wi
 many samples the run needs to reach the target loss; h is the relative excess over the best point divided by 50, so
 that ``1 + 50 h`` is "samples needed, relative to the best configuration".  The fit is ``gp_profile.fit_profile``.
 
+The bandwidth axis of the fitted profile is relative: 1.0 is the bandwidth that carries the kept fraction of the
+profile's operating point (``--ref-bandwidth`` Gbps at ``--ref-batch``), which is the unit in which the controller asks
+(it rescales the measured rate by what its own job needs at the profile's compression ratio,
+``optimizer.BatchRateOptimizer._conversion_factor``).  ``--refit`` fits again from the rows of an existing file without
+repeating the sweep.
+
 What the profile carries over to a real job is the shape of the trade-off (less bandwidth, more compression, more
 samples; larger batches, fewer but more expensive steps), not absolute numbers: the task is synthetic.
 """
@@ -98,6 +104,30 @@ def samples_to_target(total_batch: int, kept: float, world: int = 8, target: flo
     return math.inf
 
 
+def fit_rows(rows, args) -> dict:
+    """rows: (total batch, bandwidth in Gbps, kept fraction, samples to target)."""
+    finite = [r[3] for r in rows if r[3] is not None and math.isfinite(r[3])]
+    best, worst = min(finite), max(finite)
+    need = [(r[3] if r[3] is not None and math.isfinite(r[3]) else 2.0 * worst) for r in rows]
+    penalty = [(n / best - 1.0) / 50.0 for n in need]
+    batches = sorted({r[0] for r in rows})
+    kept_ref = kept_fraction(args.ref_bandwidth, args.ref_batch, args.ref_batch, args.step_ms, args.params)
+    meta = ProfileMeta(batch_size=args.ref_batch, max_batch_size=float(max(batches)), min_batch_size=float(min(batches)),
+                       bandwidth=1.0, compression=1.0 - kept_ref, model=args.model)
+    prof = fit_profile([r[0] for r in rows], [r[1] / args.ref_bandwidth for r in rows], penalty, meta,
+                       length_scale=(0.35, 1.5), noise=1e-3)
+    return {"x_train": prof.x_train.tolist(), "alpha": prof.alpha.tolist(), "length_scale": prof.length_scale.tolist(),
+            "constant": prof.constant, "nu": prof.nu, "y_mean": prof.y_mean, "y_std": prof.y_std, "metadata": meta.__dict__,
+            "sweep": {"columns": ["total_batch", "bandwidth_gbps", "kept_fraction", "samples_to_target", "h"],
+                      "rows": [[r[0], r[1], r[2], (r[3] if r[3] is not None and math.isfinite(r[3]) else None), p]
+                               for r, p in zip(rows, penalty)],
+                      "world": args.world, "params": args.params, "step_ms": args.step_ms, "ref_batch": args.ref_batch,
+                      "ref_bandwidth_gbps": args.ref_bandwidth, "best_samples": best, "worst_samples": worst,
+                      "bandwidth_axis": "multiples of ref_bandwidth_gbps",
+                      "task": "labels of a fixed random teacher MLP (32-128-8), student of the same shape, error feedback + "
+                              "top-k split over the ranks + lazy sparse Adam, target loss 1.02 on 2048 held-out samples"}}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", required=True)
@@ -109,7 +139,14 @@ def main() -> None:
     ap.add_argument("--bandwidths", default="2.5,5,10,20,40,80", help="Gbps")
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--seeds", type=int, default=2)
+    ap.add_argument("--ref-bandwidth", type=float, default=10.0, help="Gbps of the profile's operating point")
+    ap.add_argument("--refit", default=None, help="fit from the sweep rows of this file instead of training")
     args = ap.parse_args()
+    if args.refit:
+        rows = [tuple(r[:4]) for r in json.loads(Path(args.refit).read_text())["sweep"]["rows"]]
+        Path(args.out).write_text(json.dumps(fit_rows(rows, args), indent=1))
+        print(f"wrote {args.out}: fitted again from {len(rows)} rows of {args.refit}")
+        return
     torch.set_num_threads(max(1, torch.get_num_threads()))
     batches = [int(b) for b in args.batches.split(",")]
     bws = [float(b) for b in args.bandwidths.split(",")]
@@ -120,24 +157,11 @@ def main() -> None:
             need = float(np.median([samples_to_target(b, kept, args.world, seed=s) for s in range(args.seeds)]))
             rows.append((b, bw, kept, need))
             print(f"batch {b:4d}  {bw:5.1f} Gbps  kept {kept:7.4f}  samples to target {need:10.0f}", flush=True)
-    finite = [r[3] for r in rows if math.isfinite(r[3])]
-    best = min(finite)
-    worst = max(finite)
-    penalty = [((r[3] if math.isfinite(r[3]) else 2.0 * worst) / best - 1.0) / 50.0 for r in rows]
-    meta = ProfileMeta(batch_size=args.ref_batch, max_batch_size=float(max(batches)), min_batch_size=float(min(batches)),
-                       bandwidth=10.0, compression=1.0 - kept_fraction(10.0, args.ref_batch, args.ref_batch, args.step_ms, args.params),
-                       model=args.model)
-    prof = fit_profile([r[0] for r in rows], [r[1] for r in rows], penalty, meta, length_scale=(0.35, 1.5), noise=1e-3)
-    out = {"x_train": prof.x_train.tolist(), "alpha": prof.alpha.tolist(), "length_scale": prof.length_scale.tolist(),
-           "constant": prof.constant, "nu": prof.nu, "y_mean": prof.y_mean, "y_std": prof.y_std, "metadata": meta.__dict__,
-           "sweep": {"columns": ["total_batch", "bandwidth_gbps", "kept_fraction", "samples_to_target", "h"],
-                     "rows": [[r[0], r[1], r[2], (r[3] if math.isfinite(r[3]) else None), p] for r, p in zip(rows, penalty)],
-                     "world": args.world, "params": args.params, "step_ms": args.step_ms, "ref_batch": args.ref_batch,
-                     "task": "labels of a fixed random teacher MLP (32-128-8), student of the same shape, error feedback + "
-                             "top-k split over the ranks + lazy sparse Adam, target loss 1.02 on 2048 held-out samples"}}
+    out = fit_rows(rows, args)
     Path(args.out).parent.mkdir(parents=True, exist_ok=True)
     Path(args.out).write_text(json.dumps(out, indent=1))
-    print(f"wrote {args.out}: {len(rows)} points, best {best:.0f} samples, worst {worst:.0f}")
+    print(f"wrote {args.out}: {len(rows)} points, best {out['sweep']['best_samples']:.0f} samples, "
+          f"worst {out['sweep']['worst_samples']:.0f}")
 
 
 if __name__ == "__main__":

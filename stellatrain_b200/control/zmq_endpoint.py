@@ -93,6 +93,7 @@ class ZmqControllerEndpoint:
                 c.scoreboard.loc[li.gpu_id, ["location", "gpu"]] = [f"{li.rank}:{li.local_rank}", li.gpu_name]
                 if c.optimizer is not None and li.gpu_id < c.optimizer.num_gpus:
                     c.optimizer.set_max_batch(li.gpu_id, getattr(c, "max_batch", None) or max_batch_for(li.gpu_name))
+                c._choose_profile()
         elif rtype == PB.REQ_LOCAL_TELEMETRY and payload is not None:
             t: M.LocalTelemetry = payload
             c.rx.put(t)

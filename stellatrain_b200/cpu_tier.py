@@ -104,7 +104,11 @@ class CpuOffloadEngine:
                  optimizer: str = "sgd", optimizer_options: Optional[dict] = None, data_bytes: int = 0,
                  timeout_ms: int = 30000, workers: int = 0, debug_accuracy: bool = False, debug_barrier: bool = False,
                  wire_blocks: bool = True, wire_values: str = "fp32", native_copies: Optional[bool] = None,
-                 data_transport: str = "tcp"):
+                 data_transport: str = "tcp", bundle_elems: int = 1 << 16):
+        """``bundle_elems``: tensors with fewer elements than this are registered in bundles (consecutive small
+        tensors, laid end to end, closed once a bundle holds that many elements) that pass through the pipeline as one
+        task per iteration; selection still treats every tensor by itself.  0 gives one task per tensor, which is what
+        the reference does (backend/src/engine/core.cpp:1025-1095) and costs it a fixed price per tensor per iteration."""
         ext = _load()
         if data_transport == "zmq":
             # the ring between nodes over ZeroMQ PUSH/PULL sockets, the reference's transport; the native comm manager
@@ -138,25 +142,60 @@ class CpuOffloadEngine:
         for k, v in (optimizer_options or {}).items():
             self.engine.configure_optimizer(k, v)
         self.grad_accumulation = gradient_accumulation
-        self.params = []
-        self._index = {}
-        for li, (name, p) in enumerate(params):
+        self.params = [p for _, p in params]
+        self._meta["bundle_elems"] = int(bundle_elems)
+        for name, p in params:
             if not p.is_contiguous():
                 raise ValueError(f"parameter {name} must be contiguous")
-            if self.cuda:
-                # the engine never writes device memory through `user_param`; it starts the master copy from a host copy
-                # of the initial values
-                init = p.detach().reshape(-1).to("cpu", torch.float32).contiguous()
-                idx = self.engine.pre_train_init(li, name[-40:], p.numel(), 0, init.data_ptr())
+        # units: what the native engine sees as one parameter.  (first layer index, key, [(name, tensor, offset)], numel)
+        self._units = []
+        open_unit = None
+        layer_of = {name: li for li, (name, _) in enumerate(params)}
+        for li, (name, p) in enumerate(params):
+            if p.numel() >= bundle_elems:
+                self._units.append([li, name[-40:], [(name, p, 0)], p.numel()])
+                continue
+            if open_unit is None:
+                open_unit = [li, "", [], 0]
+                self._units.append(open_unit)
+            open_unit[2].append((name, p, open_unit[3]))
+            open_unit[3] += (p.numel() + 15) // 16 * 16        # aligned blocks of a member stay aligned in the bundle
+            if open_unit[3] >= bundle_elems:
+                open_unit = None
+        self._where = {}               # id(tensor) -> (engine index, member number or -1)
+        self._stash = {}               # engine index -> gradients of a bundle's members waiting for the last one
+        for unit in self._units:
+            li, key, members, total = unit
+            if len(members) == 1:
+                name, p, _ = members[0]
+                unit[1] = key = name[-40:]
+                unit[3] = total = p.numel()
+                if self.cuda:
+                    # the engine never writes device memory through `user_param`; it starts the master copy from a
+                    # host copy of the initial values
+                    init = p.detach().reshape(-1).to("cpu", torch.float32).contiguous()
+                    idx = self.engine.pre_train_init(li, key, total, 0, init.data_ptr())
+                else:
+                    idx = self.engine.pre_train_init(li, key, total, p.data.data_ptr())
+                self._where[id(p)] = (idx, -1)
             else:
-                idx = self.engine.pre_train_init(li, name[-40:], p.numel(), p.data.data_ptr())
-            self.params.append(p)
-            self._index[id(p)] = idx
+                unit[1] = key = f"{members[0][0][-28:]}+{len(members) - 1}"
+                init = torch.zeros(total, dtype=torch.float32)
+                for name, p, off in members:
+                    init[off:off + p.numel()] = p.detach().reshape(-1).to("cpu", torch.float32)
+                idx = self.engine.pre_train_init(li, key, total, 0, init.data_ptr())
+                self.engine.set_param_members(idx, [f"{layer_of[name]}@{name[-40:]}" for name, _, _ in members],
+                                              [off for _, _, off in members], [p.numel() for _, p, _ in members],
+                                              [] if self.cuda else [p.data.data_ptr() for _, p, _ in members])
+                for m, (_, p, _) in enumerate(members):
+                    self._where[id(p)] = (idx, m)
+            unit.append(idx)
             if self.cuda:
-                master = _from_ptr(self.engine.master_param(idx), p.numel())
-                p.data.copy_(master.view_as(p), non_blocking=False)
+                master = _from_ptr(self.engine.master_param(idx), total)
+                for _, p, off in members:
+                    p.data.copy_(master[off:off + p.numel()].view_as(p), non_blocking=False)
         # CUDA parameters, two ways to move data: copies issued by this class with torch streams and two helper threads,
-        # or by the native engine itself (event, stream wait, asynchronous copy and a host callback per tensor, its
+        # or by the native engine itself (event, stream wait, asynchronous copy and a host callback per task, its
         # D2H_Copy / H2D_Copy stages); the second needs no Python thread on the path of a task
         if native_copies is None:
             native_copies = self.cuda and self.engine.device_copies_available()
@@ -165,8 +204,11 @@ class CpuOffloadEngine:
             if not self.engine.device_copies_available():
                 raise RuntimeError("native_copies=True needs the CUDA runtime in this process")
             self._native_streams = [torch.cuda.Stream() for _ in range(4)]
-            for idx, p in enumerate(self.params):
-                self.engine.attach_device_param(self._index[id(p)], p.data.data_ptr())
+            for _, _, members, _, idx in self._units:
+                if len(members) == 1:
+                    self.engine.attach_device_param(idx, members[0][1].data.data_ptr())
+                else:
+                    self.engine.attach_device_members(idx, [p.data.data_ptr() for _, p, _ in members])
         self._hooks = [p.register_post_accumulate_grad_hook(self._on_grad) for p in self.params]
         self._hooks.append(module.register_forward_pre_hook(self._pre_forward))
         self._stop = False
@@ -184,37 +226,57 @@ class CpuOffloadEngine:
     def _pre_forward(self, _mod, _inp) -> None:
         if self._micro != 0:
             return   # later micro-iterations do not wait (model_wrapper.py:88-92)
-        for i in range(len(self.params)):
+        for i in range(len(self._units)):
             self.engine.pre_forward_process(i)
 
     def _on_grad(self, p: torch.Tensor) -> None:
-        idx = self._index[id(p)]
+        idx, member = self._where[id(p)]
         g = p.grad
         if not self.cuda:
-            self.engine.post_backward_process(idx, g.contiguous().data_ptr())
+            if member < 0:
+                self.engine.post_backward_process(idx, g.contiguous().data_ptr())
+            else:
+                self.engine.post_backward_member(idx, member, g.contiguous().data_ptr())
             p.grad = None
+            return
+        # device accumulation across micro-iterations, one D2H at the end (core.cpp:781-788)
+        if self._micro != self.grad_accumulation - 1:
+            return
+        g = g if (g.is_contiguous() and g.dtype == torch.float32) else g.contiguous().float()
+        p.grad = None
+        members = self._units[idx][2]
+        if member < 0:
+            grads = [g]
         else:
-            # device accumulation across micro-iterations, one D2H at the end (core.cpp:781-788)
-            last = (self._micro == self.grad_accumulation - 1)
-            if last and self.native_copies:
-                g = g if (g.is_contiguous() and g.dtype == torch.float32) else g.contiguous().float()
-                stream = self._native_streams[idx % len(self._native_streams)]
-                self.engine.post_backward_device(idx, g.data_ptr(), torch.cuda.current_stream().cuda_stream, stream.cuda_stream)
-                g.record_stream(stream)          # the allocator must not reuse the gradient before the copy has read it
-                p.grad = None
-            elif last:
-                slot = _from_ptr(self.engine.claim_grad_slot(idx), p.numel())   # one per iteration, in turn
-                ev = torch.cuda.Event()
-                cur = torch.cuda.current_stream()
-                self._copy_stream.wait_stream(cur)
-                with torch.cuda.stream(self._copy_stream):
-                    slot.copy_(g.reshape(-1), non_blocking=True)
-                    g.record_stream(self._copy_stream)
-                    ev.record(self._copy_stream)
-                p.grad = None
-                with self._d2h_cv:
-                    self._pending_events.append((ev, idx))
-                    self._d2h_cv.notify()
+            # a bundle leaves the device when its last member's gradient is there
+            stash = self._stash.setdefault(idx, {})
+            stash[member] = g
+            if len(stash) < len(members):
+                return
+            grads = [stash[m] for m in range(len(members))]
+            del self._stash[idx]
+        if self.native_copies:
+            stream = self._native_streams[idx % len(self._native_streams)]
+            cur = torch.cuda.current_stream().cuda_stream
+            if member < 0:
+                self.engine.post_backward_device(idx, g.data_ptr(), cur, stream.cuda_stream)
+            else:
+                self.engine.post_backward_device_members(idx, [t.data_ptr() for t in grads], cur, stream.cuda_stream)
+            for t in grads:
+                t.record_stream(stream)          # the allocator must not reuse the gradient before the copy has read it
+        else:
+            slot = _from_ptr(self.engine.claim_grad_slot(idx), self._units[idx][3])   # one per iteration, in turn
+            ev = torch.cuda.Event()
+            cur = torch.cuda.current_stream()
+            self._copy_stream.wait_stream(cur)
+            with torch.cuda.stream(self._copy_stream):
+                for t, (_, q, off) in zip(grads, members):
+                    slot[off:off + q.numel()].copy_(t.reshape(-1), non_blocking=True)
+                    t.record_stream(self._copy_stream)
+                ev.record(self._copy_stream)
+            with self._d2h_cv:
+                self._pending_events.append((ev, idx))
+                self._d2h_cv.notify()
 
     @property
     def _micro(self) -> int:
@@ -238,10 +300,10 @@ class CpuOffloadEngine:
         stream = torch.cuda.Stream()
         while not self._stop:
             for idx, it in self.engine.pop_ready_updates(50):
-                p = self.params[idx]
-                master = _from_ptr(self.engine.master_param(idx), p.numel())
+                master = _from_ptr(self.engine.master_param(idx), self._units[idx][3])
                 with torch.cuda.stream(stream):
-                    p.data.copy_(master.view_as(p), non_blocking=True)
+                    for _, p, off in self._units[idx][2]:
+                        p.data.copy_(master[off:off + p.numel()].view_as(p), non_blocking=True)
                 stream.synchronize()
                 self.engine.copy_out_done(idx, it)
 
@@ -277,11 +339,11 @@ class CpuOffloadEngine:
     def replica_drift(self) -> float:
         """Largest difference between this node's master copy and node 0's (0.0 on one node)."""
         self.synchronize()
-        return max((self.engine.force_model_sync(i, True) for i in range(len(self.params))), default=0.0)
+        return max((self.engine.force_model_sync(i, True) for i in range(len(self._units))), default=0.0)
 
     def broadcast_parameters(self) -> None:
         self.synchronize()
-        for i in range(len(self.params)):
+        for i in range(len(self._units)):
             self.engine.force_model_sync(i, False)
 
     # ------------------------------------------------------------------ checkpoint
@@ -293,9 +355,11 @@ class CpuOffloadEngine:
         The reference keeps all of this only in memory (backend/src/optim/adam.h:15-18, sgd.h:15-18,
         compress/thresholdv16.h:13-14, engine/core.h:63)."""
         self.synchronize()
-        names = [n for n, p in self.module.named_parameters() if p.requires_grad]
-        resid = {n: _from_ptr(self.engine.grad_residual(i), p.numel()).clone()
-                 for i, (n, p) in enumerate(zip(names, self.params))}
+        resid = {}
+        for _, _, members, total, idx in self._units:
+            whole = _from_ptr(self.engine.grad_residual(idx), total)
+            for n, p, off in members:
+                resid[n] = whole[off:off + p.numel()].clone()
         opt = {}
         for tensor, (arrays, counters) in self.engine.optimizer_state().items():
             opt[tensor] = {"arrays": {k: torch.frombuffer(bytearray(v), dtype=torch.float32).clone() if len(v) else
@@ -315,11 +379,16 @@ class CpuOffloadEngine:
             raise ValueError(f"checkpoint was written by the {sd['optimizer']['kind']} optimiser")
         self.synchronize()
         self.module.load_state_dict(sd["model"])
+        if sd["engine"].get("bundle_elems", 0) != self._meta["bundle_elems"]:
+            raise ValueError("checkpoint was written with bundle_elems=%d: the optimiser state is laid out by bundle, build "
+                             "the engine with the same value" % sd["engine"].get("bundle_elems", 0))
         if self._local_rank == 0:
-            names = [n for n, p in self.module.named_parameters() if p.requires_grad]
-            for i, (n, p) in enumerate(zip(names, self.params)):
-                _from_ptr(self.engine.master_param(i), p.numel()).copy_(p.detach().reshape(-1).to("cpu", torch.float32))
-                _from_ptr(self.engine.grad_residual(i), p.numel()).copy_(sd["sparsifier"]["residual"][n])
+            for _, _, members, total, idx in self._units:
+                master = _from_ptr(self.engine.master_param(idx), total)
+                whole = _from_ptr(self.engine.grad_residual(idx), total)
+                for n, p, off in members:
+                    master[off:off + p.numel()].copy_(p.detach().reshape(-1).to("cpu", torch.float32))
+                    whole[off:off + p.numel()].copy_(sd["sparsifier"]["residual"][n])
             self.engine.set_optimizer_state({t: ({k: v.contiguous().numpy().tobytes() for k, v in st["arrays"].items()},
                                                  {k: int(c) for k, c in st["counters"].items()})
                                              for t, st in sd["optimizer"]["state"].items()})

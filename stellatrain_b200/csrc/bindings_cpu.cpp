@@ -361,6 +361,28 @@ PYBIND11_MODULE(_Ccpu, m) {
       .def("post_backward_device", [](CpuEngine& e, int i, uint64_t grad, uint64_t producer_stream, uint64_t copy_stream) {
         e.post_backward_device(i, P<const void>(grad), P<void>(producer_stream), P<void>(copy_stream));
       }, py::arg("param_index"), py::arg("device_grad"), py::arg("producer_stream"), py::arg("copy_stream") = 0)
+      .def("set_param_members", [](CpuEngine& e, int i, const std::vector<std::string>& keys, const std::vector<uint32_t>& offsets,
+                                   const std::vector<uint32_t>& numels, const std::vector<uint64_t>& user_params) {
+        std::vector<float*> up;
+        for (uint64_t u : user_params) up.push_back(P<float>(u));
+        e.set_param_members(i, keys, offsets, numels, up);
+      }, py::arg("param_index"), py::arg("keys"), py::arg("offsets"), py::arg("numels"), py::arg("user_params") = std::vector<uint64_t>{},
+           "Declares a registered parameter to be a bundle of tensors laid end to end (offsets in steps of 16).")
+      .def("post_backward_member", [](CpuEngine& e, int i, int member, uint64_t grad) {
+        py::gil_scoped_release rel;
+        e.post_backward_member(i, member, P<const float>(grad));
+      })
+      .def("attach_device_members", [](CpuEngine& e, int i, const std::vector<uint64_t>& dev) {
+        std::vector<void*> v;
+        for (uint64_t d : dev) v.push_back(P<void>(d));
+        e.attach_device_members(i, v);
+      })
+      .def("post_backward_device_members", [](CpuEngine& e, int i, const std::vector<uint64_t>& grads, uint64_t producer_stream,
+                                              uint64_t copy_stream) {
+        std::vector<const void*> v;
+        for (uint64_t g : grads) v.push_back(P<const void>(g));
+        e.post_backward_device_members(i, v, P<void>(producer_stream), P<void>(copy_stream));
+      }, py::arg("param_index"), py::arg("device_grads"), py::arg("producer_stream"), py::arg("copy_stream") = 0)
       .def("set_tx_rate_limit", [](CpuEngine& e, double bytes_per_s, size_t burst) {
         if (e.comm()) e.comm()->set_tx_rate_limit(bytes_per_s, burst);
       }, py::arg("bytes_per_s"), py::arg("burst_bytes") = 64 << 10,

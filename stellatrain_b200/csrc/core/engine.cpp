@@ -332,6 +332,23 @@ void CpuEngine::use_engine_device() {
 }
 
 void CpuEngine::post_backward_device(int index, const void* device_grad, void* producer_stream, void* copy_stream) {
+  ParamLocal& p = params_.at(index);
+  if (!p.members.empty()) throw std::runtime_error("post_backward_device: parameter is a bundle, hand in every member");
+  copy_device_grads(index, {{device_grad, 0u, p.numel}}, producer_stream, copy_stream);
+}
+
+void CpuEngine::post_backward_device_members(int index, const std::vector<const void*>& device_grads, void* producer_stream,
+                                             void* copy_stream) {
+  ParamLocal& p = params_.at(index);
+  if (device_grads.size() != p.members.size() || p.members.empty())
+    throw std::runtime_error("post_backward_device_members: one gradient per member");
+  std::vector<GradPart> parts;
+  parts.reserve(p.members.size());
+  for (size_t m = 0; m < p.members.size(); ++m) parts.push_back({device_grads[m], p.members[m].off, p.members[m].numel});
+  copy_device_grads(index, parts, producer_stream, copy_stream);
+}
+
+void CpuEngine::copy_device_grads(int index, const std::vector<GradPart>& parts, void* producer_stream, void* copy_stream) {
   const CudaApi* api = cuda_api();
   if (!api) throw std::runtime_error("post_backward_device: no CUDA runtime in this process");
   ParamLocal& p = params_.at(index);
@@ -351,7 +368,8 @@ void CpuEngine::post_backward_device(int index, const void* device_grad, void* p
   // in order, stopping at the first failure: a callback that was never enqueued must not be waited for
   int rc = api->event_record(p.grad_event, producer_stream);
   if (rc == 0) rc = api->stream_wait_event(copy_stream, p.grad_event);
-  if (rc == 0) rc = api->memcpy_d2h_async(slot, device_grad, static_cast<size_t>(p.numel) * sizeof(float), copy_stream);
+  for (size_t i = 0; i < parts.size() && rc == 0; ++i)
+    rc = api->memcpy_d2h_async(slot + parts[i].off, parts[i].src, static_cast<size_t>(parts[i].numel) * sizeof(float), copy_stream);
   if (rc == 0) {
     callbacks_in_flight_.fetch_add(1);
     grad_copies_pending_.fetch_add(1);
@@ -366,6 +384,50 @@ void CpuEngine::post_backward_device(int index, const void* device_grad, void* p
     --p.claim_cnt;      // the slot was not used
     throw std::runtime_error("a CUDA runtime call of the gradient copy failed with code " + std::to_string(rc));
   }
+}
+
+void CpuEngine::set_param_members(int index, const std::vector<std::string>& keys, const std::vector<uint32_t>& offsets,
+                                  const std::vector<uint32_t>& numels, const std::vector<float*>& user_params) {
+  ParamLocal& p = params_.at(index);
+  if (p.alloc_cnt != 0 || p.iteration_cnt != 0) throw std::runtime_error("set_param_members: the parameter is already in use");
+  if (keys.empty() || keys.size() != offsets.size() || keys.size() != numels.size() ||
+      (!user_params.empty() && user_params.size() != keys.size()))
+    throw std::runtime_error("set_param_members: lists of different lengths");
+  uint64_t end = 0;
+  std::vector<Member> members(keys.size());
+  for (size_t m = 0; m < keys.size(); ++m) {
+    if (offsets[m] % 16 != 0 || offsets[m] < end) throw std::runtime_error("set_param_members: offsets must ascend in steps of 16");
+    end = static_cast<uint64_t>(offsets[m]) + numels[m];
+    if (end > p.numel) throw std::runtime_error("set_param_members: members exceed the parameter");
+    members[m].key = keys[m];
+    members[m].off = offsets[m];
+    members[m].numel = numels[m];
+    members[m].user_param = user_params.empty() ? nullptr : user_params[m];
+    if (members[m].user_param)
+      std::memcpy(members[m].user_param, p.master + offsets[m], static_cast<size_t>(numels[m]) * sizeof(float));
+  }
+  p.members = std::move(members);
+}
+
+void CpuEngine::attach_device_members(int index, const std::vector<void*>& device_params) {
+  const CudaApi* api = cuda_api();
+  if (!api) throw std::runtime_error("attach_device_members: no CUDA runtime in this process");
+  if (device_ < 0 && api->get_device(&device_) != 0) throw std::runtime_error("cudaGetDevice failed");
+  ParamLocal& p = params_.at(index);
+  if (device_params.size() != p.members.size() || p.members.empty())
+    throw std::runtime_error("attach_device_members: one pointer per member");
+  for (size_t m = 0; m < p.members.size(); ++m) p.members[m].device_param = device_params[m];
+}
+
+void CpuEngine::post_backward_member(int index, int member, const float* grad) {
+  ParamLocal& p = params_.at(index);
+  const Member& m = p.members.at(static_cast<size_t>(member));
+  float* dst = grad_slot(index) + m.off;
+  if (p.micro == 0) std::memcpy(dst, grad, static_cast<size_t>(m.numel) * sizeof(float));
+  else add_arrays(dst, grad, m.numel);
+  if (++p.members_seen < static_cast<int>(p.members.size())) return;
+  p.members_seen = 0;
+  post_backward_in_slot(index);
 }
 
 void CpuEngine::schedule_after_cuda(Module* next, const std::shared_ptr<TrainTask>& t, void* stream) {
@@ -768,9 +830,13 @@ double CpuEngine::force_model_sync(int index, bool dry_run) {
       if (!dry_run) std::memcpy(p.master, ref.data(), static_cast<size_t>(p.numel) * sizeof(float));
     }
   }
-  if (!dry_run && p.user_param) {
+  bool host_members = false;
+  for (const Member& m : p.members) host_members = host_members || m.user_param != nullptr;
+  if (!dry_run && (p.user_param || host_members)) {
     if (!shm_->barrier(opt_.timeout_ms)) throw std::runtime_error("node barrier timed out in model sync");
-    std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
+    if (p.user_param) std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
+    for (const Member& m : p.members)
+      if (m.user_param) std::memcpy(m.user_param, p.master + m.off, static_cast<size_t>(m.numel) * sizeof(float));
   }
   return drift;
 }

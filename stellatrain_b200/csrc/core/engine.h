@@ -157,6 +157,23 @@ class CpuEngine {
   // slot and the pipeline starts from a host callback behind it.  The caller keeps `device_grad` alive until that
   // stream has passed the copy.  `copy_stream` may be null: the engine then uses a stream of its own.
   void post_backward_device(int param_index, const void* device_grad, void* producer_stream, void* copy_stream);
+  // ---- bundles: several small tensors registered as ONE parameter, so that they share one task per iteration
+  // A model like ResNet-152 has hundreds of tensors of a few hundred elements; each task costs the same handful of
+  // barriers, wake-ups and callbacks whatever its size.  A bundle is a parameter whose elements are the members laid
+  // end to end at `offsets` (multiples of 16, so that aligned blocks of a member stay aligned in the bundle; the
+  // gaps stay zero).  Selection keeps the per-tensor rule: every member is compressed by itself, with its own k and
+  // its own threshold under its own key, and the streams are joined.  Everything else (slots, gather, exchange,
+  // merge, optimiser state, master copy) treats the bundle as one flat parameter.
+  // `user_params[m]` (host tensors; may be null) is where the engine writes member m's updated values.
+  void set_param_members(int param_index, const std::vector<std::string>& keys, const std::vector<uint32_t>& offsets,
+                         const std::vector<uint32_t>& numels, const std::vector<float*>& user_params);
+  // Host gradient of one member; the bundle's micro-iteration counts once every member has reported.
+  void post_backward_member(int param_index, int member, const float* grad);
+  void attach_device_members(int param_index, const std::vector<void*>& device_params);
+  // Accumulated device gradients of all members (same order as the members): one event, one stream wait, one copy
+  // per member into the pinned slot, one host callback that starts the task.
+  void post_backward_device_members(int param_index, const std::vector<const void*>& device_grads, void* producer_stream,
+                                    void* copy_stream);
   double force_model_sync(int param_index, bool dry_run);
   int64_t model_version(int param_index) const;
   int num_params() const { return static_cast<int>(params_.size()); }
@@ -193,6 +210,12 @@ class CpuEngine {
   CommManager* comm() { return comm_.get(); }
   ThreadPool& pool() { return *pool_; }
   Compressor& compressor() { return *compressor_; }
+  struct Member {
+    std::string key;                         // "{layer}@{name}" of the tensor: names its threshold state
+    uint32_t off = 0, numel = 0;
+    float* user_param = nullptr;
+    void* device_param = nullptr;
+  };
   struct ParamLocal {
     int layer = 0;
     std::string name;
@@ -213,6 +236,8 @@ class CpuEngine {
     void* grad_event = nullptr;              // orders the device-to-host copy after the backward kernels
     void* last_copy_stream = nullptr;        // stream of the latest device-to-host copy of this parameter
     bool checked_barrier = false;
+    std::vector<Member> members;             // empty: a plain parameter
+    int members_seen = 0;                    // members that reported their gradient in this micro-iteration
     std::vector<float> merge_scratch;        // node master: dense accumulator of the merge
     std::vector<uint8_t> merge_touched;
   };
@@ -221,6 +246,8 @@ class CpuEngine {
   void push_ready_update(int param_index, int64_t iter);
 
  private:
+  struct GradPart { const void* src; uint32_t off, numel; };
+  void copy_device_grads(int param_index, const std::vector<GradPart>& parts, void* producer_stream, void* copy_stream);
   void load_modules();
   void barrier_manager_main();
   void start_task(int param_index);

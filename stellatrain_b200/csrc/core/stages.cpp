@@ -125,15 +125,24 @@ class ModuleCompress : public Module {
     auto& p = e.param(t->param_index);
     const int W = e.options().world;
     float* acc = p.resid;                                        // gradient sum plus residual, NaN dropped, left by the gather stage
-    const uint32_t k = entries_for(p.numel, t->ratio, W);
+    // a bundle keeps the per-tensor rule: every member has its own k and its own threshold
+    uint32_t k = 0;
+    if (p.members.empty()) k = entries_for(p.numel, t->ratio, W);
+    else for (const auto& m : p.members) k += entries_for(m.numel, t->ratio, W);
     t->k = k;
     t->idx.assign(static_cast<size_t>(k) * W, 0xFFFFFFFFu);
     t->val.assign(static_cast<size_t>(k) * W, 0.f);
     t->counts.assign(W, 0);
     t->stat_start("CRIT_PATH_compress");
-    const size_t cnt = e.options().skip_critical_paths
-                           ? 0
-                           : e.compressor().compress(t->persistent_key, acc, p.numel, k, t->idx.data(), t->val.data(), 0);
+    size_t cnt = 0;
+    if (e.options().skip_critical_paths) {
+    } else if (p.members.empty()) {
+      cnt = e.compressor().compress(t->persistent_key, acc, p.numel, k, t->idx.data(), t->val.data(), 0);
+    } else {
+      for (const auto& m : p.members)
+        cnt += e.compressor().compress(m.key, acc + m.off, m.numel, entries_for(m.numel, t->ratio, W), t->idx.data() + cnt,
+                                       t->val.data() + cnt, static_cast<int32_t>(m.off));
+    }
     t->stat_end("CRIT_PATH_compress");
     t->counts[0] = cnt;
     if (e.options().debug_accuracy)
@@ -237,24 +246,37 @@ class ModuleCopyOut : public Module {
     auto& p = e.param(t->param_index);
     // the slot is consumed: clear this process's part for the next use
     std::memset(p.slot[t->iter % 2][e.options().local_rank], 0, static_cast<size_t>(p.numel) * sizeof(float));
-    if (p.device_param != nullptr) {
+    const bool device_members = !p.members.empty() && p.members[0].device_param != nullptr;
+    if (p.device_param != nullptr || device_members) {
       // host-to-device copy on the stream that carried this parameter's latest gradient copy: that copy waited for the
       // backward kernels that last read the parameter, so stream order keeps the write behind every reader
       const CudaApi* api = cuda_api();
       e.use_engine_device();
       void* stream = p.last_copy_stream ? p.last_copy_stream : e.copy_stream_for(t->param_index);
-      if (!api || api->memcpy_h2d_async(p.device_param, p.master, static_cast<size_t>(p.numel) * sizeof(float), stream) != 0) {
+      int rc = api ? 0 : -1;
+      if (rc == 0 && !device_members)
+        rc = api->memcpy_h2d_async(p.device_param, p.master, static_cast<size_t>(p.numel) * sizeof(float), stream);
+      for (size_t m = 0; rc == 0 && device_members && m < p.members.size(); ++m)
+        rc = api->memcpy_h2d_async(p.members[m].device_param, p.master + p.members[m].off,
+                                   static_cast<size_t>(p.members[m].numel) * sizeof(float), stream);
+      if (rc != 0) {
         e.fail_task(t, "host-to-device copy of the parameter failed");
         return;
       }
       e.schedule_after_cuda(e.module("CopyOutPost"), t, stream);
       return;
     }
-    if (p.user_param == nullptr) {
+    bool host_members = false;
+    for (const auto& m : p.members) {
+      if (!m.user_param) continue;
+      host_members = true;
+      std::memcpy(m.user_param, p.master + m.off, static_cast<size_t>(m.numel) * sizeof(float));
+    }
+    if (p.user_param == nullptr && !host_members) {
       e.push_ready_update(t->param_index, t->iter);   // the caller copies and reports copy_out_done()
       return;
     }
-    std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
+    if (p.user_param) std::memcpy(p.user_param, p.master, static_cast<size_t>(p.numel) * sizeof(float));
     e.schedule_after_barrier(e.module("CopyOutDone"), t, kAfterCopyOut);
   }
 };

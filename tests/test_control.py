@@ -95,6 +95,40 @@ def test_compression_follows_bandwidth():
     assert tight > loose and tight > 0.9
 
 
+def test_shipped_b200_profile_changes_the_choice_where_the_sweep_says_so():
+    """The profile fitted from the convergence sweep ships for B200 and is what the controller takes when none is named.
+    At half the bandwidth of its operating point the sweep needs fewer samples at a total batch of 128 to 256 than at 64
+    (longer iterations carry a larger share of the gradient), so on GPUs whose throughput is already flat at 8 samples
+    the objective prefers the larger batch; the analytic surrogate, monotone in the batch, stays at the knee."""
+    from stellatrain_b200.control.gp_profile import AnalyticProfile, load_profile, shipped_profile_path
+
+    assert shipped_profile_path("NVIDIA GeForce RTX 2080 Ti") is None
+    assert isinstance(load_profile(None, "NVIDIA GeForce RTX 2080 Ti"), AnalyticProfile)
+    shipped = load_profile(None, "NVIDIA B200")
+    assert isinstance(shipped, GPProfile) and shipped.meta.bandwidth == 1.0 and 0.9 < shipped.meta.compression < 0.99
+    # the fit follows the sweep it was made from (its rows are inside the file); it smooths the sweep's noise
+    import json
+
+    rows = json.loads(shipped_profile_path("NVIDIA B200").read_text())["sweep"]
+    fitted = [float(shipped.h(tb, gbps / rows["ref_bandwidth_gbps"])[0]) for tb, gbps, _, _, _ in rows["rows"]]
+    measured = [h for _, _, _, _, h in rows["rows"]]
+    assert float(np.corrcoef(fitted, measured)[0, 1]) > 0.93
+    assert max(abs(a - b) for a, b in zip(fitted, measured)) < 0.08
+    # less bandwidth never needs fewer samples at a fixed batch, within the noise of the sweep
+    assert float(shipped.h(64, 0.25)[0]) > float(shipped.h(64, 2.0)[0]) > float(shipped.h(64, 8.0)[0])
+
+    traffic = TrafficModel([1_000_000] * 100, "nvlink")
+
+    def best_total(profile):
+        opt = BatchRateOptimizer(8, 2, traffic, profile)
+        opt.alphas[:], opt.betas[:] = 8.0, 400.0                     # flat beyond 8 samples per GPU
+        half_width_mbps, conv = 500.0, 1.0                           # objective asks h(total, 0.5)
+        return min((64, 128, 256, 512), key=lambda t: opt.objective(np.full(8, t / 8.0), half_width_mbps, conv))
+
+    assert best_total(AnalyticProfile()) == 64
+    assert best_total(shipped) in (128, 256)
+
+
 def test_controller_roundtrip_with_native_client():
     from stellatrain_b200 import cpu_tier
 
@@ -119,6 +153,8 @@ def test_controller_roundtrip_with_native_client():
         assert all(ub >= 1 and 0.0 <= cr <= 0.999 for _, _, ub, cr in got)
         assert clients[0].sent() > 0 and clients[0].alive()
         assert set(ctl.scoreboard.index) == {0, 1} and ctl.scoreboard.at[0, "gpu"] == "NVIDIA B200"
+        # no profile was named: the one fitted for this kind of GPU is in use, in the optimiser too
+        assert isinstance(ctl.profile, GPProfile) and ctl.optimizer.profile is ctl.profile
         assert server.terminate()
         del clients, server
     finally:

@@ -456,8 +456,11 @@ def test_lost_peer_surfaces_as_error(mode):
     assert any(w in by_node[0][1] for w in ("timed out", "failed", "closed")), by_node[0][1]
 
 
-def _run_single_process_engine(device_copies, staleness, delay_ms=0, steps=6):
+def _run_single_process_engine(device_copies, staleness, delay_ms=0, steps=6, bundle=False):
     from _cpu_workers import SIZES, synthetic_grad
+
+    if bundle:
+        return _run_bundled_engine(device_copies, staleness, delay_ms, steps)
 
     session = (os.getpid() % 10000) * 1000 + np.random.randint(0, 900)
     if device_copies:
@@ -495,6 +498,99 @@ def _run_single_process_engine(device_copies, staleness, delay_ms=0, steps=6):
         if device_copies:
             ext.remove_fake_cuda()
         ext.ShmManager.unlink_session(session)
+
+
+def _run_bundled_engine(device_copies, staleness, delay_ms, steps):
+    """The same three tensors registered as ONE parameter with three members (offsets in steps of 16)."""
+    from _cpu_workers import SIZES, synthetic_grad
+
+    session = (os.getpid() % 10000) * 1000 + np.random.randint(0, 900)
+    if device_copies:
+        ext.install_fake_cuda(delay_ms)
+    try:
+        eng = ext.CpuEngine()
+        eng.configure("127.0.0.1", free_port(), 1, 0, session, 1, 0, "thresholdv16", 1, staleness, 0.9, 32 << 20, 20000, 4,
+                      False, True, False)
+        eng.set_optimizer("adam")
+        eng.configure_optimizer("lr", 1e-2)
+        params = [torch.full((n,), 0.5) for n in SIZES]
+        offsets, total = [], 0
+        for n in SIZES:
+            offsets.append(total)
+            total += (n + 15) // 16 * 16
+        init = torch.zeros(total)
+        for p, off in zip(params, offsets):
+            init[off:off + p.numel()] = p
+        idx = eng.pre_train_init(0, "bundle", total, 0, init.data_ptr())
+        eng.set_param_members(idx, [f"{pi}@p{pi}" for pi in range(len(SIZES))], offsets, list(SIZES),
+                              [] if device_copies else [p.data_ptr() for p in params])
+        with pytest.raises(RuntimeError, match="steps of 16"):
+            eng.set_param_members(idx, ["a", "b"], [0, 8], [4, 4], [])
+        keep = []
+        if device_copies:
+            eng.attach_device_members(idx, [p.data_ptr() for p in params])
+        for step in range(steps):
+            eng.pre_forward_process(idx)
+            grads = [synthetic_grad(0, 0, step, pi, SIZES[pi]) for pi in range(len(SIZES))]
+            keep.append(grads)
+            if device_copies:
+                eng.post_backward_device_members(idx, [g.data_ptr() for g in grads], 0)
+            else:
+                for pi in reversed(range(len(SIZES))):
+                    eng.post_backward_member(idx, pi, grads[pi].data_ptr())
+        eng.synchronize()
+        versions = [eng.model_version(idx)] * len(SIZES)
+        counters = ext.fake_cuda_counters() if device_copies else None
+        assert eng.num_params() == 1
+        del eng
+        return [p.clone() for p in params], versions, counters
+    finally:
+        if device_copies:
+            ext.remove_fake_cuda()
+        ext.ShmManager.unlink_session(session)
+
+
+@pytest.mark.parametrize("device_copies", [False, True])
+def test_a_bundle_of_tensors_is_one_task_with_per_tensor_selection(device_copies):
+    """Three tensors as one bundle: one task per iteration (one callback behind the gradient copies, one behind the
+    parameter copies), and the same parameters bit for bit as three tasks give, because every member is still selected
+    by itself under its own threshold."""
+    steps = 6
+    want, _, _ = _run_single_process_engine(False, 1, steps=steps)
+    got, versions, counters = _run_single_process_engine(device_copies, 1, 2 if device_copies else 0, steps=steps, bundle=True)
+    assert versions == [steps] * 3
+    if device_copies:
+        d2h, h2d, funcs = counters
+        assert d2h == 3 * steps and h2d == 3 * steps and funcs == 2 * steps
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("bundle_elems,units", [(0, 4), (1 << 16, 1), (512, 3)])
+def test_offload_engine_bundles_small_tensors(bundle_elems, units):
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    def run(be):
+        torch.manual_seed(5)
+        model = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 8))
+        eng = cpu_tier.CpuOffloadEngine(model, method="thresholdv16", ratio=0.9, optimizer="adam", optimizer_options={"lr": 1e-2},
+                                        staleness=1, data_bytes=8 << 20, workers=2, bundle_elems=be)
+        for i in range(6):
+            g = torch.Generator().manual_seed(70 + i)
+            x, y = torch.randn(16, 32, generator=g), torch.randint(0, 8, (16,), generator=g)
+            F.cross_entropy(model(x), y).backward()
+        eng.synchronize()
+        out = [p.detach().clone() for p in model.parameters()], eng.engine.num_params(), sorted(eng.state_dict()["sparsifier"]["threshold"])
+        eng.close()
+        return out
+
+    want, n_plain, keys_plain = run(0)
+    got, n_units, keys = run(bundle_elems)
+    assert n_plain == 4 and n_units == units
+    assert keys == keys_plain                       # thresholds stay per tensor, under the tensor's own key
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("staleness,delay_ms", [(0, 0), (1, 0), (1, 3)])
