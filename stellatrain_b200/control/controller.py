@@ -15,6 +15,7 @@ import argparse
 import os
 import queue
 import socket
+import sys
 import threading
 import time
 from dataclasses import dataclass, field
@@ -32,6 +33,7 @@ LOG_PATH = "/tmp/stellatrain-b200-controller.log"
 # backend/src/engine/batch_rate_alloc_optim.py:474-477)
 INSTRUCTION_LOG_PATH = "/tmp/stellatrain-b200-instructions.log"
 SMOOTH = 0.9     # scoreboard EWMA
+VERBOSE = os.environ.get("STELLATRAIN_CONTROLLER_VERBOSE", "0") not in ("", "0")   # registrations and replies on stderr
 
 
 @dataclass
@@ -113,12 +115,18 @@ class Controller:
                 if mtype == M.LOCAL_INIT:
                     li = M.parse(mtype, payload)
                     client = Client(li.gpu_id, li.rank, li.local_rank, li.gpu_name)
+                    if VERBOSE:
+                        print(f"[controller] {time.time():.3f} registration of gpu {li.gpu_id} ({li.gpu_name}) arrived",
+                              file=sys.stderr, flush=True)
                     with self.lock:
                         self.clients[li.gpu_id] = client
                         self.scoreboard.loc[li.gpu_id, ["location", "gpu"]] = [f"{li.rank}:{li.local_rank}", li.gpu_name]
                         if self.optimizer is not None and li.gpu_id < self.optimizer.num_gpus:
                             self.optimizer.set_max_batch(li.gpu_id, self.max_batch or max_batch_for(li.gpu_name))
                         self._choose_profile()
+                    if VERBOSE:
+                        print(f"[controller] {time.time():.3f} registration of gpu {li.gpu_id} answered, profile "
+                              f"{type(self.profile).__name__}", file=sys.stderr, flush=True)
                 elif mtype == M.LOCAL:
                     t = M.parse(mtype, payload)
                     self.rx.put(t)

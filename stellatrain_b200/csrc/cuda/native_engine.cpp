@@ -144,6 +144,11 @@ struct NativeEngine::Impl {
     c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
     const c10::cuda::CUDAStream cur_s = c10::cuda::getCurrentCUDAStream((c10::DeviceIndex)device);
     cudaStream_t cur = cur_s.stream();
+    // Gradients of this bucket that autograd handed over: they are released at the end of this function, once the
+    // select that reads them is in the sparse stream.  The allocator defers the reuse of a block that was recorded
+    // on a stream only past the work that stream had been given when the block was freed, so a release in front of
+    // the launch would leave the select reading memory that the next allocation may already have taken.
+    std::vector<at::Tensor> release;
     if (b.spec.steal) {
       const size_t n = b.spec.seg_off.size();
       check(cudaMemcpyAsync(b.spec.table_dev, row_of(b), n * sizeof(uint64_t), cudaMemcpyHostToDevice, cur));
@@ -156,7 +161,7 @@ struct NativeEngine::Impl {
         const c10::cuda::CUDAStream sparse_s = c10::cuda::getStreamFromExternal(sparse, (c10::DeviceIndex)device);
         for (auto& g : b.held)   // the allocator must not reuse them before the select has read them
           c10::cuda::CUDACachingAllocator::recordStream(g.storage().data_ptr(), sparse_s);
-        b.held.clear();
+        release.swap(b.held);
       } else {
         for (auto& g : b.held) capture_keep.push_back(std::move(g));   // a replay reads these addresses again
         b.held.clear();
@@ -169,6 +174,7 @@ struct NativeEngine::Impl {
     select(b);
     if (staleness == 0) apply(b);
     else b.has_pending_apply = true;
+    release.clear();   // after the launches, see above
   }
 };
 

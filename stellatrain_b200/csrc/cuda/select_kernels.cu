@@ -921,12 +921,19 @@ __device__ __forceinline__ bool acks_arrived(const SelectArgs& A, uint32_t epoch
 }
 
 template <bool B16>
-__global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
+__global__ void __launch_bounds__(kThreads, 8) k_fused(SelectArgs A) {
   constexpr int kWarps = kThreads / 32;
   __shared__ uint32_t s_cnt[kFusedMaxIter * kWarps];        // items over the threshold per (iteration, warp)
   __shared__ uint32_t s_tmp[kWarps + 1];
   __shared__ uint2 s_cnd[B16 ? kFusedMaxChunk / 16 : 1];    // near-miss blocks of this chunk: (block id, key)
-  __shared__ uint32_t s_word[4];   // [0] candidates staged, [1] items in front of the chunk, [2] candidate base, [3] may emit
+  __shared__ uint32_t s_word[6];   // [0] candidates staged, [1] items in front of the chunk, [2] candidate base, [3] may emit,
+                                   // [4] selected blocks staged, [5] unused
+  // Selected blocks wait here, values and all, until their stream positions are known: the emission then needs no
+  // second walk over the chunk and no second read of r.  A chunk holds kStage blocks over the threshold only when the
+  // threshold is far too low; it then falls back to walking the chunk again.
+  constexpr uint32_t kStage = B16 ? 48u : 1u;
+  __shared__ float4 s_sval[kStage * 4];     // the block's 16 values, one float4 per lane of the block
+  __shared__ uint2 s_smeta[kStage];         // (offset of the block in the chunk, cell << 8 | blocks of lower lanes in the cell)
 
   // The chunk's place is all the first loads need: they are on their way while the tensor's descriptor, threshold
   // and gradient pointer (a second level of dependent loads) are fetched.
@@ -951,7 +958,7 @@ __global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
     }
     return;
   }
-  if (threadIdx.x == 0) s_word[0] = 0;
+  if (threadIdx.x == 0) { s_word[0] = 0; s_word[4] = 0; }
 
   const uint32_t seg_rel = ch.start - sd.off;
   const bool tab = A.grad_tab != nullptr;
@@ -1002,6 +1009,16 @@ __global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
       const uint32_t leaders = __ballot_sync(0xffffffffu, sel) & 0x11111111u;
       if (lane == 0) s_cnt[it * kWarps + warp] = __popc(leaders);
       selbits |= (uint32_t)sel << it;
+      if (leaders) {
+        uint32_t slot = 0;
+        if (sel && (lane & 3u) == 0u) slot = atomicAdd(&s_word[4], 1u);
+        slot = __shfl_sync(0xffffffffu, slot, lane & ~3u);
+        if (sel && slot < kStage) {
+          s_sval[slot * 4u + (lane & 3u)] = a;
+          if ((lane & 3u) == 0u)
+            s_smeta[slot] = make_uint2(i, ((it * kWarps + warp) << 8) | __popc(leaders & ((1u << lane) - 1u)));
+        }
+      }
       if (collect && act && !sel && (lane & 3u) == 0u && key >= lo_bits && key != 0u) {
         const uint32_t slot = atomicAdd(&s_word[0], 1u);
         s_cnd[slot] = make_uint2((ch.start + i) >> 4, key);
@@ -1060,6 +1077,29 @@ __global__ void __launch_bounds__(kThreads) k_fused(SelectArgs A) {
   const uint64_t slot_off = (uint64_t)(epoch & 1u) * A.slot_stride + sd.out_off;
   const int dest = dest_of(A, sd);
   const uint32_t nb = narrow_base_of(sd);
+  if (B16 && s_word[4] <= kStage) {
+    // one thread per lane of a staged block
+    const uint32_t n_staged = s_word[4];
+    for (uint32_t j = threadIdx.x; j < n_staged * 4u; j += kThreads) {
+      const uint32_t b = j >> 2, q = j & 3u;
+      const uint2 meta = s_smeta[b];
+      const uint32_t pos = base + s_cnt[meta.y >> 8] + (meta.y & 0xFFu);
+      if (pos >= kk) continue;   // beyond the budget: the block stays in the residual
+      const float4 a = s_sval[j];
+      float v[4] = {a.x, a.y, a.z, a.w};
+      const uint32_t p0 = pos * 16u + q * 4u, i = meta.x + q * 4u;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (p0 + e < sd.k) {   // a truncated last block leaves the residual exact: only emitted elements are cleared
+          const float sv = wire_value(nb, v[e]);
+          emit_entry(A, dest, nb, slot_off, p0 + e, ch.start + i + e, sv);
+          v[e] -= sv;
+        }
+      }
+      *reinterpret_cast<float4*>(r + i) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    return;
+  }
   for (uint32_t it = 0; it < n_iter; ++it) {
     const uint32_t i = it * kPerIter + threadIdx.x * 4;
     if (B16) {
@@ -1241,12 +1281,15 @@ __global__ void __launch_bounds__(kCandThreads) k_finish(SelectArgs A) {
         if (short_of) ss.tau *= 0.99f;      // "must drop less" (thresholdv16.cpp:245-248)
         else ss.tau += ss.tau_inc;          // thresholdv16.cpp:249-252
         {
-          // keep about as many near-miss blocks as the budget: few enough to be cheap, enough to fill from
+          // Keep a sixteenth to a quarter of the budget in near-miss blocks, and at least twice what this fill took:
+          // the additive and multiplicative steps of the threshold move the count of blocks over it by a few per
+          // cent, which is all a fill ever needs, and ranking the candidates costs time in proportion to their number.
           float w = __uint_as_float(ss.reserved[0]);
           if (!(w > 0.f && w <= 1.f)) w = kWindowDefault;
+          const uint32_t needed = short_of ? kk - found : 0u;
           if (scanned) w *= 2.f;
-          else if (c_win > 2u * kk) w *= 0.75f;
-          else if (c_win < kk / 2u + 1u) w *= 1.5f;
+          else if (c_win < kk / 16u + 8u || c_win < 2u * needed) w *= 1.5f;
+          else if (c_win > kk / 4u + 32u) w *= 0.75f;
           ss.reserved[0] = __float_as_uint(fminf(fmaxf(w, 1e-3f), 1.f));
         }
       }

@@ -276,7 +276,10 @@ class SparseDPModelWrapper(nn.Module):
             self._side_stream = torch.cuda.Stream(device=eng.device)
         cur = torch.cuda.current_stream(eng.device)
         done = self._eager_by_key.get(key, 0)
-        if done < (1 if self._ever_captured else self.graph_warmup):
+        # a drained pipeline (after synchronize(), a checkpoint, a ratio change) is not the state a replay continues
+        # from: with staleness 1 every bucket must have an update outstanding, which one more eager iteration restores
+        steady = eng.cfg.staleness == 0 or all(rt.has_pending_apply for rt in eng.buckets)
+        if done < (1 if self._ever_captured else self.graph_warmup) or not steady:
             self._side_stream.wait_stream(cur)
             with torch.cuda.stream(self._side_stream):
                 loss = self._iteration(*inputs)

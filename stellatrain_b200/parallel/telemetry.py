@@ -63,7 +63,17 @@ class TelemetryHook:
             ext = cpu_tier._load()
             name = gpu_name or (torch.cuda.get_device_name(engine.device) if engine.device.type == "cuda" else "cpu")
             self._TrainConfig = ext.TrainConfig
-            self.client = ext.TelemetryClient(uri, engine.rank, name, 0, engine.rank, 5000)
+            # the controller may be busy when a job starts (it fits and optimises under the interpreter lock of its
+            # own process): a registration that is not answered in time is tried again before giving up
+            last = None
+            for _ in range(3):
+                try:
+                    self.client = ext.TelemetryClient(uri, engine.rank, name, 0, engine.rank, 10000)
+                    break
+                except RuntimeError as e:
+                    last = e
+            if self.client is None:
+                raise last
 
     # ------------------------------------------------------------------ instructions
     def _on_instruction(self, since: int, ubatch: int, grad_acc: int, ratio: float) -> None:

@@ -415,7 +415,7 @@ def test_cpu_offload_tier_with_a_cuda_model(native_copies):
     eng.close()
 
 
-def _wrapper_run(graph, data, ratio_change_at=None, eager_detour_at=None):
+def _wrapper_run(graph, data, ratio_change_at=None, eager_detour_at=None, drain_and_new_shape_at=None):
     """Train small_net through the wrapper's whole-iteration call; returns the final parameters."""
     import stellatrain_b200 as st
 
@@ -436,6 +436,10 @@ def _wrapper_run(graph, data, ratio_change_at=None, eager_detour_at=None):
         if eager_detour_at is not None and i == eager_detour_at:
             F.cross_entropy(net(x), y).backward()          # the reference's way of running an iteration, in between replays
             continue
+        if drain_and_new_shape_at is not None and i >= drain_and_new_shape_at:
+            if i == drain_and_new_shape_at + 1:
+                st.synchronize()                           # drained pipeline right in front of the capture of a new shape
+            x, y = x[: x.shape[0] // 2], y[: y.shape[0] // 2]
         losses.append(float(net.train_step(x, y)))
     st.synchronize()
     net.engine.check_status()
@@ -447,13 +451,64 @@ def _wrapper_run(graph, data, ratio_change_at=None, eager_detour_at=None):
     return out
 
 
-@pytest.mark.parametrize("scenario", ["plain", "ratio_change", "eager_detour"])
+class _LinearInGrad(nn.Module):
+    """loss = sum_t <p_t, c_t>: the gradient of every tensor is the coefficient tensor handed to forward."""
+
+    def __init__(self, sizes):
+        super().__init__()
+        g = torch.Generator().manual_seed(7)
+        self.ps = nn.ParameterList([nn.Parameter(torch.randn(n, generator=g)) for n in sizes])
+
+    def forward(self, coeffs):
+        return sum((p * c).sum() for p, c in zip(self.ps, coeffs))
+
+
+@pytest.mark.parametrize("native", [True, False])
+def test_stolen_gradients_outlive_the_select_that_reads_them(native):
+    """In pointer-table mode the select reads autograd's own gradient tensors.  They have to stay allocated until
+    that kernel has run, also when it runs late: here the backward pass sits behind a long kernel, the host is far
+    ahead, and everything the allocator considers free is taken and overwritten at once.  Exact accounting (what was
+    fed equals what moved the parameters plus what is left in the residual) fails on the first gradient that was
+    given away too early."""
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+
+    sizes = (5000, 70000, 300, 17, 4096)
+    model = _LinearInGrad(sizes).cuda()
+    p0 = [p.detach().clone() for p in model.ps]
+    eng = SparseDPEngine(model, EngineConfig(compressor="topk", ratio=0.9, optimizer="sgd", staleness=1, bucket_mb=0.5,
+                                             chunk_elems=1024, optimizer_options={"lr": 1.0}, native_hooks=native))
+    g = torch.Generator(device="cuda").manual_seed(500)
+    fed = [torch.zeros_like(p, dtype=torch.float64) for p in p0]
+    junk = []
+    for step in range(8):
+        coeffs = [torch.randn(p.numel(), device="cuda", generator=g) * (0.5 ** (step % 3)) for p in p0]
+        for f, c in zip(fed, coeffs):
+            f += c.double()
+        torch.cuda._sleep(30_000_000)           # about 15 ms of head start for the host
+        model(coeffs).backward()
+        junk = [torch.full((n,), 1e30, device="cuda") for n in sizes for _ in range(4)]
+    eng.synchronize()
+    eng.check_status()
+    by_name = {n: p for n, p in model.named_parameters()}
+    for rt, names in zip(eng.buckets, eng.param_names):
+        for seg, name in zip(rt.bucket.layout.segments, names):
+            i = int(name.split(".")[-1])
+            resid = rt.bucket.resid[seg.off: seg.off + seg.numel].double()
+            moved = p0[i].double() - by_name[name].detach().double()
+            assert float((fed[i] - resid - moved).abs().max()) < 1e-4, (name, step)
+    del junk
+    eng.close()
+
+
+@pytest.mark.parametrize("scenario", ["plain", "ratio_change", "eager_detour", "drain_and_new_shape"])
 def test_wrapper_train_step_graph_equals_eager(scenario):
     """The captured iteration is the product path of the wrapper: same parameters as eager launches, also across a
     change of the compression ratio (the capture goes stale, one eager iteration, a new capture) and across an
-    iteration run the reference's way between replays (gradient addresses of eager steps never reach a replay)."""
+    iteration run the reference's way between replays (gradient addresses of eager steps never reach a replay), and
+    when a new batch shape meets a pipeline that was just drained (one more eager iteration, then the capture)."""
     data = batches(12)
-    kw = {"ratio_change": dict(ratio_change_at=7), "eager_detour": dict(eager_detour_at=8)}.get(scenario, {})
+    kw = {"ratio_change": dict(ratio_change_at=7), "eager_detour": dict(eager_detour_at=8),
+          "drain_and_new_shape": dict(drain_and_new_shape_at=6)}.get(scenario, {})
     p_eager, l_eager, captured_e, _ = _wrapper_run(False, data, **kw)
     p_graph, l_graph, captured_g, replays = _wrapper_run(True, data, **kw)
     assert not captured_e and captured_g and replays >= 5
