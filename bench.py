@@ -556,7 +556,13 @@ def main() -> None:
                                       [p.numel() for p in model.parameters()], False, False)
         if world > 1:
             dist.barrier()
-        hook = TelemetryHook(engine, f"127.0.0.1:{ctl_port}", args.batch, apply_batch=bool(args.adapt_batch))
+        hook = TelemetryHook(engine, f"127.0.0.1:{ctl_port}", args.batch, apply_batch=bool(args.adapt_batch),
+                             ratio_min_interval=(48 if args.graph else 0))
+        if world > 1:
+            # Nobody trains before everybody is registered.  The controller lives in rank 0's interpreter here: once
+            # rank 0's first step has kernels waiting for a peer's stream, a call of its main thread that waits for
+            # the device while it holds the interpreter lock keeps the controller from answering that very peer.
+            dist.barrier()
 
     sparse_arm = engine is not None      # this package's engine: the wrapper owns the iteration (eager or captured)
 

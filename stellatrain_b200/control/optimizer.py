@@ -153,6 +153,12 @@ class BatchRateOptimizer:
         self.alphas = np.full(num_gpus, max(10.0, alpha_min))
         self.betas = np.full(num_gpus, max(200.0, beta_min))
         self.max_batch = np.full(num_gpus, np.inf)
+        # Smallest batch size every GPU has been measured at.  The allocation never goes below it: two parameters are
+        # fitted to the samples, and when all samples lie on the flat part of the curve (a fast GPU whose run started
+        # at a batch beyond its knee) the knee is not determined by them, so a batch below the sampled range would
+        # rest on the initial guess alone.  The reference ramps up from a batch of 4 and always has the low end
+        # (backend/src/engine/batch_rate_alloc_optim.py:203-215); a job that starts at its working batch does not.
+        self.min_sampled = np.full(num_gpus, np.inf)
         self.samples = [SmoothedSamples() for _ in range(num_gpus)]
         self.seen = [0] * num_gpus
         self.initialized = [False] * num_gpus
@@ -175,6 +181,7 @@ class BatchRateOptimizer:
         reference keeps only in memory, backend/src/engine/batch_rate_alloc_optim.py:117-162)."""
         return {
             "alphas": self.alphas.copy(), "betas": self.betas.copy(), "max_batch": self.max_batch.copy(),
+            "min_sampled": self.min_sampled.copy(),
             "samples": [{"values": dict(s.values), "count": s.count, "momentum": s.momentum} for s in self.samples],
             "seen": list(self.seen), "initialized": list(self.initialized), "init_batch": self.init_batch.copy(),
             "init_ratio": self.init_ratio, "phase": int(self.phase.value), "bw_estimate": self.bw_estimate,
@@ -188,6 +195,7 @@ class BatchRateOptimizer:
             raise ValueError(f"controller state is for {len(sd['alphas'])} GPUs, this job has {self.num_gpus}")
         self.alphas, self.betas = np.array(sd["alphas"], float), np.array(sd["betas"], float)
         self.max_batch = np.array(sd["max_batch"], float)
+        self.min_sampled = np.array(sd.get("min_sampled", np.full(self.num_gpus, np.inf)), float)
         self.samples = []
         for row in sd["samples"]:
             s = SmoothedSamples(row["momentum"])
@@ -212,6 +220,7 @@ class BatchRateOptimizer:
             g = row["gpu"]
             if self.seen[g] >= GPU_INIT_WARMUP_THRESH and row["bwd_ms"] > 0:
                 self.samples[g].add(int(row["batch_size"]), row["batch_size"] * 1000.0 / row["bwd_ms"])
+                self.min_sampled[g] = min(self.min_sampled[g], float(row["batch_size"]))
             self.seen[g] += 1
             self.last_rows[g] = row
             if self.phase == Phase.INIT_WARMUP:
@@ -304,12 +313,13 @@ class BatchRateOptimizer:
     def _step_running(self, measured_mbps: float) -> Optional[InstructionSet]:
         bw = self._update_bandwidth(measured_mbps)
         conv = self._conversion_factor()
-        bounds = [(1.0, float(m)) for m in self.max_batch]
+        low = [float(min(l, m)) if np.isfinite(l) else 1.0 for l, m in zip(self.min_sampled, self.max_batch)]
+        bounds = [(lo, float(m)) for lo, m in zip(low, self.max_batch)]
         if self.main_iter % self.reoptimize_every == 0 or self.prev_x is None:
             starts = []
             if self.prev_x is None:
                 for _ in range(32):
-                    starts.append(np.array([self.rng.randint(1, int(m)) for m in self.max_batch], float))
+                    starts.append(np.array([self.rng.randint(int(lo), int(m)) for lo, m in zip(low, self.max_batch)], float))
             else:
                 for scale in (1.0, 2.0):
                     starts.append(np.clip(self.prev_x * scale, 1.0, self.max_batch))
@@ -319,7 +329,7 @@ class BatchRateOptimizer:
                              options={"adaptive": True, "maxiter": 400 * self.num_gpus, "xatol": 0.5, "fatol": 1e-9})
                 if best is None or r.fun < best.fun:
                     best = r
-            self.prev_x, self.prev_fun = np.maximum(np.round(best.x), 1.0), float(best.fun)
+            self.prev_x, self.prev_fun = np.clip(np.round(best.x), low, self.max_batch), float(best.fun)
         self.main_iter += 1
         ratio = self._min_ratio_for(self.prev_x, bw)
         return InstructionSet(0, self.prev_x.copy(), ratio)

@@ -34,7 +34,7 @@ import torch.distributed as dist
 class TelemetryHook:
     def __init__(self, engine, uri: Optional[str], batch_size: int, gpu_name: Optional[str] = None,
                  apply_batch: bool = True, apply_ratio: bool = True, link_bytes_per_entry: int = 8,
-                 ratio_tolerance: float = 0.15) -> None:
+                 ratio_tolerance: float = 0.15, ratio_min_interval: int = 0) -> None:
         self.engine = engine
         self.batch_size = int(batch_size)
         self.apply_batch, self.apply_ratio = apply_batch, apply_ratio
@@ -43,6 +43,11 @@ class TelemetryHook:
         # less than this (relative) is not worth applying; the controller re-issues its current view every few
         # iterations anyway (backend/src/engine/batch_rate_alloc_optim.py:454-472).
         self.ratio_tolerance = float(ratio_tolerance)
+        # Iterations that must lie between two applied ratio changes.  With captured iterations every change costs an
+        # eager iteration and a new capture (about as much as fifty replays of a 20 ms step), so a controller that
+        # walks the ratio a little every few iterations is followed in larger steps.
+        self.ratio_min_interval = int(ratio_min_interval)
+        self._last_ratio_change = -(1 << 30)
         self.iteration = 0
         self.pending: List[Tuple[int, int, float]] = []      # (effective_since, ubatch, ratio)
         self.applied: List[Tuple[int, int, float]] = []
@@ -118,8 +123,10 @@ class TelemetryHook:
                 lo = self.engine.buckets[0].bucket.min_ratio
                 target, now = max(ratio, lo), self.engine.cfg.ratio
                 kept_now, kept_new = max(1.0 - now, 1e-9), max(1.0 - target, 1e-9)
-                if abs(kept_new - kept_now) > self.ratio_tolerance * kept_now:
+                if (abs(kept_new - kept_now) > self.ratio_tolerance * kept_now and
+                        self.iteration - self._last_ratio_change >= self.ratio_min_interval):
                     self.engine.set_compression_ratio(target)
+                    self._last_ratio_change = self.iteration
             self.applied.append((since, ubatch, ratio))
         if due and self.apply_batch and self.engine.world > 1:
             # unequal batches: weight each rank's gradient by its share of the global batch

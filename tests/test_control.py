@@ -85,6 +85,37 @@ def test_optimizer_phases_and_heterogeneous_batches():
     assert 0.0 <= final.comp_ratio <= 0.999
 
 
+def test_allocation_stays_inside_the_sampled_batch_range():
+    """A fast GPU that starts at its working batch is only ever measured on the flat part of its curve; the knee is
+    then not determined by the samples and the allocation must not go below what was measured."""
+    it = {"n": 0}
+    opt = BatchRateOptimizer(2, 1, TrafficModel([1_000_000] * 10, "nvlink"), latest_iter=lambda: it["n"], reoptimize_every=5)
+    opt.set_max_batch(0, 64); opt.set_max_batch(1, 64)
+
+    def rows(batches):
+        out = []
+        for g, b in enumerate(batches):
+            bwd = (13.0 + 0.3 * max(0.0, b - 24.0)) * (1.0 if g == 0 else 1.6)     # latency-bound below 24 samples
+            out.append({"gpu": g, "batch_size": float(b), "bwd_ms": bwd, "fwd_ms": bwd / 2, "comp_ratio": 0.99,
+                        "bwd_fwd_gap_ms": 0.0, "intra_fwd_gap_ms": 0.0})
+        return out
+
+    batches = np.array([32.0, 32.0])
+    issued = []
+    for step in range(300):
+        it["n"] = step
+        opt.update(rows(batches))
+        inst = opt.step(step, measured_mbps=20000.0)
+        if inst is not None:
+            issued.append(inst)
+            batches = inst.batch.copy()
+        if opt.phase == Phase.RUNNING and len(issued) > 8:
+            break
+    assert opt.phase == Phase.RUNNING
+    assert min(float(b) for i in issued for b in i.batch) >= 32.0, [i.batch for i in issued]
+    assert issued[-1].batch[0] >= issued[-1].batch[1]                   # the slower GPU does not get the larger share
+
+
 def test_compression_follows_bandwidth():
     traffic = TrafficModel([5_000_000] * 20, "nvlink")
     assert traffic.tx_bytes(0.99) == pytest.approx(8 * 20 * 50_000 + 64, rel=1e-3)

@@ -24,16 +24,23 @@ def _spawn(fn, world, *args, env=None):
         p = ctx.Process(target=_entry, args=(fn, r, world, port, q, env or {}, args))
         p.start()
         procs.append(p)
+    import time
+
+    deadline = time.time() + 240          # for all ranks together: a hung rank costs GPU time on every GPU of the box
     for p in procs:
-        p.join(timeout=300)
+        p.join(timeout=max(1.0, deadline - time.time()))
     results = {}
     while not q.empty():
         r, ok, payload = q.get()
         results[r] = (ok, payload)
+    hung = [r for r, p in enumerate(procs) if p.is_alive()]
     for p in procs:
         if p.is_alive():
             p.kill()
-            pytest.fail("worker did not finish")
+    if hung:
+        # a rank that failed leaves the others waiting in their next collective: say what it died of
+        died = "\n".join(f"rank {r} failed:\n{payload}" for r, (ok, payload) in sorted(results.items()) if not ok)
+        pytest.fail(f"ranks {hung} did not finish" + (f"; {died}" if died else f"; finished: {sorted(results)}"))
     assert len(results) == world, f"missing results: {sorted(results)}"
     for r in range(world):
         ok, payload = results[r]
@@ -44,6 +51,9 @@ def _spawn(fn, world, *args, env=None):
 def _entry(fn, rank, world, port, q, env, args):
     import traceback
 
+    import faulthandler
+
+    faulthandler.dump_traceback_later(200, exit=False)      # a rank that hangs says where, before the parent ends it
     os.environ.update(env)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
