@@ -421,7 +421,9 @@ def main() -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     torch.manual_seed(1234)
-    torch.backends.cudnn.benchmark = True
+    # the controller's batch sizes bring new input shapes at run time: no exhaustive search of convolution algorithms
+    # for each of them (tens of seconds for ResNet-152, during which the other ranks' bounded waits run out)
+    torch.backends.cudnn.benchmark = not args.adapt_batch
 
     lm = is_language_model(args.model)
     if args.impl == "cpu_offload":
@@ -476,6 +478,9 @@ def main() -> None:
         st.state().engine_cfg.multicast = not args.no_multicast
         st.state().engine_cfg.grad_mode = args.grad_mode
         st.state().engine_cfg.native_hooks = bool(args.native_hooks)
+        if args.adapt_batch:
+            # ranks capture their new batch shapes at different speeds: give the device-side waits room for it
+            st.state().engine_cfg.timeout_s = 120.0
         if args.impl == "nccl_sparse":
             args.graph = 0            # the library collective between the kernel chains is not captured
         net = st.FasterDpModelWrapper(model, sequential=False, graph=bool(args.graph), graph_warmup=max(3, args.warmup - 2),
