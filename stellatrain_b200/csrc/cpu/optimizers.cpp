@@ -35,12 +35,23 @@ __attribute__((target("avx512f"))) static uint32_t sgd_avx512(float* param, floa
 }
 
 // ---------------------------------------------------------------- SGD
+// The state of a tensor is created at its first update.  The arrays are allocated and zeroed outside the lock: in
+// the first iteration every tensor of the model gets here at once from the pool's threads, and touching a few hundred
+// megabytes of fresh pages under one mutex would make them queue up behind one another (updates of one tensor never
+// overlap, so nobody else can be creating the same entry meanwhile).
 SGD::State& SGD::state_for(const std::string& name, uint32_t len) {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = state_.find(name);
+    if (it != state_.end() && it->second.b.size() == len) return it->second;
+  }
+  std::vector<float> b(len, 0.f);
+  std::vector<uint32_t> last(len, 0u);
   std::lock_guard<std::mutex> lk(mu_);
   State& s = state_[name];
   if (s.b.size() != len) {
-    s.b.assign(len, 0.f);
-    s.last.assign(len, 0u);
+    s.b.swap(b);
+    s.last.swap(last);
     s.first = true;
     s.iter = 0;
   }
@@ -123,15 +134,22 @@ void SGD::import_state(const std::map<std::string, TensorState>& st) {
 
 // ---------------------------------------------------------------- Adam
 Adam::State& Adam::state_for(const std::string& name, uint32_t len) {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = state_.find(name);
+    if (it != state_.end() && it->second.m.size() == len && (!amsgrad_ || it->second.vmax.size() == len)) return it->second;
+  }
+  std::vector<float> m(len, 0.f), v(len, 0.f), vmax(amsgrad_ ? len : 0, 0.f);   // outside the lock, see SGD::state_for
   std::lock_guard<std::mutex> lk(mu_);
   State& s = state_[name];
   if (s.m.size() != len) {
-    s.m.assign(len, 0.f);
-    s.v.assign(len, 0.f);
-    s.vmax.assign(amsgrad_ ? len : 0, 0.f);
+    s.m.swap(m);
+    s.v.swap(v);
+    s.vmax.swap(vmax);
     s.tick = 1;
+  } else if (amsgrad_ && s.vmax.size() != len) {
+    s.vmax.swap(vmax);
   }
-  if (amsgrad_ && s.vmax.size() != len) s.vmax.assign(len, 0.f);
   return s;
 }
 
