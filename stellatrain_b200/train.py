@@ -62,7 +62,7 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
                                method=args.compressor, gradient_accumulation=args.gradient_accumulation,
                                staleness=args.staleness, ratio=args.compression, optimizer=args.optim,
                                wire_blocks=not args.no_wire_blocks, wire_values=args.wire_values,
-                               data_transport=args.data_transport,
+                               data_transport=args.data_transport, bundle_elems=args.bundle_elems,
                                optimizer_options={"lr": args.lr, **({"momentum": args.momentum} if args.optim == "sgd" else {})})
         net, sync, engine_of = model, eng.synchronize, (lambda: eng)
 
@@ -235,6 +235,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="CPU tier: send (index, value) pairs even where 16 aligned indices could travel as one block id")
     p.add_argument("--data-transport", default="tcp", choices=["tcp", "zmq"],
                    help="CPU tier: the gradient ring between nodes over framed TCP or over ZeroMQ PUSH/PULL sockets")
+    p.add_argument("--bundle-elems", type=int, default=1 << 16,
+                   help="CPU tier: tensors below this many elements share one task per bundle of about that size; 0 gives "
+                        "one task per tensor, as in the reference")
     p.add_argument("--log-every", type=int, default=10)
     return p
 
