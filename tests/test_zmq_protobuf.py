@@ -84,3 +84,109 @@ def test_controller_answers_protobuf_clients_over_zeromq():
     finally:
         ep.close()
         ctl.close()
+
+
+def _schema_classes():
+    """The reference's schema (backend/src/proto/message.proto:5-88) stated as a descriptor for the protobuf run time,
+    so that the real library serialises and parses next to the hand-written codec.  No protoc involved."""
+    pb2 = pytest.importorskip("google.protobuf.descriptor_pb2")
+    from google.protobuf import descriptor_pool, message_factory
+
+    F = pb2.FieldDescriptorProto
+    fd = pb2.FileDescriptorProto(name="fasterdp_message_test.proto", package="fasterdp_test", syntax="proto3")
+
+    def msg(name, fields, enums=()):
+        m = fd.message_type.add(name=name)
+        for ename, values in enums:
+            e = m.enum_type.add(name=ename)
+            for i, v in enumerate(values):
+                e.value.add(name=v, number=i)
+        for fname, number, ftype, extra in fields:
+            f = m.field.add(name=fname, number=number, type=ftype, label=extra.get("label", F.LABEL_OPTIONAL))
+            if "type_name" in extra:
+                f.type_name = extra["type_name"]
+            if "oneof" in extra:
+                if not m.oneof_decl:
+                    m.oneof_decl.add(name="payload")
+                f.oneof_index = 0
+        return m
+
+    u32, f32, boolean, string, message, enum = F.TYPE_UINT32, F.TYPE_FLOAT, F.TYPE_BOOL, F.TYPE_STRING, F.TYPE_MESSAGE, F.TYPE_ENUM
+    pkg = ".fasterdp_test."
+    msg("TrainConfig", [("ubatch_size", 1, u32, {}), ("gradient_accumulation", 2, u32, {}), ("compression_rate", 3, f32, {})])
+    msg("Measurements", [(n, i + 1, f32, {}) for i, n in enumerate(
+        ["grad_send_thpt_mbps", "grad_recv_thpt_mbps", "fwd_delay_ms", "bwd_delay_ms", "bwd_fwd_gap_ms", "intra_fwd_gap_ms"])])
+    msg("GlobalTelemetryInit", [("num_nodes", 1, u32, {}), ("num_gpus", 2, u32, {}),
+                                ("param_counts", 3, u32, {"label": F.LABEL_REPEATED}), ("grad_fp16", 4, boolean, {}),
+                                ("grad_idx_u16", 5, boolean, {})])
+    msg("LocalTelemetryInit", [("client_id", 1, u32, {}), ("rank", 2, u32, {}), ("gpu_name", 3, string, {}),
+                               ("local_rank", 4, u32, {}), ("local_world_size", 5, u32, {}), ("max_batch_size", 6, u32, {})])
+    msg("Telemetry", [("client_id", 1, u32, {}), ("message_id", 2, u32, {}), ("uiter_count", 3, u32, {}),
+                      ("config", 4, message, {"type_name": pkg + "TrainConfig"}),
+                      ("measurements", 5, message, {"type_name": pkg + "Measurements"})])
+    msg("Instruction", [("client_id", 1, u32, {}), ("message_id", 2, u32, {}), ("effective_since_uiter", 3, u32, {}),
+                        ("valid", 4, boolean, {}), ("config", 5, message, {"type_name": pkg + "TrainConfig"})])
+    msg("Request", [("type", 1, enum, {"type_name": pkg + "Request.Type"}),
+                    ("global_telemetry_init", 2, message, {"type_name": pkg + "GlobalTelemetryInit", "oneof": True}),
+                    ("local_telemetry_init", 3, message, {"type_name": pkg + "LocalTelemetryInit", "oneof": True}),
+                    ("telemetry", 4, message, {"type_name": pkg + "Telemetry", "oneof": True})],
+        enums=[("Type", ["INVALID", "INIT", "GLOBAL_TELEMETRY_INIT", "LOCAL_TELEMETRY_INIT", "LOCAL_TELEMETRY", "TERMINATE"])])
+    msg("Response", [("type", 1, enum, {"type_name": pkg + "Response.Type"}),
+                     ("instruction", 2, message, {"type_name": pkg + "Instruction", "oneof": True})],
+        enums=[("Type", ["INVALID", "OK", "INSTRUCTION"])])
+    pool = descriptor_pool.DescriptorPool()
+    pool.Add(fd)
+    return {n: message_factory.GetMessageClass(pool.FindMessageTypeByName("fasterdp_test." + n))
+            for n in ("Request", "Response", "TrainConfig")}
+
+
+def test_codec_agrees_with_the_protobuf_library_on_the_references_schema():
+    """Every message the codec writes parses with the protobuf run time into the same fields, and what the run time
+    serialises (what a process built from the reference sends) is read back by the codec."""
+    cls = _schema_classes()
+    Request, Response = cls["Request"], cls["Response"]
+
+    # ours -> library
+    t = M.LocalTelemetry(5, 1234, M.TrainConfig(48, 2, 0.95), M.Measurement(100.5, 99.25, 7.0, 14.5, 0.75, 0.125))
+    r = Request.FromString(PB.encode_request(PB.REQ_LOCAL_TELEMETRY, t, message_id=9))
+    assert r.type == 4 and r.WhichOneof("payload") == "telemetry"
+    assert (r.telemetry.client_id, r.telemetry.message_id, r.telemetry.uiter_count) == (5, 9, 1234)
+    assert (r.telemetry.config.ubatch_size, r.telemetry.config.gradient_accumulation) == (48, 2)
+    assert r.telemetry.config.compression_rate == pytest.approx(0.95, rel=1e-6)
+    assert r.telemetry.measurements.bwd_delay_ms == 14.5 and r.telemetry.measurements.intra_fwd_gap_ms == 0.125
+    g = M.GlobalInit(2, 8, False, True, [9408, 64, 2359296, 100])
+    r = Request.FromString(PB.encode_request(PB.REQ_GLOBAL_TELEMETRY_INIT, g))
+    assert r.type == 2 and list(r.global_telemetry_init.param_counts) == g.param_counts
+    assert (r.global_telemetry_init.num_nodes, r.global_telemetry_init.num_gpus) == (2, 8)
+    assert r.global_telemetry_init.grad_idx_u16 and not r.global_telemetry_init.grad_fp16
+    r = Request.FromString(PB.encode_request(PB.REQ_LOCAL_TELEMETRY_INIT, M.LocalInit(3, 1, 2, "NVIDIA B200"),
+                                             local_world_size=4, max_batch_size=64))
+    li = r.local_telemetry_init
+    assert (li.client_id, li.rank, li.gpu_name, li.local_rank, li.local_world_size, li.max_batch_size) == (3, 1, "NVIDIA B200", 2, 4, 64)
+    resp = Response.FromString(PB.encode_response(PB.RESP_INSTRUCTION, M.Instruction(77, M.TrainConfig(24, 1, 0.875)), client_id=3))
+    assert resp.type == 2 and resp.instruction.valid and resp.instruction.client_id == 3
+    assert resp.instruction.effective_since_uiter == 77 and resp.instruction.config.compression_rate == 0.875
+    assert Request.FromString(PB.encode_request(PB.REQ_TERMINATE)).type == 5
+
+    # library -> ours; where no default value is involved the bytes are the same, too
+    lib = Request(type=4)
+    lib.telemetry.client_id, lib.telemetry.message_id, lib.telemetry.uiter_count = 5, 9, 1234
+    lib.telemetry.config.ubatch_size, lib.telemetry.config.gradient_accumulation, lib.telemetry.config.compression_rate = 48, 2, 0.95
+    for name, v in zip(["grad_send_thpt_mbps", "grad_recv_thpt_mbps", "fwd_delay_ms", "bwd_delay_ms", "bwd_fwd_gap_ms",
+                        "intra_fwd_gap_ms"], t.measurement.as_tuple()):
+        setattr(lib.telemetry.measurements, name, v)
+    assert lib.SerializeToString() == PB.encode_request(PB.REQ_LOCAL_TELEMETRY, t, message_id=9)
+    rtype, got = PB.decode_request(lib.SerializeToString())
+    assert rtype == PB.REQ_LOCAL_TELEMETRY and got.uiter == 1234 and got.measurement.as_tuple() == t.measurement.as_tuple()
+    lib = Request(type=2)
+    lib.global_telemetry_init.num_nodes, lib.global_telemetry_init.num_gpus, lib.global_telemetry_init.grad_idx_u16 = 2, 8, True
+    lib.global_telemetry_init.param_counts.extend(g.param_counts)
+    assert lib.SerializeToString() == PB.encode_request(PB.REQ_GLOBAL_TELEMETRY_INIT, g)
+    assert PB.decode_request(lib.SerializeToString()) == (PB.REQ_GLOBAL_TELEMETRY_INIT, g)
+    lib = Response(type=2)
+    lib.instruction.effective_since_uiter, lib.instruction.valid = 77, True
+    lib.instruction.config.ubatch_size, lib.instruction.config.gradient_accumulation, lib.instruction.config.compression_rate = 24, 1, 0.875
+    rtype, inst = PB.decode_response(lib.SerializeToString())
+    assert rtype == PB.RESP_INSTRUCTION and inst.iter_effective_since == 77 and inst.config.ubatch_size == 24
+    lib.instruction.valid = False
+    assert PB.decode_response(lib.SerializeToString()) == (PB.RESP_INSTRUCTION, None)     # not marked valid: counts as none
