@@ -64,7 +64,7 @@ EXTENSIONS = {
             "cpu/compressors.cpp", "cpu/optimizers.cpp", "cpu/array_util.cpp", "cpu/xorshift.cpp",
             "core/threadpool.cpp", "core/task.cpp", "core/shm_manager.cpp", "core/engine.cpp", "core/cuda_api.cpp", "core/fake_cuda.cpp",
             "core/stages.cpp", "comm/comm_manager.cpp", "comm/net_util.cpp", "comm/zmq_link.cpp",
-            "telemetry/telemetry.cpp", "bindings_cpu.cpp",
+            "telemetry/telemetry.cpp", "telemetry/proto_wire.cpp", "bindings_cpu.cpp",
         ],
         "link": "g++",
     },

@@ -11,7 +11,7 @@ namespace stc {
 namespace {
 
 // The part of zmq.h (libzmq 4.x, stable ABI) that this file uses.
-constexpr int kZmqPull = 7, kZmqPush = 8;
+constexpr int kZmqPull = 7, kZmqPush = 8, kZmqReq = 3;
 constexpr int kZmqSndMore = 2;
 constexpr int kZmqLinger = 17, kZmqSndHwm = 23, kZmqRcvHwm = 24, kZmqRcvTimeo = 27, kZmqSndTimeo = 28, kZmqLastEndpoint = 32;
 struct alignas(8) ZmqMsg { unsigned char opaque[64]; };
@@ -160,6 +160,48 @@ bool ZmqLink::recv(std::string* key, uint8_t* flags, std::vector<unsigned char>*
   if (part != 3 || !ok) {
     if (malformed) *malformed = true;
     return false;
+  }
+  return true;
+}
+
+ZmqReq::ZmqReq() {
+  if (g_api.handle != nullptr) ctx_ = g_api.ctx_new();
+}
+
+ZmqReq::~ZmqReq() { close(); }
+
+void ZmqReq::close() {
+  if (sock_) { g_api.close(sock_); sock_ = nullptr; }
+  if (ctx_) { g_api.ctx_term(ctx_); ctx_ = nullptr; }
+}
+
+bool ZmqReq::connect(const std::string& endpoint) {
+  if (ctx_ == nullptr) return false;
+  sock_ = g_api.socket(ctx_, kZmqReq);
+  if (sock_ == nullptr) return false;
+  const int zero = 0;
+  g_api.setsockopt(sock_, kZmqLinger, &zero, sizeof(zero));
+  return g_api.connect(sock_, endpoint.c_str()) == 0;
+}
+
+bool ZmqReq::request(const std::vector<unsigned char>& body, std::vector<unsigned char>* reply, int timeout_ms) {
+  if (sock_ == nullptr) return false;
+  g_api.setsockopt(sock_, kZmqSndTimeo, &timeout_ms, sizeof(timeout_ms));
+  g_api.setsockopt(sock_, kZmqRcvTimeo, &timeout_ms, sizeof(timeout_ms));
+  if (g_api.send(sock_, body.data(), body.size(), 0) < 0) return false;
+  reply->clear();
+  bool more = true;
+  while (more) {
+    ZmqMsg m;
+    g_api.msg_init(&m);
+    if (g_api.msg_recv(&m, sock_, 0) < 0) {
+      g_api.msg_close(&m);
+      return false;
+    }
+    const unsigned char* d = static_cast<const unsigned char*>(g_api.msg_data(&m));
+    reply->insert(reply->end(), d, d + g_api.msg_size(&m));
+    more = g_api.msg_more(&m) != 0;
+    g_api.msg_close(&m);
   }
   return true;
 }

@@ -45,4 +45,22 @@ class ZmqLink {
   void* pull_ = nullptr;
 };
 
+// REQ socket for the control plane (the reference's telemetry client and server talk to the controller's ROUTER socket
+// this way, backend/src/engine/telemetry_client.cpp:5-37): one request, one reply.  A request that got no reply in time
+// leaves a REQ socket unusable (strict alternation), so the caller gives the connection up after a failure.
+class ZmqReq {
+ public:
+  ZmqReq();
+  ~ZmqReq();
+  ZmqReq(const ZmqReq&) = delete;
+  ZmqReq& operator=(const ZmqReq&) = delete;
+  bool connect(const std::string& endpoint);      // "tcp://host:port"
+  bool request(const std::vector<unsigned char>& body, std::vector<unsigned char>* reply, int timeout_ms);
+  void close();
+
+ private:
+  void* ctx_ = nullptr;
+  void* sock_ = nullptr;
+};
+
 }  // namespace stc

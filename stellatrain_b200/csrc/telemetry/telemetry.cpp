@@ -6,8 +6,29 @@
 
 #include "../comm/net_util.h"
 #include "../core/logger.h"
+#include "proto_wire.h"
 
 namespace stc {
+
+// "zmq://host:port" (also "zmq+tcp://"): the ZeroMQ transport; *endpoint becomes "tcp://host:port".
+static bool zmq_uri(const std::string& uri, std::string* endpoint) {
+  for (const char* scheme : {"zmq://", "zmq+tcp://"}) {
+    const std::string sc(scheme);
+    if (uri.compare(0, sc.size(), sc) == 0) {
+      *endpoint = "tcp://" + uri.substr(sc.size());
+      return true;
+    }
+  }
+  return false;
+}
+
+static std::unique_ptr<ZmqReq> zmq_connect(const std::string& endpoint, const std::string& what) {
+  std::string why;
+  if (!ZmqLibrary::load("", &why)) throw std::runtime_error(what + ": " + why);
+  auto req = std::make_unique<ZmqReq>();
+  if (!req->connect(endpoint)) throw std::runtime_error(what + ": cannot connect a ZeroMQ REQ socket to " + endpoint);
+  return req;
+}
 
 bool parse_uri(const std::string& uri, std::string* host, uint16_t* port) {
   std::string s = uri;
@@ -41,21 +62,35 @@ TelemetryClient::TelemetryClient(const std::string& uri, uint32_t gpu_id, const 
                                  uint32_t local_rank, int timeout_ms)
     : st_(std::make_shared<State>()), gpu_id_(gpu_id) {
   st_->timeout_ms = timeout_ms;
-  std::string host;
-  uint16_t port;
-  if (!parse_uri(uri, &host, &port)) throw std::invalid_argument("bad telemetry uri: " + uri);
-  st_->fd = tcp_connect(host, port, timeout_ms);
-  if (st_->fd < 0) throw std::runtime_error("telemetry: cannot reach the controller at " + uri);
   LocalTelemetryInit init{};
   init.gpu_id = gpu_id;
   init.rank = rank;
   init.local_rank = local_rank;
   std::strncpy(init.gpu_name, gpu_name.c_str(), sizeof(init.gpu_name) - 1);
-  uint32_t type;
-  std::vector<unsigned char> reply;
-  if (!send_msg(st_->fd, kTelLocalInit, &init, sizeof(init), timeout_ms) || !recv_msg(st_->fd, &type, &reply, timeout_ms)) {
-    close_fd(st_->fd);
-    throw std::runtime_error("telemetry: the controller did not acknowledge the registration");
+  std::string endpoint;
+  if (zmq_uri(uri, &endpoint)) {
+    st_->zmq = zmq_connect(endpoint, "telemetry");
+    pbwire::Bytes reply;
+    uint32_t type = 0;
+    bool has = false;
+    Instruction ins{};
+    if (!st_->zmq->request(pbwire::request_local_init(init), &reply, timeout_ms) ||
+        !pbwire::parse_response(reply, &type, &has, &ins) || type == pbwire::kRespInvalid) {
+      st_->zmq->close();
+      throw std::runtime_error("telemetry: the controller did not acknowledge the registration");
+    }
+  } else {
+    std::string host;
+    uint16_t port;
+    if (!parse_uri(uri, &host, &port)) throw std::invalid_argument("bad telemetry uri: " + uri);
+    st_->fd = tcp_connect(host, port, timeout_ms);
+    if (st_->fd < 0) throw std::runtime_error("telemetry: cannot reach the controller at " + uri);
+    uint32_t type;
+    std::vector<unsigned char> reply;
+    if (!send_msg(st_->fd, kTelLocalInit, &init, sizeof(init), timeout_ms) || !recv_msg(st_->fd, &type, &reply, timeout_ms)) {
+      close_fd(st_->fd);
+      throw std::runtime_error("telemetry: the controller did not acknowledge the registration");
+    }
   }
   worker_ = std::thread(worker_main, st_);
 }
@@ -77,6 +112,7 @@ TelemetryClient::~TelemetryClient() {
     worker_.join();
   }
   close_fd(st_->fd);
+  if (st_->zmq) st_->zmq->close();
 }
 
 void TelemetryClient::report(uint64_t uiter, const TrainConfig& cfg, const TrainMeasurement& m, InstructionCallback cb) {
@@ -112,20 +148,28 @@ void TelemetryClient::worker_main(std::shared_ptr<State> st) {
         item = std::move(st->queue.front());
         st->queue.pop_front();
       }
-      uint32_t type;
+      uint32_t type = 0;
       std::vector<unsigned char> reply;
-      if (!send_msg(st->fd, kTelLocal, &item.first, sizeof(item.first), st->timeout_ms) ||
-          !recv_msg(st->fd, &type, &reply, st->timeout_ms)) {
+      bool ok, has_instruction = false;
+      Instruction ins{};
+      if (st->zmq) {
+        ok = st->zmq->request(pbwire::request_telemetry(item.first, st->message_id++), &reply, st->timeout_ms) &&
+             pbwire::parse_response(reply, &type, &has_instruction, &ins) && type != pbwire::kRespInvalid;
+      } else {
+        ok = send_msg(st->fd, kTelLocal, &item.first, sizeof(item.first), st->timeout_ms) &&
+             recv_msg(st->fd, &type, &reply, st->timeout_ms);
+        if (ok && type == kTelInstruction && reply.size() == sizeof(Instruction)) {
+          std::memcpy(&ins, reply.data(), sizeof(ins));
+          has_instruction = true;
+        }
+      }
+      if (!ok) {
         LOG_WARN("TelemetryClient", "controller connection lost; telemetry stops, training continues");
         st->dead = true;
         break;
       }
       ++st->sent;
-      if (type == kTelInstruction && reply.size() == sizeof(Instruction) && item.second) {
-        Instruction ins;
-        std::memcpy(&ins, reply.data(), sizeof(ins));
-        item.second(ins.iter_effective_since, ins.config);
-      }
+      if (has_instruction && item.second) item.second(ins.iter_effective_since, ins.config);
     }   // the callback is released here, which may destroy the client on this very thread
     if (st->stop && st.use_count() == 1) detached = true;
   }
@@ -136,7 +180,10 @@ void TelemetryClient::worker_main(std::shared_ptr<State> st) {
     rest.swap(st->queue);
   }
   rest.clear();
-  if (detached || st.use_count() == 1) close_fd(st->fd);   // the client is gone and could not close it itself
+  if (detached || st.use_count() == 1) {   // the client is gone and could not close the connection itself
+    close_fd(st->fd);
+    if (st->zmq) st->zmq->close();
+  }
 }
 
 TelemetryServer::TelemetryServer(const std::string& uri, bool launch_controller, int timeout_ms) : timeout_ms_(timeout_ms) {
@@ -149,6 +196,18 @@ TelemetryServer::TelemetryServer(const std::string& uri, bool launch_controller,
       const int rc = std::system(cmd.c_str());
       if (rc != 0) LOG_WARN("TelemetryServer", "controller exited with status " << rc);
     });
+  }
+  std::string endpoint;
+  if (zmq_uri(uri, &endpoint)) {
+    zmq_ = zmq_connect(endpoint, "telemetry server");
+    pbwire::Bytes reply;
+    uint32_t type = 0;
+    bool has = false;
+    Instruction ins{};
+    if (!zmq_->request(pbwire::request_plain(pbwire::kReqInit), &reply, timeout_ms_) ||
+        !pbwire::parse_response(reply, &type, &has, &ins) || type == pbwire::kRespInvalid)
+      throw std::runtime_error("telemetry server: controller did not answer INIT");
+    return;
   }
   fd_ = tcp_connect(host, port, timeout_ms);
   if (fd_ < 0) {
@@ -163,11 +222,21 @@ TelemetryServer::TelemetryServer(const std::string& uri, bool launch_controller,
 
 TelemetryServer::~TelemetryServer() {
   close_fd(fd_);
+  if (zmq_) zmq_->close();
   if (launcher_.joinable()) launcher_.join();
 }
 
 bool TelemetryServer::send_global_telemetry(uint32_t num_nodes, uint32_t num_gpus, const std::vector<uint64_t>& param_counts,
                                             bool grad_fp16, bool grad_idx_u16) {
+  if (zmq_) {
+    pbwire::Bytes reply;
+    uint32_t type = 0;
+    bool has = false;
+    Instruction ins{};
+    return zmq_->request(pbwire::request_global_init(num_nodes, num_gpus, param_counts, grad_fp16, grad_idx_u16), &reply,
+                         timeout_ms_) &&
+           pbwire::parse_response(reply, &type, &has, &ins) && type == pbwire::kRespOk;
+  }
   std::vector<unsigned char> buf(16 + param_counts.size() * 8);
   const uint32_t n = static_cast<uint32_t>(param_counts.size());
   std::memcpy(buf.data(), &num_nodes, 4);
@@ -184,6 +253,14 @@ bool TelemetryServer::send_global_telemetry(uint32_t num_nodes, uint32_t num_gpu
 }
 
 bool TelemetryServer::terminate() {
+  if (zmq_) {
+    pbwire::Bytes reply;
+    uint32_t type = 0;
+    bool has = false;
+    Instruction ins{};
+    return zmq_->request(pbwire::request_plain(pbwire::kReqTerminate), &reply, timeout_ms_) &&
+           pbwire::parse_response(reply, &type, &has, &ins);
+  }
   uint32_t type;
   std::vector<unsigned char> reply;
   return send_msg(fd_, kTelTerminate, nullptr, 0, timeout_ms_) && recv_msg(fd_, &type, &reply, timeout_ms_);

@@ -7,6 +7,11 @@
 // header; the Python controller (stellatrain_b200/control/messages.py) reads and writes the same bytes.
 // Client behaviour after backend/src/engine/telemetry_client.cpp:5-110 (blocking init, queued reports
 // from a worker thread, callback on INSTRUCTION); server shim after telemetry_server.cpp:10-96.
+//
+// Second transport, the reference's own: a uri that starts with "zmq://" makes client and server speak protobuf
+// messages over a ZeroMQ REQ socket (proto_wire.h, ../comm/zmq_link.h; libzmq is opened at run time, the path in
+// STELLATRAIN_LIBZMQ or the system's), which is what the reference's controller (batch_rate_alloc.py:283-321) and this
+// package's control/zmq_endpoint.py answer.
 #pragma once
 #include <atomic>
 #include <condition_variable>
@@ -18,6 +23,8 @@
 #include <string>
 #include <thread>
 #include <vector>
+
+#include "../comm/zmq_link.h"
 
 namespace stc {
 
@@ -59,7 +66,8 @@ using InstructionCallback = std::function<void(uint64_t iter_effective_since, co
 
 class TelemetryClient {
  public:
-  // uri: "tcp://host:port" or "host:port".  Throws when the controller cannot be reached in time.
+  // uri: "tcp://host:port" or "host:port" (framed TCP), "zmq://host:port" (protobuf over ZeroMQ REQ).  Throws when the
+  // controller cannot be reached in time.
   TelemetryClient(const std::string& uri, uint32_t gpu_id, const std::string& gpu_name, uint32_t rank,
                   uint32_t local_rank, int timeout_ms = 5000);
   ~TelemetryClient();
@@ -78,6 +86,8 @@ class TelemetryClient {
   // join the thread it runs on: it lets the thread go, and the thread finishes on the shared block alone.
   struct State {
     int fd = -1;
+    std::unique_ptr<ZmqReq> zmq;      // set instead of fd for the ZeroMQ transport
+    uint32_t message_id = 0;
     int timeout_ms = 5000;
     std::mutex mu;
     std::condition_variable cv;
@@ -104,6 +114,7 @@ class TelemetryServer {
 
  private:
   int fd_ = -1;
+  std::unique_ptr<ZmqReq> zmq_;
   int timeout_ms_;
   std::thread launcher_;
 };

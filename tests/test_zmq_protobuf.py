@@ -190,3 +190,46 @@ def test_codec_agrees_with_the_protobuf_library_on_the_references_schema():
     assert rtype == PB.RESP_INSTRUCTION and inst.iter_effective_since == 77 and inst.config.ubatch_size == 24
     lib.instruction.valid = False
     assert PB.decode_response(lib.SerializeToString()) == (PB.RESP_INSTRUCTION, None)     # not marked valid: counts as none
+
+
+def test_native_client_and_server_speak_protobuf_over_zeromq(monkeypatch):
+    """The C++ telemetry client and server shim on the reference's transport: uri "zmq://..." makes them send protobuf
+    requests over a ZeroMQ REQ socket (libzmq opened at run time), answered here by the controller's ROUTER endpoint."""
+    pytest.importorskip("zmq")
+    from stellatrain_b200 import cpu_tier
+    from stellatrain_b200.control.controller import Controller
+    from stellatrain_b200.control.zmq_endpoint import ZmqControllerEndpoint
+
+    lib = cpu_tier.bundled_libzmq()
+    if not lib:
+        pytest.skip("no libzmq inside pyzmq")
+    monkeypatch.setenv("STELLATRAIN_LIBZMQ", lib)
+    ext = cpu_tier._load()
+    ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
+    ep = ZmqControllerEndpoint(ctl, "tcp://127.0.0.1:0").start()
+    got = []
+    try:
+        uri = f"zmq://127.0.0.1:{ep.port}"
+        server = ext.TelemetryServer(uri, False, 3000)
+        assert server.send_global_telemetry(1, 2, [1000, 2000, 300000], False, True)
+        gi = ctl.global_init
+        assert (gi.num_nodes, gi.num_gpus, gi.param_counts, gi.grad_fp16, gi.grad_idx_u16) == (1, 2, [1000, 2000, 300000], False, True)
+        clients = [ext.TelemetryClient(uri, g, "NVIDIA B200", 0, g, 3000) for g in range(2)]
+        assert sorted(ctl.clients) == [0, 1] and ctl.clients[1].gpu_name == "NVIDIA B200" and ctl.clients[1].local_rank == 1
+        ctl.clients[0].pending.put(M.Instruction(40, M.TrainConfig(20, 1, 0.875)))
+        for it in range(5):
+            for g, c in enumerate(clients):
+                c.report(it, ext.TrainConfig(16, 1, 0.99), [300.0, 200.0, 5.0, 10.0 + g, 1.0, 0.0],
+                         lambda since, ub, ga, cr, g=g: got.append((g, since, ub, ga, cr)))
+        deadline = time.time() + 5.0
+        while (ctl.latest_iter < 4 or not got or clients[1].sent() < 5) and time.time() < deadline:
+            time.sleep(0.02)
+        assert ctl.latest_iter >= 4 and clients[0].alive() and clients[0].sent() == 5
+        assert float(ctl.scoreboard.loc[1, "bwd_ms"]) == pytest.approx(11.0)
+        assert float(ctl.scoreboard.loc[1, "send_mbps"]) == pytest.approx(300.0)
+        assert got == [(0, 40, 20, 1, 0.875)]
+        assert server.terminate() and ctl.stop.is_set()
+        del clients, server
+    finally:
+        ep.close()
+        ctl.close()
