@@ -97,6 +97,16 @@ def bundled_libzmq() -> str:
     return found[0] if found else ""
 
 
+def prepare_telemetry_uri(uri: str) -> str:
+    """For a ``zmq://`` controller address (the reference's transport) tell the native client where pyzmq keeps its
+    libzmq, unless the environment already names one.  Returns the uri unchanged."""
+    if uri and uri.startswith("zmq") and not os.environ.get("STELLATRAIN_LIBZMQ"):
+        found = bundled_libzmq()
+        if found:
+            os.environ["STELLATRAIN_LIBZMQ"] = found
+    return uri
+
+
 class CpuOffloadEngine:
     def __init__(self, module: nn.Module, *, master_addr: str = "127.0.0.1", master_port: int = 5555, world_size: int = 1,
                  rank: int = 0, session: Optional[int] = None, local_world_size: int = 1, local_rank: int = 0,
@@ -454,7 +464,7 @@ class CpuTierTelemetry:
             ext = _load()
             name = gpu_name or (torch.cuda.get_device_name(0) if engine.cuda else "cpu")
             self._TrainConfig = ext.TrainConfig
-            self.client = ext.TelemetryClient(uri, gpu_id, name, rank, local_rank, timeout_ms)
+            self.client = ext.TelemetryClient(prepare_telemetry_uri(uri), gpu_id, name, rank, local_rank, timeout_ms)
 
     def _on_instruction(self, since: int, ubatch: int, grad_acc: int, ratio: float) -> None:
         with self._lock:

@@ -73,7 +73,7 @@ class TelemetryHook:
             last = None
             for _ in range(3):
                 try:
-                    self.client = ext.TelemetryClient(uri, engine.rank, name, 0, engine.rank, 10000)
+                    self.client = ext.TelemetryClient(cpu_tier.prepare_telemetry_uri(uri), engine.rank, name, 0, engine.rank, 10000)
                     break
                 except RuntimeError as e:
                     last = e

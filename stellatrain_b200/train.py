@@ -219,7 +219,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--graph", action="store_true",
                    help="GPU tier: capture the iteration in a CUDA graph after --graph-warmup eager iterations and replay it")
     p.add_argument("--graph-warmup", type=int, default=3)
-    p.add_argument("--telemetry-uri", default=None)
+    p.add_argument("--telemetry-uri", default=None,
+                   help="controller address: host:port or tcp://host:port (this package's frames), zmq://host:port (the "
+                        "reference's protobuf messages over ZeroMQ, e.g. its own batch_rate_alloc.py)")
     p.add_argument("--checkpoint", default=None, help="written at the end and every --checkpoint-every iterations")
     p.add_argument("--checkpoint-every", type=int, default=0)
     p.add_argument("--resume", default=None, help="checkpoint to start from")

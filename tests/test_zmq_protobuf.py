@@ -233,3 +233,43 @@ def test_native_client_and_server_speak_protobuf_over_zeromq(monkeypatch):
     finally:
         ep.close()
         ctl.close()
+
+
+def test_cpu_tier_hook_reports_over_zeromq_when_given_a_zmq_uri():
+    """`zmq://` as the controller address of the training hooks: the native client finds pyzmq's libzmq by itself."""
+    pytest.importorskip("zmq")
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from stellatrain_b200 import cpu_tier
+    from stellatrain_b200.control.controller import Controller
+    from stellatrain_b200.control.zmq_endpoint import ZmqControllerEndpoint
+
+    if not cpu_tier.bundled_libzmq():
+        pytest.skip("no libzmq inside pyzmq")
+    ctl = Controller(port=0, host="127.0.0.1", adapt=False).start()
+    ep = ZmqControllerEndpoint(ctl, "tcp://127.0.0.1:0").start()
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 4))
+    eng = cpu_tier.CpuOffloadEngine(model, method="topk", ratio=0.9, optimizer="sgd", optimizer_options={"lr": 0.05},
+                                    staleness=1, data_bytes=4 << 20, workers=2)
+    try:
+        hook = cpu_tier.CpuTierTelemetry(eng, f"zmq://127.0.0.1:{ep.port}", batch_size=8)
+        for i in range(6):
+            x, y = torch.randn(8, 16), torch.randint(0, 4, (8,))
+            with hook.step() as marker:
+                loss = F.cross_entropy(model(x), y)
+                marker.backward_begins()
+                loss.backward()
+        deadline = time.time() + 5.0
+        while ctl.latest_iter < 5 and time.time() < deadline:
+            time.sleep(0.02)
+        assert ctl.latest_iter >= 5 and 0 in ctl.clients
+        assert float(ctl.scoreboard.loc[0, "bwd_ms"]) > 0.0
+        hook.client = None
+    finally:
+        eng.synchronize()
+        eng.close()
+        ep.close()
+        ctl.close()
