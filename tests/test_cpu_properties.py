@@ -162,3 +162,39 @@ def test_wire_decoder_refuses_or_decodes_arbitrary_bytes(flags, payload, numel):
     assert len(idx) == len(val)
     if numel:
         assert all(i < numel or i == 0xFFFFFFFF for i in idx)
+
+
+@settings(max_examples=10, deadline=None)
+@given(st.lists(st.integers(1, 3000), min_size=2, max_size=7), st.sampled_from([64, 512, 2048, 1 << 16]),
+       st.sampled_from(["topk", "thresholdv", "thresholdv16"]), st.integers(0, 2**20))
+def test_bundles_train_bit_for_bit_like_one_task_per_tensor(sizes, bundle_elems, method, seed):
+    """Any mix of tensor sizes, any bundle limit, any compressor: laying small tensors end to end in one task changes
+    nothing in what is selected, merged and applied (selection stays per tensor, under the tensor's own threshold)."""
+    import torch.nn as nn
+
+    class Bag(nn.Module):
+        def __init__(self):
+            super().__init__()
+            g = torch.Generator().manual_seed(seed)
+            self.ps = nn.ParameterList([nn.Parameter(torch.randn(n, generator=g)) for n in sizes])
+
+        def forward(self, coeffs):
+            return sum((p * c).sum() for p, c in zip(self.ps, coeffs))
+
+    def run(be):
+        model = Bag()
+        eng = cpu_tier.CpuOffloadEngine(model, method=method, ratio=0.8, optimizer="adam", optimizer_options={"lr": 1e-2},
+                                        staleness=1, data_bytes=4 << 20, workers=2, bundle_elems=be)
+        g = torch.Generator().manual_seed(seed + 1)
+        for _ in range(4):
+            model([torch.randn(n, generator=g) for n in sizes]).backward()
+        eng.synchronize()
+        out = [p.detach().clone() for p in model.parameters()], eng.engine.num_params()
+        eng.close()
+        return out
+
+    want, n_plain = run(0)
+    got, n_units = run(bundle_elems)
+    assert n_plain == len(sizes) and n_units <= n_plain
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
