@@ -323,6 +323,20 @@ def test_two_nodes_two_local_processes_match_oracle(method, optimizer, staleness
             np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("mode", ["ok_bundle", "ok_bundle_device"])
+def test_two_nodes_two_local_processes_with_a_bundle_match_oracle(mode):
+    """The bundle through every stage with company: sliced gather over two local processes, per-member selection on the
+    node master, ring exchange of the joined streams between two nodes, merge, optimiser, copy-out into the members."""
+    world, local_world, steps = 2, 2, 6
+    results = _launch(world, local_world, steps, "thresholdv16", "adam", 1, mode)
+    assert len(results) == 4 and all(r[2] == "ok" for r in results), results
+    want = _oracle_run(world, local_world, steps, "thresholdv16", "adam")
+    for node, local, _, out in results:
+        assert out["drift"] == 0.0 and out["versions"] == [steps] * 3
+        for got, w in zip(out["params"], want):
+            np.testing.assert_allclose(got, w.numpy(), rtol=2e-5, atol=1e-6)
+
+
 def test_two_nodes_exchange_over_zeromq_like_over_tcp(monkeypatch):
     """The whole host pipeline with the ring on ZeroMQ PUSH/PULL sockets: same parameters as the oracle."""
     lib = _libzmq_path()
