@@ -192,6 +192,76 @@ void test_device_copies(int staleness) {
   if (!err.empty()) throw std::runtime_error("device copies, staleness " + std::to_string(staleness) + ": " + err);
 }
 
+// Several tensors as one bundle (one task per iteration, per-member selection): host gradients handed in member by
+// member, and the engine's own copies of all members behind one callback.
+void test_bundle(bool device_copies) {
+  if (device_copies) install_fake_cuda(1);
+  std::string err;
+  {
+    CpuEngine engine;
+    EngineOptions o;
+    o.session = static_cast<int64_t>(getpid()) * 100 + 80 + (device_copies ? 1 : 0);
+    o.staleness = 1;
+    o.method = "thresholdv16";
+    o.ratio = 0.9;
+    o.workers = 4;
+    o.data_bytes = 16u << 20;
+    o.timeout_ms = 20000;
+    try {
+      engine.configure(o);
+      engine.set_optimizer("adam");
+      engine.sparse_optimizer()->configure("lr", 1e-2f);
+      const std::vector<uint32_t> sizes = {4096, 17, 70000, 300};
+      std::vector<uint32_t> offsets;
+      uint32_t total = 0;
+      for (uint32_t n : sizes) { offsets.push_back(total); total += (n + 15u) / 16u * 16u; }
+      std::vector<float> init(total, 0.f);
+      std::vector<std::vector<float>> member(sizes.size());
+      std::vector<std::string> keys;
+      std::vector<float*> host_ptrs;
+      std::vector<void*> dev_ptrs;
+      for (size_t m = 0; m < sizes.size(); ++m) {
+        member[m].assign(sizes[m], 0.5f);
+        std::fill(init.begin() + offsets[m], init.begin() + offsets[m] + sizes[m], 0.5f);
+        keys.push_back(std::to_string(m) + "@m" + std::to_string(m));
+        host_ptrs.push_back(member[m].data());
+        dev_ptrs.push_back(member[m].data());
+      }
+      const int b = engine.pre_train_init(0, "bundle", total, nullptr, init.data());
+      engine.set_param_members(b, keys, offsets, sizes, device_copies ? std::vector<float*>{} : host_ptrs);
+      if (device_copies) engine.attach_device_members(b, dev_ptrs);
+      const int iters = 8;
+      std::vector<std::vector<std::vector<float>>> grads(iters, std::vector<std::vector<float>>(sizes.size()));
+      for (int it = 0; it < iters; ++it) {
+        engine.pre_forward_process(b);
+        std::vector<const void*> ptrs;
+        for (size_t m = 0; m < sizes.size(); ++m) {
+          std::vector<float>& g = grads[it][m];                  // alive until the copy stream has read it
+          g.resize(sizes[m]);
+          for (uint32_t j = 0; j < sizes[m]; ++j) g[j] = 1e-3f * static_cast<float>(((j * 2654435761u) >> 20) % 97 + 1 + it + m);
+          ptrs.push_back(g.data());
+        }
+        if (device_copies) {
+          engine.post_backward_device_members(b, ptrs, nullptr, nullptr);
+        } else {
+          for (size_t m = sizes.size(); m-- > 0;) engine.post_backward_member(b, static_cast<int>(m), grads[it][m].data());
+        }
+      }
+      engine.synchronize();
+      CHECK(engine.model_version(b) == iters && engine.num_params() == 1);
+      for (size_t m = 0; m < sizes.size(); ++m) {
+        bool moved = false;
+        for (float x : member[m]) { CHECK(std::isfinite(x)); moved |= x != 0.5f; }
+        CHECK(moved);
+      }
+    } catch (const std::exception& e) {
+      err = e.what();
+    }
+  }
+  if (device_copies) remove_fake_cuda();
+  if (!err.empty()) throw std::runtime_error(std::string("bundle, ") + (device_copies ? "device" : "host") + " copies: " + err);
+}
+
 // Telemetry client against a stand-in controller (a thread that acknowledges every frame and answers every fifth
 // report with an instruction): ordinary shutdown with reports still queued, and a client whose last owner is a
 // callback queued in its own thread, so that it is destroyed on that thread.
@@ -298,6 +368,8 @@ int main(int argc, char** argv) {
     test_single_node(1, 2, "thresholdv");
     test_device_copies(0);
     test_device_copies(1);
+    test_bundle(false);
+    test_bundle(true);
     test_two_nodes(port);
     test_telemetry(static_cast<uint16_t>(port + 7));
   } catch (const std::exception& e) {
