@@ -268,8 +268,12 @@ def _single_instance(port: int) -> None:
     pid_file = f"/tmp/stellatrain-b200-controller-{port}.pid"
     try:
         old = int(open(pid_file).read())
-        if old != os.getpid():
-            os.kill(old, 15)     # the exact pid recorded by the previous controller on this port
+        # the pid recorded by the previous controller on this port, and only while it still is a controller: a stale
+        # file may name a process id that the system has handed to somebody else since
+        with open(f"/proc/{old}/cmdline", "rb") as f:
+            still_a_controller = b"stellatrain_b200.control.controller" in f.read()
+        if old != os.getpid() and still_a_controller:
+            os.kill(old, 15)
             time.sleep(0.2)
     except (OSError, ValueError):
         pass
@@ -277,16 +281,57 @@ def _single_instance(port: int) -> None:
         f.write(str(os.getpid()))
 
 
+def spawn_controller(port: int, host: str = "127.0.0.1", max_batch: Optional[int] = None, profile: Optional[str] = None,
+                     transport: str = "nvlink", state_file: Optional[str] = None, wait_s: float = 30.0):
+    """Starts the controller in a process of its own (``python -m stellatrain_b200.control.controller``), the way the
+    reference's telemetry server starts its ``batch_rate_alloc.py`` (backend/src/engine/telemetry_server.cpp:57-73), and
+    returns the ``subprocess.Popen`` once the port accepts connections.  A controller inside a training process shares
+    that process's interpreter lock: its fits and optimisations slow the training loop down, and a training thread
+    that waits for the device with the lock held keeps it from answering anybody."""
+    import subprocess
+
+    cmd = [sys.executable, "-m", "stellatrain_b200.control.controller", "--port", str(port), "--host", host,
+           "--transport", transport]
+    if max_batch:
+        cmd += ["--max-batch", str(int(max_batch))]
+    if profile:
+        cmd += ["--profile", profile]
+    if state_file:
+        cmd += ["--state-file", state_file]
+    def _die_with_parent() -> None:      # in the child, before exec: SIGTERM when the process that started it goes away
+        import ctypes
+        import signal
+
+        try:
+            ctypes.CDLL("libc.so.6", use_errno=True).prctl(1, signal.SIGTERM)     # PR_SET_PDEATHSIG
+        except OSError:
+            pass
+
+    proc = subprocess.Popen(cmd, preexec_fn=_die_with_parent)
+    deadline = time.time() + wait_s
+    while time.time() < deadline:
+        if proc.poll() is not None:
+            raise RuntimeError(f"the controller process ended with status {proc.returncode} before it listened")
+        try:
+            with socket.create_connection((host, port), timeout=0.5):
+                return proc
+        except OSError:
+            time.sleep(0.1)
+    proc.terminate()
+    raise RuntimeError(f"the controller process did not listen on {host}:{port} within {wait_s:.0f} s")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--port", type=int, default=5556)
+    ap.add_argument("--host", default="0.0.0.0")
     ap.add_argument("--profile", default=None)
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "tcp"])
     ap.add_argument("--state-file", default=None, help="optimiser state is kept here across restarts of the controller")
     ap.add_argument("--max-batch", type=int, default=None, help="per-GPU batch ceiling (default: by device name)")
     args = ap.parse_args()
     _single_instance(args.port)
-    c = Controller(args.port, profile_path=args.profile, transport=args.transport, state_path=args.state_file,
+    c = Controller(args.port, host=args.host, profile_path=args.profile, transport=args.transport, state_path=args.state_file,
                    max_batch=args.max_batch).start()
     try:
         while not c.stop.is_set():

@@ -474,3 +474,37 @@ def test_client_destroyed_with_callbacks_still_queued_does_not_wait_for_itself()
         assert time.time() - t0 < 30
     finally:
         ctl.close()
+
+
+def test_controller_in_a_process_of_its_own_serves_clients_and_terminates():
+    """`spawn_controller` starts `python -m stellatrain_b200.control.controller`, waits until it listens, and the
+    native server shim and clients work against it; TERMINATE ends the process."""
+    from stellatrain_b200 import cpu_tier
+    from stellatrain_b200.control.controller import spawn_controller
+
+    ext = cpu_tier._load()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    proc = spawn_controller(port, max_batch=48)
+    try:
+        uri = f"127.0.0.1:{port}"
+        server = ext.TelemetryServer(uri, False, 5000)
+        assert server.send_global_telemetry(1, 2, [1000, 2000, 300000], False, False)
+        clients = [ext.TelemetryClient(uri, g, "NVIDIA B200", 0, g, 5000) for g in range(2)]
+        got = []
+        cfg = [ext.TrainConfig(8, 1, 0.99), ext.TrainConfig(8, 1, 0.99)]
+        for it in range(200):
+            for g, c in enumerate(clients):
+                c.report(it, cfg[g], [300.0, 300.0, 1.0, cfg[g].ubatch_size * 0.5 + 2.0, 0.0, 0.0],
+                         lambda since, ub, ga, cr, g=g: (got.append((g, since, ub, cr)), setattr(cfg[g], "ubatch_size", ub)))
+            time.sleep(0.01)
+            if len(got) >= 4:
+                break
+        assert len(got) >= 2 and all(1 <= ub <= 48 for _, _, ub, _ in got), got      # the batch ceiling reached the child
+        assert server.terminate()
+        assert proc.wait(timeout=10) == 0
+        del clients, server
+    finally:
+        if proc.poll() is None:
+            proc.kill()
