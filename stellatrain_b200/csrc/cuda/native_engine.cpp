@@ -40,6 +40,8 @@ struct BucketRec {
   cudaEvent_t grad_ready = nullptr;
   cudaEvent_t apply_done = nullptr;
   bool apply_done_set = false;
+  cudaEvent_t select_done = nullptr;       // the latest select of this bucket has read its gradients
+  bool select_done_set = false;
   bool has_pending_apply = false;
   int64_t select_count = 0, apply_count = 0;
 };
@@ -111,6 +113,10 @@ struct NativeEngine::Impl {
       kernels += 1;
     }
     check(h->select(sparse));
+    if (!capturing) {
+      check(cudaEventRecord(b.select_done, sparse));
+      b.select_done_set = true;
+    }
     b.select_count += 1;
     kernels += h->select_kernels();
   }
@@ -151,6 +157,11 @@ struct NativeEngine::Impl {
     std::vector<at::Tensor> release;
     if (b.spec.steal) {
       const size_t n = b.spec.seg_off.size();
+      // The bucket has one table of gradient addresses on the device.  The select of the previous iteration reads it
+      // in the sparse stream and may still be waiting there (for acknowledgements of a slow peer, for the link shaper)
+      // when this iteration's backward pass gets here: the new addresses go in behind it.  Replays of a captured
+      // iteration follow one another on their stream and need no such wait.
+      if (!capturing && b.select_done_set) check(cudaStreamWaitEvent(cur, b.select_done, 0));
       check(cudaMemcpyAsync(b.spec.table_dev, row_of(b), n * sizeof(uint64_t), cudaMemcpyHostToDevice, cur));
       if (!capturing) {
         check(cudaEventRecord(b.tab_events[b.tab_slot], cur));
@@ -213,6 +224,7 @@ NativeEngine::~NativeEngine() {
     for (auto ev : b.tab_events) cudaEventDestroy(ev);
     if (b.grad_ready) cudaEventDestroy(b.grad_ready);
     if (b.apply_done) cudaEventDestroy(b.apply_done);
+    if (b.select_done) cudaEventDestroy(b.select_done);
   }
   delete impl_;
 }
@@ -234,7 +246,8 @@ int NativeEngine::add_bucket(const NativeBucketSpec& spec) {
   for (auto& ev : b.tab_events)
     if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) throw std::runtime_error("cudaEventCreate failed");
   if (cudaEventCreateWithFlags(&b.grad_ready, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&b.apply_done, cudaEventDisableTiming) != cudaSuccess)
+      cudaEventCreateWithFlags(&b.apply_done, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&b.select_done, cudaEventDisableTiming) != cudaSuccess)
     throw std::runtime_error("cudaEventCreate failed");
   impl_->buckets.push_back(std::move(b));
   return (int)impl_->buckets.size() - 1;
@@ -293,6 +306,9 @@ void NativeEngine::wait_applies(uint64_t stream, int bucket) {
     if (bucket >= 0 && i != bucket) continue;
     BucketRec& b = impl_->buckets[i];
     if (b.apply_done_set) impl_->check(cudaStreamWaitEvent(s, b.apply_done, 0));
+    // With a flat gradient buffer the coming backward pass accumulates into the memory that the latest select reads
+    // and clears: the two must not overlap (with stolen gradients the select has its own tensors, see bucket_ready).
+    if (!b.spec.steal && b.select_done_set) impl_->check(cudaStreamWaitEvent(s, b.select_done, 0));
   }
 }
 
@@ -332,6 +348,7 @@ PyObject* NativeEngine::end_capture() {
     BucketRec& b = impl_->buckets[i];
     b.capture_row = at::Tensor();
     b.apply_done_set = false;      // events recorded under capture are not waitable outside
+    b.select_done_set = false;     // and the selects of a replay are joined before the replay ends
   }
   PyObject* list = PyList_New((Py_ssize_t)impl_->capture_keep.size());
   for (size_t i = 0; i < impl_->capture_keep.size(); ++i)

@@ -80,6 +80,7 @@ class _BucketRuntime:
         self._pending = self.full
         self.grad_ready = torch.cuda.Event()
         self.apply_done: Optional[torch.cuda.Event] = None
+        self.select_done: Optional[torch.cuda.Event] = None      # Python hooks: the latest select has read its gradients
         self._has_pending_apply = False
         self._select_count = 0
         self._apply_count = 0
@@ -534,6 +535,9 @@ class SparseDPEngine:
                 ev = self.buckets[bi].apply_done
                 if ev is not None:
                     cur.wait_event(ev)
+                ev = self.buckets[bi].select_done
+                if self.cfg.grad_mode == "flat" and ev is not None:
+                    cur.wait_event(ev)
 
         return pre
 
@@ -579,6 +583,9 @@ class SparseDPEngine:
                     continue
                 if rt.apply_done is not None:
                     cur.wait_event(rt.apply_done)
+                # flat gradient buffer: the coming backward pass accumulates into what the latest select reads and clears
+                if self.cfg.grad_mode == "flat" and rt.select_done is not None:
+                    cur.wait_event(rt.select_done)
         if self.cfg.step_clock:
             self.stamp(0)             # behind the waits: time spent blocked on updates counts as gap, not as forward
         self._forward_count = getattr(self, "_forward_count", 0) + 1
@@ -591,6 +598,10 @@ class SparseDPEngine:
         s = self.sparse_stream
         if self.cfg.grad_mode != "flat":
             b = rt.bucket
+            # one table of gradient addresses per bucket on the device: the previous iteration's select, which may still
+            # be waiting in the sparse stream (a slow peer, the link shaper), has to have read it before it is rewritten
+            if not self._capturing and rt.select_done is not None:
+                cur.wait_event(rt.select_done)
             b.grad_tab_dev.copy_(self._table_row(rt), non_blocking=True)   # compute stream, before the event
             if not self._capturing:
                 ev = torch.cuda.Event()
@@ -654,6 +665,11 @@ class SparseDPEngine:
                 self.shaper.take(nbytes, s)
                 self.stats["kernels"] += 1
             b.select(s)
+        if self._capturing:
+            rt.select_done = None
+        else:
+            rt.select_done = torch.cuda.Event()
+            rt.select_done.record(s)
         rt.select_count += 1
         self.stats["select_launches"] += 1
         self.stats["kernels"] += (b.select_handle or b.handle).select_kernels

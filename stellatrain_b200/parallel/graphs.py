@@ -63,6 +63,7 @@ class GraphedStep:
             self._per_replay.append((rt.select_count - s0, rt.apply_count - a0))
             rt.select_count, rt.apply_count = s0, a0
             rt.apply_done = None          # events recorded under capture are not waitable outside
+            rt.select_done = None
         self._kernels_per_replay = engine.kernels_launched() - kernels0
         engine.stats["kernels"] -= self._kernels_per_replay
         self._shaped_per_replay = engine.shaped_bytes - shaped0

@@ -500,6 +500,45 @@ def test_stolen_gradients_outlive_the_select_that_reads_them(native):
     eng.close()
 
 
+@pytest.mark.parametrize("grad_mode", ["steal", "flat"])
+@pytest.mark.parametrize("native", [True, False])
+def test_a_select_that_runs_late_still_reads_its_own_iterations_gradients(native, grad_mode):
+    """A shaped link holds every select for about 20 ms while an iteration of this small model takes far less, so the
+    host and the compute stream are an iteration ahead of the sparse stream all the time.  The select of iteration i
+    must nevertheless read the gradients of iteration i: the bucket's table of gradient addresses (or its flat
+    gradient buffer) may only be rewritten once that select has read it.  Exact accounting shows a gradient that was
+    dropped or taken twice."""
+    from stellatrain_b200.control.shaper import BandwidthSchedule, DeviceTokenBucket
+    from stellatrain_b200.parallel.engine import EngineConfig, SparseDPEngine
+
+    sizes = (5000, 70000, 300, 17, 4096)
+    model = _LinearInGrad(sizes).cuda()
+    p0 = [p.detach().clone() for p in model.ps]
+    eng = SparseDPEngine(model, EngineConfig(compressor="topk", ratio=0.9, optimizer="sgd", staleness=1, bucket_mb=0.5,
+                                             chunk_elems=1024, optimizer_options={"lr": 1.0}, native_hooks=native,
+                                             grad_mode=grad_mode))
+    sched = BandwidthSchedule(seed=1, lo_gbps=0.025, hi_gbps=0.025, period_s=10.0)       # about 3 MB/s
+    eng.set_link_shaper(DeviceTokenBucket(sched, eng.device, burst_bytes=1 << 12), destinations=1)
+    g = torch.Generator(device="cuda").manual_seed(500)
+    fed = [torch.zeros_like(p, dtype=torch.float64) for p in p0]
+    for step in range(8):
+        coeffs = [torch.randn(p.numel(), device="cuda", generator=g) * (0.5 ** (step % 3)) for p in p0]
+        for f, c in zip(fed, coeffs):
+            f += c.double()
+        model(coeffs).backward()
+    eng.synchronize()
+    eng.check_status()
+    assert eng.shaper.stats()["waited_s"] > 0.05            # the link did hold the selects back
+    by_name = {n: p for n, p in model.named_parameters()}
+    for rt, names in zip(eng.buckets, eng.param_names):
+        for seg, name in zip(rt.bucket.layout.segments, names):
+            i = int(name.split(".")[-1])
+            resid = rt.bucket.resid[seg.off: seg.off + seg.numel].double()
+            moved = p0[i].double() - by_name[name].detach().double()
+            assert float((fed[i] - resid - moved).abs().max()) < 1e-4, name
+    eng.close()
+
+
 @pytest.mark.parametrize("scenario", ["plain", "ratio_change", "eager_detour", "drain_and_new_shape"])
 def test_wrapper_train_step_graph_equals_eager(scenario):
     """The captured iteration is the product path of the wrapper: same parameters as eager launches, also across a
