@@ -528,7 +528,7 @@ def test_a_select_that_runs_late_still_reads_its_own_iterations_gradients(native
         model(coeffs).backward()
     eng.synchronize()
     eng.check_status()
-    assert eng.shaper.stats()["waited_s"] > 0.05            # the link did hold the selects back
+    assert eng.shaper.stats()["waited_s"] > 0.02            # the link did hold the selects back
     by_name = {n: p for n, p in model.named_parameters()}
     for rt, names in zip(eng.buckets, eng.param_names):
         for seg, name in zip(rt.bucket.layout.segments, names):
