@@ -87,7 +87,8 @@ def train_worker(local_rank: int, master_pid: int, local_world_size: int, args: 
         from stellatrain_b200.parallel.telemetry import TelemetryHook
 
         net._ensure_engine()
-        hook = TelemetryHook(net.engine, args.telemetry_uri, args.batch_size)
+        # under captured iterations every applied ratio change costs an eager iteration and a new capture
+        hook = TelemetryHook(net.engine, args.telemetry_uri, args.batch_size, ratio_min_interval=(48 if args.graph else 0))
     elif args.telemetry_uri:
         from stellatrain_b200.cpu_tier import CpuTierTelemetry
 
