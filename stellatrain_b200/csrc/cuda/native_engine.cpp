@@ -132,7 +132,12 @@ struct NativeEngine::Impl {
       const uint32_t off = b.spec.seg_off[pr.seg], numel = b.spec.seg_numel[pr.seg];
       if (!g.defined() || g.scalar_type() != at::kFloat || g.strides() != param.strides() ||
           (reinterpret_cast<uintptr_t>(g.data_ptr()) & 15u)) {
-        // not the parameter's layout, or not aligned for 16-byte loads: through the flat buffer
+        // not the parameter's layout, or not aligned for 16-byte loads: through the flat buffer, which the previous
+        // iteration's select may still have to read (see bucket_ready)
+        if (!capturing && b.select_done_set) {
+          c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+          check(cudaStreamWaitEvent(c10::cuda::getCurrentCUDAStream((c10::DeviceIndex)device).stream(), b.select_done, 0));
+        }
         at::Tensor flat = b.flat_grad.narrow(0, off, numel).as_strided(param.sizes(), param.strides());
         if (g.defined()) flat.copy_(g); else flat.zero_();
         g = flat;

@@ -505,6 +505,8 @@ class SparseDPEngine:
         g = p.grad
         if g.dtype != torch.float32 or g.stride() != p.stride() or (g.data_ptr() & 15):
             flat = rt.bucket.grad[seg.off : seg.off + seg.numel].as_strided(p.shape, p.stride())
+            if not self._capturing and rt.select_done is not None:
+                torch.cuda.current_stream(self.device).wait_event(rt.select_done)   # a late select may still read this
             flat.copy_(g)
             g = flat
         self._table_row(rt)[si] = g.data_ptr()
