@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 
@@ -43,6 +44,15 @@ def report(build: bool = False) -> dict:
 
         ext = cpu_tier._load()
         out["cpu_simd"] = ext.best_isa()
+        # the reference's transports (ZeroMQ sockets, protobuf messages) are options that need a libzmq at run time
+        lib = os.environ.get("STELLATRAIN_LIBZMQ") or cpu_tier.bundled_libzmq()
+        try:
+            import zmq
+
+            pyzmq = zmq.__version__
+        except ImportError:
+            pyzmq = None
+        out["zeromq"] = {"pyzmq": pyzmq, "libzmq": lib or None}
     except Exception as e:  # noqa: BLE001
         out["cpu_tier_error"] = repr(e)
     return out
