@@ -508,3 +508,29 @@ def test_controller_in_a_process_of_its_own_serves_clients_and_terminates():
     finally:
         if proc.poll() is None:
             proc.kill()
+
+
+def test_single_instance_guard_leaves_other_processes_alone(tmp_path):
+    """The pid file of a controller that is long gone may name a process id that belongs to somebody else by now: the
+    guard only ends a process that still is a controller."""
+    import subprocess
+    import sys
+
+    from stellatrain_b200.control import controller as C
+
+    port = 59999
+    pid_file = f"/tmp/stellatrain-b200-controller-{port}.pid"
+    bystander = subprocess.Popen([sys.executable, "-c", "import time; time.sleep(30)"])
+    try:
+        with open(pid_file, "w") as f:
+            f.write(str(bystander.pid))
+        C._single_instance(port)
+        time.sleep(0.3)
+        assert bystander.poll() is None                       # still running
+        assert int(open(pid_file).read()) == os.getpid()      # the file names the new owner
+    finally:
+        bystander.kill()
+        try:
+            os.unlink(pid_file)
+        except OSError:
+            pass
