@@ -148,12 +148,18 @@ class Controller:
             conn.close()
 
     def _choose_profile(self) -> None:
-        """Called with the lock held, whenever a client or the job description arrives."""
+        """Called with the lock held, whenever a client or the job description arrives: the shipped profile for the
+        clients' kind of GPU and, once the job description is there, for a model of the job's size."""
         if self.profile_path:
             return
+        n_params = float(sum(self.global_init.param_counts)) if self.global_init is not None else None
         for c in self.clients.values():
-            chosen = load_profile(None, c.gpu_name)
-            if isinstance(self.profile, AnalyticProfile) and not isinstance(chosen, AnalyticProfile):
+            want = (c.gpu_name, n_params)
+            if getattr(self, "_profile_for", None) == want:
+                return
+            chosen = load_profile(None, c.gpu_name, n_params)
+            if not isinstance(chosen, AnalyticProfile):
+                self._profile_for = want
                 self.profile = chosen
                 if self.optimizer is not None:
                     self.optimizer.profile = chosen

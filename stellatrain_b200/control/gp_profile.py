@@ -122,24 +122,32 @@ class AnalyticProfile:
         return batch_term + bw_term
 
 
-# Profiles that ship with the package, by a substring of the device name a client reports.
-SHIPPED_PROFILES = {"B200": "b200_gpt2_small.json"}
+# Profiles that ship with the package, by a substring of the device name a client reports: (file, parameters of the
+# model it was taken for).  The reference ships one profile per model too (bayesian/profile/*.pkl).
+SHIPPED_PROFILES = {"B200": [("b200_gpt2_small.json", 124.4e6), ("b200_resnet152.json", 58.3e6)]}
 
 
-def shipped_profile_path(gpu_name: Optional[str]) -> Optional[Path]:
-    """The fitted profile that ships for this kind of GPU (``sweep_profile.py`` produced it), or None."""
-    for needle, fname in SHIPPED_PROFILES.items():
+def shipped_profile_path(gpu_name: Optional[str], n_params: Optional[float] = None) -> Optional[Path]:
+    """The fitted profile that ships for this kind of GPU (``sweep_profile.py`` produced it), or None.  Of several, the
+    one taken for the model closest in size (ratio of parameter counts); the first one while the size is unknown."""
+    import math
+
+    for needle, entries in SHIPPED_PROFILES.items():
         if gpu_name and needle in gpu_name:
-            path = Path(__file__).parent / "profiles" / fname
-            if path.exists():
-                return path
+            present = [(f, n) for f, n in entries if (Path(__file__).parent / "profiles" / f).exists()]
+            if not present:
+                return None
+            if n_params and n_params > 0:
+                present.sort(key=lambda e: abs(math.log(e[1] / float(n_params))))
+            return Path(__file__).parent / "profiles" / present[0][0]
     return None
 
 
-def load_profile(path: Optional[str], gpu_name: Optional[str] = None):
-    """``path`` (or, without one, the profile that ships for ``gpu_name``; the analytic surrogate when there is none)."""
+def load_profile(path: Optional[str], gpu_name: Optional[str] = None, n_params: Optional[float] = None):
+    """``path`` (or, without one, the profile that ships for ``gpu_name`` and a model of ``n_params`` parameters; the
+    analytic surrogate when there is none)."""
     if not path:
-        shipped = shipped_profile_path(gpu_name)
+        shipped = shipped_profile_path(gpu_name, n_params)
         if shipped is None:
             return AnalyticProfile()
         return GPProfile.load(shipped)

@@ -137,6 +137,11 @@ def test_shipped_b200_profile_changes_the_choice_where_the_sweep_says_so():
     assert isinstance(load_profile(None, "NVIDIA GeForce RTX 2080 Ti"), AnalyticProfile)
     shipped = load_profile(None, "NVIDIA B200")
     assert isinstance(shipped, GPProfile) and shipped.meta.bandwidth == 1.0 and 0.9 < shipped.meta.compression < 0.99
+    # one profile per model, as the reference ships them: the one taken for the model closest in size is chosen
+    assert shipped_profile_path("NVIDIA B200").name == "b200_gpt2_small.json"
+    assert shipped_profile_path("NVIDIA B200", 60e6).name == "b200_resnet152.json"
+    assert shipped_profile_path("NVIDIA B200", 110e6).name == "b200_gpt2_small.json"
+    assert "resnet152" in load_profile(None, "NVIDIA B200", 25e6).meta.model
     # the fit follows the sweep it was made from (its rows are inside the file); it smooths the sweep's noise
     import json
 
