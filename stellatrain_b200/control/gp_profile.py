@@ -124,12 +124,15 @@ class AnalyticProfile:
 
 # Profiles that ship with the package, by a substring of the device name a client reports: (file, parameters of the
 # model it was taken for).  The reference ships one profile per model too (bayesian/profile/*.pkl).
-SHIPPED_PROFILES = {"B200": [("b200_gpt2_small.json", 124.4e6), ("b200_resnet152.json", 58.3e6)]}
+SHIPPED_PROFILES = {"B200": [("b200_gpt2_small.json", 124.4e6), ("b200_resnet152.json", 58.3e6), ("b200_resnet50.json", 23.7e6),
+                             ("b200_vitb16.json", 85.9e6), ("b200_swinb.json", 87.0e6)]}
 
 
 def shipped_profile_path(gpu_name: Optional[str], n_params: Optional[float] = None) -> Optional[Path]:
     """The fitted profile that ships for this kind of GPU (``sweep_profile.py`` produced it), or None.  Of several, the
-    one taken for the model closest in size (ratio of parameter counts); the first one while the size is unknown."""
+    one taken for the model closest in size (ratio of parameter counts); the first one while the size is unknown.
+    Models of nearly the same size (ViT-B/16 and Swin-B) cannot be told apart this way: name the profile then
+    (``--profile`` / ``MODEL_PROFILE``, as the reference requires for every run)."""
     import math
 
     for needle, entries in SHIPPED_PROFILES.items():
