@@ -141,7 +141,7 @@ def test_shipped_b200_profile_changes_the_choice_where_the_sweep_says_so():
     assert shipped_profile_path("NVIDIA B200").name == "b200_gpt2_small.json"
     assert shipped_profile_path("NVIDIA B200", 60e6).name == "b200_resnet152.json"
     assert shipped_profile_path("NVIDIA B200", 110e6).name == "b200_gpt2_small.json"
-    assert "resnet152" in load_profile(None, "NVIDIA B200", 25e6).meta.model
+    assert "resnet50" in load_profile(None, "NVIDIA B200", 25e6).meta.model
     # the fit follows the sweep it was made from (its rows are inside the file); it smooths the sweep's noise
     import json
 
